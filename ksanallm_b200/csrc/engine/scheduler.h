@@ -1,0 +1,163 @@
+// Continuous-batching scheduler: owns the sequences and their KV blocks and turns the request
+// queues into one StepPlan per engine step.
+//
+// The per-step passes and thresholds follow the reference strategy
+// (src/ksana_llm/batch_scheduler/strategy/continuous_batching.cpp:28-841,
+//  src/ksana_llm/batch_scheduler/batch_scheduler.cpp:53-158): admission limits, waiting timeout,
+// abort, running -> swapped -> waiting priority, swap-out / swap-in / launch block thresholds,
+// SWAP or RECOMPUTE preemption of the most recently admitted request, split-fuse chunked prefill.
+// Differences that come from the block design (see cache_manager.h): swaps are executed on the
+// compute stream at the start of the step that decided them, so there are no pending-swap queues;
+// sibling sequences (parallel sampling, beams) fork from one prefill instead of each running its own.
+#pragma once
+#include <cstdint>
+#include <deque>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "cache_manager.h"
+#include "common.h"
+
+namespace ksana {
+
+struct SchedulerConfig {
+  int schedule_strategy = 0;            // 0 continuous batching, 1 auto (static) batching
+  int64_t waiting_timeout_in_ms = 600000;
+  int max_waiting_queue_len = 256;
+  int max_step_tokens = 4096;
+  int max_batch_size = 8;
+  int max_token_len = 2048;
+  float swapout_block_threshold = 1.0f;
+  float swapin_block_threshold = 2.0f;
+  float launch_block_threshold = 2.0f;
+  int preempt_mode = 0;                 // 0 SWAP, 1 RECOMPUTE
+  int split_fuse_token_num = 0;
+  int min_flexible_cache_num = 0;
+  bool enable_prefix_cache = false;
+  int block_token_num = 16;
+  int auto_batch_wait_ms = 100;
+  std::vector<int> eos_token_ids;
+};
+
+enum class SeqState : int { WAITING = 0, RUNNING = 1, SWAPPED = 2, FINISHED = 3 };
+
+struct Sequence {
+  int64_t seq_id = 0;
+  int64_t req_id = 0;
+  int index = 0;                 // position inside its request group
+  std::vector<int> tokens;       // prompt + generated
+  int prompt_len = 0;
+  int kv_cached = 0;             // tokens whose K/V is in the cache
+  int chunk = 0;                 // tokens forwarded in the step being planned / executed
+  int promoted = 0;              // blocks entered into the prefix tree
+  int prefix_hit_tokens = 0;
+  int flexible_hit_tokens = 0;
+  int sampled = 0;               // tokens sampled so far (RNG counter)
+  std::vector<int> blocks;
+  std::vector<int> host_blocks;
+  std::shared_ptr<SamplingConfig> cfg;
+  int64_t arrive_ms = 0;
+  int64_t first_token_ms = 0;
+  bool aborted = false;
+  bool forked_pending = false;   // sibling that waits for its leader's prefill
+  int64_t leader = -1;
+  SeqState state = SeqState::WAITING;
+  Status finish_status;
+  int preempt_count = 0;
+};
+
+struct SeqEvent {                // what PostStep / Schedule report back to the runtime
+  int64_t seq_id; int64_t req_id; int index;
+  int new_token;                 // -1: none
+  bool finished; int code; std::string message;
+};
+
+struct StepPlan {
+  std::vector<int64_t> seq_ids;            // multi-token sequences first, then single-token ones
+  std::vector<int> q_lens, kv_lens;
+  std::vector<int> input_ids, positions, slots, cu_q;
+  std::vector<int> block_table; int max_blocks = 0;
+  std::vector<int64_t> sample_seq_ids;     // sequences that sample this step ...
+  std::vector<int> sample_rows;            // ... and the token row whose logits they use
+  std::vector<SwapCopy> swap_out, swap_in;
+  std::vector<BlockCopy> copies;
+  int num_multi = 0, num_single = 0, num_tokens = 0, num_multi_tokens = 0, max_q_len = 0;
+  std::vector<SeqEvent> events;            // timeouts / aborts / rejections decided while planning
+  bool empty() const { return seq_ids.empty(); }
+  void Clear() { *this = StepPlan(); }
+  // Flat int32 image (header + arrays) used for the single host->device upload and for
+  // broadcasting the step to the other ranks / nodes.
+  std::vector<int32_t> Pack() const;
+  static bool Unpack(const int32_t* data, size_t n, StepPlan* out);
+};
+
+struct SampledToken {
+  int token;
+  int64_t parent_seq = -1;       // beam search: take this sibling's history before appending
+};
+
+struct SchedulerStats {
+  int64_t waiting = 0, running = 0, swapped = 0;
+  int64_t free_blocks = 0, used_blocks = 0, usable_blocks = 0, free_host_blocks = 0;
+  int64_t total_requests = 0, finished = 0, timeouts = 0, aborted = 0, rejected = 0;
+  int64_t preempt_swap = 0, preempt_recompute = 0, swap_in = 0, steps = 0;
+  int64_t step_tokens = 0, input_tokens = 0, output_tokens = 0;
+  CacheStats cache;
+};
+
+class Scheduler {
+ public:
+  Scheduler(const SchedulerConfig& cfg, int num_device_blocks, int num_host_blocks);
+
+  // Creates max(num_beams, num_return_sequences, 1) sequences for one request. Returns their ids.
+  Status AddRequest(int64_t req_id, const std::vector<int>& prompt, const SamplingConfig& cfg,
+                    std::vector<int64_t>* seq_ids);
+  void Abort(int64_t req_id);
+  bool Idle();
+
+  // Plans the next step. Returns false when there is nothing to run (plan->events may still carry
+  // timeouts / aborts).
+  bool Schedule(StepPlan* plan);
+  // Consumes the step's sampled tokens (one per plan.sample_seq_ids entry, same order).
+  void PostStep(const StepPlan& plan, const std::vector<SampledToken>& sampled, std::vector<SeqEvent>* events);
+
+  // Runtime hooks: stop strings and structured output need the tokenizer, which lives outside.
+  void FinishSequence(int64_t seq_id, int keep_tokens, int code, const std::string& message,
+                      std::vector<SeqEvent>* events);
+  bool ReplaceGenerated(int64_t seq_id, const std::vector<int>& generated);
+  std::vector<int> GetTokens(int64_t seq_id);
+  int GetPromptLen(int64_t seq_id);
+
+  SchedulerStats GetStats();
+  bool CheckInvariants(std::string* why);
+  const SchedulerConfig& config() const { return cfg_; }
+
+ private:
+  using SeqPtr = std::shared_ptr<Sequence>;
+  void MergeWaitingBuffer();
+  void FinishLocked(const SeqPtr& s, int code, const std::string& msg, int new_token, std::vector<SeqEvent>* ev);
+  void ExpireAndAbort(int64_t now, std::vector<SeqEvent>* ev);
+  void PreemptLocked(const SeqPtr& victim, StepPlan* plan);
+  int BlocksNeeded(const Sequence& s) const;
+  bool CheckFinishLocked(const SeqPtr& s, int token, std::vector<SeqEvent>* ev);
+  void EmitSequence(const SeqPtr& s, StepPlan* plan);
+  int StepTokenCap(int num_decodes) const;
+
+  SchedulerConfig cfg_;
+  CacheManager cache_;
+  std::mutex mu_;
+  std::deque<SeqPtr> waiting_buffer_, waiting_;
+  std::vector<SeqPtr> running_;
+  std::deque<SeqPtr> swapped_;
+  std::unordered_map<int64_t, SeqPtr> by_id_;
+  std::unordered_map<int64_t, std::vector<SeqPtr>> groups_;
+  int64_t next_seq_id_ = 1;
+  bool split_fuse_on_;
+  std::vector<BlockCopy> pending_copies_;   // fork copies decided in PostStep, executed by the next step
+  SchedulerStats stats_;
+};
+
+}  // namespace ksana

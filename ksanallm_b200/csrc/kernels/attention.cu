@@ -1,0 +1,510 @@
+// Paged attention for sm_100a: causal prefill (chunked-prefill and prefix-cache
+// aware) and split-KV decode, both reading K/V in place from the paged cache
+// through a block table.
+//
+// Grouped-query packing: the query heads that share one KV head are packed into
+// the M dimension of the tensor-core tiles together with the query tokens, so a
+// K/V tile staged in shared memory is used by the whole head group (8 heads for
+// Llama-3 / Qwen2 70B) instead of being re-read per query head.
+//
+//   virtual row r of (sequence s, kv head g):  token = r / G,  head = g*G + r % G
+//
+// Prefill: 64 rows per CTA (4 warps x 16), K/V tiles of 64 tokens, online
+// softmax in fp32 (exp2), only the NEW query rows are computed: the causal
+// offset is kv_len - q_len, so cached prefixes cost no attention work.
+// Decode: one CTA per (kv head, sequence, split); the 4 warps walk disjoint
+// 16-token slices of each tile, partial (m, l, O) are merged in shared memory
+// and, when the sequence was split, by a small reduce kernel.
+//
+// FP8 (e4m3) caches are dequantised with a per-layer scale while staging tiles.
+//
+// Functional counterpart of the reference's decode kernels
+// (3rdparty/LLM_kernels/csrc/kernels/nvidia/paged_attention/paged_attention.cu:81-640)
+// and of its FlashAttention-2 call (src/ksana_llm/kernels/nvidia/kernel_wrapper.cpp:437-588),
+// without the reverse cache copy the latter needs.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace ksana {
+
+typedef __nv_bfloat16 bf16;
+constexpr int kTileTok = 64;     // KV tokens per shared-memory tile
+constexpr int kAttnThreads = 128;
+
+struct AttnParams {
+  const bf16* q; long long q_stride;     // [T, q_stride] ; head h at column h*D
+  bf16* out; long long out_stride;       // [T, out_stride]
+  const void* cache;                     // layer base: [block][2][Hkv][block_tokens][D]
+  long long block_stride;                // elements between blocks
+  int block_tokens;
+  const int* block_table; int table_stride;   // [B][table_stride]
+  const int* cu_q;                       // [B+1] query row offsets (prefill) or null (decode: row = s)
+  const int* kv_lens;                    // [B]
+  const float* alibi;                    // [Hq] slopes or null
+  int Hq, Hkv;
+  float scale_log2;                      // softmax scale * log2(e)
+  float k_scale, v_scale;                // fp8 cache dequant scales
+  // decode split workspace
+  float* part_o; float* part_ml; int num_splits;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Shared tile: `rows` rows of D bf16; 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
+template <int D>
+__device__ __forceinline__ bf16* tile_ptr(bf16* base, int r, int chunk) {
+  return base + r * D + ((chunk ^ (r & 7)) << 3);
+}
+
+// Stage one K or V tile (kTileTok tokens x D) of kv head g into shared memory.
+template <int D, bool FP8>
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const AttnParams& p, const int* table, int g, int which,
+                                             int tok0, int kv_len, float dq) {
+  constexpr int CH = D / 8;
+  for (int i = threadIdx.x; i < kTileTok * CH; i += kAttnThreads) {
+    const int r = i / CH, c = i % CH;
+    const int tok = tok0 + r;
+    bf16* d = tile_ptr<D>(dst, r, c);
+    if (tok < kv_len) {
+      const int blk = table[tok / p.block_tokens];
+      const size_t off = static_cast<size_t>(blk) * p.block_stride +
+                         ((static_cast<size_t>(which) * p.Hkv + g) * p.block_tokens + tok % p.block_tokens) * D + c * 8;
+      if (FP8) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.cache) + off);
+        const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __half_raw h0 = __nv_cvt_fp8_to_halfraw(b[2 * e], __NV_E4M3);
+          const __half_raw h1 = __nv_cvt_fp8_to_halfraw(b[2 * e + 1], __NV_E4M3);
+          ow[e] = pack_bf16(__half2float(__half(h0)) * dq, __half2float(__half(h1)) * dq);
+        }
+        *reinterpret_cast<uint4*>(d) = o;
+      } else {
+        cp_async16(d, static_cast<const bf16*>(p.cache) + off);
+      }
+    } else {
+      *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+// One warp: S(16 x NT*8 tokens) = Q(16 x D) K^T over tokens [t0, t0 + NT*8) of the staged tile.
+template <int D, int NT>
+__device__ __forceinline__ void warp_qk(float (&s)[NT][4], const uint32_t (&qf)[D / 16][4], bf16* ks, int t0, int lane) {
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+    for (int jp = 0; jp < NT / 2; ++jp) {
+      uint32_t b[4];
+      const int r = t0 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int c = kk * 2 + ((lane >> 3) & 1);
+      ldsm_x4(b, smem_addr(tile_ptr<D>(ks, r, c)));
+      mma16816(s[2 * jp], qf[kk], b[0], b[1]);
+      mma16816(s[2 * jp + 1], qf[kk], b[2], b[3]);
+    }
+  }
+}
+
+// One warp: O(16 x D) += P(16 x NT*8) V over tokens [t0, t0 + NT*8).
+template <int D, int NT>
+__device__ __forceinline__ void warp_pv(float (&o)[D / 8][4], const float (&s)[NT][4], bf16* vs, int t0, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {
+      uint32_t b[4];
+      const int r = t0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      const int c = np * 2 + (lane >> 4);
+      ldsm_x4_t(b, smem_addr(tile_ptr<D>(vs, r, c)));
+      mma16816(o[2 * np], a, b[0], b[1]);
+      mma16816(o[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Mask + online-softmax update for one warp's 16 x (NT*8) score tile.
+// Rows lane/4 and lane/4+8; limit[i] = last visible kv position of that row (-1 = row inactive).
+template <int D, int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
+                                               const int (&limit)[2], const float (&slope)[2], int tok0, int lane,
+                                               float scale_log2) {
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = e >> 1;
+      const int tok = tok0 + j * 8 + (lane & 3) * 2 + (e & 1);
+      float v = s[j][e] * scale_log2;
+      if (slope[i] != 0.f) v += slope[i] * 1.44269504f * static_cast<float>(tok - limit[i]);
+      v = tok <= limit[i] ? v : -INFINITY;
+      s[j][e] = v;
+      mx[i] = fmaxf(mx[i], v);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+  }
+  float corr[2], mnew[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mnew[i] = fmaxf(m[i], mx[i]);
+    corr[i] = (mnew[i] == -INFINITY) ? 1.f : exp2f(m[i] - mnew[i]);
+    m[i] = mnew[i];
+    l[i] *= corr[i];
+  }
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = e >> 1;
+      const float pv = (mnew[i] == -INFINITY) ? 0.f : exp2f(s[j][e] - mnew[i]);
+      s[j][e] = pv;
+      l[i] += pv;   // per-thread partial; reduced over the 4 lanes of a row at the end
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- prefill
+template <int D, bool FP8>
+__global__ void __launch_bounds__(kAttnThreads)
+paged_prefill_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem_attn[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_attn);            // 64 x D
+  bf16* ks = qs + 64 * D;                                   // 2 x (64 x D)
+  bf16* vs = ks + 2 * kTileTok * D;                         // 2 x (64 x D)
+
+  const int s = blockIdx.z, g = blockIdx.y;
+  const int G = p.Hq / p.Hkv;
+  const int q0 = p.cu_q[s], q_len = p.cu_q[s + 1] - q0;
+  const int kv_len = p.kv_lens[s];
+  const int row0 = blockIdx.x * 64;
+  if (row0 >= q_len * G) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* table = p.block_table + static_cast<size_t>(s) * p.table_stride;
+  const int past = kv_len - q_len;   // tokens already in the cache before this chunk
+
+  // stage Q rows (zero for rows beyond the sequence)
+  constexpr int CH = D / 8;
+  for (int i = threadIdx.x; i < 64 * CH; i += kAttnThreads) {
+    const int r = i / CH, c = i % CH;
+    const int vr = row0 + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (vr < q_len * G) {
+      const int tok = vr / G, head = g * G + vr % G;
+      v = *reinterpret_cast<const uint4*>(p.q + static_cast<size_t>(q0 + tok) * p.q_stride + head * D + c * 8);
+    }
+    *reinterpret_cast<uint4*>(tile_ptr<D>(qs, r, c)) = v;
+  }
+  // causal bound of this CTA's rows
+  const int last_row = min(row0 + 63, q_len * G - 1);
+  const int kv_end = min(kv_len, past + last_row / G + 1);
+  const int ntiles = (kv_end + kTileTok - 1) / kTileTok;
+
+  load_kv_tile<D, FP8>(ks, p, table, g, 0, 0, kv_len, p.k_scale);
+  load_kv_tile<D, FP8>(vs, p, table, g, 1, 0, kv_len, p.v_scale);
+  cp_commit();
+  __syncthreads();
+
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int r = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int c = kk * 2 + (lane >> 4);
+    ldsm_x4(qf[kk], smem_addr(tile_ptr<D>(qs, r, c)));
+  }
+  int limit[2]; float slope[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int vr = row0 + warp * 16 + (lane >> 2) + i * 8;
+    limit[i] = vr < q_len * G ? past + vr / G : -1;
+    slope[i] = (p.alibi && vr < q_len * G) ? p.alibi[g * G + vr % G] : 0.f;
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < ntiles) {
+      load_kv_tile<D, FP8>(ks + (buf ^ 1) * kTileTok * D, p, table, g, 0, (t + 1) * kTileTok, kv_len, p.k_scale);
+      load_kv_tile<D, FP8>(vs + (buf ^ 1) * kTileTok * D, p, table, g, 1, (t + 1) * kTileTok, kv_len, p.v_scale);
+      cp_commit();
+      cp_wait<1>();
+    } else {
+      cp_wait<0>();
+    }
+    __syncthreads();
+    float sc[8][4];
+    warp_qk<D, 8>(sc, qf, ks + buf * kTileTok * D, 0, lane);
+    softmax_update<D, 8>(sc, o, m, l, limit, slope, t * kTileTok, lane, p.scale_log2);
+    warp_pv<D, 8>(o, sc, vs + buf * kTileTok * D, 0, lane);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int vr = row0 + warp * 16 + (lane >> 2) + i * 8;
+    if (vr >= q_len * G) continue;
+    const int tok = vr / G, head = g * G + vr % G;
+    const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+    bf16* dst = p.out + static_cast<size_t>(q0 + tok) * p.out_stride + head * D + (lane & 3) * 2;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ decode
+// grid (Hkv, B, splits). Rows = the G query heads of kv head g (G <= 16), one new token each.
+template <int D, bool FP8>
+__global__ void __launch_bounds__(kAttnThreads)
+paged_decode_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem_attn[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_attn);            // 16 x D
+  bf16* ks = qs + 16 * D;                                   // 2 x (64 x D)
+  bf16* vs = ks + 2 * kTileTok * D;
+  float* merge = reinterpret_cast<float*>(vs + 2 * kTileTok * D);   // 4 warps x 16 rows x (D + 2)
+
+  const int g = blockIdx.x, s = blockIdx.y, split = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int kv_len = p.kv_lens[s];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* table = p.block_table + static_cast<size_t>(s) * p.table_stride;
+  const int total_tiles = (kv_len + kTileTok - 1) / kTileTok;
+  const int tiles_per = (total_tiles + p.num_splits - 1) / p.num_splits;
+  const int t_begin = split * tiles_per, t_end = min(total_tiles, t_begin + tiles_per);
+
+  constexpr int CH = D / 8;
+  for (int i = threadIdx.x; i < 16 * CH; i += kAttnThreads) {
+    const int r = i / CH, c = i % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G) v = *reinterpret_cast<const uint4*>(p.q + static_cast<size_t>(s) * p.q_stride + (g * G + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(tile_ptr<D>(qs, r, c)) = v;
+  }
+  if (t_begin < t_end) {
+    load_kv_tile<D, FP8>(ks, p, table, g, 0, t_begin * kTileTok, kv_len, p.k_scale);
+    load_kv_tile<D, FP8>(vs, p, table, g, 1, t_begin * kTileTok, kv_len, p.v_scale);
+  }
+  cp_commit();
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int r = (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int c = kk * 2 + (lane >> 4);
+    ldsm_x4(qf[kk], smem_addr(tile_ptr<D>(qs, r, c)));
+  }
+  int limit[2]; float slope[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (lane >> 2) + i * 8;
+    limit[i] = r < G ? kv_len - 1 : -1;
+    slope[i] = (p.alibi && r < G) ? p.alibi[g * G + r] : 0.f;
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  for (int t = t_begin; t < t_end; ++t) {
+    const int buf = (t - t_begin) & 1;
+    if (t + 1 < t_end) {
+      load_kv_tile<D, FP8>(ks + (buf ^ 1) * kTileTok * D, p, table, g, 0, (t + 1) * kTileTok, kv_len, p.k_scale);
+      load_kv_tile<D, FP8>(vs + (buf ^ 1) * kTileTok * D, p, table, g, 1, (t + 1) * kTileTok, kv_len, p.v_scale);
+      cp_commit();
+      cp_wait<1>();
+    } else {
+      cp_wait<0>();
+    }
+    __syncthreads();
+    float sc[2][4];
+    warp_qk<D, 2>(sc, qf, ks + buf * kTileTok * D, warp * 16, lane);
+    softmax_update<D, 2>(sc, o, m, l, limit, slope, t * kTileTok + warp * 16, lane, p.scale_log2);
+    warp_pv<D, 2>(o, sc, vs + buf * kTileTok * D, warp * 16, lane);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  // merge the 4 warps' streams: stage (m, l, O) per warp, then every thread combines a slice
+  constexpr int MS = D + 2;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = (lane >> 2) + i * 8;
+    float* dst = merge + (warp * 16 + r) * MS;
+    if ((lane & 3) == 0) { dst[D] = m[i]; dst[D + 1] = l[i]; }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      dst[n * 8 + (lane & 3) * 2] = o[n][2 * i];
+      dst[n * 8 + (lane & 3) * 2 + 1] = o[n][2 * i + 1];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += kAttnThreads) {
+    const int r = i / D, d = i % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[(w * 16 + r) * MS + D]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float* src = merge + (w * 16 + r) * MS;
+      const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - mm);
+      acc += src[d] * f;
+      ll += src[D + 1] * f;
+    }
+    const int head = g * G + r;
+    if (p.num_splits == 1) {
+      p.out[static_cast<size_t>(s) * p.out_stride + head * D + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+    } else {
+      const size_t base = (static_cast<size_t>(s) * p.Hq + head) * p.num_splits + split;
+      p.part_o[base * D + d] = acc;
+      if (d == 0) { p.part_ml[base * 2] = mm; p.part_ml[base * 2 + 1] = ll; }
+    }
+  }
+}
+
+// grid (Hq, B): combine the per-split partials.
+template <int D>
+__global__ void decode_reduce_kernel(const AttnParams p) {
+  const int head = blockIdx.x, s = blockIdx.y;
+  const size_t base = (static_cast<size_t>(s) * p.Hq + head) * p.num_splits;
+  float mm = -INFINITY;
+  for (int k = 0; k < p.num_splits; ++k) mm = fmaxf(mm, p.part_ml[(base + k) * 2]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f, ll = 0.f;
+    for (int k = 0; k < p.num_splits; ++k) {
+      const float mk = p.part_ml[(base + k) * 2];
+      const float f = (mk == -INFINITY) ? 0.f : exp2f(mk - mm);
+      acc += p.part_o[(base + k) * D + d] * f;
+      ll += p.part_ml[(base + k) * 2 + 1] * f;
+    }
+    p.out[static_cast<size_t>(s) * p.out_stride + head * D + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+  }
+}
+
+template <int D, bool FP8>
+static int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_t st) {
+  const int smem = (64 + 4 * kTileTok) * D * 2;
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(paged_prefill_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess) return -3;
+    set = true;
+  }
+  const int G = p.Hq / p.Hkv;
+  dim3 grid((max_q_len * G + 63) / 64, p.Hkv, B);
+  paged_prefill_kernel<D, FP8><<<grid, kAttnThreads, smem, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+template <int D, bool FP8>
+static int launch_decode(const AttnParams& p, int B, cudaStream_t st) {
+  const int smem = (16 + 4 * kTileTok) * D * 2 + 4 * 16 * (D + 2) * 4;
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(paged_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess) return -3;
+    set = true;
+  }
+  dim3 grid(p.Hkv, B, p.num_splits);
+  paged_decode_kernel<D, FP8><<<grid, kAttnThreads, smem, st>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  if (p.num_splits > 1) {
+    decode_reduce_kernel<D><<<dim3(p.Hq, B), D < 128 ? 64 : 128, 0, st>>>(p);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+  }
+  return 0;
+}
+
+}  // namespace ksana
+
+using namespace ksana;
+
+// Causal attention of new query rows against the paged cache (which already holds their K/V).
+extern "C" int ksana_paged_prefill(const void* q, long long q_stride, void* out, long long out_stride,
+                                   const void* cache, long long block_stride, int block_tokens, const int* block_table,
+                                   int table_stride, const int* cu_q, const int* kv_lens, const float* alibi, int B,
+                                   int max_q_len, int Hq, int Hkv, int D, float scale, int cache_fp8, float k_scale,
+                                   float v_scale, cudaStream_t st) {
+  if (B <= 0 || max_q_len <= 0) return 0;
+  if (Hq % Hkv) return -10;
+  AttnParams p{};
+  p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.out_stride = out_stride;
+  p.cache = cache; p.block_stride = block_stride; p.block_tokens = block_tokens;
+  p.block_table = block_table; p.table_stride = table_stride; p.cu_q = cu_q; p.kv_lens = kv_lens; p.alibi = alibi;
+  p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.44269504f; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.num_splits = 1;
+  if (D == 128) return cache_fp8 ? launch_prefill<128, true>(p, B, max_q_len, st) : launch_prefill<128, false>(p, B, max_q_len, st);
+  if (D == 64) return cache_fp8 ? launch_prefill<64, true>(p, B, max_q_len, st) : launch_prefill<64, false>(p, B, max_q_len, st);
+  return -11;
+}
+
+// One new token per sequence. workspace: part_o [B*Hq*splits*D] fp32, part_ml [B*Hq*splits*2] fp32 (splits > 1).
+extern "C" int ksana_paged_decode(const void* q, long long q_stride, void* out, long long out_stride,
+                                  const void* cache, long long block_stride, int block_tokens, const int* block_table,
+                                  int table_stride, const int* kv_lens, const float* alibi, int B, int Hq, int Hkv,
+                                  int D, float scale, int cache_fp8, float k_scale, float v_scale, int num_splits,
+                                  float* part_o, float* part_ml, cudaStream_t st) {
+  if (B <= 0) return 0;
+  if (Hq % Hkv || Hq / Hkv > 16) return -10;
+  if (num_splits < 1) num_splits = 1;
+  if (num_splits > 1 && (!part_o || !part_ml)) return -12;
+  AttnParams p{};
+  p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.out_stride = out_stride;
+  p.cache = cache; p.block_stride = block_stride; p.block_tokens = block_tokens;
+  p.block_table = block_table; p.table_stride = table_stride; p.cu_q = nullptr; p.kv_lens = kv_lens; p.alibi = alibi;
+  p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.44269504f; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml;
+  if (D == 128) return cache_fp8 ? launch_decode<128, true>(p, B, st) : launch_decode<128, false>(p, B, st);
+  if (D == 64) return cache_fp8 ? launch_decode<64, true>(p, B, st) : launch_decode<64, false>(p, B, st);
+  return -11;
+}

@@ -1,0 +1,519 @@
+// Memory-bound fused ops for sm_100a. Each kernel moves 16-byte vectors, touches
+// every activation byte once, and can emit the next GEMM's FP8 operand
+// (e4m3 values + one fp32 scale per 128 consecutive elements) directly, so that
+// no stand-alone quantisation pass reads the activation again.
+//
+// Covers the reference kernels
+//   layernorm  : 3rdparty/LLM_kernels/csrc/kernels/nvidia/layernorm/layernorm.cu:378-587
+//   add        : .../add/add.cu:55-90
+//   activation : .../activation/activation.cu:205-232,497-507
+//   embedding  : .../embedding/embedding.cu:20-75
+//   assemble   : .../assemble_last_token/assemble_last_token.cu:14-42
+//   rotary     : .../rotary_embedding/rotary_embedding.cu:70-197
+//   cache copy : .../paged_attention/cache_copy.cu:21-254
+//   fp8 quant  : 3rdparty/LLM_kernels/csrc/utils/nvidia/cuda_fp8_utils.cu:27-140
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace ksana {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+// 8 floats -> 8 e4m3 bytes (two 32-bit words)
+__device__ __forceinline__ uint2 pack8_e4m3(const float (&f)[8], float inv_scale) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+        make_float2(f[4 * h] * inv_scale, f[4 * h + 1] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+        make_float2(f[4 * h + 2] * inv_scale, f[4 * h + 3] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+    w[h] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+  }
+  return make_uint2(w[0], w[1]);
+}
+// amax over the 16 lanes that share one 128-element group (8 elements per lane)
+__device__ __forceinline__ float group16_max(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+constexpr float kE4m3Max = 448.f;
+
+// ----------------------------------------------------------------------------
+// (residual +=) x ; y = norm(residual or x) * w (+ beta) ; optional fp8 copy of y.
+// mode 0 = RMSNorm, 1 = LayerNorm. One CTA per row; up to kMaxVec vectors per thread.
+constexpr int kMaxVec = 4;
+
+template <int MODE>
+__global__ void norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf16* __restrict__ w,
+                            const bf16* __restrict__ beta, bf16* __restrict__ y, uint8_t* __restrict__ yq,
+                            float* __restrict__ yscale, int scale_ld, int H, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int nvec = H >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
+  uint4* rr = residual ? reinterpret_cast<uint4*>(residual + static_cast<size_t>(row) * H) : nullptr;
+  float v[kMaxVec][8];
+  float s = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < kMaxVec; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < nvec) {
+      unpack8(xr[i], v[j]);
+      if (rr) {
+        float r[8];
+        unpack8(rr[i], r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j][e] += r[e];
+        const uint4 packed = pack8(v[j]);
+        rr[i] = packed;
+        unpack8(packed, v[j]);   // normalise exactly what the residual stream now holds
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { s += v[j][e]; s2 += v[j][e] * v[j][e]; }
+    }
+  }
+  float mean = 0.f, rstd;
+  if (MODE == 1) {
+    mean = block_sum(s, red) / H;
+    float var = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { const float d = v[j][e] - mean; var += d * d; }
+      }
+    }
+    rstd = rsqrtf(block_sum(var, red) / H + eps);
+  } else {
+    rstd = rsqrtf(block_sum(s2, red) / H + eps);
+  }
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const uint4* br = beta ? reinterpret_cast<const uint4*>(beta) : nullptr;
+#pragma unroll
+  for (int j = 0; j < kMaxVec; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;   // blockDim is a multiple of 32, so groups of 16 lanes stay aligned
+    const bool on = i < nvec;
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = 0.f;
+    if (on) {
+      float wf[8];
+      unpack8(wr[i], wf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (v[j][e] - mean) * rstd * wf[e];
+      if (br) {
+        float bfv[8];
+        unpack8(br[i], bfv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += bfv[e];
+      }
+      // round to bf16 first so that the fp8 copy quantises the same values y holds
+      const uint4 packed = pack8(o);
+      if (y) reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * H)[i] = packed;
+      unpack8(packed, o);
+    }
+    if (yq) {
+      float am = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(o[e]));
+      am = group16_max(am);
+      const float scale = fmaxf(am, 1e-10f) / kE4m3Max;
+      if (on) {
+        reinterpret_cast<uint2*>(yq + static_cast<size_t>(row) * H)[i] = pack8_e4m3(o, 1.f / scale);
+        if ((i & 15) == 0) yscale[static_cast<size_t>(i >> 4) * scale_ld + row] = scale;
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// out[m, i] = act(gate_up[m, i]) * gate_up[m, I + i] ; optional fp8 copy. act: 0 silu 1 gelu(tanh) 2 relu
+// When `gated` is 0 the input is [M, I] and out = act(in).
+__device__ __forceinline__ float act_fn(float x, int act) {
+  if (act == 0) return x / (1.f + __expf(-x));
+  if (act == 1) return 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
+  return fmaxf(x, 0.f);
+}
+
+__global__ void act_mul_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, uint8_t* __restrict__ outq,
+                               float* __restrict__ oscale, int scale_ld, int M, int I, int in_ld, int act, int gated) {
+  const int nvec = I >> 3;
+  const long long total = static_cast<long long>(M) * nvec;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       idx < ((total + 31) / 32) * 32; idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const bool on = idx < total;
+    const int m = on ? static_cast<int>(idx / nvec) : 0;
+    const int i = on ? static_cast<int>(idx % nvec) : 0;
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = 0.f;
+    if (on) {
+      const uint4* row = reinterpret_cast<const uint4*>(in + static_cast<size_t>(m) * in_ld);
+      float g[8];
+      unpack8(row[i], g);
+      if (gated) {
+        float u[8];
+        unpack8(row[nvec + i], u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = act_fn(g[e], act) * u[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = act_fn(g[e], act);
+      }
+      const uint4 packed = pack8(o);
+      if (out) reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * I)[i] = packed;
+      unpack8(packed, o);
+    }
+    if (outq) {   // nvec is a multiple of 16 on this path, so 16 consecutive lanes share (m, group)
+      float am = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(o[e]));
+      am = group16_max(am);
+      const float scale = fmaxf(am, 1e-10f) / kE4m3Max;
+      if (on) {
+        reinterpret_cast<uint2*>(outq + static_cast<size_t>(m) * I)[i] = pack8_e4m3(o, 1.f / scale);
+        if ((i & 15) == 0) oscale[static_cast<size_t>(i >> 4) * scale_ld + m] = scale;
+      }
+    }
+  }
+}
+
+// x[M,K] bf16 -> e4m3 + one scale per (row, 128 columns); scales stored [K/128][scale_ld].
+__global__ void quant_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
+                                 int scale_ld, int M, int K, int x_ld) {
+  const int nvec = K >> 3;                                    // a multiple of 16
+  const long long total = static_cast<long long>(M) * nvec;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       idx < ((total + 31) / 32) * 32; idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const bool on = idx < total;                              // whole warps stay in the loop for the shuffles
+    const int m = on ? static_cast<int>(idx / nvec) : 0, i = on ? static_cast<int>(idx % nvec) : 0;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    if (on) unpack8(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * x_ld)[i], f);
+    float am = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(f[e]));
+    am = group16_max(am);
+    const float sc = fmaxf(am, 1e-10f) / kE4m3Max;
+    if (on) {
+      reinterpret_cast<uint2*>(q + static_cast<size_t>(m) * K)[i] = pack8_e4m3(f, 1.f / sc);
+      if ((i & 15) == 0) scale[static_cast<size_t>(i >> 4) * scale_ld + m] = sc;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Embedding gather with vocabulary-shard awareness; rows whose id falls outside
+// [vocab_lo, vocab_hi) are zero-filled (the TP all-reduce then completes them).
+// Optional learned position table add and scale (GPT-style models).
+__global__ void embedding_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
+                                 const int* __restrict__ positions, const bf16* __restrict__ pos_table,
+                                 bf16* __restrict__ out, int H, int vocab_lo, int vocab_hi, float scale) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool mine = id >= vocab_lo && id < vocab_hi;
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(mine ? id - vocab_lo : 0) * H);
+  const uint4* psrc = pos_table ? reinterpret_cast<const uint4*>(pos_table + static_cast<size_t>(positions[t]) * H)
+                                : nullptr;
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) {
+    float f[8];
+    if (mine) {
+      unpack8(src[i], f);
+      if (scale != 1.f) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= scale;
+      }
+      if (psrc) {
+        float pf[8];
+        unpack8(psrc[i], pf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += pf[e];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+    dst[i] = pack8(f);
+  }
+}
+
+// out[r, :] = in[idx[r], :]  (last-token assembly, logits gather)
+__global__ void gather_rows_kernel(const bf16* __restrict__ in, const int* __restrict__ idx, bf16* __restrict__ out,
+                                   int H) {
+  const uint4* src = reinterpret_cast<const uint4*>(in + static_cast<size_t>(idx[blockIdx.x]) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(blockIdx.x) * H);
+  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) dst[i] = src[i];
+}
+
+// rows[pos[r], :] = emb[r, :] (fp32 source): input-refit embeddings from plugins.
+__global__ void refit_rows_kernel(bf16* __restrict__ hidden, const int* __restrict__ pos, const float* __restrict__ emb,
+                                  int H) {
+  const float* src = emb + static_cast<size_t>(blockIdx.x) * H;
+  bf16* dst = hidden + static_cast<size_t>(pos[blockIdx.x]) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = __float2bfloat16(src[i]);
+}
+
+// ----------------------------------------------------------------------------
+// RoPE on q and k of the packed qkv activations + append of k, v to the paged
+// cache (optionally as fp8 with per-layer scales), one CTA per token.
+// qkv row layout: [Hq*D | Hkv*D | Hkv*D]. cos_sin: [max_pos][rot_dim] = cos(rot/2) | sin(rot/2).
+// Cache layout per layer: [block][2][Hkv][block_tokens][D] with `block_stride` elements between blocks.
+// slot < 0 skips the cache write (padding rows). neox: rotate halves; otherwise rotate pairs.
+// positions may carry 3 rows ([3][T]) for multimodal rotary sections (mrope_s0/s1 = section ends in pairs).
+template <typename CacheT>
+__global__ void rope_kv_append_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions, int pos_stride,
+                                      const int* __restrict__ slots, const float* __restrict__ cos_sin,
+                                      CacheT* __restrict__ cache, long long block_stride, int block_tokens, int Hq,
+                                      int Hkv, int D, int rot_dim, int neox, int mrope_s0, int mrope_s1,
+                                      float k_scale_inv, float v_scale_inv, int apply_rope) {
+  const int t = blockIdx.x;
+  bf16* row = qkv + static_cast<size_t>(t) * (Hq + 2 * Hkv) * D;
+  const int half = rot_dim >> 1;
+  if (apply_rope) {
+    const int nrot = (Hq + Hkv) * half;
+    for (int i = threadIdx.x; i < nrot; i += blockDim.x) {
+      const int h = i / half, j = i % half;
+      int pos = positions[t];
+      if (pos_stride) {   // multimodal: pair index selects the temporal / height / width position row
+        const int sec = j < mrope_s0 ? 0 : (j < mrope_s1 ? 1 : 2);
+        pos = positions[sec * pos_stride + t];
+      }
+      const float* cs = cos_sin + static_cast<size_t>(pos) * rot_dim;
+      const float c = cs[j], s = cs[half + j];
+      bf16* hp = row + static_cast<size_t>(h) * D;
+      const int i0 = neox ? j : 2 * j, i1 = neox ? j + half : 2 * j + 1;
+      const float x0 = __bfloat162float(hp[i0]), x1 = __bfloat162float(hp[i1]);
+      hp[i0] = __float2bfloat16(x0 * c - x1 * s);
+      hp[i1] = __float2bfloat16(x1 * c + x0 * s);
+    }
+    __syncthreads();
+  }
+  const int slot = slots[t];
+  if (slot < 0 || cache == nullptr) return;
+  const int blk = slot / block_tokens, off = slot % block_tokens;
+  CacheT* kbase = cache + static_cast<size_t>(blk) * block_stride;
+  const bf16* ksrc = row + static_cast<size_t>(Hq) * D;
+  const int n = Hkv * D;
+  for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) {
+    const int kv = i / n, r = i % n;
+    const int h = r / D, d = r % D;
+    const float val = __bfloat162float(ksrc[i]);
+    const size_t dst = ((static_cast<size_t>(kv) * Hkv + h) * block_tokens + off) * D + d;
+    if constexpr (sizeof(CacheT) == 1) {
+      kbase[dst] = static_cast<CacheT>(
+          __nv_cvt_float_to_fp8(val * (kv ? v_scale_inv : k_scale_inv), __NV_SATFINITE, __NV_E4M3));
+    } else {
+      kbase[dst] = ksrc[i];
+    }
+  }
+}
+
+// Block-to-block copy inside the paged cache (beam fork, flexible cache, swap staging):
+// pairs[2*i] = source block, pairs[2*i+1] = destination block; copies all layers of a block.
+__global__ void copy_blocks_kernel(uint4* __restrict__ cache, const int* __restrict__ pairs, long long block_vec) {
+  const uint4* src = cache + static_cast<size_t>(pairs[2 * blockIdx.x]) * block_vec;
+  uint4* dst = cache + static_cast<size_t>(pairs[2 * blockIdx.x + 1]) * block_vec;
+  for (long long i = blockIdx.y * static_cast<long long>(blockDim.x) + threadIdx.x; i < block_vec;
+       i += static_cast<long long>(gridDim.y) * blockDim.x)
+    dst[i] = src[i];
+}
+
+// Gather / scatter of whole cache blocks between the device cache and a pinned host staging
+// area (one launch per swap instead of one memcpy per block). dir 0: cache->stage, 1: stage->cache.
+__global__ void swap_blocks_kernel(uint4* __restrict__ cache, uint4* __restrict__ stage, const int* __restrict__ ids,
+                                   long long block_vec, int dir) {
+  uint4* c = cache + static_cast<size_t>(ids[blockIdx.x]) * block_vec;
+  uint4* s = stage + static_cast<size_t>(blockIdx.x) * block_vec;
+  for (long long i = blockIdx.y * static_cast<long long>(blockDim.x) + threadIdx.x; i < block_vec;
+       i += static_cast<long long>(gridDim.y) * blockDim.x) {
+    if (dir == 0) s[i] = c[i]; else c[i] = s[i];
+  }
+}
+
+// out = a + b (+ bias), bf16 (used for unfused residual paths and the baseline backend)
+__global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, const bf16* __restrict__ bias,
+                           bf16* __restrict__ out, long long nvec_total, int nvec_row) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec_total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float x[8], y[8];
+    unpack8(reinterpret_cast<const uint4*>(a)[i], x);
+    if (b) {
+      unpack8(reinterpret_cast<const uint4*>(b)[i], y);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] += y[e];
+    }
+    if (bias) {
+      unpack8(reinterpret_cast<const uint4*>(bias)[i % nvec_row], y);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] += y[e];
+    }
+    reinterpret_cast<uint4*>(out)[i] = pack8(x);
+  }
+}
+
+// bf16 -> fp32 cast of selected rows (logits for the sampler when the GEMM wrote bf16)
+__global__ void cast_f32_kernel(const bf16* __restrict__ in, float* __restrict__ out, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = __bfloat162float(in[i]);
+}
+
+static inline int grid_for(long long work, int threads, int cap = 148 * 8) {
+  long long g = (work + threads - 1) / threads;
+  if (g < 1) g = 1;
+  return static_cast<int>(g > cap ? cap : g);
+}
+static inline int norm_threads(int H) {
+  int t = ((H >> 3) + kMaxVec - 1) / kMaxVec;
+  t = ((t + 31) / 32) * 32;
+  if (t < 32) t = 32;
+  return t > 1024 ? 1024 : t;
+}
+
+}  // namespace ksana
+
+using namespace ksana;
+
+extern "C" int ksana_norm(const void* x, void* residual, const void* w, const void* beta, void* y, void* yq,
+                          float* yscale, int scale_ld, int M, int H, float eps, int layernorm, cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (H % 8 || H > 8 * kMaxVec * 1024) return -10;
+  if (yq && (H % 128)) return -11;
+  const int threads = norm_threads(H);
+  if (layernorm)
+    norm_kernel<1><<<M, threads, 0, st>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, (const bf16*)beta, (bf16*)y,
+                                          (uint8_t*)yq, yscale, scale_ld, H, eps);
+  else
+    norm_kernel<0><<<M, threads, 0, st>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, (const bf16*)beta, (bf16*)y,
+                                          (uint8_t*)yq, yscale, scale_ld, H, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_act_mul(const void* in, void* out, void* outq, float* oscale, int scale_ld, int M, int I,
+                             int in_ld, int act, int gated, cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (I % 8 || in_ld % 8) return -10;
+  if (outq && (I % 128)) return -11;
+  const long long total = static_cast<long long>(M) * (I >> 3);
+  act_mul_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)in, (bf16*)out, (uint8_t*)outq, oscale, scale_ld, M,
+                                                       I, in_ld, act, gated);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_quant_fp8(const void* x, void* q, float* scale, int scale_ld, int M, int K, int x_ld,
+                               cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (K % 128 || x_ld % 8) return -10;
+  const long long total = static_cast<long long>(M) * (K >> 3);
+  quant_fp8_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (uint8_t*)q, scale, scale_ld, M, K, x_ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_embedding(const int* ids, const void* table, const int* positions, const void* pos_table,
+                               void* out, int T, int H, int vocab_lo, int vocab_hi, float scale, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8) return -10;
+  embedding_kernel<<<T, 256, 0, st>>>(ids, (const bf16*)table, positions, (const bf16*)pos_table, (bf16*)out, H,
+                                      vocab_lo, vocab_hi, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_gather_rows(const void* in, const int* idx, void* out, int R, int H, cudaStream_t st) {
+  if (R <= 0) return 0;
+  if (H % 8) return -10;
+  gather_rows_kernel<<<R, 256, 0, st>>>((const bf16*)in, idx, (bf16*)out, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_refit_rows(void* hidden, const int* pos, const float* emb, int R, int H, cudaStream_t st) {
+  if (R <= 0) return 0;
+  refit_rows_kernel<<<R, 256, 0, st>>>((bf16*)hidden, pos, emb, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_rope_kv_append(void* qkv, const int* positions, int pos_stride, const int* slots,
+                                    const float* cos_sin, void* cache, long long block_stride, int block_tokens, int T,
+                                    int Hq, int Hkv, int D, int rot_dim, int neox, int mrope_s0, int mrope_s1,
+                                    int cache_fp8, float k_scale, float v_scale, int apply_rope, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (cache_fp8)
+    rope_kv_append_kernel<uint8_t><<<T, 256, 0, st>>>((bf16*)qkv, positions, pos_stride, slots, cos_sin,
+                                                      (uint8_t*)cache, block_stride, block_tokens, Hq, Hkv, D, rot_dim,
+                                                      neox, mrope_s0, mrope_s1, 1.f / k_scale, 1.f / v_scale,
+                                                      apply_rope);
+  else
+    rope_kv_append_kernel<bf16><<<T, 256, 0, st>>>((bf16*)qkv, positions, pos_stride, slots, cos_sin, (bf16*)cache,
+                                                   block_stride, block_tokens, Hq, Hkv, D, rot_dim, neox, mrope_s0,
+                                                   mrope_s1, 1.f, 1.f, apply_rope);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_copy_blocks(void* cache, const int* pairs, int npairs, long long block_bytes, cudaStream_t st) {
+  if (npairs <= 0) return 0;
+  if (block_bytes % 16) return -10;
+  copy_blocks_kernel<<<dim3(npairs, 16), 256, 0, st>>>((uint4*)cache, pairs, block_bytes / 16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_swap_blocks(void* cache, void* stage, const int* ids, int n, long long block_bytes, int dir,
+                                 cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (block_bytes % 16) return -10;
+  swap_blocks_kernel<<<dim3(n, 16), 256, 0, st>>>((uint4*)cache, (uint4*)stage, ids, block_bytes / 16, dir);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_add(const void* a, const void* b, const void* bias, void* out, long long M, int H,
+                         cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (H % 8) return -10;
+  const long long nvec = M * (H >> 3);
+  add_kernel<<<grid_for(nvec, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, (const bf16*)bias, (bf16*)out, nvec,
+                                                  H >> 3);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_cast_f32(const void* in, float* out, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  cast_f32_kernel<<<grid_for(n, 256), 256, 0, st>>>((const bf16*)in, out, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -1,0 +1,414 @@
+// Dense GEMMs for sm_100a on the 5th-generation tensor cores.
+//
+//   D[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) (+ residual[M,N])
+//
+// Two operand kinds share one warp-specialised persistent kernel:
+//   * bf16 x bf16 (tcgen05.mma kind::f16), the whole K loop accumulates in TMEM;
+//   * fp8-e4m3 x fp8-e4m3 with fine-grained scales (kind::f8f6f4): activations
+//     carry one fp32 scale per (row, 128-wide K group), weights one per
+//     (128 x 128) block. Each 128-deep K block is multiplied into a fresh TMEM
+//     accumulator and promoted into fp32 registers with its scale product, so
+//     the scales stay exact fp32 (no power-of-two restriction).
+//
+// CTA layout (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
+// issuer (one elected lane), warps 2..5 = epilogue (each owns the 32 TMEM lanes
+// its warp id modulo 4 selects). Operand tiles are 128-byte-swizzled rows
+// written by TMA into a multi-stage shared-memory ring; accumulators are
+// multi-buffered in TMEM so the epilogue of tile i overlaps the MMAs of tile
+// i+1. No cluster multicast is used anywhere, so the kernel is safe in
+// multi-GPU processes.
+//
+// Replaces the cuBLASLt wrapper of the reference
+// (3rdparty/LLM_kernels/csrc/kernels/nvidia/gemm_wrapper/gemm_wrapper.cc:24-125)
+// and its per-tensor FP8 path (src/ksana_llm/kernels/nvidia/kernel_wrapper.cpp:1014-1048).
+#include "sm100_ptx.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <stdio.h>
+
+namespace ksana {
+
+constexpr int kBM = 128;          // rows per tile = TMEM lanes
+constexpr int kRowBytes = 128;    // one swizzled smem row: 64 bf16 or 128 fp8
+constexpr int kGemmThreads = 192;
+constexpr int kSmemBudget = 200 * 1024;
+
+enum GemmKind { kBf16 = 0, kFp8Block = 1 };
+
+struct GemmParams {
+  int M, N, K;
+  __nv_bfloat16* D;       // bf16 output (may be null when out_f32 is set)
+  float* out_f32;         // optional fp32 output
+  int ldd;
+  const __nv_bfloat16* bias;      // [N] or null
+  const __nv_bfloat16* residual;  // [M, ldr] or null
+  int ldr;
+  const float* a_scale;   // fp8: [K/128][a_scale_ld]   (k-group major, contiguous over rows)
+  int a_scale_ld;
+  const float* w_scale;   // fp8: [ceil(N/128)][K/128]
+  int* err;               // device word, set non-zero when a bounded wait gave up
+};
+
+template <int BN, int KIND>
+struct GemmCfg {
+  static constexpr int kABytes = kBM * kRowBytes;
+  static constexpr int kBBytes = BN * kRowBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+  static constexpr int kAccStages = (KIND == kBf16) ? 2 : ((512 / BN) > 4 ? 4 : (512 / BN));
+  static constexpr int kTmemCols = kAccStages * BN < 32 ? 32 : kAccStages * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int kElemsPerRow = (KIND == kBf16) ? 64 : 128;  // K elements per stage
+  static constexpr int kMmaK = (KIND == kBf16) ? 16 : 32;
+};
+
+template <int BN, int KIND>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmParams p) {
+  using Cfg = GemmCfg<BN, KIND>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::kStages;
+  uint64_t* tfull_bar = bars + 2 * Cfg::kStages;
+  uint64_t* tempty_bar = tfull_bar + Cfg::kAccStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + Cfg::kAccStages);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + kBM - 1) / kBM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (p.K + Cfg::kElemsPerRow - 1) / Cfg::kElemsPerRow;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * kBM;
+        const int n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_2d(sa, &tma_a, &full_bar[stage], kb * Cfg::kElemsPerRow, m0);
+          tma_load_2d(sb, &tma_b, &full_bar[stage], kb * Cfg::kElemsPerRow, n0);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = (KIND == kBf16) ? make_idesc(kBM, BN, 1, 1) : make_idesc(kBM, BN, 0, 0);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (KIND == kBf16) {
+          if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (KIND == kFp8Block) {
+            if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+          }
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint64_t adesc = make_smem_desc_sw128(sa);
+          const uint64_t bdesc = make_smem_desc_sw128(sa + Cfg::kABytes);
+          const uint32_t d_tmem = tmem_base + acc * BN;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // 32 bytes of K per MMA for both kinds (16 bf16 or 32 fp8): +2 in 16-byte units
+            const uint32_t accum = (KIND == kBf16) ? ((kb | k) != 0) : (k != 0);
+            if (KIND == kBf16) mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+            else mma_f8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+          if (KIND == kFp8Block) {
+            tc_commit(&tfull_bar[acc]);
+            if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+          }
+        }
+        if (KIND == kBf16 && ok) {
+          tc_commit(&tfull_bar[acc]);
+          if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;                     // TMEM lane quarter this warp may touch
+    const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % m_tiles) * kBM;
+      const int n0 = (tile / m_tiles) * BN;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+
+      auto store_chunk = [&](int c0, const float (&v)[32]) {
+        if (!row_ok) return;
+        const int col0 = n0 + c0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int col = col0 + g * 8;
+          if (col >= p.N) continue;   // N is a multiple of 8 (checked on the host)
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = v[g * 8 + i];
+          if (p.bias) {
+            const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(b2[i]); o[2 * i] += f.x; o[2 * i + 1] += f.y; }
+          }
+          if (p.residual) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(row) * p.ldr + col);
+            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(r2[i]); o[2 * i] += f.x; o[2 * i + 1] += f.y; }
+          }
+          if (p.out_f32) {
+            float4* dst = reinterpret_cast<float4*>(p.out_f32 + static_cast<size_t>(row) * p.ldd + col);
+            dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+          } else {
+            uint4 ov;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+            *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(row) * p.ldd + col) = ov;
+          }
+        }
+      };
+
+      if (KIND == kBf16) {
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + lane_base + acc * BN + c0, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          store_chunk(c0, v);
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty_bar[acc]);
+        if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+      } else {
+        float accv[BN];
+#pragma unroll
+        for (int i = 0; i < BN; ++i) accv[i] = 0.f;
+        const int nkb_scale = (p.K + 127) / 128;
+        const float* ws = p.w_scale + static_cast<size_t>(n0 / 128) * nkb_scale;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const float s = (row_ok ? p.a_scale[static_cast<size_t>(kb) * p.a_scale_ld + row] : 0.f) * ws[kb];
+          if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + lane_base + acc * BN + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) accv[c0 + i] = fmaf(s, __uint_as_float(r[i]), accv[c0 + i]);
+          }
+          tc_fence_before();
+          mbar_arrive(&tempty_bar[acc]);
+          if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+        }
+        if (ok) {
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = accv[c0 + i];
+            store_chunk(c0, v);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up: report, give copies/MMAs in flight a bounded time to land, then free TMEM.
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, 1);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Row-major [rows, cols] operand with `ld` elements between rows; box = 128 bytes x box_rows.
+static int make_operand_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int elem_bytes,
+                            int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / elem_bytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN, int KIND>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_ctas,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, KIND>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return -3;
+    attr_set = true;
+  }
+  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  gemm_tcgen05_kernel<BN, KIND><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ma, mb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+static int pick_bn(int M, int N, int kind, int bn_hint) {
+  if (bn_hint == 32 || bn_hint == 64 || bn_hint == 128 || (bn_hint == 256 && kind == kBf16)) return bn_hint;
+  const int sms = num_sms();
+  const int m_tiles = (M + kBM - 1) / kBM;
+  const int cands_bf16[4] = {256, 128, 64, 32};
+  const int cands_fp8[3] = {128, 64, 32};
+  const int* c = kind == kBf16 ? cands_bf16 : cands_fp8;
+  const int nc = kind == kBf16 ? 4 : 3;
+  for (int i = 0; i < nc; ++i) {
+    const int tiles = m_tiles * ((N + c[i] - 1) / c[i]);
+    if (tiles >= sms) return c[i];   // at least one full wave with the widest tile that allows it
+  }
+  return c[nc - 1];
+}
+
+}  // namespace ksana
+
+using namespace ksana;
+
+// D = A[M,K](bf16, row stride lda) * W[N,K]^T (bf16) (+bias)(+residual); output bf16 or fp32.
+// Returns 0 on launch success, negative on argument / setup errors.
+extern "C" int ksana_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, void* out_f32, int ldd,
+                               const void* bias, const void* residual, int ldr, int M, int N, int K, int bn_hint,
+                               int max_ctas, int* err_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N % 8) || (K % 8) || (lda % 8) || (ldw % 8) || (ldd % 8) || (residual && (ldr % 8))) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -11;
+  const int bn = pick_bn(M, N, kBf16, bn_hint);
+  CUtensorMap ma, mb;
+  if (make_operand_map(&ma, A, M, K, lda, 2, kBM)) return -12;
+  if (make_operand_map(&mb, W, N, K, ldw, 2, bn)) return -13;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.D = static_cast<__nv_bfloat16*>(D); p.out_f32 = static_cast<float*>(out_f32); p.ldd = ldd;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+  p.err = err_flag;
+  switch (bn) {
+    case 256: return launch_gemm<256, kBf16>(ma, mb, p, max_ctas, stream);
+    case 128: return launch_gemm<128, kBf16>(ma, mb, p, max_ctas, stream);
+    case 64: return launch_gemm<64, kBf16>(ma, mb, p, max_ctas, stream);
+    default: return launch_gemm<32, kBf16>(ma, mb, p, max_ctas, stream);
+  }
+}
+
+// Block-scaled FP8: A_q[M,K] e4m3 with a_scale[K/128][a_scale_ld] fp32, W_q[N,K] e4m3 with
+// w_scale[ceil(N/128)][K/128] fp32. K must be a multiple of 128.
+extern "C" int ksana_gemm_fp8_block(const void* Aq, int lda, const float* a_scale, int a_scale_ld, const void* Wq,
+                                    int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
+                                    const void* residual, int ldr, int M, int N, int K, int bn_hint, int max_ctas,
+                                    int* err_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N % 8) || (K % 128) || (lda % 16) || (ldw % 16) || (ldd % 8) || (residual && (ldr % 8))) return -10;
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Wq)) & 15) return -11;
+  const int bn = pick_bn(M, N, kFp8Block, bn_hint);
+  CUtensorMap ma, mb;
+  if (make_operand_map(&ma, Aq, M, K, lda, 1, kBM)) return -12;
+  if (make_operand_map(&mb, Wq, N, K, ldw, 1, bn)) return -13;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.D = static_cast<__nv_bfloat16*>(D); p.out_f32 = static_cast<float*>(out_f32); p.ldd = ldd;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+  p.a_scale = a_scale; p.a_scale_ld = a_scale_ld; p.w_scale = w_scale;
+  p.err = err_flag;
+  switch (bn) {
+    case 128: return launch_gemm<128, kFp8Block>(ma, mb, p, max_ctas, stream);
+    case 64: return launch_gemm<64, kFp8Block>(ma, mb, p, max_ctas, stream);
+    default: return launch_gemm<32, kFp8Block>(ma, mb, p, max_ctas, stream);
+  }
+}

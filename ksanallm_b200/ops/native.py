@@ -1,0 +1,291 @@
+"""ctypes bindings to ``libksana_kernels.so`` (the hand-written sm_100a kernels).
+
+Every wrapper takes torch CUDA tensors, passes raw pointers plus the current CUDA stream and
+raises if the native library is missing or a launch is rejected, so a GPU box can never fall
+back silently to PyTorch ops.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_LIB = None
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libksana_kernels.so"
+
+vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+
+_SIGS = {
+    "ksana_gemm_bf16": [vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+    "ksana_gemm_fp8_block": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+    "ksana_norm": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp],
+    "ksana_act_mul": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+    "ksana_quant_fp8": [vp, vp, vp, i32, i32, i32, i32, vp],
+    "ksana_embedding": [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
+    "ksana_gather_rows": [vp, vp, vp, i32, i32, vp],
+    "ksana_refit_rows": [vp, vp, vp, i32, i32, vp],
+    "ksana_rope_kv_append": [vp, vp, i32, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32,
+                             i32, vp],
+    "ksana_copy_blocks": [vp, vp, i32, i64, vp],
+    "ksana_swap_blocks": [vp, vp, vp, i32, i64, i32, vp],
+    "ksana_add": [vp, vp, vp, vp, i64, i32, vp],
+    "ksana_cast_f32": [vp, vp, i64, vp],
+    "ksana_paged_prefill": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32,
+                            f32, f32, vp],
+    "ksana_paged_decode": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, f32, f32,
+                           i32, vp, vp, vp],
+    "ksana_sample": [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, vp],
+    "ksana_repetition_penalty": [vp, i64, vp, vp, vp, vp, i32, i32, vp],
+    "ksana_ban_tokens": [vp, i64, vp, vp, vp, i32, i32, vp],
+}
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of native kernel launches issued through this module (bench accounting)."""
+    return _launches
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(
+                f"native kernel library {_LIB_PATH} is missing: run `python -m ksanallm_b200.build` "
+                "(CUDA tensors are never served by a PyTorch fallback)")
+        _LIB = C.CDLL(str(_LIB_PATH))
+        for name, sig in _SIGS.items():
+            fn = getattr(_LIB, name, None)
+            if fn is not None:
+                fn.argtypes = sig
+                fn.restype = C.c_int
+    return _LIB
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _st():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, name: str):
+    global _launches
+    _launches += 1
+    if rc != 0:
+        raise RuntimeError(f"{name} rejected its arguments or failed to launch (code {rc})")
+
+
+_err_flags = {}
+
+
+def err_flag(device) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits set when a wait gave up."""
+    key = torch.device(device).index or 0
+    if key not in _err_flags:
+        _err_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _err_flags[key]
+
+
+def check_err_flag(device) -> None:
+    flag = err_flag(device)
+    if int(flag.item()) != 0:
+        flag.zero_()
+        raise RuntimeError("a device-side bounded wait timed out (kernel reported an error status)")
+
+
+# ------------------------------------------------------------------------------------- GEMM
+def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0):
+    """out[M,N] = x[M,K] @ w[N,K]^T (+bias)(+residual). bf16 in, bf16 (or fp32) out."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.stride(1) == 1 and w.stride(1) == 1 and w.shape[1] == K
+    if out is None and out_f32 is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    dst = out if out_f32 is None else out_f32
+    rc = lib().ksana_gemm_bf16(_p(x), x.stride(0), _p(w), w.stride(0), _p(out) if out_f32 is None else None,
+                               _p(out_f32), dst.stride(0), _p(bias), _p(residual),
+                               residual.stride(0) if residual is not None else 0, M, N, K, bn, max_ctas,
+                               _p(err_flag(x.device)), _st())
+    _check(rc, "ksana_gemm_bf16")
+    return dst
+
+
+def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0):
+    """Block-scaled FP8 GEMM. xq [M,K] e4m3, xs [K/128, ld] fp32; wq [N,K] e4m3, ws [ceil(N/128), K/128] fp32."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    if out is None and out_f32 is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
+    dst = out if out_f32 is None else out_f32
+    rc = lib().ksana_gemm_fp8_block(_p(xq), xq.stride(0), _p(xs), xs.stride(0), _p(wq), wq.stride(0), _p(ws),
+                                    _p(out) if out_f32 is None else None, _p(out_f32), dst.stride(0), _p(bias),
+                                    _p(residual), residual.stride(0) if residual is not None else 0, M, N, K, bn,
+                                    max_ctas, _p(err_flag(xq.device)), _st())
+    _check(rc, "ksana_gemm_fp8_block")
+    return dst
+
+
+def quant_fp8(x, q=None, s=None):
+    M, K = x.shape
+    if q is None:
+        q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    if s is None:
+        s = torch.empty(K // 128, max(4, (M + 3) // 4 * 4), dtype=torch.float32, device=x.device)
+    _check(lib().ksana_quant_fp8(_p(x), _p(q), _p(s), s.stride(0), M, K, x.stride(0), _st()), "ksana_quant_fp8")
+    return q, s
+
+
+# -------------------------------------------------------------------------------- elementwise
+def norm(x, w, eps, residual=None, beta=None, out=None, layernorm=False, quant=False, q=None, s=None,
+         want_out=True):
+    """y = norm(x (+residual, updated in place)) * w (+beta); optionally also the FP8 operand of y."""
+    M, H = x.shape
+    if want_out and out is None:
+        out = torch.empty(M, H, dtype=torch.bfloat16, device=x.device)
+    if quant:
+        if q is None:
+            q = torch.empty(M, H, dtype=torch.float8_e4m3fn, device=x.device)
+        if s is None:
+            s = torch.empty(H // 128, max(4, (M + 3) // 4 * 4), dtype=torch.float32, device=x.device)
+    rc = lib().ksana_norm(_p(x), _p(residual), _p(w), _p(beta), _p(out) if want_out else None, _p(q) if quant else None,
+                          _p(s) if quant else None, s.stride(0) if quant else 0, M, H, float(eps), int(layernorm),
+                          _st())
+    _check(rc, "ksana_norm")
+    return (out, q, s) if quant else out
+
+
+_ACTS = {"silu": 0, "swiglu": 0, "gelu": 1, "gelu_new": 1, "gelu_pytorch_tanh": 1, "relu": 2}
+
+
+def act_mul(x, act="silu", gated=True, out=None, quant=False, q=None, s=None, want_out=True):
+    M = x.shape[0]
+    inter = x.shape[1] // 2 if gated else x.shape[1]
+    if want_out and out is None:
+        out = torch.empty(M, inter, dtype=torch.bfloat16, device=x.device)
+    if quant:
+        if q is None:
+            q = torch.empty(M, inter, dtype=torch.float8_e4m3fn, device=x.device)
+        if s is None:
+            s = torch.empty(inter // 128, max(4, (M + 3) // 4 * 4), dtype=torch.float32, device=x.device)
+    rc = lib().ksana_act_mul(_p(x), _p(out) if want_out else None, _p(q) if quant else None, _p(s) if quant else None,
+                             s.stride(0) if quant else 0, M, inter, x.stride(0), _ACTS[act], int(gated), _st())
+    _check(rc, "ksana_act_mul")
+    return (out, q, s) if quant else out
+
+
+def embedding(ids, table, out=None, vocab_lo=0, vocab_hi=None, positions=None, pos_table=None, scale=1.0):
+    T, H = ids.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=table.device)
+    hi = vocab_lo + table.shape[0] if vocab_hi is None else vocab_hi
+    rc = lib().ksana_embedding(_p(ids), _p(table), _p(positions), _p(pos_table), _p(out), T, H, vocab_lo, hi,
+                               float(scale), _st())
+    _check(rc, "ksana_embedding")
+    return out
+
+
+def gather_rows(x, idx, out=None):
+    R, H = idx.numel(), x.shape[1]
+    if out is None:
+        out = torch.empty(R, H, dtype=torch.bfloat16, device=x.device)
+    _check(lib().ksana_gather_rows(_p(x), _p(idx), _p(out), R, H, _st()), "ksana_gather_rows")
+    return out
+
+
+def refit_rows(hidden, pos, emb):
+    _check(lib().ksana_refit_rows(_p(hidden), _p(pos), _p(emb), pos.numel(), hidden.shape[1], _st()),
+           "ksana_refit_rows")
+
+
+def add(a, b=None, bias=None, out=None):
+    if out is None:
+        out = torch.empty_like(a)
+    H = a.shape[-1]
+    _check(lib().ksana_add(_p(a), _p(b), _p(bias), _p(out), a.numel() // H, H, _st()), "ksana_add")
+    return out
+
+
+def cast_f32(x, out=None):
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    _check(lib().ksana_cast_f32(_p(x), _p(out), x.numel(), _st()), "ksana_cast_f32")
+    return out
+
+
+# ---------------------------------------------------------------------------- attention path
+def rope_kv_append(qkv, positions, slots, cos_sin, cache_layer, block_stride, block_tokens, Hq, Hkv, D, rot_dim,
+                   neox=True, mrope_sections=None, k_scale=1.0, v_scale=1.0, apply_rope=True):
+    """In-place RoPE on q,k of qkv [T,(Hq+2Hkv)*D] and append of k,v into the layer's paged cache."""
+    T = qkv.shape[0]
+    fp8 = cache_layer is not None and cache_layer.dtype != torch.bfloat16
+    pos_stride, s0, s1 = 0, 0, 0
+    if mrope_sections is not None:
+        pos_stride = positions.stride(0)
+        s0, s1 = mrope_sections[0], mrope_sections[0] + mrope_sections[1]
+    rc = lib().ksana_rope_kv_append(_p(qkv), _p(positions), pos_stride, _p(slots), _p(cos_sin), _p(cache_layer),
+                                    block_stride, block_tokens, T, Hq, Hkv, D, rot_dim, int(neox), s0, s1, int(fp8),
+                                    float(k_scale), float(v_scale), int(apply_rope), _st())
+    _check(rc, "ksana_rope_kv_append")
+
+
+def paged_prefill(q, q_stride, out, cache_layer, block_stride, block_tokens, block_table, cu_q, kv_lens, B, max_q_len,
+                  Hq, Hkv, D, scale, alibi=None, k_scale=1.0, v_scale=1.0):
+    fp8 = cache_layer.dtype != torch.bfloat16
+    rc = lib().ksana_paged_prefill(_p(q), q_stride, _p(out), out.stride(0), _p(cache_layer), block_stride,
+                                   block_tokens, _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_lens),
+                                   _p(alibi), B, max_q_len, Hq, Hkv, D, float(scale), int(fp8), float(k_scale),
+                                   float(v_scale), _st())
+    _check(rc, "ksana_paged_prefill")
+
+
+def paged_decode(q, q_stride, out, cache_layer, block_stride, block_tokens, block_table, kv_lens, B, Hq, Hkv, D, scale,
+                 alibi=None, k_scale=1.0, v_scale=1.0, num_splits=1, part_o=None, part_ml=None):
+    fp8 = cache_layer.dtype != torch.bfloat16
+    rc = lib().ksana_paged_decode(_p(q), q_stride, _p(out), out.stride(0), _p(cache_layer), block_stride, block_tokens,
+                                  _p(block_table), block_table.stride(0), _p(kv_lens), _p(alibi), B, Hq, Hkv, D,
+                                  float(scale), int(fp8), float(k_scale), float(v_scale), num_splits, _p(part_o),
+                                  _p(part_ml), _st())
+    _check(rc, "ksana_paged_decode")
+
+
+def copy_blocks(cache, pairs, block_bytes):
+    _check(lib().ksana_copy_blocks(_p(cache), _p(pairs), pairs.numel() // 2, block_bytes, _st()), "ksana_copy_blocks")
+
+
+def swap_blocks(cache, stage, ids, block_bytes, to_host: bool):
+    _check(lib().ksana_swap_blocks(_p(cache), _p(stage), _p(ids), ids.numel(), block_bytes, 0 if to_host else 1, _st()),
+           "ksana_swap_blocks")
+
+
+# ----------------------------------------------------------------------------------- sampler
+def sample(logits, temperature, top_k, top_p, seeds, steps, out_tokens, row_idx=None, num_logprobs=0, lp_ids=None,
+           lp_vals=None):
+    B = out_tokens.numel()
+    rc = lib().ksana_sample(_p(logits), logits.stride(0), _p(row_idx), _p(temperature), _p(top_k), _p(top_p),
+                            _p(seeds), _p(steps), _p(out_tokens), num_logprobs, _p(lp_ids), _p(lp_vals), B,
+                            logits.shape[1], _st())
+    _check(rc, "ksana_sample")
+
+
+def repetition_penalty(logits, offsets, ids, penalty, row_idx=None):
+    B = penalty.numel()
+    rc = lib().ksana_repetition_penalty(_p(logits), logits.stride(0), _p(row_idx), _p(offsets), _p(ids), _p(penalty),
+                                        B, logits.shape[1], _st())
+    _check(rc, "ksana_repetition_penalty")
+
+
+def ban_tokens(logits, offsets, ids, row_idx=None):
+    B = offsets.numel() - 1
+    rc = lib().ksana_ban_tokens(_p(logits), logits.stride(0), _p(row_idx), _p(offsets), _p(ids), B, logits.shape[1],
+                                _st())
+    _check(rc, "ksana_ban_tokens")
