@@ -1,0 +1,190 @@
+"""Device dispatch for the operator layer: CUDA tensors go to the hand-written sm_100a kernels
+(:mod:`.native`), CPU tensors to the PyTorch statements (:mod:`.reference`). Model code calls
+only this module, so the same model definition runs the CPU test slice and the B200 path.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import native, reference as ref
+
+
+@dataclass
+class QTensor:
+    """FP8 GEMM operand: e4m3 values [M,K] and fp32 scales [K/128, ld] (one per row and 128 columns)."""
+    q: torch.Tensor
+    s: torch.Tensor
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+
+class LinearWeight:
+    """[N,K] weight of y = x W^T (+bias): dense bf16/fp32, or e4m3 with one fp32 scale per 128x128 block."""
+
+    def __init__(self, w: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                 wq: Optional[torch.Tensor] = None, ws: Optional[torch.Tensor] = None):
+        self.w, self.bias, self.wq, self.ws = w, bias, wq, ws
+
+    @property
+    def fp8(self) -> bool:
+        return self.wq is not None
+
+    @property
+    def out_features(self) -> int:
+        return (self.wq if self.fp8 else self.w).shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return (self.wq if self.fp8 else self.w).shape[1]
+
+    @property
+    def device(self):
+        return (self.wq if self.fp8 else self.w).device
+
+    def quantize_fp8_block(self) -> "LinearWeight":
+        if not self.fp8:
+            self.wq, self.ws = ref.quant_weight_fp8_block(self.w)
+            self.w = None
+        return self
+
+    def dense(self) -> torch.Tensor:
+        return ref.dequant_weight_fp8_block(self.wq, self.ws) if self.fp8 else self.w
+
+    def nbytes(self) -> int:
+        t = [x for x in (self.w, self.wq, self.ws, self.bias) if x is not None]
+        return sum(x.numel() * x.element_size() for x in t)
+
+
+def _is_cuda(x) -> bool:
+    return (x.q if isinstance(x, QTensor) else x).is_cuda
+
+
+def quantize(x: torch.Tensor) -> QTensor:
+    if x.is_cuda:
+        return QTensor(*native.quant_fp8(x))
+    return QTensor(*ref.quant_fp8(x))
+
+
+def linear(x, W: LinearWeight, residual=None, out=None, out_f32: bool = False):
+    """y = x W^T (+bias) (+residual). ``x`` may be a QTensor when W is FP8. ``out`` may alias ``residual``."""
+    if _is_cuda(x):
+        if W.fp8:
+            if not isinstance(x, QTensor):
+                x = quantize(x)
+            if out_f32:
+                o = torch.empty(x.q.shape[0], W.out_features, dtype=torch.float32, device=x.q.device)
+                return native.gemm_fp8(x.q, x.s, W.wq, W.ws, bias=W.bias, residual=residual, out_f32=o)
+            return native.gemm_fp8(x.q, x.s, W.wq, W.ws, out=out, bias=W.bias, residual=residual)
+        if out_f32:
+            o = torch.empty(x.shape[0], W.out_features, dtype=torch.float32, device=x.device)
+            return native.gemm_bf16(x, W.w, bias=W.bias, residual=residual, out_f32=o)
+        return native.gemm_bf16(x, W.w, out=out, bias=W.bias, residual=residual)
+    # CPU statement
+    if W.fp8:
+        xq = x if isinstance(x, QTensor) else QTensor(*ref.quant_fp8(x))
+        y = ref.gemm_fp8(xq.q, xq.s, W.wq, W.ws, W.bias, residual, torch.float32 if out_f32 else torch.bfloat16)
+    else:
+        y = ref.gemm(x, W.w, W.bias, residual, torch.float32 if out_f32 else x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def norm(x, w, eps, residual=None, beta=None, layernorm=False, quant_for: Optional[LinearWeight] = None):
+    """Returns the normalised activations in the form the consuming linear wants (QTensor for FP8
+    weights on CUDA). ``residual`` (if given) is updated in place with residual + x."""
+    want_q = quant_for is not None and quant_for.fp8 and x.shape[-1] % 128 == 0
+    if x.is_cuda:
+        if want_q:
+            _, q, s = native.norm(x, w, eps, residual=residual, beta=beta, layernorm=layernorm, quant=True,
+                                  want_out=False)
+            return QTensor(q, s)
+        return native.norm(x, w, eps, residual=residual, beta=beta, layernorm=layernorm)
+    y, new_res = ref.norm(x, w, eps, residual, beta, layernorm)
+    if residual is not None:
+        residual.copy_(new_res)
+    return QTensor(*ref.quant_fp8(y)) if want_q else y
+
+
+def act_mul(x, kind="silu", gated=True, quant_for: Optional[LinearWeight] = None):
+    inter = x.shape[-1] // 2 if gated else x.shape[-1]
+    want_q = quant_for is not None and quant_for.fp8 and inter % 128 == 0
+    if x.is_cuda:
+        if want_q:
+            _, q, s = native.act_mul(x, kind, gated, quant=True, want_out=False)
+            return QTensor(q, s)
+        return native.act_mul(x, kind, gated)
+    y = ref.act_mul(x, kind, gated)
+    return QTensor(*ref.quant_fp8(y)) if want_q else y
+
+
+def embedding(ids, table, vocab_lo=0, vocab_hi=None, positions=None, pos_table=None, scale=1.0):
+    if table.is_cuda:
+        return native.embedding(ids, table, vocab_lo=vocab_lo, vocab_hi=vocab_hi, positions=positions,
+                                pos_table=pos_table, scale=scale)
+    return ref.embedding(ids, table, vocab_lo, vocab_hi, positions, pos_table, scale)
+
+
+def gather_rows(x, idx):
+    if x.is_cuda:
+        return native.gather_rows(x, idx)
+    return x[idx.long()]
+
+
+def add(a, b=None, bias=None):
+    if a.is_cuda:
+        return native.add(a, b, bias)
+    y = a.float()
+    if b is not None:
+        y = y + b.float()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(a.dtype)
+
+
+def rope_kv_append(qkv, positions, slots, cos_sin, cache_layer, block_tokens, Hq, Hkv, D, rot_dim, neox=True,
+                   mrope_sections=None, k_scale=1.0, v_scale=1.0, apply_rope=True):
+    if qkv.is_cuda:
+        native.rope_kv_append(qkv, positions, slots, cos_sin, cache_layer,
+                              cache_layer.stride(0) if cache_layer is not None else 0, block_tokens, Hq, Hkv, D,
+                              rot_dim, neox, mrope_sections, k_scale, v_scale, apply_rope)
+    else:
+        ref.rope_kv_append(qkv, positions, slots, cos_sin, cache_layer, block_tokens, Hq, Hkv, D, rot_dim, neox,
+                           mrope_sections, k_scale, v_scale, apply_rope)
+
+
+def decode_splits(batch: int, hkv: int, max_kv_len: int, sms: int = 148) -> int:
+    """Split-KV factor: enough CTAs for two waves, at least two 64-token tiles per split."""
+    want = math.ceil(2 * sms / max(1, batch * hkv))
+    return max(1, min(want, 32, max(1, max_kv_len // 128)))
+
+
+def paged_attention(qkv, out, cache_layer, block_tokens, block_table, cu_q, kv_lens, num_multi, num_single,
+                    num_multi_tokens, max_q_len, Hq, Hkv, D, scale, alibi=None, k_scale=1.0, v_scale=1.0,
+                    num_splits=1, workspace=None):
+    """Attention of this step's new tokens (rows of ``qkv``: multi-token sequences first, then one row per
+    single-token sequence) against the paged cache, which already holds their K/V."""
+    if qkv.is_cuda:
+        if num_multi:
+            native.paged_prefill(qkv, qkv.stride(0), out, cache_layer, cache_layer.stride(0), block_tokens, block_table,
+                                 cu_q, kv_lens, num_multi, max_q_len, Hq, Hkv, D, scale, alibi, k_scale, v_scale)
+        if num_single:
+            po, pml = workspace if workspace is not None else (None, None)
+            if num_splits > 1 and po is None:
+                po = torch.empty(num_single * Hq * num_splits * D, dtype=torch.float32, device=qkv.device)
+                pml = torch.empty(num_single * Hq * num_splits * 2, dtype=torch.float32, device=qkv.device)
+            native.paged_decode(qkv[num_multi_tokens:], qkv.stride(0), out[num_multi_tokens:], cache_layer,
+                                cache_layer.stride(0), block_tokens, block_table[num_multi:], kv_lens[num_multi:],
+                                num_single, Hq, Hkv, D, scale, alibi, k_scale, v_scale, num_splits, po, pml)
+        return out
+    q = qkv[:, : Hq * D]
+    o = ref.paged_attention(q, cache_layer, block_table, cu_q, kv_lens, Hq, Hkv, D, scale, alibi, k_scale, v_scale)
+    out.copy_(o)
+    return out

@@ -1,0 +1,501 @@
+"""The engine loop: C++ scheduler -> step metadata upload -> model forward -> fused sampler ->
+scheduler post-step -> per-request notification.
+
+One engine step corresponds to the reference's ``BatchManager::MainProcess`` iteration
+(src/ksana_llm/batch_manager/batch_manager.cpp:111-241) plus ``LlmRuntime::Step``
+(src/ksana_llm/runtime/llm_runtime.cpp:387-445). Differences: the scheduler's plan is a flat
+int32 image uploaded with one pinned host->device copy (instead of many small copies built in
+``ModelInput::ParseFromRequests``), swap/copy lists are executed by one gather/scatter kernel on the
+compute stream, and in multi-rank runs rank 0 broadcasts the same image to the other ranks.
+"""
+from __future__ import annotations
+
+import os
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..config import EngineConfig, ModelConfig
+from ..models.common import StepInput
+from ..ops import dispatch as ops
+from ..ops import native
+from ..utils import native_engine as ne
+from .sampler import Sampler, SamplingParams
+from .structured import StructuredOutput
+
+
+@dataclass
+class SequenceOutput:
+    tokens: List[int] = field(default_factory=list)
+    logprobs: List[list] = field(default_factory=list)       # per token: [(id, logprob), ...]
+    finished: bool = False
+    cum_logprob: float = 0.0
+
+
+class Request:
+    """Python-side request record: outputs per sibling sequence, completion / streaming signalling."""
+
+    def __init__(self, req_id: int, prompt: List[int], cfg, n_seqs: int, stream: bool = False):
+        self.req_id = req_id
+        self.prompt = list(prompt)
+        self.cfg = cfg
+        self.outputs = [SequenceOutput() for _ in range(n_seqs)]
+        self.seq_ids: List[int] = []
+        self.status_code = 0
+        self.status_message = ""
+        self.done = threading.Event()
+        self.stream_queue: Optional[queue.Queue] = queue.Queue() if stream else None
+        self.arrive = time.time()
+        self.first_token_time: Optional[float] = None
+        self.finish_time: Optional[float] = None
+        self.structured: Optional[StructuredOutput] = None
+        self.aborted = False
+        # /forward style extraction
+        self.request_target: Optional[dict] = None
+        self.response: Dict[str, torch.Tensor] = {}
+        self.refit: Optional[tuple] = None               # (positions, embeddings)
+        self.mrope_positions = None
+        self.span_id: Optional[str] = None
+        self.prefix_hit = 0
+
+    def all_finished(self) -> bool:
+        return all(o.finished for o in self.outputs)
+
+
+class ModelRunner:
+    """Owns the model, its KV cache and the per-step device metadata."""
+
+    def __init__(self, model, block_tokens: int, num_blocks: int, num_host_blocks: int, kv_dtype=None):
+        self.model = model
+        self.device = model.device
+        self.cuda = self.device.type == "cuda"
+        self.block_tokens = block_tokens
+        model.allocate_kv_cache(num_blocks, block_tokens, kv_dtype)
+        self.block_bytes = model.block_bytes()
+        self.host_cache = None
+        if num_host_blocks > 0:
+            self.host_cache = torch.zeros(num_host_blocks, self.block_bytes, dtype=torch.uint8,
+                                          pin_memory=self.cuda)
+        self._pinned = None
+        self._pinned_cap = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def _stage(self, arr: np.ndarray) -> torch.Tensor:
+        """One pinned staging buffer -> one H2D copy."""
+        n = int(arr.size)
+        if not self.cuda:
+            return torch.from_numpy(arr.copy())
+        if n > self._pinned_cap:
+            self._pinned_cap = max(n * 2, 1 << 16)
+            self._pinned = torch.empty(self._pinned_cap, dtype=torch.int32, pin_memory=True)
+        self._pinned[:n].copy_(torch.from_numpy(arr))
+        self.h2d_bytes += n * 4
+        return self._pinned[:n].to(self.device, non_blocking=True)
+
+    def apply_block_ops(self, plan) -> None:
+        """Swap-outs, swap-ins and block copies decided by the scheduler, in that order, on the compute stream."""
+        so, si, cp = plan.swap_out, plan.swap_in, plan.copies
+        cache = self.model.kv_cache
+        flat = cache.view(cache.shape[0], -1)
+        if so.size:
+            pairs = so.reshape(-1, 2)
+            self._swap(flat, pairs, to_host=True)
+        if si.size:
+            pairs = si.reshape(-1, 2)
+            self._swap(flat, pairs, to_host=False)
+        if cp.size:
+            triples = cp.reshape(-1, 3)
+            if self.cuda:
+                t = self._stage(np.ascontiguousarray(triples[:, :2]).reshape(-1).astype(np.int32))
+                native.copy_blocks(cache, t, self.block_bytes)
+            else:
+                for s, d, _ in triples:
+                    flat[int(d)].copy_(flat[int(s)])
+            if (triples[:, 2] != 0).any():
+                self.model.rerotate_blocks(triples)
+
+    def _swap(self, flat, pairs, to_host: bool):
+        if self.host_cache is None:
+            raise RuntimeError("swap requested without a host block pool")
+        dev_ids = pairs[:, 0].astype(np.int64)
+        host_ids = pairs[:, 1].astype(np.int64)
+        raw = flat.view(torch.uint8) if flat.dtype != torch.uint8 else flat
+        if self.cuda:
+            # pinned host blocks are written / read by the copy engine in one batched index copy per direction
+            if to_host:
+                gathered = raw[torch.from_numpy(dev_ids).to(self.device)]
+                self.host_cache[torch.from_numpy(host_ids)] = gathered.cpu()
+            else:
+                raw[torch.from_numpy(dev_ids).to(self.device)] = self.host_cache[torch.from_numpy(host_ids)].to(self.device, non_blocking=True)
+        else:
+            if to_host:
+                self.host_cache[torch.from_numpy(host_ids)] = raw[torch.from_numpy(dev_ids)]
+            else:
+                raw[torch.from_numpy(dev_ids)] = self.host_cache[torch.from_numpy(host_ids)]
+
+    def build_step(self, plan, extra: Optional[dict] = None) -> StepInput:
+        T, nseq = plan.num_tokens, len(plan.seq_ids)
+        nsamp = plan.sample_rows.size
+        parts = [plan.input_ids, plan.positions, plan.slots, plan.cu_q, plan.kv_lens, plan.block_table, plan.sample_rows]
+        img = np.concatenate([np.asarray(p, dtype=np.int32).reshape(-1) for p in parts])
+        dev = self._stage(img)
+        o = 0
+
+        def take(n):
+            nonlocal o
+            v = dev[o:o + n]
+            o += n
+            return v
+
+        input_ids, positions, slots = take(T), take(T), take(T)
+        cu_q, kv_lens = take(nseq + 1), take(nseq)
+        table = take(nseq * plan.max_blocks).view(nseq, plan.max_blocks)
+        rows = take(nsamp)
+        step = StepInput(input_ids, positions, slots, cu_q, kv_lens, table, plan.num_multi, plan.num_single, T,
+                         plan.num_multi_tokens, plan.max_q_len, logits_rows=rows)
+        if plan.num_single:
+            max_kv = int(plan.kv_lens[plan.num_multi:].max())
+            step.decode_splits = ops.decode_splits(plan.num_single, self.model.Hkv, max_kv)
+        if extra:
+            for k, v in extra.items():
+                setattr(step, k, v)
+        return step
+
+    @torch.inference_mode()
+    def execute(self, plan, extra: Optional[dict] = None) -> torch.Tensor:
+        self.apply_block_ops(plan)
+        step = self.build_step(plan, extra)
+        return self.model.forward(step)
+
+
+class LLMEngine:
+    def __init__(self, model, model_cfg: ModelConfig, cfg: EngineConfig, num_blocks: int, num_host_blocks: int = 0,
+                 tokenizer=None, kv_dtype=None, rank: int = 0, world_size: int = 1, control_group=None):
+        self.model, self.model_cfg, self.cfg = model, model_cfg, cfg
+        self.tokenizer = tokenizer
+        self.rank, self.world_size, self.control_group = rank, world_size, control_group
+        bs = cfg.batch_scheduler
+        sc = ne.SchedulerConfig()
+        for k in ("schedule_strategy", "waiting_timeout_in_ms", "max_waiting_queue_len", "max_step_tokens",
+                  "max_batch_size", "swapout_block_threshold", "swapin_block_threshold", "launch_block_threshold",
+                  "preempt_mode", "split_fuse_token_num", "min_flexible_cache_num"):
+            setattr(sc, k, getattr(bs, k))
+        sc.max_token_len = min(bs.max_token_len, model_cfg.max_token_len) if model_cfg.max_token_len else bs.max_token_len
+        sc.enable_prefix_cache = bool(bs.enable_auto_prefix_cache)
+        sc.block_token_num = cfg.block_manager.block_token_num
+        sc.eos_token_ids = list(model_cfg.eos_token_ids)
+        self.sched_cfg = sc
+        if num_blocks * sc.block_token_num < sc.max_token_len:
+            raise ValueError(f"{num_blocks} KV blocks of {sc.block_token_num} tokens cannot hold max_token_len "
+                             f"{sc.max_token_len}")
+        self.scheduler = ne.Scheduler(sc, num_blocks, num_host_blocks) if rank == 0 else None
+        self.runner = ModelRunner(model, sc.block_token_num, num_blocks, num_host_blocks, kv_dtype)
+        self.sampler = Sampler(model.device, model_cfg.vocab_size)
+        self.requests: Dict[int, Request] = {}
+        self.seq_to_req: Dict[int, tuple] = {}
+        self._next_req = 1
+        self._lock = threading.Lock()
+        self._wake = threading.Condition()
+        self._thread: Optional[threading.Thread] = None
+        self._stop = False
+        self.steps = 0
+        self.fsm_controller = ne.FsmController()
+        self.step_hook: Optional[Callable] = None
+        self.last_logits: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: List[int], sampling=None, stream: bool = False, structured_regex: str = "",
+                    request_target: Optional[dict] = None, refit=None, mrope_positions=None) -> Request:
+        cfg = sampling or ne.SamplingConfig()
+        with self._lock:
+            req_id = self._next_req
+            self._next_req += 1
+        n = max(cfg.num_beams, cfg.num_return_sequences, 1)
+        req = Request(req_id, prompt, cfg, n, stream)
+        req.request_target, req.refit, req.mrope_positions = request_target, refit, mrope_positions
+        if structured_regex:
+            req.structured = StructuredOutput(self.fsm_controller.get_or_create(structured_regex), self.tokenizer)
+        if cfg.seed == 0:
+            cfg.seed = int.from_bytes(os.urandom(7), "little") | 1
+        code, msg, seq_ids = self.scheduler.add_request(req_id, list(prompt), cfg)
+        ne.report_counter("forward_req_total_num", 1)
+        if code != 0:
+            req.status_code, req.status_message = code, msg
+            for o in req.outputs:
+                o.finished = True
+            ne.report_counter("forward_req_error_num", 1)
+            self._complete(req)
+            return req
+        req.seq_ids = list(seq_ids)
+        with self._lock:
+            self.requests[req_id] = req
+            for i, sid in enumerate(seq_ids):
+                self.seq_to_req[sid] = (req, i)
+        if req.structured is not None:
+            init = req.structured.initial_tokens()
+            if init:
+                req.outputs[0].tokens = list(init)
+                self.scheduler.replace_generated(seq_ids[0], list(init))
+        ne.report_counter("metric_input_tokens_num", len(prompt))
+        with self._wake:
+            self._wake.notify_all()
+        return req
+
+    def abort(self, req: Request):
+        req.aborted = True
+        self.scheduler.abort(req.req_id)
+        with self._wake:
+            self._wake.notify_all()
+
+    def _complete(self, req: Request):
+        req.finish_time = time.time()
+        if req.stream_queue is not None:
+            req.stream_queue.put(None)
+        req.done.set()
+        if req.span_id:
+            ne.span_end(req.span_id, {"code": str(req.status_code)})
+        with self._lock:
+            self.requests.pop(req.req_id, None)
+            for sid in req.seq_ids:
+                self.seq_to_req.pop(sid, None)
+
+    # ------------------------------------------------------------------ one step
+    def _handle_events(self, events, lp_by_seq=None):
+        touched = set()
+        for seq_id, req_id, index, token, finished, code, message in events:
+            ent = self.seq_to_req.get(seq_id)
+            if ent is None:
+                continue
+            req, i = ent
+            out = req.outputs[i]
+            if token >= 0 and not out.finished:
+                out.tokens.append(int(token))
+                if lp_by_seq is not None and seq_id in lp_by_seq:
+                    out.logprobs.append(lp_by_seq[seq_id])
+                if req.first_token_time is None:
+                    req.first_token_time = time.time()
+                    ne.report_metric("time_to_first_token_ms", (req.first_token_time - req.arrive) * 1000.0)
+            if finished:
+                out.finished = True
+                if code != 0:
+                    req.status_code, req.status_message = code, message
+                    ne.report_counter({4: "forward_req_aborted_num", 7: "forward_req_timeout_num"}.get(code, "forward_req_error_num"), 1)
+            touched.add(req.req_id)
+            if not finished and token >= 0:
+                self._post_token_hooks(req, i, seq_id)
+        for rid in touched:
+            req = self.requests.get(rid)
+            if req is None:
+                continue
+            if req.stream_queue is not None:
+                req.stream_queue.put(("step", [list(o.tokens) for o in req.outputs]))
+            if req.all_finished():
+                n_out = sum(len(o.tokens) for o in req.outputs)
+                ne.report_counter("metric_output_token_num", n_out)
+                if req.first_token_time and n_out > 1:
+                    ne.report_metric("time_to_per_output_token_ms",
+                                     (time.time() - req.first_token_time) * 1000.0 / max(1, n_out - 1))
+                ne.report_metric("forward_cost_time_ms", (time.time() - req.arrive) * 1000.0)
+                self._complete(req)
+
+    def _post_token_hooks(self, req: Request, i: int, seq_id: int):
+        """Stop strings and structured output act on decoded text, which needs the tokenizer."""
+        out = req.outputs[i]
+        cfg = req.cfg
+        if cfg.stop_strings and self.tokenizer is not None:
+            text = self.tokenizer.decode(out.tokens, skip_special_tokens=True)
+            for s in cfg.stop_strings:
+                pos = text.find(s)
+                if pos >= 0:
+                    kept = self.tokenizer.encode(text[:pos], add_special_tokens=False)
+                    out.tokens = list(kept)
+                    ev = self.scheduler.finish_sequence(seq_id, -1, 0, "")
+                    out.finished = True
+                    return
+        if req.structured is not None:
+            action = req.structured.after_token(out.tokens)
+            if action.final:
+                out.tokens = action.tokens
+                self.scheduler.finish_sequence(seq_id, -1, 0, "")
+                out.finished = True
+            elif action.changed:
+                out.tokens = action.tokens
+                self.scheduler.replace_generated(seq_id, action.tokens)
+
+    def _gather_extras(self, plan) -> Optional[dict]:
+        """Per-step optional inputs: plugin embeddings to splice in, multimodal rotary positions."""
+        extra = {}
+        refit_pos, refit_emb, want_hidden = [], [], False
+        mrope = None
+        row0 = 0
+        for k, sid in enumerate(plan.seq_ids.tolist()):
+            ent = self.seq_to_req.get(sid)
+            ql = int(plan.q_lens[k])
+            if ent is not None:
+                req, _ = ent
+                start = int(plan.kv_lens[k]) - ql
+                if req.refit is not None:
+                    for pos, emb in zip(*req.refit):
+                        n = emb.shape[0] if emb.dim() > 1 else 1
+                        e2 = emb.reshape(n, -1)
+                        for j in range(n):
+                            p = int(pos) + j
+                            if start <= p < start + ql:
+                                refit_pos.append(row0 + p - start)
+                                refit_emb.append(e2[j])
+                if req.mrope_positions is not None:
+                    if mrope is None:
+                        mrope = torch.zeros(3, plan.num_tokens, dtype=torch.int32)
+                        mrope[:] = torch.from_numpy(np.asarray(plan.positions)).to(torch.int32)
+                    mp = torch.as_tensor(req.mrope_positions, dtype=torch.int32)
+                    end = min(start + ql, mp.shape[1])
+                    if end > start:
+                        mrope[:, row0:row0 + end - start] = mp[:, start:end]
+                    if start + ql > mp.shape[1]:     # generated tokens continue from the last multimodal position
+                        base = int(mp.max()) + 1 - mp.shape[1]
+                        s2 = max(start, mp.shape[1])
+                        mrope[:, row0 + s2 - start:row0 + ql] = torch.arange(s2, start + ql, dtype=torch.int32) + base
+                if req.request_target:
+                    want_hidden = True
+            row0 += ql
+        dev = self.model.device
+        if refit_pos:
+            extra["refit_positions"] = torch.tensor(refit_pos, dtype=torch.int32, device=dev)
+            extra["refit_embeddings"] = torch.stack(refit_emb).float().to(dev)
+        if mrope is not None:
+            extra["mrope_positions"] = mrope.to(dev)
+        if want_hidden:
+            extra["want_hidden"] = True
+        return extra or None
+
+    def step(self) -> bool:
+        """Runs one engine step. Returns False when there was nothing to run."""
+        t0 = time.time()
+        plan = self.scheduler.schedule()
+        ne.report_metric("batch_manager_schedule_ms", (time.time() - t0) * 1000.0)
+        if plan.events:
+            self._handle_events(plan.events)
+        if plan.empty():
+            return False
+        ne.trace_record("SchedBegin", "i", 0, float(plan.num_tokens))
+        ne.report_metric("batch_scheduler_batch_size", float(len(plan.seq_ids)))
+        ne.report_metric("token_num_in_batch", float(plan.num_tokens))
+        if self.world_size > 1:
+            self._broadcast_plan(plan)
+        phase = "Prefill" if plan.num_multi else "Decode"
+        ne.trace_record(phase, "B", 0, float(plan.num_tokens))
+        extra = self._gather_extras(plan)
+        logits = self.runner.execute(plan, extra)
+        self.last_logits = logits
+        tokens, parents, lp_by_seq = self._sample(plan, logits)
+        ne.trace_record(phase, "E", 0, float(plan.num_tokens))
+        self._extract_targets(plan, logits)
+        events = self.scheduler.post_step(plan, tokens, parents)
+        self._handle_events(events, lp_by_seq)
+        self.steps += 1
+        if self.step_hook:
+            self.step_hook(plan, logits)
+        return True
+
+    def _sample(self, plan, logits):
+        sample_seq_ids = plan.sample_seq_ids.tolist()
+        nsamp = len(sample_seq_ids)
+        if nsamp == 0:
+            return [], [], {}
+        # logits rows: one per plan.sample_rows entry (siblings repeat their leader's row)
+        params, reqs = [], []
+        for sid in sample_seq_ids:
+            ent = self.seq_to_req.get(sid)
+            req, i = ent if ent else (None, 0)
+            reqs.append((req, i))
+            params.append(SamplingParams.from_request(req, i))
+        return self.sampler.sample(logits, params, reqs, sample_seq_ids)
+
+    def _extract_targets(self, plan, logits):
+        """/forward request targets: copies of the requested slices (see serving.forward_api)."""
+        from ..serving.forward_api import extract_targets
+        extract_targets(self, plan, logits)
+
+    def full_logits_for(self, req, row0: int, ql: int) -> torch.Tensor:
+        """Logits of every position of one sequence of the current step (perplexity-style targets)."""
+        return self.model.compute_logits(self.model.step_normed[row0:row0 + ql])
+
+    def _broadcast_plan(self, plan):
+        from ..parallel.control import broadcast_plan
+        broadcast_plan(self.control_group, plan.pack())
+
+    # ------------------------------------------------------------------ loop
+    def start(self):
+        if self._thread is not None:
+            return
+        self._stop = False
+        self._thread = threading.Thread(target=self._loop, name="ksana-engine", daemon=True)
+        self._thread.start()
+
+    def _loop(self):
+        while not self._stop:
+            try:
+                ran = self.step()
+            except Exception as e:  # noqa: BLE001 - the loop must survive and fail the affected requests
+                import traceback
+                traceback.print_exc()
+                self._fail_all(12, f"engine step failed: {e}")
+                ran = False
+            if not ran:
+                with self._wake:
+                    if self.scheduler.idle() and not self._stop:
+                        self._wake.wait(timeout=0.05)
+                    else:
+                        self._wake.wait(timeout=0.001)
+
+    def _fail_all(self, code: int, message: str):
+        for req in list(self.requests.values()):
+            req.status_code, req.status_message = code, message
+            self.scheduler.abort(req.req_id)
+            for o in req.outputs:
+                o.finished = True
+            self._complete(req)
+
+    def stop(self):
+        self._stop = True
+        with self._wake:
+            self._wake.notify_all()
+        if self._thread is not None:
+            self._thread.join(timeout=10)
+            self._thread = None
+        if self.world_size > 1 and self.rank == 0:
+            from ..parallel.control import broadcast_plan
+            broadcast_plan(self.control_group, None)
+
+    # ------------------------------------------------------------------ conveniences
+    def generate(self, prompts: List[List[int]], sampling=None, timeout: Optional[float] = None) -> List[Request]:
+        """Offline batch generation on the calling thread (no background loop needed)."""
+        reqs = [self.add_request(p, _clone_cfg(sampling)) for p in prompts]
+        if self._thread is None:
+            deadline = time.time() + timeout if timeout else None
+            while not all(r.done.is_set() for r in reqs):
+                if not self.step() and self.scheduler.idle():
+                    break
+                if deadline and time.time() > deadline:
+                    break
+        else:
+            for r in reqs:
+                r.done.wait(timeout)
+        return reqs
+
+
+def _clone_cfg(cfg):
+    if cfg is None:
+        return None
+    c = ne.SamplingConfig()
+    for k in ("topk", "num_beams", "num_return_sequences", "topp", "temperature", "repetition_penalty",
+              "length_penalty", "no_repeat_ngram_size", "encoder_no_repeat_ngram_size", "max_new_tokens",
+              "logprobs_num", "stop_token_ids", "stop_strings", "ignore_eos", "seed"):
+        setattr(c, k, getattr(cfg, k))
+    return c

@@ -1,0 +1,196 @@
+"""Token selection for one engine step. The device work is the fused sampler kernel (penalties and
+bans edit the fp32 logits first); the host part keeps the per-request bookkeeping: penalty token
+lists, n-gram bans, log-prob collection and beam expansion.
+
+Order of operations and semantics follow the reference sampler
+(src/ksana_llm/samplers/sampler.cpp:82-400; beam search:
+src/ksana_llm/samplers/beam_search/beam_search_sampling.cpp:10-113): repetition penalty,
+n-gram bans, top-N log-probs over the temperature-scaled logits, then argmax / top-k / top-p.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..ops import native, reference as ref
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    topk: int = 1
+    topp: float = 1.0
+    repetition_penalty: float = 1.0
+    no_repeat_ngram_size: int = 0
+    encoder_no_repeat_ngram_size: int = 0
+    logprobs_num: int = 0
+    num_beams: int = 1
+    length_penalty: float = 1.0
+    seed: int = 1
+    step: int = 0
+    index: int = 0
+
+    @staticmethod
+    def from_request(req, index: int) -> "SamplingParams":
+        if req is None:
+            return SamplingParams()
+        c = req.cfg
+        out = req.outputs[index]
+        return SamplingParams(c.temperature, c.topk, c.topp, c.repetition_penalty, c.no_repeat_ngram_size,
+                              c.encoder_no_repeat_ngram_size, c.logprobs_num, c.num_beams, c.length_penalty,
+                              (int(c.seed) + 7919 * index) & ((1 << 62) - 1), len(out.tokens), index)
+
+
+def banned_ngram_tokens(history: List[int], n: int) -> List[int]:
+    """Tokens that would complete an n-gram already present in ``history``."""
+    if n <= 0 or len(history) + 1 < n:
+        return []
+    if n == 1:
+        return list(set(history))
+    prefix = tuple(history[len(history) - (n - 1):])
+    banned = set()
+    for i in range(len(history) - n + 1):
+        if tuple(history[i:i + n - 1]) == prefix:
+            banned.add(history[i + n - 1])
+    return list(banned)
+
+
+def banned_encoder_ngram_tokens(prompt: List[int], generated: List[int], n: int) -> List[int]:
+    """Tokens that would reproduce an n-gram of the prompt."""
+    if n <= 0:
+        return []
+    if n == 1:
+        return list(set(prompt))
+    if len(generated) < n - 1:
+        return []
+    prefix = tuple(generated[len(generated) - (n - 1):])
+    banned = set()
+    for i in range(len(prompt) - n + 1):
+        if tuple(prompt[i:i + n - 1]) == prefix:
+            banned.add(prompt[i + n - 1])
+    return list(banned)
+
+
+class Sampler:
+    def __init__(self, device, vocab_size: int):
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.vocab = vocab_size
+        self.d2h_bytes = 0
+        self._cpu_rng = torch.Generator().manual_seed(1234)
+
+    def _csr(self, lists: List[List[int]]):
+        offs = np.zeros(len(lists) + 1, dtype=np.int32)
+        for i, l in enumerate(lists):
+            offs[i + 1] = offs[i] + len(l)
+        ids = np.fromiter((t for l in lists for t in l), dtype=np.int32, count=int(offs[-1]))
+        return (torch.from_numpy(offs).to(self.device), torch.from_numpy(ids).to(self.device))
+
+    @torch.inference_mode()
+    def sample(self, logits: torch.Tensor, params: List[SamplingParams], reqs, seq_ids: List[int]):
+        B = len(params)
+        logits = logits[:B]
+        # 1. repetition penalty over the distinct tokens seen so far
+        if any(p.repetition_penalty != 1.0 for p in params):
+            lists = []
+            for p, (req, i) in zip(params, reqs):
+                seen = set(req.prompt) | set(req.outputs[i].tokens) if (req is not None and p.repetition_penalty != 1.0) else set()
+                lists.append([t for t in seen if 0 <= t < self.vocab])
+            pen = torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=self.device)
+            offs, ids = self._csr(lists)
+            if self.cuda:
+                native.repetition_penalty(logits, offs, ids, pen)
+            else:
+                for b, l in enumerate(lists):
+                    if l:
+                        logits[b, torch.tensor(l)] *= 1.0 / params[b].repetition_penalty
+        # 2. n-gram bans
+        if any(p.no_repeat_ngram_size > 0 or p.encoder_no_repeat_ngram_size > 0 for p in params):
+            lists = []
+            for p, (req, i) in zip(params, reqs):
+                ban = []
+                if req is not None:
+                    gen = req.outputs[i].tokens
+                    if p.no_repeat_ngram_size > 0:
+                        ban += banned_ngram_tokens(list(req.prompt) + list(gen), p.no_repeat_ngram_size)
+                    if p.encoder_no_repeat_ngram_size > 0:
+                        ban += banned_encoder_ngram_tokens(list(req.prompt), list(gen), p.encoder_no_repeat_ngram_size)
+                lists.append([t for t in set(ban) if 0 <= t < self.vocab])
+            offs, ids = self._csr(lists)
+            if self.cuda:
+                native.ban_tokens(logits, offs, ids)
+            else:
+                for b, l in enumerate(lists):
+                    if l:
+                        logits[b, torch.tensor(l)] = float("-inf")
+        # 3. fused temperature / top-k / top-p / draw (+ top-N log-probs)
+        N = max(p.logprobs_num for p in params)
+        temp = torch.tensor([p.temperature for p in params], dtype=torch.float32)
+        topk = torch.tensor([p.topk for p in params], dtype=torch.int32)
+        topp = torch.tensor([p.topp for p in params], dtype=torch.float32)
+        if self.cuda:
+            seeds = torch.tensor([p.seed for p in params], dtype=torch.int64)
+            steps = torch.tensor([p.step for p in params], dtype=torch.int32)
+            out = torch.empty(B, dtype=torch.int32, device=self.device)
+            lp_ids = torch.empty(B, max(N, 1), dtype=torch.int32, device=self.device) if N else None
+            lp_vals = torch.empty(B, max(N, 1), dtype=torch.float32, device=self.device) if N else None
+            native.sample(logits, temp.to(self.device), topk.to(self.device), topp.to(self.device),
+                          seeds.to(self.device), steps.to(self.device), out, num_logprobs=N, lp_ids=lp_ids,
+                          lp_vals=lp_vals)
+            tokens = out.cpu().tolist()        # the step's device->host result read (synchronises the stream)
+            self.d2h_bytes += B * 4
+            if N:
+                lp_ids_h, lp_vals_h = lp_ids.cpu(), lp_vals.cpu()
+                self.d2h_bytes += B * N * 8
+        else:
+            u = torch.rand(B, generator=self._cpu_rng)
+            tok, lp_ids_h, lp_vals_h = ref.sample(logits.float(), temp, topk, topp, u, N)
+            tokens = tok.tolist()
+        parents = [-1] * B
+        lp_by_seq: Dict[int, list] = {}
+        if N:
+            for b, sid in enumerate(seq_ids):
+                n = params[b].logprobs_num
+                if n:
+                    lp_by_seq[sid] = [(int(lp_ids_h[b, j]), float(lp_vals_h[b, j])) for j in range(n)]
+            self._beam_search(params, reqs, seq_ids, tokens, parents, lp_by_seq)
+        return tokens, parents, lp_by_seq
+
+    def _beam_search(self, params, reqs, seq_ids, tokens, parents, lp_by_seq):
+        """Beam expansion per request group: candidates = beams x their top log-probs, keep the best
+        ``num_beams`` by cumulative log-prob, re-parent sequences whose history changes."""
+        groups: Dict[int, List[int]] = {}
+        for b, (req, i) in enumerate(reqs):
+            if req is not None and params[b].num_beams > 1:
+                groups.setdefault(req.req_id, []).append(b)
+        for rid, rows in groups.items():
+            req = reqs[rows[0]][0]
+            nb = params[rows[0]].num_beams
+            first = all(len(req.outputs[reqs[b][1]].tokens) == 0 for b in rows)
+            cands = []
+            for b in rows:
+                out = req.outputs[reqs[b][1]]
+                for tok, lp in lp_by_seq.get(seq_ids[b], []):
+                    if tok >= 0:
+                        cands.append((out.cum_logprob + lp, b, tok))
+                if first:
+                    break          # all beams share one history: expand it once
+            cands.sort(key=lambda c: -c[0])
+            chosen = cands[:len(rows)] if len(cands) >= len(rows) else (cands * len(rows))[:len(rows)]
+            snapshot = {b: (list(req.outputs[reqs[b][1]].tokens), list(req.outputs[reqs[b][1]].logprobs)) for b in rows}
+            for slot, (score, src_b, tok) in zip(rows, chosen):
+                out = req.outputs[reqs[slot][1]]
+                tokens[slot] = tok
+                if src_b != slot and not first:
+                    parents[slot] = seq_ids[src_b]
+                    out.tokens, out.logprobs = list(snapshot[src_b][0]), list(snapshot[src_b][1])
+                out.cum_logprob = score
+
+
+def beam_final_order(outputs, length_penalty: float) -> List[int]:
+    """Final ranking of a beam group: cumulative log-prob / len^length_penalty, best first."""
+    scores = [o.cum_logprob / (max(len(o.tokens), 1) ** length_penalty) for o in outputs]
+    return sorted(range(len(outputs)), key=lambda i: -scores[i])
