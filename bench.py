@@ -1,0 +1,216 @@
+"""Headline benchmark: offline output tokens/s of a Llama-3-70B-architecture model with block-scaled
+FP8 weights (128x128 scale blocks, fp32 scales) and bf16 activations, tensor parallel over N GPUs.
+
+One "step" is one offline batch: B random prompts of 2048 tokens, 256 greedy output tokens each
+(ignore_eos), run through the engine's public ``LLM.generate`` (C++ scheduler, paged KV cache,
+chunked prefill, native kernels). The same total work is done at every N (strong scaling).
+
+  python bench.py --gpus N --steps K --warmup W            (N > 1: launched with torchrun)
+  python bench.py --impl reference ...                     (prints the reference arm's status line)
+
+Timing: W untimed warm-up steps, then K steps bracketed by barrier + synchronize, timed with CUDA
+events on the compute stream, max over ranks. The working set (70 GB of weights per pass) is far
+larger than L2, so no explicit L2 flush is needed. ``e2e`` repeats K steps timed by the host clock
+around the public API call; every engine step inside copies its inputs from pinned host memory and
+reads the sampled tokens back.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+REFERENCE_UNAVAILABLE = ("refused by a safety check: installing the reference (pip install of /root/reference, which "
+                         "runs its setup.py / CMake build) was denied in this environment, so baseline/_ref does not exist")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def llama3_70b():
+    from ksanallm_b200.config import ModelConfig
+    return ModelConfig(model_type="llama", hidden_size=8192, num_layers=80, num_heads=64, num_kv_heads=8, head_dim=128,
+                       intermediate_size=28672, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0,
+                       max_position_embeddings=8192, max_token_len=8192, eos_token_ids=[128001])
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--input-len", type=int, default=2048)
+    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import numpy as np
+    import torch
+    from ksanallm_b200.config import EngineConfig
+    from ksanallm_b200.llm import LLM
+    from ksanallm_b200.ops import native
+    from ksanallm_b200.utils import native_engine as ne
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            print(json.dumps({"error": "launch with torchrun for --gpus > 1"}))
+            return 2
+    mc = llama3_70b()
+    if args.layers:
+        mc.num_layers = args.layers
+    B, S_in, S_out = args.batch, args.input_len, args.output_len
+    ec = EngineConfig()
+    ec.global_.comm_backend = args.comm
+    ec.global_.enable_cuda_graph = not args.no_graphs
+    ec.batch_scheduler.max_batch_size = max(B, 8)
+    ec.batch_scheduler.max_token_len = S_in + S_out + 16
+    ec.batch_scheduler.max_step_tokens = 16384
+    ec.batch_scheduler.max_waiting_queue_len = 4096
+    ec.batch_scheduler.preempt_mode = 1
+    ec.block_manager.block_token_num = 16
+    blocks_per_seq = (S_in + S_out + 15) // 16 + 1
+    ec.block_manager.device_blocks_num = B * blocks_per_seq + 4 * max(B, 8) + 64
+    ec.quantization.weight_quant_method = "fp8_block"
+    llm = LLM(ec, mc, weights="random", device="cuda", max_positions=S_in + S_out + 64)
+    dev = llm.device
+    s = ne.SamplingConfig()
+    s.max_new_tokens, s.ignore_eos, s.topk = S_out, True, 1
+    rng = np.random.default_rng(1234)
+
+    def one_step(i):
+        prompts = [rng.integers(0, mc.vocab_size, S_in).tolist() for _ in range(B)] if rank == 0 else []
+        reqs = llm.generate(prompts, s)
+        if rank == 0:
+            assert all(len(r.outputs[0].tokens) == S_out for r in reqs), "short generation"
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        one_step(i)
+    barrier()
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    l0, h0, d0 = native.launch_count(), llm.engine.runner.h2d_bytes, llm.engine.sampler.d2h_bytes
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        one_step(i)
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    launches = native.launch_count() - l0
+    h2d = (llm.engine.runner.h2d_bytes - h0) / max(args.steps, 1)
+    d2h = (llm.engine.sampler.d2h_bytes - d0) / max(args.steps, 1)
+    # end-to-end arm: host clock around the public API (inputs are host lists -> pinned staging -> H2D each
+    # engine step; sampled tokens are read back every engine step)
+    e2e_ms = None
+    if not args.no_e2e:
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            one_step(i)
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1000.0
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms, e2e_ms or 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), (float(t[1]) if e2e_ms is not None else None)
+    native.check_err_flag(dev)
+    if rank == 0:
+        out_tokens = args.steps * B * S_out
+        value = out_tokens / (ms / 1000.0)
+        res = {
+            "metric": "output tok/s (offline, max over ranks) at Llama-3-70B fp8 TP%d" % world,
+            "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8-e4m3 block-scaled weights (128x128, fp32 scales), bf16 activations", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": "Llama-3-70B architecture, random-init N(0,0.02)" + (" [DEBUG %d layers: INVALID]" % args.layers if args.layers else ""),
+                       "global_batch": B, "seq_len": S_in, "output_len": S_out, "parallelism": "tp%d" % world,
+                       "comm": args.comm, "kv_block_tokens": 16, "cuda_graph_decode": not args.no_graphs,
+                       "l2": "inputs larger than L2 (weights 70 GB per pass); no explicit flush"},
+            "clocks": clocks, "gpu_launches": launches,
+            "graph_replays": getattr(llm.engine.runner, "graph_replays", 0),
+        }
+        if e2e_ms is not None:
+            res["e2e"] = {"value": out_tokens / (e2e_ms / 1000.0), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                          "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps}
+        print(json.dumps(res))
+    llm.shutdown()
+    if world > 1:
+        import torch.distributed as dist
+        if rank == 0:
+            from ksanallm_b200.parallel.control import broadcast_plan
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,416 @@
+// Skinny GEMM for decode steps (M <= 128 tokens) on tcgen05 tensor cores:
+//
+//   D[M,N] = X[M,K] * W[N,K]^T (+bias)(+residual)
+//
+// A decode GEMM is a weight stream: every byte of W is read once and the math is
+// negligible, so the kernel is organised around keeping HBM busy.
+//   * Operands are swapped: the 128-row MMA dimension carries weight rows (a full
+//     128-byte-swizzled TMA tile of W per stage, all of it useful), the MMA N
+//     dimension carries the (padded) tokens. TMEM lane = output feature, TMEM
+//     column = token.
+//   * K is split across CTAs so that small N still fills all SMs; partial tiles
+//     go to a scratch buffer and the last CTA to arrive for an output tile sums
+//     them in a fixed order (deterministic), adds bias/residual and writes bf16.
+//     Counters are reset by that CTA, so the scratch needs no host-side clearing
+//     between launches once it started zeroed.
+//   * FP8 (e4m3 x e4m3, 1x128 activation scales, 128x128 weight scales): each
+//     128-deep K block lands in a fresh TMEM accumulator and is promoted into
+//     fp32 registers with its per-token scale.
+// Same warp roles and bounded waits as gemm_tcgen05.cu. No cluster multicast.
+#include "sm100_ptx.cuh"
+#include <cuda_bf16.h>
+#include <stdio.h>
+
+namespace ksana {
+
+constexpr int kSmThreads = 192;
+constexpr int kSmRowBytes = 128;
+constexpr int kSmSmemBudget = 200 * 1024;
+
+struct SmallMParams {
+  int M, N, K;
+  __nv_bfloat16* D; float* out_f32; int ldd;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual; int ldr;
+  const float* a_scale; int a_scale_ld;   // [K/128][ld]
+  const float* w_scale;                   // [ceil(N/128)][K/128]
+  int seg_cap;                            // scratch slots per output tile
+  float* scratch;                         // [n_tiles][seg_cap][MP][128] fp32 partial tiles
+  unsigned int* counters;                 // [n_tiles], zero before the first launch
+  int* err;
+};
+
+template <int MP, int KIND>   // MP: padded token count (16..128); KIND 0 bf16, 1 fp8 block-scaled
+struct SmallMCfg {
+  static constexpr int kWBytes = 128 * kSmRowBytes;
+  static constexpr int kXBytes = MP * kSmRowBytes;
+  static constexpr int kStageBytes = kWBytes + kXBytes;
+  static constexpr int kStagesRaw = kSmSmemBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
+  static constexpr int kAccStages = KIND == 0 ? 2 : ((512 / MP) > 4 ? 4 : (512 / MP));
+  static constexpr int kTmemCols = (kAccStages * MP) < 32 ? 32 : (kAccStages * MP);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+  static constexpr int kElems = KIND == 0 ? 64 : 128;
+};
+
+// Work decomposition ("stream-K"): the (tile, k-block) units of the whole GEMM are laid out in one
+// line and cut into gridDim.x equal pieces, one per persistent CTA. A piece is a list of segments
+// (tile, kb0, kb1); a tile cut across CTAs is finished by whichever CTA arrives last.
+struct Segment { int tile, kb0, kb1; };
+
+__device__ __forceinline__ long long cut(long long c, long long U, long long P) { return c * U / P; }
+
+__device__ __forceinline__ bool next_segment(long long& u, long long end, int num_kb, Segment& s) {
+  if (u >= end) return false;
+  s.tile = static_cast<int>(u / num_kb);
+  s.kb0 = static_cast<int>(u % num_kb);
+  const long long room = end - u;
+  s.kb1 = static_cast<int>(room < (num_kb - s.kb0) ? s.kb0 + room : num_kb);
+  u += s.kb1 - s.kb0;
+  return true;
+}
+
+// CTA that owns unit x
+__device__ __forceinline__ int owner_of(long long x, long long U, long long P) {
+  long long c = x * P / U;
+  while (c + 1 < P && cut(c + 1, U, P) <= x) ++c;
+  while (c > 0 && cut(c, U, P) > x) --c;
+  return static_cast<int>(c);
+}
+
+template <int MP, int KIND>
+__global__ void __launch_bounds__(kSmThreads, 1)
+gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
+                   const SmallMParams p) {
+  using Cfg = SmallMCfg<MP, KIND>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::kStages;
+  uint64_t* tfull_bar = bars + 2 * Cfg::kStages;
+  uint64_t* tempty_bar = tfull_bar + Cfg::kAccStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + Cfg::kAccStages);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint32_t* last_flag = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (p.N + 127) / 128;
+  const int num_kb = (p.K + Cfg::kElems - 1) / Cfg::kElems;
+  const long long U = static_cast<long long>(n_tiles) * num_kb, P = gridDim.x;
+  const long long u_begin = cut(blockIdx.x, U, P), u_end = cut(blockIdx.x + 1, U, P);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128); }
+    *abort_flag = 0;
+    *last_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_w);
+      tma_prefetch_desc(&tma_x);
+      int stage = 0; uint32_t phase = 0;
+      long long u = u_begin; Segment sg; bool ok = true;
+      while (ok && next_segment(u, u_end, num_kb, sg)) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sw = smem + stage * Cfg::kStageBytes;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_2d(sw, &tma_w, &full_bar[stage], kb * Cfg::kElems, sg.tile * 128);
+          tma_load_2d(sw + Cfg::kWBytes, &tma_x, &full_bar[stage], kb * Cfg::kElems, 0);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = KIND == 0 ? make_idesc(128, MP, 1, 1) : make_idesc(128, MP, 0, 0);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      long long u = u_begin; Segment sg; bool ok = true;
+      while (ok && next_segment(u, u_end, num_kb, sg)) {
+        if (KIND == 0) {
+          if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+        }
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if (KIND == 1) {
+            if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+          }
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sw = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint64_t wdesc = make_smem_desc_sw128(sw);
+          const uint64_t xdesc = make_smem_desc_sw128(sw + Cfg::kWBytes);
+          const uint32_t d_tmem = tmem_base + acc * MP;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t accum = KIND == 0 ? ((kb != sg.kb0) || k != 0) : (k != 0);
+            if (KIND == 0) mma_f16(d_tmem, wdesc + 2 * k, xdesc + 2 * k, idesc, accum);
+            else mma_f8(d_tmem, wdesc + 2 * k, xdesc + 2 * k, idesc, accum);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+          if (KIND == 1) {
+            tc_commit(&tfull_bar[acc]);
+            if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+          }
+        }
+        if (KIND == 0 && ok) {
+          tc_commit(&tfull_bar[acc]);
+          if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    const int nrow = q * 32 + lane;          // output feature inside the tile
+    int acc = 0; uint32_t acc_phase = 0;
+    const int nkb_scale = (p.K + 127) / 128;
+    long long u = u_begin; Segment sg; bool ok = true;
+    while (ok && next_segment(u, u_end, num_kb, sg)) {
+      const int n = sg.tile * 128 + nrow;
+      float accv[MP];
+#pragma unroll
+      for (int i = 0; i < MP; ++i) accv[i] = 0.f;
+      if (KIND == 0) {
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if constexpr (MP >= 32) {
+#pragma unroll
+          for (int c0 = 0; c0 < MP; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + lane_base + acc * MP + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) accv[c0 + i] = __uint_as_float(r[i]);
+          }
+        } else {
+          uint32_t r[16];
+          tmem_ld16(tmem_base + lane_base + acc * MP, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) accv[i] = __uint_as_float(r[i]);
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty_bar[acc]);
+        if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+      } else {
+        const float* ws = p.w_scale + static_cast<size_t>(sg.tile) * nkb_scale;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          const float wsc = ws[kb];
+          const float* as = p.a_scale + static_cast<size_t>(kb) * p.a_scale_ld;
+          if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          if constexpr (MP >= 32) {
+#pragma unroll
+            for (int c0 = 0; c0 < MP; c0 += 32) {
+              uint32_t r[32];
+              tmem_ld32(tmem_base + lane_base + acc * MP + c0, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float sc = (c0 + i < p.M) ? as[c0 + i] * wsc : 0.f;
+                accv[c0 + i] = fmaf(sc, __uint_as_float(r[i]), accv[c0 + i]);
+              }
+            }
+          } else {
+            uint32_t r[16];
+            tmem_ld16(tmem_base + lane_base + acc * MP, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float sc = (i < p.M) ? as[i] * wsc : 0.f;
+              accv[i] = fmaf(sc, __uint_as_float(r[i]), accv[i]);
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(&tempty_bar[acc]);
+          if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+        }
+        if (!ok) break;
+      }
+
+      auto finish = [&](const float (&v)[MP]) {
+        if (n >= p.N) return;
+        const float b = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+          if (m < p.M) {
+            float o = v[m] + b;
+            if (p.residual) o += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n]);
+            if (p.out_f32) p.out_f32[static_cast<size_t>(m) * p.ldd + n] = o;
+            else p.D[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16(o);
+          }
+        }
+      };
+
+      if (sg.kb0 == 0 && sg.kb1 == num_kb) {
+        finish(accv);                        // this CTA covered the whole K range of the tile
+      } else {
+        const long long t0 = static_cast<long long>(sg.tile) * num_kb;
+        const int first = owner_of(t0, U, P), lastc = owner_of(t0 + num_kb - 1, U, P);
+        const int nseg = lastc - first + 1;
+        const int my = static_cast<int>(blockIdx.x) - first;
+        float* tile_scratch = p.scratch + static_cast<size_t>(sg.tile) * p.seg_cap * MP * 128;
+        float* mine = tile_scratch + static_cast<size_t>(my) * MP * 128;
+#pragma unroll
+        for (int m = 0; m < MP; ++m) mine[m * 128 + nrow] = accv[m];
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const unsigned int prev = atomicAdd(&p.counters[sg.tile], 1u);
+          const bool last = prev == static_cast<unsigned int>(nseg - 1);
+          if (last) p.counters[sg.tile] = 0;   // ready for the next launch
+          *last_flag = last ? 1u : 0u;
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          float sum[MP];
+#pragma unroll
+          for (int m = 0; m < MP; ++m) sum[m] = 0.f;
+          for (int sgi = 0; sgi < nseg; ++sgi) {       // fixed order: deterministic sums
+            const volatile float* src = tile_scratch + static_cast<size_t>(sgi) * MP * 128;
+#pragma unroll
+            for (int m = 0; m < MP; ++m) sum[m] += src[m * 128 + nrow];
+          }
+          finish(sum);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is reused by the next segment
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, 2);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, Cfg::kTmemCols); }
+}
+
+// ------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn2 encode_fn2() {
+  static EncodeTiledFn2 fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn2>(ptr);
+  }
+  return fn;
+}
+static int make_map2(CUtensorMap* map, const void* base, int rows, int cols, int ld, int esz, int box_rows) {
+  EncodeTiledFn2 enc = encode_fn2();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * esz};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kSmRowBytes / esz), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int MP, int KIND>
+static int launch_smallm(const CUtensorMap& mw, const CUtensorMap& mx, const SmallMParams& p, int ctas,
+                         cudaStream_t st) {
+  using Cfg = SmallMCfg<MP, KIND>;
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(gemm_smallm_kernel<MP, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes) != cudaSuccess) return -3;
+    set = true;
+  }
+  gemm_smallm_kernel<MP, KIND><<<ctas, kSmThreads, Cfg::kSmemBytes, st>>>(mw, mx, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace ksana
+
+using namespace ksana;
+
+// Scratch needed: n_tiles * seg_cap * MP * 128 * 4 bytes (seg_cap = pieces a tile can be cut into);
+// counters: n_tiles words, zero before the first launch (the kernel leaves them zero).
+// kind 0: X, W bf16. kind 1: e4m3 with scales. ctas_hint > 0 fixes the number of persistent CTAs
+// (1 = no K splitting at all when there is a single tile per CTA...). Returns 0 on success; -20 when M > 128.
+extern "C" int ksana_gemm_smallm(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld, const void* W,
+                                 int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
+                                 const void* residual, int ldr, int M, int N, int K, int ctas_hint, void* scratch,
+                                 long long scratch_bytes, void* counters, int counters_len, int* err_flag,
+                                 cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > 128) return -20;
+  const int esz = kind == 0 ? 2 : 1;
+  if ((K % (kind == 0 ? 8 : 128)) || (ldx % (16 / esz)) || (ldw % (16 / esz))) return -10;
+  const int MP = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  const int n_tiles = (N + 127) / 128;
+  const int num_kb = (K + (kind == 0 ? 64 : 128) - 1) / (kind == 0 ? 64 : 128);
+  int sms = 148;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const long long U = static_cast<long long>(n_tiles) * num_kb;
+  long long P = ctas_hint > 0 ? ctas_hint : sms;
+  if (P > sms) P = sms;
+  if (P > U / 4) P = U / 4 > 0 ? U / 4 : 1;      // at least four k-blocks per CTA
+  // a tile may be cut only if scratch and counters can hold the pieces
+  auto seg_cap_for = [&](long long ctas) {
+    const long long per = U / ctas;               // smallest piece
+    return static_cast<int>((num_kb + per - 1) / per + 1);
+  };
+  int seg_cap = seg_cap_for(P);
+  const bool can_split = scratch != nullptr && counters != nullptr && counters_len >= n_tiles;
+  while (P > 1 && (!can_split || static_cast<long long>(n_tiles) * seg_cap * MP * 128 * 4 > scratch_bytes)) {
+    // fall back to whole tiles per CTA: pieces end on tile boundaries when P divides n_tiles evenly
+    P = can_split ? P / 2 : 1;
+    if (P < 1) P = 1;
+    seg_cap = seg_cap_for(P);
+    if (!can_split) break;
+  }
+  if (!can_split && P != 1) P = 1;
+  CUtensorMap mw, mx;
+  if (make_map2(&mw, W, N, K, ldw, esz, 128)) return -12;
+  if (make_map2(&mx, X, M, K, ldx, esz, MP)) return -13;
+  SmallMParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.D = static_cast<__nv_bfloat16*>(D); p.out_f32 = static_cast<float*>(out_f32); p.ldd = ldd;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+  p.a_scale = a_scale; p.a_scale_ld = a_scale_ld; p.w_scale = w_scale;
+  p.seg_cap = seg_cap; p.scratch = static_cast<float*>(scratch); p.counters = static_cast<unsigned int*>(counters);
+  p.err = err_flag;
+  const int ctas = static_cast<int>(P);
+#define KSANA_SM_DISPATCH(MPV)                                                                        \
+  case MPV: return kind == 0 ? launch_smallm<MPV, 0>(mw, mx, p, ctas, st) : launch_smallm<MPV, 1>(mw, mx, p, ctas, st);
+  switch (MP) {
+    KSANA_SM_DISPATCH(16)
+    KSANA_SM_DISPATCH(32)
+    KSANA_SM_DISPATCH(64)
+    KSANA_SM_DISPATCH(128)
+  }
+#undef KSANA_SM_DISPATCH
+  return -21;
+}

@@ -30,7 +30,6 @@ namespace ksana {
 
 constexpr int kBM = 128;          // rows per tile = TMEM lanes
 constexpr int kRowBytes = 128;    // one swizzled smem row: 64 bf16 or 128 fp8
-constexpr int kGemmThreads = 192;
 constexpr int kSmemBudget = 200 * 1024;
 
 enum GemmKind { kBf16 = 0, kFp8Block = 1 };
@@ -47,6 +46,11 @@ struct GemmParams {
   int a_scale_ld;
   const float* w_scale;   // fp8: [ceil(N/128)][K/128]
   int* err;               // device word, set non-zero when a bounded wait gave up
+  // grouped (mixture-of-experts) mode: row tile i multiplies with expert tile_expert[i] (< 0: tile unused);
+  // W stacks the experts as [E * expert_rows, K] and w_scale as [E * scale_rows_per_expert][K/128].
+  const int* tile_expert;
+  int expert_rows;
+  int scale_rows_per_expert;
 };
 
 template <int BN, int KIND>
@@ -57,14 +61,32 @@ struct GemmCfg {
   static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr int kAccStages = (KIND == kBf16) ? 2 : ((512 / BN) > 4 ? 4 : (512 / BN));
+  // FP8 promotion costs one FMA per accumulator element per 128-deep K block; with 256-wide tiles two
+  // epilogue warpgroups split the columns so that promotion keeps up with the tensor pipe.
+  static constexpr int kEpiWG = (KIND == kFp8Block && BN == 256) ? 2 : 1;
+  static constexpr int kThreads = 64 + 128 * kEpiWG;
+  static constexpr int kEpiCols = BN / kEpiWG;
   static constexpr int kTmemCols = kAccStages * BN < 32 ? 32 : kAccStages * BN;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 512 /*barriers*/;
   static constexpr int kElemsPerRow = (KIND == kBf16) ? 64 : 128;  // K elements per stage
   static constexpr int kMmaK = (KIND == kBf16) ? 16 : 32;
 };
 
+// Tile order: groups of kGroupM row-tiles sweep all column-tiles before the next group starts, so the
+// CTAs running at any moment share a few A panels and W panels that stay resident in L2.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& m_blk, int& n_blk) {
+  const int per_group = kGroupM * n_tiles;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int gsz = min(m_tiles - first_m, kGroupM);
+  const int in_group = tile - group * per_group;
+  m_blk = first_m + in_group % gsz;
+  n_blk = in_group / gsz;
+}
+
 template <int BN, int KIND>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(GemmCfg<BN, KIND>::kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const GemmParams p) {
   using Cfg = GemmCfg<BN, KIND>;
@@ -87,7 +109,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-    for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128); }
+    for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128 * Cfg::kEpiWG); }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -108,15 +130,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * kBM;
-        const int n0 = (tile / m_tiles) * BN;
+        int m_blk, n_blk;
+        tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
+        const int m0 = m_blk * kBM;
+        const int n0 = n_blk * BN;
+        int w_row0 = n0;
+        if (p.tile_expert) {
+          const int e = p.tile_expert[m_blk];
+          if (e < 0) continue;
+          w_row0 = e * p.expert_rows + n0;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           tma_load_2d(sa, &tma_a, &full_bar[stage], kb * Cfg::kElemsPerRow, m0);
-          tma_load_2d(sb, &tma_b, &full_bar[stage], kb * Cfg::kElemsPerRow, n0);
+          tma_load_2d(sb, &tma_b, &full_bar[stage], kb * Cfg::kElemsPerRow, w_row0);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -129,6 +159,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (p.tile_expert) {
+          int m_blk, n_blk;
+          tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
+          if (p.tile_expert[m_blk] < 0) continue;
+        }
         if (KIND == kBf16) {
           if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
@@ -168,11 +203,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;                     // TMEM lane quarter this warp may touch
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    const int wg = (warp - 2) >> 2;             // epilogue warpgroup -> column slice of the tile
+    constexpr int EC = Cfg::kEpiCols;
+    const int col_off = wg * EC;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % m_tiles) * kBM;
-      const int n0 = (tile / m_tiles) * BN;
+      int m_blk, n_blk;
+      tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
+      const int m0 = m_blk * kBM;
+      const int n0 = n_blk * BN + col_off;
+      int expert = 0;
+      if (p.tile_expert) {
+        expert = p.tile_expert[m_blk];
+        if (expert < 0) continue;
+      }
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
 
@@ -229,19 +274,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         mbar_arrive(&tempty_bar[acc]);
         if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
       } else {
-        float accv[BN];
+        float accv[EC];
 #pragma unroll
-        for (int i = 0; i < BN; ++i) accv[i] = 0.f;
+        for (int i = 0; i < EC; ++i) accv[i] = 0.f;
         const int nkb_scale = (p.K + 127) / 128;
-        const float* ws = p.w_scale + static_cast<size_t>(n0 / 128) * nkb_scale;
+        const float* ws = p.w_scale + (static_cast<size_t>(expert) * p.scale_rows_per_expert + n0 / 128) * nkb_scale;
         for (int kb = 0; kb < num_kb; ++kb) {
           const float s = (row_ok ? p.a_scale[static_cast<size_t>(kb) * p.a_scale_ld + row] : 0.f) * ws[kb];
           if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int c0 = 0; c0 < BN; c0 += 32) {
+          for (int c0 = 0; c0 < EC; c0 += 32) {
             uint32_t r[32];
-            tmem_ld32(tmem_base + lane_base + acc * BN + c0, r);
+            tmem_ld32(tmem_base + lane_base + acc * BN + col_off + c0, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) accv[c0 + i] = fmaf(s, __uint_as_float(r[i]), accv[c0 + i]);
@@ -252,7 +297,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         if (ok) {
 #pragma unroll
-          for (int c0 = 0; c0 < BN; c0 += 32) {
+          for (int c0 = 0; c0 < EC; c0 += 32) {
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = accv[c0 + i];
@@ -337,18 +382,18 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  gemm_tcgen05_kernel<BN, KIND><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ma, mb, p);
+  gemm_tcgen05_kernel<BN, KIND><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 static int pick_bn(int M, int N, int kind, int bn_hint) {
-  if (bn_hint == 32 || bn_hint == 64 || bn_hint == 128 || (bn_hint == 256 && kind == kBf16)) return bn_hint;
+  if (bn_hint == 32 || bn_hint == 64 || bn_hint == 128 || bn_hint == 256) return bn_hint;
   const int sms = num_sms();
   const int m_tiles = (M + kBM - 1) / kBM;
   const int cands_bf16[4] = {256, 128, 64, 32};
-  const int cands_fp8[3] = {128, 64, 32};
-  const int* c = kind == kBf16 ? cands_bf16 : cands_fp8;
-  const int nc = kind == kBf16 ? 4 : 3;
+  const int* c = cands_bf16;
+  const int nc = 4;
+  (void)kind;
   for (int i = 0; i < nc; ++i) {
     const int tiles = m_tiles * ((N + c[i] - 1) / c[i]);
     if (tiles >= sms) return c[i];   // at least one full wave with the widest tile that allows it
@@ -407,8 +452,45 @@ extern "C" int ksana_gemm_fp8_block(const void* Aq, int lda, const float* a_scal
   p.a_scale = a_scale; p.a_scale_ld = a_scale_ld; p.w_scale = w_scale;
   p.err = err_flag;
   switch (bn) {
+    case 256: return launch_gemm<256, kFp8Block>(ma, mb, p, max_ctas, stream);
     case 128: return launch_gemm<128, kFp8Block>(ma, mb, p, max_ctas, stream);
     case 64: return launch_gemm<64, kFp8Block>(ma, mb, p, max_ctas, stream);
     default: return launch_gemm<32, kFp8Block>(ma, mb, p, max_ctas, stream);
+  }
+}
+
+// Grouped GEMM for mixture-of-experts: rows of A are expert-major (each expert's segment padded to a
+// multiple of 128 rows), tile_expert[m_tile] names the expert of every 128-row tile (-1 = unused).
+// W: [E*N, K]; w_scale (fp8): [E * ceil(N/128)][K/128]. kind 0 = bf16, 1 = block-scaled fp8.
+extern "C" int ksana_gemm_grouped(int kind, const void* A, int lda, const float* a_scale, int a_scale_ld, const void* W,
+                                  int ldw, const float* w_scale, void* D, int ldd, int M_cap, int N, int K, int E,
+                                  const int* tile_expert, int bn_hint, int* err_flag, cudaStream_t stream) {
+  if (M_cap <= 0 || N <= 0 || K <= 0 || E <= 0) return 0;
+  const int esz = kind == kBf16 ? 2 : 1;
+  if ((N % 8) || (K % (kind == kBf16 ? 8 : 128)) || (lda % (16 / esz)) || (ldw % (16 / esz)) || (ldd % 8) || (M_cap % 128)) return -10;
+  int bn = (bn_hint == 32 || bn_hint == 64 || bn_hint == 128 || bn_hint == 256) ? bn_hint : (N % 256 == 0 ? 256 : 128);
+  if (kind == kFp8Block && N % 128) return -14;
+  CUtensorMap ma, mb;
+  if (make_operand_map(&ma, A, M_cap, K, lda, esz, kBM)) return -12;
+  if (make_operand_map(&mb, W, E * N, K, ldw, esz, bn)) return -13;
+  GemmParams p{};
+  p.M = M_cap; p.N = N; p.K = K;
+  p.D = static_cast<__nv_bfloat16*>(D); p.ldd = ldd;
+  p.a_scale = a_scale; p.a_scale_ld = a_scale_ld; p.w_scale = w_scale;
+  p.err = err_flag;
+  p.tile_expert = tile_expert; p.expert_rows = N; p.scale_rows_per_expert = (N + 127) / 128;
+  if (kind == kBf16) {
+    switch (bn) {
+      case 256: return launch_gemm<256, kBf16>(ma, mb, p, 0, stream);
+      case 128: return launch_gemm<128, kBf16>(ma, mb, p, 0, stream);
+      case 64: return launch_gemm<64, kBf16>(ma, mb, p, 0, stream);
+      default: return launch_gemm<32, kBf16>(ma, mb, p, 0, stream);
+    }
+  }
+  switch (bn) {
+    case 256: return launch_gemm<256, kFp8Block>(ma, mb, p, 0, stream);
+    case 128: return launch_gemm<128, kFp8Block>(ma, mb, p, 0, stream);
+    case 64: return launch_gemm<64, kFp8Block>(ma, mb, p, 0, stream);
+    default: return launch_gemm<32, kFp8Block>(ma, mb, p, 0, stream);
   }
 }

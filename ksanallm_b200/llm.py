@@ -1,0 +1,168 @@
+"""Offline / embedded entry point: builds the model, the KV cache and the engine from a serving
+YAML (or explicit configs) and exposes ``generate``. One process per GPU; with ``WORLD_SIZE`` > 1
+(torchrun) the ranks form one tensor-parallel group, rank 0 schedules and the others follow the
+broadcast step plans (the reference runs one thread per GPU inside one process instead:
+src/ksana_llm/runtime/worker.cpp:43-54).
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from .config import EngineConfig, ModelConfig, check_tp, load_kv_scales, load_model_config, load_yaml_config
+from .models.weights import CheckpointSource, RandomSource, build_model
+from .parallel.comm import TPComm
+from .runtime.engine import LLMEngine
+from .utils import native_engine as ne
+
+
+def _dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def init_distributed(device_type: str):
+    """Process groups for the tensor-parallel run: a device group (NCCL / gloo) for collectives and a
+    CPU gloo group for step-plan broadcast. Rendezvous uses MASTER_ADDR / MASTER_PORT (127.0.0.1 on one node)."""
+    import torch.distributed as dist
+    rank, world, local = _dist_env()
+    if world == 1:
+        return 0, 1, None, None
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    if not dist.is_initialized():
+        backend = "nccl" if device_type == "cuda" else "gloo"
+        if device_type == "cuda":
+            torch.cuda.set_device(local)
+            dist.init_process_group(backend, rank=rank, world_size=world, device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group(backend, rank=rank, world_size=world)
+    dev_group = dist.group.WORLD
+    ctl_group = dist.new_group(backend="gloo") if device_type == "cuda" else dev_group
+    return rank, world, dev_group, ctl_group
+
+
+def kv_dtype_from(cfg: EngineConfig, default):
+    k = cfg.quantization.kv_cache_dtype
+    if k == "fp8_e4m3":
+        return torch.float8_e4m3fn
+    if k == "fp8_e5m2":
+        return torch.float8_e4m3fn   # stored as e4m3 (the tensor-core friendly 8-bit format on sm_100a)
+    return default
+
+
+def auto_num_blocks(cfg: EngineConfig, block_bytes: int, device) -> int:
+    """Device blocks from free memory: (free - reserved share) / block bytes, or the explicit ratio
+    (src/ksana_llm/block_manager/block_manager.cpp:102-163)."""
+    bm = cfg.block_manager
+    if bm.device_blocks_num > 0:
+        return bm.device_blocks_num
+    if torch.device(device).type != "cuda":
+        return 256
+    free, total = torch.cuda.mem_get_info(device)
+    if bm.block_device_memory_ratio >= 0:
+        budget = int(total * bm.block_device_memory_ratio)
+    else:
+        budget = free - int(total * bm.reserved_device_memory_ratio)
+    return max(int(budget // block_bytes), 0)
+
+
+def auto_host_blocks(cfg: EngineConfig, num_device_blocks: int, block_bytes: int) -> int:
+    bm = cfg.block_manager
+    if bm.host_blocks_num > 0:
+        return bm.host_blocks_num
+    if cfg.batch_scheduler.preempt_mode != 0:
+        return 0
+    try:
+        import psutil
+        host_free = psutil.virtual_memory().available
+    except Exception:  # noqa: BLE001
+        host_free = 8 << 30
+    return int(min(num_device_blocks * bm.block_host_memory_factor, 0.8 * host_free / block_bytes))
+
+
+class LLM:
+    def __init__(self, engine_cfg: Optional[EngineConfig] = None, model_cfg: Optional[ModelConfig] = None,
+                 config_file: Optional[str] = None, weights="checkpoint", device: Optional[str] = None,
+                 dtype=torch.bfloat16, tokenizer=None, seed: int = 0, max_positions: Optional[int] = None):
+        if config_file is not None:
+            engine_cfg = load_yaml_config(config_file)
+        self.engine_cfg = engine_cfg or EngineConfig()
+        if model_cfg is None:
+            model_cfg = load_model_config(self.engine_cfg.model_dir)
+        self.model_cfg = model_cfg
+        dev_type = "cuda" if (device is None and torch.cuda.is_available()) or (device and "cuda" in str(device)) else "cpu"
+        self.rank, self.world, dev_group, ctl_group = init_distributed(dev_type)
+        local = _dist_env()[2]
+        self.device = torch.device("cuda", local) if dev_type == "cuda" else torch.device("cpu")
+        if dev_type == "cuda":
+            torch.cuda.set_device(self.device)
+        tp = self.world
+        check_tp(model_cfg, tp)
+        self.comm = TPComm(dev_group, self.rank, tp, self.engine_cfg.global_.comm_backend if dev_type == "cuda" else "nccl",
+                           self.device) if tp > 1 else None
+        quant = self.engine_cfg.quantization.weight_quant_method
+        quant = {"auto": None, "fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "nvfp4": "fp8_block"}[quant]
+        if model_cfg.fp8_checkpoint and quant is None:
+            quant = "fp8_block"
+        if weights == "random":
+            source = RandomSource(seed=seed, on_device=dev_type == "cuda" and model_cfg.hidden_size >= 2048)
+        elif weights == "checkpoint":
+            source = CheckpointSource(self.engine_cfg.model_dir, model_cfg.model_type)
+        else:
+            source = weights
+        kv_path = os.path.join(self.engine_cfg.model_dir or ".", "kv_cache_scales.json")
+        if self.engine_cfg.quantization.kv_cache_dtype != "auto" and os.path.exists(kv_path):
+            model_cfg.kv_scales = load_kv_scales(kv_path, model_cfg.num_layers)
+        mp = max_positions or min(model_cfg.max_token_len, max(self.engine_cfg.batch_scheduler.max_token_len, 16))
+        self.model = build_model(model_cfg, source, self.rank, tp, self.comm, self.device, dtype, quant,
+                                 max_positions=mp)
+        kv_dtype = kv_dtype_from(self.engine_cfg, dtype)
+        bt = self.engine_cfg.block_manager.block_token_num
+        probe = self.model.allocate_kv_cache(1, bt, kv_dtype)
+        block_bytes = probe[0].numel() * probe.element_size()
+        self.model.kv_cache = None
+        nblocks = auto_num_blocks(self.engine_cfg, block_bytes, self.device)
+        nhost = auto_host_blocks(self.engine_cfg, nblocks, block_bytes)
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([nblocks, nhost], dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=ctl_group)
+            nblocks, nhost = int(t[0]), int(t[1])
+        self.engine = LLMEngine(self.model, model_cfg, self.engine_cfg, nblocks, nhost, tokenizer, kv_dtype,
+                                self.rank, self.world, ctl_group)
+        self.tokenizer = tokenizer
+
+    # ------------------------------------------------------------------ API
+    def generate(self, prompt_token_ids: List[List[int]], sampling=None, timeout: Optional[float] = None):
+        """Blocking batch generation. On ranks other than 0 this serves steps until rank 0 is done."""
+        if self.rank != 0:
+            self.follow()
+            return []
+        reqs = self.engine.generate(prompt_token_ids, sampling, timeout)
+        if self.world > 1:
+            from .parallel.control import broadcast_plan
+            broadcast_plan(self.engine.control_group, np.zeros(0, dtype=np.int32))   # end of this batch
+        return reqs
+
+    def follow(self):
+        """Worker ranks: execute broadcast step plans until the end-of-batch (empty image) or stop (None) signal."""
+        from .parallel.control import broadcast_plan
+        while True:
+            img = broadcast_plan(self.engine.control_group, None)
+            if img is None:
+                return False
+            if img.size == 0:
+                return True
+            plan = ne.StepPlan.unpack(img)
+            self.engine.runner.execute(plan, None)
+
+    def shutdown(self, stop_followers: bool = False):
+        """Stops the engine loop. ``stop_followers`` additionally releases worker ranks blocked in ``follow``."""
+        if self.rank == 0:
+            self.engine.stop()
+            if stop_followers and self.world > 1:
+                from .parallel.control import broadcast_plan
+                broadcast_plan(self.engine.control_group, None)

@@ -1,0 +1,199 @@
+"""Mixture-of-experts block: router -> top-k -> expert-major permutation -> grouped GEMM (gate|up) ->
+act*mul -> grouped GEMM (down) -> top-k weighted combine (+ shared expert), then the tensor-parallel
+reduction and the residual add.
+
+Covers Mixtral (softmax top-2, renormalised), Qwen2-MoE (softmax top-k, optional renorm, shared expert
+with a sigmoid gate) and DeepSeek-V3 (sigmoid scores, correction bias, group-limited top-8, scaling,
+shared experts). Reference semantics: src/ksana_llm/models/common_moe/common_moe_model.cpp:35-63,
+src/ksana_llm/models/qwen2_moe/qwen2_moe_model.cpp:57-130 and the routing kernels in
+3rdparty/LLM_kernels/csrc/kernels/nvidia/mixture_of_experts/moe_kernels.cu:209-433,779 (renorm modes).
+Experts are stacked [E, 2*inter/tp, hidden] and [E, hidden, inter/tp]
+(src/ksana_llm/models/common_moe/common_moe_weight.cpp:31-104); ``expert_range`` restricts a rank to
+its own experts for expert parallelism.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import dispatch as ops
+from ..ops import native, reference as ref
+from ..ops.dispatch import LinearWeight
+
+
+@dataclass
+class MoEWeights:
+    router: torch.Tensor                    # [E, H]
+    router_bias: Optional[torch.Tensor]     # selection-only correction bias [E]
+    w13: torch.Tensor                       # [E * 2I, H]  (gate rows then up rows per expert), bf16 or e4m3
+    w13_scale: Optional[torch.Tensor]
+    w2: torch.Tensor                        # [E * H, I]
+    w2_scale: Optional[torch.Tensor]
+    num_experts: int
+    inter: int
+    hidden: int
+    shared_gate_up: Optional[LinearWeight] = None
+    shared_down: Optional[LinearWeight] = None
+    shared_gate: Optional[torch.Tensor] = None       # [1, H] sigmoid gate of the shared expert (Qwen2-MoE)
+    expert_lo: int = 0
+    expert_hi: int = 0
+
+    def nbytes(self) -> int:
+        n = 0
+        for t in (self.router, self.w13, self.w13_scale, self.w2, self.w2_scale, self.shared_gate):
+            if t is not None:
+                n += t.numel() * t.element_size()
+        for w in (self.shared_gate_up, self.shared_down):
+            if w is not None:
+                n += w.nbytes()
+        return n
+
+
+def _rows(t, rank, size):
+    n = (t.shape[0] + size - 1) // size
+    return t[rank * n:(rank + 1) * n]
+
+
+def _cols(t, rank, size):
+    n = (t.shape[1] + size - 1) // size
+    return t[:, rank * n:(rank + 1) * n]
+
+
+def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dtype, quant, ep_rank=0, ep_size=1):
+    from .weights import RandomSource, _make_linear
+    H, E, I_full = cfg.hidden_size, cfg.num_experts, cfg.moe_intermediate_size
+    I = (I_full + tp_size - 1) // tp_size
+    per = (E + ep_size - 1) // ep_size
+    lo, hi = ep_rank * per, min(E, (ep_rank + 1) * per)
+    rnd = isinstance(source, RandomSource)
+    router = source.get(prefix + "mlp.gate.weight", (E, H), device=device).to(device=device, dtype=torch.float32)
+    rbias = None
+    if cfg.moe_scoring == "sigmoid":
+        name = prefix + "mlp.gate.e_score_correction_bias"
+        if rnd or source.has(name):
+            rbias = source.get(name, (E,), device=device, kind="zeros").to(device=device, dtype=torch.float32)
+    w13_parts, w2_parts = [], []
+    for e in range(E):
+        if not (lo <= e < hi):
+            # experts owned by other expert-parallel ranks keep a zero-size placeholder row range
+            continue
+        ep = f"{prefix}mlp.experts.{e}."
+        if rnd and source.on_device:
+            g_u = source.get(ep + f"gate_up_proj.weight.tp{tp_rank}", (2 * I, H), device=device)
+            d = source.get(ep + f"down_proj.weight.tp{tp_rank}", (H, I), device=device)
+        else:
+            g = _rows(source.get(ep + "gate_proj.weight", (I_full, H), device=device), tp_rank, tp_size)
+            u = _rows(source.get(ep + "up_proj.weight", (I_full, H), device=device), tp_rank, tp_size)
+            g_u = torch.cat([g, u], 0)
+            d = _cols(source.get(ep + "down_proj.weight", (H, I_full), device=device), tp_rank, tp_size)
+        w13_parts.append(g_u.to(device))
+        w2_parts.append(d.to(device))
+    n_local = hi - lo
+    w13 = torch.cat(w13_parts, 0)
+    w2 = torch.cat(w2_parts, 0)
+    w13_s = w2_s = None
+    if quant == "fp8_block" and H % 128 == 0 and I % 128 == 0:
+        w13, w13_s = ref.quant_weight_fp8_block(w13)
+        w2, w2_s = ref.quant_weight_fp8_block(w2)
+    else:
+        w13, w2 = w13.to(dtype).contiguous(), w2.to(dtype).contiguous()
+    mw = MoEWeights(router, rbias, w13, w13_s, w2, w2_s, E, I, H, expert_lo=lo, expert_hi=hi)
+    sI_full = cfg.shared_expert_intermediate_size
+    if sI_full:
+        sp = prefix + "mlp.shared_expert."
+        g = _rows(source.get(sp + "gate_proj.weight", (sI_full, H), device=device), tp_rank, tp_size)
+        u = _rows(source.get(sp + "up_proj.weight", (sI_full, H), device=device), tp_rank, tp_size)
+        d = _cols(source.get(sp + "down_proj.weight", (H, sI_full), device=device), tp_rank, tp_size)
+        mw.shared_gate_up = _make_linear(torch.cat([g, u], 0), None, device, dtype, quant)
+        mw.shared_down = _make_linear(d, None, device, dtype, quant)
+        if cfg.shared_expert_gate:
+            mw.shared_gate = source.get(prefix + "mlp.shared_expert_gate.weight", (1, H), device=device).to(device=device, dtype=dtype)
+    return mw
+
+
+def route_reference(logits, cfg: ModelConfig, bias=None):
+    """Plain statement of the routing rules; returns (ids [T,K] int64, weights [T,K] fp32)."""
+    K = cfg.num_experts_per_tok
+    if cfg.moe_scoring == "sigmoid":
+        score = torch.sigmoid(logits.float())
+    else:
+        score = torch.softmax(logits.float(), dim=-1)
+    sel = score + (bias.float() if bias is not None else 0.0)
+    if cfg.n_group > 1 and cfg.topk_group < cfg.n_group:
+        T, E = sel.shape
+        grp = sel.view(T, cfg.n_group, E // cfg.n_group)
+        gscore = grp.topk(2, dim=-1).values.sum(-1)
+        keep = gscore.topk(cfg.topk_group, dim=-1).indices
+        mask = torch.zeros(T, cfg.n_group, dtype=torch.bool, device=sel.device).scatter_(1, keep, True)
+        sel = sel.masked_fill(~mask.unsqueeze(-1).expand_as(grp).reshape(T, E), float("-inf"))
+    ids = sel.topk(K, dim=-1).indices
+    w = score.gather(1, ids)
+    if cfg.norm_topk_prob:
+        w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+    return ids, w * cfg.routed_scaling_factor
+
+
+def moe_forward(model, mw: MoEWeights, x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+    """h += MoE(x) (reduced over the TP group). ``x`` is the normalised hidden state [T, H] (bf16)."""
+    cfg = model.cfg
+    T, H = x.shape
+    K, E = cfg.num_experts_per_tok, mw.num_experts
+    n_local = mw.expert_hi - mw.expert_lo
+    if x.is_cuda:
+        logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
+        native.gemm_bf16(x, mw.router.to(torch.bfloat16) if mw.router.dtype != torch.bfloat16 else mw.router, out_f32=logits)
+        ids, w = native.moe_route(logits, K, cfg.moe_scoring, cfg.norm_topk_prob, cfg.routed_scaling_factor,
+                                  mw.router_bias, cfg.n_group, cfg.topk_group)
+        dst_row, tile_expert, _, _, cap = native.moe_align(ids, E, mw.expert_lo, mw.expert_hi)
+        if mw.expert_lo:
+            tile_expert = torch.where(tile_expert >= 0, tile_expert - mw.expert_lo, tile_expert)
+        perm = native.moe_permute(x, dst_row, K, cap)
+        if mw.w13_scale is not None:
+            pq, ps = native.quant_fp8(perm)
+            g = native.gemm_grouped(pq, mw.w13, tile_expert, n_local, 2 * mw.inter, a_scale=ps, w_scale=mw.w13_scale)
+            _, aq, as_ = native.act_mul(g, cfg.activation, True, quant=True, want_out=False)
+            y = native.gemm_grouped(aq, mw.w2, tile_expert, n_local, H, a_scale=as_, w_scale=mw.w2_scale)
+        else:
+            g = native.gemm_grouped(perm, mw.w13, tile_expert, n_local, 2 * mw.inter)
+            a = native.act_mul(g, cfg.activation, True)
+            y = native.gemm_grouped(a, mw.w2, tile_expert, n_local, H)
+        out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+        have_shared = mw.shared_gate_up is not None
+        if have_shared:
+            sg = ops.linear(x, mw.shared_gate_up)
+            sa = ops.act_mul(sg, cfg.activation, True, quant_for=mw.shared_down)
+            ops.linear(sa, mw.shared_down, out=out)
+            if mw.shared_gate is not None:
+                gate = torch.sigmoid(x.float() @ mw.shared_gate.float().t())
+                out = (out.float() * gate).to(x.dtype)
+        native.moe_combine(y, dst_row, w, out, K, accumulate=have_shared)
+    else:
+        logits = x.float() @ mw.router.float().t()
+        ids, w = route_reference(logits, cfg, mw.router_bias)
+        out = torch.zeros(T, H, dtype=torch.float32)
+        w13 = ref.dequant_weight_fp8_block(mw.w13, mw.w13_scale) if mw.w13_scale is not None else mw.w13.float()
+        w2 = ref.dequant_weight_fp8_block(mw.w2, mw.w2_scale) if mw.w2_scale is not None else mw.w2.float()
+        for e in range(mw.expert_lo, mw.expert_hi):
+            tok, slot = (ids == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            le = e - mw.expert_lo
+            xe = x[tok].float()
+            gu = xe @ w13[le * 2 * mw.inter:(le + 1) * 2 * mw.inter].t()
+            a = ref.act(gu[:, :mw.inter], cfg.activation) * gu[:, mw.inter:]
+            ye = a @ w2[le * H:(le + 1) * H].t()
+            out.index_add_(0, tok, ye * w[tok, slot].unsqueeze(-1))
+        if mw.shared_gate_up is not None:
+            sg = ops.linear(x, mw.shared_gate_up)
+            sa = ops.act_mul(sg, cfg.activation, True, quant_for=mw.shared_down)
+            so = ops.linear(sa, mw.shared_down).float()
+            if mw.shared_gate is not None:
+                so = so * torch.sigmoid(x.float() @ mw.shared_gate.float().t())
+            out = out + so
+        out = out.to(x.dtype)
+    if model.tp_size > 1:
+        out = model.comm.all_reduce(out)
+    return ops.add(h, out)

@@ -21,6 +21,13 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 _SIGS = {
     "ksana_gemm_bf16": [vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_fp8_block": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+    "ksana_gemm_smallm": [i32, vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i64, vp, i32,
+                          vp, vp],
+    "ksana_gemm_grouped": [i32, vp, i32, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp, vp],
+    "ksana_moe_route": [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp],
+    "ksana_moe_align": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+    "ksana_moe_permute": [vp, vp, vp, i32, i32, i32, vp],
+    "ksana_moe_combine": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
     "ksana_norm": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp],
     "ksana_act_mul": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
     "ksana_quant_fp8": [vp, vp, vp, i32, i32, i32, i32, vp],
@@ -104,7 +111,38 @@ def check_err_flag(device) -> None:
 
 
 # ------------------------------------------------------------------------------------- GEMM
-def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0):
+SMALL_M_FP8 = 16                   # FP8: per-token scale promotion makes the skinny kernel pay off up to 16 rows
+SMALL_M_BF16 = 128                 # bf16: no per-K-block promotion, the skinny kernel wins up to a full token tile
+_SCRATCH_BYTES = 64 << 20
+_COUNTERS = 4096
+_workspaces = {}
+
+
+def gemm_workspace(device):
+    """Per-device scratch for tiles whose K range is cut across CTAs (fp32 partial tiles) and the tile
+    arrival counters (zeroed once; the kernel leaves them zero). Launches that share it must be
+    ordered on one stream. ``splits`` of the GEMM wrappers: 0 = automatic, > 0 = number of persistent
+    CTAs, < 0 = force the skinny kernel for M up to 128."""
+    key = torch.device(device).index or 0
+    if key not in _workspaces:
+        _workspaces[key] = (torch.empty(_SCRATCH_BYTES // 4, dtype=torch.float32, device=device),
+                            torch.zeros(_COUNTERS, dtype=torch.int32, device=device))
+    return _workspaces[key]
+
+
+def _gemm_smallm(kind, x, xs, w, ws, out, out_f32, bias, residual, M, N, K, splits):
+    dst = out if out_f32 is None else out_f32
+    scratch, counters = gemm_workspace(x.device)
+    rc = lib().ksana_gemm_smallm(kind, _p(x), x.stride(0), _p(xs), xs.stride(0) if xs is not None else 0, _p(w),
+                                 w.stride(0), _p(ws), _p(out) if out_f32 is None else None, _p(out_f32), dst.stride(0),
+                                 _p(bias), _p(residual), residual.stride(0) if residual is not None else 0, M, N, K,
+                                 max(splits, 0), _p(scratch), scratch.numel() * 4, _p(counters), counters.numel(),
+                                 _p(err_flag(x.device)), _st())
+    _check(rc, "ksana_gemm_smallm")
+    return dst
+
+
+def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0, splits=0):
     """out[M,N] = x[M,K] @ w[N,K]^T (+bias)(+residual). bf16 in, bf16 (or fp32) out."""
     M, K = x.shape
     N = w.shape[0]
@@ -112,6 +150,8 @@ def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_
     if out is None and out_f32 is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     dst = out if out_f32 is None else out_f32
+    if (M <= SMALL_M_BF16 or splits < 0) and M <= 128 and bn == 0 and K % 8 == 0:
+        return _gemm_smallm(0, x, None, w, None, out, out_f32, bias, residual, M, N, K, splits)
     rc = lib().ksana_gemm_bf16(_p(x), x.stride(0), _p(w), w.stride(0), _p(out) if out_f32 is None else None,
                                _p(out_f32), dst.stride(0), _p(bias), _p(residual),
                                residual.stride(0) if residual is not None else 0, M, N, K, bn, max_ctas,
@@ -120,13 +160,17 @@ def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_
     return dst
 
 
-def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0):
+def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0, splits=0):
     """Block-scaled FP8 GEMM. xq [M,K] e4m3, xs [K/128, ld] fp32; wq [N,K] e4m3, ws [ceil(N/128), K/128] fp32."""
     M, K = xq.shape
     N = wq.shape[0]
     if out is None and out_f32 is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
     dst = out if out_f32 is None else out_f32
+    if (M <= SMALL_M_FP8 or splits < 0) and M <= 128 and bn == 0:
+        return _gemm_smallm(1, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)
+    if bn == 0 and M <= 128:
+        bn = 128 if N >= 16384 else 64     # decode-sized rows on the tiled kernel: measured best tile widths
     rc = lib().ksana_gemm_fp8_block(_p(xq), xq.stride(0), _p(xs), xs.stride(0), _p(wq), wq.stride(0), _p(ws),
                                     _p(out) if out_f32 is None else None, _p(out_f32), dst.stride(0), _p(bias),
                                     _p(residual), residual.stride(0) if residual is not None else 0, M, N, K, bn,
@@ -289,3 +333,56 @@ def ban_tokens(logits, offsets, ids, row_idx=None):
     rc = lib().ksana_ban_tokens(_p(logits), logits.stride(0), _p(row_idx), _p(offsets), _p(ids), B, logits.shape[1],
                                 _st())
     _check(rc, "ksana_ban_tokens")
+
+
+# --------------------------------------------------------------------------- mixture of experts
+def gemm_grouped(a, w, tile_expert, E, N, out=None, a_scale=None, w_scale=None, bn=0):
+    """Expert-major rows of ``a`` [cap, K] (128-row tiles, one expert each) times stacked W [E*N, K]."""
+    cap, K = a.shape
+    kind = 0 if a_scale is None else 1
+    if out is None:
+        out = torch.empty(cap, N, dtype=torch.bfloat16, device=a.device)
+    rc = lib().ksana_gemm_grouped(kind, _p(a), a.stride(0), _p(a_scale), a_scale.stride(0) if a_scale is not None else 0,
+                                  _p(w), w.stride(0), _p(w_scale), _p(out), out.stride(0), cap, N, K, E,
+                                  _p(tile_expert), bn, _p(err_flag(a.device)), _st())
+    _check(rc, "ksana_gemm_grouped")
+    return out
+
+
+def moe_route(logits, K, scoring="softmax", renorm=True, scale=1.0, bias=None, n_group=1, topk_group=1):
+    T, E = logits.shape
+    ids = torch.empty(T, K, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, K, dtype=torch.float32, device=logits.device)
+    rc = lib().ksana_moe_route(_p(logits), _p(bias), _p(ids), _p(w), T, E, K, 0 if scoring == "softmax" else 1,
+                               int(renorm), float(scale), n_group, topk_group, _st())
+    _check(rc, "ksana_moe_route")
+    return ids, w
+
+
+def moe_align(topk_ids, E, expert_lo=0, expert_hi=None):
+    TK = topk_ids.numel()
+    hi = E if expert_hi is None else expert_hi
+    max_tiles = (TK + (hi - expert_lo) * 127 + 127) // 128
+    dev = topk_ids.device
+    dst_row = torch.empty(TK, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    total = torch.empty(1, dtype=torch.int32, device=dev)
+    rc = lib().ksana_moe_align(_p(topk_ids), _p(dst_row), _p(tile_expert), _p(offsets), _p(total), TK, E, max_tiles,
+                               expert_lo, hi, _st())
+    _check(rc, "ksana_moe_align")
+    return dst_row, tile_expert, offsets, total, max_tiles * 128
+
+
+def moe_permute(x, dst_row, K, cap):
+    T, H = x.shape
+    perm = torch.empty(cap, H, dtype=torch.bfloat16, device=x.device)
+    _check(lib().ksana_moe_permute(_p(x), _p(dst_row), _p(perm), T, K, H, _st()), "ksana_moe_permute")
+    return perm
+
+
+def moe_combine(y, dst_row, topk_w, out, K, accumulate):
+    T, H = out.shape
+    _check(lib().ksana_moe_combine(_p(y), _p(dst_row), _p(topk_w), _p(out), T, K, H, int(accumulate), _st()),
+           "ksana_moe_combine")
+    return out

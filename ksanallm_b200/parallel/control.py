@@ -27,5 +27,6 @@ def broadcast_plan(group, image: Optional[np.ndarray], src: int = 0):
     if n < 0:
         return None
     buf = torch.empty(n, dtype=torch.int32)
-    dist.broadcast(buf, src=src, group=group)
+    if n > 0:
+        dist.broadcast(buf, src=src, group=group)
     return buf.numpy()

@@ -167,9 +167,79 @@ class ModelRunner:
                 setattr(step, k, v)
         return step
 
+    # ------------------------------------------------------------------ CUDA-graph decode
+    GRAPH_SIZES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    def enable_graphs(self, max_batch: int, max_token_len: int):
+        """Whole-model CUDA graphs for pure-decode steps, one per padded batch size (the reference captures
+        per-layer graphs for batch sizes 1..3 only: src/ksana_llm/runtime/cuda_graph_runner.cpp:11-30)."""
+        if not self.cuda:
+            return
+        self.graphs = {}
+        self.graph_max_batch = max_batch
+        self.graph_max_blocks = (max_token_len + self.block_tokens - 1) // self.block_tokens + 1
+        self.graph_max_kv = max_token_len
+
+    def _graph_for(self, bs: int):
+        g = self.graphs.get(bs)
+        if g is not None:
+            return g
+        mb = self.graph_max_blocks
+        n = 4 * bs + bs * mb
+        img = torch.zeros(n, dtype=torch.int32, device=self.device)
+        ids, pos, slots, kvl = img[0:bs], img[bs:2 * bs], img[2 * bs:3 * bs], img[3 * bs:4 * bs]
+        table = img[4 * bs:].view(bs, mb)
+        slots.fill_(-1)
+        cu_q = torch.arange(bs + 1, dtype=torch.int32, device=self.device)
+        step = StepInput(ids, pos, slots, cu_q, kvl, table, 0, bs, bs, 0, 1, logits_rows=None)
+        step.decode_splits = ops.decode_splits(bs, self.model.Hkv, self.graph_max_kv)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.model.forward(step)          # warm-up: lazy initialisations must not happen under capture
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(step)
+        g = (graph, img, logits, mb)
+        self.graphs[bs] = g
+        return g
+
+    def _try_graph(self, plan) -> Optional[torch.Tensor]:
+        nseq = len(plan.seq_ids)
+        if getattr(self, "graphs", None) is None or plan.num_multi or nseq == 0 or nseq > self.graph_max_batch:
+            return None
+        if plan.sample_rows.size != nseq or plan.max_blocks > self.graph_max_blocks:
+            return None
+        bs = next(b for b in self.GRAPH_SIZES if b >= nseq)
+        graph, img, logits, mb = self._graph_for(bs)
+        host = np.zeros(4 * bs + bs * mb, dtype=np.int32)
+        host[0:nseq] = plan.input_ids
+        host[bs:bs + nseq] = plan.positions
+        host[2 * bs:3 * bs] = -1
+        host[2 * bs:2 * bs + nseq] = plan.slots
+        host[3 * bs:3 * bs + nseq] = plan.kv_lens
+        tbl = host[4 * bs:].reshape(bs, mb)
+        tbl[:nseq, :plan.max_blocks] = np.asarray(plan.block_table).reshape(nseq, plan.max_blocks)
+        n = host.size
+        if n > self._pinned_cap:
+            self._pinned_cap = max(n * 2, 1 << 16)
+            self._pinned = torch.empty(self._pinned_cap, dtype=torch.int32, pin_memory=True)
+        self._pinned[:n].copy_(torch.from_numpy(host))
+        img.copy_(self._pinned[:n], non_blocking=True)
+        self.h2d_bytes += n * 4
+        graph.replay()
+        self.graph_replays = getattr(self, "graph_replays", 0) + 1
+        return logits[:nseq]
+
     @torch.inference_mode()
     def execute(self, plan, extra: Optional[dict] = None) -> torch.Tensor:
         self.apply_block_ops(plan)
+        if extra is None:
+            out = self._try_graph(plan)
+            if out is not None:
+                return out
         step = self.build_step(plan, extra)
         return self.model.forward(step)
 
@@ -196,6 +266,8 @@ class LLMEngine:
                              f"{sc.max_token_len}")
         self.scheduler = ne.Scheduler(sc, num_blocks, num_host_blocks) if rank == 0 else None
         self.runner = ModelRunner(model, sc.block_token_num, num_blocks, num_host_blocks, kv_dtype)
+        if cfg.global_.enable_cuda_graph:
+            self.runner.enable_graphs(bs.max_batch_size, sc.max_token_len)
         self.sampler = Sampler(model.device, model_cfg.vocab_size)
         self.requests: Dict[int, Request] = {}
         self.seq_to_req: Dict[int, tuple] = {}
@@ -469,9 +541,6 @@ class LLMEngine:
         if self._thread is not None:
             self._thread.join(timeout=10)
             self._thread = None
-        if self.world_size > 1 and self.rank == 0:
-            from ..parallel.control import broadcast_plan
-            broadcast_plan(self.control_group, None)
 
     # ------------------------------------------------------------------ conveniences
     def generate(self, prompts: List[List[int]], sampling=None, timeout: Optional[float] = None) -> List[Request]:

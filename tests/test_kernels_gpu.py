@@ -49,8 +49,9 @@ def test_gemm_bf16_epilogue():
     assert rel_err(res2, ref.gemm(x, w, None, res, out_dtype=torch.float32)) < 1e-2
 
 
-@pytest.mark.parametrize("M,N,K,bn", [(128, 256, 512, 0), (300, 1280, 1024, 64), (5, 4096, 8192, 32),
-                                       (2048, 8192, 8192, 128), (1000, 7168, 3584, 0)])
+@pytest.mark.parametrize("M,N,K,bn", [(128, 256, 512, 128), (300, 1280, 1024, 64), (5, 4096, 8192, 32),
+                                       (2048, 8192, 8192, 128), (1000, 7168, 3584, 0), (4096, 10240, 8192, 256),
+                                       (300, 1000, 1024, 256), (2500, 57344, 1024, 0)])
 def test_gemm_fp8_block(M, N, K, bn):
     torch.manual_seed(2)
     x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
@@ -58,7 +59,8 @@ def test_gemm_fp8_block(M, N, K, bn):
     wq, ws = ref.quant_weight_fp8_block(w)
     xq, xs = native.quant_fp8(x)
     xq_r, xs_r = ref.quant_fp8(x)
-    assert torch.equal(xq.float(), xq_r.float())
+    # identical up to e4m3 rounding ties (the kernel multiplies by the reciprocal scale)
+    assert (xq.float() != xq_r.float()).float().mean() < 1e-3
     assert torch.allclose(xs[:, :M], xs_r, rtol=1e-6)
     y = native.gemm_fp8(xq, xs, wq, ws, bn=bn)
     torch.cuda.synchronize()
@@ -67,6 +69,41 @@ def test_gemm_fp8_block(M, N, K, bn):
     assert rel_err(y, want) < 1e-2, rel_err(y, want)
     # and the quantised product stays close to the unquantised one
     assert rel_err(y, x.float() @ w.t()) < 6e-2
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8"])
+@pytest.mark.parametrize("M,N,K,splits", [(1, 512, 1024, 0), (8, 8192, 8192, 0), (16, 1280, 8192, 37), (17, 4096, 4096, 7),
+                                            (64, 57344, 8192, -1), (64, 8192, 28672, -1), (128, 1000, 2048, 3),
+                                            (100, 128256, 1024, -1), (8, 10240, 8192, 0), (32, 57344, 8192, 0),
+                                            (3, 8192, 28672, 0), (8, 7168, 8192, 1)])
+def test_gemm_smallm(kind, M, N, K, splits):
+    torch.manual_seed(5)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    if kind == "bf16":
+        w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+        for _ in range(2):   # twice: the tile counters must come back to zero
+            y = native.gemm_bf16(x, w, bias=bias, residual=res, splits=splits)
+        want = ref.gemm(x, w, bias, res, out_dtype=torch.float32)
+        yf = torch.empty(M, N, device=DEV, dtype=torch.float32)
+        native.gemm_bf16(x, w, out_f32=yf, splits=splits)
+        assert rel_err(yf, ref.gemm(x, w, out_dtype=torch.float32)) < 3e-3
+    else:
+        w = torch.randn(N, K, device=DEV, dtype=torch.float32) * 0.05
+        wq, ws = ref.quant_weight_fp8_block(w)
+        xq, xs = native.quant_fp8(x)
+        for _ in range(2):
+            y = native.gemm_fp8(xq, xs, wq, ws, bias=bias, residual=res, splits=splits)
+        want = ref.gemm_fp8(xq, xs, wq, ws, bias, res, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    assert rel_err(y, want) < 1e-2, rel_err(y, want)
+    # in-place residual accumulate
+    r2 = res.clone()
+    if kind == "bf16":
+        native.gemm_bf16(x, w, out=r2, residual=r2, splits=splits)
+        assert rel_err(r2, ref.gemm(x, w, None, res, out_dtype=torch.float32)) < 1e-2
 
 
 @pytest.mark.parametrize("H", [256, 4096, 8192, 5120])
@@ -89,7 +126,7 @@ def test_norm(H, layernorm):
         y3, q, s = native.norm(x, w, 1e-5, beta=beta, layernorm=layernorm, quant=True)
         q_r, s_r = ref.quant_fp8(y3)
         assert torch.allclose(s[:, :M], s_r, rtol=1e-6)
-        assert (q.float() - q_r.float()).abs().max() == 0
+        assert (q.float() != q_r.float()).float().mean() < 1e-3
 
 
 @pytest.mark.parametrize("kind,gated", [("silu", True), ("gelu", True), ("relu", False), ("gelu", False)])
@@ -102,7 +139,7 @@ def test_act_mul(kind, gated):
     y2, q, s = native.act_mul(x, kind, gated, quant=True)
     q_r, s_r = ref.quant_fp8(y2)
     assert torch.allclose(s[:, :M], s_r, rtol=1e-6)
-    assert (q.float() - q_r.float()).abs().max() == 0
+    assert (q.float() != q_r.float()).float().mean() < 1e-3
 
 
 def test_embedding_and_gather():
