@@ -1,0 +1,375 @@
+// Tensor-parallel collectives over NVLink peer memory, fused with the memory-bound work that
+// follows them. One process per GPU; every rank maps every peer's symmetric buffer, so kernels
+// address peers with plain pointers (P2P loads / stores through NVSwitch).
+//
+// Row-parallel linear (o_proj, down_proj) in two kernels:
+//   1. the GEMM kernels (gemm_tcgen05.cu / gemm_smallm.cu) run in "push" mode: their epilogue stores
+//      each partial tile straight into the receive slot of the rank that will reduce those rows
+//      (posted P2P stores, so the reduce-scatter traffic overlaps the remaining tiles' math);
+//   2. reduce_norm_kernel (here): waits - bounded - until every peer's pushes for this epoch are
+//      flagged, sums the partial slots in rank order (identical bits on every rank), adds the
+//      residual, applies RMSNorm / LayerNorm, optionally quantises to FP8 (1x128 scales) for the next
+//      GEMM, and (large batches) pushes its row slice of the results to every peer (all-gather).
+// This replaces NCCL all-reduce + add + norm (+ quant) of the reference op sequence
+// (src/ksana_llm/models/common/common_model.cpp:498-527,549-569,586-615) and its custom all-reduce
+// (3rdparty/LLM_kernels/csrc/kernels/nvidia/all_reduce/custom_all_reduce.cu:116-400), whose flag
+// spins are unbounded.
+//
+// Flags: each rank owns a pad of 32-bit words in its symmetric memory. Word [kind*16 + r] holds the
+// last epoch for which rank r signalled `kind` to this rank. Epochs only grow, so flags are never reset.
+// The epoch of a call is read from a device counter (ctrs[kind]) and advanced by the last block of the
+// call, so a launch captured in a CUDA graph gets a fresh epoch on every replay. All ranks issue the same
+// sequence of collective calls, which keeps their counters in step.
+// A wait that exceeds its budget sets the error word and the kernel skips the dependent work.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace ksana {
+
+typedef __nv_bfloat16 bf16;
+constexpr int kMaxRanks = 8;
+constexpr int kFlagStride = 16;
+
+struct CommPeers {
+  void* data[kMaxRanks];          // peers' symmetric data buffers (same layout on every rank)
+  uint32_t* flags[kMaxRanks];     // peers' flag pads
+  int rank, size;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Budget of a peer wait: kSpinLimit polls with a short sleep each (about a second in total).
+constexpr int kSpinLimit = 1 << 20;
+
+// Signal `kind` for `epoch` to every peer (one thread per peer of block 0), then every block waits until
+// all peers have signalled the same. Returns false on timeout (err word set).
+__device__ __forceinline__ bool signal_and_wait(const CommPeers& c, int kind, uint32_t epoch, int* err, bool do_signal) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (do_signal && blockIdx.x == 0 && threadIdx.x < c.size) {
+    __threadfence_system();
+    st_release_sys(c.flags[threadIdx.x] + kind * kFlagStride + c.rank, epoch);
+  }
+  if (threadIdx.x < c.size) {
+    const uint32_t* f = c.flags[c.rank] + kind * kFlagStride + threadIdx.x;
+    int it = 0;
+    // signed distance handles wrap-around of the 32-bit epoch
+    while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
+      if (++it > kSpinLimit) { s_ok = 0; if (err) atomicExch(err, 3); break; }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__device__ __forceinline__ void unpack8c(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8c(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+__device__ __forceinline__ uint2 pack8_e4m3c(const float (&f)[8], float inv_scale) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+        make_float2(f[4 * h] * inv_scale, f[4 * h + 1] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+        make_float2(f[4 * h + 2] * inv_scale, f[4 * h + 3] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+    w[h] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+// Epoch bookkeeping in local device memory: ctrs[kind] = last completed epoch, ctrs[8 + kind] = blocks done.
+__device__ __forceinline__ uint32_t begin_epoch(const uint32_t* ctrs, int kind) {
+  return *reinterpret_cast<const volatile uint32_t*>(ctrs + kind) + 1;
+}
+__device__ __forceinline__ void end_epoch(uint32_t* ctrs, int kind, uint32_t epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ctrs + 8 + kind, 1u) == gridDim.x - 1) {
+      ctrs[8 + kind] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(ctrs + kind) = epoch;
+    }
+  }
+}
+
+struct ReduceNormParams {
+  CommPeers peers;
+  uint32_t* ctrs;
+  // receive slots in the local symmetric buffer: slot r at slots_off + r * slot_stride (bytes), each
+  // [rows_local, H] bf16 where rows_local = rows this rank reduces
+  long long slots_off, slot_stride;
+  int row_begin, row_count;       // rows of the full [M, H] problem this rank reduces (all rows in one-shot mode)
+  int M, H;
+  bf16* h;                        // residual stream [M, H] (local, full); rows reduced here are updated in place
+  const bf16* norm_w; const bf16* norm_b; float eps; int layernorm;   // norm_w null: no norm (plain all-reduce + residual)
+  bf16* y;                        // normalised output [M, H] (local) or null
+  uint8_t* yq; float* yscale; int scale_ld;   // fp8 operand of y or null
+  int gather;                     // 1: push this rank's rows of h / y / yq to every peer, then wait for theirs
+  long long h_sym_off, y_sym_off, yq_sym_off, ys_sym_off;   // offsets of h / y / yq / yscale inside the symmetric buffer (gather mode: those tensors live there)
+  int* err;
+};
+
+constexpr int kRnMaxVec = 4;
+
+// grid = row_count blocks; block handles one row (up to kRnMaxVec * blockDim vectors of 8).
+__global__ void reduce_norm_kernel(const ReduceNormParams p) {
+  __shared__ float red[32];
+  const CommPeers& c = p.peers;
+  const uint32_t epoch = begin_epoch(p.ctrs, 0);
+  if (!signal_and_wait(c, 0, epoch, p.err, true)) return;
+  const int lrow = blockIdx.x;                  // row inside this rank's slice
+  if (lrow >= p.row_count) { end_epoch(p.ctrs, 0, epoch); return; }   // a rank without rows only exchanges flags
+  const int row = p.row_begin + lrow;
+  const int nvec = p.H >> 3;
+  const uint8_t* base = static_cast<const uint8_t*>(c.data[c.rank]) + p.slots_off;
+  float v[kRnMaxVec][8];
+  float s = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRnMaxVec; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < nvec) {
+      float acc[8];
+      if (p.h) unpack8c(reinterpret_cast<const uint4*>(p.h + static_cast<size_t>(row) * p.H)[i], acc);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      }
+      for (int r = 0; r < c.size; ++r) {        // fixed order: every rank produces the same bits
+        const uint4 pv = reinterpret_cast<const uint4*>(base + r * p.slot_stride + (static_cast<size_t>(lrow) * p.H) * 2)[i];
+        float f[8];
+        unpack8c(pv, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      }
+      const uint4 packed = pack8c(acc);
+      if (p.h) reinterpret_cast<uint4*>(p.h + static_cast<size_t>(row) * p.H)[i] = packed;
+      if (p.gather && p.h) {
+        for (int r = 0; r < c.size; ++r) {
+          if (r == c.rank) continue;
+          bf16* ph = reinterpret_cast<bf16*>(static_cast<uint8_t*>(c.data[r]) + p.h_sym_off);
+          reinterpret_cast<uint4*>(ph + static_cast<size_t>(row) * p.H)[i] = packed;
+        }
+      }
+      unpack8c(packed, v[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { s += v[j][e]; s2 += v[j][e] * v[j][e]; }
+    }
+  }
+  if (p.norm_w) {
+    // block reductions
+    auto block_sum = [&](float x) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+      const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+      if (l == 0) red[w] = x;
+      __syncthreads();
+      float t = l < nw ? red[l] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      __syncthreads();
+      return t;
+    };
+    float mean = 0.f, rstd;
+    if (p.layernorm) {
+      mean = block_sum(s) / p.H;
+      float var = 0.f;
+#pragma unroll
+      for (int j = 0; j < kRnMaxVec; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nvec) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { const float d = v[j][e] - mean; var += d * d; }
+        }
+      }
+      rstd = rsqrtf(block_sum(var) / p.H + p.eps);
+    } else {
+      rstd = rsqrtf(block_sum(s2) / p.H + p.eps);
+    }
+#pragma unroll
+    for (int j = 0; j < kRnMaxVec; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      const bool on = i < nvec;
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = 0.f;
+      if (on) {
+        float wf[8];
+        unpack8c(reinterpret_cast<const uint4*>(p.norm_w)[i], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = (v[j][e] - mean) * rstd * wf[e];
+        if (p.norm_b) {
+          float bfv[8];
+          unpack8c(reinterpret_cast<const uint4*>(p.norm_b)[i], bfv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += bfv[e];
+        }
+        const uint4 packed = pack8c(o);
+        if (p.y) {
+          reinterpret_cast<uint4*>(p.y + static_cast<size_t>(row) * p.H)[i] = packed;
+          if (p.gather) {
+            for (int r = 0; r < c.size; ++r) {
+              if (r == c.rank) continue;
+              bf16* py = reinterpret_cast<bf16*>(static_cast<uint8_t*>(c.data[r]) + p.y_sym_off);
+              reinterpret_cast<uint4*>(py + static_cast<size_t>(row) * p.H)[i] = packed;
+            }
+          }
+        }
+        unpack8c(packed, o);
+      }
+      if (p.yq) {
+        float am = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(o[e]));
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
+        const float scale = fmaxf(am, 1e-10f) / 448.f;
+        if (on) {
+          const uint2 q = pack8_e4m3c(o, 1.f / scale);
+          reinterpret_cast<uint2*>(p.yq + static_cast<size_t>(row) * p.H)[i] = q;
+          if ((i & 15) == 0) p.yscale[static_cast<size_t>(i >> 4) * p.scale_ld + row] = scale;
+          if (p.gather) {
+            for (int r = 0; r < c.size; ++r) {
+              if (r == c.rank) continue;
+              uint8_t* pq = static_cast<uint8_t*>(c.data[r]) + p.yq_sym_off;
+              reinterpret_cast<uint2*>(pq + static_cast<size_t>(row) * p.H)[i] = q;
+              if ((i & 15) == 0) {
+                float* ps = reinterpret_cast<float*>(static_cast<uint8_t*>(c.data[r]) + p.ys_sym_off);
+                ps[static_cast<size_t>(i >> 4) * p.scale_ld + row] = scale;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  end_epoch(p.ctrs, 0, epoch);
+}
+
+// Second half of the gather mode: flag "my slice is delivered" and wait for every peer's slice.
+// Runs as its own small launch after reduce_norm_kernel so that all blocks' pushes are complete.
+__global__ void gather_fence_kernel(const CommPeers c, uint32_t* ctrs, int* err) {
+  const uint32_t epoch = begin_epoch(ctrs, 1);
+  if (signal_and_wait(c, 1, epoch, err, true)) end_epoch(ctrs, 1, epoch);
+}
+
+// Plain barrier across ranks (bounded).
+__global__ void barrier_kernel(const CommPeers c, uint32_t* ctrs, int* err) {
+  const uint32_t epoch = begin_epoch(ctrs, 2);
+  if (signal_and_wait(c, 2, epoch, err, true)) end_epoch(ctrs, 2, epoch);
+}
+
+// One-shot pull all-reduce of a buffer every rank holds at the same symmetric offset: out = sum_r peer_r[off..]
+// (+ residual). For small tensors (router outputs, embeddings, MoE sums).
+__global__ void allreduce_pull_kernel(const CommPeers c, uint32_t* ctrs, long long off, bf16* out, const bf16* residual,
+                                      long long nvec, int* err) {
+  const uint32_t epoch = begin_epoch(ctrs, 3);
+  if (!signal_and_wait(c, 3, epoch, err, true)) return;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+    if (residual) unpack8c(reinterpret_cast<const uint4*>(residual)[i], acc);
+    else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    }
+    for (int r = 0; r < c.size; ++r) {
+      float f[8];
+      unpack8c(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(c.data[r]) + off)[i], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    reinterpret_cast<uint4*>(out)[i] = pack8c(acc);
+  }
+  end_epoch(ctrs, 3, epoch);
+}
+
+static CommPeers make_peers(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank, int size) {
+  CommPeers c{};
+  for (int i = 0; i < size && i < kMaxRanks; ++i) {
+    c.data[i] = reinterpret_cast<void*>(data_ptrs[i]);
+    c.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  c.rank = rank;
+  c.size = size;
+  return c;
+}
+
+}  // namespace ksana
+
+using namespace ksana;
+
+// Reduce the partial slots that the peers' GEMM epilogues pushed, add the residual, normalise, optionally
+// quantise and all-gather. See ReduceNormParams. Launches 1 kernel (2 in gather mode).
+extern "C" int ksana_reduce_norm(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank,
+                                 int size, void* ctrs, long long slots_off, long long slot_stride,
+                                 int row_begin, int row_count, int M, int H, void* h, const void* norm_w,
+                                 const void* norm_b, float eps, int layernorm, void* y, void* yq, float* yscale,
+                                 int scale_ld, int gather, long long h_sym_off, long long y_sym_off,
+                                 long long yq_sym_off, long long ys_sym_off, int* err, cudaStream_t st) {
+  if (size > kMaxRanks || H % 8 || H > 8 * kRnMaxVec * 1024) return -10;
+  if (yq && H % 128) return -11;
+  ReduceNormParams p{};
+  p.peers = make_peers(data_ptrs, flag_ptrs, rank, size);
+  p.ctrs = static_cast<uint32_t*>(ctrs); p.slots_off = slots_off; p.slot_stride = slot_stride;
+  p.row_begin = row_begin; p.row_count = row_count; p.M = M; p.H = H;
+  p.h = static_cast<bf16*>(h);
+  p.norm_w = static_cast<const bf16*>(norm_w); p.norm_b = static_cast<const bf16*>(norm_b);
+  p.eps = eps; p.layernorm = layernorm;
+  p.y = static_cast<bf16*>(y); p.yq = static_cast<uint8_t*>(yq); p.yscale = yscale; p.scale_ld = scale_ld;
+  p.gather = gather; p.h_sym_off = h_sym_off; p.y_sym_off = y_sym_off; p.yq_sym_off = yq_sym_off; p.ys_sym_off = ys_sym_off;
+  p.err = err;
+  int threads = (((H >> 3) + kRnMaxVec - 1) / kRnMaxVec + 31) / 32 * 32;
+  if (threads < 32) threads = 32;
+  if (threads > 1024) threads = 1024;
+  // a rank with no rows still takes part in the flag exchange
+  reduce_norm_kernel<<<row_count > 0 ? row_count : 1, threads, 0, st>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return -4;
+  if (gather) {
+    gather_fence_kernel<<<1, 32, 0, st>>>(p.peers, p.ctrs, err);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+  }
+  return 0;
+}
+
+extern "C" int ksana_comm_barrier(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank,
+                                  int size, void* ctrs, int* err, cudaStream_t st) {
+  barrier_kernel<<<1, 32, 0, st>>>(make_peers(data_ptrs, flag_ptrs, rank, size), static_cast<uint32_t*>(ctrs), err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_allreduce_pull(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank,
+                                    int size, void* ctrs, long long off, void* out, const void* residual,
+                                    long long n_elems, int* err, cudaStream_t st) {
+  if (n_elems % 8) return -10;
+  const long long nvec = n_elems / 8;
+  long long g = (nvec + 255) / 256;
+  if (g > 148 * 4) g = 148 * 4;
+  if (g < 1) g = 1;
+  allreduce_pull_kernel<<<static_cast<int>(g), 256, 0, st>>>(make_peers(data_ptrs, flag_ptrs, rank, size),
+                                                             static_cast<uint32_t*>(ctrs), off,
+                                                             static_cast<bf16*>(out),
+                                                             static_cast<const bf16*>(residual), nvec, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -38,6 +38,9 @@ struct SmallMParams {
   float* scratch;                         // [n_tiles][seg_cap][MP][128] fp32 partial tiles
   unsigned int* counters;                 // [n_tiles], zero before the first launch
   int* err;
+  // push mode: the (partial) result is stored into every rank's receive slot for this rank instead of D
+  __nv_bfloat16* push[8];
+  int push_n;
 };
 
 template <int MP, int KIND>   // MP: padded token count (16..128); KIND 0 bf16, 1 fp8 block-scaled
@@ -250,7 +253,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           if (m < p.M) {
             float o = v[m] + b;
             if (p.residual) o += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n]);
-            if (p.out_f32) p.out_f32[static_cast<size_t>(m) * p.ldd + n] = o;
+            if (p.push_n) {
+              const __nv_bfloat16 ob = __float2bfloat16(o);
+              for (int r = 0; r < p.push_n; ++r) p.push[r][static_cast<size_t>(m) * p.ldd + n] = ob;
+            } else if (p.out_f32) p.out_f32[static_cast<size_t>(m) * p.ldd + n] = o;
             else p.D[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16(o);
           }
         }
@@ -354,11 +360,11 @@ using namespace ksana;
 // counters: n_tiles words, zero before the first launch (the kernel leaves them zero).
 // kind 0: X, W bf16. kind 1: e4m3 with scales. ctas_hint > 0 fixes the number of persistent CTAs
 // (1 = no K splitting at all when there is a single tile per CTA...). Returns 0 on success; -20 when M > 128.
-extern "C" int ksana_gemm_smallm(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld, const void* W,
-                                 int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
-                                 const void* residual, int ldr, int M, int N, int K, int ctas_hint, void* scratch,
-                                 long long scratch_bytes, void* counters, int counters_len, int* err_flag,
-                                 cudaStream_t st) {
+static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld, const void* W,
+                       int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
+                       const void* residual, int ldr, int M, int N, int K, int ctas_hint, void* scratch,
+                       long long scratch_bytes, void* counters, int counters_len, int* err_flag,
+                       cudaStream_t st, const unsigned long long* push_ptrs, int push_n) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (M > 128) return -20;
   const int esz = kind == 0 ? 2 : 1;
@@ -402,6 +408,8 @@ extern "C" int ksana_gemm_smallm(int kind, const void* X, int ldx, const float* 
   p.a_scale = a_scale; p.a_scale_ld = a_scale_ld; p.w_scale = w_scale;
   p.seg_cap = seg_cap; p.scratch = static_cast<float*>(scratch); p.counters = static_cast<unsigned int*>(counters);
   p.err = err_flag;
+  for (int i = 0; i < push_n && i < 8; ++i) p.push[i] = reinterpret_cast<__nv_bfloat16*>(push_ptrs[i]);
+  p.push_n = push_n;
   const int ctas = static_cast<int>(P);
 #define KSANA_SM_DISPATCH(MPV)                                                                        \
   case MPV: return kind == 0 ? launch_smallm<MPV, 0>(mw, mx, p, ctas, st) : launch_smallm<MPV, 1>(mw, mx, p, ctas, st);
@@ -413,4 +421,24 @@ extern "C" int ksana_gemm_smallm(int kind, const void* X, int ldx, const float* 
   }
 #undef KSANA_SM_DISPATCH
   return -21;
+}
+
+extern "C" int ksana_gemm_smallm(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld, const void* W,
+                                 int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
+                                 const void* residual, int ldr, int M, int N, int K, int ctas_hint, void* scratch,
+                                 long long scratch_bytes, void* counters, int counters_len, int* err_flag,
+                                 cudaStream_t st) {
+  return smallm_impl(kind, X, ldx, a_scale, a_scale_ld, W, ldw, w_scale, D, out_f32, ldd, bias, residual, ldr, M, N, K,
+                     ctas_hint, scratch, scratch_bytes, counters, counters_len, err_flag, st, nullptr, 0);
+}
+
+// Push mode (tensor parallel, decode-sized batches): the partial product is stored into every rank's
+// receive slot for this rank (push_ptrs[r], row stride ldd) with plain P2P stores from the epilogue.
+extern "C" int ksana_gemm_smallm_push(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld,
+                                      const void* W, int ldw, const float* w_scale, int ldd, const void* bias, int M,
+                                      int N, int K, void* scratch, long long scratch_bytes, void* counters,
+                                      int counters_len, const unsigned long long* push_ptrs, int push_n, int* err_flag,
+                                      cudaStream_t st) {
+  return smallm_impl(kind, X, ldx, a_scale, a_scale_ld, W, ldw, w_scale, nullptr, nullptr, ldd, bias, nullptr, 0, M, N,
+                     K, 0, scratch, scratch_bytes, counters, counters_len, err_flag, st, push_ptrs, push_n);
 }

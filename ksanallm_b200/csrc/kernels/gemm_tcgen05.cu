@@ -51,6 +51,11 @@ struct GemmParams {
   const int* tile_expert;
   int expert_rows;
   int scale_rows_per_expert;
+  // push mode (tensor-parallel row-parallel linear): rows [r*push_rows, (r+1)*push_rows) of the partial
+  // product are stored into rank r's receive slot for this rank (peer memory, plain P2P stores) instead of D.
+  __nv_bfloat16* push[8];
+  int push_n;
+  int push_rows;
 };
 
 template <int BN, int KIND>
@@ -252,7 +257,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
             for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
-            *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(row) * p.ldd + col) = ov;
+            if (p.push_n) {
+              const int owner = min(row / p.push_rows, p.push_n - 1);
+              *reinterpret_cast<uint4*>(p.push[owner] + static_cast<size_t>(row - owner * p.push_rows) * p.ldd + col) = ov;
+            } else {
+              *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(row) * p.ldd + col) = ov;
+            }
           }
         }
       };
@@ -407,9 +417,10 @@ using namespace ksana;
 
 // D = A[M,K](bf16, row stride lda) * W[N,K]^T (bf16) (+bias)(+residual); output bf16 or fp32.
 // Returns 0 on launch success, negative on argument / setup errors.
-extern "C" int ksana_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, void* out_f32, int ldd,
-                               const void* bias, const void* residual, int ldr, int M, int N, int K, int bn_hint,
-                               int max_ctas, int* err_flag, cudaStream_t stream) {
+static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* D, void* out_f32, int ldd,
+                          const void* bias, const void* residual, int ldr, int M, int N, int K, int bn_hint,
+                          int max_ctas, int* err_flag, cudaStream_t stream, const unsigned long long* push_ptrs,
+                          int push_n, int push_rows) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N % 8) || (K % 8) || (lda % 8) || (ldw % 8) || (ldd % 8) || (residual && (ldr % 8))) return -10;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -11;
@@ -423,6 +434,8 @@ extern "C" int ksana_gemm_bf16(const void* A, int lda, const void* W, int ldw, v
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
   p.err = err_flag;
+  for (int i = 0; i < push_n && i < 8; ++i) p.push[i] = reinterpret_cast<__nv_bfloat16*>(push_ptrs[i]);
+  p.push_n = push_n; p.push_rows = push_rows;
   switch (bn) {
     case 256: return launch_gemm<256, kBf16>(ma, mb, p, max_ctas, stream);
     case 128: return launch_gemm<128, kBf16>(ma, mb, p, max_ctas, stream);
@@ -431,12 +444,29 @@ extern "C" int ksana_gemm_bf16(const void* A, int lda, const void* W, int ldw, v
   }
 }
 
+extern "C" int ksana_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, void* out_f32, int ldd,
+                               const void* bias, const void* residual, int ldr, int M, int N, int K, int bn_hint,
+                               int max_ctas, int* err_flag, cudaStream_t stream) {
+  return gemm_bf16_impl(A, lda, W, ldw, D, out_f32, ldd, bias, residual, ldr, M, N, K, bn_hint, max_ctas, err_flag,
+                        stream, nullptr, 0, 0);
+}
+
+// Push mode: partial rows go to the peers' receive slots (push_ptrs[r] = slot of this rank inside rank r's
+// symmetric buffer; rows [r*push_rows, (r+1)*push_rows) belong to rank r). ldd is the slot's row stride.
+extern "C" int ksana_gemm_bf16_push(const void* A, int lda, const void* W, int ldw, int ldd, const void* bias, int M,
+                                    int N, int K, int bn_hint, const unsigned long long* push_ptrs, int push_n,
+                                    int push_rows, int* err_flag, cudaStream_t stream) {
+  return gemm_bf16_impl(A, lda, W, ldw, nullptr, nullptr, ldd, bias, nullptr, 0, M, N, K, bn_hint, 0, err_flag, stream,
+                        push_ptrs, push_n, push_rows);
+}
+
 // Block-scaled FP8: A_q[M,K] e4m3 with a_scale[K/128][a_scale_ld] fp32, W_q[N,K] e4m3 with
 // w_scale[ceil(N/128)][K/128] fp32. K must be a multiple of 128.
-extern "C" int ksana_gemm_fp8_block(const void* Aq, int lda, const float* a_scale, int a_scale_ld, const void* Wq,
-                                    int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
-                                    const void* residual, int ldr, int M, int N, int K, int bn_hint, int max_ctas,
-                                    int* err_flag, cudaStream_t stream) {
+static int gemm_fp8_impl(const void* Aq, int lda, const float* a_scale, int a_scale_ld, const void* Wq,
+                         int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
+                         const void* residual, int ldr, int M, int N, int K, int bn_hint, int max_ctas,
+                         int* err_flag, cudaStream_t stream, const unsigned long long* push_ptrs, int push_n,
+                         int push_rows) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N % 8) || (K % 128) || (lda % 16) || (ldw % 16) || (ldd % 8) || (residual && (ldr % 8))) return -10;
   if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Wq)) & 15) return -11;
@@ -451,12 +481,30 @@ extern "C" int ksana_gemm_fp8_block(const void* Aq, int lda, const float* a_scal
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
   p.a_scale = a_scale; p.a_scale_ld = a_scale_ld; p.w_scale = w_scale;
   p.err = err_flag;
+  for (int i = 0; i < push_n && i < 8; ++i) p.push[i] = reinterpret_cast<__nv_bfloat16*>(push_ptrs[i]);
+  p.push_n = push_n; p.push_rows = push_rows;
   switch (bn) {
     case 256: return launch_gemm<256, kFp8Block>(ma, mb, p, max_ctas, stream);
     case 128: return launch_gemm<128, kFp8Block>(ma, mb, p, max_ctas, stream);
     case 64: return launch_gemm<64, kFp8Block>(ma, mb, p, max_ctas, stream);
     default: return launch_gemm<32, kFp8Block>(ma, mb, p, max_ctas, stream);
   }
+}
+
+extern "C" int ksana_gemm_fp8_block(const void* Aq, int lda, const float* a_scale, int a_scale_ld, const void* Wq,
+                                    int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
+                                    const void* residual, int ldr, int M, int N, int K, int bn_hint, int max_ctas,
+                                    int* err_flag, cudaStream_t stream) {
+  return gemm_fp8_impl(Aq, lda, a_scale, a_scale_ld, Wq, ldw, w_scale, D, out_f32, ldd, bias, residual, ldr, M, N, K,
+                       bn_hint, max_ctas, err_flag, stream, nullptr, 0, 0);
+}
+
+extern "C" int ksana_gemm_fp8_block_push(const void* Aq, int lda, const float* a_scale, int a_scale_ld, const void* Wq,
+                                         int ldw, const float* w_scale, int ldd, const void* bias, int M, int N, int K,
+                                         int bn_hint, const unsigned long long* push_ptrs, int push_n, int push_rows,
+                                         int* err_flag, cudaStream_t stream) {
+  return gemm_fp8_impl(Aq, lda, a_scale, a_scale_ld, Wq, ldw, w_scale, nullptr, nullptr, ldd, bias, nullptr, 0, M, N, K,
+                       bn_hint, 0, err_flag, stream, push_ptrs, push_n, push_rows);
 }
 
 // Grouped GEMM for mixture-of-experts: rows of A are expert-major (each expert's segment padded to a

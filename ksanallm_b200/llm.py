@@ -102,7 +102,8 @@ class LLM:
         tp = self.world
         check_tp(model_cfg, tp)
         self.comm = TPComm(dev_group, self.rank, tp, self.engine_cfg.global_.comm_backend if dev_type == "cuda" else "nccl",
-                           self.device) if tp > 1 else None
+                           self.device, max_tokens=self.engine_cfg.batch_scheduler.max_step_tokens,
+                           hidden=model_cfg.hidden_size) if tp > 1 else None
         quant = self.engine_cfg.quantization.weight_quant_method
         quant = {"auto": None, "fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "nvfp4": "fp8_block"}[quant]
         if model_cfg.fp8_checkpoint and quant is None:

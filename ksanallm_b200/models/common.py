@@ -246,11 +246,53 @@ class CommonModel:
         """Runs this pipeline stage. The last stage returns fp32 logits [rows, vocab]; earlier stages return
         the hidden states to ship to the next stage."""
         h = self.embed_tokens(step) if self.is_first_stage else hidden_in
+        if self._tp_fused_ok(h):
+            return self._forward_tp_fused(h, step)
         for i, lw in enumerate(self.layers):
             h = self.layer_forward(self.layer_lo + i, lw, h, step)
         if not self.is_last_stage:
             return h
         return self.lm_head_forward(h, step)
+
+    # ------------------------------------------------------------------ fused tensor-parallel path
+    def _tp_fused_ok(self, h) -> bool:
+        symm = getattr(self.comm, "symm", None) if self.comm is not None else None
+        return (symm is not None and h.is_cuda and not self.cfg.post_norm and self.is_last_stage
+                and all(l.moe is None for l in self.layers) and h.shape[0] <= symm.max_tokens
+                and h.shape[1] == symm.hidden)
+
+    def _forward_tp_fused(self, h0: torch.Tensor, step: StepInput) -> torch.Tensor:
+        """Row-parallel GEMMs push their partial tiles into peer memory from the epilogue; one kernel then
+        reduces, adds the residual and applies the following norm (and FP8 quantisation), so a layer has
+        no stand-alone all-reduce, add or norm launches."""
+        from ..parallel.symm import ONE_SHOT_ROWS
+        cfg, symm = self.cfg, self.comm.symm
+        ln = cfg.norm_type == "layernorm"
+        symm.begin_forward()
+        T = h0.shape[0]
+        if T > ONE_SHOT_ROWS:
+            h = symm.h[:T]
+            h.copy_(h0)
+        else:
+            h = h0
+        first = self.layers[0]
+        x = ops.norm(h, first.input_norm, cfg.rms_norm_eps, beta=first.input_norm_bias, layernorm=ln, quant_for=first.qkv)
+        n = len(self.layers)
+        for i, lw in enumerate(self.layers):
+            a = self.attention(self.layer_lo + i, lw, x, step)
+            h, x = symm.row_parallel_norm(a, lw.o_proj, h, lw.post_norm, lw.post_norm_bias, cfg.rms_norm_eps, ln,
+                                          quant_for=lw.gate_up)
+            gu = ops.linear(x, lw.gate_up)
+            act = ops.act_mul(gu, cfg.activation, cfg.gated_mlp, quant_for=lw.down)
+            if i + 1 < n:
+                nw, nb, nq = self.layers[i + 1].input_norm, self.layers[i + 1].input_norm_bias, self.layers[i + 1].qkv
+            else:
+                nw, nb, nq = self.final_norm, self.final_norm_bias, None
+            h, x = symm.row_parallel_norm(act, lw.down, h, nw, nb, cfg.rms_norm_eps, ln, quant_for=nq)
+        if step.want_hidden:
+            self.step_hidden, self.step_normed = h, x
+        hn = ops.gather_rows(x, step.logits_rows) if step.logits_rows is not None else x
+        return self.compute_logits(hn)
 
     # ------------------------------------------------------------------ misc
     embed_sharded = False

@@ -85,18 +85,25 @@ class CheckpointSource:
         st = sorted(glob.glob(os.path.join(model_dir, "*.safetensors")))
         bins = sorted(glob.glob(os.path.join(model_dir, "*.bin")) + glob.glob(os.path.join(model_dir, "*.pt")))
         bins = [b for b in bins if "training_args" not in os.path.basename(b) and "optimizer" not in os.path.basename(b)]
+        def add(kind, f, k):
+            name = apply_weight_map(k, self.rules)
+            transpose = name.endswith(".conv1d_t")        # GPT-2 style Conv1D weights are stored [in, out]
+            if transpose:
+                name = name[: -len(".conv1d_t")]
+            self.index[name] = (kind, f, k, transpose)
+
         if st:
             from safetensors import safe_open
             for f in st:
                 with safe_open(f, framework="pt") as sf:
                     for k in sf.keys():
-                        self.index[apply_weight_map(k, self.rules)] = ("st", f, k)
+                        add("st", f, k)
         elif bins:
             for f in bins:
                 sd = torch.load(f, map_location="cpu", weights_only=True)
                 self._bin_cache[f] = sd
                 for k in sd.keys():
-                    self.index[apply_weight_map(k, self.rules)] = ("bin", f, k)
+                    add("bin", f, k)
         else:
             raise FileNotFoundError(f"no safetensors / bin weights under {model_dir}")
 
@@ -107,18 +114,25 @@ class CheckpointSource:
         return list(self.index.keys())
 
     def get(self, name: str, shape=None, device="cpu", kind: str = "normal") -> torch.Tensor:
-        kind_, f, k = self.index[name]
+        kind_, f, k, transpose = self.index[name]
         if kind_ == "st":
             from safetensors import safe_open
             with safe_open(f, framework="pt") as sf:
-                return sf.get_tensor(k)
-        return self._bin_cache[f][k]
+                t = sf.get_tensor(k)
+        else:
+            t = self._bin_cache[f][k]
+        return t.t().contiguous() if transpose else t
 
 
 class DictSource:
     def __init__(self, tensors: Dict[str, torch.Tensor], model_type: str = "llama"):
         rules = load_weight_map(model_type)
-        self.t = {apply_weight_map(k, rules): v for k, v in tensors.items()}
+        self.t = {}
+        for k, v in tensors.items():
+            name = apply_weight_map(k, rules)
+            if name.endswith(".conv1d_t"):
+                name, v = name[: -len(".conv1d_t")], v.t().contiguous()
+            self.t[name] = v
 
     def has(self, name):
         return name in self.t

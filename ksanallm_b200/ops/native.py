@@ -28,6 +28,13 @@ _SIGS = {
     "ksana_moe_align": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
     "ksana_moe_permute": [vp, vp, vp, i32, i32, i32, vp],
     "ksana_moe_combine": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "ksana_gemm_smallm_push": [i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, vp, i64, vp, i32, vp, i32, vp, vp],
+    "ksana_gemm_fp8_block_push": [vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
+    "ksana_gemm_bf16_push": [vp, i32, vp, i32, i32, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
+    "ksana_reduce_norm": [vp, vp, i32, i32, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp, f32, i32, vp, vp, vp, i32, i32,
+                          i64, i64, i64, i64, vp, vp],
+    "ksana_comm_barrier": [vp, vp, i32, i32, vp, vp, vp],
+    "ksana_allreduce_pull": [vp, vp, i32, i32, vp, i64, vp, vp, i64, vp, vp],
     "ksana_norm": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp],
     "ksana_act_mul": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
     "ksana_quant_fp8": [vp, vp, vp, i32, i32, i32, i32, vp],

@@ -19,13 +19,14 @@ from ..ops import dispatch as ops
 
 
 class TPComm:
-    def __init__(self, group=None, rank: int = 0, size: int = 1, backend: str = "nccl", device=None):
+    def __init__(self, group=None, rank: int = 0, size: int = 1, backend: str = "nccl", device=None,
+                 max_tokens: int = 16384, hidden: int = 8192):
         self.group, self.rank, self.size, self.backend = group, rank, size, backend
         self.device = device
         self.symm = None
         if backend == "fused" and size > 1 and device is not None and torch.device(device).type == "cuda":
             from .symm import SymmetricComm
-            self.symm = SymmetricComm(group, rank, size, device)
+            self.symm = SymmetricComm(group, rank, size, device, max_tokens, hidden)
 
     # ---- primitives
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -51,7 +52,10 @@ class TPComm:
         """h += all_reduce(x W^T). Baseline: GEMM, library all-reduce, add. Fused backend: the partial
         product is written into the symmetric buffer and one kernel reduces over peers and adds the residual."""
         if self.symm is not None:
-            return self.symm.row_parallel_linear(x, W, h)
+            return self.symm.row_parallel_norm(x, W, h, None)[0] if h.shape[0] <= 16 else self._rp_nccl(x, W, h)
+        return self._rp_nccl(x, W, h)
+
+    def _rp_nccl(self, x, W, h):
         partial = ops.linear(x, W)
         dist.all_reduce(partial, group=self.group)
         return ops.add(h, partial)

@@ -1,0 +1,180 @@
+"""Symmetric (peer-mapped) buffers and the fused tensor-parallel paths built on them.
+
+Every rank allocates one buffer of identical layout with ``torch.distributed._symmetric_memory`` and
+maps all peers' buffers, so the kernels in ``comm.cu`` and the GEMM push epilogues address peers with
+plain pointers over NVLink. Layout (bytes):
+
+    [0, 4 KiB)              flag pad (per kind and peer: last signalled epoch)
+    slots[2][size]          receive slots for partial products (double buffered by call parity)
+    h, y, yq, yscale        all-gathered residual stream / normalised activations (large batches)
+    stage                   staging area for the plain all-reduce
+
+Row-parallel linear:
+  * up to ``ONE_SHOT_ROWS`` rows: the skinny GEMM pushes its partial product to every rank; each rank sums
+    the slots, adds the residual and normalises all rows itself (one flag exchange, no gather);
+  * more rows: the tiled GEMM pushes each row block to the rank that owns it (reduce-scatter inside the
+    GEMM epilogue); the owner reduces + adds the residual + normalises (+ FP8 quantises) its rows and
+    pushes them to every peer (all-gather), followed by one more flag exchange.
+Every wait is bounded in the kernels; a timeout sets the device error word (see native.check_err_flag).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from ..ops.dispatch import LinearWeight, QTensor, quantize
+
+FLAG_BYTES = 4096
+ONE_SHOT_ROWS = 16
+
+
+def _align(x: int, a: int = 256) -> int:
+    return (x + a - 1) // a * a
+
+
+class SymmetricComm:
+    def __init__(self, group, rank: int, size: int, device, max_tokens: int = 16384, hidden: int = 8192):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group, self.rank, self.size, self.device = group, rank, size, torch.device(device)
+        self.max_tokens, self.hidden = max_tokens, hidden
+        rows_rs = (max_tokens + size - 1) // size
+        self.slot_rows = max(rows_rs, ONE_SHOT_ROWS)
+        self.slot_bytes = _align(self.slot_rows * hidden * 2)
+        off = FLAG_BYTES
+        self.slots_off = [off, off + size * self.slot_bytes]
+        off += 2 * size * self.slot_bytes
+        self.h_off = off; off += _align(max_tokens * hidden * 2)
+        self.y_off = off; off += _align(max_tokens * hidden * 2)
+        self.yq_off = off; off += _align(max_tokens * hidden)
+        self.scale_ld = _align(max_tokens, 4)
+        self.ys_off = off; off += _align((hidden // 128 + 1) * self.scale_ld * 4)
+        self.stage_off = off
+        self.stage_bytes = _align(max_tokens * hidden * 2)
+        off += self.stage_bytes
+        self.total = off
+        self.buf = symm_mem.empty(self.total, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.data_ptrs = (C.c_ulonglong * 8)(*(ptrs + [0] * (8 - size)))
+        self.flag_ptrs = (C.c_ulonglong * 8)(*(ptrs + [0] * (8 - size)))       # flags live at offset 0
+        self.ctrs = torch.zeros(16, dtype=torch.int32, device=self.device)
+        self.parity = 0
+        dist.barrier(group)
+        # local views
+        self.h = self._view(self.h_off, (max_tokens, hidden), torch.bfloat16)
+        self.y = self._view(self.y_off, (max_tokens, hidden), torch.bfloat16)
+        self.yq = self._view(self.yq_off, (max_tokens, hidden), torch.float8_e4m3fn)
+        self.ys = self._view(self.ys_off, (hidden // 128 + 1, self.scale_ld), torch.float32)
+        self.stage = self._view(self.stage_off, (self.stage_bytes // 2,), torch.bfloat16)
+
+    def _view(self, off: int, shape, dtype):
+        n = 1
+        for s in shape:
+            n *= s
+        esz = torch.empty(0, dtype=dtype).element_size()
+        return self.buf[off:off + n * esz].view(dtype).view(*shape)
+
+    def fits(self, x: torch.Tensor) -> bool:
+        return x.is_cuda and x.dtype == torch.bfloat16 and x.numel() * 2 <= self.stage_bytes and x.numel() % 8 == 0
+
+    # ------------------------------------------------------------------ plain collectives
+    def barrier(self):
+        rc = native.lib().ksana_comm_barrier(self.data_ptrs, self.flag_ptrs, self.rank, self.size, self.ctrs.data_ptr(),
+                                             native.err_flag(self.device).data_ptr(), native._st())
+        native._check(rc, "ksana_comm_barrier")
+
+    def all_reduce(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x (bf16, contiguous) summed over ranks (+ residual); one-shot pull over peer memory."""
+        n = x.numel()
+        self.stage[:n].copy_(x.reshape(-1))
+        out = torch.empty_like(x)
+        rc = native.lib().ksana_allreduce_pull(self.data_ptrs, self.flag_ptrs, self.rank, self.size,
+                                               self.ctrs.data_ptr(), self.stage_off, out.data_ptr(),
+                                               residual.data_ptr() if residual is not None else None, n,
+                                               native.err_flag(self.device).data_ptr(), native._st())
+        native._check(rc, "ksana_allreduce_pull")
+        # the staging area is reused by the next call: peers must be done reading it
+        self.barrier()
+        return out
+
+    # ------------------------------------------------------------------ fused row-parallel linear
+    def begin_forward(self):
+        self.parity = 0
+
+    def _push_ptrs(self, parity: int):
+        base = self.slots_off[parity] + self.rank * self.slot_bytes
+        return (C.c_ulonglong * 8)(*[int(self.handle.buffer_ptrs[r]) + base if r < self.size else 0 for r in range(8)])
+
+    def row_parallel_norm(self, x, W: LinearWeight, h: torch.Tensor, norm_w, norm_b=None, eps: float = 1e-6,
+                          layernorm: bool = False, quant_for: Optional[LinearWeight] = None, want_y: bool = True):
+        """h += sum_ranks(x W^T); y = norm(h) in the form the next linear wants. Returns (h, y).
+
+        ``h`` must be the symmetric residual view (``self.h[:M]``) when M > ONE_SHOT_ROWS."""
+        M = x.q.shape[0] if isinstance(x, QTensor) else x.shape[0]
+        H = W.out_features
+        parity = self.parity
+        self.parity ^= 1
+        push = self._push_ptrs(parity)
+        err = native.err_flag(self.device).data_ptr()
+        st = native._st()
+        lib = native.lib()
+        if W.fp8 and not isinstance(x, QTensor):
+            x = quantize(x)
+        one_shot = M <= ONE_SHOT_ROWS
+        rows_per = M if one_shot else (M + self.size - 1) // self.size
+        bias = W.bias.data_ptr() if (W.bias is not None and self.rank == 0) else None
+        if one_shot:
+            scratch, counters = native.gemm_workspace(self.device)
+            if W.fp8:
+                rc = lib.ksana_gemm_smallm_push(1, x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0),
+                                                W.wq.data_ptr(), W.wq.stride(0), W.ws.data_ptr(), H, bias, M, H,
+                                                W.in_features, scratch.data_ptr(), scratch.numel() * 4,
+                                                counters.data_ptr(), counters.numel(), push, self.size, err, st)
+            else:
+                rc = lib.ksana_gemm_smallm_push(0, x.data_ptr(), x.stride(0), None, 0, W.w.data_ptr(), W.w.stride(0),
+                                                None, H, bias, M, H, W.in_features, scratch.data_ptr(),
+                                                scratch.numel() * 4, counters.data_ptr(), counters.numel(), push,
+                                                self.size, err, st)
+            native._check(rc, "ksana_gemm_smallm_push")
+        else:
+            if W.fp8:
+                rc = lib.ksana_gemm_fp8_block_push(x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0),
+                                                   W.wq.data_ptr(), W.wq.stride(0), W.ws.data_ptr(), H, bias, M, H,
+                                                   W.in_features, 0, push, self.size, rows_per, err, st)
+            else:
+                rc = lib.ksana_gemm_bf16_push(x.data_ptr(), x.stride(0), W.w.data_ptr(), W.w.stride(0), H, bias, M, H,
+                                              W.in_features, 0, push, self.size, rows_per, err, st)
+            native._check(rc, "ksana_gemm_push")
+        want_q = quant_for is not None and quant_for.fp8 and H % 128 == 0 and norm_w is not None
+        if one_shot:
+            row_begin, row_count, gather = 0, M, 0
+            y = torch.empty(M, H, dtype=torch.bfloat16, device=self.device) if (norm_w is not None and not want_q) else None
+            yq = torch.empty(M, H, dtype=torch.float8_e4m3fn, device=self.device) if want_q else None
+            ys = torch.empty(H // 128, 16, dtype=torch.float32, device=self.device) if want_q else None
+            scale_ld = 16
+        else:
+            row_begin = min(self.rank * rows_per, M)
+            row_count = max(0, min(rows_per, M - row_begin))
+            gather = 1
+            assert h.data_ptr() == self.h.data_ptr(), "large-batch row-parallel linear needs the symmetric residual view"
+            y = self.y[:M] if (norm_w is not None and not want_q) else None
+            yq = self.yq[:M] if want_q else None
+            ys = self.ys if want_q else None
+            scale_ld = self.scale_ld
+        rc = lib.ksana_reduce_norm(self.data_ptrs, self.flag_ptrs, self.rank, self.size, self.ctrs.data_ptr(),
+                                   self.slots_off[parity], self.slot_bytes, row_begin, row_count, M, H, h.data_ptr(),
+                                   norm_w.data_ptr() if norm_w is not None else None,
+                                   norm_b.data_ptr() if norm_b is not None else None, float(eps), int(layernorm),
+                                   y.data_ptr() if y is not None else None, yq.data_ptr() if yq is not None else None,
+                                   ys.data_ptr() if ys is not None else None, scale_ld, gather, self.h_off, self.y_off,
+                                   self.yq_off, self.ys_off, err, st)
+        native._check(rc, "ksana_reduce_norm")
+        if norm_w is None:
+            return h, None
+        return h, (QTensor(yq, ys) if want_q else y)

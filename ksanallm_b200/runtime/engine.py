@@ -285,6 +285,7 @@ class LLMEngine:
     def add_request(self, prompt: List[int], sampling=None, stream: bool = False, structured_regex: str = "",
                     request_target: Optional[dict] = None, refit=None, mrope_positions=None) -> Request:
         cfg = sampling or ne.SamplingConfig()
+        cfg.verify_args()          # normalises in place (e.g. beams need as many log-probs as beams); errors resurface below
         with self._lock:
             req_id = self._next_req
             self._next_req += 1

@@ -1,0 +1,236 @@
+"""The serving object behind the HTTP front and the Python package API: owns the LLM (model + engine
+loop), converts generation configs into native SamplingConfig objects, runs plugin pre/post-processing,
+and exposes blocking, streaming and forward (tensor extraction) calls.
+
+Public behaviour follows src/ksana_llm/python/ksana_llm/serving_model.py:22-233 and the service layer
+behind it (src/ksana_llm/endpoints/local/local_endpoint.cpp:31-128,
+src/ksana_llm/endpoints/streaming/streaming_iterator.cpp:17-100): generate returns (Status, output) where
+output carries input_tokens / output_tokens / logprobs per returned sequence; the streaming iterator yields
+the cumulative outputs after every step and aborts the request when it is dropped.
+"""
+from __future__ import annotations
+
+import asyncio
+import threading
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from ..config import load_model_config, load_yaml_config
+from ..llm import LLM
+from ..runtime.sampler import beam_final_order
+from ..utils import native_engine as ne
+from .forward_api import verify_request_target
+from .plugin import KsanaPlugin, PluginConfig
+from .request_packer import pack_responses, unpack_requests
+
+
+@dataclass
+class EndpointConfig:
+    type: str = "python"
+    host: str = "0.0.0.0"
+    port: int = 8080
+    access_log: bool = True
+
+
+class Status:
+    def __init__(self, code: int = 0, message: str = ""):
+        self.code, self.message = int(code), message
+
+    def OK(self) -> bool:
+        return self.code == 0
+
+    def GetCode(self):
+        return self
+
+    @property
+    def value(self) -> int:
+        return self.code
+
+    def GetMessage(self) -> str:
+        return self.message
+
+    def ToString(self) -> str:
+        return "OK" if self.OK() else f"{self.code}: {self.message}"
+
+
+@dataclass
+class KsanaPythonOutput:
+    input_tokens: List[int] = field(default_factory=list)
+    output_tokens: List[List[int]] = field(default_factory=list)
+    logprobs: List[list] = field(default_factory=list)
+    response: Dict[str, Any] = field(default_factory=dict)
+    finished: bool = False
+
+
+def make_sampling_config(gen: Any) -> "ne.SamplingConfig":
+    """HF-style generation config (object or dict) -> native SamplingConfig. ``do_sample=False`` (or unset
+    with default top-k) means greedy, i.e. topk=1 (serving_model.py:220-233 of the reference)."""
+    get = (lambda k, d=None: gen.get(k, d)) if isinstance(gen, dict) else (lambda k, d=None: getattr(gen, k, d))
+    c = ne.SamplingConfig()
+    c.topk = int(get("top_k", get("topk", 1)) or 1)
+    c.topp = float(get("top_p", get("topp", 1.0)) or 1.0)
+    c.temperature = float(get("temperature", 1.0) or 1.0)
+    do_sample = get("do_sample", None)
+    if do_sample is False or (do_sample is None and c.topk == 1):
+        c.topk = 1
+    mx = get("max_new_tokens", -1)
+    c.max_new_tokens = int(mx) if mx is not None and int(mx) > 0 else 1024
+    c.logprobs_num = int(get("logprobs_num", get("logprobs", 0)) or 0)
+    c.repetition_penalty = float(get("repetition_penalty", 1.0) or 1.0)
+    c.no_repeat_ngram_size = int(get("no_repeat_ngram_size", 0) or 0)
+    c.encoder_no_repeat_ngram_size = int(get("encoder_no_repeat_ngram_size", 0) or 0)
+    c.num_beams = int(get("num_beams", 1) or 1)
+    c.num_return_sequences = int(get("num_return_sequences", 1) or 1)
+    c.length_penalty = float(get("length_penalty", 1.0) or 1.0)
+    c.stop_strings = list(get("stop_strings", []) or [])
+    c.stop_token_ids = [int(t) for t in (get("stop_token_ids", []) or [])]
+    c.ignore_eos = bool(get("ignore_eos", False))
+    seed = get("seed", 0)
+    c.seed = int(seed) if seed else 0
+    return c
+
+
+class PyAsyncStreamingIterator:
+    """Async iterator over a streaming request. Dropping it (client disconnect) aborts the request."""
+
+    def __init__(self, engine, req, output_fn):
+        self.engine, self.req, self.output_fn = engine, req, output_fn
+        self._done = False
+
+    def __aiter__(self):
+        return self
+
+    def _next_blocking(self):
+        item = self.req.stream_queue.get()
+        return item
+
+    async def __anext__(self):
+        if self._done:
+            raise StopAsyncIteration
+        loop = asyncio.get_event_loop()
+        item = await loop.run_in_executor(None, self._next_blocking)
+        if item is None:
+            self._done = True
+            if self.req.status_code != 0:
+                raise StopAsyncIteration
+            raise StopAsyncIteration
+        return self.output_fn(self.req)
+
+    def __del__(self):
+        if not self._done and not self.req.done.is_set():
+            self.engine.abort(self.req)
+
+
+class ServingModel:
+    def __init__(self, config_file: str, llm: Optional[LLM] = None, tokenizer=None):
+        self._config_file = config_file
+        self.llm = llm
+        self.tokenizer = tokenizer
+        self.plugin: Optional[KsanaPlugin] = None
+        self.endpoint_config = EndpointConfig()
+        self.model_cfg = llm.model_cfg if llm is not None else None
+
+    # ------------------------------------------------------------------ lifecycle
+    def init_serving(self, plugin_config: Optional[PluginConfig] = None, endpoint_config: Optional[EndpointConfig] = None,
+                     weights="checkpoint", device: Optional[str] = None):
+        if endpoint_config is not None:
+            self.endpoint_config = endpoint_config
+        if self.llm is None:
+            cfg = load_yaml_config(self._config_file)
+            self.llm = LLM(cfg, None, weights=weights, device=device, tokenizer=self.tokenizer)
+            self.model_cfg = self.llm.model_cfg
+        self.llm.engine.tokenizer = self.tokenizer
+        if plugin_config is not None:
+            self.plugin = KsanaPlugin(plugin_config)
+        prof = self.llm.engine_cfg.profiler
+        if prof.attributes:
+            ne.metrics_set_attributes(dict(prof.attributes))
+        if prof.metrics_export_url:
+            ne.metrics_start_export(prof.metrics_export_url, prof.export_interval_millis)
+        if prof.trace_export_url:
+            ne.span_set_sink(prof.trace_export_url)
+        if self.llm.rank == 0:
+            self.llm.engine.start()
+
+    def shutdown(self):
+        if self.llm is not None:
+            self.llm.shutdown(stop_followers=True)
+        ne.metrics_stop_export()
+
+    # ------------------------------------------------------------------ generate
+    def _output_of(self, req) -> KsanaPythonOutput:
+        outs = list(req.outputs)
+        cfg = req.cfg
+        if cfg.num_beams > 1 and req.all_finished():
+            order = beam_final_order(outs, cfg.length_penalty)
+            outs = [outs[i] for i in order][:max(cfg.num_return_sequences, 1)]
+        return KsanaPythonOutput(input_tokens=list(req.prompt), output_tokens=[list(o.tokens) for o in outs],
+                                 logprobs=[list(o.logprobs) for o in outs], finished=req.all_finished())
+
+    def generate(self, model_name: str = "", inputs: Optional[List[int]] = None, generation_config: Any = None,
+                 streamer=None, messages=None, req_ctx: Optional[Dict[str, str]] = None, **kwargs):
+        """Returns (Status, KsanaPythonOutput) or, with ``streamer``, (Status, async iterator)."""
+        gen = generation_config if generation_config is not None else {}
+        sampling = make_sampling_config(gen)
+        code, msg = sampling.verify_args()
+        if code != 0:
+            return Status(code, msg), None
+        ksana_input = {"input_tokens": list(inputs or []), "input_refit_embedding": kwargs.get("input_refit_embedding") or {},
+                       "additional_params": kwargs.get("additional_params") or {}, "prompt": kwargs.get("prompt")}
+        if self.plugin is not None:
+            self.plugin.preprocess(ksana_python_input=ksana_input, messages=messages,
+                                   additional_params=ksana_input["additional_params"])
+        tokens = ksana_input["input_tokens"]
+        if not tokens:
+            return Status(1, "empty input tokens"), None
+        refit = None
+        emb = ksana_input.get("input_refit_embedding") or {}
+        if emb.get("pos") and emb.get("embeddings") is not None:
+            embs = [torch.as_tensor(e, dtype=torch.float32) for e in emb["embeddings"]]
+            refit = (list(emb["pos"]), embs)
+        mrope = ksana_input.get("additional_tensors", {}).get("mrope_positions") if isinstance(ksana_input.get("additional_tensors"), dict) else None
+        span = ne.span_start("generate", (req_ctx or {}).get("traceparent", ""))
+        req = self.llm.engine.add_request(tokens, sampling, stream=bool(streamer),
+                                          structured_regex=kwargs.get("structured_output_regex") or "",
+                                          refit=refit, mrope_positions=mrope)
+        req.span_id = span
+        if req.done.is_set() and req.status_code != 0:
+            return Status(req.status_code, req.status_message), None
+        if streamer:
+            return Status(), PyAsyncStreamingIterator(self.llm.engine, req, self._output_of)
+        req.done.wait()
+        if req.status_code != 0:
+            return Status(req.status_code, req.status_message), None
+        out = self._output_of(req)
+        if self.plugin is not None:
+            self.plugin.postprocess(ksana_python_input=ksana_input, ksana_python_output=out)
+        return Status(), out
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, request_bytes: bytes, req_ctx: Optional[Dict[str, str]] = None):
+        """msgpack batch of prefill-only requests with request targets -> msgpack responses."""
+        try:
+            reqs_in = unpack_requests(request_bytes, self.tokenizer)
+        except Exception as e:  # noqa: BLE001
+            return Status(1, f"failed to parse request: {e}"), None
+        engine = self.llm.engine
+        pending = []
+        for r in reqs_in:
+            code, msg = verify_request_target(r["request_target"], len(r["input_tokens"]))
+            if code != 0:
+                return Status(code, msg), None
+        for r in reqs_in:
+            s = ne.SamplingConfig()
+            s.max_new_tokens = 1
+            refit = None
+            emb = r.get("input_refit_embedding") or {}
+            if emb.get("pos") and emb.get("embeddings") is not None:
+                refit = (list(emb["pos"]), [torch.as_tensor(e, dtype=torch.float32) for e in emb["embeddings"]])
+            pending.append(engine.add_request(r["input_tokens"], s, request_target=r["request_target"], refit=refit))
+        for req in pending:
+            req.done.wait()
+            if req.status_code != 0:
+                return Status(req.status_code, req.status_message), None
+        return Status(), pack_responses([(req.prompt, req.response) for req in pending])

@@ -1,0 +1,225 @@
+"""HTTP front: ``POST /generate`` (JSON in; JSON out, or a stream of JSON chunks each terminated by a
+zero byte) and ``POST /forward`` (msgpack in / out), plus ``GET /metrics`` (Prometheus text).
+
+Request / response fields, the chunk framing and the HTTP 500 ``{"message", "code"}`` error body follow
+src/ksana_llm/python/serving_server.py:41-449. Only node rank 0 serves HTTP; other ranks follow the
+engine's broadcast step plans.
+
+  python -m ksanallm_b200.serving.serving_server --config_file ksana_llm.yaml --port 8080
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import os
+from concurrent.futures import ThreadPoolExecutor
+from functools import partial
+from typing import Any, Dict, List, Optional
+
+import msgpack
+import yaml
+
+from ..utils import native_engine as ne
+from .plugin import PluginConfig
+from .serving_model import EndpointConfig, ServingModel
+
+TRACE_HEADERS = ("x-remote-ip", "traceparent")
+
+
+def args_config(argv=None):
+    p = argparse.ArgumentParser()
+    p.add_argument("--config_file", type=str, default="examples/ksana_llm.yaml", help="serving config file")
+    p.add_argument("--tokenizer_dir", type=str, default=None, help="tokenizer dir (default: the model dir)")
+    p.add_argument("--host", type=str, default="0.0.0.0")
+    p.add_argument("--port", type=int, default=8080)
+    p.add_argument("--endpoint", type=str, default="python", help="server endpoint type")
+    p.add_argument("--access-log", action=argparse.BooleanOptionalAction, default=True)
+    p.add_argument("--ssl-keyfile", type=str, default=None)
+    p.add_argument("--ssl-certfile", type=str, default=None)
+    p.add_argument("--root-path", type=str, default=None)
+    p.add_argument("--random-weights", action="store_true", help="serve a random-init model (tests, benchmarks)")
+    args = p.parse_args(argv)
+    prepare_config(args)
+    return args
+
+
+def prepare_config(args):
+    """Resolve model / tokenizer dirs and the plugin settings from the YAML."""
+    args.config_file = os.path.abspath(args.config_file)
+    with open(args.config_file, "r", encoding="utf-8") as f:
+        doc = yaml.safe_load(f) or {}
+    base = (doc.get("model_spec") or {}).get("base_model") or {}
+    model_dir = str(base.get("model_dir", ""))
+    if model_dir and not os.path.isabs(model_dir):
+        model_dir = os.path.normpath(os.path.join(os.path.dirname(args.config_file), model_dir))
+    args.model_dir = model_dir
+    if args.tokenizer_dir is None:
+        args.tokenizer_dir = base.get("tokenizer_dir") or model_dir
+    plugin = (doc.get("model_spec") or {}).get("plugin_model") or {}
+    args.plugin_enable_trt = bool(plugin.get("enable_tensorrt", True))
+    args.plugin_thread_pool_size = int(plugin.get("plugin_thread_pool_size", 1))
+    args.endpoint = (doc.get("setting") or {}).get("endpoint_type", args.endpoint)
+    args.model_type = ""
+    cfg_path = os.path.join(model_dir, "config.json")
+    if os.path.exists(cfg_path):
+        with open(cfg_path, "r", encoding="utf-8") as f:
+            mc = json.load(f)
+        args.model_type = mc.get("model_type", "")
+        if args.model_type == "qwen" and "visual" in mc:
+            args.model_type = "qwen_vl"
+
+
+def load_tokenizer(tokenizer_dir: str):
+    from transformers import AutoTokenizer
+    return AutoTokenizer.from_pretrained(tokenizer_dir, trust_remote_code=True)
+
+
+def _sampling_dict(sampling_config: Optional[dict], tokenizer) -> dict:
+    sc = dict(sampling_config or {})
+    stop_token_ids = list(sc.get("stop_token_ids", []) or [])
+    ignore_eos = bool(sc.get("ignore_eos", False))
+    eos = getattr(tokenizer, "eos_token_id", None) if tokenizer is not None else None
+    if eos is not None and not ignore_eos and eos not in stop_token_ids:
+        stop_token_ids.append(eos)
+    return {
+        "top_k": sc.get("topk", 1), "do_sample": sc.get("do_sample", None), "top_p": sc.get("topp", 1.0),
+        "temperature": sc.get("temperature", 1.0), "max_new_tokens": sc.get("max_new_tokens", -1),
+        "logprobs_num": sc.get("logprobs", 0), "repetition_penalty": sc.get("repetition_penalty", 1.0),
+        "no_repeat_ngram_size": sc.get("no_repeat_ngram_size", 0),
+        "encoder_no_repeat_ngram_size": sc.get("encoder_no_repeat_ngram_size", 0),
+        "num_beams": sc.get("num_beams", 1), "num_return_sequences": sc.get("num_return_sequences", 1),
+        "length_penalty": sc.get("length_penalty", 1.0), "stop_strings": sc.get("stop_strings", []),
+        "stop_token_ids": stop_token_ids, "ignore_eos": ignore_eos, "seed": sc.get("seed", 0),
+    }
+
+
+def _decode(tokenizer, tokens: List[int], strip_partial: bool = False) -> str:
+    if tokenizer is None:
+        return ""
+    text = tokenizer.decode(tokens, skip_special_tokens=True)
+    return text.rstrip("�") if strip_partial else text
+
+
+def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExecutor] = None):
+    from fastapi import FastAPI, Request
+    from fastapi.responses import JSONResponse, PlainTextResponse, Response, StreamingResponse
+
+    app = FastAPI()
+    executor = executor or ThreadPoolExecutor(max_workers=256)
+
+    def trace_ctx(request) -> Dict[str, str]:
+        return {h: request.headers.get(h) for h in TRACE_HEADERS if request.headers.get(h) is not None}
+
+    def to_json(out) -> dict:
+        return {"texts": [_decode(tokenizer, t) for t in out.output_tokens], "output_token_ids": out.output_tokens,
+                "logprobs": out.logprobs, "input_token_ids": out.input_tokens}
+
+    def render_messages(messages) -> Optional[List[int]]:
+        if tokenizer is None or not hasattr(tokenizer, "apply_chat_template"):
+            return None
+        return tokenizer.apply_chat_template(messages, tokenize=True, add_generation_prompt=True)
+
+    async def process_request(request_dict: Dict[str, Any], req_ctx: Dict[str, str]):
+        model_name = request_dict.pop("model_name", "")
+        prompt_text = request_dict.pop("prompt", None)
+        messages = request_dict.pop("messages", None)
+        enable_streaming = request_dict.pop("stream", True)
+        sampling_config = request_dict.pop("sampling_config", None)
+        regex = request_dict.pop("structured_output_regex", None)
+        input_tokens = request_dict.pop("input_tokens", None)
+        if input_tokens is None and prompt_text is not None and tokenizer is not None:
+            input_tokens = tokenizer.encode(prompt_text, add_special_tokens=True)
+        if input_tokens is None and messages is not None and (model.plugin is None or not model.plugin.loaded):
+            input_tokens = render_messages(messages)
+        kwargs = {"input_refit_embedding": {}, "additional_params": request_dict.pop("additional_params", None) or {},
+                  "prompt": prompt_text}
+        emb = request_dict.pop("input_refit_embedding", None)
+        if emb is not None:
+            for k in ("pos", "embeddings"):
+                if k in emb:
+                    kwargs["input_refit_embedding"][k] = emb[k]
+        if regex is not None:
+            kwargs["structured_output_regex"] = regex
+        gen = _sampling_dict(sampling_config, tokenizer)
+        loop = asyncio.get_event_loop()
+        call = partial(model.generate, model_name=model_name, inputs=input_tokens, generation_config=gen,
+                       messages=messages, streamer=True if enable_streaming else None, req_ctx=req_ctx, **kwargs)
+        status, result = await loop.run_in_executor(executor, call)
+        if not status.OK():
+            return status, None, enable_streaming
+        if enable_streaming:
+            async def stream_results():
+                async for out in result:
+                    if out is None:
+                        return
+                    body = {"texts": [_decode(tokenizer, t, True) for t in out.output_tokens],
+                            "output_token_ids": out.output_tokens, "logprobs": out.logprobs,
+                            "input_token_ids": out.input_tokens}
+                    yield json.dumps(body).encode() + b"\0"
+            return status, stream_results(), True
+        return status, to_json(result), False
+
+    @app.post("/generate")
+    async def generate(request: Request):
+        req_ctx = trace_ctx(request)
+        request_dict = await request.json()
+        status, results, streaming = await process_request(request_dict, req_ctx)
+        if not status.OK():
+            return JSONResponse({"message": status.GetMessage(), "code": status.GetCode().value}, status_code=500)
+        if streaming:
+            return StreamingResponse(results)
+        return JSONResponse(results)
+
+    @app.post("/forward")
+    async def forward(request: Request):
+        req_ctx = trace_ctx(request)
+        body = await request.body()
+        loop = asyncio.get_event_loop()
+        status, response_bytes = await loop.run_in_executor(executor, partial(model.forward, body, req_ctx))
+        if status.OK() and response_bytes is not None:
+            return Response(content=response_bytes, media_type="application/x-msgpack")
+        err = msgpack.packb({"message": status.GetMessage(), "code": status.GetCode().value})
+        return Response(content=err, status_code=500, media_type="application/x-msgpack")
+
+    @app.get("/metrics")
+    async def metrics():
+        return PlainTextResponse(ne.metrics_prometheus())
+
+    @app.get("/health")
+    async def health():
+        return JSONResponse({"status": "ok"})
+
+    return app
+
+
+def main(argv=None):
+    args = args_config(argv)
+    tokenizer = load_tokenizer(args.tokenizer_dir) if args.tokenizer_dir and os.path.isdir(args.tokenizer_dir) else None
+    model = ServingModel(args.config_file, tokenizer=tokenizer)
+    plugin_config = PluginConfig(model_dir=args.model_dir, config_file=args.config_file, plugin_name=args.model_type,
+                                 enable_trt=args.plugin_enable_trt, thread_num=args.plugin_thread_pool_size)
+    endpoint_config = EndpointConfig(args.endpoint, args.host, args.port, args.access_log)
+    model.init_serving(plugin_config, endpoint_config, weights="random" if args.random_weights else "checkpoint")
+    rank = int(os.environ.get("RANK", "0"))
+    node_rank = int(os.environ.get("NODE_RANK", "0"))
+    if rank != 0 or node_rank != 0:
+        while model.llm.follow():      # worker ranks: execute broadcast step plans until the stop signal
+            pass
+        return
+    import uvicorn
+    app = create_app(model, tokenizer)
+    log_level = os.environ.get("KLLM_LOG_LEVEL", "INFO").lower()
+    if log_level in ("debug", "info", "warning", "error"):
+        pass
+    else:
+        log_level = "info"
+    try:
+        uvicorn.run(app, host=args.host, port=args.port, log_level=log_level, access_log=args.access_log,
+                    ssl_keyfile=args.ssl_keyfile, ssl_certfile=args.ssl_certfile, root_path=args.root_path or "")
+    finally:
+        model.shutdown()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,135 @@
+"""Request-level features through the real engine on CPU: parallel sampling, beam search, log-probs,
+penalties, n-gram bans, stop strings, structured output, streaming + abort, /forward targets, swap."""
+import math
+import threading
+
+import torch
+
+from helpers import ByteTokenizer, sampling, tiny_engine, tiny_model_cfg
+from ksanallm_b200.runtime.sampler import banned_encoder_ngram_tokens, banned_ngram_tokens, beam_final_order
+from ksanallm_b200.serving.forward_api import verify_request_target
+
+
+def test_parallel_sampling_returns_distinct_sequences():
+    eng = tiny_engine()
+    req = eng.generate([[5, 6, 7, 8, 9]], sampling(max_new_tokens=6, ignore_eos=True, topk=50, temperature=1.5,
+                                                   num_return_sequences=4, seed=7))[0]
+    assert req.status_code == 0 and len(req.outputs) == 4
+    assert all(len(o.tokens) == 6 for o in req.outputs)
+    assert len({tuple(o.tokens) for o in req.outputs}) > 1
+    again = tiny_engine().generate([[5, 6, 7, 8, 9]], sampling(max_new_tokens=6, ignore_eos=True, topk=50, temperature=1.5,
+                                                               num_return_sequences=4, seed=7))[0]
+    assert [o.tokens for o in again.outputs] == [o.tokens for o in req.outputs]      # per-request seed
+
+
+def test_greedy_is_argmax_and_logprobs_are_topn_logsoftmax():
+    eng = tiny_engine()
+    captured = []
+    eng.step_hook = lambda plan, logits: captured.append(logits.clone())
+    req = eng.generate([[11, 12, 13]], sampling(max_new_tokens=3, ignore_eos=True, logprobs_num=4))[0]
+    out = req.outputs[0]
+    assert len(out.logprobs) == 3
+    for step, (tok, lps) in enumerate(zip(out.tokens, out.logprobs)):
+        row = captured[step][0]
+        assert tok == int(row.argmax())
+        top = torch.topk(row, 4)
+        want = torch.log_softmax(top.values, -1)
+        assert [i for i, _ in lps] == top.indices.tolist()
+        assert all(abs(a - float(b)) < 1e-4 for (_, a), b in zip(lps, want))
+
+
+def test_repetition_penalty_and_ngram_bans_change_choices():
+    base = tiny_engine().generate([[20, 21, 22, 23]], sampling(max_new_tokens=12, ignore_eos=True))[0].outputs[0].tokens
+    pen = tiny_engine().generate([[20, 21, 22, 23]], sampling(max_new_tokens=12, ignore_eos=True,
+                                                              no_repeat_ngram_size=1))[0].outputs[0].tokens
+    assert len(set(pen + [20, 21, 22, 23])) == len(pen) + 4      # 1-gram ban: no token is ever repeated
+    assert banned_ngram_tokens([1, 2, 3, 1, 2], 3) == [3]
+    assert banned_encoder_ngram_tokens([5, 6, 7], [9, 5], 2) == [6]
+    assert isinstance(base, list)
+
+
+def test_beam_search_orders_by_score_and_beats_greedy():
+    prompt = [30, 31, 32, 33, 34]
+    eng = tiny_engine()
+    req = eng.generate([prompt], sampling(max_new_tokens=5, ignore_eos=True, num_beams=3, num_return_sequences=3))[0]
+    assert req.status_code == 0 and all(len(o.tokens) == 5 for o in req.outputs)
+    order = beam_final_order(req.outputs, 1.0)
+    scores = [req.outputs[i].cum_logprob for i in order]
+    assert scores == sorted(scores, reverse=True)
+    assert len({tuple(o.tokens) for o in req.outputs}) == 3
+    assert eng.scheduler.check_invariants()[0]
+
+
+def test_stop_strings_truncate_output():
+    tok = ByteTokenizer()
+    eng = tiny_engine(tokenizer=tok)
+    free = eng.generate([tok.encode("hello")], sampling(max_new_tokens=12, ignore_eos=True))[0].outputs[0].tokens
+    text = tok.decode(free)
+    stop = text[4:6]
+    eng2 = tiny_engine(tokenizer=tok)
+    req = eng2.generate([tok.encode("hello")], sampling(max_new_tokens=12, ignore_eos=True, stop_strings=[stop]))[0]
+    got = tok.decode(req.outputs[0].tokens)
+    assert stop not in got and text.startswith(got) and len(got) <= text.find(stop)
+    assert eng2.scheduler.idle()
+
+
+def test_structured_output_injects_constants_and_finishes():
+    tok = ByteTokenizer()
+    eng = tiny_engine(tokenizer=tok)
+    regex = r'\{"a": "[a-z]*", "n": [0-9]+\}'
+    req = eng.add_request(tok.encode("x"), sampling(max_new_tokens=60, ignore_eos=True, topk=40, temperature=2.0, seed=3),
+                          structured_regex=regex)
+    while not req.done.is_set():
+        if not eng.step() and eng.scheduler.idle():
+            break
+    text = tok.decode(req.outputs[0].tokens)
+    assert text.startswith('{"a": "')
+    if '", "n": ' in text:              # the free segment ended: the injected constant follows verbatim
+        assert text.count('{"a": "') == 1
+
+
+def test_streaming_queue_and_abort():
+    eng = tiny_engine()
+    eng.start()
+    try:
+        req = eng.add_request([40, 41, 42], sampling(max_new_tokens=200, ignore_eos=True), stream=True)
+        first = req.stream_queue.get(timeout=30)
+        assert first[0] == "step" and len(first[1][0]) >= 1
+        eng.abort(req)
+        assert req.done.wait(30)
+        assert req.status_code == 4 and len(req.outputs[0].tokens) < 200
+    finally:
+        eng.stop()
+
+
+def test_forward_targets_validation_and_values():
+    assert verify_request_target({"logits": {"slice_pos": [[0, 3]], "token_reduce_mode": "GATHER_TOKEN_ID"}}, 6)[0] == 0
+    assert verify_request_target({"logits": {"slice_pos": [[0, 5]], "token_reduce_mode": "GATHER_TOKEN_ID"}}, 6)[0] == 1
+    assert verify_request_target({"logits": {"slice_pos": [[0, 2]], "token_reduce_mode": "GATHER_ALL"}}, 6)[0] == 1
+    assert verify_request_target({"transformer": {"token_id": [3], "slice_pos": [[0, 1]]}}, 6)[0] == 1
+    assert verify_request_target({"bogus": {}}, 6)[0] == 1
+    assert verify_request_target({"layernorm": {"slice_pos": [[-2, -1]]}}, 6) == (0, "")
+    eng = tiny_engine()
+    prompt = [50, 51, 52, 53, 54, 55]
+    target = {"logits": {"slice_pos": [[0, 4]], "token_reduce_mode": "GATHER_TOKEN_ID", "token_id": []},
+              "transformer": {"slice_pos": [[5, 5]], "token_reduce_mode": "GATHER_ALL", "token_id": []},
+              "layernorm": {"slice_pos": [], "token_reduce_mode": "GATHER_ALL", "token_id": []}}
+    req = eng.add_request(prompt, sampling(max_new_tokens=1), request_target=target)
+    while not req.done.is_set():
+        eng.step()
+    probs = req.response["logits"]
+    assert probs.shape == (5,) and bool(((probs > 0) & (probs <= 1)).all())
+    assert req.response["transformer"].shape == (1, 64) and req.response["layernorm"].shape == (1, 64)
+    ppl = math.exp(-float(probs.log().mean()))
+    assert ppl > 1.0
+
+
+def test_swap_under_pressure_keeps_results():
+    prompts = [[60 + i, 61 + i, 62 + i, 63 + i] for i in range(6)]
+    s = sampling(max_new_tokens=40, ignore_eos=True)
+    calm = tiny_engine(num_blocks=128, max_token_len=64).generate(prompts, s)
+    tight = tiny_engine(num_blocks=10, host_blocks=64, max_token_len=64)
+    pressed = tight.generate(prompts, s)
+    assert [r.outputs[0].tokens for r in pressed] == [r.outputs[0].tokens for r in calm]
+    st = tight.scheduler.stats()
+    assert st["preempt_swap"] > 0 and st["swap_in"] > 0

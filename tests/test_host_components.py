@@ -1,0 +1,295 @@
+"""Host runtime components: cache manager, control plane over localhost TCP (incl. host-side failure
+injection), structured-output FSM, profiler / trace recorder, config parsing."""
+import json
+import os
+import threading
+import time
+
+import pytest
+import yaml
+
+from ksanallm_b200 import config as cfgmod
+from ksanallm_b200.utils import native_engine as ne
+
+
+# ----------------------------------------------------------------------------------- cache manager
+def test_cache_manager_prefix_share_evict_and_swap():
+    c = ne.CacheManager(16, 8, 4, True)
+    toks = list(range(100, 119))                       # 4 full blocks + 3 tokens
+    n, blocks = c.acquire_prefix(toks)
+    assert n == 0 and blocks == []
+    ok, blocks = c.allocate(5)
+    assert ok and c.free_blocks == 11
+    promoted, blocks = c.promote(toks, blocks, 19, 0)
+    assert promoted == 4 and all(c.in_tree(b) for b in blocks[:4]) and not c.in_tree(blocks[4])
+    # a second sequence with the same prefix shares the four full blocks
+    n, shared = c.acquire_prefix(toks[:16] + [1, 2])
+    assert n == 16 and shared == blocks[:4] and all(c.ref_count(b) == 2 for b in shared)
+    # identical content computed privately is deduplicated on promotion
+    ok, own = c.allocate(2)
+    p2, merged = c.promote(toks[:8], own, 8, 0)
+    assert p2 == 2 and merged == blocks[:2] and c.ref_count(blocks[0]) == 3
+    c.release(merged); c.release(shared)
+    # swap-out moves only exclusively owned blocks; shared ones stay
+    n, other = c.acquire_prefix(toks[:8] + [9])
+    ok, kept, host, pairs = c.swap_out(list(blocks))
+    assert ok and kept == blocks[:2] and len(host) == 3 and [p[0] for p in pairs] == blocks[2:]
+    assert c.free_host_blocks == 5
+    ok, back, pairs_in = c.swap_in(kept, host)
+    assert ok and len(back) == 5 and c.free_host_blocks == 8
+    c.release(back); c.release(other)
+    assert c.check_invariants()[0] and c.usable_blocks == 16
+    # eviction: filling the pool reclaims cached blocks, oldest first
+    ok, big = c.allocate(16)
+    assert ok and c.free_blocks == 0 and c.evictable_blocks == 0
+    assert c.acquire_prefix(toks)[0] == 0
+    c.release(big)
+    assert c.check_invariants()[0]
+
+
+def test_cache_manager_fork_and_flexible():
+    c = ne.CacheManager(32, 0, 4, True)
+    toks = list(range(50, 64))                         # 3 full + 2
+    ok, blocks = c.allocate(4)
+    _, blocks = c.promote(toks, blocks, 14, 0)
+    ok, dst, copies = c.fork(blocks, 14)
+    assert ok and dst[:3] == blocks[:3] and dst[3] != blocks[3] and copies == [(blocks[3], dst[3])]
+    assert all(c.ref_count(b) == 2 for b in blocks[:3])
+    # flexible cache: the same 8 tokens appear at another position of a new prompt
+    new = [1, 2, 3, 4] + toks[4:12] + [9]
+    n, pre = c.acquire_prefix(new)
+    assert n == 0
+    got, fb, tasks = c.acquire_flexible([7, 7, 7, 7] + toks[4:12] + [9, 9], 4, 8)
+    assert got == 8 and len(fb) == 2 and [t[0] for t in tasks] == blocks[1:3] and all(t[2] == 0 for t in tasks)
+    got2, fb2, tasks2 = c.acquire_flexible(toks[4:12] + [9, 9], 0, 8)
+    assert got2 == 8 and all(t[2] == -4 for t in tasks2)     # one block earlier than where it was computed
+    assert c.check_invariants()[0]
+
+
+# ----------------------------------------------------------------------------------- control plane
+def test_control_plane_barrier_layers_blocknum_broadcast():
+    master = ne.ControlMaster("127.0.0.1", 0, 3, 50, 2000)
+    workers = [ne.ControlWorker("127.0.0.1", master.port, r, 50, 2000) for r in (1, 2)]
+    assert all(w.connect(3000) for w in workers)
+    assert master.wait_for_nodes(3000)
+    res = {}
+
+    def wk(i, w):
+        res[("bar", i)] = w.barrier(3000)
+        res[("layers", i)] = w.get_layers(3000)
+        res[("blocks", i)] = w.sync_block_num(10 - i * 3, 3000)
+        res[("bc", i)] = w.recv_broadcast(3000)
+
+    ts = [threading.Thread(target=wk, args=(i, w)) for i, w in enumerate(workers, 1)]
+    [t.start() for t in ts]
+    assert master.barrier(3000)
+    ranges = master.assign_layers(32, 3000)
+    assert ranges == [(0, 10), (11, 21), (22, 31)]
+    assert master.sync_block_num(6, 3000) == 4
+    assert master.broadcast(b"plan-bytes")
+    [t.join() for t in ts]
+    assert res[("bar", 1)] and res[("bar", 2)]
+    assert res[("layers", 1)] == (11, 21) and res[("layers", 2)] == (22, 31)
+    assert res[("blocks", 1)] == 4 and res[("blocks", 2)] == 4
+    assert res[("bc", 1)] == b"plan-bytes" and res[("bc", 2)] == b"plan-bytes"
+    assert ne.split_layers(32, 2) == [(0, 15), (16, 31)]
+    master.shutdown_cluster()
+    time.sleep(0.2)
+    assert all(w.shutdown_requested() for w in workers)
+    [w.stop() for w in workers]; master.stop()
+
+
+def test_failure_detection_by_eof_and_missed_heartbeats():
+    """Host-side fault injection only: a worker that closes its socket, and one that stops heart-beating."""
+    master = ne.ControlMaster("127.0.0.1", 0, 2, 30, 300)
+    w = ne.ControlWorker("127.0.0.1", master.port, 1, 30, 300)
+    assert w.connect(3000) and master.wait_for_nodes(3000) and master.alive()
+    w.stop()                                            # peer exits between steps
+    for _ in range(100):
+        if not master.alive():
+            break
+        time.sleep(0.02)
+    assert not master.alive() and master.failed_nodes() == [1]
+    assert master.barrier(200) is False                 # collectives fail fast instead of hanging
+    master.stop()
+    # silent worker: registers, then never heart-beats (huge interval) -> the master times it out
+    master = ne.ControlMaster("127.0.0.1", 0, 2, 30, 200)
+    silent = ne.ControlWorker("127.0.0.1", master.port, 1, 10_000_000, 10_000_000)
+    assert silent.connect(3000) and master.wait_for_nodes(3000)
+    for _ in range(150):
+        if not master.alive():
+            break
+        time.sleep(0.02)
+    assert not master.alive()
+    # and the other direction: the master disappears, the worker notices
+    m2 = ne.ControlMaster("127.0.0.1", 0, 2, 30, 300)
+    w2 = ne.ControlWorker("127.0.0.1", m2.port, 1, 30, 300)
+    assert w2.connect(3000) and m2.wait_for_nodes(3000)
+    m2.stop()
+    for _ in range(100):
+        if not w2.alive():
+            break
+        time.sleep(0.02)
+    assert not w2.alive() and w2.barrier(200) is False
+    w2.stop(); silent.stop(); master.stop()
+
+
+# ----------------------------------------------------------------------------------- FSM
+def test_fsm_segments_and_steps():
+    f = ne.FiniteStateMachine(r'\{"name": "[\w\d\s]*", "age": [\d]+\}')
+    segs = f.segments()
+    assert [t for t, _ in segs] == [0, 1, 0, 1, 0]
+    assert segs[0][1] == '{"name": "' and segs[2][1] == '", "age": ' and segs[4][1] == '}'
+    changed, final, text, seg, start = f.step("", 0, 0)
+    assert changed and not final and text == '{"name": "' and seg == 1
+    # free generation continues until the next constant's first character shows up
+    assert f.step(text + "Bob Sm", seg, start)[:3] == (False, False, text + "Bob Sm")
+    changed, final, text2, seg2, start2 = f.step(text + 'Bob Smith"xyz', seg, start)
+    assert changed and text2 == '{"name": "Bob Smith", "age": ' and seg2 == 3
+    changed, final, text3, seg3, _ = f.step(text2 + "42}", seg2, start2)
+    assert final and text3 == '{"name": "Bob Smith", "age": 42}'
+    ctl = ne.FsmController()
+    assert ctl.get_or_create("a[0-9]+b") is ctl.get_or_create("a[0-9]+b") and ctl.size() == 1
+    assert [t for t, _ in ne.FiniteStateMachine(r"yes|no").segments()] == [1]
+    assert ne.FiniteStateMachine(r"a\.b\n").segments() == [(0, "a.b\n")]
+
+
+# ----------------------------------------------------------------------------------- profiler
+def test_metrics_spans_and_chrome_trace(tmp_path):
+    ne.metrics_reset()
+    names = ne.metric_names()
+    assert len(names) == 25 and "time_to_first_token_ms" in names and "block_num_free" in names
+    ne.report_metric("time_to_first_token_ms", 12.5)
+    ne.report_metric("time_to_first_token_ms", 7.5)
+    ne.report_counter("forward_req_total_num", 3)
+    snap = ne.metrics_snapshot()
+    assert snap["time_to_first_token_ms"]["count"] == 2 and snap["time_to_first_token_ms"]["sum"] == 20.0
+    assert snap["forward_req_total_num"]["sum"] == 3
+    text = ne.metrics_prometheus()
+    assert "ksana_time_to_first_token_ms_count 2" in text and "ksana_block_num_used_count 0" in text
+    assert json.loads(ne.metrics_json())["metrics"]["forward_req_total_num"]["sum"] == 3
+    tp = "00-0af7651916cd43dd8448eb211c80319c-b7ad6b7169203331-01"
+    sid = ne.span_start("generate", tp)
+    ne.span_end(sid, {"code": "0"})
+    span = json.loads(ne.spans_finished()[-1])
+    assert span["trace_id"] == "0af7651916cd43dd8448eb211c80319c" and span["parent_id"] == "b7ad6b7169203331"
+    path = str(tmp_path / "trace.json")
+    assert set(ne.trace_event_names()) >= {"SchedBegin", "Prefill", "Decode", "SwapOut", "SwapIn", "FinishReq"}
+    ne.trace_enable(path)
+    ne.trace_record("Prefill", "B", 0, 17)
+    ne.trace_record("Prefill", "E", 0, 17)
+    ne.trace_record("UsableBlockNum", "C", 0, 99)
+    ne.trace_disable()
+    events = json.load(open(path))
+    assert [e["name"] for e in events[:3]] == ["Prefill", "Prefill", "UsableBlockNum"] and events[2]["args"]["value"] == 99
+
+
+# ----------------------------------------------------------------------------------- config
+REFERENCE_STYLE_YAML = """
+setting:
+  global:
+    tensor_para_size: 2
+    pipeline_para_size: 1
+    enable_lora_adapter: false
+    embed_tokens_use_cpu: false
+    enable_cuda_graph: false
+  batch_scheduler:
+    schedule_strategy: 0
+    waiting_timeout_in_ms: 3600000
+    max_waiting_queue_len: 1200
+    max_step_tokens: 4096
+    max_batch_size: 128
+    max_token_len: 2048
+    swapout_block_threshold: 1.0
+    swapin_block_threshold: 2.0
+    launch_block_threshold: 2.0
+    enable_auto_prefix_cache: true
+    split_fuse_token_num: 256
+    swap_threadpool_size: 8
+    preempt_mode: 0
+    min_flexible_cache_num: 0
+  block_manager:
+    block_token_num: 16
+    reserved_device_memory_ratio: 0.01
+    lora_deivce_memory_ratio: 0.0
+    lora_host_memory_factor: 10.0
+    block_device_memory_ratio: -1.0
+    block_host_memory_factor: 2.0
+  quantization_config:
+    gptq_backend: cutlass
+    kv_cache:
+      dtype: fp8_e4m3
+    weight:
+      quant_method: auto
+  profiler:
+    export_interval_millis: 30000
+    export_timeout_millis: 1000
+    attributes:
+      instance: "1.1.1.1"
+      version: "1.1"
+  endpoint_type: python
+  some_future_key: 1
+model_spec:
+  base_model:
+    model_dir: ./model
+  plugin_model:
+    enable_tensorrt: true
+    plugin_thread_pool_size: 1
+"""
+
+
+def test_yaml_config_schema_and_defaults(tmp_path):
+    p = tmp_path / "ksana_llm.yaml"
+    p.write_text(REFERENCE_STYLE_YAML)
+    c = cfgmod.load_yaml_config(str(p))
+    assert c.global_.tensor_para_size == 2 and c.batch_scheduler.max_batch_size == 128
+    assert c.batch_scheduler.split_fuse_token_num == 256 and c.batch_scheduler.enable_auto_prefix_cache
+    assert c.block_manager.block_host_memory_factor == 2.0 and c.quantization.kv_cache_dtype == "fp8_e4m3"
+    assert c.profiler.attributes == {"instance": "1.1.1.1", "version": "1.1"}
+    assert c.model_dir == str(tmp_path / "model") and c.tokenizer_dir == c.model_dir
+    d = cfgmod.EngineConfig()            # defaults of the reference's structs
+    assert (d.batch_scheduler.max_batch_size, d.batch_scheduler.max_waiting_queue_len, d.batch_scheduler.waiting_timeout_in_ms,
+            d.batch_scheduler.max_step_tokens, d.block_manager.reserved_device_memory_ratio,
+            d.block_manager.block_host_memory_factor) == (8, 256, 600000, 4096, 0.05, 10.0)
+    with pytest.raises(ValueError):
+        cfgmod.load_yaml_config({"setting": {"quantization_config": {"kv_cache": {"dtype": "int3"}}}})
+
+
+def test_hf_model_config_variants():
+    llama3 = {"model_type": "llama", "hidden_size": 8192, "num_hidden_layers": 80, "num_attention_heads": 64,
+              "num_key_value_heads": 8, "intermediate_size": 28672, "vocab_size": 128256, "rope_theta": 500000.0,
+              "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "eos_token_id": [128001, 128009],
+              "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                               "original_max_position_embeddings": 8192}}
+    m = cfgmod.model_config_from_hf(llama3)
+    assert (m.head_dim, m.num_kv_heads, m.eos_token_ids) == (128, 8, [128001, 128009]) and m.rope_scaling["factor"] == 8.0
+    q = cfgmod.model_config_from_hf({"model_type": "qwen2", "hidden_size": 8192, "num_attention_heads": 64,
+                                     "num_key_value_heads": 8, "num_hidden_layers": 80, "intermediate_size": 29568,
+                                     "vocab_size": 152064})
+    assert q.model_type == "qwen" and q.qkv_bias
+    g = cfgmod.model_config_from_hf({"model_type": "gpt2", "n_embd": 768, "n_layer": 12, "n_head": 12, "vocab_size": 50257})
+    assert g.norm_type == "layernorm" and not g.gated_mlp and g.position_embedding == "learned" and g.tie_word_embeddings
+    b = cfgmod.model_config_from_hf({"model_type": "baichuan", "hidden_size": 5120, "num_attention_heads": 40,
+                                     "num_hidden_layers": 40, "intermediate_size": 13696, "vocab_size": 125696})
+    assert b.position_embedding == "alibi" and b.lm_head_norm
+    glm = cfgmod.model_config_from_hf({"model_type": "chatglm", "hidden_size": 4096, "num_attention_heads": 32,
+                                       "num_layers": 28, "ffn_hidden_size": 13696, "multi_query_group_num": 2,
+                                       "multi_query_attention": True, "padded_vocab_size": 65024, "kv_channels": 128})
+    assert glm.rotary_dim == 64 and not glm.rope_neox and glm.num_kv_heads == 2
+    ds = cfgmod.model_config_from_hf({"model_type": "deepseek_v3", "hidden_size": 7168, "num_hidden_layers": 61,
+                                      "num_attention_heads": 128, "n_routed_experts": 256, "num_experts_per_tok": 8,
+                                      "moe_intermediate_size": 2048, "n_shared_experts": 1, "kv_lora_rank": 512,
+                                      "q_lora_rank": 1536, "qk_nope_head_dim": 128, "qk_rope_head_dim": 64,
+                                      "v_head_dim": 128, "first_k_dense_replace": 3, "n_group": 8, "topk_group": 4,
+                                      "intermediate_size": 18432, "vocab_size": 129280,
+                                      "quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}})
+    assert ds.is_mla and ds.is_moe and ds.moe_scoring == "sigmoid" and ds.fp8_checkpoint and ds.head_dim == 192
+    assert cfgmod.kv_block_bytes(m, 16, 8, 1, 2) == 80 * 1 * 128 * 16 * 2 * 2
+    with pytest.raises(ValueError):
+        cfgmod.check_tp(m, 3)
+
+
+def test_kv_scale_file(tmp_path):
+    p = tmp_path / "kv_cache_scales.json"
+    p.write_text(json.dumps({"kv_cache": {"dtype": "float8_e4m3fn", "scaling_factor": {"0": {"0": 0.5, "1": 0.25}}}}))
+    assert cfgmod.load_kv_scales(str(p), 2) == [[0.5, 0.5], [0.25, 0.25]]

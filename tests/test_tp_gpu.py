@@ -1,0 +1,44 @@
+"""Tensor parallelism on 2+ GPUs: fused peer-memory path vs the NCCL path vs a single-GPU run."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _launch(nproc, out, backend, quant, port):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py"),
+           out, backend, quant]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return torch.load(out)
+
+
+def rel(a, b):
+    return float((a - b).norm() / b.norm())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("quant,tol", [("auto", 3e-2), ("fp8_block", 0.15)])
+def test_tp2_fused_matches_nccl_and_single(tmp_path, quant, tol):
+    n = 2
+    single = _launch(1, str(tmp_path / "single.pt"), "nccl", quant, 29631)
+    nccl = _launch(n, str(tmp_path / "nccl.pt"), "nccl", quant, 29632)
+    fused = _launch(n, str(tmp_path / "fused.pt"), "fused", quant, 29633)
+    assert rel(nccl["first"], single["first"]) < tol
+    assert rel(fused["first"], single["first"]) < tol
+    assert rel(fused["first"], nccl["first"]) < tol
+    assert fused["graph_replays"] > 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_tp4_fused(tmp_path):
+    single = _launch(1, str(tmp_path / "single.pt"), "nccl", "auto", 29641)
+    fused = _launch(4, str(tmp_path / "fused4.pt"), "fused", "auto", 29642)
+    assert rel(fused["first"], single["first"]) < 3e-2

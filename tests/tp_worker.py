@@ -1,0 +1,59 @@
+"""Worker of the multi-GPU tests (launched by torchrun, one rank per GPU): runs a small Llama with tensor
+parallelism through the fused peer-memory path and through the NCCL path and writes the logits of rank 0."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ksanallm_b200.config import EngineConfig, ModelConfig  # noqa: E402
+from ksanallm_b200.llm import LLM  # noqa: E402
+from ksanallm_b200.models.weights import RandomSource  # noqa: E402
+from ksanallm_b200.ops import native  # noqa: E402
+from ksanallm_b200.utils import native_engine as ne  # noqa: E402
+
+
+def main():
+    out_path, backend, quant = sys.argv[1], sys.argv[2], sys.argv[3]
+    mc = ModelConfig(model_type="llama", hidden_size=1024, num_layers=3, num_heads=8, num_kv_heads=4, head_dim=128,
+                     intermediate_size=2048, vocab_size=32000, rms_norm_eps=1e-5, max_position_embeddings=512,
+                     max_token_len=512)
+    ec = EngineConfig()
+    ec.global_.comm_backend = backend
+    ec.global_.enable_cuda_graph = backend == "fused"
+    ec.batch_scheduler.max_batch_size = 8
+    ec.batch_scheduler.max_token_len = 300
+    ec.batch_scheduler.max_step_tokens = 512
+    ec.block_manager.device_blocks_num = 128
+    ec.quantization.weight_quant_method = quant
+    llm = LLM(ec, mc, weights=RandomSource(seed=11, std=0.05), device="cuda")
+    first, last = {}, {}
+
+    def hook(plan, lg):
+        for i, sid in enumerate(plan.sample_seq_ids.tolist()):
+            row = lg[i].float().cpu().clone()
+            first.setdefault(sid, row)
+            last[sid] = row
+
+    llm.engine.step_hook = hook
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (70, 5, 33, 128)]
+    s = ne.SamplingConfig()
+    s.max_new_tokens, s.ignore_eos = 5, True
+    reqs = llm.generate(prompts if llm.rank == 0 else [], s)
+    torch.cuda.synchronize()
+    native.check_err_flag(llm.device)
+    if llm.rank == 0:
+        order = sorted(first)
+        torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "first": torch.stack([first[k] for k in order]),
+                    "last": torch.stack([last[k] for k in order]),
+                    "graph_replays": getattr(llm.engine.runner, "graph_replays", 0)}, out_path)
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
