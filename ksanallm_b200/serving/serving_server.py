@@ -19,6 +19,8 @@ from typing import Any, Dict, List, Optional
 
 import msgpack
 import yaml
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, Response, StreamingResponse
 
 from ..utils import native_engine as ne
 from .plugin import PluginConfig
@@ -102,9 +104,6 @@ def _decode(tokenizer, tokens: List[int], strip_partial: bool = False) -> str:
 
 
 def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExecutor] = None):
-    from fastapi import FastAPI, Request
-    from fastapi.responses import JSONResponse, PlainTextResponse, Response, StreamingResponse
-
     app = FastAPI()
     executor = executor or ThreadPoolExecutor(max_workers=256)
 

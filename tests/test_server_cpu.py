@@ -1,0 +1,98 @@
+"""HTTP surface on CPU: /generate (blocking + zero-byte-delimited streaming), /forward (msgpack), errors, metrics."""
+import json
+
+import msgpack
+import pytest
+import torch
+
+from helpers import ByteTokenizer, tiny_model_cfg
+from ksanallm_b200.config import EngineConfig
+from ksanallm_b200.llm import LLM
+from ksanallm_b200.serving.clients import perplexity_from_forward
+from ksanallm_b200.serving.request_packer import unpack_tensor
+from ksanallm_b200.serving.serving_model import ServingModel, make_sampling_config
+from ksanallm_b200.serving.serving_server import create_app
+
+
+@pytest.fixture(scope="module")
+def client():
+    from fastapi.testclient import TestClient
+    tok = ByteTokenizer()
+    ec = EngineConfig()
+    ec.batch_scheduler.max_batch_size = 8
+    ec.batch_scheduler.max_token_len = 128
+    ec.block_manager.device_blocks_num = 128
+    ec.block_manager.host_blocks_num = 16
+    llm = LLM(ec, tiny_model_cfg(), weights="random", device="cpu", dtype=torch.float32, tokenizer=tok)
+    model = ServingModel("", llm=llm, tokenizer=tok)
+    model.init_serving()
+    with TestClient(create_app(model, tok)) as c:
+        yield c
+    model.shutdown()
+
+
+def test_generate_blocking(client):
+    r = client.post("/generate", json={"prompt": "hello", "stream": False,
+                                       "sampling_config": {"max_new_tokens": 6, "ignore_eos": True, "logprobs": 2}})
+    assert r.status_code == 200
+    body = r.json()
+    assert set(body) == {"texts", "output_token_ids", "logprobs", "input_token_ids"}
+    assert len(body["output_token_ids"]) == 1 and len(body["output_token_ids"][0]) == 6
+    assert body["input_token_ids"] == ByteTokenizer().encode("hello")
+    assert len(body["logprobs"][0]) == 6 and len(body["logprobs"][0][0]) == 2
+    r2 = client.post("/generate", json={"input_tokens": body["input_token_ids"], "stream": False,
+                                        "sampling_config": {"max_new_tokens": 6, "ignore_eos": True}})
+    assert r2.json()["output_token_ids"] == body["output_token_ids"]       # greedy is deterministic
+
+
+def test_generate_streaming_chunks(client):
+    with client.stream("POST", "/generate", json={"prompt": "abc", "stream": True,
+                                                  "sampling_config": {"max_new_tokens": 5, "ignore_eos": True}}) as r:
+        raw = b"".join(r.iter_bytes())
+    chunks = [json.loads(c) for c in raw.split(b"\0") if c]
+    assert len(chunks) >= 1 and len(chunks[-1]["output_token_ids"][0]) == 5
+    lens = [len(c["output_token_ids"][0]) for c in chunks]
+    assert lens == sorted(lens)
+
+
+def test_generate_chat_messages_and_n(client):
+    r = client.post("/generate", json={"messages": [{"role": "user", "content": "hi"}], "stream": False,
+                                       "sampling_config": {"max_new_tokens": 3, "ignore_eos": True, "topk": 20,
+                                                           "temperature": 1.3, "num_return_sequences": 2}})
+    assert r.status_code == 200 and len(r.json()["output_token_ids"]) == 2
+
+
+def test_generate_errors_are_http_500_with_code(client):
+    r = client.post("/generate", json={"prompt": "x", "stream": False, "sampling_config": {"topk": 5000}})
+    assert r.status_code == 500 and r.json()["code"] == 1 and "topk" in r.json()["message"]
+    r = client.post("/generate", json={"input_tokens": list(range(3, 203)), "stream": False, "sampling_config": {}})
+    assert r.status_code == 500 and r.json()["code"] == 6
+
+
+def test_forward_msgpack_roundtrip(client):
+    toks = ByteTokenizer().encode("perplexity")
+    req = {"requests": [{"input_tokens": toks, "request_target": [
+        {"target_name": "logits", "slice_pos": [[0, len(toks) - 2]], "token_reduce_mode": "GATHER_TOKEN_ID"},
+        {"target_name": "layernorm", "token_reduce_mode": "GATHER_ALL"}]}]}
+    r = client.post("/forward", content=msgpack.packb(req, use_bin_type=True))
+    assert r.status_code == 200
+    doc = msgpack.unpackb(r.content, raw=False)
+    assert doc["code"] == 0 and doc["responses"][0]["input_token_ids"] == toks
+    tensors = {t["target_name"]: unpack_tensor(t["tensor"]) for t in doc["responses"][0]["response"]}
+    assert tensors["logits"].shape == (len(toks) - 1,) and tensors["layernorm"].shape == (1, 64)
+    for t in doc["responses"][0]["response"]:
+        t["tensor"] = unpack_tensor(t["tensor"])
+    assert perplexity_from_forward(doc)[0] > 1.0
+    bad = {"requests": [{"input_tokens": toks, "request_target": [{"target_name": "logits", "slice_pos": [[0, len(toks) - 1]],
+                                                                   "token_reduce_mode": "GATHER_TOKEN_ID"}]}]}
+    r = client.post("/forward", content=msgpack.packb(bad, use_bin_type=True))
+    assert r.status_code == 500 and msgpack.unpackb(r.content, raw=False)["code"] == 1
+
+
+def test_metrics_endpoint_and_sampling_mapping(client):
+    text = client.get("/metrics").text
+    assert "ksana_forward_req_total_num_count" in text and "ksana_time_to_first_token_ms_count" in text
+    c = make_sampling_config({"top_k": 40, "do_sample": False, "max_new_tokens": -1})
+    assert c.topk == 1 and c.max_new_tokens == 1024
+    c = make_sampling_config({"top_k": 40, "do_sample": True, "top_p": 0.9, "stop_token_ids": [2]})
+    assert c.topk == 40 and abs(c.topp - 0.9) < 1e-6 and c.stop_token_ids == [2]

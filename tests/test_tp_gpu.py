@@ -20,6 +20,19 @@ def _launch(nproc, out, backend, quant, port):
     return torch.load(out)
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_peer_memory_primitives(tmp_path):
+    out_dir = os.environ.get("KSANA_TP_LOG_DIR", str(tmp_path))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    n = min(torch.cuda.device_count(), 8)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", "29621", os.path.join(ROOT, "tests", "tp_comm_worker.py"), out_dir]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    logs = "".join(open(os.path.join(out_dir, f)).read() for f in sorted(os.listdir(out_dir)) if f.startswith("tp_comm_rank"))
+    assert r.returncode == 0, logs + r.stdout[-2000:] + r.stderr[-3000:]
+    assert "done" in logs
+
+
 def rel(a, b):
     return float((a - b).norm() / b.norm())
 
