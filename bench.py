@@ -202,13 +202,13 @@ def main():
             res["e2e"] = {"value": out_tokens / (e2e_ms / 1000.0), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps}
         print(json.dumps(res))
+    sys.stdout.flush()
     llm.shutdown()
     if world > 1:
         import torch.distributed as dist
-        if rank == 0:
-            from ksanallm_b200.parallel.control import broadcast_plan
         dist.barrier()
-        dist.destroy_process_group()
+        # nothing is in flight and the result line is out: leave without communicator teardown
+        os._exit(0)
     return 0
 
 

@@ -305,6 +305,25 @@ __global__ void allreduce_pull_kernel(const CommPeers c, uint32_t* ctrs, long lo
   end_epoch(ctrs, 3, epoch);
 }
 
+// All-gather along the last dimension by pulling: every rank staged its [rows, src_ld] fp32 shard at the same
+// symmetric offset; out[row, r * cols + c] = shard_r[row, c] for c < cols.
+__global__ void allgather_pull_kernel(const CommPeers c, uint32_t* ctrs, long long off, float* out, int rows, int cols,
+                                      int src_ld, int dst_ld, int* err) {
+  const uint32_t epoch = begin_epoch(ctrs, 3);
+  if (!signal_and_wait(c, 3, epoch, err, true)) return;
+  const long long per_rank = static_cast<long long>(rows) * cols;
+  const long long total = per_rank * c.size;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / per_rank);
+    const long long j = i - r * per_rank;
+    const int row = static_cast<int>(j / cols), col = static_cast<int>(j % cols);
+    const float* src = reinterpret_cast<const float*>(static_cast<const uint8_t*>(c.data[r]) + off);
+    out[static_cast<long long>(row) * dst_ld + static_cast<long long>(r) * cols + col] = src[static_cast<long long>(row) * src_ld + col];
+  }
+  end_epoch(ctrs, 3, epoch);
+}
+
 static CommPeers make_peers(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank, int size) {
   CommPeers c{};
   for (int i = 0; i < size && i < kMaxRanks; ++i) {
@@ -371,5 +390,18 @@ extern "C" int ksana_allreduce_pull(const unsigned long long* data_ptrs, const u
                                                              static_cast<uint32_t*>(ctrs), off,
                                                              static_cast<bf16*>(out),
                                                              static_cast<const bf16*>(residual), nvec, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_allgather_pull(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank,
+                                    int size, void* ctrs, long long off, float* out, int rows, int cols, int src_ld,
+                                    int dst_ld, int* err, cudaStream_t st) {
+  const long long total = static_cast<long long>(rows) * cols * size;
+  long long g = (total + 255) / 256;
+  if (g > 148 * 8) g = 148 * 8;
+  if (g < 1) g = 1;
+  allgather_pull_kernel<<<static_cast<int>(g), 256, 0, st>>>(make_peers(data_ptrs, flag_ptrs, rank, size),
+                                                             static_cast<uint32_t*>(ctrs), off, out, rows, cols,
+                                                             src_ld, dst_ld, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

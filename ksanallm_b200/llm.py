@@ -162,6 +162,7 @@ class LLM:
 
     def shutdown(self, stop_followers: bool = False):
         """Stops the engine loop. ``stop_followers`` additionally releases worker ranks blocked in ``follow``."""
+        self.engine.runner.release_graphs()
         if self.rank == 0:
             self.engine.stop()
             if stop_followers and self.world > 1:

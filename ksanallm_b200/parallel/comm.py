@@ -42,6 +42,10 @@ class TPComm:
         if self.size == 1:
             return x
         x = x.contiguous()
+        if self.symm is not None and x.is_cuda:
+            out = self.symm.all_gather_cols(x, valid or x.shape[1])
+            if out is not None:
+                return out
         parts = [torch.empty_like(x) for _ in range(self.size)]
         dist.all_gather(parts, x, group=self.group)
         v = valid or x.shape[1]

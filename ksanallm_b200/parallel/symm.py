@@ -103,6 +103,21 @@ class SymmetricComm:
         self.barrier()
         return out
 
+    def all_gather_cols(self, x: torch.Tensor, valid: int) -> Optional[torch.Tensor]:
+        """[rows, n] fp32 shards -> [rows, size * valid] by pulling the peers' staged shards. None if it does not fit."""
+        rows, n = x.shape
+        if x.dtype != torch.float32 or rows * n * 4 > self.stage_bytes:
+            return None
+        stage = self.stage.view(torch.float32)[: rows * n].view(rows, n)
+        stage.copy_(x)
+        out = torch.empty(rows, self.size * valid, dtype=torch.float32, device=self.device)
+        rc = native.lib().ksana_allgather_pull(self.data_ptrs, self.flag_ptrs, self.rank, self.size,
+                                               self.ctrs.data_ptr(), self.stage_off, out.data_ptr(), rows, valid, n,
+                                               self.size * valid, native.err_flag(self.device).data_ptr(), native._st())
+        native._check(rc, "ksana_allgather_pull")
+        self.barrier()          # peers are done reading the stage before it is written again
+        return out
+
     # ------------------------------------------------------------------ fused row-parallel linear
     def begin_forward(self):
         self.parity = 0

@@ -180,6 +180,13 @@ class ModelRunner:
         self.graph_max_blocks = (max_token_len + self.block_tokens - 1) // self.block_tokens + 1
         self.graph_max_kv = max_token_len
 
+    def release_graphs(self):
+        """Drop the captured graphs (before tearing down process groups / the device context)."""
+        if getattr(self, "graphs", None):
+            self.graphs.clear()
+            if self.cuda:
+                torch.cuda.synchronize(self.device)
+
     def _graph_for(self, bs: int):
         g = self.graphs.get(bs)
         if g is not None:

@@ -86,6 +86,14 @@ def main():
             say(f"row_parallel_norm M={M} quant={quant}: rel err h {e_h:.4f} y {e_y:.4f}")
             results[(M, quant)] = (e_h, e_y)
             assert e_h < 2e-2 and e_y < (8e-2 if quant else 2e-2)
+    # column all-gather (logits shards)
+    shard = torch.randn(5, 1000, device=dev, dtype=torch.float32) + rank
+    gathered = comm.all_gather_cols(shard, 996)
+    parts = [torch.empty_like(shard) for _ in range(world)]
+    dist.all_gather(parts, shard)
+    torch.cuda.synchronize()
+    assert torch.equal(gathered, torch.cat([p[:, :996] for p in parts], 1))
+    say("all_gather_cols ok")
     # device-timed comparison with the library path on a decode-sized and a prefill-sized case
     for M in (8, 2048 if MAXT >= 2048 else 512):
         K = 1024
@@ -122,7 +130,8 @@ def main():
     native.check_err_flag(dev)
     say("done")
     dist.barrier()
-    dist.destroy_process_group()
+    log.close()
+    os._exit(0)
 
 
 if __name__ == "__main__":

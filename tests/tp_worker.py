@@ -16,18 +16,39 @@ from ksanallm_b200.utils import native_engine as ne  # noqa: E402
 
 def main():
     out_path, backend, quant = sys.argv[1], sys.argv[2], sys.argv[3]
+    graphs = (sys.argv[4] == "graphs") if len(sys.argv) > 4 else backend == "fused"
+    log_dir = os.environ.get("KSANA_TP_LOG_DIR")
+    rank_env = os.environ.get("RANK", "0")
+    log = open(os.path.join(log_dir, f"tp_model_{backend}_{quant}_{int(graphs)}_rank{rank_env}.log"), "w") if log_dir else None
+
+    def say(*a):
+        if log:
+            log.write(" ".join(str(x) for x in a) + "\n")
+            log.flush()
+
     mc = ModelConfig(model_type="llama", hidden_size=1024, num_layers=3, num_heads=8, num_kv_heads=4, head_dim=128,
                      intermediate_size=2048, vocab_size=32000, rms_norm_eps=1e-5, max_position_embeddings=512,
                      max_token_len=512)
     ec = EngineConfig()
     ec.global_.comm_backend = backend
-    ec.global_.enable_cuda_graph = backend == "fused"
+    ec.global_.enable_cuda_graph = graphs
     ec.batch_scheduler.max_batch_size = 8
     ec.batch_scheduler.max_token_len = 300
     ec.batch_scheduler.max_step_tokens = 512
     ec.block_manager.device_blocks_num = 128
     ec.quantization.weight_quant_method = quant
+    say("building")
     llm = LLM(ec, mc, weights=RandomSource(seed=11, std=0.05), device="cuda")
+    say("llm ready")
+    inner = llm.engine.runner.execute
+
+    def traced(plan, extra=None):
+        say("execute: seqs", len(plan.seq_ids), "tokens", plan.num_tokens, "multi", plan.num_multi)
+        out = inner(plan, extra)
+        say("launched")
+        return out
+
+    llm.engine.runner.execute = traced
     first, last = {}, {}
 
     def hook(plan, lg):
@@ -42,7 +63,9 @@ def main():
     s = ne.SamplingConfig()
     s.max_new_tokens, s.ignore_eos = 5, True
     reqs = llm.generate(prompts if llm.rank == 0 else [], s)
+    say("generate returned")
     torch.cuda.synchronize()
+    say("synchronised")
     native.check_err_flag(llm.device)
     if llm.rank == 0:
         order = sorted(first)
@@ -50,9 +73,15 @@ def main():
                     "last": torch.stack([last[k] for k in order]),
                     "graph_replays": getattr(llm.engine.runner, "graph_replays", 0)}, out_path)
     import torch.distributed as dist
+    llm.shutdown()
+    say("shut down")
     if dist.is_initialized():
         dist.barrier()
-        dist.destroy_process_group()
+        say("barrier passed")
+    if log:
+        log.close()
+    sys.stdout.flush()
+    os._exit(0)      # skip communicator teardown: nothing is in flight and the results are on disk
 
 
 if __name__ == "__main__":
