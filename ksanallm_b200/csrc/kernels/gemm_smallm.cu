@@ -442,3 +442,77 @@ extern "C" int ksana_gemm_smallm_push(int kind, const void* X, int ldx, const fl
   return smallm_impl(kind, X, ldx, a_scale, a_scale_ld, W, ldw, w_scale, nullptr, nullptr, ldd, bias, nullptr, 0, M, N,
                      K, 0, scratch, scratch_bytes, counters, counters_len, err_flag, st, push_ptrs, push_n);
 }
+
+// ----------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (see ksana_noalloc.h). The scratch the split-K path needs is
+// a device array inside this library image; host code only ever holds its device address, which
+// it gets from cudaGetSymbolAddress once per device.
+#include "ksana_noalloc.h"
+#include <stdio.h>
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kKsanaNoAllocScratchBytes];
+static __device__ __align__(256) unsigned int g_noalloc_counters[kKsanaNoAllocMaxTiles];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_noalloc_scratch_addr[kMaxDevices];      // device addresses, filled on first use per device
+void* g_noalloc_counter_addr[kMaxDevices];
+bool g_noalloc_ready[kMaxDevices];
+thread_local char g_noalloc_msg[256] = "";
+}  // namespace
+
+extern "C" const char* ksana_noalloc_last_error(void) { return g_noalloc_msg; }
+
+extern "C" int ksana_gemm_smallm_noalloc(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld,
+                                         const void* W, int ldw, const float* w_scale, void* D, int ldd,
+                                         const void* bias, const void* residual, int ldr, int M, int N, int K,
+                                         int* err_flag, cudaStream_t stream) {
+  g_noalloc_msg[0] = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ksana_gemm_smallm_noalloc: cannot query the current device");
+    return KSANA_NOALLOC_SETUP_FAILED;
+  }
+  if (!g_noalloc_ready[dev]) {
+    // In host code the array names are host-side stand-ins, not device pointers: ask the runtime for the
+    // device addresses, with this device current, and check that it worked.
+    void* s = nullptr;
+    void* c = nullptr;
+    const cudaError_t e1 = cudaGetSymbolAddress(&s, g_noalloc_scratch);
+    const cudaError_t e2 = cudaGetSymbolAddress(&c, g_noalloc_counters);
+    if (e1 != cudaSuccess || e2 != cudaSuccess || s == nullptr || c == nullptr) {
+      snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ksana_gemm_smallm_noalloc: cudaGetSymbolAddress failed on device %d: %s",
+               dev, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+      return KSANA_NOALLOC_SETUP_FAILED;
+    }
+    g_noalloc_scratch_addr[dev] = s;
+    g_noalloc_counter_addr[dev] = c;
+    g_noalloc_ready[dev] = true;
+  }
+  if (M <= 0 || N <= 0 || K <= 0) return KSANA_NOALLOC_OK;
+  const int n_tiles = (N + 127) / 128;
+  if (M > 128 || n_tiles > kKsanaNoAllocMaxTiles) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg),
+             "ksana_gemm_smallm_noalloc: M=%d N=%d exceed the built-in limits (M <= 128, N <= %d)", M, N,
+             128 * kKsanaNoAllocMaxTiles);
+    return KSANA_NOALLOC_TOO_LARGE;
+  }
+  // The built-in scratch must hold the partial tiles of the split the kernel would choose; the shared
+  // implementation shrinks the split to what fits, so only the no-split minimum can be too large.
+  const int MP = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  const long long min_need = static_cast<long long>(n_tiles) * 2 * MP * 128 * 4;
+  if (min_need > kKsanaNoAllocScratchBytes) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg),
+             "ksana_gemm_smallm_noalloc: M=%d N=%d need %lld bytes of scratch, the built-in array has %d", M, N,
+             min_need, static_cast<int>(kKsanaNoAllocScratchBytes));
+    return KSANA_NOALLOC_TOO_LARGE;
+  }
+  // Counters must start at zero; an earlier call that gave up half-way may have left some behind.
+  if (cudaMemsetAsync(g_noalloc_counter_addr[dev], 0, sizeof(unsigned int) * n_tiles, stream) != cudaSuccess) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ksana_gemm_smallm_noalloc: clearing the tile counters failed");
+    return KSANA_NOALLOC_SETUP_FAILED;
+  }
+  return smallm_impl(kind, X, ldx, a_scale, a_scale_ld, W, ldw, w_scale, D, nullptr, ldd, bias, residual, ldr, M, N, K,
+                     0, g_noalloc_scratch_addr[dev], kKsanaNoAllocScratchBytes, g_noalloc_counter_addr[dev],
+                     kKsanaNoAllocMaxTiles, err_flag, stream, nullptr, 0);
+}
