@@ -211,9 +211,26 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
       } else {
         const float* ws = p.w_scale + static_cast<size_t>(sg.tile) * nkb_scale;
-        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+        // Activation scales of one k-block are MP consecutive floats: lane l keeps tokens l, l+32, ... and the
+        // value for column i is broadcast with a shuffle. The next k-block's scales are fetched before waiting
+        // for the current accumulator, so no load sits on the critical path.
+        constexpr int NS = (MP + 31) / 32;
+        float s_next[NS];
+        auto fetch = [&](int kb, float (&dst)[NS]) {
           const float wsc = ws[kb];
           const float* as = p.a_scale + static_cast<size_t>(kb) * p.a_scale_ld;
+#pragma unroll
+          for (int j = 0; j < NS; ++j) {
+            const int tok = j * 32 + lane;
+            dst[j] = (tok < p.M) ? as[tok] * wsc : 0.f;
+          }
+        };
+        fetch(sg.kb0, s_next);
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          float s_cur[NS];
+#pragma unroll
+          for (int j = 0; j < NS; ++j) s_cur[j] = s_next[j];
+          if (kb + 1 < sg.kb1) fetch(kb + 1, s_next);
           if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           if constexpr (MP >= 32) {
@@ -224,7 +241,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const float sc = (c0 + i < p.M) ? as[c0 + i] * wsc : 0.f;
+                const float sc = __shfl_sync(0xffffffffu, s_cur[c0 / 32], i);
                 accv[c0 + i] = fmaf(sc, __uint_as_float(r[i]), accv[c0 + i]);
               }
             }
@@ -234,7 +251,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float sc = (i < p.M) ? as[i] * wsc : 0.f;
+              const float sc = __shfl_sync(0xffffffffu, s_cur[0], i);
               accv[i] = fmaf(sc, __uint_as_float(r[i]), accv[i]);
             }
           }

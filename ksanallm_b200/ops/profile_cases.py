@@ -1,0 +1,118 @@
+"""Small, self-contained launches of the hot kernels for profiling (each case runs its kernel twice).
+
+  python -m ksanallm_b200.ops.profile_cases [case ...]
+  ncu --set full --clock-control none -k regex:<kernel> -c <n> -o prof python -m ksanallm_b200.ops.profile_cases <case>
+
+Cases keep a few hundred MB on the device: larger than L2 where DRAM figures matter, small enough for a
+multi-pass capture to finish in a minute or two.
+"""
+from __future__ import annotations
+
+import math
+import sys
+
+import torch
+
+from . import native, reference as ref
+
+DEV = "cuda"
+
+
+def _w8(n, k):
+    wq = (torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * 0.05).to(torch.float8_e4m3fn)
+    return wq, torch.ones((n + 127) // 128, k // 128, device=DEV)
+
+
+def case_skinny_fp8():       # decode gate|up shard: 8 tokens, 235 MB of FP8 weights streamed once
+    wq, ws = _w8(28672, 8192)
+    xq, xs = native.quant_fp8(torch.randn(8, 8192, device=DEV, dtype=torch.bfloat16))
+    y = torch.empty(8, 28672, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        native.gemm_fp8(xq, xs, wq, ws, out=y)
+
+
+def case_skinny_bf16():
+    w = torch.randn(14336, 8192, device=DEV, dtype=torch.bfloat16) * 0.05
+    x = torch.randn(8, 8192, device=DEV, dtype=torch.bfloat16)
+    y = torch.empty(8, 14336, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        native.gemm_bf16(x, w, out=y)
+
+
+def case_gemm_fp8():         # prefill-sized FP8 GEMM: 4096 x 10240 x 8192 (256-wide tiles, split epilogue)
+    wq, ws = _w8(10240, 8192)
+    xq, xs = native.quant_fp8(torch.randn(4096, 8192, device=DEV, dtype=torch.bfloat16))
+    y = torch.empty(4096, 10240, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        native.gemm_fp8(xq, xs, wq, ws, out=y)
+
+
+def case_gemm_bf16():
+    w = torch.randn(8192, 8192, device=DEV, dtype=torch.bfloat16) * 0.05
+    x = torch.randn(4096, 8192, device=DEV, dtype=torch.bfloat16)
+    y = torch.empty(4096, 8192, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        native.gemm_bf16(x, w, out=y)
+
+
+def _paged(B, kv_len, Hq, Hkv, D, q_len):
+    bt = 16
+    nblk = (kv_len + bt - 1) // bt
+    cache = torch.randn(B * nblk, 2, Hkv, bt, D, device=DEV, dtype=torch.bfloat16)
+    table = torch.arange(B * nblk, device=DEV, dtype=torch.int32).view(B, nblk)
+    q = torch.randn(B * q_len, (Hq + 2 * Hkv) * D, device=DEV, dtype=torch.bfloat16)
+    cu = torch.arange(0, (B + 1) * q_len, q_len, device=DEV, dtype=torch.int32)
+    kvl = torch.full((B,), kv_len, device=DEV, dtype=torch.int32)
+    out = torch.empty(B * q_len, Hq * D, device=DEV, dtype=torch.bfloat16)
+    return q, cache, table, cu, kvl, out
+
+
+def case_decode_attn():      # 64 sequences x 2304 cached tokens, 64 q / 8 kv heads: 604 MB of K/V read once
+    B, kv, Hq, Hkv, D = 64, 2304, 64, 8, 128
+    q, cache, table, cu, kvl, out = _paged(B, kv, Hq, Hkv, D, 1)
+    splits = 1
+    for _ in range(2):
+        native.paged_decode(q, q.stride(0), out, cache, cache.stride(0), 16, table, kvl, B, Hq, Hkv, D, 1 / math.sqrt(D),
+                            num_splits=splits)
+
+
+def case_prefill_attn():     # 4 sequences x 2048 new tokens, 64 q / 8 kv heads
+    B, kv, Hq, Hkv, D = 4, 2048, 64, 8, 128
+    q, cache, table, cu, kvl, out = _paged(B, kv, Hq, Hkv, D, kv)
+    for _ in range(2):
+        native.paged_prefill(q, q.stride(0), out, cache, cache.stride(0), 16, table, cu, kvl, B, kv, Hq, Hkv, D,
+                             1 / math.sqrt(D))
+
+
+def case_norm_quant():       # residual add + RMSNorm + FP8 quantisation of 16384 x 8192 activations (805 MB moved)
+    x = torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16)
+    r = torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16)
+    w = torch.ones(8192, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        native.norm(x, w, 1e-5, residual=r, quant=True, want_out=False)
+
+
+def case_sampler():
+    logits = torch.randn(64, 128256, device=DEV)
+    B = 64
+    args = (torch.ones(B, device=DEV), torch.full((B,), 50, device=DEV, dtype=torch.int32), torch.full((B,), 0.9, device=DEV),
+            torch.arange(B, device=DEV, dtype=torch.int64) + 1, torch.zeros(B, device=DEV, dtype=torch.int32),
+            torch.zeros(B, device=DEV, dtype=torch.int32))
+    for _ in range(2):
+        native.sample(logits, *args)
+
+
+CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
+
+
+def main(argv):
+    names = argv or list(CASES)
+    for n in names:
+        CASES[n]()
+        torch.cuda.synchronize()
+        native.check_err_flag(DEV)
+        print("ran", n)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
