@@ -22,16 +22,22 @@
 // (3rdparty/LLM_kernels/csrc/kernels/nvidia/paged_attention/paged_attention.cu:81-640)
 // and of its FlashAttention-2 call (src/ksana_llm/kernels/nvidia/kernel_wrapper.cpp:437-588),
 // without the reverse cache copy the latter needs.
-#include <cuda_runtime.h>
+#include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
 
 namespace ksana {
 
+// K/V staging modes: plain cp.async (any block size), FP8 cache with conversion, or TMA: one elected thread
+// issues a 2-D bulk tensor copy per (cache block, 64-column half) - the per-16-byte address arithmetic of
+// the cp.async path made the decode kernel instruction-bound at a third of HBM bandwidth.
+enum KvMode { kKvCpAsync = 0, kKvFp8 = 1, kKvTma = 2 };
+
 typedef __nv_bfloat16 bf16;
 constexpr int kTileTok = 64;     // KV tokens per shared-memory tile
 constexpr int kAttnThreads = 128;
+constexpr int kKvStages = 3;      // K/V tile ring: two tiles in flight while one is consumed
 
 struct AttnParams {
   const bf16* q; long long q_stride;     // [T, q_stride] ; head h at column h*D
@@ -48,6 +54,7 @@ struct AttnParams {
   float k_scale, v_scale;                // fp8 cache dequant scales
   // decode split workspace
   float* part_o; float* part_ml; int num_splits;
+  int* err;                              // device word set when a bounded wait gave up
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -76,10 +83,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Shared tile: `rows` rows of D bf16; 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
-template <int D>
+// Shared tile of ROWS rows x D bf16, stored as D/64 panels of [ROWS][64] (128-byte rows); inside a panel the
+// 16-byte chunk cc of row r lives at chunk (cc ^ (r & 7)): exactly what a TMA copy with the 128-byte swizzle
+// writes, and conflict-free for ldmatrix.
+template <int D, int ROWS>
 __device__ __forceinline__ bf16* tile_ptr(bf16* base, int r, int chunk) {
-  return base + r * D + ((chunk ^ (r & 7)) << 3);
+  return base + (chunk >> 3) * (ROWS * 64) + r * 64 + (((chunk & 7) ^ (r & 7)) << 3);
 }
 
 // Stage one K or V tile (kTileTok tokens x D) of kv head g into shared memory.
@@ -90,7 +99,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* dst, const AttnParams& p, con
   for (int i = threadIdx.x; i < kTileTok * CH; i += kAttnThreads) {
     const int r = i / CH, c = i % CH;
     const int tok = tok0 + r;
-    bf16* d = tile_ptr<D>(dst, r, c);
+    bf16* d = tile_ptr<D, kTileTok>(dst, r, c);
     if (tok < kv_len) {
       const int blk = table[tok / p.block_tokens];
       const size_t off = static_cast<size_t>(blk) * p.block_stride +
@@ -116,6 +125,42 @@ __device__ __forceinline__ void load_kv_tile(bf16* dst, const AttnParams& p, con
   }
 }
 
+// TMA staging of one K + V tile (one thread): a box of [block_tokens rows x 64 columns] per cache block and
+// 64-column panel. Tokens past kv_len inside the last block are loaded as they are (finite cache contents)
+// and masked by the softmax; blocks past the sequence are not loaded at all.
+template <int D>
+__device__ __forceinline__ void tma_issue_kv(bf16* ks, bf16* vs, uint64_t* bar, const CUtensorMap* map, const AttnParams& p,
+                                             const int* table, int g, int tok0, int kv_len, long long rows_per_block) {
+  const int bt = p.block_tokens;
+  const int nblk = min(kTileTok / bt, (kv_len - tok0 + bt - 1) / bt);
+  constexpr int PANELS = D / 64;
+  mbar_expect_tx(bar, static_cast<uint32_t>(nblk) * 2 * PANELS * bt * 128);
+  for (int b = 0; b < nblk; ++b) {
+    const long long row0 = static_cast<long long>(table[tok0 / bt + b]) * rows_per_block;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      bf16* dst = which ? vs : ks;
+      const int y = static_cast<int>(row0 + (static_cast<long long>(which) * p.Hkv + g) * bt);
+#pragma unroll
+      for (int h = 0; h < PANELS; ++h) tma_load_2d(dst + h * (kTileTok * 64) + b * bt * 64, map, bar, h * 64, y);
+    }
+  }
+}
+
+// After a TMA-staged tile has landed: zero the V rows of tokens past the sequence end (rows of blocks that were
+// not loaded hold stale shared memory, rows past kv_len inside the last block hold whatever the cache has there);
+// their probabilities are exactly 0, but 0 x NaN would poison the output. K needs nothing: its scores are masked.
+template <int D>
+__device__ __forceinline__ void zero_v_tail(bf16* vs, int valid_rows) {
+  if (valid_rows >= kTileTok) return;
+  constexpr int CH = D / 8;
+  const int n = (kTileTok - valid_rows) * CH;
+  for (int i = threadIdx.x; i < n; i += kAttnThreads) {
+    const int r = valid_rows + i / CH, c = i % CH;
+    *reinterpret_cast<uint4*>(tile_ptr<D, kTileTok>(vs, r, c)) = make_uint4(0, 0, 0, 0);
+  }
+}
+
 // One warp: S(16 x NT*8 tokens) = Q(16 x D) K^T over tokens [t0, t0 + NT*8) of the staged tile.
 template <int D, int NT>
 __device__ __forceinline__ void warp_qk(float (&s)[NT][4], const uint32_t (&qf)[D / 16][4], bf16* ks, int t0, int lane) {
@@ -128,7 +173,7 @@ __device__ __forceinline__ void warp_qk(float (&s)[NT][4], const uint32_t (&qf)[
       uint32_t b[4];
       const int r = t0 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
       const int c = kk * 2 + ((lane >> 3) & 1);
-      ldsm_x4(b, smem_addr(tile_ptr<D>(ks, r, c)));
+      ldsm_x4(b, smem_addr(tile_ptr<D, kTileTok>(ks, r, c)));
       mma16816(s[2 * jp], qf[kk], b[0], b[1]);
       mma16816(s[2 * jp + 1], qf[kk], b[2], b[3]);
     }
@@ -150,7 +195,7 @@ __device__ __forceinline__ void warp_pv(float (&o)[D / 8][4], const float (&s)[N
       uint32_t b[4];
       const int r = t0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
       const int c = np * 2 + (lane >> 4);
-      ldsm_x4_t(b, smem_addr(tile_ptr<D>(vs, r, c)));
+      ldsm_x4_t(b, smem_addr(tile_ptr<D, kTileTok>(vs, r, c)));
       mma16816(o[2 * np], a, b[0], b[1]);
       mma16816(o[2 * np + 1], a, b[2], b[3]);
     }
@@ -205,13 +250,17 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[D /
 }
 
 // ----------------------------------------------------------------------------- prefill
-template <int D, bool FP8>
+template <int D, int MODE>
 __global__ void __launch_bounds__(kAttnThreads)
-paged_prefill_kernel(const AttnParams p) {
-  extern __shared__ __align__(128) uint8_t smem_attn[];
+paged_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams p, const long long rows_per_block) {
+  constexpr bool FP8 = MODE == kKvFp8;
+  extern __shared__ uint8_t smem_attn_raw[];
+  uint8_t* smem_attn = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_attn_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[kKvStages];
+  __shared__ uint32_t abort_word;
   bf16* qs = reinterpret_cast<bf16*>(smem_attn);            // 64 x D
-  bf16* ks = qs + 64 * D;                                   // 2 x (64 x D)
-  bf16* vs = ks + 2 * kTileTok * D;                         // 2 x (64 x D)
+  bf16* ks = qs + 64 * D;                                   // kKvStages x (64 x D)
+  bf16* vs = ks + kKvStages * kTileTok * D;                 // kKvStages x (64 x D)
 
   const int s = blockIdx.z, g = blockIdx.y;
   const int G = p.Hq / p.Hkv;
@@ -233,16 +282,35 @@ paged_prefill_kernel(const AttnParams p) {
       const int tok = vr / G, head = g * G + vr % G;
       v = *reinterpret_cast<const uint4*>(p.q + static_cast<size_t>(q0 + tok) * p.q_stride + head * D + c * 8);
     }
-    *reinterpret_cast<uint4*>(tile_ptr<D>(qs, r, c)) = v;
+    *reinterpret_cast<uint4*>(tile_ptr<D, 64>(qs, r, c)) = v;
   }
   // causal bound of this CTA's rows
   const int last_row = min(row0 + 63, q_len * G - 1);
   const int kv_end = min(kv_len, past + last_row / G + 1);
   const int ntiles = (kv_end + kTileTok - 1) / kTileTok;
 
-  load_kv_tile<D, FP8>(ks, p, table, g, 0, 0, kv_len, p.k_scale);
-  load_kv_tile<D, FP8>(vs, p, table, g, 1, 0, kv_len, p.v_scale);
-  cp_commit();
+  if (MODE == kKvTma && threadIdx.x == 0) {
+    for (int i = 0; i < kKvStages; ++i) mbar_init(&full_bar[i], 1);
+    abort_word = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  auto issue = [&](int t) {      // cp.async modes always commit a group so that the wait counts stay uniform
+    const int st = t % kKvStages;
+    if (MODE == kKvTma) {
+      if (threadIdx.x == 0 && t < ntiles)
+        tma_issue_kv<D>(ks + st * kTileTok * D, vs + st * kTileTok * D, &full_bar[st], &kv_map, p, table, g,
+                        t * kTileTok, kv_len, rows_per_block);
+      return;
+    }
+    if (t < ntiles) {
+      load_kv_tile<D, FP8>(ks + st * kTileTok * D, p, table, g, 0, t * kTileTok, kv_len, p.k_scale);
+      load_kv_tile<D, FP8>(vs + st * kTileTok * D, p, table, g, 1, t * kTileTok, kv_len, p.v_scale);
+    }
+    cp_commit();
+  };
+  issue(0);
+  issue(1);
   __syncthreads();
 
   uint32_t qf[D / 16][4];
@@ -250,7 +318,7 @@ paged_prefill_kernel(const AttnParams p) {
   for (int kk = 0; kk < D / 16; ++kk) {
     const int r = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
     const int c = kk * 2 + (lane >> 4);
-    ldsm_x4(qf[kk], smem_addr(tile_ptr<D>(qs, r, c)));
+    ldsm_x4(qf[kk], smem_addr(tile_ptr<D, 64>(qs, r, c)));
   }
   int limit[2]; float slope[2];
 #pragma unroll
@@ -264,22 +332,25 @@ paged_prefill_kernel(const AttnParams p) {
   for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+  bool ok = true;
   for (int t = 0; t < ntiles; ++t) {
-    const int buf = t & 1;
-    if (t + 1 < ntiles) {
-      load_kv_tile<D, FP8>(ks + (buf ^ 1) * kTileTok * D, p, table, g, 0, (t + 1) * kTileTok, kv_len, p.k_scale);
-      load_kv_tile<D, FP8>(vs + (buf ^ 1) * kTileTok * D, p, table, g, 1, (t + 1) * kTileTok, kv_len, p.v_scale);
-      cp_commit();
-      cp_wait<1>();
+    const int buf = t % kKvStages;
+    if (MODE == kKvTma) {
+      if (!mbar_wait(&full_bar[buf], (t / kKvStages) & 1, &abort_word)) { ok = false; break; }
+      zero_v_tail<D>(vs + buf * kTileTok * D, kv_len - t * kTileTok);
     } else {
-      cp_wait<0>();
+      cp_wait<1>();               // tile t has landed (only the newest group may still be in flight)
     }
-    __syncthreads();
+    __syncthreads();              // ... for every thread, and everyone is done with tile t-1
+    issue(t + 2);                 // refill the stage tile t-1 used
     float sc[8][4];
     warp_qk<D, 8>(sc, qf, ks + buf * kTileTok * D, 0, lane);
     softmax_update<D, 8>(sc, o, m, l, limit, slope, t * kTileTok, lane, p.scale_log2);
     warp_pv<D, 8>(o, sc, vs + buf * kTileTok * D, 0, lane);
-    __syncthreads();
+  }
+  if (!ok) {                      // a bounded wait gave up: leave the output untouched, report through the error word
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, 4);
+    return;
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -302,14 +373,18 @@ paged_prefill_kernel(const AttnParams p) {
 
 // ------------------------------------------------------------------------------ decode
 // grid (Hkv, B, splits). Rows = the G query heads of kv head g (G <= 16), one new token each.
-template <int D, bool FP8>
+template <int D, int MODE>
 __global__ void __launch_bounds__(kAttnThreads)
-paged_decode_kernel(const AttnParams p) {
-  extern __shared__ __align__(128) uint8_t smem_attn[];
+paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams p, const long long rows_per_block) {
+  constexpr bool FP8 = MODE == kKvFp8;
+  extern __shared__ uint8_t smem_attn_raw[];
+  uint8_t* smem_attn = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_attn_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[kKvStages];
+  __shared__ uint32_t abort_word;
   bf16* qs = reinterpret_cast<bf16*>(smem_attn);            // 16 x D
-  bf16* ks = qs + 16 * D;                                   // 2 x (64 x D)
-  bf16* vs = ks + 2 * kTileTok * D;
-  float* merge = reinterpret_cast<float*>(vs + 2 * kTileTok * D);   // 4 warps x 16 rows x (D + 2)
+  bf16* ks = qs + 16 * D;                                   // kKvStages x (64 x D)
+  bf16* vs = ks + kKvStages * kTileTok * D;
+  float* merge = reinterpret_cast<float*>(ks);              // 4 warps x 16 rows x (D + 2), reuses the K ring after the loop
 
   const int g = blockIdx.x, s = blockIdx.y, split = blockIdx.z;
   const int G = p.Hq / p.Hkv;
@@ -325,20 +400,37 @@ paged_decode_kernel(const AttnParams p) {
     const int r = i / CH, c = i % CH;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < G) v = *reinterpret_cast<const uint4*>(p.q + static_cast<size_t>(s) * p.q_stride + (g * G + r) * D + c * 8);
-    *reinterpret_cast<uint4*>(tile_ptr<D>(qs, r, c)) = v;
+    *reinterpret_cast<uint4*>(tile_ptr<D, 16>(qs, r, c)) = v;
   }
-  if (t_begin < t_end) {
-    load_kv_tile<D, FP8>(ks, p, table, g, 0, t_begin * kTileTok, kv_len, p.k_scale);
-    load_kv_tile<D, FP8>(vs, p, table, g, 1, t_begin * kTileTok, kv_len, p.v_scale);
+  if (MODE == kKvTma && threadIdx.x == 0) {
+    for (int i = 0; i < kKvStages; ++i) mbar_init(&full_bar[i], 1);
+    abort_word = 0;
+    mbar_fence_init();
   }
-  cp_commit();
+  __syncthreads();
+  auto issue = [&](int t) {
+    const int st = (t - t_begin) % kKvStages;
+    if (MODE == kKvTma) {
+      if (threadIdx.x == 0 && t < t_end)
+        tma_issue_kv<D>(ks + st * kTileTok * D, vs + st * kTileTok * D, &full_bar[st], &kv_map, p, table, g,
+                        t * kTileTok, kv_len, rows_per_block);
+      return;
+    }
+    if (t < t_end) {
+      load_kv_tile<D, FP8>(ks + st * kTileTok * D, p, table, g, 0, t * kTileTok, kv_len, p.k_scale);
+      load_kv_tile<D, FP8>(vs + st * kTileTok * D, p, table, g, 1, t * kTileTok, kv_len, p.v_scale);
+    }
+    cp_commit();
+  };
+  issue(t_begin);
+  issue(t_begin + 1);
   __syncthreads();
   uint32_t qf[D / 16][4];
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const int r = (lane & 7) + (((lane >> 3) & 1) << 3);
     const int c = kk * 2 + (lane >> 4);
-    ldsm_x4(qf[kk], smem_addr(tile_ptr<D>(qs, r, c)));
+    ldsm_x4(qf[kk], smem_addr(tile_ptr<D, 16>(qs, r, c)));
   }
   int limit[2]; float slope[2];
 #pragma unroll
@@ -352,22 +444,27 @@ paged_decode_kernel(const AttnParams p) {
   for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+  bool ok = true;
   for (int t = t_begin; t < t_end; ++t) {
-    const int buf = (t - t_begin) & 1;
-    if (t + 1 < t_end) {
-      load_kv_tile<D, FP8>(ks + (buf ^ 1) * kTileTok * D, p, table, g, 0, (t + 1) * kTileTok, kv_len, p.k_scale);
-      load_kv_tile<D, FP8>(vs + (buf ^ 1) * kTileTok * D, p, table, g, 1, (t + 1) * kTileTok, kv_len, p.v_scale);
-      cp_commit();
-      cp_wait<1>();
+    const int buf = (t - t_begin) % kKvStages;
+    if (MODE == kKvTma) {
+      if (!mbar_wait(&full_bar[buf], ((t - t_begin) / kKvStages) & 1, &abort_word)) { ok = false; break; }
+      zero_v_tail<D>(vs + buf * kTileTok * D, kv_len - t * kTileTok);
     } else {
-      cp_wait<0>();
+      cp_wait<1>();
     }
     __syncthreads();
+    issue(t + 2);
     float sc[2][4];
     warp_qk<D, 2>(sc, qf, ks + buf * kTileTok * D, warp * 16, lane);
     softmax_update<D, 2>(sc, o, m, l, limit, slope, t * kTileTok + warp * 16, lane, p.scale_log2);
     warp_pv<D, 2>(o, sc, vs + buf * kTileTok * D, warp * 16, lane);
-    __syncthreads();
+  }
+  cp_wait<0>();
+  __syncthreads();                // the merge area aliases the K ring: every warp must be out of the loop
+  if (!ok) {
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, 4);
+    return;
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -431,32 +528,68 @@ __global__ void decode_reduce_kernel(const AttnParams p) {
   }
 }
 
-template <int D, bool FP8>
-static int launch_prefill(const AttnParams& p, int B, int max_q_len, cudaStream_t st) {
-  const int smem = (64 + 4 * kTileTok) * D * 2;
+// ------------------------------------------------------------------------------------ host
+typedef CUresult (*AttnEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static AttnEncodeFn attn_encode_fn() {
+  static AttnEncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) return nullptr;
+    fn = reinterpret_cast<AttnEncodeFn>(ptr);
+  }
+  return fn;
+}
+
+// The layer's cache seen as rows of D bf16 (row = one token of one head of K or V of one block); box = one
+// cache block's tokens x 64 columns, 128-byte swizzle.
+static bool make_kv_map(CUtensorMap* map, const void* cache, long long rows, int D, int block_tokens) {
+  AttnEncodeFn enc = attn_encode_fn();
+  if (!enc || (reinterpret_cast<uintptr_t>(cache) & 15)) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(D) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(block_tokens)};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool tma_ok(const AttnParams& p, int D) {
+  const int bt = p.block_tokens;
+  return (bt == 8 || bt == 16 || bt == 32 || bt == 64) && p.block_stride % D == 0;
+}
+
+template <int D, int MODE>
+static int launch_prefill(const AttnParams& p, const CUtensorMap& map, long long rows_per_block, int B, int max_q_len,
+                          cudaStream_t st) {
+  const int smem = (64 + 2 * kKvStages * kTileTok) * D * 2 + 1024;
   static bool set = false;
   if (!set) {
-    if (cudaFuncSetAttribute(paged_prefill_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+    if (cudaFuncSetAttribute(paged_prefill_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess) return -3;
     set = true;
   }
   const int G = p.Hq / p.Hkv;
   dim3 grid((max_q_len * G + 63) / 64, p.Hkv, B);
-  paged_prefill_kernel<D, FP8><<<grid, kAttnThreads, smem, st>>>(p);
+  paged_prefill_kernel<D, MODE><<<grid, kAttnThreads, smem, st>>>(map, p, rows_per_block);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-template <int D, bool FP8>
-static int launch_decode(const AttnParams& p, int B, cudaStream_t st) {
-  const int smem = (16 + 4 * kTileTok) * D * 2 + 4 * 16 * (D + 2) * 4;
+template <int D, int MODE>
+static int launch_decode(const AttnParams& p, const CUtensorMap& map, long long rows_per_block, int B, cudaStream_t st) {
+  const int smem = (16 + 2 * kKvStages * kTileTok) * D * 2 + 1024;   // the fp32 merge area fits inside the K ring
   static bool set = false;
   if (!set) {
-    if (cudaFuncSetAttribute(paged_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+    if (cudaFuncSetAttribute(paged_decode_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess) return -3;
     set = true;
   }
   dim3 grid(p.Hkv, B, p.num_splits);
-  paged_decode_kernel<D, FP8><<<grid, kAttnThreads, smem, st>>>(p);
+  paged_decode_kernel<D, MODE><<<grid, kAttnThreads, smem, st>>>(map, p, rows_per_block);
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (p.num_splits > 1) {
     decode_reduce_kernel<D><<<dim3(p.Hq, B), D < 128 ? 64 : 128, 0, st>>>(p);
@@ -465,16 +598,37 @@ static int launch_decode(const AttnParams& p, int B, cudaStream_t st) {
   return 0;
 }
 
+template <int D>
+static int dispatch_prefill(const AttnParams& p, int cache_fp8, long long cache_rows, int B, int max_q_len, cudaStream_t st) {
+  CUtensorMap map{};
+  const long long rpb = p.block_stride / D;
+  if (cache_fp8) return launch_prefill<D, kKvFp8>(p, map, rpb, B, max_q_len, st);
+  if (tma_ok(p, D) && cache_rows > 0 && make_kv_map(&map, p.cache, cache_rows, D, p.block_tokens))
+    return launch_prefill<D, kKvTma>(p, map, rpb, B, max_q_len, st);
+  return launch_prefill<D, kKvCpAsync>(p, map, rpb, B, max_q_len, st);
+}
+
+template <int D>
+static int dispatch_decode(const AttnParams& p, int cache_fp8, long long cache_rows, int B, cudaStream_t st) {
+  CUtensorMap map{};
+  const long long rpb = p.block_stride / D;
+  if (cache_fp8) return launch_decode<D, kKvFp8>(p, map, rpb, B, st);
+  if (tma_ok(p, D) && cache_rows > 0 && make_kv_map(&map, p.cache, cache_rows, D, p.block_tokens))
+    return launch_decode<D, kKvTma>(p, map, rpb, B, st);
+  return launch_decode<D, kKvCpAsync>(p, map, rpb, B, st);
+}
+
 }  // namespace ksana
 
 using namespace ksana;
 
 // Causal attention of new query rows against the paged cache (which already holds their K/V).
+// cache_rows: number of D-wide rows addressable from `cache` (blocks * block_stride / D); 0 disables the TMA path.
 extern "C" int ksana_paged_prefill(const void* q, long long q_stride, void* out, long long out_stride,
                                    const void* cache, long long block_stride, int block_tokens, const int* block_table,
                                    int table_stride, const int* cu_q, const int* kv_lens, const float* alibi, int B,
                                    int max_q_len, int Hq, int Hkv, int D, float scale, int cache_fp8, float k_scale,
-                                   float v_scale, cudaStream_t st) {
+                                   float v_scale, long long cache_rows, int* err, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (Hq % Hkv) return -10;
   AttnParams p{};
@@ -482,9 +636,9 @@ extern "C" int ksana_paged_prefill(const void* q, long long q_stride, void* out,
   p.cache = cache; p.block_stride = block_stride; p.block_tokens = block_tokens;
   p.block_table = block_table; p.table_stride = table_stride; p.cu_q = cu_q; p.kv_lens = kv_lens; p.alibi = alibi;
   p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.44269504f; p.k_scale = k_scale; p.v_scale = v_scale;
-  p.num_splits = 1;
-  if (D == 128) return cache_fp8 ? launch_prefill<128, true>(p, B, max_q_len, st) : launch_prefill<128, false>(p, B, max_q_len, st);
-  if (D == 64) return cache_fp8 ? launch_prefill<64, true>(p, B, max_q_len, st) : launch_prefill<64, false>(p, B, max_q_len, st);
+  p.num_splits = 1; p.err = err;
+  if (D == 128) return dispatch_prefill<128>(p, cache_fp8, cache_rows, B, max_q_len, st);
+  if (D == 64) return dispatch_prefill<64>(p, cache_fp8, cache_rows, B, max_q_len, st);
   return -11;
 }
 
@@ -493,7 +647,7 @@ extern "C" int ksana_paged_decode(const void* q, long long q_stride, void* out, 
                                   const void* cache, long long block_stride, int block_tokens, const int* block_table,
                                   int table_stride, const int* kv_lens, const float* alibi, int B, int Hq, int Hkv,
                                   int D, float scale, int cache_fp8, float k_scale, float v_scale, int num_splits,
-                                  float* part_o, float* part_ml, cudaStream_t st) {
+                                  float* part_o, float* part_ml, long long cache_rows, int* err, cudaStream_t st) {
   if (B <= 0) return 0;
   if (Hq % Hkv || Hq / Hkv > 16) return -10;
   if (num_splits < 1) num_splits = 1;
@@ -503,8 +657,8 @@ extern "C" int ksana_paged_decode(const void* q, long long q_stride, void* out, 
   p.cache = cache; p.block_stride = block_stride; p.block_tokens = block_tokens;
   p.block_table = block_table; p.table_stride = table_stride; p.cu_q = nullptr; p.kv_lens = kv_lens; p.alibi = alibi;
   p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.44269504f; p.k_scale = k_scale; p.v_scale = v_scale;
-  p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml;
-  if (D == 128) return cache_fp8 ? launch_decode<128, true>(p, B, st) : launch_decode<128, false>(p, B, st);
-  if (D == 64) return cache_fp8 ? launch_decode<64, true>(p, B, st) : launch_decode<64, false>(p, B, st);
+  p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml; p.err = err;
+  if (D == 128) return dispatch_decode<128>(p, cache_fp8, cache_rows, B, st);
+  if (D == 64) return dispatch_decode<64>(p, cache_fp8, cache_rows, B, st);
   return -11;
 }

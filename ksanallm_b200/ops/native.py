@@ -20,6 +20,7 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 
 _SIGS = {
     "ksana_gemm_bf16": [vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+    "ksana_gemm_pair": [i32, vp, i32, vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_gemm_fp8_block": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_smallm": [i32, vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i64, vp, i32,
                           vp, vp],
@@ -49,9 +50,9 @@ _SIGS = {
     "ksana_add": [vp, vp, vp, vp, i64, i32, vp],
     "ksana_cast_f32": [vp, vp, i64, vp],
     "ksana_paged_prefill": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32,
-                            f32, f32, vp],
+                            f32, f32, i64, vp, vp],
     "ksana_paged_decode": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, f32, f32,
-                           i32, vp, vp, vp],
+                           i32, vp, vp, i64, vp, vp],
     "ksana_sample": [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, vp],
     "ksana_repetition_penalty": [vp, i64, vp, vp, vp, vp, i32, i32, vp],
     "ksana_ban_tokens": [vp, i64, vp, vp, vp, i32, i32, vp],
@@ -119,7 +120,7 @@ def check_err_flag(device) -> None:
 
 
 # ------------------------------------------------------------------------------------- GEMM
-SMALL_M_FP8 = 16                   # FP8: per-token scale promotion makes the skinny kernel pay off up to 16 rows
+SMALL_M_FP8 = 32                   # FP8: per-k-block promotion costs grow with the row count (measured crossover)
 SMALL_M_BF16 = 128                 # bf16: no per-K-block promotion, the skinny kernel wins up to a full token tile
 _SCRATCH_BYTES = 64 << 20
 _COUNTERS = 4096
@@ -150,6 +151,26 @@ def _gemm_smallm(kind, x, xs, w, ws, out, out_f32, bias, residual, M, N, K, spli
     return dst
 
 
+PAIR_MIN_M = 1024                  # CTA-pair (cta_group::2) kernel from this many rows; 0 disables it
+
+
+def gemm_pair(kind, x, xs, w, ws, out, bias=None, residual=None, push=None, push_n=0, push_rows=0):
+    """CTA-pair tcgen05 GEMM (256 x 256 tiles over two SMs). kind 0: bf16, 1: block-scaled FP8. bf16 output only."""
+    M, K = x.shape
+    N = w.shape[0]
+    rc = lib().ksana_gemm_pair(kind, _p(x), x.stride(0), _p(xs), xs.stride(0) if xs is not None else 0, _p(w),
+                               w.stride(0), _p(ws), _p(out), out.stride(0) if out is not None else N, _p(bias),
+                               _p(residual), residual.stride(0) if residual is not None else 0, M, N, K, push, push_n,
+                               push_rows, _p(err_flag(x.device)), _st())
+    _check(rc, "ksana_gemm_pair")
+    return out
+
+
+def _pair_ok(M, N, K, kind, bn, out_f32, max_ctas):
+    return (PAIR_MIN_M > 0 and M >= PAIR_MIN_M and bn == 0 and max_ctas == 0 and out_f32 is None and N % 8 == 0
+            and N >= 256 and K % (128 if kind else 8) == 0)
+
+
 def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0, splits=0):
     """out[M,N] = x[M,K] @ w[N,K]^T (+bias)(+residual). bf16 in, bf16 (or fp32) out."""
     M, K = x.shape
@@ -160,6 +181,8 @@ def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_
     dst = out if out_f32 is None else out_f32
     if (M <= SMALL_M_BF16 or splits < 0) and M <= 128 and bn == 0 and K % 8 == 0:
         return _gemm_smallm(0, x, None, w, None, out, out_f32, bias, residual, M, N, K, splits)
+    if _pair_ok(M, N, K, 0, bn, out_f32, max_ctas):
+        return gemm_pair(0, x, None, w, None, out, bias, residual)
     rc = lib().ksana_gemm_bf16(_p(x), x.stride(0), _p(w), w.stride(0), _p(out) if out_f32 is None else None,
                                _p(out_f32), dst.stride(0), _p(bias), _p(residual),
                                residual.stride(0) if residual is not None else 0, M, N, K, bn, max_ctas,
@@ -175,10 +198,13 @@ def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, b
     if out is None and out_f32 is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
     dst = out if out_f32 is None else out_f32
-    if (M <= SMALL_M_FP8 or splits < 0) and M <= 128 and bn == 0:
+    skinny = M <= SMALL_M_FP8 or (M <= 64 and K >= 16384 and N <= 16384)
+    if (skinny or splits < 0) and M <= 128 and bn == 0:
         return _gemm_smallm(1, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)
+    if _pair_ok(M, N, K, 1, bn, out_f32, max_ctas):
+        return gemm_pair(1, xq, xs, wq, ws, out, bias, residual)
     if bn == 0 and M <= 128:
-        bn = 128 if N >= 16384 else 64     # decode-sized rows on the tiled kernel: measured best tile widths
+        bn = 128 if N >= 10240 else 64     # decode-sized rows on the tiled kernel: measured best tile widths
     rc = lib().ksana_gemm_fp8_block(_p(xq), xq.stride(0), _p(xs), xs.stride(0), _p(wq), wq.stride(0), _p(ws),
                                     _p(out) if out_f32 is None else None, _p(out_f32), dst.stride(0), _p(bias),
                                     _p(residual), residual.stride(0) if residual is not None else 0, M, N, K, bn,
@@ -290,13 +316,18 @@ def rope_kv_append(qkv, positions, slots, cos_sin, cache_layer, block_stride, bl
     _check(rc, "ksana_rope_kv_append")
 
 
+def _cache_rows(cache_layer, block_stride, D):
+    """Rows of D elements addressable from the layer's base pointer (bounds of the TMA tensor map)."""
+    return int(cache_layer.shape[0]) * int(block_stride) // int(D)
+
+
 def paged_prefill(q, q_stride, out, cache_layer, block_stride, block_tokens, block_table, cu_q, kv_lens, B, max_q_len,
                   Hq, Hkv, D, scale, alibi=None, k_scale=1.0, v_scale=1.0):
     fp8 = cache_layer.dtype != torch.bfloat16
     rc = lib().ksana_paged_prefill(_p(q), q_stride, _p(out), out.stride(0), _p(cache_layer), block_stride,
                                    block_tokens, _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_lens),
                                    _p(alibi), B, max_q_len, Hq, Hkv, D, float(scale), int(fp8), float(k_scale),
-                                   float(v_scale), _st())
+                                   float(v_scale), _cache_rows(cache_layer, block_stride, D), _p(err_flag(q.device)), _st())
     _check(rc, "ksana_paged_prefill")
 
 
@@ -306,7 +337,7 @@ def paged_decode(q, q_stride, out, cache_layer, block_stride, block_tokens, bloc
     rc = lib().ksana_paged_decode(_p(q), q_stride, _p(out), out.stride(0), _p(cache_layer), block_stride, block_tokens,
                                   _p(block_table), block_table.stride(0), _p(kv_lens), _p(alibi), B, Hq, Hkv, D,
                                   float(scale), int(fp8), float(k_scale), float(v_scale), num_splits, _p(part_o),
-                                  _p(part_ml), _st())
+                                  _p(part_ml), _cache_rows(cache_layer, block_stride, D), _p(err_flag(q.device)), _st())
     _check(rc, "ksana_paged_decode")
 
 

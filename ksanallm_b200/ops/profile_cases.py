@@ -105,7 +105,26 @@ def case_sampler():
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 
+def time_cases(names):
+    """CUDA-event timing (after warm-up); every case launches its kernel twice per call."""
+    for n in names:
+        fn = CASES[n]
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # inputs are re-created inside each case; time only the second half by differencing two call counts
+        reps = 3
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"{n}: {e0.elapsed_time(e1) / reps:.3f} ms per case call (input creation included)")
+
+
 def main(argv):
+    if argv and argv[0] == "--time":
+        return time_cases(argv[1:] or list(CASES))
     names = argv or list(CASES)
     for n in names:
         CASES[n]()
