@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
+#include "fp8_scale.cuh"
 
 namespace ksana {
 
@@ -244,7 +245,7 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
         for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(o[e]));
 #pragma unroll
         for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
-        const float scale = fmaxf(am, 1e-10f) / 448.f;
+        const float scale = fp8_group_scale(am);
         if (on) {
           const uint2 q = pack8_e4m3c(o, 1.f / scale);
           reinterpret_cast<uint2*>(p.yq + static_cast<size_t>(row) * p.H)[i] = q;

@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
+#include "fp8_scale.cuh"
 
 namespace ksana {
 
@@ -72,7 +73,6 @@ __device__ __forceinline__ float group16_max(float v) {
   for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
-constexpr float kE4m3Max = 448.f;
 
 // ----------------------------------------------------------------------------
 // (residual +=) x ; y = norm(residual or x) * w (+ beta) ; optional fp8 copy of y.
@@ -154,7 +154,7 @@ __global__ void norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ resid
 #pragma unroll
       for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(o[e]));
       am = group16_max(am);
-      const float scale = fmaxf(am, 1e-10f) / kE4m3Max;
+      const float scale = fp8_group_scale(am);
       if (on) {
         reinterpret_cast<uint2*>(yq + static_cast<size_t>(row) * H)[i] = pack8_e4m3(o, 1.f / scale);
         if ((i & 15) == 0) yscale[static_cast<size_t>(i >> 4) * scale_ld + row] = scale;
@@ -206,7 +206,7 @@ __global__ void act_mul_kernel(const bf16* __restrict__ in, bf16* __restrict__ o
 #pragma unroll
       for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(o[e]));
       am = group16_max(am);
-      const float scale = fmaxf(am, 1e-10f) / kE4m3Max;
+      const float scale = fp8_group_scale(am);
       if (on) {
         reinterpret_cast<uint2*>(outq + static_cast<size_t>(m) * I)[i] = pack8_e4m3(o, 1.f / scale);
         if ((i & 15) == 0) oscale[static_cast<size_t>(i >> 4) * scale_ld + m] = scale;
@@ -232,7 +232,7 @@ __global__ void quant_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restrict
 #pragma unroll
     for (int e = 0; e < 8; ++e) am = fmaxf(am, fabsf(f[e]));
     am = group16_max(am);
-    const float sc = fmaxf(am, 1e-10f) / kE4m3Max;
+    const float sc = fp8_group_scale(am);
     if (on) {
       reinterpret_cast<uint2*>(q + static_cast<size_t>(m) * K)[i] = pack8_e4m3(f, 1.f / sc);
       if ((i & 15) == 0) scale[static_cast<size_t>(i >> 4) * scale_ld + m] = sc;

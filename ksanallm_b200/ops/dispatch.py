@@ -30,6 +30,8 @@ class LinearWeight:
     def __init__(self, w: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
                  wq: Optional[torch.Tensor] = None, ws: Optional[torch.Tensor] = None):
         self.w, self.bias, self.wq, self.ws = w, bias, wq, ws
+        # power-of-two block scales: the tensor cores can apply them (hardware block-scaled MMA)
+        self.ue8m0 = ws is not None and ref.is_pow2(ws)
 
     @property
     def fp8(self) -> bool:
@@ -51,6 +53,7 @@ class LinearWeight:
         if not self.fp8:
             self.wq, self.ws = ref.quant_weight_fp8_block(self.w)
             self.w = None
+            self.ue8m0 = True
         return self
 
     def dense(self) -> torch.Tensor:
@@ -79,8 +82,8 @@ def linear(x, W: LinearWeight, residual=None, out=None, out_f32: bool = False):
                 x = quantize(x)
             if out_f32:
                 o = torch.empty(x.q.shape[0], W.out_features, dtype=torch.float32, device=x.q.device)
-                return native.gemm_fp8(x.q, x.s, W.wq, W.ws, bias=W.bias, residual=residual, out_f32=o)
-            return native.gemm_fp8(x.q, x.s, W.wq, W.ws, out=out, bias=W.bias, residual=residual)
+                return native.gemm_fp8(x.q, x.s, W.wq, W.ws, bias=W.bias, residual=residual, out_f32=o, hw_scale=W.ue8m0)
+            return native.gemm_fp8(x.q, x.s, W.wq, W.ws, out=out, bias=W.bias, residual=residual, hw_scale=W.ue8m0)
         if out_f32:
             o = torch.empty(x.shape[0], W.out_features, dtype=torch.float32, device=x.device)
             return native.gemm_bf16(x, W.w, bias=W.bias, residual=residual, out_f32=o)

@@ -21,6 +21,8 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 _SIGS = {
     "ksana_gemm_bf16": [vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_pair": [i32, vp, i32, vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
+    "ksana_gemm_mxfp8": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, vp,
+                         vp],
     "ksana_gemm_fp8_block": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_smallm": [i32, vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i64, vp, i32,
                           vp, vp],
@@ -151,7 +153,7 @@ def _gemm_smallm(kind, x, xs, w, ws, out, out_f32, bias, residual, M, N, K, spli
     return dst
 
 
-PAIR_MIN_M = 1024                  # CTA-pair (cta_group::2) kernel from this many rows; 0 disables it
+PAIR_MIN_M = 0                     # CTA-pair (cta_group::2) kernel from this many rows; 0 disables it
 
 
 def gemm_pair(kind, x, xs, w, ws, out, bias=None, residual=None, push=None, push_n=0, push_rows=0):
@@ -191,18 +193,38 @@ def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_
     return dst
 
 
-def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0, splits=0):
-    """Block-scaled FP8 GEMM. xq [M,K] e4m3, xs [K/128, ld] fp32; wq [N,K] e4m3, ws [ceil(N/128), K/128] fp32."""
+MX_MIN_M = 33                      # hardware-scaled kernel from this many rows (below: the skinny stream-K kernel)
+
+
+def gemm_mxfp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0, push=None,
+               push_n=0, push_rows=0, ldd=None):
+    """FP8 GEMM whose power-of-two scales are applied by the tensor cores (tcgen05 block_scale MMA)."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    dst = out if out_f32 is None else out_f32
+    rc = lib().ksana_gemm_mxfp8(_p(xq), xq.stride(0), _p(xs), xs.stride(0), _p(wq), wq.stride(0), _p(ws),
+                                _p(out) if out_f32 is None else None, _p(out_f32),
+                                dst.stride(0) if dst is not None else ldd, _p(bias), _p(residual),
+                                residual.stride(0) if residual is not None else 0, M, N, K, bn, max_ctas, push, push_n,
+                                push_rows, _p(err_flag(xq.device)), _st())
+    _check(rc, "ksana_gemm_mxfp8")
+    return dst
+
+
+def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0, splits=0,
+             hw_scale=False):
+    """Block-scaled FP8 GEMM. xq [M,K] e4m3, xs [K/128, ld] fp32; wq [N,K] e4m3, ws [ceil(N/128), K/128] fp32.
+    hw_scale: every scale is a power of two, so the tensor cores may apply them (large-M path)."""
     M, K = xq.shape
     N = wq.shape[0]
     if out is None and out_f32 is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
     dst = out if out_f32 is None else out_f32
+    if hw_scale and M >= MX_MIN_M and splits == 0 and (bn == 0 or bn >= 128):
+        return gemm_mxfp8(xq, xs, wq, ws, out, bias, residual, out_f32, bn, max_ctas)
     skinny = M <= SMALL_M_FP8 or (M <= 64 and K >= 16384 and N <= 16384)
     if (skinny or splits < 0) and M <= 128 and bn == 0:
         return _gemm_smallm(1, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)
-    if _pair_ok(M, N, K, 1, bn, out_f32, max_ctas):
-        return gemm_pair(1, xq, xs, wq, ws, out, bias, residual)
     if bn == 0 and M <= 128:
         bn = 128 if N >= 10240 else 64     # decode-sized rows on the tiled kernel: measured best tile widths
     rc = lib().ksana_gemm_fp8_block(_p(xq), xq.stride(0), _p(xs), xs.stride(0), _p(wq), wq.stride(0), _p(ws),

@@ -22,25 +22,40 @@ def gemm(x, w, bias=None, residual=None, out_dtype=None):
     return y.to(out_dtype or x.dtype)
 
 
+def pow2_scale(amax):
+    """Smallest power of two >= amax / 448 (UE8M0 scale), computed on the fp32 bit pattern like the kernels do."""
+    s = amax.float().clamp_min(1e-10) * (1.0 / E4M3_MAX)
+    bits = s.contiguous().view(torch.int32)
+    e = (bits >> 23) + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    return (e << 23).view(torch.float32)
+
+
+def is_pow2(scale) -> bool:
+    """True when every (positive, normal) fp32 scale is an exact power of two."""
+    bits = scale.float().contiguous().view(torch.int32)
+    return bool(((bits & 0x7FFFFF) == 0).all() and (bits > 0).all())
+
+
 def quant_fp8(x):
-    """Per (row, 128 columns) e4m3 quantisation; scales returned as [K/128, M] (k-group major)."""
+    """Per (row, 128 columns) e4m3 quantisation with power-of-two scales; scales returned as [K/128, M]
+    (k-group major)."""
     M, K = x.shape
     g = x.float().reshape(M, K // 128, 128)
-    amax = g.abs().amax(dim=-1).clamp_min(1e-10)
-    scale = amax / E4M3_MAX
+    scale = pow2_scale(g.abs().amax(dim=-1))
     q = (g / scale.unsqueeze(-1)).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).reshape(M, K)
     return q, scale.t().contiguous()
 
 
-def quant_weight_fp8_block(w, block=128):
-    """[N,K] weight -> e4m3 + one fp32 scale per (128 x 128) block, scales [ceil(N/128), ceil(K/128)]."""
+def quant_weight_fp8_block(w, block=128, pow2=True):
+    """[N,K] weight -> e4m3 + one fp32 scale per (128 x 128) block, scales [ceil(N/128), ceil(K/128)].
+    pow2: power-of-two scales (what the tensor cores can apply themselves); False: amax / 448 exactly."""
     N, K = w.shape
     nb, kb = (N + block - 1) // block, (K + block - 1) // block
     wp = torch.zeros(nb * block, kb * block, dtype=torch.float32, device=w.device)
     wp[:N, :K] = w.float()
     blocks = wp.reshape(nb, block, kb, block)
     amax = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-10)
-    scale = amax / E4M3_MAX
+    scale = pow2_scale(amax) if pow2 else amax / E4M3_MAX
     q = (blocks / scale[:, None, :, None]).clamp(-E4M3_MAX, E4M3_MAX).reshape(nb * block, kb * block)[:N, :K]
     return q.to(torch.float8_e4m3fn).contiguous(), scale.contiguous()
 

@@ -158,7 +158,11 @@ class SymmetricComm:
                                                 self.size, err, st)
             native._check(rc, "ksana_gemm_smallm_push")
         else:
-            if W.fp8:
+            if W.fp8 and W.ue8m0 and M >= native.MX_MIN_M:
+                native.gemm_mxfp8(x.q, x.s, W.wq, W.ws, bias=W.bias if self.rank == 0 else None, push=push,
+                                  push_n=self.size, push_rows=rows_per, ldd=H)
+                rc = 0
+            elif W.fp8:
                 rc = lib.ksana_gemm_fp8_block_push(x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0),
                                                    W.wq.data_ptr(), W.wq.stride(0), W.ws.data_ptr(), H, bias, M, H,
                                                    W.in_features, 0, push, self.size, rows_per, err, st)

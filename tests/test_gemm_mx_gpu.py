@@ -1,0 +1,66 @@
+"""Hardware block-scaled FP8 GEMM (tcgen05 block_scale MMA, power-of-two scales) against the fp32 statement."""
+import pytest
+import torch
+
+from ksanallm_b200.ops import native, reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+def _operands(M, N, K, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    # rows, weight blocks and K groups of very different magnitude: a scale applied to the wrong row, block
+    # or K group shows up as a gross error
+    x = torch.randn(M, K, generator=g) * torch.exp2(torch.randint(-6, 7, (M, 1), generator=g).float())
+    x = x * torch.exp2(torch.randint(-3, 4, (1, K // 128), generator=g).float()).repeat_interleave(128, 1)
+    w = torch.randn(N, K, generator=g) * 0.05
+    nb, kb = (N + 127) // 128, K // 128
+    blk = torch.exp2(torch.randint(-5, 6, (nb, kb), generator=g).float())
+    w = w * blk.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)
+    return x.to(DEV, torch.bfloat16), w.to(DEV)
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(128, 256, 128, 256), (128, 128, 512, 128), (300, 1000, 640, 256),
+                                      (300, 1000, 640, 128), (77, 264, 1024, 0), (1000, 7168, 3584, 0),
+                                      (4096, 10240, 8192, 256), (2500, 57344, 1024, 0), (64, 8192, 8192, 0)])
+def test_gemm_mxfp8(M, N, K, bn):
+    x, w = _operands(M, N, K, seed=M + N + K)
+    wq, ws = ref.quant_weight_fp8_block(w)
+    assert ref.is_pow2(ws)
+    xq, xs = native.quant_fp8(x)
+    assert ref.is_pow2(xs[:, :M])
+    xq_r, xs_r = ref.quant_fp8(x)
+    assert torch.equal(xs[:, :M], xs_r) and torch.equal(xq.float(), xq_r.float())
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        y = native.gemm_mxfp8(xq, xs, wq, ws, torch.empty(M, N, device=DEV, dtype=torch.bfloat16), bias, res, bn=bn)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    want = ref.gemm_fp8(xq, xs, wq, ws, bias, res, out_dtype=torch.float32)
+    assert rel_err(y, want) < 1e-2, rel_err(y, want)
+    yf = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    native.gemm_mxfp8(xq, xs, wq, ws, None, out_f32=yf, bn=bn)
+    assert rel_err(yf, ref.gemm_fp8(xq, xs, wq, ws, out_dtype=torch.float32)) < 2e-3
+
+
+def test_gemm_fp8_exact_scales_still_served():
+    """Weights whose scales are not powers of two (a checkpoint's own) stay on the exact-fp32-scale kernel."""
+    from ksanallm_b200.ops.dispatch import LinearWeight, linear
+    x, w = _operands(300, 1024, 1024, seed=3)
+    wq, ws = ref.quant_weight_fp8_block(w, pow2=False)
+    W = LinearWeight(wq=wq, ws=ws)
+    assert not W.ue8m0
+    y = linear(x, W)
+    xq, xs = native.quant_fp8(x)
+    assert rel_err(y, ref.gemm_fp8(xq, xs, wq, ws, out_dtype=torch.float32)) < 1e-2
+    W2 = LinearWeight(w=w.to(torch.bfloat16)).quantize_fp8_block()
+    assert W2.ue8m0
+    y2 = linear(x, W2)
+    assert rel_err(y2, ref.gemm_fp8(xq, xs, W2.wq, W2.ws, out_dtype=torch.float32)) < 1e-2
