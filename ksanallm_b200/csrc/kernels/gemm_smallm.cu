@@ -16,6 +16,9 @@
 //   * FP8 (e4m3 x e4m3, 1x128 activation scales, 128x128 weight scales): each
 //     128-deep K block lands in a fresh TMEM accumulator and is promoted into
 //     fp32 registers with its per-token scale.
+//   * FP8 with power-of-two scales (kind 2): the tensor cores apply the scales themselves (block-scaled MMA,
+//     scale chunks packed by one extra warp and copied into TMEM, see gemm_tcgen05_mx.cu), so a whole K
+//     segment accumulates in TMEM and the epilogue runs once per segment, as for bf16.
 // Same warp roles and bounded waits as gemm_tcgen05.cu. No cluster multicast.
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
@@ -23,7 +26,9 @@
 
 namespace ksana {
 
-constexpr int kSmThreads = 192;
+constexpr int kSmThreads = 192;        // + one scale-packer warp (warp 6) for kind 2
+constexpr int kSmSfStages = 4;        // scale-chunk buffers
+constexpr int kSmSfBatch = 1;
 constexpr int kSmRowBytes = 128;
 constexpr int kSmSmemBudget = 200 * 1024;
 
@@ -43,16 +48,21 @@ struct SmallMParams {
   int push_n;
 };
 
-template <int MP, int KIND>   // MP: padded token count (16..128); KIND 0 bf16, 1 fp8 block-scaled
+constexpr int pow2_at_least(int x) { int p = 32; while (p < x) p *= 2; return p; }
+
+template <int MP, int KIND>   // MP: padded token count (16..128); KIND 0 bf16, 1 fp8 fp32 scales, 2 fp8 UE8M0 scales
 struct SmallMCfg {
+  static constexpr int kThreads = KIND == 2 ? kSmThreads + 32 : kSmThreads;
+  static constexpr int kSfBytes = KIND == 2 ? kSmSfStages * 1024 : 0;     // per stage: weight chunk + token chunk
   static constexpr int kWBytes = 128 * kSmRowBytes;
   static constexpr int kXBytes = MP * kSmRowBytes;
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kStagesRaw = kSmSmemBudget / kStageBytes;
+  static constexpr int kStagesRaw = (kSmSmemBudget - kSfBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
-  static constexpr int kAccStages = KIND == 0 ? 2 : ((512 / MP) > 4 ? 4 : (512 / MP));
-  static constexpr int kTmemCols = (kAccStages * MP) < 32 ? 32 : (kAccStages * MP);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+  static constexpr int kAccStages = KIND != 1 ? 2 : ((512 / MP) > 4 ? 4 : (512 / MP));
+  static constexpr int kSfBase = kAccStages * MP;                         // kind 2: two sets of 8 scale columns
+  static constexpr int kTmemCols = pow2_at_least(kAccStages * MP + (KIND == 2 ? 16 : 0));
+  static constexpr int kSmemBytes = kStages * kStageBytes + kSfBytes + 1024 + 512;
   static constexpr int kElems = KIND == 0 ? 64 : 128;
 };
 
@@ -82,18 +92,21 @@ __device__ __forceinline__ int owner_of(long long x, long long U, long long P) {
 }
 
 template <int MP, int KIND>
-__global__ void __launch_bounds__(kSmThreads, 1)
+__global__ void __launch_bounds__(SmallMCfg<MP, KIND>::kThreads, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
                    const SmallMParams p) {
   using Cfg = SmallMCfg<MP, KIND>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint8_t* sf_smem = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + Cfg::kSfBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Cfg::kStages;
   uint64_t* tfull_bar = bars + 2 * Cfg::kStages;
   uint64_t* tempty_bar = tfull_bar + Cfg::kAccStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + Cfg::kAccStages);
+  uint64_t* sf_full = tempty_bar + Cfg::kAccStages;
+  uint64_t* sf_empty = sf_full + kSmSfStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + kSmSfStages);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint32_t* last_flag = tmem_slot + 2;
 
@@ -106,6 +119,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128); }
+    for (int i = 0; i < kSmSfStages; ++i) { mbar_init(&sf_full[i], 1); mbar_init(&sf_empty[i], 1); }
     *abort_flag = 0;
     *last_flag = 0;
     mbar_fence_init();
@@ -139,10 +153,45 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       long long u = u_begin; Segment sg; bool ok = true;
+      int sfs = 0; uint32_t sf_phase = 0, set = 0;
       while (ok && next_segment(u, u_end, num_kb, sg)) {
-        if (KIND == 0) {
+        if (KIND != 1) {
           if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
+        }
+        if constexpr (KIND == 2) {
+          // groups of up to four K blocks share one pair of scale chunks (byte j of a chunk = block kb0 + 4g + j)
+          const uint32_t d_tmem = tmem_base + acc * MP;
+          for (int g0 = sg.kb0; g0 < sg.kb1 && ok; g0 += 4) {
+            if (!mbar_wait(&sf_full[sfs], sf_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tsfa = tmem_base + Cfg::kSfBase + set * 8;
+            const uint32_t tsfb = tsfa + 4;
+            const uint32_t sf_addr = smem_u32(sf_smem + sfs * 1024);
+            tmem_cp_sf(tsfa, make_sf_desc(sf_addr));
+            tmem_cp_sf(tsfb, make_sf_desc(sf_addr + 512));
+            for (int j = 0; j < 4 && g0 + j < sg.kb1; ++j) {
+              if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t sw = smem_u32(smem + stage * Cfg::kStageBytes);
+              const uint64_t wdesc = make_smem_desc_sw128(sw);
+              const uint64_t xdesc = make_smem_desc_sw128(sw + Cfg::kWBytes);
+              const uint32_t idesc = make_idesc_mx(128, MP, static_cast<uint32_t>(j));
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                mma_mxf8(d_tmem, wdesc + 2 * k, xdesc + 2 * k, idesc, (g0 + j != sg.kb0) || k != 0, tsfa, tsfb);
+              tc_commit(&empty_bar[stage]);
+              if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+            }
+            tc_commit(&sf_empty[sfs]);
+            if (++sfs == kSmSfStages) { sfs = 0; sf_phase ^= 1; }
+            set ^= 1;
+          }
+          if (ok) {
+            tc_commit(&tfull_bar[acc]);
+            if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+          }
+          continue;
         }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (KIND == 1) {
@@ -174,6 +223,65 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       }
     }
     __syncwarp();
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ scale packer (kind 2 only)
+    if constexpr (KIND == 2) {
+      // One group = up to four K blocks of one segment. The scales of the next group are fetched while the
+      // current one waits for its buffer, so the L2 latency of the loads stays off the packer's critical path.
+      struct GroupIter { long long u; Segment sg; int g0; bool valid; };
+      auto next_group = [&](GroupIter& it) {
+        if (it.valid && it.g0 + 4 < it.sg.kb1) { it.g0 += 4; return true; }
+        it.valid = next_segment(it.u, u_end, num_kb, it.sg);
+        it.g0 = it.sg.kb0;
+        return it.valid;
+      };
+      auto load_group = [&](const GroupIter& it, uint32_t (&w)[5]) {   // w[0]: weight chunk word, w[1..4]: token words
+        const float* ws = p.w_scale + static_cast<size_t>(it.sg.tile) * num_kb;
+        w[0] = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[0] |= (it.g0 + j < it.sg.kb1 ? ue8m0_of(ws[it.g0 + j]) : 127u) << (8 * j);
+#pragma unroll
+        for (int r4 = 0; r4 < 4; ++r4) {
+          const int tok = r4 * 32 + lane;
+          uint32_t word = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t e = 127u;
+            if (tok < p.M && it.g0 + j < it.sg.kb1)
+              e = ue8m0_of(p.a_scale[static_cast<size_t>(it.g0 + j) * p.a_scale_ld + tok]);
+            word |= e << (8 * j);
+          }
+          w[1 + r4] = word;
+        }
+      };
+      // Four groups per round (half of the buffers): their loads are all in flight together, so the packer exposes
+      // one L2 round trip per four groups, and the MMA issuer works through the other half meanwhile.
+      int sfs = 0; uint32_t sf_phase = 0;
+      GroupIter it{u_begin, Segment{0, 0, 0}, 0, false};
+      bool more = true, ok = true;
+      while (more && ok) {
+        uint32_t w[kSmSfBatch][5];
+        bool have[kSmSfBatch];
+#pragma unroll
+        for (int i = 0; i < kSmSfBatch; ++i) {
+          have[i] = more && next_group(it);
+          more = have[i];
+          if (have[i]) load_group(it, w[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < kSmSfBatch; ++i) {
+          if (!have[i] || !ok) continue;
+          if (!mbar_wait(&sf_empty[sfs], sf_phase ^ 1, abort_flag)) { ok = false; continue; }
+          uint8_t* buf = sf_smem + sfs * 1024;
+          *reinterpret_cast<uint4*>(buf + lane * 16) = make_uint4(w[i][0], w[i][0], w[i][0], w[i][0]);
+          *reinterpret_cast<uint4*>(buf + 512 + lane * 16) = make_uint4(w[i][1], w[i][2], w[i][3], w[i][4]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sf_full[sfs]);
+          if (++sfs == kSmSfStages) { sfs = 0; sf_phase ^= 1; }
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------ epilogue warps
     const int q = warp & 3;
@@ -187,7 +295,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       float accv[MP];
 #pragma unroll
       for (int i = 0; i < MP; ++i) accv[i] = 0.f;
-      if (KIND == 0) {
+      if (KIND != 1) {
         if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if constexpr (MP >= 32) {
@@ -265,16 +373,27 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       auto finish = [&](const float (&v)[MP]) {
         if (n >= p.N) return;
         const float b = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+        // eight tokens at a time: the residual loads of a batch are issued together before its stores (the output
+        // may alias the residual, so the compiler cannot move a load above an earlier store by itself)
 #pragma unroll
-        for (int m = 0; m < MP; ++m) {
-          if (m < p.M) {
-            float o = v[m] + b;
-            if (p.residual) o += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n]);
+        for (int m0 = 0; m0 < MP; m0 += 8) {
+          if (m0 >= p.M) break;
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = m0 + i;
+            o[i] = v[m] + b;
+            if (p.residual && m < p.M) o[i] += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n]);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = m0 + i;
+            if (m >= p.M) continue;
             if (p.push_n) {
-              const __nv_bfloat16 ob = __float2bfloat16(o);
+              const __nv_bfloat16 ob = __float2bfloat16(o[i]);
               for (int r = 0; r < p.push_n; ++r) p.push[r][static_cast<size_t>(m) * p.ldd + n] = ob;
-            } else if (p.out_f32) p.out_f32[static_cast<size_t>(m) * p.ldd + n] = o;
-            else p.D[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16(o);
+            } else if (p.out_f32) p.out_f32[static_cast<size_t>(m) * p.ldd + n] = o[i];
+            else p.D[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16(o[i]);
           }
         }
       };
@@ -289,7 +408,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         float* tile_scratch = p.scratch + static_cast<size_t>(sg.tile) * p.seg_cap * MP * 128;
         float* mine = tile_scratch + static_cast<size_t>(my) * MP * 128;
 #pragma unroll
-        for (int m = 0; m < MP; ++m) mine[m * 128 + nrow] = accv[m];
+        for (int m4 = 0; m4 < MP / 4; ++m4)       // [MP/4][128 features][4 tokens]: 16-byte stores, coalesced over lanes
+          reinterpret_cast<float4*>(mine)[m4 * 128 + nrow] =
+              make_float4(accv[4 * m4], accv[4 * m4 + 1], accv[4 * m4 + 2], accv[4 * m4 + 3]);
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
@@ -306,9 +427,13 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 #pragma unroll
           for (int m = 0; m < MP; ++m) sum[m] = 0.f;
           for (int sgi = 0; sgi < nseg; ++sgi) {       // fixed order: deterministic sums
-            const volatile float* src = tile_scratch + static_cast<size_t>(sgi) * MP * 128;
+            // written by other SMs: read through L2 (ld.global.cg), never through this SM's L1
+            const float4* src = reinterpret_cast<const float4*>(tile_scratch + static_cast<size_t>(sgi) * MP * 128);
 #pragma unroll
-            for (int m = 0; m < MP; ++m) sum[m] += src[m * 128 + nrow];
+            for (int m4 = 0; m4 < MP / 4; ++m4) {
+              const float4 v = __ldcg(src + m4 * 128 + nrow);
+              sum[4 * m4] += v.x; sum[4 * m4 + 1] += v.y; sum[4 * m4 + 2] += v.z; sum[4 * m4 + 3] += v.w;
+            }
           }
           finish(sum);
         }
@@ -365,7 +490,7 @@ static int launch_smallm(const CUtensorMap& mw, const CUtensorMap& mx, const Sma
                              Cfg::kSmemBytes) != cudaSuccess) return -3;
     set = true;
   }
-  gemm_smallm_kernel<MP, KIND><<<ctas, kSmThreads, Cfg::kSmemBytes, st>>>(mw, mx, p);
+  gemm_smallm_kernel<MP, KIND><<<ctas, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mw, mx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -375,7 +500,8 @@ using namespace ksana;
 
 // Scratch needed: n_tiles * seg_cap * MP * 128 * 4 bytes (seg_cap = pieces a tile can be cut into);
 // counters: n_tiles words, zero before the first launch (the kernel leaves them zero).
-// kind 0: X, W bf16. kind 1: e4m3 with scales. ctas_hint > 0 fixes the number of persistent CTAs
+// kind 0: X, W bf16. kind 1: e4m3 with fp32 scales. kind 2: e4m3 with power-of-two scales, applied by the tensor
+// cores. ctas_hint > 0 fixes the number of persistent CTAs
 // (1 = no K splitting at all when there is a single tile per CTA...). Returns 0 on success; -20 when M > 128.
 static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld, const void* W,
                        int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
@@ -429,7 +555,8 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
   p.push_n = push_n;
   const int ctas = static_cast<int>(P);
 #define KSANA_SM_DISPATCH(MPV)                                                                        \
-  case MPV: return kind == 0 ? launch_smallm<MPV, 0>(mw, mx, p, ctas, st) : launch_smallm<MPV, 1>(mw, mx, p, ctas, st);
+  case MPV: return kind == 0 ? launch_smallm<MPV, 0>(mw, mx, p, ctas, st)                            \
+                 : (kind == 1 ? launch_smallm<MPV, 1>(mw, mx, p, ctas, st) : launch_smallm<MPV, 2>(mw, mx, p, ctas, st));
   switch (MP) {
     KSANA_SM_DISPATCH(16)
     KSANA_SM_DISPATCH(32)

@@ -220,8 +220,17 @@ def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, b
     if out is None and out_f32 is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
     dst = out if out_f32 is None else out_f32
-    if hw_scale and M >= MX_MIN_M and splits == 0 and (bn == 0 or bn >= 128):
-        return gemm_mxfp8(xq, xs, wq, ws, out, bias, residual, out_f32, bn, max_ctas)
+    if hw_scale:
+        # power-of-two scales: both kernels let the tensor cores apply them. Skinny stream-K kernel for decode-sized
+        # M, and for mid-sized M when the output has too few tiles to fill the SMs and K is long; tiled kernel
+        # otherwise (256-wide tiles when they fill the SMs). Crossovers are measured.
+        t256 = ((M + 127) // 128) * ((N + 255) // 256)
+        skinny = M <= SMALL_M_FP8 or (M <= 64 and t256 < 100 and K >= 16384)
+        if (skinny or splits != 0) and M <= 128 and bn == 0:
+            return _gemm_smallm(2, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)
+        if bn == 0 or bn >= 128:
+            return gemm_mxfp8(xq, xs, wq, ws, out, bias, residual, out_f32, bn or (256 if t256 >= 100 else 128),
+                              max_ctas)
     skinny = M <= SMALL_M_FP8 or (M <= 64 and K >= 16384 and N <= 16384)
     if (skinny or splits < 0) and M <= 128 and bn == 0:
         return _gemm_smallm(1, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)

@@ -31,6 +31,22 @@ def case_skinny_fp8():       # decode gate|up shard: 8 tokens, 235 MB of FP8 wei
         native.gemm_fp8(xq, xs, wq, ws, out=y)
 
 
+def case_skinny_mx_m64():    # decode at batch 64 with tensor-core-applied scales: 470 MB of FP8 weights streamed once
+    wq, ws = _w8(57344, 8192)
+    xq, xs = native.quant_fp8(torch.randn(64, 8192, device=DEV, dtype=torch.bfloat16))
+    y = torch.empty(64, 57344, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        native.gemm_fp8(xq, xs, wq, ws, out=y, splits=-1, hw_scale=True)
+
+
+def case_gemm_mxfp8():       # prefill-sized hardware-scaled FP8 GEMM: 4096 x 10240 x 8192
+    wq, ws = _w8(10240, 8192)
+    xq, xs = native.quant_fp8(torch.randn(4096, 8192, device=DEV, dtype=torch.bfloat16))
+    y = torch.empty(4096, 10240, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        native.gemm_mxfp8(xq, xs, wq, ws, y)
+
+
 def case_skinny_bf16():
     w = torch.randn(14336, 8192, device=DEV, dtype=torch.bfloat16) * 0.05
     x = torch.randn(8, 8192, device=DEV, dtype=torch.bfloat16)

@@ -64,3 +64,22 @@ def test_gemm_fp8_exact_scales_still_served():
     assert W2.ue8m0
     y2 = linear(x, W2)
     assert rel_err(y2, ref.gemm_fp8(xq, xs, W2.wq, W2.ws, out_dtype=torch.float32)) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(1, 512, 1024, 0), (8, 8192, 8192, 0), (16, 1280, 8192, 37), (17, 4096, 4096, 7),
+                                          (64, 57344, 8192, -1), (64, 8192, 28672, -1), (128, 1000, 2048, 3),
+                                          (100, 10240, 1024, -1), (32, 57344, 8192, 0), (3, 8192, 28672, 0),
+                                          (8, 7168, 640, 1), (33, 8192, 8192, 0)])
+def test_gemm_smallm_hw_scaled(M, N, K, splits):
+    """Skinny stream-K kernel with tensor-core-applied scales (kind 2), through the public routing."""
+    x, w = _operands(M, N, K, seed=M * 7 + N + K)
+    wq, ws = ref.quant_weight_fp8_block(w)
+    xq, xs = native.quant_fp8(x)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):   # twice: the tile counters must come back to zero
+        y = native.gemm_fp8(xq, xs, wq, ws, bias=bias, residual=res, splits=splits, hw_scale=True)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    want = ref.gemm_fp8(xq, xs, wq, ws, bias, res, out_dtype=torch.float32)
+    assert rel_err(y, want) < 1e-2, rel_err(y, want)
