@@ -51,6 +51,8 @@ _SIGS = {
     "ksana_swap_blocks": [vp, vp, vp, i32, i64, i32, vp],
     "ksana_add": [vp, vp, vp, vp, i64, i32, vp],
     "ksana_cast_f32": [vp, vp, i64, vp],
+    "ksana_paged_prefill_tc": [vp, i64, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i64,
+                               vp, vp],
     "ksana_paged_prefill": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32,
                             f32, f32, i64, vp, vp],
     "ksana_paged_decode": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, f32, f32,
@@ -352,9 +354,21 @@ def _cache_rows(cache_layer, block_stride, D):
     return int(cache_layer.shape[0]) * int(block_stride) // int(D)
 
 
+PREFILL_TC = True                  # prefill attention on tcgen05 where the kernel covers the configuration
+
+
 def paged_prefill(q, q_stride, out, cache_layer, block_stride, block_tokens, block_table, cu_q, kv_lens, B, max_q_len,
                   Hq, Hkv, D, scale, alibi=None, k_scale=1.0, v_scale=1.0):
     fp8 = cache_layer.dtype != torch.bfloat16
+    if PREFILL_TC and not fp8 and D == 128:
+        # tcgen05 kernel (head dim 128, bf16 cache, group size dividing 128); -100 = configuration not covered
+        rc = lib().ksana_paged_prefill_tc(_p(q), q_stride, q.shape[0], _p(out), out.stride(0), _p(cache_layer),
+                                          block_stride, block_tokens, _p(block_table), block_table.stride(0),
+                                          _p(cu_q), _p(kv_lens), _p(alibi), B, max_q_len, Hq, Hkv, D, float(scale),
+                                          _cache_rows(cache_layer, block_stride, D), _p(err_flag(q.device)), _st())
+        if rc != -100:
+            _check(rc, "ksana_paged_prefill_tc")
+            return
     rc = lib().ksana_paged_prefill(_p(q), q_stride, _p(out), out.stride(0), _p(cache_layer), block_stride,
                                    block_tokens, _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_lens),
                                    _p(alibi), B, max_q_len, Hq, Hkv, D, float(scale), int(fp8), float(k_scale),

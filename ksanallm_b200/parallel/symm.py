@@ -147,7 +147,7 @@ class SymmetricComm:
         if one_shot:
             scratch, counters = native.gemm_workspace(self.device)
             if W.fp8:
-                rc = lib.ksana_gemm_smallm_push(1, x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0),
+                rc = lib.ksana_gemm_smallm_push(2 if W.ue8m0 else 1, x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0),
                                                 W.wq.data_ptr(), W.wq.stride(0), W.ws.data_ptr(), H, bias, M, H,
                                                 W.in_features, scratch.data_ptr(), scratch.numel() * 4,
                                                 counters.data_ptr(), counters.numel(), push, self.size, err, st)

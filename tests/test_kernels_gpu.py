@@ -190,6 +190,32 @@ def test_paged_prefill(Hq, Hkv, D, fp8):
     assert rel_err(out, want) < 2e-2, rel_err(out, want)
 
 
+@pytest.mark.parametrize("tc", [True, False])
+@pytest.mark.parametrize("Hq,Hkv,bt,alibi", [(16, 2, 16, False), (8, 8, 32, True), (4, 1, 64, False)])
+def test_paged_prefill_long(Hq, Hkv, bt, alibi, tc):
+    """Chunked prefill with a cached prefix, several KV tiles per query tile; tcgen05 kernel and general kernel."""
+    D = 128
+    q_lens, kv_lens = [1000, 77, 513], [1500, 77, 2048]
+    B = len(q_lens)
+    q, cache, table, cu_q, kvl = _make_paged(B, q_lens, kv_lens, Hq, Hkv, D, bt, False, seed=7)
+    # rows past a sequence's end inside its last block hold NaN: they must not leak into the output
+    last_blk, last = table[1, (kv_lens[1] - 1) // bt].long(), kv_lens[1] % bt
+    cache[last_blk, :, :, last:] = float("nan")
+    slopes = torch.tensor([2.0 ** (-(i + 1) / 2) for i in range(Hq)], device=DEV, dtype=torch.float32) if alibi else None
+    out = torch.zeros(q.shape[0], Hq * D, device=DEV, dtype=torch.bfloat16)
+    old = native.PREFILL_TC
+    native.PREFILL_TC = tc
+    try:
+        native.paged_prefill(q, q.stride(0), out, cache, cache.stride(0), bt, table, cu_q, kvl, B, max(q_lens), Hq, Hkv, D,
+                             1 / math.sqrt(D), alibi=slopes)
+        torch.cuda.synchronize()
+        native.check_err_flag(DEV)
+    finally:
+        native.PREFILL_TC = old
+    want = ref.paged_attention(q, torch.nan_to_num(cache), table, cu_q, kvl, Hq, Hkv, D, 1 / math.sqrt(D), alibi=slopes)
+    assert rel_err(out, want) < 2e-2, rel_err(out, want)
+
+
 @pytest.mark.parametrize("Hq,Hkv,D", [(8, 1, 128), (4, 2, 64), (64, 8, 128), (16, 16, 128)])
 @pytest.mark.parametrize("splits", [1, 4])
 @pytest.mark.parametrize("fp8", [False, True])
