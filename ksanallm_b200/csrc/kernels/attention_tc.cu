@@ -176,70 +176,85 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       const int t0 = j * kFaTile;
       if (!mbar_wait(s_full, par, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const bool need_mask = (t0 + kFaTile - 1 > limit) || slope2 != 0.f;
-      // pass 1: row maximum of the scaled, masked scores
-      float mx = -CUDART_INF_F;
+      const bool need_mask = (t0 + kFaTile - 1 > limit) || slope2 != 0.f || p.scale_log2 <= 0.f;
+      // lazy rescale of O: keep the old reference maximum unless the row's maximum grew by more than 2^8
+      auto update_reference = [&](float mx) {
+        float m_new = m_used;
+        if (mx > m_used + kFaRescaleLog2 || m_used == -CUDART_INF_F) m_new = (mx == -CUDART_INF_F) ? m_used : mx;
+        const bool grow = j > 0 && m_new != m_used && m_used != -CUDART_INF_F;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float f = grow ? exp2f(m_used - m_new) : 1.f;
+          l *= f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_s + lane_off + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem_o + lane_off + c * 32, o);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int pos = t0 + c * 32 + i;
-            float v = __uint_as_float(r[i]) * p.scale_log2 + slope2 * static_cast<float>(pos - limit);
-            mx = fmaxf(mx, pos <= limit ? v : -CUDART_INF_F);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st32(tmem_o + lane_off + c * 32, o);
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * p.scale_log2);
         }
-      }
-      // lazy rescale: keep the old reference maximum unless the row's maximum grew by more than 2^8
-      float m_new = m_used;
-      if (mx > m_used + kFaRescaleLog2 || m_used == -CUDART_INF_F) m_new = (mx == -CUDART_INF_F) ? m_used : mx;
-      const bool grow = j > 0 && m_new != m_used && m_used != -CUDART_INF_F;
-      if (__any_sync(0xffffffffu, grow)) {
-        const float f = grow ? exp2f(m_used - m_new) : 1.f;
-        l *= f;
+        m_used = m_new;
+        return (m_used == -CUDART_INF_F) ? 0.f : m_used;
+      };
+      if (!__any_sync(0xffffffffu, need_mask)) {
+        // interior tile: the whole row in registers with a single TMEM round trip
+        uint32_t r[128];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_off + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        tmem_ld_wait();
+        float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int i = 0; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+        const float mref = update_reference(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2);
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 128; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mref));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -mref));
+          l4[(i >> 1) & 3] += p0 + p1;
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          r[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);        // in place: slot i/2 has already been consumed
+        }
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_st16(tmem_s + lane_off + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&r[c * 16]));
+      } else {
+        // diagonal / last / ALiBi tile: masked two-pass form
+        float mx = -CUDART_INF_F;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
-          tmem_ld32(tmem_o + lane_off + c * 32, r);
+          tmem_ld32(tmem_s + lane_off + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-          tmem_st32(tmem_o + lane_off + c * 32, r);
+          for (int i = 0; i < 32; ++i) {
+            const int pos = t0 + c * 32 + i;
+            const float v = __uint_as_float(r[i]) * p.scale_log2 + slope2 * static_cast<float>(pos - limit);
+            mx = fmaxf(mx, pos <= limit ? v : -CUDART_INF_F);
+          }
         }
-      }
-      m_used = m_new;
-      const float mref = (m_used == -CUDART_INF_F) ? 0.f : m_used;
-      // pass 2: probabilities as bf16 pairs over the first 64 columns of S
+        const float mref = update_reference(mx);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_s + lane_off + c * 32, r);
-        tmem_ld_wait();
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_s + lane_off + c * 32, r);
+          tmem_ld_wait();
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0, p1;
-          if (need_mask) {
+          for (int i = 0; i < 32; i += 2) {
             const int pos = t0 + c * 32 + i;
             const float v0 = __uint_as_float(r[i]) * p.scale_log2 + slope2 * static_cast<float>(pos - limit) - mref;
             const float v1 = __uint_as_float(r[i + 1]) * p.scale_log2 + slope2 * static_cast<float>(pos + 1 - limit) - mref;
-            p0 = pos <= limit ? fast_exp2(v0) : 0.f;
-            p1 = pos + 1 <= limit ? fast_exp2(v1) : 0.f;
-          } else {
-            p0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -mref));
-            p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -mref));
+            const float p0 = pos <= limit ? fast_exp2(v0) : 0.f;
+            const float p1 = pos + 1 <= limit ? fast_exp2(v1) : 0.f;
+            l += p0 + p1;
+            __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);
           }
-          l += p0 + p1;
-          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+          tmem_st16(tmem_s + lane_off + c * 16, pk);
         }
-        tmem_st16(tmem_s + lane_off + c * 16, pk);
       }
       tmem_st_wait();
       if (t0 + kFaTile > kv_len) {
