@@ -38,7 +38,7 @@ struct FaParams {
   const int* block_table; int table_stride;
   const int* cu_q; const int* kv_lens; const float* alibi;
   int Hq, Hkv, G, block_tokens;
-  long long rows_per_block;                  // cache rows (of D elements) per block = 2 * Hkv * block_tokens
+  long long rows_per_block;                  // cache rows (of D elements) between consecutive blocks
   float scale_log2;
   int* err;
 };
@@ -330,7 +330,8 @@ using namespace ksana;
 // Returns 0 when launched, -100 when this kernel does not cover the configuration (the caller then uses the
 // general kernel of attention.cu), other negatives on setup errors.
 // q: [T, q_stride] bf16 with head h at column h*128 (T = rows addressable from q); cache: layer base of
-// [block][2][Hkv][block_tokens][128] bf16 with cache_rows rows of 128 elements addressable.
+// [block][2][Hkv][block_tokens][128] bf16, blocks block_stride elements apart, cache_rows rows of 128 elements
+// addressable.
 extern "C" int ksana_paged_prefill_tc(const void* q, long long q_stride, long long q_rows, void* out, long long out_stride,
                                       const void* cache, long long block_stride, int block_tokens,
                                       const int* block_table, int table_stride, const int* cu_q, const int* kv_lens,
@@ -341,7 +342,7 @@ extern "C" int ksana_paged_prefill_tc(const void* q, long long q_stride, long lo
   const int G = Hq / Hkv;
   const int bt = block_tokens;
   if (kFaTile % G || G > 128 || !(bt == 8 || bt == 16 || bt == 32 || bt == 64 || bt == 128)) return -100;
-  if (block_stride != 2LL * Hkv * bt * D || cache_rows <= 0 || q_rows <= 0) return -100;
+  if (block_stride % D || block_stride < 2LL * Hkv * bt * D || cache_rows <= 0 || q_rows <= 0) return -100;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) & 15 || (q_stride % 8)) return -100;
   FaEncodeFn enc = fa_encode_fn();
   if (!enc) return -100;
@@ -374,7 +375,7 @@ extern "C" int ksana_paged_prefill_tc(const void* q, long long q_stride, long lo
   p.out = static_cast<bf16*>(out); p.out_stride = out_stride;
   p.block_table = block_table; p.table_stride = table_stride; p.cu_q = cu_q; p.kv_lens = kv_lens; p.alibi = alibi;
   p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.block_tokens = bt;
-  p.rows_per_block = 2LL * Hkv * bt;
+  p.rows_per_block = block_stride / D;        // a block of one layer may sit inside a larger per-block record
   p.scale_log2 = scale * 1.44269504f;
   p.err = err;
   dim3 grid((max_q_len * G + kFaTile - 1) / kFaTile, Hkv, B);

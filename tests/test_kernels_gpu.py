@@ -201,6 +201,10 @@ def test_paged_prefill_long(Hq, Hkv, bt, alibi, tc):
     # rows past a sequence's end inside its last block hold NaN: they must not leak into the output
     last_blk, last = table[1, (kv_lens[1] - 1) // bt].long(), kv_lens[1] % bt
     cache[last_blk, :, :, last:] = float("nan")
+    # the layer's blocks sit inside a per-block record that holds several layers, as in the engine's cache
+    record = torch.zeros(cache.shape[0], 3, *cache.shape[1:], device=DEV, dtype=cache.dtype)
+    record[:, 1] = cache
+    cache = record[:, 1]
     slopes = torch.tensor([2.0 ** (-(i + 1) / 2) for i in range(Hq)], device=DEV, dtype=torch.float32) if alibi else None
     out = torch.zeros(q.shape[0], Hq * D, device=DEV, dtype=torch.bfloat16)
     old = native.PREFILL_TC
