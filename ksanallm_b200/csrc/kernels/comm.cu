@@ -127,7 +127,10 @@ struct ReduceNormParams {
   const bf16* norm_w; const bf16* norm_b; float eps; int layernorm;   // norm_w null: no norm (plain all-reduce + residual)
   bf16* y;                        // normalised output [M, H] (local) or null
   uint8_t* yq; float* yscale; int scale_ld;   // fp8 operand of y or null
-  int gather;                     // 1: push this rank's rows of h / y / yq to every peer, then wait for theirs
+  int gather;                     // bit 0: push this rank's rows of y / yq to every peer, then wait for theirs;
+                                  // bit 1: push its rows of h too; bit 2: pull mode - every rank's partial
+                                  // product [M, H] sits at slots_off in its own buffer and the row owner reads
+                                  // its rows from all peers (coalesced peer loads) instead of receiving pushes
   long long h_sym_off, y_sym_off, yq_sym_off, ys_sym_off;   // offsets of h / y / yq / yscale inside the symmetric buffer (gather mode: those tensors live there)
   int* err;
 };
@@ -157,16 +160,30 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.f;
       }
-      for (int r = 0; r < c.size; ++r) {        // fixed order: every rank produces the same bits
-        const uint4 pv = reinterpret_cast<const uint4*>(base + r * p.slot_stride + (static_cast<size_t>(lrow) * p.H) * 2)[i];
-        float f[8];
-        unpack8c(pv, f);
+      // all loads first (peer loads in pull mode: one NVLink round trip, not one per rank), then a fixed summation
+      // order so that every rank produces the same bits
+      uint4 pv[kMaxRanks];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r < c.size) {
+          const uint8_t* src = (p.gather & 4)
+              ? static_cast<const uint8_t*>(c.data[r]) + p.slots_off + (static_cast<size_t>(row) * p.H) * 2
+              : base + r * p.slot_stride + (static_cast<size_t>(lrow) * p.H) * 2;
+          pv[r] = reinterpret_cast<const uint4*>(src)[i];
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r < c.size) {
+          float f[8];
+          unpack8c(pv[r], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += f[e];
+        }
       }
       const uint4 packed = pack8c(acc);
       if (p.h) reinterpret_cast<uint4*>(p.h + static_cast<size_t>(row) * p.H)[i] = packed;
-      if (p.gather && p.h) {
+      if ((p.gather & 2) && p.h) {
         for (int r = 0; r < c.size; ++r) {
           if (r == c.rank) continue;
           bf16* ph = reinterpret_cast<bf16*>(static_cast<uint8_t*>(c.data[r]) + p.h_sym_off);
@@ -229,7 +246,7 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
         const uint4 packed = pack8c(o);
         if (p.y) {
           reinterpret_cast<uint4*>(p.y + static_cast<size_t>(row) * p.H)[i] = packed;
-          if (p.gather) {
+          if (p.gather & 1) {
             for (int r = 0; r < c.size; ++r) {
               if (r == c.rank) continue;
               bf16* py = reinterpret_cast<bf16*>(static_cast<uint8_t*>(c.data[r]) + p.y_sym_off);
@@ -250,7 +267,7 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
           const uint2 q = pack8_e4m3c(o, 1.f / scale);
           reinterpret_cast<uint2*>(p.yq + static_cast<size_t>(row) * p.H)[i] = q;
           if ((i & 15) == 0) p.yscale[static_cast<size_t>(i >> 4) * p.scale_ld + row] = scale;
-          if (p.gather) {
+          if (p.gather & 1) {
             for (int r = 0; r < c.size; ++r) {
               if (r == c.rank) continue;
               uint8_t* pq = static_cast<uint8_t*>(c.data[r]) + p.yq_sym_off;
@@ -366,7 +383,7 @@ extern "C" int ksana_reduce_norm(const unsigned long long* data_ptrs, const unsi
   // a rank with no rows still takes part in the flag exchange
   reduce_norm_kernel<<<row_count > 0 ? row_count : 1, threads, 0, st>>>(p);
   if (cudaGetLastError() != cudaSuccess) return -4;
-  if (gather) {
+  if (gather & 1) {
     gather_fence_kernel<<<1, 32, 0, st>>>(p.peers, p.ctrs, err);
     if (cudaGetLastError() != cudaSuccess) return -5;
   }

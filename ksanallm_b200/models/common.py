@@ -288,7 +288,8 @@ class CommonModel:
                 nw, nb, nq = self.layers[i + 1].input_norm, self.layers[i + 1].input_norm_bias, self.layers[i + 1].qkv
             else:
                 nw, nb, nq = self.final_norm, self.final_norm_bias, None
-            h, x = symm.row_parallel_norm(act, lw.down, h, nw, nb, cfg.rms_norm_eps, ln, quant_for=nq)
+            h, x = symm.row_parallel_norm(act, lw.down, h, nw, nb, cfg.rms_norm_eps, ln, quant_for=nq,
+                                          gather_h=step.want_hidden and i + 1 == n)
         if step.want_hidden:
             self.step_hidden, self.step_normed = h, x
         hn = ops.gather_rows(x, step.logits_rows) if step.logits_rows is not None else x

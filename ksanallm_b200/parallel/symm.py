@@ -10,11 +10,15 @@ plain pointers over NVLink. Layout (bytes):
     stage                   staging area for the plain all-reduce
 
 Row-parallel linear:
-  * up to ``ONE_SHOT_ROWS`` rows: the skinny GEMM pushes its partial product to every rank; each rank sums
-    the slots, adds the residual and normalises all rows itself (one flag exchange, no gather);
-  * more rows: the tiled GEMM pushes each row block to the rank that owns it (reduce-scatter inside the
-    GEMM epilogue); the owner reduces + adds the residual + normalises (+ FP8 quantises) its rows and
-    pushes them to every peer (all-gather), followed by one more flag exchange.
+  * up to ``ONE_SHOT_ROWS`` rows: the GEMM writes its partial product into its own symmetric buffer; after
+    one flag exchange every rank pulls all rows from every peer, sums them in rank order, adds the residual
+    and normalises all rows itself (no gather phase);
+  * more rows: the GEMM writes its partial product into its own symmetric buffer; one kernel per rank then
+    pulls the rows it owns from every peer (coalesced peer loads: reduce-scatter), adds the residual,
+    normalises (+ FP8 quantises) and pushes the result rows to every peer (all-gather), followed by one more
+    flag exchange. The residual stream stays sharded by rows: only its owner ever reads it. (Pushing partial
+    tiles from the GEMM epilogue, one 16-byte store per row and thread, ran NVLink at a fraction of its rate;
+    ``PUSH_EPILOGUE`` keeps that variant selectable.)
 Every wait is bounded in the kernels; a timeout sets the device error word (see native.check_err_flag).
 """
 from __future__ import annotations
@@ -29,7 +33,8 @@ from ..ops import native
 from ..ops.dispatch import LinearWeight, QTensor, quantize
 
 FLAG_BYTES = 4096
-ONE_SHOT_ROWS = 16
+ONE_SHOT_ROWS = 64             # up to this many rows every rank reduces all rows itself (one flag exchange)
+PUSH_EPILOGUE = False          # large batches: reduce-scatter by GEMM-epilogue pushes instead of owner pulls
 
 
 def _align(x: int, a: int = 256) -> int:
@@ -127,10 +132,12 @@ class SymmetricComm:
         return (C.c_ulonglong * 8)(*[int(self.handle.buffer_ptrs[r]) + base if r < self.size else 0 for r in range(8)])
 
     def row_parallel_norm(self, x, W: LinearWeight, h: torch.Tensor, norm_w, norm_b=None, eps: float = 1e-6,
-                          layernorm: bool = False, quant_for: Optional[LinearWeight] = None, want_y: bool = True):
+                          layernorm: bool = False, quant_for: Optional[LinearWeight] = None, want_y: bool = True,
+                          gather_h: bool = False):
         """h += sum_ranks(x W^T); y = norm(h) in the form the next linear wants. Returns (h, y).
 
-        ``h`` must be the symmetric residual view (``self.h[:M]``) when M > ONE_SHOT_ROWS."""
+        ``h`` must be the symmetric residual view (``self.h[:M]``) when M > ONE_SHOT_ROWS; there every rank
+        keeps only the rows it owns up to date unless ``gather_h`` asks for the full residual stream."""
         M = x.q.shape[0] if isinstance(x, QTensor) else x.shape[0]
         H = W.out_features
         parity = self.parity
@@ -144,7 +151,16 @@ class SymmetricComm:
         one_shot = M <= ONE_SHOT_ROWS
         rows_per = M if one_shot else (M + self.size - 1) // self.size
         bias = W.bias.data_ptr() if (W.bias is not None and self.rank == 0) else None
-        if one_shot:
+        if not PUSH_EPILOGUE:
+            # partial product [M, H] into this rank's own symmetric buffer (the slot area of this parity); the
+            # reduce kernel of every row owner (one-shot: of every rank) pulls it from there
+            part = self.buf[self.slots_off[parity]: self.slots_off[parity] + M * H * 2].view(torch.bfloat16).view(M, H)
+            wb = W.bias if self.rank == 0 else None
+            if W.fp8:
+                native.gemm_fp8(x.q, x.s, W.wq, W.ws, out=part, bias=wb, hw_scale=W.ue8m0)
+            else:
+                native.gemm_bf16(x, W.w, out=part, bias=wb)
+        elif one_shot:
             scratch, counters = native.gemm_workspace(self.device)
             if W.fp8:
                 rc = lib.ksana_gemm_smallm_push(2 if W.ue8m0 else 1, x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0),
@@ -172,15 +188,15 @@ class SymmetricComm:
             native._check(rc, "ksana_gemm_push")
         want_q = quant_for is not None and quant_for.fp8 and H % 128 == 0 and norm_w is not None
         if one_shot:
-            row_begin, row_count, gather = 0, M, 0
+            row_begin, row_count, gather = 0, M, (0 if PUSH_EPILOGUE else 4)
             y = torch.empty(M, H, dtype=torch.bfloat16, device=self.device) if (norm_w is not None and not want_q) else None
             yq = torch.empty(M, H, dtype=torch.float8_e4m3fn, device=self.device) if want_q else None
-            ys = torch.empty(H // 128, 16, dtype=torch.float32, device=self.device) if want_q else None
-            scale_ld = 16
+            scale_ld = (M + 3) // 4 * 4
+            ys = torch.empty(H // 128, scale_ld, dtype=torch.float32, device=self.device) if want_q else None
         else:
             row_begin = min(self.rank * rows_per, M)
             row_count = max(0, min(rows_per, M - row_begin))
-            gather = 1
+            gather = 1 | (2 if gather_h else 0) | (0 if PUSH_EPILOGUE else 4)
             assert h.data_ptr() == self.h.data_ptr(), "large-batch row-parallel linear needs the symmetric residual view"
             y = self.y[:M] if (norm_w is not None and not want_q) else None
             yq = self.yq[:M] if want_q else None

@@ -11,7 +11,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from ksanallm_b200.ops import native, reference as ref  # noqa: E402
 from ksanallm_b200.ops.dispatch import LinearWeight  # noqa: E402
-from ksanallm_b200.parallel.symm import SymmetricComm  # noqa: E402
+from ksanallm_b200.parallel.symm import ONE_SHOT_ROWS, SymmetricComm  # noqa: E402
 
 
 def main():
@@ -45,7 +45,7 @@ def main():
     say("all_reduce max err", err)
     assert err < 0.1
     results = {}
-    for M in (4, 16, 200):
+    for M in (4, 16, 64, 200):
         for quant in (False, True):
             torch.manual_seed(7)
             K = 2048
@@ -61,12 +61,12 @@ def main():
             nxt = LinearWeight(wq=torch.empty(8, H, device=dev, dtype=torch.float8_e4m3fn), ws=torch.empty(1, 8, device=dev)) if quant else None
             for rep in range(3):
                 comm.begin_forward()
-                if M > 16:
+                if M > ONE_SHOT_ROWS:
                     h = comm.h[:M]
                     h.copy_(h0)
                 else:
                     h = h0.clone()
-                h, y = comm.row_parallel_norm(xs, W, h, nw, None, 1e-5, False, quant_for=nxt)
+                h, y = comm.row_parallel_norm(xs, W, h, nw, None, 1e-5, False, quant_for=nxt, gather_h=True)
                 torch.cuda.synchronize()
                 native.check_err_flag(dev)
             # oracle: full product of the (de)quantised operands + residual, then RMSNorm
@@ -101,7 +101,7 @@ def main():
         xs = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         nw = torch.ones(H, device=dev, dtype=torch.bfloat16)
         W = LinearWeight(w=w)
-        hbuf = comm.h[:M] if M > 16 else torch.zeros(M, H, device=dev, dtype=torch.bfloat16)
+        hbuf = comm.h[:M] if M > ONE_SHOT_ROWS else torch.zeros(M, H, device=dev, dtype=torch.bfloat16)
 
         def fused():
             comm.begin_forward()
