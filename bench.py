@@ -95,6 +95,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--scale-mode", default="ue8m0", choices=["ue8m0", "fp32"],
+                    help="weight scales: powers of two applied by the tensor cores, or exact amax/448 fp32 scales")
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
     args = ap.parse_args()
 
@@ -131,6 +133,7 @@ def main():
     blocks_per_seq = (S_in + S_out + 15) // 16 + 1
     ec.block_manager.device_blocks_num = B * blocks_per_seq + 4 * max(B, 8) + 64
     ec.quantization.weight_quant_method = "fp8_block"
+    ec.quantization.fp8_scale_mode = args.scale_mode
     llm = LLM(ec, mc, weights="random", device="cuda", max_positions=S_in + S_out + 64)
     dev = llm.device
     s = ne.SamplingConfig()
@@ -189,11 +192,15 @@ def main():
             "metric": "output tok/s (offline, max over ranks) at Llama-3-70B fp8 TP%d" % world,
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "fp8-e4m3 block-scaled weights (128x128, fp32 scales), bf16 activations", "data": "synthetic",
+            "dtype": ("fp8-e4m3 block-scaled weights (128x128 blocks, fp32 scales holding powers of two so that the tensor "
+                      "cores apply them), fp8-e4m3 1x128-scaled GEMM inputs, bf16 activations and KV cache"
+                      if args.scale_mode == "ue8m0" else
+                      "fp8-e4m3 block-scaled weights (128x128 blocks, exact amax/448 fp32 scales), fp8-e4m3 "
+                      "1x128-scaled GEMM inputs, bf16 activations and KV cache"), "data": "synthetic",
             "impl": "ours",
             "config": {"model": "Llama-3-70B architecture, random-init N(0,0.02)" + (" [DEBUG %d layers: INVALID]" % args.layers if args.layers else ""),
                        "global_batch": B, "seq_len": S_in, "output_len": S_out, "parallelism": "tp%d" % world,
-                       "comm": args.comm, "kv_block_tokens": 16, "cuda_graph_decode": not args.no_graphs,
+                       "comm": args.comm, "kv_block_tokens": 16, "weight_scale_mode": args.scale_mode, "cuda_graph_decode": not args.no_graphs,
                        "l2": "inputs larger than L2 (weights 70 GB per pass); no explicit flush"},
             "clocks": clocks, "gpu_launches": launches,
             "graph_replays": getattr(llm.engine.runner, "graph_replays", 0),

@@ -69,6 +69,9 @@ class QuantConfig:
     gptq_backend: str = "cutlass"
     kv_cache_dtype: str = "auto"              # auto | fp8_e5m2 | fp8_e4m3
     weight_quant_method: str = "auto"         # auto | fp8_e4m3 | fp8_block | nvfp4
+    # scales of weights quantised at load time: "ue8m0" = powers of two (applied by the tensor cores through the
+    # block-scaled MMA), "fp32" = amax / 448 exactly (served by the register-promotion GEMM)
+    fp8_scale_mode: str = "ue8m0"
 
 
 @dataclass
@@ -146,6 +149,9 @@ def load_yaml_config(path_or_dict) -> EngineConfig:
     cfg.quantization.gptq_backend = str(q.get("gptq_backend", cfg.quantization.gptq_backend))
     cfg.quantization.kv_cache_dtype = str((q.get("kv_cache") or {}).get("dtype", "auto"))
     cfg.quantization.weight_quant_method = str((q.get("weight") or {}).get("quant_method", "auto"))
+    cfg.quantization.fp8_scale_mode = str((q.get("weight") or {}).get("scale_mode", cfg.quantization.fp8_scale_mode))
+    if cfg.quantization.fp8_scale_mode not in ("ue8m0", "fp32"):
+        raise ValueError(f"unsupported weight.scale_mode {cfg.quantization.fp8_scale_mode}")
     if cfg.quantization.kv_cache_dtype not in ("auto", "fp8_e5m2", "fp8_e4m3"):
         raise ValueError(f"unsupported kv_cache.dtype {cfg.quantization.kv_cache_dtype}")
     if cfg.quantization.weight_quant_method not in ("auto", "fp8_e4m3", "fp8_block", "nvfp4"):

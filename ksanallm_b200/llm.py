@@ -108,6 +108,8 @@ class LLM:
         quant = {"auto": None, "fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "nvfp4": "fp8_block"}[quant]
         if model_cfg.fp8_checkpoint and quant is None:
             quant = "fp8_block"
+        from .ops import reference as _ref
+        _ref.WEIGHT_SCALE_POW2 = self.engine_cfg.quantization.fp8_scale_mode != "fp32"
         if weights == "random":
             source = RandomSource(seed=seed, on_device=dev_type == "cuda" and model_cfg.hidden_size >= 2048)
         elif weights == "checkpoint":

@@ -46,9 +46,15 @@ def quant_fp8(x):
     return q, scale.t().contiguous()
 
 
-def quant_weight_fp8_block(w, block=128, pow2=True):
+WEIGHT_SCALE_POW2 = True   # default scale rule of quant_weight_fp8_block (engine option quantization.fp8_scale_mode)
+
+
+def quant_weight_fp8_block(w, block=128, pow2=None):
     """[N,K] weight -> e4m3 + one fp32 scale per (128 x 128) block, scales [ceil(N/128), ceil(K/128)].
-    pow2: power-of-two scales (what the tensor cores can apply themselves); False: amax / 448 exactly."""
+    pow2: power-of-two scales (what the tensor cores can apply themselves); False: amax / 448 exactly;
+    None: the module default ``WEIGHT_SCALE_POW2``."""
+    if pow2 is None:
+        pow2 = WEIGHT_SCALE_POW2
     N, K = w.shape
     nb, kb = (N + block - 1) // block, (K + block - 1) // block
     wp = torch.zeros(nb * block, kb * block, dtype=torch.float32, device=w.device)
