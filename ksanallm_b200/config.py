@@ -236,6 +236,7 @@ class ModelConfig:
     first_k_dense_replace: int = 0
     moe_layer_freq: int = 1
     shared_expert_gate: bool = False
+    expert_para_size: int = 1             # > 1: whole experts per rank of the tensor-parallel group (set by the engine)
     # MLA
     q_lora_rank: int = 0
     kv_lora_rank: int = 0

@@ -101,6 +101,10 @@ class LLM:
             torch.cuda.set_device(self.device)
         tp = self.world
         check_tp(model_cfg, tp)
+        ep = self.engine_cfg.global_.expert_para_size
+        if ep not in (1, tp):
+            raise ValueError(f"expert_para_size {ep} must be 1 or equal to the tensor-parallel size {tp}")
+        model_cfg.expert_para_size = ep
         self.comm = TPComm(dev_group, self.rank, tp, self.engine_cfg.global_.comm_backend if dev_type == "cuda" else "nccl",
                            self.device, max_tokens=self.engine_cfg.batch_scheduler.max_step_tokens,
                            hidden=model_cfg.hidden_size) if tp > 1 else None

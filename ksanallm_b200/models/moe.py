@@ -63,7 +63,13 @@ def _cols(t, rank, size):
 
 
 def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dtype, quant, ep_rank=0, ep_size=1):
+    """Expert parallelism (``ep_size`` > 1, over the tensor-parallel group whose ranks all hold every token):
+    each rank keeps whole experts ``[lo, hi)`` (no intermediate-dimension slicing) and computes only their
+    contributions; the block's all-reduce is the combine. The shared expert stays tensor-parallel."""
     from .weights import RandomSource, _make_linear
+    sh_rank, sh_size = tp_rank, tp_size
+    if ep_size > 1:
+        tp_rank, tp_size = 0, 1
     H, E, I_full = cfg.hidden_size, cfg.num_experts, cfg.moe_intermediate_size
     I = (I_full + tp_size - 1) // tp_size
     per = (E + ep_size - 1) // ep_size
@@ -104,9 +110,9 @@ def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dt
     sI_full = cfg.shared_expert_intermediate_size
     if sI_full:
         sp = prefix + "mlp.shared_expert."
-        g = _rows(source.get(sp + "gate_proj.weight", (sI_full, H), device=device), tp_rank, tp_size)
-        u = _rows(source.get(sp + "up_proj.weight", (sI_full, H), device=device), tp_rank, tp_size)
-        d = _cols(source.get(sp + "down_proj.weight", (H, sI_full), device=device), tp_rank, tp_size)
+        g = _rows(source.get(sp + "gate_proj.weight", (sI_full, H), device=device), sh_rank, sh_size)
+        u = _rows(source.get(sp + "up_proj.weight", (sI_full, H), device=device), sh_rank, sh_size)
+        d = _cols(source.get(sp + "down_proj.weight", (H, sI_full), device=device), sh_rank, sh_size)
         mw.shared_gate_up = _make_linear(torch.cat([g, u], 0), None, device, dtype, quant)
         mw.shared_down = _make_linear(d, None, device, dtype, quant)
         if cfg.shared_expert_gate:

@@ -44,3 +44,24 @@ def test_route_reference_group_limited():
     groups = ids // 4
     assert all(len(set(g.tolist())) <= 2 for g in groups)
     assert torch.allclose(w.sum(-1), torch.full((9,), 2.5), atol=1e-5)
+
+
+def test_expert_parallel_partials_sum_to_full():
+    """Expert parallelism over a 2-rank tensor-parallel group: each rank holds whole experts and the
+    tensor-parallel slice of the shared expert; the sum of the ranks' block outputs (the all-reduce) equals
+    the single-rank block."""
+    from types import SimpleNamespace
+    from ksanallm_b200.models.moe import load_moe, moe_forward
+    for kind in ("mixtral", "qwen2_moe"):
+        cfg = moe_cfg(kind)
+        src = RandomSource(seed=9, std=0.05)
+        stub = SimpleNamespace(cfg=cfg, tp_size=1, comm=None)
+        x = torch.randn(11, cfg.hidden_size)
+        zero = torch.zeros(11, cfg.hidden_size)
+        full = moe_forward(stub, load_moe(cfg, src, "model.layers.0.", 0, 1, "cpu", torch.float32, None), x, zero)
+        parts = []
+        for r in range(2):
+            mw = load_moe(cfg, src, "model.layers.0.", r, 2, "cpu", torch.float32, None, ep_rank=r, ep_size=2)
+            assert (mw.expert_lo, mw.expert_hi) == (4 * r, 4 * r + 4) and mw.inter == cfg.moe_intermediate_size
+            parts.append(moe_forward(stub, mw, x, zero))
+        assert torch.allclose(parts[0] + parts[1], full, atol=1e-5, rtol=1e-4)
