@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
 #include <stdint.h>
 #include "fp8_scale.cuh"
 
@@ -409,6 +410,38 @@ static inline int norm_threads(int H) {
   return t > 1024 ? 1024 : t;
 }
 
+// ----------------------------------------------------------------------------
+// NVFP4 quantisation of GEMM inputs: 16-element blocks along K, e2m1 values (two per byte, even element in the
+// low nibble), one e4m3 scale per block, one fp32 scale per tensor (given): x ~= e2m1 * block_scale * tensor_scale.
+__global__ void quant_nvfp4_kernel(const bf16* __restrict__ x, int ldx, uint8_t* __restrict__ q, int ldq,
+                                   uint8_t* __restrict__ bs, int ldbs, const float* __restrict__ ts, int M, int K) {
+  const int nb = K >> 4;
+  const long long total = static_cast<long long>(M) * nb;
+  const float inv_ts = 1.f / (ts ? *ts : 1.f);
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(idx / nb), b = static_cast<int>(idx % nb);
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx + b * 16);
+    float f[16];
+    unpack8(src[0], *reinterpret_cast<float(*)[8]>(&f[0]));
+    unpack8(src[1], *reinterpret_cast<float(*)[8]>(&f[8]));
+    float am = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { f[i] *= inv_ts; am = fmaxf(am, fabsf(f[i])); }
+    const __nv_fp8_storage_t sc8 = __nv_cvt_float_to_fp8(fminf(am / 6.f, 448.f), __NV_SATFINITE, __NV_E4M3);
+    const float scf = fmaxf(__half2float(__half(__nv_cvt_fp8_to_halfraw(sc8, __NV_E4M3))), 1.f / 512.f);
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const __nv_fp4x2_storage_t v = __nv_cvt_float2_to_fp4x2(make_float2(f[2 * i] / scf, f[2 * i + 1] / scf), __NV_E2M1,
+                                                              cudaRoundNearest);
+      w[i >> 2] |= static_cast<uint32_t>(v) << (8 * (i & 3));
+    }
+    *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * ldq + b * 8) = make_uint2(w[0], w[1]);
+    bs[static_cast<size_t>(row) * ldbs + b] = sc8;
+  }
+}
+
 }  // namespace ksana
 
 using namespace ksana;
@@ -445,6 +478,17 @@ extern "C" int ksana_quant_fp8(const void* x, void* q, float* scale, int scale_l
   if (K % 128 || x_ld % 8) return -10;
   const long long total = static_cast<long long>(M) * (K >> 3);
   quant_fp8_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (uint8_t*)q, scale, scale_ld, M, K, x_ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// x [M, K] bf16 -> q [M, K/2] packed e2m1, bs [M, K/16] e4m3 block scales; ts: device fp32 tensor scale (null = 1).
+extern "C" int ksana_quant_nvfp4(const void* x, int x_ld, void* q, int q_ld, void* bs, int bs_ld, const float* ts, int M,
+                                 int K, cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (K % 16 || x_ld % 8 || q_ld % 8) return -10;
+  const long long total = static_cast<long long>(M) * (K >> 4);
+  quant_nvfp4_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, x_ld, (uint8_t*)q, q_ld, (uint8_t*)bs, bs_ld,
+                                                           ts, M, K);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

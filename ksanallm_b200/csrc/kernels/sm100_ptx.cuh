@@ -241,6 +241,17 @@ __device__ __forceinline__ void mma_mxf8(uint32_t d_tmem, uint64_t adesc, uint64
 __host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t m, uint32_t n, uint32_t sf) {
   return (sf << 4) | (1u << 23) | ((n >> 3) << 17) | ((m >> 4) << 24) | (sf << 29);
 }
+// NVFP4: e2m1 x e2m1 with e4m3 scales per 16 elements, K = 64 per MMA, four scale bytes (one TMEM word) per row.
+__device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                                         uint32_t tsfa, uint32_t tsfb) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb) : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc_nvf4(uint32_t m, uint32_t n) {
+  return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);     // e2m1 operands, UE4M3 scales, K-major
+}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 }  // namespace ksana

@@ -117,7 +117,13 @@ class LLM:
         if weights == "random":
             source = RandomSource(seed=seed, on_device=dev_type == "cuda" and model_cfg.hidden_size >= 2048)
         elif weights == "checkpoint":
-            source = CheckpointSource(self.engine_cfg.model_dir, model_cfg.model_type)
+            import glob as _glob
+            ggufs = sorted(_glob.glob(os.path.join(self.engine_cfg.model_dir, "*.gguf")))
+            if ggufs and not _glob.glob(os.path.join(self.engine_cfg.model_dir, "*.safetensors")):
+                from .models.gguf import GGUFSource
+                source = GGUFSource(ggufs[0])
+            else:
+                source = CheckpointSource(self.engine_cfg.model_dir, model_cfg.model_type)
         else:
             source = weights
         kv_path = os.path.join(self.engine_cfg.model_dir or ".", "kv_cache_scales.json")

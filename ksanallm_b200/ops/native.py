@@ -21,6 +21,8 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 _SIGS = {
     "ksana_gemm_bf16": [vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_pair": [i32, vp, i32, vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
+    "ksana_gemm_nvfp4": [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+    "ksana_quant_nvfp4": [vp, i32, vp, i32, vp, i32, vp, i32, i32, vp],
     "ksana_gemm_mxfp8": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, vp,
                          vp],
     "ksana_gemm_fp8_block": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
@@ -243,6 +245,32 @@ def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, b
                                     _p(residual), residual.stride(0) if residual is not None else 0, M, N, K, bn,
                                     max_ctas, _p(err_flag(xq.device)), _st())
     _check(rc, "ksana_gemm_fp8_block")
+    return dst
+
+
+def quant_nvfp4(x, tensor_scale):
+    """bf16 [M, K] -> (packed e2m1 [M, K/2] uint8, e4m3 block scales [M, K/16], tensor_scale). K % 16 == 0.
+    ``tensor_scale``: fp32 scalar tensor on the device (calibrated or amax / (448 * 6))."""
+    M, K = x.shape
+    q = torch.empty(M, K // 2, dtype=torch.uint8, device=x.device)
+    bs = torch.empty(M, K // 16, dtype=torch.float8_e4m3fn, device=x.device)
+    _check(lib().ksana_quant_nvfp4(_p(x), x.stride(0), _p(q), q.stride(0), _p(bs), bs.stride(0), _p(tensor_scale), M, K,
+                                   _st()), "ksana_quant_nvfp4")
+    return q, bs, tensor_scale
+
+
+def gemm_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0):
+    """NVFP4 x NVFP4 GEMM (e2m1 values, e4m3 scales per 16 elements, fp32 tensor scales) on the block-scaled tensor
+    cores. aq [M, K/2], wq [N, K/2] packed bytes; K % 256 == 0."""
+    M, N, K = aq.shape[0], wq.shape[0], aq.shape[1] * 2
+    if out is None and out_f32 is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
+    dst = out if out_f32 is None else out_f32
+    rc = lib().ksana_gemm_nvfp4(_p(aq), aq.stride(0), _p(a_bs), a_bs.stride(0), _p(a_ts), _p(wq), wq.stride(0), _p(w_bs),
+                                w_bs.stride(0), _p(w_ts), _p(out) if out_f32 is None else None, _p(out_f32),
+                                dst.stride(0), _p(bias), _p(residual), residual.stride(0) if residual is not None else 0,
+                                M, N, K, bn, max_ctas, _p(err_flag(aq.device)), _st())
+    _check(rc, "ksana_gemm_nvfp4")
     return dst
 
 

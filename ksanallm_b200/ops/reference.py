@@ -288,3 +288,52 @@ def sample(logits, temperature, top_k, top_p, uniforms, num_logprobs=0):
         pick = int((cum[:keep] > u).nonzero()[0]) if bool((cum[:keep] > u).any()) else keep - 1
         tokens[b] = idx[pick]
     return tokens, lp_ids, lp_vals
+
+
+# ------------------------------------------------------------------------------------- NVFP4
+# e2m1 values in blocks of 16 along K, one e4m3 scale per block and one fp32 scale per tensor:
+#   x ~= e2m1 * e4m3_block_scale * tensor_scale.  Two values per byte, the even element in the low nibble.
+_E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def quant_nvfp4(x, tensor_scale=None):
+    """[M, K] -> (packed uint8 [M, K/2], block scales float8_e4m3fn [M, K/16], tensor scale fp32 scalar tensor).
+    K must be a multiple of 16. ``tensor_scale`` None: amax / (448 * 6), so that block scales use the e4m3 range."""
+    M, K = x.shape
+    xf = x.float()
+    if tensor_scale is None:
+        tensor_scale = (xf.abs().amax().clamp_min(1e-12) / (448.0 * 6.0)).reshape(())
+    tensor_scale = torch.as_tensor(tensor_scale, dtype=torch.float32, device=x.device).reshape(())
+    g = xf.reshape(M, K // 16, 16) / tensor_scale
+    bs = (g.abs().amax(dim=-1) / 6.0).clamp(max=448.0).to(torch.float8_e4m3fn)       # e4m3 rounding of amax / 6
+    bsf = bs.float().clamp_min(2.0 ** -9)
+    v = (g / bsf.unsqueeze(-1)).clamp(-6.0, 6.0)
+    grid = torch.tensor(_E2M1_VALUES, device=x.device)
+    # round to nearest e2m1 magnitude, ties to the even code (codes 0..7)
+    mag = v.abs()
+    mids = (grid[1:] + grid[:-1]) / 2
+    code = torch.bucketize(mag, mids, right=False)            # mag == midpoint -> lower code
+    tie = mag == mids[(code).clamp(max=6)]
+    up = tie & (code % 2 == 1) & (code < 7)
+    code = torch.where(up, code + 1, code)
+    code = (code | ((v < 0).to(code.dtype) << 3)).to(torch.uint8).reshape(M, K)
+    packed = code[:, 0::2] | (code[:, 1::2] << 4)
+    return packed.contiguous(), bs.contiguous(), tensor_scale
+
+
+def dequant_nvfp4(packed, block_scale, tensor_scale):
+    M, K2 = packed.shape
+    grid = torch.tensor(_E2M1_VALUES, device=packed.device)
+    lo, hi = packed & 0xF, packed >> 4
+    codes = torch.stack([lo, hi], dim=-1).reshape(M, K2 * 2).long()
+    val = grid[codes & 7] * torch.where((codes & 8) != 0, -1.0, 1.0)
+    return (val.reshape(M, -1, 16) * block_scale.float().unsqueeze(-1)).reshape(M, K2 * 2) * tensor_scale
+
+
+def gemm_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, bias=None, residual=None, out_dtype=torch.bfloat16):
+    y = dequant_nvfp4(aq, a_bs, a_ts) @ dequant_nvfp4(wq, w_bs, w_ts).t()
+    if bias is not None:
+        y = y + bias.float()
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(out_dtype)
