@@ -109,7 +109,7 @@ class LLM:
                            self.device, max_tokens=self.engine_cfg.batch_scheduler.max_step_tokens,
                            hidden=model_cfg.hidden_size) if tp > 1 else None
         quant = self.engine_cfg.quantization.weight_quant_method
-        quant = {"auto": None, "fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "nvfp4": "fp8_block"}[quant]
+        quant = {"auto": None, "fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "nvfp4": "nvfp4"}[quant]
         if model_cfg.fp8_checkpoint and quant is None:
             quant = "fp8_block"
         from .ops import reference as _ref

@@ -101,7 +101,7 @@ def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dt
     w13 = torch.cat(w13_parts, 0)
     w2 = torch.cat(w2_parts, 0)
     w13_s = w2_s = None
-    if quant == "fp8_block" and H % 128 == 0 and I % 128 == 0:
+    if quant in ("fp8_block", "nvfp4") and H % 128 == 0 and I % 128 == 0:     # grouped experts: FP8 blocks
         w13, w13_s = ref.quant_weight_fp8_block(w13)
         w2, w2_s = ref.quant_weight_fp8_block(w2)
     else:

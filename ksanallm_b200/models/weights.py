@@ -158,7 +158,10 @@ def _cols(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
 def _make_linear(w: torch.Tensor, bias, device, dtype, quant: Optional[str]) -> LinearWeight:
     w = w.to(device)
     b = bias.to(device=device, dtype=dtype) if bias is not None else None
-    if quant == "fp8_block" and w.shape[1] % 128 == 0:
+    if quant == "nvfp4" and w.shape[1] % 256 == 0:
+        lw = LinearWeight(w=w.float(), bias=b).quantize_nvfp4()
+        return lw
+    if quant in ("fp8_block", "nvfp4") and w.shape[1] % 128 == 0:
         wq, ws = ref.quant_weight_fp8_block(w)
         return LinearWeight(bias=b, wq=wq.contiguous(), ws=ws.contiguous())
     return LinearWeight(w=w.to(dtype).contiguous(), bias=b)

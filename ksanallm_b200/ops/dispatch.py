@@ -30,6 +30,8 @@ class LinearWeight:
     def __init__(self, w: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
                  wq: Optional[torch.Tensor] = None, ws: Optional[torch.Tensor] = None):
         self.w, self.bias, self.wq, self.ws = w, bias, wq, ws
+        # NVFP4 form: packed e2m1 [N, K/2], e4m3 scales per 16 elements [N, K/16], fp32 tensor scale
+        self.w4 = self.w4_bs = self.w4_ts = None
         # power-of-two block scales: the tensor cores can apply them (hardware block-scaled MMA)
         self.ue8m0 = ws is not None and ref.is_pow2(ws)
 
@@ -38,16 +40,40 @@ class LinearWeight:
         return self.wq is not None
 
     @property
+    def nvfp4(self) -> bool:
+        return self.w4 is not None
+
+    def _any(self) -> torch.Tensor:
+        return self.w4 if self.nvfp4 else (self.wq if self.fp8 else self.w)
+
+    @property
     def out_features(self) -> int:
-        return (self.wq if self.fp8 else self.w).shape[0]
+        return self._any().shape[0]
 
     @property
     def in_features(self) -> int:
-        return (self.wq if self.fp8 else self.w).shape[1]
+        return self.w4.shape[1] * 2 if self.nvfp4 else self._any().shape[1]
 
     @property
     def device(self):
-        return (self.wq if self.fp8 else self.w).device
+        return self._any().device
+
+    def without_bias(self) -> "LinearWeight":
+        """Shallow copy that shares the weight tensors and has no bias (row-parallel ranks other than the first)."""
+        if self.bias is None:
+            return self
+        if getattr(self, "_nb", None) is None:
+            import copy
+            self._nb = copy.copy(self)
+            self._nb.bias = None
+        return self._nb
+
+    def quantize_nvfp4(self) -> "LinearWeight":
+        """e2m1 weights with e4m3 scales per 16 input features (in_features must be a multiple of 256)."""
+        if not self.nvfp4 and not self.fp8:
+            self.w4, self.w4_bs, self.w4_ts = ref.quant_nvfp4(self.w)
+            self.w = None
+        return self
 
     def quantize_fp8_block(self) -> "LinearWeight":
         if not self.fp8:
@@ -57,10 +83,12 @@ class LinearWeight:
         return self
 
     def dense(self) -> torch.Tensor:
+        if self.nvfp4:
+            return ref.dequant_nvfp4(self.w4, self.w4_bs, self.w4_ts)
         return ref.dequant_weight_fp8_block(self.wq, self.ws) if self.fp8 else self.w
 
     def nbytes(self) -> int:
-        t = [x for x in (self.w, self.wq, self.ws, self.bias) if x is not None]
+        t = [x for x in (self.w, self.wq, self.ws, self.bias, self.w4, self.w4_bs) if x is not None]
         return sum(x.numel() * x.element_size() for x in t)
 
 
@@ -76,6 +104,21 @@ def quantize(x: torch.Tensor) -> QTensor:
 
 def linear(x, W: LinearWeight, residual=None, out=None, out_f32: bool = False):
     """y = x W^T (+bias) (+residual). ``x`` may be a QTensor when W is FP8. ``out`` may alias ``residual``."""
+    if W.nvfp4:
+        # activations are quantised to NVFP4 too (per-tensor scale from the tensor's own maximum, no host sync)
+        a_ts = (x.float().abs().amax() / (448.0 * 6.0)).clamp_min(1e-12).reshape(())
+        if x.is_cuda:
+            aq, a_bs, _ = native.quant_nvfp4(x, a_ts)
+            if out_f32:
+                o = torch.empty(x.shape[0], W.out_features, dtype=torch.float32, device=x.device)
+                return native.gemm_nvfp4(aq, a_bs, a_ts, W.w4, W.w4_bs, W.w4_ts, bias=W.bias, residual=residual, out_f32=o)
+            return native.gemm_nvfp4(aq, a_bs, a_ts, W.w4, W.w4_bs, W.w4_ts, out=out, bias=W.bias, residual=residual)
+        aq, a_bs, _ = ref.quant_nvfp4(x, a_ts)
+        y = ref.gemm_nvfp4(aq, a_bs, a_ts, W.w4, W.w4_bs, W.w4_ts, W.bias, residual, torch.float32 if out_f32 else x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
     if _is_cuda(x):
         if W.fp8:
             if not isinstance(x, QTensor):

