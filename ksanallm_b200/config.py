@@ -24,6 +24,7 @@ log = logging.getLogger("ksana_llm")
 class GlobalConfig:
     tensor_para_size: int = 1
     pipeline_para_size: int = 1
+    pipeline_micro_batches: int = 2      # micro-batches of one step in flight across the pipeline stages
     expert_para_size: int = 1
     attn_data_para_size: int = 1
     enable_lora_adapter: bool = False

@@ -1,7 +1,7 @@
 """Offline / embedded entry point: builds the model, the KV cache and the engine from a serving
 YAML (or explicit configs) and exposes ``generate``. One process per GPU; with ``WORLD_SIZE`` > 1
-(torchrun) the ranks form one tensor-parallel group, rank 0 schedules and the others follow the
-broadcast step plans (the reference runs one thread per GPU inside one process instead:
+(torchrun) the ranks form ``pipeline_para_size`` stages of tensor-parallel groups, rank 0 schedules and
+the others follow the broadcast step plans (the reference runs one thread per GPU inside one process instead:
 src/ksana_llm/runtime/worker.cpp:43-54).
 """
 from __future__ import annotations
@@ -23,13 +23,16 @@ def _dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
 
 
-def init_distributed(device_type: str):
-    """Process groups for the tensor-parallel run: a device group (NCCL / gloo) for collectives and a
-    CPU gloo group for step-plan broadcast. Rendezvous uses MASTER_ADDR / MASTER_PORT (127.0.0.1 on one node)."""
+def init_distributed(device_type: str, pp: int = 1):
+    """Process groups of the job: a device group (NCCL / gloo) for this rank's tensor-parallel collectives and a
+    CPU gloo group over all ranks for step-plan broadcast. With ``pp`` pipeline stages the ranks
+    ``[s*tp, (s+1)*tp)`` form stage ``s`` and get a tensor-parallel group of their own; hidden states travel
+    between stages point to point over the world group. Rendezvous uses MASTER_ADDR / MASTER_PORT (127.0.0.1 on
+    one node). Returns (rank, world, tensor-parallel group, control group, world device group)."""
     import torch.distributed as dist
     rank, world, local = _dist_env()
     if world == 1:
-        return 0, 1, None, None
+        return 0, 1, None, None, None
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29511")
     if not dist.is_initialized():
@@ -39,9 +42,18 @@ def init_distributed(device_type: str):
             dist.init_process_group(backend, rank=rank, world_size=world, device_id=torch.device("cuda", local))
         else:
             dist.init_process_group(backend, rank=rank, world_size=world)
-    dev_group = dist.group.WORLD
-    ctl_group = dist.new_group(backend="gloo") if device_type == "cuda" else dev_group
-    return rank, world, dev_group, ctl_group
+    world_group = dist.group.WORLD
+    dev_group = world_group
+    if pp > 1:
+        if world % pp:
+            raise ValueError(f"world size {world} is not a multiple of pipeline_para_size {pp}")
+        tp = world // pp
+        for stage in range(pp):                  # every rank creates every group (collective call)
+            g = dist.new_group(ranks=list(range(stage * tp, (stage + 1) * tp)))
+            if rank // tp == stage:
+                dev_group = g
+    ctl_group = dist.new_group(backend="gloo") if device_type == "cuda" else world_group
+    return rank, world, dev_group, ctl_group, world_group
 
 
 def kv_dtype_from(cfg: EngineConfig, default):
@@ -94,19 +106,25 @@ class LLM:
             model_cfg = load_model_config(self.engine_cfg.model_dir)
         self.model_cfg = model_cfg
         dev_type = "cuda" if (device is None and torch.cuda.is_available()) or (device and "cuda" in str(device)) else "cpu"
-        self.rank, self.world, dev_group, ctl_group = init_distributed(dev_type)
+        pp = max(1, self.engine_cfg.global_.pipeline_para_size) if _dist_env()[1] > 1 else 1
+        self.rank, self.world, dev_group, ctl_group, world_group = init_distributed(dev_type, pp)
         local = _dist_env()[2]
         self.device = torch.device("cuda", local) if dev_type == "cuda" else torch.device("cpu")
         if dev_type == "cuda":
             torch.cuda.set_device(self.device)
-        tp = self.world
+        tp = self.world // pp
+        self.pp_size, self.tp_size = pp, tp
+        self.pp_rank, self.tp_rank = self.rank // tp, self.rank % tp
         check_tp(model_cfg, tp)
         ep = self.engine_cfg.global_.expert_para_size
         if ep not in (1, tp):
             raise ValueError(f"expert_para_size {ep} must be 1 or equal to the tensor-parallel size {tp}")
         model_cfg.expert_para_size = ep
-        self.comm = TPComm(dev_group, self.rank, tp, self.engine_cfg.global_.comm_backend if dev_type == "cuda" else "nccl",
-                           self.device, max_tokens=self.engine_cfg.batch_scheduler.max_step_tokens,
+        # the peer-memory kernels address ranks of the world group: with several stages the tensor-parallel
+        # groups are sub-groups and use the library collectives
+        backend = self.engine_cfg.global_.comm_backend if (dev_type == "cuda" and pp == 1) else "nccl"
+        self.comm = TPComm(dev_group, self.tp_rank, tp, backend, self.device,
+                           max_tokens=self.engine_cfg.batch_scheduler.max_step_tokens,
                            hidden=model_cfg.hidden_size) if tp > 1 else None
         quant = self.engine_cfg.quantization.weight_quant_method
         quant = {"auto": None, "fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "nvfp4": "nvfp4"}[quant]
@@ -130,8 +148,12 @@ class LLM:
         if self.engine_cfg.quantization.kv_cache_dtype != "auto" and os.path.exists(kv_path):
             model_cfg.kv_scales = load_kv_scales(kv_path, model_cfg.num_layers)
         mp = max_positions or min(model_cfg.max_token_len, max(self.engine_cfg.batch_scheduler.max_token_len, 16))
-        self.model = build_model(model_cfg, source, self.rank, tp, self.comm, self.device, dtype, quant,
-                                 max_positions=mp)
+        layer_range = None
+        if pp > 1:
+            from .parallel.pipeline import stage_layers
+            layer_range = stage_layers(model_cfg.num_layers, pp, self.pp_rank)
+        self.model = build_model(model_cfg, source, self.tp_rank, tp, self.comm, self.device, dtype, quant,
+                                 layer_range=layer_range, max_positions=mp)
         kv_dtype = kv_dtype_from(self.engine_cfg, dtype)
         bt = self.engine_cfg.block_manager.block_token_num
         probe = self.model.allocate_kv_cache(1, bt, kv_dtype)
@@ -144,8 +166,13 @@ class LLM:
             t = torch.tensor([nblocks, nhost], dtype=torch.int64)
             dist.all_reduce(t, op=dist.ReduceOp.MIN, group=ctl_group)
             nblocks, nhost = int(t[0]), int(t[1])
+        pipeline = None
+        if pp > 1:
+            from .parallel.pipeline import PipelineRunner
+            pipeline = PipelineRunner(self.model, self.pp_rank, pp, self.tp_rank, tp, world_group,
+                                      micro_batches=self.engine_cfg.global_.pipeline_micro_batches)
         self.engine = LLMEngine(self.model, model_cfg, self.engine_cfg, nblocks, nhost, tokenizer, kv_dtype,
-                                self.rank, self.world, ctl_group)
+                                self.rank, self.world, ctl_group, pipeline=pipeline)
         self.tokenizer = tokenizer
 
     # ------------------------------------------------------------------ API

@@ -38,6 +38,7 @@ class StepInput:
     num_tokens: int = 0
     num_multi_tokens: int = 0
     max_q_len: int = 0
+    max_kv_len: int = 0                  # host-side upper bound of kv_lens (split heuristics, no device sync)
     logits_rows: Optional[torch.Tensor] = None
     mrope_positions: Optional[torch.Tensor] = None      # [3, T]
     refit_positions: Optional[torch.Tensor] = None      # rows to overwrite with plugin embeddings
@@ -241,6 +242,14 @@ class CommonModel:
                 r = torch.stack([x0 * cos - x1 * sin, x1 * cos + x0 * sin], dim=-1).flatten(-2)
             k[..., : self.rot_dim] = r
             self.kv_cache[int(dst), :, 0] = k.to(self.kv_cache.dtype)
+
+    def forward_layers(self, step: StepInput, hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """This stage's layers only (embedding on the first stage): the hidden states to hand to the next
+        pipeline stage, or to ``lm_head_forward`` on the last one."""
+        h = self.embed_tokens(step) if self.is_first_stage else hidden_in
+        for i, lw in enumerate(self.layers):
+            h = self.layer_forward(self.layer_lo + i, lw, h, step)
+        return h
 
     def forward(self, step: StepInput, hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs this pipeline stage. The last stage returns fp32 logits [rows, vocab]; earlier stages return

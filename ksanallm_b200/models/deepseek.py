@@ -11,8 +11,9 @@ Absorbed attention (per head h):   q_lat[h] = q_nope[h] @ W_uk[h]            (12
                                    o_lat[h] = softmax(s) @ c_kv                (512)
                                    o[h] = o_lat[h] @ W_uv[h]^T                 (512 -> 128)
 so attention is multi-query over a single 576/512-wide latent "head" shared by all query heads.
-The projections run on the tcgen05 GEMMs; the latent attention core currently uses batched PyTorch
-matmuls over the gathered latent rows of each sequence (a dedicated MLA kernel is future work).
+The projections run on the tcgen05 GEMMs. On a GPU with the DeepSeek-V2/V3 dimensions (latent 512, rotary 64)
+the attention core is the tcgen05 latent-attention kernel (csrc/kernels/mla_attention.cu); other dimensions
+and the CPU use batched PyTorch matmuls over the gathered latent rows of each sequence.
 """
 from __future__ import annotations
 
@@ -74,8 +75,10 @@ class DeepseekModel(CommonModel):
             q = ops.linear(qa, mw.q_b)
         else:
             q = ops.linear(x, mw.q_b)
-        q = q.view(T, Hq, self.nope + self.rope)
         kv = ops.linear(x, mw.kv_a)                               # [T, lora + rope]
+        if q.is_cuda and self._mla_native_ok(q):
+            return self._attention_native(li, mw, q, kv, step)
+        q = q.view(T, Hq, self.nope + self.rope)
         c_kv = ops.norm(kv[:, : self.lora].contiguous(), mw.kv_a_norm, cfg.rms_norm_eps)
         k_pe = kv[:, self.lora:].reshape(T, 1, self.rope)
         q_pe = q[..., self.nope:]
@@ -107,6 +110,33 @@ class DeepseekModel(CommonModel):
             out_lat[q0:q1] = torch.einsum("hqk,kl->qhl", torch.softmax(sc, -1), ckv)
         out = torch.einsum("thl,hvl->thv", out_lat, mw.w_uv.float())                       # [T, Hq, v]
         return out.reshape(T, Hq * self.vdim).to(q.dtype)
+
+
+    # ------------------------------------------------------------------ tcgen05 latent attention (GPU)
+    def _mla_native_ok(self, q) -> bool:
+        Hq = self.Hq
+        return (self.lora == 512 and self.rope == 64 and q.dtype == torch.bfloat16 and Hq <= 128 and Hq & (Hq - 1) == 0
+                and self.kv_cache is not None and self.kv_cache.dtype == torch.bfloat16)
+
+    def _attention_native(self, li, mw, q, kv, step):
+        """Fused latent norm + rotations + cache append, q_nope W_uk as a batched GEMM into the packed query rows,
+        the tcgen05 latent-attention kernel (prefill rows and decode rows in one launch), then W_uv."""
+        from ..ops import native
+        T, Hq = q.shape[0], self.Hq
+        cache = self.kv_cache[:, li - self.layer_lo]                # [blocks, bt, 576]
+        qfull = torch.empty(T, Hq, self.lora + self.rope, dtype=q.dtype, device=q.device)
+        native.mla_rope_append(q, self.nope, kv, mw.kv_a_norm, self.cfg.rms_norm_eps, step.positions, step.slots,
+                               self.cos_sin, qfull, cache, cache.stride(0), self.block_tokens, Hq)
+        q_nope = q.view(T, Hq, self.nope + self.rope)[..., : self.nope].transpose(0, 1)          # [Hq, T, nope]
+        qfull[..., : self.lora].copy_(torch.bmm(q_nope, mw.w_uk).transpose(0, 1))
+        o_lat = torch.empty(T, Hq, self.lora, dtype=q.dtype, device=q.device)
+        B = step.num_multi + step.num_single
+        nsplit = native.mla_splits(B, step.max_q_len, step.max_kv_len) if step.num_multi == 0 else 1
+        if not native.mla_attention(qfull, o_lat, cache, cache.stride(0), self.block_tokens, step.block_table, step.cu_q,
+                                    step.kv_lens, B, max(step.max_q_len, 1), Hq, self.scale, nsplit):
+            raise RuntimeError("latent-attention kernel rejected a configuration that _mla_native_ok accepted")
+        o = torch.bmm(o_lat.transpose(0, 1), mw.w_uv.transpose(1, 2))                            # [Hq, T, v]
+        return o.transpose(0, 1).reshape(T, Hq * self.vdim)
 
 
 def build_deepseek(cfg: ModelConfig, source, tp_rank, tp_size, comm, device, dtype, quant, layer_range, max_positions):

@@ -59,6 +59,8 @@ _SIGS = {
                             f32, f32, i64, vp, vp],
     "ksana_paged_decode": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, f32, f32,
                            i32, vp, vp, i64, vp, vp],
+    "ksana_mla_attention": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, f32, i64, i32, vp, vp, vp, vp],
+    "ksana_mla_rope_append": [vp, i64, i32, vp, i64, vp, f32, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
     "ksana_sample": [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, vp],
     "ksana_repetition_penalty": [vp, i64, vp, vp, vp, vp, i32, i32, vp],
     "ksana_ban_tokens": [vp, i64, vp, vp, vp, i32, i32, vp],
@@ -412,6 +414,45 @@ def paged_decode(q, q_stride, out, cache_layer, block_stride, block_tokens, bloc
                                   float(scale), int(fp8), float(k_scale), float(v_scale), num_splits, _p(part_o),
                                   _p(part_ml), _cache_rows(cache_layer, block_stride, D), _p(err_flag(q.device)), _st())
     _check(rc, "ksana_paged_decode")
+
+
+def mla_rope_append(q, nope, kv, norm_w, eps, positions, slots, cos_sin, qfull, cache_layer, block_stride, block_tokens, G):
+    """Latent RMSNorm + rotary key rotation + append to the paged latent cache, and q_pe rotation into ``qfull``
+    ([T, G, 576]; its first 512 columns are filled by the caller). q: [T, G*(nope+64)], kv: [T, 576]."""
+    T = q.shape[0]
+    rc = lib().ksana_mla_rope_append(_p(q), q.stride(0), nope, _p(kv), kv.stride(0), _p(norm_w), float(eps), _p(positions),
+                                     _p(slots), _p(cos_sin), _p(qfull), _p(cache_layer), block_stride, block_tokens, T, G,
+                                     _st())
+    _check(rc, "ksana_mla_rope_append")
+
+
+def mla_splits(num_seqs: int, max_q_len: int, max_kv: int, sms: int = 148) -> int:
+    """KV splits for the latent-attention kernel: only pure decode steps split, until about two waves of CTAs
+    (two output halves per sequence) exist or a split would hold fewer than 8 tiles of 32 tokens."""
+    if max_q_len != 1 or num_seqs <= 0:
+        return 1
+    want = (2 * sms + 2 * num_seqs - 1) // (2 * num_seqs)
+    most = max(1, (max_kv + 255) // 256)
+    return max(1, min(want, most, 32))
+
+
+def mla_attention(qfull, out, cache_layer, block_stride, block_tokens, block_table, cu_q, kv_lens, B, max_q_len, G, scale,
+                  nsplit=1) -> bool:
+    """Absorbed multi-head latent attention on tcgen05 (see csrc/kernels/mla_attention.cu). qfull [T, G, 576],
+    out [T, G, 512]. Returns False when the kernel does not cover the configuration."""
+    T = qfull.shape[0]
+    po = pml = None
+    if nsplit > 1:
+        po = torch.empty(nsplit * T * G * 512, dtype=torch.float32, device=qfull.device)
+        pml = torch.empty(nsplit * T * G * 2, dtype=torch.float32, device=qfull.device)
+    rc = lib().ksana_mla_attention(_p(qfull), T, _p(out), out.stride(0), _p(cache_layer), block_stride, block_tokens,
+                                   _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_lens), B, max_q_len, G,
+                                   float(scale), _cache_rows(cache_layer, block_stride, 576), nsplit, _p(po), _p(pml),
+                                   _p(err_flag(qfull.device)), _st())
+    if rc == -100:
+        return False
+    _check(rc, "ksana_mla_attention")
+    return True
 
 
 def copy_blocks(cache, pairs, block_bytes):

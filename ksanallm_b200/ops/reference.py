@@ -337,3 +337,24 @@ def gemm_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, bias=None, residual=None, out_dty
     if residual is not None:
         y = y + residual.float()
     return y.to(out_dtype)
+
+
+def mla_attention(qfull, cache_layer, block_table, cu_q, kv_lens, scale, lora=512):
+    """Absorbed multi-head latent attention, plain fp32 statement. qfull [T, G, lora+rope] (q_lat | q_pe),
+    cache_layer [blocks, block_tokens, lora+rope] (c_kv | k_pe). Returns [T, G, lora] fp32."""
+    T, G, _ = qfull.shape
+    bt = cache_layer.shape[1]
+    out = torch.zeros(T, G, lora, dtype=torch.float32, device=qfull.device)
+    cu, kvl = cu_q.tolist(), kv_lens.tolist()
+    for s in range(len(kvl)):
+        q0, q1, kl = cu[s], cu[s + 1], kvl[s]
+        if q1 == q0:
+            continue
+        nblk = (kl + bt - 1) // bt
+        rows = cache_layer[block_table[s, :nblk].long()].reshape(nblk * bt, -1)[:kl].float()
+        sc = torch.einsum("qhd,kd->hqk", qfull[q0:q1].float(), rows) * scale
+        qpos = torch.arange(kl - (q1 - q0), kl, device=qfull.device).unsqueeze(1)
+        kpos = torch.arange(kl, device=qfull.device).unsqueeze(0)
+        sc = sc.masked_fill(kpos > qpos, float("-inf"))
+        out[q0:q1] = torch.einsum("hqk,kl->qhl", torch.softmax(sc, -1), rows[:, :lora])
+    return out

@@ -83,6 +83,7 @@ class ModelRunner:
                                           pin_memory=self.cuda)
         self._pinned = None
         self._pinned_cap = 0
+        self.pipeline = None             # parallel.pipeline.PipelineRunner when the job has several stages
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -159,6 +160,7 @@ class ModelRunner:
         rows = take(nsamp)
         step = StepInput(input_ids, positions, slots, cu_q, kv_lens, table, plan.num_multi, plan.num_single, T,
                          plan.num_multi_tokens, plan.max_q_len, logits_rows=rows)
+        step.max_kv_len = int(np.max(plan.kv_lens)) if nseq else 0
         if plan.num_single:
             max_kv = int(plan.kv_lens[plan.num_multi:].max())
             step.decode_splits = ops.decode_splits(plan.num_single, self.model.Hkv, max_kv)
@@ -173,7 +175,7 @@ class ModelRunner:
     def enable_graphs(self, max_batch: int, max_token_len: int):
         """Whole-model CUDA graphs for pure-decode steps, one per padded batch size (the reference captures
         per-layer graphs for batch sizes 1..3 only: src/ksana_llm/runtime/cuda_graph_runner.cpp:11-30)."""
-        if not self.cuda:
+        if not self.cuda or self.pipeline is not None:
             return
         self.graphs = {}
         self.graph_max_batch = max_batch
@@ -200,6 +202,7 @@ class ModelRunner:
         cu_q = torch.arange(bs + 1, dtype=torch.int32, device=self.device)
         step = StepInput(ids, pos, slots, cu_q, kvl, table, 0, bs, bs, 0, 1, logits_rows=None)
         step.decode_splits = ops.decode_splits(bs, self.model.Hkv, self.graph_max_kv)
+        step.max_kv_len = self.graph_max_kv
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -248,12 +251,14 @@ class ModelRunner:
             if out is not None:
                 return out
         step = self.build_step(plan, extra)
+        if self.pipeline is not None:
+            return self.pipeline.forward(step, plan)
         return self.model.forward(step)
 
 
 class LLMEngine:
     def __init__(self, model, model_cfg: ModelConfig, cfg: EngineConfig, num_blocks: int, num_host_blocks: int = 0,
-                 tokenizer=None, kv_dtype=None, rank: int = 0, world_size: int = 1, control_group=None):
+                 tokenizer=None, kv_dtype=None, rank: int = 0, world_size: int = 1, control_group=None, pipeline=None):
         self.model, self.model_cfg, self.cfg = model, model_cfg, cfg
         self.tokenizer = tokenizer
         self.rank, self.world_size, self.control_group = rank, world_size, control_group
@@ -273,6 +278,7 @@ class LLMEngine:
                              f"{sc.max_token_len}")
         self.scheduler = ne.Scheduler(sc, num_blocks, num_host_blocks) if rank == 0 else None
         self.runner = ModelRunner(model, sc.block_token_num, num_blocks, num_host_blocks, kv_dtype)
+        self.runner.pipeline = pipeline
         if cfg.global_.enable_cuda_graph:
             self.runner.enable_graphs(bs.max_batch_size, sc.max_token_len)
         self.sampler = Sampler(model.device, model_cfg.vocab_size)
