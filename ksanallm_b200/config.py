@@ -69,7 +69,7 @@ class BlockManagerConfig:
 class QuantConfig:
     gptq_backend: str = "cutlass"
     kv_cache_dtype: str = "auto"              # auto | fp8_e5m2 | fp8_e4m3
-    weight_quant_method: str = "auto"         # auto | fp8_e4m3 | fp8_block | nvfp4
+    weight_quant_method: str = "auto"         # auto | fp8_e4m3 | fp8_block | nvfp4 | w4a16 (gptq / awq select w4a16)
     # scales of weights quantised at load time: "ue8m0" = powers of two (applied by the tensor cores through the
     # block-scaled MMA), "fp32" = amax / 448 exactly (served by the register-promotion GEMM)
     fp8_scale_mode: str = "ue8m0"
@@ -155,7 +155,7 @@ def load_yaml_config(path_or_dict) -> EngineConfig:
         raise ValueError(f"unsupported weight.scale_mode {cfg.quantization.fp8_scale_mode}")
     if cfg.quantization.kv_cache_dtype not in ("auto", "fp8_e5m2", "fp8_e4m3"):
         raise ValueError(f"unsupported kv_cache.dtype {cfg.quantization.kv_cache_dtype}")
-    if cfg.quantization.weight_quant_method not in ("auto", "fp8_e4m3", "fp8_block", "nvfp4"):
+    if cfg.quantization.weight_quant_method not in ("auto", "fp8_e4m3", "fp8_block", "nvfp4", "w4a16", "gptq", "awq"):
         raise ValueError(f"unsupported weight.quant_method {cfg.quantization.weight_quant_method}")
     prof = setting.get("profiler", {}) or {}
     for k in ("trace_export_url", "metrics_export_url"):

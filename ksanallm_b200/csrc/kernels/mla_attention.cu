@@ -142,20 +142,39 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 #pragma unroll
       for (int pn = 0; pn < kMlaPanels; ++pn) tma_load_3d(q_s + pn * kMlaQPanelBytes, &q_map, q_full, pn * 64, 0, tok0);
       const int bt = p.block_tokens, br = p.box_rows;
+      const int boxes = kMlaTok / br;                       // at most 4 (8-token blocks)
+      // block-table entries of a tile are fetched one tile ahead, so that their global-memory latency is not part
+      // of the chain "buffer freed -> TMA issued"
+      int blk[4], blk_next[4];
+      auto fetch = [&](int j, int (&dst)[4]) {
+        const int t0 = (tile_lo + j) * kMlaTok;
+#pragma unroll
+        for (int bx = 0; bx < 4; ++bx) {
+          const int t = t0 + bx * br;
+          dst[bx] = (bx < boxes && t < kv_len) ? __ldg(table + t / bt) : 0;
+        }
+      };
+      fetch(0, blk_next);
       bool ok = true;
       for (int j = 0; j < ntiles && ok; ++j) {
         const int b = j & 1;
         const int t0 = (tile_lo + j) * kMlaTok;
-        const int nbox = min(kMlaTok / br, (kv_len - t0 + br - 1) / br);
+        const int nbox = min(boxes, (kv_len - t0 + br - 1) / br);
+#pragma unroll
+        for (int bx = 0; bx < 4; ++bx) blk[bx] = blk_next[bx];
+        if (j + 1 < ntiles) fetch(j + 1, blk_next);
         if (!mbar_wait(kv_empty + b, ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
         mbar_expect_tx(kv_full + b, static_cast<uint32_t>(nbox) * br * 128 * kMlaPanels);
         uint8_t* dst = kv_s + b * kMlaKvBytes;
-        for (int bx = 0; bx < nbox; ++bx) {
-          const int t = t0 + bx * br;
-          const long long r0 = static_cast<long long>(table[t / bt]) * p.rows_per_block + (t % bt);
 #pragma unroll
-          for (int pn = 0; pn < kMlaPanels; ++pn)
-            tma_load_2d(dst + pn * kMlaKvPanelBytes + bx * br * 128, &kv_map, kv_full + b, pn * 64, static_cast<int>(r0));
+        for (int bx = 0; bx < 4; ++bx) {
+          if (bx < nbox) {
+            const int t = t0 + bx * br;
+            const long long r0 = static_cast<long long>(blk[bx]) * p.rows_per_block + (t % bt);
+#pragma unroll
+            for (int pn = 0; pn < kMlaPanels; ++pn)
+              tma_load_2d(dst + pn * kMlaKvPanelBytes + bx * br * 128, &kv_map, kv_full + b, pn * 64, static_cast<int>(r0));
+          }
         }
       }
     }
@@ -166,36 +185,50 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       constexpr uint32_t idesc_qk = make_idesc(128, kMlaTok, 1, 1);
       constexpr uint32_t idesc_pv = make_idesc(128, 256, 1, 1) | (1u << 16);     // B (= V) is MN-major
       bool ok = mbar_wait(q_full, 0, abort_flag);
-      auto issue_s = [&](int j) -> bool {
-        const int b = j & 1;
-        if (!mbar_wait(kv_full + b, (j >> 1) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t qb = smem_u32(q_s), kb = smem_u32(kv_s + b * kMlaKvBytes);
+      const uint32_t qb = smem_u32(q_s);
+      // S of tile j+1 may be issued ahead of P V of tile j (it then overlaps the softmax of tile j), but whichever
+      // of the two becomes ready first goes first: issuing P V as soon as P is ready frees the tile's buffer
+      // early, which is what gives the next TMA load its lead time.
+      int s_next = 0, pv_next = 0;         // next tile whose S / P V has not been issued
+      uint32_t idle = 0;
+      while (ok && pv_next < ntiles) {
+        bool progress = false;
+        if (pv_next < s_next && mbar_try_wait(p_full + (pv_next & 1), (pv_next >> 1) & 1)) {
+          const int j = pv_next, bb = j & 1;
+          tc_fence_after();
+          const uint32_t vb = smem_u32(kv_s + bb * kMlaKvBytes) + half * 4 * kMlaKvPanelBytes;
 #pragma unroll
-        for (int k = 0; k < 4 * kMlaPanels; ++k) {
-          const uint64_t adesc = make_smem_desc_sw128(qb + (k >> 2) * kMlaQPanelBytes) + 2 * (k & 3);
-          const uint64_t bdesc = make_smem_desc_sw128(kb + (k >> 2) * kMlaKvPanelBytes) + 2 * (k & 3);
-          mma_f16(tmem_s + 32 * b, adesc, bdesc, idesc_qk, k != 0);
-        }
-        tc_commit(s_full + b);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int b = j & 1;
-        if (j + 1 < ntiles && !issue_s(j + 1)) { ok = false; break; }
-        if (!mbar_wait(p_full + b, (j >> 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t vb = smem_u32(kv_s + b * kMlaKvBytes) + half * 4 * kMlaKvPanelBytes;
+          for (int k = 0; k < kMlaTok / 16; ++k) {
+            // 16 tokens per MMA: 8 TMEM columns of P (two bf16 each), 16 rows (2 KB per panel) of the tile
+            const uint64_t bdesc = make_smem_desc_mn_sw128(vb + k * 2048, kMlaKvPanelBytes);
+            mma_f16_ts(tmem_o, tmem_s + 32 * bb + 8 * k, bdesc, idesc_pv, (j | k) != 0);
+          }
+          tc_commit(kv_empty + bb);
+          tc_commit(pv_done);
+          if (j == ntiles - 1) tc_commit(o_full);
+          ++pv_next;
+          progress = true;
+        } else if (s_next < ntiles && s_next <= pv_next + 1 && mbar_try_wait(kv_full + (s_next & 1), (s_next >> 1) & 1)) {
+          // (s_next <= pv_next + 1: the S/P buffer of tile s_next was last read by P V of tile s_next - 2)
+          const int bb = s_next & 1;
+          tc_fence_after();
+          const uint32_t kb = smem_u32(kv_s + bb * kMlaKvBytes);
 #pragma unroll
-        for (int k = 0; k < kMlaTok / 16; ++k) {
-          // 16 tokens per MMA: 8 TMEM columns of P (two bf16 each), 16 rows (2 KB per panel) of the tile
-          const uint64_t bdesc = make_smem_desc_mn_sw128(vb + k * 2048, kMlaKvPanelBytes);
-          mma_f16_ts(tmem_o, tmem_s + 32 * b + 8 * k, bdesc, idesc_pv, (j | k) != 0);
+          for (int k = 0; k < 4 * kMlaPanels; ++k) {
+            const uint64_t adesc = make_smem_desc_sw128(qb + (k >> 2) * kMlaQPanelBytes) + 2 * (k & 3);
+            const uint64_t bdesc = make_smem_desc_sw128(kb + (k >> 2) * kMlaKvPanelBytes) + 2 * (k & 3);
+            mma_f16(tmem_s + 32 * bb, adesc, bdesc, idesc_qk, k != 0);
+          }
+          tc_commit(s_full + bb);
+          ++s_next;
+          progress = true;
         }
-        tc_commit(kv_empty + b);
-        tc_commit(pv_done);
-        if (j == ntiles - 1) tc_commit(o_full);
+        if (progress) {
+          idle = 0;
+        } else if (++idle >= kWaitPolls || ((idle & 63u) == 63u && *abort_flag)) {
+          *abort_flag = 1;
+          ok = false;
+        }
       }
     }
     __syncwarp();

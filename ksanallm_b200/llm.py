@@ -127,9 +127,14 @@ class LLM:
                            max_tokens=self.engine_cfg.batch_scheduler.max_step_tokens,
                            hidden=model_cfg.hidden_size) if tp > 1 else None
         quant = self.engine_cfg.quantization.weight_quant_method
-        quant = {"auto": None, "fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "nvfp4": "nvfp4"}[quant]
+        quant = {"auto": None, "fp8_e4m3": "fp8_block", "fp8_block": "fp8_block", "nvfp4": "nvfp4", "w4a16": "w4a16",
+                 "gptq": "w4a16", "awq": "w4a16"}[quant]
         if model_cfg.fp8_checkpoint and quant is None:
             quant = "fp8_block"
+        if model_cfg.quant_method in ("gptq", "awq") and quant is None:
+            quant = "w4a16"                  # 4-bit checkpoints stay 4-bit unless another format is asked for
+        if quant == "w4a16" and model_cfg.quant_group_size > 0:
+            quant = f"w4a16:{model_cfg.quant_group_size}"
         from .ops import reference as _ref
         _ref.WEIGHT_SCALE_POW2 = self.engine_cfg.quantization.fp8_scale_mode != "fp32"
         if weights == "random":

@@ -267,8 +267,7 @@ class CommonModel:
     def _tp_fused_ok(self, h) -> bool:
         symm = getattr(self.comm, "symm", None) if self.comm is not None else None
         return (symm is not None and h.is_cuda and not self.cfg.post_norm and self.is_last_stage
-                and all(l.moe is None for l in self.layers) and h.shape[0] <= symm.max_tokens
-                and h.shape[1] == symm.hidden)
+                and self.is_first_stage and h.shape[0] <= symm.max_tokens and h.shape[1] == symm.hidden)
 
     def _forward_tp_fused(self, h0: torch.Tensor, step: StepInput) -> torch.Tensor:
         """Row-parallel GEMMs push their partial tiles into peer memory from the epilogue; one kernel then
@@ -290,15 +289,23 @@ class CommonModel:
         for i, lw in enumerate(self.layers):
             a = self.attention(self.layer_lo + i, lw, x, step)
             h, x = symm.row_parallel_norm(a, lw.o_proj, h, lw.post_norm, lw.post_norm_bias, cfg.rms_norm_eps, ln,
-                                          quant_for=lw.gate_up)
-            gu = ops.linear(x, lw.gate_up)
-            act = ops.act_mul(gu, cfg.activation, cfg.gated_mlp, quant_for=lw.down)
+                                          quant_for=lw.gate_up if lw.moe is None else None)
             if i + 1 < n:
                 nw, nb, nq = self.layers[i + 1].input_norm, self.layers[i + 1].input_norm_bias, self.layers[i + 1].qkv
             else:
                 nw, nb, nq = self.final_norm, self.final_norm_bias, None
+            last_h = step.want_hidden and i + 1 == n
+            if lw.moe is not None:
+                # expert (or expert-slice) outputs of this rank are combined into the peer-visible slot; the
+                # cross-rank sum, the residual add and the next norm are the same reduce kernel as for a GEMM
+                from .moe import moe_partial
+                h, x = symm.partial_norm(lambda part, _m=lw.moe, _x=x: moe_partial(self, _m, _x, into=part), T, h, nw, nb,
+                                         cfg.rms_norm_eps, ln, quant_for=nq, gather_h=last_h)
+                continue
+            gu = ops.linear(x, lw.gate_up)
+            act = ops.act_mul(gu, cfg.activation, cfg.gated_mlp, quant_for=lw.down)
             h, x = symm.row_parallel_norm(act, lw.down, h, nw, nb, cfg.rms_norm_eps, ln, quant_for=nq,
-                                          gather_h=step.want_hidden and i + 1 == n)
+                                          gather_h=last_h)
         if step.want_hidden:
             self.step_hidden, self.step_normed = h, x
         hn = ops.gather_rows(x, step.logits_rows) if step.logits_rows is not None else x

@@ -144,6 +144,16 @@ def route_reference(logits, cfg: ModelConfig, bias=None):
 
 def moe_forward(model, mw: MoEWeights, x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
     """h += MoE(x) (reduced over the TP group). ``x`` is the normalised hidden state [T, H] (bf16)."""
+    out = moe_partial(model, mw, x)
+    if model.tp_size > 1:
+        out = model.comm.all_reduce(out)
+    return ops.add(h, out)
+
+
+def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """This rank's share of MoE(x): the weighted outputs of the experts (or expert slices) it holds plus its slice
+    of the shared expert, before any reduction over ranks. ``into`` ([T, H], e.g. a peer-visible buffer that a
+    reduce kernel pulls from) receives the result when given."""
     cfg = model.cfg
     T, H = x.shape
     K, E = cfg.num_experts_per_tok, mw.num_experts
@@ -166,7 +176,7 @@ def moe_forward(model, mw: MoEWeights, x: torch.Tensor, h: torch.Tensor) -> torc
             g = native.gemm_grouped(perm, mw.w13, tile_expert, n_local, 2 * mw.inter)
             a = native.act_mul(g, cfg.activation, True)
             y = native.gemm_grouped(a, mw.w2, tile_expert, n_local, H)
-        out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+        out = into if into is not None else torch.empty(T, H, dtype=x.dtype, device=x.device)
         have_shared = mw.shared_gate_up is not None
         if have_shared:
             sg = ops.linear(x, mw.shared_gate_up)
@@ -174,8 +184,9 @@ def moe_forward(model, mw: MoEWeights, x: torch.Tensor, h: torch.Tensor) -> torc
             ops.linear(sa, mw.shared_down, out=out)
             if mw.shared_gate is not None:
                 gate = torch.sigmoid(x.float() @ mw.shared_gate.float().t())
-                out = (out.float() * gate).to(x.dtype)
+                out.copy_(out.float() * gate)
         native.moe_combine(y, dst_row, w, out, K, accumulate=have_shared)
+        return out
     else:
         logits = x.float() @ mw.router.float().t()
         ids, w = route_reference(logits, cfg, mw.router_bias)
@@ -200,6 +211,7 @@ def moe_forward(model, mw: MoEWeights, x: torch.Tensor, h: torch.Tensor) -> torc
                 so = so * torch.sigmoid(x.float() @ mw.shared_gate.float().t())
             out = out + so
         out = out.to(x.dtype)
-    if model.tp_size > 1:
-        out = model.comm.all_reduce(out)
-    return ops.add(h, out)
+    if into is not None:
+        into.copy_(out)
+        return into
+    return out

@@ -74,7 +74,25 @@ def apply_weight_map(name: str, rules: List[tuple]) -> str:
     return name
 
 
-class CheckpointSource:
+class _PackedW4Mixin:
+    """``<layer>.weight`` of a GPTQ / AWQ layer (stored as qweight / qzeros / scales [/ g_idx]) is served as its exact
+    dense expansion; see models/quant_w4.py."""
+
+    def _packed(self, name: str) -> Optional[str]:
+        if name.endswith(".weight"):
+            base = name[: -len("weight")]
+            if self._has_raw(base + "qweight") and self._has_raw(base + "scales"):
+                return base
+        return None
+
+    def _dense_from_packed(self, base: str) -> torch.Tensor:
+        from .quant_w4 import unpack_auto
+        g_idx = self._get_raw(base + "g_idx") if self._has_raw(base + "g_idx") else None
+        return unpack_auto(self._get_raw(base + "qweight"), self._get_raw(base + "qzeros"), self._get_raw(base + "scales"),
+                           g_idx)
+
+
+class CheckpointSource(_PackedW4Mixin):
     """Tensors of a Hugging Face checkpoint directory (``*.safetensors`` preferred, then ``*.bin`` /
     ``*.pt``), renamed to canonical names through the optional regex weight map."""
 
@@ -108,12 +126,22 @@ class CheckpointSource:
             raise FileNotFoundError(f"no safetensors / bin weights under {model_dir}")
 
     def has(self, name: str) -> bool:
+        return name in self.index or self._packed(name) is not None
+
+    def _has_raw(self, name: str) -> bool:
         return name in self.index
 
     def names(self):
         return list(self.index.keys())
 
     def get(self, name: str, shape=None, device="cpu", kind: str = "normal") -> torch.Tensor:
+        if name not in self.index:
+            base = self._packed(name)
+            if base is not None:
+                return self._dense_from_packed(base)
+        return self._get_raw(name)
+
+    def _get_raw(self, name: str) -> torch.Tensor:
         kind_, f, k, transpose = self.index[name]
         if kind_ == "st":
             from safetensors import safe_open
@@ -124,7 +152,7 @@ class CheckpointSource:
         return t.t().contiguous() if transpose else t
 
 
-class DictSource:
+class DictSource(_PackedW4Mixin):
     def __init__(self, tensors: Dict[str, torch.Tensor], model_type: str = "llama"):
         rules = load_weight_map(model_type)
         self.t = {}
@@ -135,12 +163,22 @@ class DictSource:
             self.t[name] = v
 
     def has(self, name):
+        return name in self.t or self._packed(name) is not None
+
+    def _has_raw(self, name):
         return name in self.t
+
+    def _get_raw(self, name):
+        return self.t[name]
 
     def names(self):
         return list(self.t.keys())
 
     def get(self, name, shape=None, device="cpu", kind="normal"):
+        if name not in self.t:
+            base = self._packed(name)
+            if base is not None:
+                return self._dense_from_packed(base)
         return self.t[name]
 
 
@@ -158,6 +196,11 @@ def _cols(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
 def _make_linear(w: torch.Tensor, bias, device, dtype, quant: Optional[str]) -> LinearWeight:
     w = w.to(device)
     b = bias.to(device=device, dtype=dtype) if bias is not None else None
+    if quant and quant.startswith("w4a16") and w.shape[1] % 32 == 0:
+        group = int(quant.split(":")[1]) if ":" in quant else 128
+        while w.shape[1] % group:
+            group //= 2
+        return LinearWeight(w=w.float(), bias=b).quantize_w4(max(group, 32))
     if quant == "nvfp4" and w.shape[1] % 256 == 0:
         lw = LinearWeight(w=w.float(), bias=b).quantize_nvfp4()
         return lw

@@ -32,6 +32,8 @@ class LinearWeight:
         self.w, self.bias, self.wq, self.ws = w, bias, wq, ws
         # NVFP4 form: packed e2m1 [N, K/2], e4m3 scales per 16 elements [N, K/16], fp32 tensor scale
         self.w4 = self.w4_bs = self.w4_ts = None
+        # weight-only 4-bit groups (GPTQ / AWQ family): packed levels [N, K/2], fp16 scale and zero*scale [N, K/g]
+        self.q4 = self.q4_scale = self.q4_zs = None
         # power-of-two block scales: the tensor cores can apply them (hardware block-scaled MMA)
         self.ue8m0 = ws is not None and ref.is_pow2(ws)
 
@@ -43,7 +45,13 @@ class LinearWeight:
     def nvfp4(self) -> bool:
         return self.w4 is not None
 
+    @property
+    def w4a16(self) -> bool:
+        return self.q4 is not None
+
     def _any(self) -> torch.Tensor:
+        if self.w4a16:
+            return self.q4
         return self.w4 if self.nvfp4 else (self.wq if self.fp8 else self.w)
 
     @property
@@ -52,7 +60,7 @@ class LinearWeight:
 
     @property
     def in_features(self) -> int:
-        return self.w4.shape[1] * 2 if self.nvfp4 else self._any().shape[1]
+        return self._any().shape[1] * 2 if (self.nvfp4 or self.w4a16) else self._any().shape[1]
 
     @property
     def device(self):
@@ -75,6 +83,13 @@ class LinearWeight:
             self.w = None
         return self
 
+    def quantize_w4(self, group: int = 128) -> "LinearWeight":
+        """4-bit weight-only groups along the input features (in_features must be a multiple of 32)."""
+        if not (self.w4a16 or self.nvfp4 or self.fp8):
+            self.q4, self.q4_scale, self.q4_zs = ref.quant_w4(self.w, group)
+            self.w = None
+        return self
+
     def quantize_fp8_block(self) -> "LinearWeight":
         if not self.fp8:
             self.wq, self.ws = ref.quant_weight_fp8_block(self.w)
@@ -83,12 +98,15 @@ class LinearWeight:
         return self
 
     def dense(self) -> torch.Tensor:
+        if self.w4a16:
+            return ref.dequant_w4(self.q4, self.q4_scale, self.q4_zs)
         if self.nvfp4:
             return ref.dequant_nvfp4(self.w4, self.w4_bs, self.w4_ts)
         return ref.dequant_weight_fp8_block(self.wq, self.ws) if self.fp8 else self.w
 
     def nbytes(self) -> int:
-        t = [x for x in (self.w, self.wq, self.ws, self.bias, self.w4, self.w4_bs) if x is not None]
+        t = [x for x in (self.w, self.wq, self.ws, self.bias, self.w4, self.w4_bs, self.q4, self.q4_scale, self.q4_zs)
+             if x is not None]
         return sum(x.numel() * x.element_size() for x in t)
 
 
@@ -104,6 +122,18 @@ def quantize(x: torch.Tensor) -> QTensor:
 
 def linear(x, W: LinearWeight, residual=None, out=None, out_f32: bool = False):
     """y = x W^T (+bias) (+residual). ``x`` may be a QTensor when W is FP8. ``out`` may alias ``residual``."""
+    if W.w4a16:
+        if isinstance(x, QTensor):
+            raise TypeError("4-bit weight-only layers take bf16 activations")
+        if x.is_cuda:
+            if out_f32:
+                return native.linear_w4(x, W.q4, W.q4_scale, W.q4_zs, bias=W.bias, residual=residual).float()
+            return native.linear_w4(x, W.q4, W.q4_scale, W.q4_zs, out=out, bias=W.bias, residual=residual)
+        y = ref.gemm(x, W.dense().to(x.dtype), W.bias, residual, torch.float32 if out_f32 else None)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
     if W.nvfp4:
         # activations are quantised to NVFP4 too (per-tensor scale from the tensor's own maximum, no host sync)
         a_ts = (x.float().abs().amax() / (448.0 * 6.0)).clamp_min(1e-12).reshape(())

@@ -61,6 +61,8 @@ _SIGS = {
                            i32, vp, vp, i64, vp, vp],
     "ksana_mla_attention": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, f32, i64, i32, vp, vp, vp, vp],
     "ksana_mla_rope_append": [vp, i64, i32, vp, i64, vp, f32, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
+    "ksana_w4_gemv": [vp, i64, vp, vp, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, vp],
+    "ksana_w4_dequant": [vp, vp, vp, vp, i64, i32, i32, i32, vp],
     "ksana_sample": [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, vp],
     "ksana_repetition_penalty": [vp, i64, vp, vp, vp, vp, i32, i32, vp],
     "ksana_ban_tokens": [vp, i64, vp, vp, vp, i32, i32, vp],
@@ -276,6 +278,33 @@ def gemm_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, out=None, bias=None, residual=Non
     return dst
 
 
+W4_GEMV_MAX_M = 32          # up to this many rows the 4-bit weights are streamed by the GEMV kernel (8 rows per pass)
+_w4_scratch = {}
+
+
+def linear_w4(x, q4, scale, zs, out=None, bias=None, residual=None):
+    """y = x W^T (+bias, +residual) for 4-bit group-quantised W (see csrc/kernels/w4a16.cu)."""
+    M, K = x.shape
+    N = q4.shape[0]
+    g = K // scale.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if M <= W4_GEMV_MAX_M:
+        rc = lib().ksana_w4_gemv(_p(x), x.stride(0), _p(q4), _p(scale), _p(zs), _p(bias), _p(residual),
+                                 residual.stride(0) if residual is not None else 0, _p(out), out.stride(0), M, N, K, g, _st())
+        _check(rc, "ksana_w4_gemv")
+        return out
+    # compute-bound: expand once into a per-device scratch matrix shared by all layers, then the tcgen05 bf16 GEMM
+    key = (x.device.index or 0)
+    buf = _w4_scratch.get(key)
+    if buf is None or buf.numel() < N * K:
+        buf = torch.empty(N * K, dtype=torch.bfloat16, device=x.device)
+        _w4_scratch[key] = buf
+    w = buf[: N * K].view(N, K)
+    _check(lib().ksana_w4_dequant(_p(q4), _p(scale), _p(zs), _p(w), K, N, K, g, _st()), "ksana_w4_dequant")
+    return gemm_bf16(x, w, out=out, bias=bias, residual=residual)
+
+
 def quant_fp8(x, q=None, s=None):
     M, K = x.shape
     if q is None:
@@ -427,13 +456,19 @@ def mla_rope_append(q, nope, kv, norm_w, eps, positions, slots, cos_sin, qfull, 
 
 
 def mla_splits(num_seqs: int, max_q_len: int, max_kv: int, sms: int = 148) -> int:
-    """KV splits for the latent-attention kernel: only pure decode steps split, until about two waves of CTAs
-    (two output halves per sequence) exist or a split would hold fewer than 8 tiles of 32 tokens."""
+    """KV splits for the latent-attention kernel: only pure decode steps split; the count minimises the number of
+    CTA waves times the tiles per CTA, and a split never holds fewer than 8 tiles of 32 tokens."""
     if max_q_len != 1 or num_seqs <= 0:
         return 1
-    want = (2 * sms + 2 * num_seqs - 1) // (2 * num_seqs)
-    most = max(1, (max_kv + 255) // 256)
-    return max(1, min(want, most, 32))
+    tiles = max(1, (max_kv + 31) // 32)
+    most = max(1, min(32, tiles // 8))
+    best, best_cost = 1, None
+    for n in range(1, most + 1):
+        waves = (2 * num_seqs * n + sms - 1) // sms            # one CTA per SM, two output halves per sequence
+        cost = waves * ((tiles + n - 1) // n + 2)              # tile times of the longest CTA chain (+ set-up)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = n, cost
+    return best
 
 
 def mla_attention(qfull, out, cache_layer, block_stride, block_tokens, block_table, cu_q, kv_lens, B, max_q_len, G, scale,

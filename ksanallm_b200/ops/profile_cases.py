@@ -100,6 +100,47 @@ def case_prefill_attn():     # 4 sequences x 2048 new tokens, 64 q / 8 kv heads
                              1 / math.sqrt(D))
 
 
+def _mla(B, q_len, kv_len, G, nsplit):
+    bt = 16
+    nblk = (kv_len + bt - 1) // bt
+    cache = torch.randn(B * nblk, 1, bt, 576, device=DEV, dtype=torch.bfloat16) * 0.5
+    layer = cache[:, 0]
+    table = torch.arange(B * nblk, device=DEV, dtype=torch.int32).view(B, nblk)
+    q = torch.randn(B * q_len, G, 576, device=DEV, dtype=torch.bfloat16) * 0.3
+    cu = torch.arange(0, (B + 1) * q_len, q_len, device=DEV, dtype=torch.int32)
+    kvl = torch.full((B,), kv_len, device=DEV, dtype=torch.int32)
+    out = torch.empty(B * q_len, G, 512, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        native.mla_attention(q, out, layer, layer.stride(0), bt, table, cu, kvl, B, q_len, G, 1 / math.sqrt(192), nsplit)
+    # work per launch: causal pairs x heads x (576 + 512) x 2 flops; cache bytes read once
+    pairs = B * (q_len * (kv_len - q_len) + q_len * (q_len + 1) // 2)
+    run.flops = pairs * G * (576 + 512) * 2
+    run.bytes = B * kv_len * 576 * 2
+    return run
+
+
+def case_mla_decode():       # DeepSeek-V3 decode, all 128 heads on one GPU: 32 sequences x 4096 cached tokens (151 MB)
+    run = _mla(32, 1, 4096, 128, native.mla_splits(32, 1, 4096))
+    for _ in range(2):
+        run()
+    return run
+
+
+def case_mla_decode_tp8():   # 16 heads per rank (TP8): 64 sequences x 4096 cached tokens (302 MB)
+    run = _mla(64, 1, 4096, 16, native.mla_splits(64, 1, 4096))
+    for _ in range(2):
+        run()
+    return run
+
+
+def case_mla_prefill():      # 2 sequences x 2048 new tokens, 128 heads (absorbed form)
+    run = _mla(2, 2048, 2048, 128, 1)
+    for _ in range(2):
+        run()
+    return run
+
+
 def case_norm_quant():       # residual add + RMSNorm + FP8 quantisation of 16384 x 8192 activations (805 MB moved)
     x = torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16)
     r = torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16)
@@ -125,9 +166,26 @@ def time_cases(names):
     """CUDA-event timing (after warm-up); every case launches its kernel twice per call."""
     for n in names:
         fn = CASES[n]
-        fn()
+        run = fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if callable(run):
+            # the case handed back its launch closure: time the kernel alone (inputs stay resident; cases are
+            # sized beyond L2 where DRAM traffic matters)
+            reps = 10
+            e0.record()
+            for _ in range(reps):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            extra = ""
+            if getattr(run, "flops", 0):
+                extra += f", {run.flops / ms / 1e9:.1f} TFLOP/s"
+            if getattr(run, "bytes", 0):
+                extra += f", {run.bytes / ms / 1e6:.1f} GB/s of cache rows"
+            print(f"{n}: {ms * 1000:.1f} us per launch{extra}")
+            continue
         # inputs are re-created inside each case; time only the second half by differencing two call counts
         reps = 3
         e0.record()

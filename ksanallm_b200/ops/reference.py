@@ -358,3 +358,53 @@ def mla_attention(qfull, cache_layer, block_table, cu_q, kv_lens, scale, lora=51
         sc = sc.masked_fill(kpos > qpos, float("-inf"))
         out[q0:q1] = torch.einsum("hqk,kl->qhl", torch.softmax(sc, -1), rows[:, :lora])
     return out
+
+
+# ----------------------------------------------------------------------------- 4-bit weight-only groups (W4A16)
+def quant_w4(w, group=128):
+    """Asymmetric 4-bit group quantisation along K of w [N, K]: returns (packed uint8 [N, K/2] with the even k in
+    the low nibble, scale fp16 [N, K/g], zs = zero_point * scale fp16 [N, K/g]); w ~= q * scale - zs.
+    Per group the step is (max - min) / n for the n in 15..12 with the smallest error, so a group whose values
+    already sit on a 16-level lattice (a dequantised GPTQ / AWQ group, which need not use all 16 levels) is
+    reproduced up to the fp16 rounding of zs."""
+    N, K = w.shape
+    g = min(group, K)
+    wf = w.float().reshape(N, K // g, g)
+    lo, hi = wf.amin(-1, keepdim=True), wf.amax(-1, keepdim=True)
+    best = None
+    for n in (15.0, 14.0, 13.0, 12.0):
+        scale = ((hi - lo) / n).clamp_min(1e-8).to(torch.float16).float()
+        zp = torch.round(-lo / scale)
+        q = torch.round(wf / scale + zp).clamp(0, 15)
+        zs = (zp * scale).to(torch.float16).float()
+        err = (q * scale - zs - wf).abs().amax(-1, keepdim=True)
+        if best is None:
+            best = [err, q, scale, zs]
+        else:
+            take = err < best[0] * 0.5          # a coarser step must be clearly better (an exact lattice hit)
+            best = [torch.where(take, err, best[0]), torch.where(take, q, best[1]), torch.where(take, scale, best[2]),
+                    torch.where(take, zs, best[3])]
+    _, q, scale, zs = best
+    q = q.to(torch.uint8).reshape(N, K)
+    packed = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+    return packed, scale.to(torch.float16).reshape(N, K // g).contiguous(), zs.to(torch.float16).reshape(N, K // g).contiguous()
+
+
+def pack_w4(q, scale, zero):
+    """From integer levels q [N, K] (0..15), scales and integer zero points [N, K/g] to the packed form."""
+    q = q.to(torch.uint8)
+    packed = (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+    sb = scale.to(torch.float16)
+    return packed, sb.contiguous(), (zero.float() * sb.float()).to(torch.float16).contiguous()
+
+
+def dequant_w4(packed, scale, zs):
+    N, K2 = packed.shape
+    K = K2 * 2
+    q = torch.empty(N, K, dtype=torch.float32, device=packed.device)
+    q[:, 0::2] = (packed & 15).float()
+    q[:, 1::2] = (packed >> 4).float()
+    g = K // scale.shape[1]
+    s = scale.float().repeat_interleave(g, dim=1)
+    z = zs.float().repeat_interleave(g, dim=1)
+    return q * s - z

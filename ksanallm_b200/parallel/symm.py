@@ -139,19 +139,34 @@ class SymmetricComm:
         ``h`` must be the symmetric residual view (``self.h[:M]``) when M > ONE_SHOT_ROWS; there every rank
         keeps only the rows it owns up to date unless ``gather_h`` asks for the full residual stream."""
         M = x.q.shape[0] if isinstance(x, QTensor) else x.shape[0]
-        H = W.out_features
+        return self._partial_norm(x, W, M, W.out_features, h, norm_w, norm_b, eps, layernorm, quant_for, gather_h)
+
+    def partial_norm(self, write_partial, M: int, h: torch.Tensor, norm_w, norm_b=None, eps: float = 1e-6,
+                     layernorm: bool = False, quant_for: Optional[LinearWeight] = None, gather_h: bool = False):
+        """h += sum_ranks(partial); y = norm(h). ``write_partial(part)`` fills this rank's partial result
+        ``part`` ([M, hidden] bf16, a view of the symmetric slot) - e.g. the top-k weighted combine of the experts
+        this rank owns - and the same reduce kernel as for row-parallel GEMMs pulls, sums, adds the residual and
+        normalises. Returns (h, y)."""
+        return self._partial_norm(write_partial, None, M, self.hidden, h, norm_w, norm_b, eps, layernorm, quant_for,
+                                  gather_h)
+
+    def _partial_norm(self, x, W, M, H, h, norm_w, norm_b, eps, layernorm, quant_for, gather_h):
+        writer = x if W is None else None
         parity = self.parity
         self.parity ^= 1
         push = self._push_ptrs(parity)
         err = native.err_flag(self.device).data_ptr()
         st = native._st()
         lib = native.lib()
-        if W.fp8 and not isinstance(x, QTensor):
+        if writer is None and W.fp8 and not isinstance(x, QTensor):
             x = quantize(x)
         one_shot = M <= ONE_SHOT_ROWS
         rows_per = M if one_shot else (M + self.size - 1) // self.size
-        bias = W.bias.data_ptr() if (W.bias is not None and self.rank == 0) else None
-        if not PUSH_EPILOGUE:
+        bias = W.bias.data_ptr() if (writer is None and W.bias is not None and self.rank == 0) else None
+        if writer is not None:
+            part = self.buf[self.slots_off[parity]: self.slots_off[parity] + M * H * 2].view(torch.bfloat16).view(M, H)
+            writer(part)
+        elif not PUSH_EPILOGUE:
             # partial product [M, H] into this rank's own symmetric buffer (the slot area of this parity); the
             # reduce kernel of every row owner (one-shot: of every rank) pulls it from there
             part = self.buf[self.slots_off[parity]: self.slots_off[parity] + M * H * 2].view(torch.bfloat16).view(M, H)
@@ -184,7 +199,7 @@ class SymmetricComm:
             native._check(rc, "ksana_gemm_push")
         want_q = quant_for is not None and quant_for.fp8 and H % 128 == 0 and norm_w is not None
         if one_shot:
-            row_begin, row_count, gather = 0, M, (0 if PUSH_EPILOGUE else 4)
+            row_begin, row_count, gather = 0, M, (4 if (writer is not None or not PUSH_EPILOGUE) else 0)
             y = torch.empty(M, H, dtype=torch.bfloat16, device=self.device) if (norm_w is not None and not want_q) else None
             yq = torch.empty(M, H, dtype=torch.float8_e4m3fn, device=self.device) if want_q else None
             scale_ld = (M + 3) // 4 * 4
@@ -192,7 +207,7 @@ class SymmetricComm:
         else:
             row_begin = min(self.rank * rows_per, M)
             row_count = max(0, min(rows_per, M - row_begin))
-            gather = 1 | (2 if gather_h else 0) | (0 if PUSH_EPILOGUE else 4)
+            gather = 1 | (2 if gather_h else 0) | (4 if (writer is not None or not PUSH_EPILOGUE) else 0)
             assert h.data_ptr() == self.h.data_ptr(), "large-batch row-parallel linear needs the symmetric residual view"
             y = self.y[:M] if (norm_w is not None and not want_q) else None
             yq = self.yq[:M] if want_q else None

@@ -1,0 +1,81 @@
+"""The serving benchmark client against a live (CPU, tiny model) server: statistics and both request modes."""
+import math
+import os
+import socket
+import sys
+import threading
+import time
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks"))
+import benchmark_throughput as bt  # noqa: E402
+from helpers import ByteTokenizer, tiny_model_cfg  # noqa: E402
+
+
+def test_summary_statistics():
+    recs = []
+    for i in range(4):
+        r = bt.RequestRecord(prompt_len=10, output_len=5, start=0.0, first_token=0.1 * (i + 1), end=1.0 + i)
+        r.chunk_times = [r.first_token, r.first_token + 0.2, r.first_token + 0.5]
+        recs.append(r)
+    bad = bt.RequestRecord(prompt_len=3, ok=False)
+    s = bt.summarize(recs + [bad], wall=4.0, percentiles=(50, 99))
+    assert s["finished"] == 4 and s["failed"] == 1
+    assert s["request_throughput"] == 1.0 and s["token_throughput"] == 15.0
+    assert math.isclose(s["avg_latency_s"], 2.5) and math.isclose(s["p50_latency_s"], 2.5)
+    assert math.isclose(s["avg_ttft_s"], 0.25)
+    assert math.isclose(recs[0].tpot, (1.0 - 0.1) / 4)
+    assert math.isclose(s["avg_itl_s"], 0.25)
+    assert bt.percentile([1, 2, 3, 4], 100) == 4 and math.isnan(bt.percentile([], 50))
+    w = bt.synthetic_prompts("5:20:7:0.5", 300, seed=1)
+    assert len(w) == 5 and all(o == 7 and all(3 <= t < 300 for t in p) for p, o in w)
+
+
+@pytest.fixture(scope="module")
+def server():
+    import uvicorn
+    from ksanallm_b200.config import EngineConfig
+    from ksanallm_b200.llm import LLM
+    from ksanallm_b200.serving.serving_model import ServingModel
+    from ksanallm_b200.serving.serving_server import create_app
+    tok = ByteTokenizer()
+    ec = EngineConfig()
+    ec.batch_scheduler.max_batch_size = 8
+    ec.batch_scheduler.max_token_len = 128
+    ec.block_manager.device_blocks_num = 128
+    llm = LLM(ec, tiny_model_cfg(), weights="random", device="cpu", dtype=torch.float32, tokenizer=tok)
+    model = ServingModel("", llm=llm, tokenizer=tok)
+    model.init_serving()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    srv = uvicorn.Server(uvicorn.Config(create_app(model, tok), host="127.0.0.1", port=port, log_level="warning"))
+    th = threading.Thread(target=srv.run, daemon=True)
+    th.start()
+    for _ in range(200):
+        if srv.started:
+            break
+        time.sleep(0.05)
+    assert srv.started
+    yield port
+    srv.should_exit = True
+    th.join(timeout=10)
+    model.shutdown()
+
+
+@pytest.mark.parametrize("extra", [["--stream", "--request_rate", "50", "--random"], ["--mode", "sync", "--concurrency", "3"]])
+def test_client_against_live_server(server, tmp_path, extra):
+    perf = tmp_path / "perf.csv"
+    args = bt.args_config(["--port", str(server), "--synthetic", "6:12:5", "--vocab_size", "250", "--perf_csv", str(perf),
+                           "--output_csv", str(tmp_path / "out.csv"), "--client_timeout", "60"] + extra)
+    res = bt.run_benchmark(args)
+    assert len(res) == 1
+    s = res[0]
+    assert s["finished"] == 6 and s["failed"] == 0
+    assert s["avg_output_tokens"] == 5 and s["avg_input_tokens"] == 12
+    assert s["token_throughput"] > 0
+    if "--stream" in extra:
+        assert s["avg_ttft_s"] > 0 and s["p99_ttft_s"] >= s["p50_ttft_s"] and "avg_tpot_s" in s
+    assert perf.exists() and (tmp_path / "out.csv").read_text().count("\n") == 7

@@ -10,13 +10,15 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _launch(nproc, out, backend, quant, port, graphs=None):
+def _launch(nproc, out, backend, quant, port, graphs=None, arch=None):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py"),
            out, backend, quant]
-    if graphs is not None:
-        cmd.append("graphs" if graphs else "eager")
+    if graphs is not None or arch is not None:
+        cmd.append("graphs" if (graphs or graphs is None and backend == "fused") else "eager")
+    if arch is not None:
+        cmd.append(arch)
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=150)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return torch.load(out)
@@ -59,3 +61,17 @@ def test_tp4_fused(tmp_path):
     single = _launch(1, str(tmp_path / "single.pt"), "nccl", "auto", 29641)
     fused = _launch(4, str(tmp_path / "fused4.pt"), "fused", "auto", 29642)
     assert rel(fused["first"], single["first"]) < 3e-2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("arch", ["moe", "moe_ep"])
+def test_tp2_moe_fused_combine(tmp_path, arch):
+    """MoE layers on the fused path: each rank's expert outputs are combined into its peer-visible slot and the
+    cross-rank sum + residual + norm is the reduce kernel (experts sliced by tensor parallelism, or whole experts
+    per rank with expert parallelism)."""
+    single = _launch(1, str(tmp_path / "single.pt"), "nccl", "auto", 29651, arch="moe")
+    nccl = _launch(2, str(tmp_path / "nccl.pt"), "nccl", "auto", 29652, arch=arch)
+    fused = _launch(2, str(tmp_path / "fused.pt"), "fused", "auto", 29653, arch=arch)
+    assert rel(nccl["first"], single["first"]) < 4e-2
+    assert rel(fused["first"], single["first"]) < 4e-2
+    assert fused["graph_replays"] > 0

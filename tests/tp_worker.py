@@ -17,9 +17,10 @@ from ksanallm_b200.utils import native_engine as ne  # noqa: E402
 def main():
     out_path, backend, quant = sys.argv[1], sys.argv[2], sys.argv[3]
     graphs = (sys.argv[4] == "graphs") if len(sys.argv) > 4 else backend == "fused"
+    arch = sys.argv[5] if len(sys.argv) > 5 else "llama"          # llama | moe (experts sliced) | moe_ep (whole experts)
     log_dir = os.environ.get("KSANA_TP_LOG_DIR")
     rank_env = os.environ.get("RANK", "0")
-    log = open(os.path.join(log_dir, f"tp_model_{backend}_{quant}_{int(graphs)}_rank{rank_env}.log"), "w") if log_dir else None
+    log = open(os.path.join(log_dir, f"tp_model_{backend}_{quant}_{int(graphs)}_{sys.argv[5] if len(sys.argv) > 5 else 'llama'}_rank{rank_env}.log"), "w") if log_dir else None
 
     def say(*a):
         if log:
@@ -29,7 +30,11 @@ def main():
     mc = ModelConfig(model_type="llama", hidden_size=1024, num_layers=3, num_heads=8, num_kv_heads=4, head_dim=128,
                      intermediate_size=2048, vocab_size=32000, rms_norm_eps=1e-5, max_position_embeddings=512,
                      max_token_len=512)
+    if arch.startswith("moe"):
+        mc.model_type, mc.num_experts, mc.num_experts_per_tok, mc.moe_intermediate_size = "mixtral", 8, 2, 512
     ec = EngineConfig()
+    if arch == "moe_ep":
+        ec.global_.expert_para_size = int(os.environ.get("WORLD_SIZE", "1"))
     ec.global_.comm_backend = backend
     ec.global_.enable_cuda_graph = graphs
     ec.batch_scheduler.max_batch_size = 8
