@@ -113,10 +113,20 @@ class LLM:
         if dev_type == "cuda":
             torch.cuda.set_device(self.device)
         tp = self.world // pp
+        adp = max(1, self.engine_cfg.global_.attn_data_para_size) if self.world > 1 else 1
+        if adp > 1:
+            # attention data parallel over all ranks, routed experts spread over the same ranks
+            if adp != self.world or pp != 1:
+                raise ValueError(f"attn_data_para_size {adp} must equal the world size {self.world} (no pipeline stages)")
+            if not model_cfg.is_moe:
+                raise ValueError("attn_data_para_size > 1 needs a mixture-of-experts model (dense models: run replicas)")
+            tp = 1
+            model_cfg.ep_layout_override = (self.rank, self.world)
+        self.adp_size = adp
         self.pp_size, self.tp_size = pp, tp
-        self.pp_rank, self.tp_rank = self.rank // tp, self.rank % tp
+        self.pp_rank, self.tp_rank = (self.rank // tp, self.rank % tp) if adp == 1 else (0, 0)
         check_tp(model_cfg, tp)
-        ep = self.engine_cfg.global_.expert_para_size
+        ep = self.engine_cfg.global_.expert_para_size if adp == 1 else 1
         if ep not in (1, tp):
             raise ValueError(f"expert_para_size {ep} must be 1 or equal to the tensor-parallel size {tp}")
         model_cfg.expert_para_size = ep
@@ -159,6 +169,9 @@ class LLM:
             layer_range = stage_layers(model_cfg.num_layers, pp, self.pp_rank)
         self.model = build_model(model_cfg, source, self.tp_rank, tp, self.comm, self.device, dtype, quant,
                                  layer_range=layer_range, max_positions=mp)
+        if adp > 1:
+            from .parallel.data_parallel import AttentionDP
+            self.model.dp = AttentionDP(self.rank, self.world, dev_group)
         kv_dtype = kv_dtype_from(self.engine_cfg, dtype)
         bt = self.engine_cfg.block_manager.block_token_num
         probe = self.model.allocate_kv_cache(1, bt, kv_dtype)

@@ -106,6 +106,7 @@ class CommonModel:
         if cfg.position_embedding in ("rope", "mrope"):
             n = max_positions or cfg.max_token_len
             self.cos_sin = ref.build_cos_sin_cache(self.rot_dim, n, cfg.rope_theta, cfg.rope_scaling, self.device)
+        self.dp = None                       # parallel.data_parallel.AttentionDP when attention runs data parallel
         self.step_hidden: Optional[torch.Tensor] = None
         self.step_normed: Optional[torch.Tensor] = None
 
@@ -242,6 +243,14 @@ class CommonModel:
                 r = torch.stack([x0 * cos - x1 * sin, x1 * cos + x0 * sin], dim=-1).flatten(-2)
             k[..., : self.rot_dim] = r
             self.kv_cache[int(dst), :, 0] = k.to(self.kv_cache.dtype)
+
+    def forward_empty_dp(self) -> None:
+        """Attention data parallelism, a step in which this rank owns no rows: it still takes part in the dispatch /
+        combine collectives of every MoE block (its experts may be needed by the other ranks' rows)."""
+        x = torch.zeros(0, self.cfg.hidden_size, dtype=self.dtype, device=self.device)
+        for lw in self.layers:
+            if lw.moe is not None:
+                self.dp.moe(self, lw.moe, x, x)
 
     def forward_layers(self, step: StepInput, hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
         """This stage's layers only (embedding on the first stage): the hidden states to hand to the next

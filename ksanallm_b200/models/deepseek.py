@@ -177,9 +177,9 @@ def build_deepseek(cfg: ModelConfig, source, tp_rank, tp_size, comm, device, dty
             post_norm=get(lp + "post_attention_layernorm.weight", (H,), "ones").to(device=device, dtype=dtype),
             post_norm_bias=None, attn_extra={"mla": mla})
         if cfg.is_moe and li >= cfg.first_k_dense_replace and li % max(cfg.moe_layer_freq, 1) == 0:
-            ep = tp_size if cfg.expert_para_size > 1 else 1
-            lw.moe = load_moe(cfg, source, lp, tp_rank, tp_size, device, dtype, quant, ep_rank=tp_rank if ep > 1 else 0,
-                              ep_size=ep)
+            from .moe import ep_layout
+            ep_rank, ep = ep_layout(cfg, tp_rank, tp_size)
+            lw.moe = load_moe(cfg, source, lp, tp_rank, tp_size, device, dtype, quant, ep_rank=ep_rank, ep_size=ep)
         else:
             inter = cfg.intermediate_size
             g = _rows(get(lp + "mlp.gate_proj.weight", (inter, H)), tp_rank, tp_size)

@@ -144,13 +144,36 @@ def route_reference(logits, cfg: ModelConfig, bias=None):
 
 def moe_forward(model, mw: MoEWeights, x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
     """h += MoE(x) (reduced over the TP group). ``x`` is the normalised hidden state [T, H] (bf16)."""
+    if getattr(model, "dp", None) is not None:
+        return model.dp.moe(model, mw, x, h)           # attention data parallelism: dispatch / experts / combine
     out = moe_partial(model, mw, x)
     if model.tp_size > 1:
         out = model.comm.all_reduce(out)
     return ops.add(h, out)
 
 
-def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+def ep_layout(cfg: ModelConfig, tp_rank: int, tp_size: int):
+    """(expert-parallel rank, size) of this rank: an explicit layout set by the engine (attention data parallelism:
+    experts spread over the data-parallel ranks) or the tensor-parallel group when ``expert_para_size`` > 1."""
+    forced = getattr(cfg, "ep_layout_override", None)
+    if forced is not None:
+        return forced
+    return (tp_rank, tp_size) if cfg.expert_para_size > 1 else (0, 1)
+
+
+def shared_expert(model, mw: MoEWeights, x: torch.Tensor) -> torch.Tensor:
+    """Shared expert(s) of an MoE block applied to ``x`` (this rank's slice under tensor parallelism)."""
+    cfg = model.cfg
+    sg = ops.linear(x, mw.shared_gate_up)
+    sa = ops.act_mul(sg, cfg.activation, True, quant_for=mw.shared_down)
+    so = ops.linear(sa, mw.shared_down)
+    if mw.shared_gate is not None:
+        so = (so.float() * torch.sigmoid(x.float() @ mw.shared_gate.float().t())).to(x.dtype)
+    return so
+
+
+def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Tensor] = None,
+                shared: bool = True) -> torch.Tensor:
     """This rank's share of MoE(x): the weighted outputs of the experts (or expert slices) it holds plus its slice
     of the shared expert, before any reduction over ranks. ``into`` ([T, H], e.g. a peer-visible buffer that a
     reduce kernel pulls from) receives the result when given."""
@@ -177,7 +200,7 @@ def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Ten
             a = native.act_mul(g, cfg.activation, True)
             y = native.gemm_grouped(a, mw.w2, tile_expert, n_local, H)
         out = into if into is not None else torch.empty(T, H, dtype=x.dtype, device=x.device)
-        have_shared = mw.shared_gate_up is not None
+        have_shared = shared and mw.shared_gate_up is not None
         if have_shared:
             sg = ops.linear(x, mw.shared_gate_up)
             sa = ops.act_mul(sg, cfg.activation, True, quant_for=mw.shared_down)
@@ -203,7 +226,7 @@ def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Ten
             a = ref.act(gu[:, :mw.inter], cfg.activation) * gu[:, mw.inter:]
             ye = a @ w2[le * H:(le + 1) * H].t()
             out.index_add_(0, tok, ye * w[tok, slot].unsqueeze(-1))
-        if mw.shared_gate_up is not None:
+        if shared and mw.shared_gate_up is not None:
             sg = ops.linear(x, mw.shared_gate_up)
             sa = ops.act_mul(sg, cfg.activation, True, quant_for=mw.shared_down)
             so = ops.linear(sa, mw.shared_down).float()

@@ -282,9 +282,9 @@ def build_model(cfg: ModelConfig, source, tp_rank: int = 0, tp_size: int = 1, co
         is_moe_layer = cfg.is_moe and li >= cfg.first_k_dense_replace and (li % max(cfg.moe_layer_freq, 1) == 0)
         if is_moe_layer:
             from .moe import load_moe
-            ep = tp_size if cfg.expert_para_size > 1 else 1
-            lw.moe = load_moe(cfg, source, p, tp_rank, tp_size, device, dtype, quant, ep_rank=tp_rank if ep > 1 else 0,
-                              ep_size=ep)
+            from .moe import ep_layout
+            ep_rank, ep = ep_layout(cfg, tp_rank, tp_size)
+            lw.moe = load_moe(cfg, source, p, tp_rank, tp_size, device, dtype, quant, ep_rank=ep_rank, ep_size=ep)
         else:
             inter = cfg.intermediate_size
             isz = (inter + tp_size - 1) // tp_size

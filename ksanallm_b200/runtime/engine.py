@@ -175,7 +175,7 @@ class ModelRunner:
     def enable_graphs(self, max_batch: int, max_token_len: int):
         """Whole-model CUDA graphs for pure-decode steps, one per padded batch size (the reference captures
         per-layer graphs for batch sizes 1..3 only: src/ksana_llm/runtime/cuda_graph_runner.cpp:11-30)."""
-        if not self.cuda or self.pipeline is not None:
+        if not self.cuda or self.pipeline is not None or getattr(self.model, "dp", None) is not None:
             return
         self.graphs = {}
         self.graph_max_batch = max_batch
@@ -246,6 +246,16 @@ class ModelRunner:
     @torch.inference_mode()
     def execute(self, plan, extra: Optional[dict] = None) -> torch.Tensor:
         self.apply_block_ops(plan)
+        dp = getattr(self.model, "dp", None)
+        if dp is not None:
+            # attention data parallelism: this rank runs only its own sequences; rank 0 collects the logits rows
+            sub = dp.sub_plan(plan)
+            local = None
+            if sub.num_tokens:
+                local = self.model.forward(self.build_step(sub, None))
+            else:
+                self.model.forward_empty_dp()
+            return dp.gather_logits(local, self.model.cfg.vocab_size, self.device)
         if extra is None:
             out = self._try_graph(plan)
             if out is not None:

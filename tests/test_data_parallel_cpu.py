@@ -1,0 +1,69 @@
+"""Attention data parallelism + expert parallelism on CPU ranks (gloo) against a single-process run."""
+import os
+import subprocess
+import sys
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from ksanallm_b200.parallel.data_parallel import AttentionDP
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_sub_plan_selects_own_sequences():
+    plan = SimpleNamespace(seq_ids=np.array([4, 7, 9, 10, 12]), cu_q=np.array([0, 3, 8, 9, 10, 11]),
+                           kv_lens=np.array([3, 20, 31, 5, 8]), input_ids=np.arange(11) + 100, positions=np.arange(11),
+                           slots=np.arange(11) + 50, block_table=np.arange(10), max_blocks=2,
+                           sample_rows=np.array([2, 7, 8, 9, 10]), sample_seq_ids=np.array([4, 7, 9, 10, 12]),
+                           num_multi=2, num_single=3, num_tokens=11, num_multi_tokens=8, max_q_len=5,
+                           swap_out=np.zeros(0), swap_in=np.zeros(0), copies=np.zeros(0))
+    dp = AttentionDP(rank=0, size=2)
+    sub = dp.sub_plan(plan)                      # even sequence ids: 4, 10, 12
+    assert dp.counts == [5, 6]
+    assert sub.seq_ids.tolist() == [4, 10, 12] and sub.cu_q.tolist() == [0, 3, 4, 5]
+    assert sub.input_ids.tolist() == [100, 101, 102, 109, 110] and sub.kv_lens.tolist() == [3, 5, 8]
+    assert sub.block_table.tolist() == [0, 1, 6, 7, 8, 9]
+    assert (sub.num_multi, sub.num_single, sub.num_multi_tokens, sub.max_q_len) == (1, 2, 3, 3)
+    assert sub.sample_rows.tolist() == [2, 3, 4]
+    sub1 = AttentionDP(rank=1, size=2).sub_plan(plan)
+    assert sub1.seq_ids.tolist() == [7, 9] and sub1.sample_rows.tolist() == [4, 5] and sub1.num_multi == 1
+
+
+def _single():
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from dp_worker import engine_cfg, model_cfg, prompts_for
+    from ksanallm_b200.models.weights import RandomSource, build_model
+    from ksanallm_b200.runtime.engine import LLMEngine
+    from ksanallm_b200.utils import native_engine as ne
+    mc = model_cfg("cpu")
+    model = build_model(mc, RandomSource(seed=11, std=0.2), device="cpu", dtype=torch.float32)
+    eng = LLMEngine(model, mc, engine_cfg(), num_blocks=128)
+    first = {}
+
+    def hook(plan, lg):
+        for i, sid in enumerate(plan.sample_seq_ids.tolist()):
+            first.setdefault(sid, lg[i].float().clone())
+
+    eng.step_hook = hook
+    s = ne.SamplingConfig()
+    s.max_new_tokens, s.ignore_eos = 5, True
+    reqs = eng.generate(prompts_for(mc.vocab_size), s)
+    return [r.outputs[0].tokens for r in reqs], torch.stack([first[k] for k in sorted(first)])
+
+
+@pytest.mark.parametrize("nproc,port", [(2, 29721), (4, 29722)])
+def test_attention_dp_matches_single_process(tmp_path, nproc, port):
+    want_tokens, want_first = _single()
+    out = str(tmp_path / "dp.pt")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "dp_worker.py"), out, "cpu"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    assert got["experts"] == (0, 8 // nproc)                    # rank 0 holds whole experts, a 1/nproc share
+    assert got["gathered_bytes"] > 0
+    assert float((got["first"] - want_first).abs().max()) < 1e-3
+    assert got["tokens"] == want_tokens
