@@ -293,6 +293,16 @@ def parse_model_max_length(hf: dict, max_pos: int) -> int:
 
 
 def model_config_from_hf(hf: dict, generation: Optional[dict] = None) -> ModelConfig:
+    rp = hf.get("rope_parameters")
+    if isinstance(rp, dict):
+        # newer config.json files keep rope_theta and the scaling description together under rope_parameters
+        hf = dict(hf)
+        if rp.get("rope_theta") is not None and hf.get("rope_theta") is None:
+            hf["rope_theta"] = rp["rope_theta"]
+        if hf.get("rope_scaling") is None and rp.get("rope_type", rp.get("type", "default")) != "default":
+            hf["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+        elif hf.get("rope_scaling") is None and rp.get("mrope_section"):
+            hf["rope_scaling"] = {"mrope_section": rp["mrope_section"]}
     mt = hf.get("model_type", "llama")
     arch = _ARCH_ALIASES.get(mt, mt)
     c = ModelConfig(model_type=arch)

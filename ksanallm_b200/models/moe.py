@@ -82,12 +82,21 @@ def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dt
         if rnd or source.has(name):
             rbias = source.get(name, (E,), device=device, kind="zeros").to(device=device, dtype=torch.float32)
     w13_parts, w2_parts = [], []
+    fused_gu, fused_d = prefix + "mlp.experts.gate_up_proj", prefix + "mlp.experts.down_proj"
+    fused = (not rnd) and source.has(fused_gu) and source.has(fused_d)
+    if fused:
+        # checkpoints that stack the experts: gate_up_proj [E, 2*I, H] (gate rows, then up rows), down_proj [E, H, I]
+        gu_all, d_all = source.get(fused_gu, None, device=device), source.get(fused_d, None, device=device)
     for e in range(E):
         if not (lo <= e < hi):
             # experts owned by other expert-parallel ranks keep a zero-size placeholder row range
             continue
         ep = f"{prefix}mlp.experts.{e}."
-        if rnd and source.on_device:
+        if fused:
+            g, u = gu_all[e, :I_full], gu_all[e, I_full:]
+            g_u = torch.cat([_rows(g, tp_rank, tp_size), _rows(u, tp_rank, tp_size)], 0)
+            d = _cols(d_all[e], tp_rank, tp_size)
+        elif rnd and source.on_device:
             g_u = source.get(ep + f"gate_up_proj.weight.tp{tp_rank}", (2 * I, H), device=device)
             d = source.get(ep + f"down_proj.weight.tp{tp_rank}", (H, I), device=device)
         else:

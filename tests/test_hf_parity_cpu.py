@@ -1,0 +1,107 @@
+"""Architecture parity with the Hugging Face implementations: tiny randomly initialised HF models, their state
+dicts loaded through the weight maps, logits compared on CPU in fp32 (prefill of one sequence)."""
+import pytest
+import torch
+
+from ksanallm_b200.config import model_config_from_hf
+from ksanallm_b200.models.common import StepInput
+from ksanallm_b200.models.weights import DictSource, build_model
+
+transformers = pytest.importorskip("transformers")
+
+
+def _ours(hf_cfg: dict, state_dict, tokens):
+    cfg = model_config_from_hf(hf_cfg)
+    cfg.max_token_len = min(cfg.max_token_len, 256)
+    sd = {k: v.detach().clone() for k, v in state_dict.items()}
+    model = build_model(cfg, DictSource(sd, cfg.model_type), device="cpu", dtype=torch.float32)
+    T = len(tokens)
+    model.allocate_kv_cache(8, 16)
+    ar = torch.arange(T, dtype=torch.int32)
+    step = StepInput(torch.tensor(tokens, dtype=torch.int32), ar, ar.clone(), torch.tensor([0, T], dtype=torch.int32),
+                     torch.tensor([T], dtype=torch.int32), torch.arange(8, dtype=torch.int32).view(1, 8),
+                     num_multi=1, num_single=0, num_tokens=T, num_multi_tokens=T, max_q_len=T, max_kv_len=T)
+    return model.forward(step)
+
+
+def _check(hf_model, hf_cfg, tol=2e-4):
+    torch.manual_seed(0)
+    tokens = torch.randint(3, hf_cfg["vocab_size"], (23,)).tolist()
+    hf_model.eval()
+    with torch.no_grad():
+        want = hf_model(torch.tensor([tokens])).logits[0].float()
+        got = _ours(hf_cfg, hf_model.state_dict(), tokens)
+    assert got.shape == want.shape
+    err = float((got - want).abs().max())
+    assert err < tol * max(1.0, float(want.abs().max())), err
+
+
+def _init(model, std=0.05):
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g) * std)
+            elif "norm" in n or "ln_" in n:
+                p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=g) if n.endswith("weight") else 0.1 * torch.randn(p.shape, generator=g))
+            else:
+                p.copy_(torch.randn(p.shape, generator=g) * std)
+    return model
+
+
+def test_llama_gqa_with_llama3_rope_scaling():
+    from transformers import LlamaConfig, LlamaForCausalLM
+    c = LlamaConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                    vocab_size=200, max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=10000.0,
+                    rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                  "original_max_position_embeddings": 64}, tie_word_embeddings=False)
+    _check(_init(LlamaForCausalLM(c)), c.to_dict())
+
+
+def test_qwen2_qkv_bias_and_tied_embeddings():
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    c = Qwen2Config(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                    vocab_size=200, max_position_embeddings=256, rms_norm_eps=1e-6, tie_word_embeddings=True)
+    _check(_init(Qwen2ForCausalLM(c)), c.to_dict())
+
+
+def test_gpt2_learned_positions_layernorm_gelu_conv1d():
+    from transformers import GPT2Config, GPT2LMHeadModel
+    c = GPT2Config(n_embd=64, n_layer=2, n_head=4, vocab_size=200, n_positions=128, activation_function="gelu_new")
+    _check(_init(GPT2LMHeadModel(c)), c.to_dict(), tol=5e-4)
+
+
+def test_mixtral_softmax_top2_experts():
+    from transformers import MixtralConfig, MixtralForCausalLM
+    c = MixtralConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=96,
+                      vocab_size=200, max_position_embeddings=256, num_local_experts=4, num_experts_per_tok=2,
+                      rms_norm_eps=1e-5, sliding_window=None, tie_word_embeddings=False)
+    _check(_init(MixtralForCausalLM(c)), c.to_dict())
+
+
+def test_qwen2_moe_shared_expert_gate():
+    from transformers import Qwen2MoeConfig, Qwen2MoeForCausalLM
+    c = Qwen2MoeConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                       intermediate_size=128, moe_intermediate_size=48, shared_expert_intermediate_size=80, num_experts=4,
+                       num_experts_per_tok=2, norm_topk_prob=False, vocab_size=200, max_position_embeddings=256,
+                       decoder_sparse_step=1, mlp_only_layers=[], tie_word_embeddings=False)
+    _check(_init(Qwen2MoeForCausalLM(c)), c.to_dict())
+
+
+def test_deepseek_v3_mla_and_grouped_sigmoid_routing():
+    try:
+        from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+    except ImportError:
+        pytest.skip("this transformers build has no DeepseekV3")
+    c = DeepseekV3Config(hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+                         intermediate_size=128, moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1,
+                         num_experts_per_tok=2, n_group=4, topk_group=2, routed_scaling_factor=2.5, norm_topk_prob=True,
+                         first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                         v_head_dim=16, vocab_size=200, max_position_embeddings=256, rms_norm_eps=1e-6, rope_scaling=None,
+                         tie_word_embeddings=False)
+    m = _init(DeepseekV3ForCausalLM(c))
+    with torch.no_grad():
+        for n, b in m.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.copy_(0.1 * torch.randn(b.shape, generator=torch.Generator().manual_seed(5)))
+    _check(m, c.to_dict(), tol=5e-4)
