@@ -83,12 +83,81 @@ def llama3_70b():
                        max_position_embeddings=8192, max_token_len=8192, eos_token_ids=[128001])
 
 
+def run_library_baseline(args):
+    """Same model shape, batch and timing protocol, executed by baseline/library_engine.py."""
+    import torch
+    import torch.distributed as dist
+    from baseline.library_engine import LibraryLlama
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    mc = llama3_70b()
+    if args.layers:
+        mc.num_layers = args.layers
+    B, S_in, S_out = args.batch, args.input_len, args.output_len
+    model = LibraryLlama(mc, rank, world, dev, B, S_in + S_out + 16)
+    g = torch.Generator().manual_seed(1234)
+    pinned = torch.empty(B, S_in, dtype=torch.int64).pin_memory()
+
+    def one_step():
+        pinned.copy_(torch.randint(0, mc.vocab_size, (B, S_in), generator=g))
+        prompts = pinned.to(dev, non_blocking=True)
+        if world > 1:
+            dist.broadcast(prompts, 0)
+        toks = model.generate(prompts, S_out)
+        return toks.cpu()                       # sampled tokens are read back, as the engine does every step
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        one_step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        one_step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    if rank == 0:
+        out_tokens = args.steps * B * S_out
+        print(json.dumps({
+            "metric": "output tok/s (offline, max over ranks) at Llama-3-70B fp8 TP%d" % world, "impl": "baseline",
+            "value": out_tokens / (ms / 1000.0), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "dtype":
+            "fp8-e4m3 per-tensor weights and GEMM inputs (cuBLASLt), bf16 activations and KV cache", "data": "synthetic",
+            "config": {"model": "Llama-3-70B architecture, random-init N(0,0.02)" + (" [DEBUG %d layers: INVALID]" % args.layers if args.layers else ""),
+                       "global_batch": B, "seq_len": S_in, "output_len": S_out,
+                       "parallelism": "tp%d" % world, "path": "torch._scaled_mm + SDPA + NCCL, unfused, contiguous KV cache"},
+            "clocks": clocks}))
+    sys.stdout.flush()
+    if world > 1:
+        dist.barrier()
+        os._exit(0)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"],
+                    help="baseline: the same batch through library calls only (per-tensor FP8 cuBLASLt GEMMs, SDPA, NCCL, "
+                         "unfused ops; baseline/library_engine.py), the constructed measuring stick")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--input-len", type=int, default=2048)
     ap.add_argument("--output-len", type=int, default=256)
@@ -103,6 +172,9 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
+
+    if args.impl == "baseline":
+        return run_library_baseline(args)
 
     import numpy as np
     import torch
