@@ -105,7 +105,7 @@ def build_engine(force: bool = False) -> Path:
             list(ex.map(_run, jobs))
     out = engine_lib_path()
     if force or jobs or not out.exists():
-        _run(["g++", "-shared", "-pthread", "-o", str(out), *map(str, objs)])
+        _run(["g++", "-shared", "-pthread", "-o", str(out), *map(str, objs), "-ldl"])
     return out
 
 

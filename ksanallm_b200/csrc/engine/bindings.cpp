@@ -2,6 +2,7 @@
 // Blocking calls release the GIL. Counterpart of the reference binding layer
 // (src/ksana_llm/torch_op/serving_op.cpp:98-245), reduced to the engine-facing objects: the
 // HTTP-facing Python package builds the request/response objects on top of these.
+#include "endpoint_plugin.h"
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
@@ -50,8 +51,61 @@ py::dict StatsToDict(const SchedulerStats& s) {
 
 }  // namespace
 
+namespace {
+// Bridges a plug-in's C callbacks to Python callables: handler(kind, bytes) -> (status, bytes); shutdown().
+struct PluginBridge {
+  py::object handler, shutdown;
+};
+void BridgeHandle(void* ctx, const char* kind, const char* data, unsigned long long len, ksana::KsanaReplyFn reply,
+                  void* reply_ctx) {
+  auto* b = static_cast<PluginBridge*>(ctx);
+  py::gil_scoped_acquire gil;
+  try {
+    py::object r = b->handler(py::str(kind), py::bytes(data, static_cast<size_t>(len)));
+    py::tuple t = r.cast<py::tuple>();
+    std::string body = t[1].cast<std::string>();
+    reply(reply_ctx, body.data(), body.size(), t[0].cast<int>());
+  } catch (const std::exception& e) {
+    std::string msg = e.what();
+    reply(reply_ctx, msg.data(), msg.size(), 500);
+  }
+}
+void BridgeGenerate(void* ctx, const char* d, unsigned long long n, ksana::KsanaReplyFn r, void* rc) {
+  BridgeHandle(ctx, "generate", d, n, r, rc);
+}
+void BridgeForward(void* ctx, const char* d, unsigned long long n, ksana::KsanaReplyFn r, void* rc) {
+  BridgeHandle(ctx, "forward", d, n, r, rc);
+}
+void BridgeShutdown(void* ctx) {
+  auto* b = static_cast<PluginBridge*>(ctx);
+  py::gil_scoped_acquire gil;
+  if (!b->shutdown.is_none()) b->shutdown();
+}
+struct PyEndpointPlugin {
+  PyEndpointPlugin(const std::string& name, const std::string& dir) : plugin(name, dir) {}
+  ksana::EndpointPlugin plugin;
+  PluginBridge bridge;
+};
+}  // namespace
+
 PYBIND11_MODULE(_ksana_engine, m) {
   m.doc() = "native host runtime: scheduler, KV cache manager, structured-output FSM, profiler, control plane";
+
+  py::class_<PyEndpointPlugin>(m, "EndpointPlugin")
+      .def(py::init<const std::string&, const std::string&>(), py::arg("name"), py::arg("search_dir") = "")
+      .def_property_readonly("symbol", [](const PyEndpointPlugin& p) { return p.plugin.symbol(); })
+      .def_property_readonly("path", [](const PyEndpointPlugin& p) { return p.plugin.path(); })
+      .def("start", [](PyEndpointPlugin& p, py::object handler, py::object shutdown, const std::string& host, int port) {
+        p.bridge.handler = handler;
+        p.bridge.shutdown = shutdown;
+        ksana::KsanaEndpointApi api{&p.bridge, BridgeGenerate, BridgeForward, BridgeShutdown};
+        py::gil_scoped_release rel;
+        return p.plugin.Start(api, host, port);
+      }, py::arg("handler"), py::arg("shutdown") = py::none(), py::arg("host") = "0.0.0.0", py::arg("port") = 8080)
+      .def("stop", [](PyEndpointPlugin& p) {
+        py::gil_scoped_release rel;
+        return p.plugin.Stop();
+      });
 
   py::enum_<RetCode>(m, "RetCode")
       .value("RET_SUCCESS", RET_SUCCESS).value("RET_INVALID_ARGUMENT", RET_INVALID_ARGUMENT)

@@ -9,16 +9,20 @@
 // i.e. multi-query attention with one shared 576/512-wide "KV head".
 //
 // One CTA owns 128 packed query rows (row = (token, head), all G heads of this rank share every staged tile) and
-// one half (256 columns) of the output: the O accumulator of a half takes 256 of the 512 TMEM columns, which
-// leaves room for a double-buffered S/P tile. The sibling CTA of the other half recomputes S (the two run
-// concurrently and share the tile reads through L2). Per 32-token tile:
-//   S = Q K^T      36 tcgen05.mma (9 panels of 64 columns, K = 16 each), K-major operands staged by TMA
+// one half (256 columns) of the output. TMEM (512 columns): the O accumulator of the half (256), a double-buffered
+// 32-token S/P tile (2 x 32) and the first 384 columns of Q as an A operand (192 columns of bf16 pairs). The
+// sibling CTA of the other half recomputes S (the two run concurrently and share the tile reads through L2).
+// Set-up: TMA brings the Q tile in (panels 0..5 into the not yet used KV stages), the softmax warps move those
+// panels row by row into TMEM; only the last three panels (latent 384..511 and the rotary part) stay in shared
+// memory, which leaves room for four KV stages. Per 32-token tile:
+//   S = Q K^T      36 tcgen05.mma (9 panels of 64 columns, K = 16 each): 24 with A from TMEM, 12 with A from
+//                  shared memory; B = the staged tile, K-major (TMA, 128-byte swizzle)
 //   softmax        4 warps, one thread per row (TMEM lane), online maximum with a lazy rescale of O
 //   O += P V       P read from TMEM (bf16 pairs over S's columns), V = MN-major view of the same staged tile
-// The MMA thread issues S of tile j+1 before P V of tile j, so the softmax of one tile overlaps the tensor work
-// of its neighbours. Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..5 softmax +
-// epilogue. Split-KV (decode): grid.x carries `nsplit` ranges of KV tiles whose unnormalised partial outputs
-// (fp32 O, running maximum, row sum) are merged by mla_merge_kernel.
+// The MMA thread issues S of tile j+1 ahead of P V of tile j when it is ready first, so the softmax of one tile
+// overlaps the tensor work of its neighbours. Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner,
+// warps 2..5 softmax + epilogue. Split-KV (decode): grid.x carries `nsplit` ranges of KV tiles whose unnormalised
+// partial outputs (fp32 O, running maximum, row sum) are merged by mla_merge_kernel.
 // Every wait is bounded; a timeout sets the error word and leaves the output untouched.
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
@@ -33,11 +37,15 @@ constexpr int kMlaTok = 32;                   // KV tokens per tile
 constexpr int kMlaLora = 512, kMlaDk = 576;
 constexpr int kMlaPanels = 9;                 // 64-column panels of a 576-wide row
 constexpr int kMlaQPanelBytes = kMlaM * 128;
-constexpr int kMlaQBytes = kMlaPanels * kMlaQPanelBytes;
+constexpr int kMlaQTmemPanels = 6;            // Q columns [0, 384) live in TMEM (192 columns of bf16 pairs)
+constexpr int kMlaQSmemPanels = kMlaPanels - kMlaQTmemPanels;   // columns [384, 576) stay in shared memory
+constexpr int kMlaQBytes = kMlaQSmemPanels * kMlaQPanelBytes;
 constexpr int kMlaKvPanelBytes = kMlaTok * 128;
 constexpr int kMlaKvBytes = kMlaPanels * kMlaKvPanelBytes;
-constexpr int kMlaSmemBytes = kMlaQBytes + 2 * kMlaKvBytes + 1024 + 256;
-constexpr uint32_t kMlaTmemCols = 512;        // O half at [0,256), S/P buffers at 256 and 288
+constexpr int kMlaStages = 4;                 // KV tiles in flight
+constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaKvBytes + 1024 + 256;
+constexpr uint32_t kMlaTmemCols = 512;        // O half [0,256), S/P buffers at 256 and 288, Q at [320, 512)
+static_assert(kMlaQTmemPanels * kMlaQPanelBytes <= kMlaStages * kMlaKvBytes, "Q staging must fit in the KV stages");
 constexpr float kMlaRescaleLog2 = 8.f;
 
 struct MlaParams {
@@ -63,15 +71,16 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mla_smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
   uint8_t* kv_s = smem + kMlaQBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kMlaQBytes + 2 * kMlaKvBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kMlaQBytes + kMlaStages * kMlaKvBytes);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;      // [2]
-  uint64_t* kv_empty = bars + 3;     // [2]
-  uint64_t* s_full = bars + 5;       // [2]
-  uint64_t* p_full = bars + 7;       // [2]
-  uint64_t* pv_done = bars + 9;
-  uint64_t* o_full = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* kv_full = bars + 1;      // [kMlaStages]
+  uint64_t* kv_empty = bars + 5;     // [kMlaStages]
+  uint64_t* s_full = bars + 9;       // [2]
+  uint64_t* p_full = bars + 11;      // [2]
+  uint64_t* pv_done = bars + 13;
+  uint64_t* o_full = bars + 14;
+  uint64_t* q_moved = bars + 15;     // the softmax warps have copied the TMEM part of Q out of the staging area
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,10 +127,9 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); mbar_init(s_full + i, 1); mbar_init(p_full + i, 4);
-    }
-    mbar_init(pv_done, 1); mbar_init(o_full, 1);
+    for (int i = 0; i < kMlaStages; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(s_full + i, 1); mbar_init(p_full + i, 4); }
+    mbar_init(pv_done, 1); mbar_init(o_full, 1); mbar_init(q_moved, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -130,17 +138,21 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base, tmem_s = tmem_base + 256;
+  const uint32_t tmem_o = tmem_base, tmem_s = tmem_base + 256, tmem_q = tmem_base + 320;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&q_map);
       tma_prefetch_desc(&kv_map);
-      mbar_expect_tx(q_full, kMlaQBytes);
+      // Q: panels 0..5 into the (still unused) KV stages as a staging area for their copy to TMEM, 6..8 to their home
+      mbar_expect_tx(q_full, kMlaPanels * kMlaQPanelBytes);
       const int tok0 = q0 + row0 / G;
 #pragma unroll
-      for (int pn = 0; pn < kMlaPanels; ++pn) tma_load_3d(q_s + pn * kMlaQPanelBytes, &q_map, q_full, pn * 64, 0, tok0);
+      for (int pn = 0; pn < kMlaPanels; ++pn) {
+        uint8_t* dst = pn < kMlaQTmemPanels ? kv_s + pn * kMlaQPanelBytes : q_s + (pn - kMlaQTmemPanels) * kMlaQPanelBytes;
+        tma_load_3d(dst, &q_map, q_full, pn * 64, 0, tok0);
+      }
       const int bt = p.block_tokens, br = p.box_rows;
       const int boxes = kMlaTok / br;                       // at most 4 (8-token blocks)
       // block-table entries of a tile are fetched one tile ahead, so that their global-memory latency is not part
@@ -155,15 +167,15 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         }
       };
       fetch(0, blk_next);
-      bool ok = true;
+      bool ok = mbar_wait(q_moved, 0, abort_flag);           // the staging area is free
       for (int j = 0; j < ntiles && ok; ++j) {
-        const int b = j & 1;
+        const int b = j % kMlaStages;
         const int t0 = (tile_lo + j) * kMlaTok;
         const int nbox = min(boxes, (kv_len - t0 + br - 1) / br);
 #pragma unroll
         for (int bx = 0; bx < 4; ++bx) blk[bx] = blk_next[bx];
         if (j + 1 < ntiles) fetch(j + 1, blk_next);
-        if (!mbar_wait(kv_empty + b, ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(kv_empty + b, ((j / kMlaStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
         mbar_expect_tx(kv_full + b, static_cast<uint32_t>(nbox) * br * 128 * kMlaPanels);
         uint8_t* dst = kv_s + b * kMlaKvBytes;
 #pragma unroll
@@ -184,7 +196,8 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(128, kMlaTok, 1, 1);
       constexpr uint32_t idesc_pv = make_idesc(128, 256, 1, 1) | (1u << 16);     // B (= V) is MN-major
-      bool ok = mbar_wait(q_full, 0, abort_flag);
+      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(q_moved, 0, abort_flag);
+      tc_fence_after();
       const uint32_t qb = smem_u32(q_s);
       // S of tile j+1 may be issued ahead of P V of tile j (it then overlaps the softmax of tile j), but whichever
       // of the two becomes ready first goes first: issuing P V as soon as P is ready frees the tile's buffer
@@ -194,30 +207,37 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       while (ok && pv_next < ntiles) {
         bool progress = false;
         if (pv_next < s_next && mbar_try_wait(p_full + (pv_next & 1), (pv_next >> 1) & 1)) {
-          const int j = pv_next, bb = j & 1;
+          const int j = pv_next, bb = j & 1, st = j % kMlaStages;
           tc_fence_after();
-          const uint32_t vb = smem_u32(kv_s + bb * kMlaKvBytes) + half * 4 * kMlaKvPanelBytes;
+          const uint32_t vb = smem_u32(kv_s + st * kMlaKvBytes) + half * 4 * kMlaKvPanelBytes;
 #pragma unroll
           for (int k = 0; k < kMlaTok / 16; ++k) {
             // 16 tokens per MMA: 8 TMEM columns of P (two bf16 each), 16 rows (2 KB per panel) of the tile
             const uint64_t bdesc = make_smem_desc_mn_sw128(vb + k * 2048, kMlaKvPanelBytes);
             mma_f16_ts(tmem_o, tmem_s + 32 * bb + 8 * k, bdesc, idesc_pv, (j | k) != 0);
           }
-          tc_commit(kv_empty + bb);
+          tc_commit(kv_empty + st);
           tc_commit(pv_done);
           if (j == ntiles - 1) tc_commit(o_full);
           ++pv_next;
           progress = true;
-        } else if (s_next < ntiles && s_next <= pv_next + 1 && mbar_try_wait(kv_full + (s_next & 1), (s_next >> 1) & 1)) {
+        } else if (s_next < ntiles && s_next <= pv_next + 1 &&
+                   mbar_try_wait(kv_full + (s_next % kMlaStages), (s_next / kMlaStages) & 1)) {
           // (s_next <= pv_next + 1: the S/P buffer of tile s_next was last read by P V of tile s_next - 2)
           const int bb = s_next & 1;
           tc_fence_after();
-          const uint32_t kb = smem_u32(kv_s + bb * kMlaKvBytes);
+          const uint32_t kb = smem_u32(kv_s + (s_next % kMlaStages) * kMlaKvBytes);
 #pragma unroll
           for (int k = 0; k < 4 * kMlaPanels; ++k) {
-            const uint64_t adesc = make_smem_desc_sw128(qb + (k >> 2) * kMlaQPanelBytes) + 2 * (k & 3);
-            const uint64_t bdesc = make_smem_desc_sw128(kb + (k >> 2) * kMlaKvPanelBytes) + 2 * (k & 3);
-            mma_f16(tmem_s + 32 * bb, adesc, bdesc, idesc_qk, k != 0);
+            const int pn = k >> 2;
+            const uint64_t bdesc = make_smem_desc_sw128(kb + pn * kMlaKvPanelBytes) + 2 * (k & 3);
+            if (pn < kMlaQTmemPanels) {
+              // A (16 Q columns = 8 TMEM columns of bf16 pairs) straight from TMEM: no shared-memory read of Q
+              mma_f16_ts(tmem_s + 32 * bb, tmem_q + 8 * k, bdesc, idesc_qk, k != 0);
+            } else {
+              const uint64_t adesc = make_smem_desc_sw128(qb + (pn - kMlaQTmemPanels) * kMlaQPanelBytes) + 2 * (k & 3);
+              mma_f16(tmem_s + 32 * bb, adesc, bdesc, idesc_qk, k != 0);
+            }
           }
           tc_commit(s_full + bb);
           ++s_next;
@@ -241,8 +261,28 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     const int tok = vr / G, head = vr % G;
     const int limit = active ? past + tok : -1;            // last visible KV position
     float m_used = -CUDART_INF_F, l = 0.f;
-    bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
+    bool ok = mbar_wait(q_full, 0, abort_flag);
+    if (ok) {
+      // this thread's Q row, columns [0, 384): staging area (128-byte-swizzled panels) -> registers -> TMEM, in the
+      // layout the MMA reads an A operand from TMEM (row = lane, two consecutive bf16 per 32-bit column)
+      const int rr = qd * 32 + lane;
+#pragma unroll 1
+      for (int pn = 0; pn < kMlaQTmemPanels; ++pn) {
+        const uint8_t* src = kv_s + pn * kMlaQPanelBytes + rr * 128;
+        uint32_t v[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 q4 = *reinterpret_cast<const uint4*>(src + ((c ^ (rr & 7)) << 4));
+          v[4 * c] = q4.x; v[4 * c + 1] = q4.y; v[4 * c + 2] = q4.z; v[4 * c + 3] = q4.w;
+        }
+        tmem_st32(tmem_q + lane_off + pn * 32, v);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_moved);
+    }
+    for (int j = 0; ok && j < ntiles; ++j) {
       const int b = j & 1;
       const int t0 = (tile_lo + j) * kMlaTok;
       if (!mbar_wait(s_full + b, (j >> 1) & 1, abort_flag)) { ok = false; break; }
@@ -295,7 +335,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         // there; their probabilities are 0, but 0 x NaN would poison O. Zero them before the P V MMA reads them.
         const int first_bad = kv_len - t0;
         const int nchunks = (kMlaTok - first_bad) * (kMlaPanels * 8);      // 16-byte chunks
-        uint8_t* buf = kv_s + b * kMlaKvBytes;
+        uint8_t* buf = kv_s + (j % kMlaStages) * kMlaKvBytes;
         for (int i = threadIdx.x - 64; i < nchunks; i += 128) {
           const int rr = first_bad + i / (kMlaPanels * 8), c = i % (kMlaPanels * 8);
           *reinterpret_cast<uint4*>(buf + (c >> 3) * kMlaKvPanelBytes + rr * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);

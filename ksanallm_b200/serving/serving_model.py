@@ -153,8 +153,45 @@ class ServingModel:
             ne.span_set_sink(prof.trace_export_url)
         if self.llm.rank == 0:
             self.llm.engine.start()
+            self._start_rpc_endpoint()
+
+    def _start_rpc_endpoint(self):
+        """An ``endpoint_type`` other than "python" names a plug-in: ``lib<name>_endpoint.so`` exporting
+        ``Create<Name>Endpoint`` (looked up in the model directory, then on the loader path), which serves requests
+        through its own transport and calls back into this model
+        (src/ksana_llm/endpoints/endpoint_factory.cpp:19-39, src/ksana_llm/service/inference_server.cpp:96-118)."""
+        kind = (self.endpoint_config.type or "python").lower()
+        self.rpc_endpoint = None
+        if kind in ("python", "", "none"):
+            return
+        import json
+        search = self.llm.engine_cfg.model_dir or ""
+        self.rpc_endpoint = ne.EndpointPlugin(kind, search)
+
+        def handler(which: str, body: bytes):
+            try:
+                if which == "forward":
+                    status, out = self.forward(body)
+                    return (200 if status.OK() else 500), (out or b"")
+                req = json.loads(body.decode("utf-8"))
+                status, out = self.generate(inputs=req.get("input_tokens"), generation_config=req.get("sampling_config") or {},
+                                            messages=req.get("messages"))
+                if not status.OK():
+                    return 500, json.dumps({"message": status.message, "code": status.code}).encode()
+                return 200, json.dumps({"output_token_ids": out.output_tokens, "input_token_ids": out.input_tokens,
+                                        "logprobs": out.logprobs}).encode()
+            except Exception as e:  # noqa: BLE001 - a transport plug-in gets an error reply, never an exception
+                return 500, str(e).encode()
+
+        rc = self.rpc_endpoint.start(handler, self.shutdown, self.endpoint_config.host, int(self.endpoint_config.port))
+        if rc != 0:
+            raise RuntimeError(f"endpoint plug-in {self.rpc_endpoint.path} failed to start (code {rc})")
 
     def shutdown(self):
+        ep = getattr(self, "rpc_endpoint", None)
+        if ep is not None:
+            self.rpc_endpoint = None
+            ep.stop()
         if self.llm is not None:
             self.llm.shutdown(stop_followers=True)
         ne.metrics_stop_export()
