@@ -25,6 +25,10 @@ import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
+# Output tok/s of the library-only measuring stick (``--impl baseline``: per-tensor FP8 cuBLASLt GEMMs, SDPA, NCCL,
+# unfused ops) on the same batch, by GPU count; the numbers BASELINE.md lists. ``vs_baseline`` divides by them.
+BASELINE_TOK_S = {1: 576.2}
+
 REFERENCE_UNAVAILABLE = ("refused by a safety check: installing the reference (pip install of /root/reference, which "
                          "runs its setup.py / CMake build) was denied in this environment, so baseline/_ref does not exist")
 
@@ -263,7 +267,9 @@ def main():
         res = {
             "metric": "output tok/s (offline, max over ranks) at Llama-3-70B fp8 TP%d" % world,
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / BASELINE_TOK_S[world]) if (world in BASELINE_TOK_S and not args.layers and
+                                                               (B, S_in, S_out) == (64, 2048, 256)) else None,
             "dtype": ("fp8-e4m3 block-scaled weights (128x128 blocks, fp32 scales holding powers of two so that the tensor "
                       "cores apply them), fp8-e4m3 1x128-scaled GEMM inputs, bf16 activations and KV cache"
                       if args.scale_mode == "ue8m0" else
