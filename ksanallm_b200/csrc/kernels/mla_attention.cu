@@ -10,13 +10,15 @@
 //
 // One CTA owns 128 packed query rows (row = (token, head), all G heads of this rank share every staged tile) and
 // one half (256 columns) of the output. TMEM (512 columns): the O accumulator of the half (256), a double-buffered
-// 32-token S/P tile (2 x 32) and the first 384 columns of Q as an A operand (192 columns of bf16 pairs). The
+// 64-token S/P tile (2 x 64) and the first 256 columns of Q as an A operand (128 columns of bf16 pairs). The
 // sibling CTA of the other half recomputes S (the two run concurrently and share the tile reads through L2).
-// Set-up: TMA brings the Q tile in (panels 0..5 into the not yet used KV stages), the softmax warps move those
-// panels row by row into TMEM; only the last three panels (latent 384..511 and the rotary part) stay in shared
-// memory, which leaves room for four KV stages. Per 32-token tile:
-//   S = Q K^T      36 tcgen05.mma (9 panels of 64 columns, K = 16 each): 24 with A from TMEM, 12 with A from
-//                  shared memory; B = the staged tile, K-major (TMA, 128-byte swizzle)
+// Set-up: TMA brings the Q tile in (panels 0..3 into the not yet used KV stages), the softmax warps move those
+// panels row by row into TMEM; the other five panels (latent 256..511 and the rotary part) stay in shared
+// memory next to two 64-token KV stages. Per tile:
+//   S = Q K^T      36 tcgen05.mma (9 panels of 64 columns, K = 16 each, N = 64): 16 with A from TMEM, 20 with A from
+//                  shared memory; B = the staged tile, K-major (TMA, 128-byte swizzle). The 36 MMAs accumulate into
+//                  one tile and are latency-bound as a chain, which is why the tile is 64 tokens wide and not 32
+//                  (measured: same time per tile at either width).
 //   softmax        4 warps, one thread per row (TMEM lane), online maximum with a lazy rescale of O
 //   O += P V       P read from TMEM (bf16 pairs over S's columns), V = MN-major view of the same staged tile
 // The MMA thread issues S of tile j+1 ahead of P V of tile j when it is ready first, so the softmax of one tile
@@ -33,18 +35,19 @@ namespace ksana {
 typedef __nv_bfloat16 bf16;
 constexpr int kMlaThreads = 192;
 constexpr int kMlaM = 128;                    // packed query rows per CTA
-constexpr int kMlaTok = 32;                   // KV tokens per tile
+constexpr int kMlaTok = 64;                   // KV tokens per tile
 constexpr int kMlaLora = 512, kMlaDk = 576;
 constexpr int kMlaPanels = 9;                 // 64-column panels of a 576-wide row
 constexpr int kMlaQPanelBytes = kMlaM * 128;
-constexpr int kMlaQTmemPanels = 6;            // Q columns [0, 384) live in TMEM (192 columns of bf16 pairs)
+constexpr int kMlaQTmemPanels = 4;            // Q columns [0, 256) live in TMEM (128 columns of bf16 pairs)
 constexpr int kMlaQSmemPanels = kMlaPanels - kMlaQTmemPanels;   // columns [384, 576) stay in shared memory
 constexpr int kMlaQBytes = kMlaQSmemPanels * kMlaQPanelBytes;
 constexpr int kMlaKvPanelBytes = kMlaTok * 128;
 constexpr int kMlaKvBytes = kMlaPanels * kMlaKvPanelBytes;
-constexpr int kMlaStages = 4;                 // KV tiles in flight
+constexpr int kMlaStages = 2;                 // KV tiles in flight
 constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaKvBytes + 1024 + 256;
-constexpr uint32_t kMlaTmemCols = 512;        // O half [0,256), S/P buffers at 256 and 288, Q at [320, 512)
+constexpr uint32_t kMlaTmemCols = 512;        // O half [0,256), S/P buffers at 256 and 320, Q at [384, 512)
+constexpr int kMlaMaxBoxes = kMlaTok / 8;      // TMA boxes per tile with the smallest (8-token) cache blocks
 static_assert(kMlaQTmemPanels * kMlaQPanelBytes <= kMlaStages * kMlaKvBytes, "Q staging must fit in the KV stages");
 constexpr float kMlaRescaleLog2 = 8.f;
 
@@ -138,7 +141,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base, tmem_s = tmem_base + 256, tmem_q = tmem_base + 320;
+  const uint32_t tmem_o = tmem_base, tmem_s = tmem_base + 256, tmem_q = tmem_base + 256 + 2 * kMlaTok;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -154,14 +157,14 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         tma_load_3d(dst, &q_map, q_full, pn * 64, 0, tok0);
       }
       const int bt = p.block_tokens, br = p.box_rows;
-      const int boxes = kMlaTok / br;                       // at most 4 (8-token blocks)
+      const int boxes = kMlaTok / br;                       // at most kMlaMaxBoxes (8-token blocks)
       // block-table entries of a tile are fetched one tile ahead, so that their global-memory latency is not part
       // of the chain "buffer freed -> TMA issued"
-      int blk[4], blk_next[4];
-      auto fetch = [&](int j, int (&dst)[4]) {
+      int blk[kMlaMaxBoxes], blk_next[kMlaMaxBoxes];
+      auto fetch = [&](int j, int (&dst)[kMlaMaxBoxes]) {
         const int t0 = (tile_lo + j) * kMlaTok;
 #pragma unroll
-        for (int bx = 0; bx < 4; ++bx) {
+        for (int bx = 0; bx < kMlaMaxBoxes; ++bx) {
           const int t = t0 + bx * br;
           dst[bx] = (bx < boxes && t < kv_len) ? __ldg(table + t / bt) : 0;
         }
@@ -173,13 +176,13 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         const int t0 = (tile_lo + j) * kMlaTok;
         const int nbox = min(boxes, (kv_len - t0 + br - 1) / br);
 #pragma unroll
-        for (int bx = 0; bx < 4; ++bx) blk[bx] = blk_next[bx];
+        for (int bx = 0; bx < kMlaMaxBoxes; ++bx) blk[bx] = blk_next[bx];
         if (j + 1 < ntiles) fetch(j + 1, blk_next);
         if (!mbar_wait(kv_empty + b, ((j / kMlaStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
         mbar_expect_tx(kv_full + b, static_cast<uint32_t>(nbox) * br * 128 * kMlaPanels);
         uint8_t* dst = kv_s + b * kMlaKvBytes;
 #pragma unroll
-        for (int bx = 0; bx < 4; ++bx) {
+        for (int bx = 0; bx < kMlaMaxBoxes; ++bx) {
           if (bx < nbox) {
             const int t = t0 + bx * br;
             const long long r0 = static_cast<long long>(blk[bx]) * p.rows_per_block + (t % bt);
@@ -214,7 +217,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           for (int k = 0; k < kMlaTok / 16; ++k) {
             // 16 tokens per MMA: 8 TMEM columns of P (two bf16 each), 16 rows (2 KB per panel) of the tile
             const uint64_t bdesc = make_smem_desc_mn_sw128(vb + k * 2048, kMlaKvPanelBytes);
-            mma_f16_ts(tmem_o, tmem_s + 32 * bb + 8 * k, bdesc, idesc_pv, (j | k) != 0);
+            mma_f16_ts(tmem_o, tmem_s + kMlaTok * bb + 8 * k, bdesc, idesc_pv, (j | k) != 0);
           }
           tc_commit(kv_empty + st);
           tc_commit(pv_done);
@@ -233,10 +236,10 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
             const uint64_t bdesc = make_smem_desc_sw128(kb + pn * kMlaKvPanelBytes) + 2 * (k & 3);
             if (pn < kMlaQTmemPanels) {
               // A (16 Q columns = 8 TMEM columns of bf16 pairs) straight from TMEM: no shared-memory read of Q
-              mma_f16_ts(tmem_s + 32 * bb, tmem_q + 8 * k, bdesc, idesc_qk, k != 0);
+              mma_f16_ts(tmem_s + kMlaTok * bb, tmem_q + 8 * k, bdesc, idesc_qk, k != 0);
             } else {
               const uint64_t adesc = make_smem_desc_sw128(qb + (pn - kMlaQTmemPanels) * kMlaQPanelBytes) + 2 * (k & 3);
-              mma_f16(tmem_s + 32 * bb, adesc, bdesc, idesc_qk, k != 0);
+              mma_f16(tmem_s + kMlaTok * bb, adesc, bdesc, idesc_qk, k != 0);
             }
           }
           tc_commit(s_full + bb);
@@ -287,12 +290,14 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const int t0 = (tile_lo + j) * kMlaTok;
       if (!mbar_wait(s_full + b, (j >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      uint32_t r[32];
-      tmem_ld32(tmem_s + 32 * b + lane_off, r);
+      uint32_t r[kMlaTok];
+#pragma unroll
+      for (int c = 0; c < kMlaTok / 32; ++c)
+        tmem_ld32(tmem_s + kMlaTok * b + lane_off + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
       tmem_ld_wait();
       float mx = -CUDART_INF_F;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < kMlaTok; ++i) {
         const float v = (t0 + i <= limit) ? __uint_as_float(r[i]) * p.scale_log2 : -CUDART_INF_F;
         r[i] = __float_as_uint(v);
         mx = fmaxf(mx, v);
@@ -319,16 +324,17 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       }
       m_used = m_new;
       const float mref = (m_used == -CUDART_INF_F) ? 0.f : m_used;
-      uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
+      for (int i = 0; i < kMlaTok; i += 2) {
         const float p0 = mla_exp2(__uint_as_float(r[i]) - mref);
         const float p1 = mla_exp2(__uint_as_float(r[i + 1]) - mref);
         l += p0 + p1;
         __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        pk[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);
+        r[i >> 1] = *reinterpret_cast<uint32_t*>(&pb);          // in place: slot i/2 has already been consumed
       }
-      tmem_st16(tmem_s + 32 * b + lane_off, pk);
+#pragma unroll
+      for (int c = 0; c < kMlaTok / 32; ++c)
+        tmem_st16(tmem_s + kMlaTok * b + lane_off + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&r[c * 16]));
       tmem_st_wait();
       if (t0 + kMlaTok > kv_len) {
         // last tile of the sequence: rows past the sequence end hold stale shared memory or whatever the cache has

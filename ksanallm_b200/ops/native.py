@@ -457,11 +457,11 @@ def mla_rope_append(q, nope, kv, norm_w, eps, positions, slots, cos_sin, qfull, 
 
 def mla_splits(num_seqs: int, max_q_len: int, max_kv: int, sms: int = 148) -> int:
     """KV splits for the latent-attention kernel: only pure decode steps split; the count minimises the number of
-    CTA waves times the tiles per CTA, and a split never holds fewer than 8 tiles of 32 tokens."""
+    CTA waves times the tiles per CTA, and a split never holds fewer than 4 tiles of 64 tokens."""
     if max_q_len != 1 or num_seqs <= 0:
         return 1
-    tiles = max(1, (max_kv + 31) // 32)
-    most = max(1, min(32, tiles // 8))
+    tiles = max(1, (max_kv + 63) // 64)
+    most = max(1, min(32, tiles // 4))
     best, best_cost = 1, None
     for n in range(1, most + 1):
         waves = (2 * num_seqs * n + sms - 1) // sms            # one CTA per SM, two output halves per sequence

@@ -75,3 +75,31 @@ def test_tp2_moe_fused_combine(tmp_path, arch):
     assert rel(nccl["first"], single["first"]) < 4e-2
     assert rel(fused["first"], single["first"]) < 4e-2
     assert fused["graph_replays"] > 0
+
+
+def _launch_worker(script, nproc, out, port, *args):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", script), out, "cuda", *map(str, args)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=200)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return torch.load(out)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pipeline_two_stages_over_nccl_p2p(tmp_path):
+    """Two pipeline stages on two GPUs (hidden states by NCCL send / recv, two micro-batches in flight)."""
+    single = _launch_worker("pp_worker.py", 1, str(tmp_path / "single.pt"), 29661, 1, 1)
+    pp = _launch_worker("pp_worker.py", 2, str(tmp_path / "pp.pt"), 29662, 2, 2)
+    assert pp["layers"] == (0, 1) and pp["sent_bytes"] > 0
+    assert rel(pp["first"], single["first"]) < 3e-2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_attention_dp_with_expert_parallel_over_nccl(tmp_path):
+    """Sequences split over two GPUs, routed experts split over the same two (all-gather dispatch, reduce-scatter
+    combine)."""
+    single = _launch_worker("dp_worker.py", 1, str(tmp_path / "single.pt"), 29671)
+    dp = _launch_worker("dp_worker.py", 2, str(tmp_path / "dp.pt"), 29672)
+    assert dp["experts"] == (0, 4) and dp["gathered_bytes"] > 0
+    assert rel(dp["first"], single["first"]) < 4e-2
