@@ -156,6 +156,11 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
         uint8_t* dst = pn < kMlaQTmemPanels ? kv_s + pn * kMlaQPanelBytes : q_s + (pn - kMlaQTmemPanels) * kMlaQPanelBytes;
         tma_load_3d(dst, &q_map, q_full, pn * 64, 0, tok0);
       }
+    }
+    __syncwarp();
+    {
+      // KV tiles: the whole warp runs the loop; lane 0 owns the barrier traffic, lanes 0..8 each issue the boxes of
+      // one 64-column panel (36 box copies per tile from a single thread were a microsecond of issue time)
       const int bt = p.block_tokens, br = p.box_rows;
       const int boxes = kMlaTok / br;                       // at most kMlaMaxBoxes (8-token blocks)
       // block-table entries of a tile are fetched one tile ahead, so that their global-memory latency is not part
@@ -171,24 +176,26 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       };
       fetch(0, blk_next);
       bool ok = mbar_wait(q_moved, 0, abort_flag);           // the staging area is free
-      for (int j = 0; j < ntiles && ok; ++j) {
+      for (int j = 0; j < ntiles; ++j) {
         const int b = j % kMlaStages;
         const int t0 = (tile_lo + j) * kMlaTok;
         const int nbox = min(boxes, (kv_len - t0 + br - 1) / br);
 #pragma unroll
         for (int bx = 0; bx < kMlaMaxBoxes; ++bx) blk[bx] = blk_next[bx];
         if (j + 1 < ntiles) fetch(j + 1, blk_next);
-        if (!mbar_wait(kv_empty + b, ((j / kMlaStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(kv_full + b, static_cast<uint32_t>(nbox) * br * 128 * kMlaPanels);
-        uint8_t* dst = kv_s + b * kMlaKvBytes;
+        ok = ok && mbar_wait(kv_empty + b, ((j / kMlaStages) & 1) ^ 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        if (lane == 0) mbar_expect_tx(kv_full + b, static_cast<uint32_t>(nbox) * br * 128 * kMlaPanels);
+        __syncwarp();
+        if (lane < kMlaPanels) {
+          uint8_t* dst = kv_s + b * kMlaKvBytes + lane * kMlaKvPanelBytes;
 #pragma unroll
-        for (int bx = 0; bx < kMlaMaxBoxes; ++bx) {
-          if (bx < nbox) {
-            const int t = t0 + bx * br;
-            const long long r0 = static_cast<long long>(blk[bx]) * p.rows_per_block + (t % bt);
-#pragma unroll
-            for (int pn = 0; pn < kMlaPanels; ++pn)
-              tma_load_2d(dst + pn * kMlaKvPanelBytes + bx * br * 128, &kv_map, kv_full + b, pn * 64, static_cast<int>(r0));
+          for (int bx = 0; bx < kMlaMaxBoxes; ++bx) {
+            if (bx < nbox) {
+              const int t = t0 + bx * br;
+              const long long r0 = static_cast<long long>(blk[bx]) * p.rows_per_block + (t % bt);
+              tma_load_2d(dst + bx * br * 128, &kv_map, kv_full + b, lane * 64, static_cast<int>(r0));
+            }
           }
         }
       }
@@ -204,12 +211,13 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const uint32_t qb = smem_u32(q_s);
       // S of tile j+1 may be issued ahead of P V of tile j (it then overlaps the softmax of tile j), but whichever
       // of the two becomes ready first goes first: issuing P V as soon as P is ready frees the tile's buffer
-      // early, which is what gives the next TMA load its lead time.
+      // early, which is what gives the next TMA load its lead time. The polls are test_wait (non-blocking): a
+      // try_wait on the barrier that is not ready yet suspends the thread and hides the other one becoming ready.
       int s_next = 0, pv_next = 0;         // next tile whose S / P V has not been issued
       uint32_t idle = 0;
       while (ok && pv_next < ntiles) {
         bool progress = false;
-        if (pv_next < s_next && mbar_try_wait(p_full + (pv_next & 1), (pv_next >> 1) & 1)) {
+        if (pv_next < s_next && mbar_test_wait(p_full + (pv_next & 1), (pv_next >> 1) & 1)) {
           const int j = pv_next, bb = j & 1, st = j % kMlaStages;
           tc_fence_after();
           const uint32_t vb = smem_u32(kv_s + st * kMlaKvBytes) + half * 4 * kMlaKvPanelBytes;
@@ -225,7 +233,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
           ++pv_next;
           progress = true;
         } else if (s_next < ntiles && s_next <= pv_next + 1 &&
-                   mbar_try_wait(kv_full + (s_next % kMlaStages), (s_next / kMlaStages) & 1)) {
+                   mbar_test_wait(kv_full + (s_next % kMlaStages), (s_next / kMlaStages) & 1)) {
           // (s_next <= pv_next + 1: the S/P buffer of tile s_next was last read by P V of tile s_next - 2)
           const int bb = s_next & 1;
           tc_fence_after();

@@ -51,6 +51,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a phase (try_wait may suspend the thread for a hardware-defined time slice).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. `abort_flag` is a shared-memory word any role sets when it has
 // given up; every waiter polls it so that one timeout unwinds the whole CTA.
 // Budget: kWaitPolls polls; try_wait itself blocks for a hardware-defined slice,
