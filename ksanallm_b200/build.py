@@ -109,11 +109,27 @@ def build_engine(force: bool = False) -> Path:
     return out
 
 
+def build_host_stress(sanitizer: str = "thread") -> Path:
+    """Stand-alone stress driver of the scheduler / cache manager / control plane (csrc/engine/host_stress.cpp)
+    compiled with -fsanitize=<thread|address|undefined>; run the returned binary, it exits 0 when clean."""
+    OBJ.mkdir(exist_ok=True)
+    edir = CSRC / "engine"
+    srcs = [edir / n for n in ("host_stress.cpp", "scheduler.cpp", "cache_manager.cpp", "control_channel.cpp")]
+    out = OBJ / f"host_stress_{sanitizer}"
+    if _newer(out, [*srcs, *sorted(edir.glob("*.h"))]):
+        _run(["g++", "-O1", "-g", "-std=c++17", "-pthread", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer",
+              "-DKSANA_NO_PYBIND", "-I", str(edir), *map(str, srcs), "-o", str(out)])
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False):
     return build_kernels(force, verbose), build_engine(force)
 
 
 if __name__ == "__main__":
+    if "--sanitizer" in sys.argv:
+        print(build_host_stress(sys.argv[sys.argv.index("--sanitizer") + 1]))
+        sys.exit(0)
     k, e = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(k)
     print(e)

@@ -5,8 +5,10 @@
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <poll.h>
+#ifndef KSANA_NO_PYBIND
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
+#endif
 #include <sys/socket.h>
 #include <unistd.h>
 
@@ -419,6 +421,7 @@ bool ControlWorker::RecvBroadcast(std::string* bytes, int timeout_ms) {
   return true;
 }
 
+#ifndef KSANA_NO_PYBIND
 void BindControlChannel(pybind11::module_& m) {
   namespace py = pybind11;
   m.def("split_layers", &SplitLayers);
@@ -456,5 +459,7 @@ void BindControlChannel(pybind11::module_& m) {
       .def("shutdown_requested", &ControlWorker::shutdown_requested)
       .def("stop", &ControlWorker::Stop, py::call_guard<py::gil_scoped_release>());
 }
+
+#endif  // KSANA_NO_PYBIND
 
 }  // namespace ksana

@@ -1,0 +1,152 @@
+// Stand-alone stress driver of the host runtime for sanitizer builds (ThreadSanitizer / AddressSanitizer):
+//   python -m ksanallm_b200.build --sanitizer thread     ->  ksanallm_b200/build/host_stress_thread
+// 1. Scheduler + cache manager under concurrency: client threads add and abort requests while one engine thread
+//    plans steps and feeds back fake tokens; a small block pool forces preemption, swap-out / swap-in and prefix
+//    sharing. At the end every request is finished and the block accounting invariants hold.
+// 2. Control plane: a master and two workers over localhost TCP (registration, barrier, layer assignment,
+//    block-number consensus, step-plan broadcast, heartbeats, cluster shutdown), each on its own thread.
+// The reference ships no sanitizer configuration (only gcov flags: CMakeLists.txt WITH_TESTING); its scheduler is
+// guarded by two hand-placed mutexes (src/ksana_llm/batch_scheduler/state/batch_state.h).
+#include <atomic>
+#include <cstdio>
+#include <random>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "control_channel.h"
+#include "scheduler.h"
+
+using namespace ksana;
+
+static int g_failures = 0;
+#define EXPECT(cond)                                                         \
+  do {                                                                       \
+    if (!(cond)) { std::fprintf(stderr, "FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond); ++g_failures; } \
+  } while (0)
+
+static void SchedulerStress(int preempt_mode) {
+  SchedulerConfig cfg;
+  cfg.max_batch_size = 16;
+  cfg.max_step_tokens = 256;
+  cfg.max_token_len = 224;
+  cfg.launch_block_threshold = 0.25f;     // admit eagerly so that growing sequences run out of blocks
+  cfg.max_waiting_queue_len = 4096;
+  cfg.enable_prefix_cache = true;
+  cfg.split_fuse_token_num = 64;
+  cfg.preempt_mode = preempt_mode;
+  cfg.block_token_num = 16;
+  cfg.eos_token_ids = {2};
+  Scheduler sched(cfg, /*device blocks*/ 40, /*host blocks*/ preempt_mode == 0 ? 64 : 0);
+  constexpr int kClients = 4, kPerClient = 40;
+  std::atomic<int> added{0}, finished{0}, rejected{0};
+  std::atomic<bool> clients_done{false};
+  std::vector<std::thread> clients;
+  for (int c = 0; c < kClients; ++c) {
+    clients.emplace_back([&, c] {
+      std::mt19937 rng(1234 + c);
+      for (int i = 0; i < kPerClient; ++i) {
+        const int64_t req_id = c * 1000 + i + 1;
+        std::vector<int> prompt(8 + rng() % 90);
+        for (size_t k = 0; k < prompt.size(); ++k) prompt[k] = 3 + (k < 32 ? static_cast<int>(k) : static_cast<int>(rng() % 200));
+        SamplingConfig sc;
+        sc.max_new_tokens = 16 + static_cast<int>(rng() % 100);
+        sc.ignore_eos = (rng() % 2) == 0;
+        if (rng() % 8 == 0) sc.num_return_sequences = 2, sc.topk = 4;
+        std::vector<int64_t> ids;
+        Status st = sched.AddRequest(req_id, prompt, sc, &ids);
+        if (st.ok()) {
+          added += static_cast<int>(ids.size());
+          if (rng() % 10 == 0) sched.Abort(req_id);
+        } else {
+          ++rejected;
+        }
+        if (i % 8 == 0) std::this_thread::sleep_for(std::chrono::microseconds(200));
+      }
+    });
+  }
+  std::thread engine([&] {
+    std::mt19937 rng(99);
+    int idle_rounds = 0;
+    while (idle_rounds < 2000) {
+      StepPlan plan;
+      const bool run = sched.Schedule(&plan);
+      for (const SeqEvent& e : plan.events) finished += e.finished ? 1 : 0;
+      if (!run) {
+        if (clients_done.load() && sched.Idle()) break;
+        ++idle_rounds;
+        std::this_thread::sleep_for(std::chrono::microseconds(100));
+        continue;
+      }
+      idle_rounds = 0;
+      std::vector<SampledToken> sampled(plan.sample_seq_ids.size());
+      for (auto& t : sampled) t.token = (rng() % 200 == 0) ? 2 : 3 + static_cast<int>(rng() % 200);
+      std::vector<SeqEvent> events;
+      sched.PostStep(plan, sampled, &events);
+      for (const SeqEvent& e : events) finished += e.finished ? 1 : 0;
+    }
+  });
+  for (auto& t : clients) t.join();
+  clients_done = true;
+  engine.join();
+  std::string why;
+  EXPECT(sched.CheckInvariants(&why));
+  if (!why.empty()) std::fprintf(stderr, "invariants: %s\n", why.c_str());
+  EXPECT(sched.Idle());
+  EXPECT(finished.load() == added.load());
+  const SchedulerStats st = sched.GetStats();
+  std::printf("scheduler stress (preempt mode %d): %d sequences, %d rejected, %lld steps, %lld swap preemptions, %lld recompute "
+              "preemptions, %lld prefix hit tokens\n", preempt_mode, added.load(), rejected.load(),
+              static_cast<long long>(st.steps), static_cast<long long>(st.preempt_swap),
+              static_cast<long long>(st.preempt_recompute), static_cast<long long>(st.cache.prefix_hit_tokens));
+}
+
+static void ControlPlaneStress() {
+  ControlMaster master("127.0.0.1", 0, 3, /*heartbeat interval ms*/ 50, /*timeout ms*/ 2000);
+  const int port = master.port();
+  std::atomic<int> got{0};
+  std::vector<std::thread> workers;
+  for (int r = 1; r <= 2; ++r) {
+    workers.emplace_back([&, r] {
+      ControlWorker w("127.0.0.1", port, r, 50, 2000);
+      EXPECT(w.Connect(5000));
+      EXPECT(w.Barrier(5000));
+      auto range = w.GetLayers(5000);
+      EXPECT(range.first >= 0 && range.second >= range.first);
+      EXPECT(w.SyncBlockNum(100 + r, 5000) == 100);
+      for (int i = 0; i < 20; ++i) {
+        std::string bytes;
+        EXPECT(w.RecvBroadcast(&bytes, 5000));
+        if (bytes.size() == 64 + static_cast<size_t>(i)) ++got;
+      }
+      for (int i = 0; i < 100 && !w.shutdown_requested(); ++i) std::this_thread::sleep_for(std::chrono::milliseconds(20));
+      EXPECT(w.shutdown_requested());
+      w.Stop();
+    });
+  }
+  EXPECT(master.WaitForNodes(5000));
+  EXPECT(master.Barrier(5000));
+  auto ranges = master.AssignLayers(10, 5000);
+  EXPECT(ranges.size() == 3);
+  EXPECT(master.SyncBlockNum(100, 5000) == 100);
+  for (int i = 0; i < 20; ++i) EXPECT(master.Broadcast(std::string(64 + i, 'x')));
+  std::this_thread::sleep_for(std::chrono::milliseconds(200));      // a few heartbeats in both directions
+  EXPECT(master.alive() && master.FailedNodes().empty());
+  master.ShutdownCluster();
+  for (auto& t : workers) t.join();
+  master.Stop();
+  EXPECT(got.load() == 40);
+  std::printf("control plane stress: %d broadcasts received\n", got.load());
+}
+
+int main() {
+  SchedulerStress(0);
+  SchedulerStress(1);
+  ControlPlaneStress();
+  if (g_failures) {
+    std::fprintf(stderr, "%d check(s) failed\n", g_failures);
+    return 1;
+  }
+  std::printf("host stress ok\n");
+  return 0;
+}
