@@ -5,20 +5,23 @@ Request:  {"requests": [{"prompt" | "input_tokens", "input_refit_embedding"?, "r
 Response: {"responses": [{"input_token_ids": [...], "response": [{"target_name", "tensor":
             {"data": bytes, "shape": [...], "dtype": "float32"}}]}], "message": str, "code": int}
 (src/ksana_llm/utils/request_serial.h:15-66, src/ksana_llm/utils/request_packer.cpp:1-124).
+Decoding, validation and encoding run in the native runtime (csrc/engine/request_packer.cpp); this module maps the
+decoded tree to engine requests and tensors to their wire form.
 """
 from __future__ import annotations
 
 from typing import Dict, List, Tuple
 
-import msgpack
 import numpy as np
 import torch
+
+from ..utils import native_engine as ne
 
 _DTYPES = {torch.float32: "float32", torch.float16: "float16", torch.bfloat16: "bfloat16", torch.int32: "int32"}
 
 
 def unpack_requests(data: bytes, tokenizer=None) -> List[dict]:
-    doc = msgpack.unpackb(data, raw=False)
+    doc = ne.unpack_forward_body(bytes(data))          # native decode + validation (raises ValueError)
     out = []
     for r in doc.get("requests", []):
         tokens = r.get("input_tokens")
@@ -55,7 +58,7 @@ def pack_responses(items: List[Tuple[List[int], Dict[str, torch.Tensor]]], code:
     for tokens, resp in items:
         responses.append({"input_token_ids": list(tokens),
                           "response": [{"target_name": k, "tensor": pack_tensor(v)} for k, v in resp.items()]})
-    return msgpack.packb({"responses": responses, "message": message, "code": code}, use_bin_type=True)
+    return ne.msgpack_pack({"responses": responses, "message": message, "code": code})
 
 
 def unpack_tensor(d: dict) -> np.ndarray:

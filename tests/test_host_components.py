@@ -293,3 +293,33 @@ def test_kv_scale_file(tmp_path):
     p = tmp_path / "kv_cache_scales.json"
     p.write_text(json.dumps({"kv_cache": {"dtype": "float8_e4m3fn", "scaling_factor": {"0": {"0": 0.5, "1": 0.25}}}}))
     assert cfgmod.load_kv_scales(str(p), 2) == [[0.5, 0.5], [0.25, 0.25]]
+
+
+def test_native_msgpack_matches_the_python_codec_and_validates_forward_bodies():
+    import msgpack
+    import pytest
+    from ksanallm_b200.utils import native_engine as ne
+    docs = [None, True, 0, 127, 128, 255, 256, 65535, 65536, 2**32, 2**63 - 1, 2**64 - 1, -1, -32, -33, -129, -32769, -2**31 - 1,
+            -2**63, 1.5, -0.25, "", "héllo", "x" * 40, "y" * 300, b"", b"\x00\x01" * 200, [], [1, [2, [3]]], list(range(20)),
+            {"a": 1, "b": {"c": [1.0, None, b"zz"]}}, {str(i): i for i in range(20)}]
+    for d in docs:
+        packed = ne.msgpack_pack(d)
+        assert msgpack.unpackb(packed, raw=False, strict_map_key=False) == d
+        assert ne.msgpack_unpack(msgpack.packb(d, use_bin_type=True)) == d
+    assert ne.msgpack_unpack(msgpack.packb(1.5, use_single_float=True)) == 1.5
+    big = {"requests": [{"input_tokens": list(range(70000)), "request_target": [{"target_name": "logits"}]}]}
+    assert ne.unpack_forward_body(msgpack.packb(big))["requests"][0]["input_tokens"][-1] == 69999
+    for bad in (b"\xc1", b"\x92\x01", msgpack.packb(1) + b"\x00", b"\xd4\x01\x00"):
+        with pytest.raises(RuntimeError):
+            ne.msgpack_unpack(bad)
+    ok = {"requests": [{"input_tokens": [1, 2, 3], "request_target": [
+        {"target_name": "transformer", "slice_pos": [[0, 1]], "token_reduce_mode": "GATHER_ALL"}]}]}
+    assert ne.unpack_forward_body(msgpack.packb(ok)) == ok
+    for broken, why in ((dict(requests=[]), "no requests"),
+                        (dict(requests=[{"input_tokens": [1], "request_target": []}]), "request_target is empty"),
+                        (dict(requests=[{"request_target": [{"target_name": "logits"}]}]), "input_tokens or a prompt"),
+                        (dict(requests=[{"input_tokens": [1], "request_target": [{"target_name": "bogus"}]}]), "unknown target_name"),
+                        (dict(requests=[{"input_tokens": [1], "request_target": [{"target_name": "logits", "slice_pos": [[1]]}]}]),
+                         "slice_pos")):
+        with pytest.raises(ValueError, match=why):
+            ne.unpack_forward_body(msgpack.packb(broken))
