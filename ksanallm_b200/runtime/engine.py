@@ -23,6 +23,7 @@ import torch
 from ..config import EngineConfig, ModelConfig
 from ..models.common import StepInput
 from ..ops import dispatch as ops
+from ..ops import checks as _checks
 from ..ops import native
 from ..utils import native_engine as ne
 from .sampler import Sampler, SamplingParams
@@ -261,6 +262,8 @@ class ModelRunner:
             if out is not None:
                 return out
         step = self.build_step(plan, extra)
+        if _checks.enabled():
+            _checks.check_step(step, self.model)
         if self.pipeline is not None:
             return self.pipeline.forward(step, plan)
         return self.model.forward(step)

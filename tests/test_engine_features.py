@@ -133,3 +133,39 @@ def test_swap_under_pressure_keeps_results():
     assert [r.outputs[0].tokens for r in pressed] == [r.outputs[0].tokens for r in calm]
     st = tight.scheduler.stats()
     assert st["preempt_swap"] > 0 and st["swap_in"] > 0
+
+
+def test_debug_input_checks_catch_bad_indices(monkeypatch):
+    """KSANA_CHECK_INPUTS=1: every step of a normal run passes the host-side validation; corrupted metadata is
+    reported before any kernel would consume it."""
+    import torch
+    from ksanallm_b200.ops import checks
+    monkeypatch.setenv("KSANA_CHECK_INPUTS", "1")
+    eng = tiny_engine(enable_auto_prefix_cache=True, split_fuse_token_num=16)
+    steps = []
+    real = eng.runner.build_step
+
+    def spy(plan, extra=None):
+        st = real(plan, extra)
+        steps.append(st)
+        return st
+
+    eng.runner.build_step = spy
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 300, (n,), generator=g).tolist() for n in (40, 7, 23)]
+    reqs = eng.generate(prompts, sampling(max_new_tokens=5, ignore_eos=True))
+    assert all(len(r.outputs[0].tokens) == 5 for r in reqs) and len(steps) > 3
+    model = eng.runner.model
+    nb, bt = model.kv_cache.shape[0], model.block_tokens
+    good = steps[0]
+    assert checks.step_violations(good, nb, bt, 300, 512) == []
+    import dataclasses
+    bad_table = dataclasses.replace(good, block_table=good.block_table.clone())
+    bad_table.block_table[0, 0] = nb + 5
+    assert any("block id outside" in v for v in checks.step_violations(bad_table, nb, bt, 300, 512))
+    bad_ids = dataclasses.replace(good, input_ids=good.input_ids.clone())
+    bad_ids.input_ids[0] = 300
+    assert any("token id outside" in v for v in checks.step_violations(bad_ids, nb, bt, 300, 512))
+    bad_slots = dataclasses.replace(good, slots=good.slots.clone())
+    bad_slots.slots[1] = bad_slots.slots[0]
+    assert any("same cache slot" in v or "says otherwise" in v for v in checks.step_violations(bad_slots, nb, bt, 300, 512))

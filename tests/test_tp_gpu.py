@@ -63,17 +63,20 @@ def test_tp4_fused(tmp_path):
     assert rel(fused["first"], single["first"]) < 3e-2
 
 
+@pytest.fixture(scope="module")
+def moe_single(tmp_path_factory):
+    return _launch(1, str(tmp_path_factory.mktemp("moe") / "single.pt"), "nccl", "auto", 29651, arch="moe")
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("arch", ["moe", "moe_ep"])
-def test_tp2_moe_fused_combine(tmp_path, arch):
+def test_tp2_moe_fused_combine(tmp_path, moe_single, arch):
     """MoE layers on the fused path: each rank's expert outputs are combined into its peer-visible slot and the
     cross-rank sum + residual + norm is the reduce kernel (experts sliced by tensor parallelism, or whole experts
-    per rank with expert parallelism)."""
-    single = _launch(1, str(tmp_path / "single.pt"), "nccl", "auto", 29651, arch="moe")
-    nccl = _launch(2, str(tmp_path / "nccl.pt"), "nccl", "auto", 29652, arch=arch)
+    per rank with expert parallelism). Checked against a single-GPU run; the library-collective path of the same
+    layouts is covered by the CPU (gloo) tests."""
     fused = _launch(2, str(tmp_path / "fused.pt"), "fused", "auto", 29653, arch=arch)
-    assert rel(nccl["first"], single["first"]) < 4e-2
-    assert rel(fused["first"], single["first"]) < 4e-2
+    assert rel(fused["first"], moe_single["first"]) < 4e-2
     assert fused["graph_replays"] > 0
 
 
