@@ -44,6 +44,12 @@ def main():
     ec.quantization.weight_quant_method = quant
     say("building")
     llm = LLM(ec, mc, weights=RandomSource(seed=11, std=0.05), device="cuda")
+    if arch.startswith("moe"):
+        # decisive routing: with near-tied router logits, rounding differences between layouts flip expert choices
+        # and the comparison would measure routing luck instead of the kernels
+        for lw in llm.model.layers:
+            if lw.moe is not None:
+                lw.moe.router.mul_(16.0)
     say("llm ready")
     inner = llm.engine.runner.execute
 
