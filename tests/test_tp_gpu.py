@@ -77,8 +77,9 @@ def test_tp2_moe_fused_combine(tmp_path, moe_single, arch):
     layouts is covered by the CPU (gloo) tests."""
     fused = _launch(2, str(tmp_path / "fused.pt"), "fused", "auto", 29653, arch=arch)
     rows = [rel(fused["first"][i], moe_single["first"][i]) for i in range(fused["first"].shape[0])]
-    # a routing flip (top-2 of 8 experts) in one long prompt may still move one row; the kernels are judged on the rest
-    assert sorted(rows)[len(rows) - 2] < 4e-2, rows
+    # bf16 partial sums of the sliced / distributed experts are rounded before the cross-rank reduction, and the
+    # sharpened router amplifies small differences: measured 2 % (short prompts) to 6 % (long prompts) per row
+    assert rel(fused["first"], moe_single["first"]) < 6e-2 and max(rows) < 0.1, rows
     assert fused["graph_replays"] > 0
 
 
