@@ -171,7 +171,13 @@ class LLM:
                                  layer_range=layer_range, max_positions=mp)
         if adp > 1:
             from .parallel.data_parallel import AttentionDP
-            self.model.dp = AttentionDP(self.rank, self.world, dev_group)
+            symm = None
+            if dev_type == "cuda" and self.engine_cfg.global_.comm_backend == "fused":
+                from .parallel.symm import SymmetricComm
+                # room for every rank's padded rows: the longest per-rank row count times the ranks (bounded)
+                cap = self.engine_cfg.batch_scheduler.max_step_tokens * min(self.world, 4)
+                symm = SymmetricComm(dev_group, self.rank, self.world, self.device, cap, model_cfg.hidden_size)
+            self.model.dp = AttentionDP(self.rank, self.world, dev_group, symm)
         kv_dtype = kv_dtype_from(self.engine_cfg, dtype)
         bt = self.engine_cfg.block_manager.block_token_num
         probe = self.model.allocate_kv_cache(1, bt, kv_dtype)

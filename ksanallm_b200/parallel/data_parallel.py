@@ -25,8 +25,9 @@ import torch.distributed as dist
 
 
 class AttentionDP:
-    def __init__(self, rank: int, size: int, group=None):
+    def __init__(self, rank: int, size: int, group=None, symm=None):
         self.rank, self.size, self.group = rank, size, group
+        self.symm = symm                             # parallel.symm.SymmetricComm: dispatch / combine over peer memory
         self.counts: List[int] = [0] * size          # rows per rank of the step being executed
         self.gathered_bytes = 0
 
@@ -99,6 +100,20 @@ class AttentionDP:
         if t_max == 0:
             return h
         pad = x if T == t_max else torch.cat([x, x.new_zeros(t_max - T, H)], 0)
+        if self.symm is not None and x.is_cuda:
+            # peer-memory path: rows pulled from the peers' staging areas (dispatch), this rank's experts run over
+            # all rows with their weighted outputs written into its peer-visible slot, and one kernel pulls this
+            # rank's rows from every peer, sums them and adds them to the residual (combine)
+            gathered = self.symm.all_gather_rows(pad.contiguous())
+            if gathered is not None:
+                self.gathered_bytes += gathered.numel() * gathered.element_size()
+                out_rows = h.contiguous() if T else h
+                if mw.shared_gate_up is not None and T:
+                    out_rows = ops.add(out_rows, shared_expert(model, mw, x).contiguous())
+                if self.symm.reduce_rows_into(lambda part: moe_partial(model, mw, gathered, into=part, shared=False),
+                                              self.size * t_max, self.rank * t_max, out_rows):
+                    return out_rows
+                raise RuntimeError("expert combine does not fit the symmetric buffer (raise max_step_tokens head room)")
         gathered = torch.empty(self.size * t_max, H, dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(gathered, pad.contiguous(), group=self.group)        # dispatch
         self.gathered_bytes += gathered.numel() * gathered.element_size()

@@ -123,6 +123,44 @@ class SymmetricComm:
         self.barrier()          # peers are done reading the stage before it is written again
         return out
 
+    def all_gather_rows(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """[rows, H] bf16 (the same ``rows`` on every rank) -> [size * rows, H]: rank r's rows at r * rows, pulled
+        from the peers' staging areas (raw 32-bit copies). None if it does not fit the staging area."""
+        rows, H = x.shape
+        if x.dtype != torch.bfloat16 or H % 2 or rows * H * 2 > self.stage_bytes or rows == 0:
+            return None
+        n = rows * H // 2                                    # 32-bit words per rank
+        self.stage[: rows * H].copy_(x.reshape(-1))
+        out = torch.empty(self.size * rows, H, dtype=torch.bfloat16, device=self.device)
+        rc = native.lib().ksana_allgather_pull(self.data_ptrs, self.flag_ptrs, self.rank, self.size,
+                                               self.ctrs.data_ptr(), self.stage_off, out.data_ptr(), 1, n, n,
+                                               self.size * n, native.err_flag(self.device).data_ptr(), native._st())
+        native._check(rc, "ksana_allgather_pull")
+        self.barrier()          # peers are done reading the stage before it is written again
+        return out
+
+    def reduce_rows_into(self, write_partial, M: int, row_begin: int, h_rows: torch.Tensor) -> bool:
+        """Reduce-scatter with the residual add fused: every rank fills its partial result for all ``M`` rows
+        (``write_partial(part)``, part = [M, hidden] view of its peer-visible slot); this rank then pulls rows
+        ``[row_begin, row_begin + len(h_rows))`` from every peer, sums them in rank order and adds them to ``h_rows``
+        in place. False if M does not fit the slots."""
+        H = self.hidden
+        if M * H * 2 > self.size * self.slot_bytes or h_rows.dtype != torch.bfloat16:
+            return False
+        parity = self.parity
+        self.parity ^= 1
+        part = self.buf[self.slots_off[parity]: self.slots_off[parity] + M * H * 2].view(torch.bfloat16).view(M, H)
+        write_partial(part)
+        n = int(h_rows.shape[0])
+        # the kernel addresses the residual by global row: bias the pointer so that row_begin lands on h_rows[0]
+        h_base = h_rows.data_ptr() - row_begin * H * 2 if n else 0
+        rc = native.lib().ksana_reduce_norm(self.data_ptrs, self.flag_ptrs, self.rank, self.size, self.ctrs.data_ptr(),
+                                            self.slots_off[parity], self.slot_bytes, row_begin, n, M, H, h_base or None,
+                                            None, None, 0.0, 0, None, None, None, 0, 4, self.h_off, self.y_off,
+                                            self.yq_off, self.ys_off, native.err_flag(self.device).data_ptr(), native._st())
+        native._check(rc, "ksana_reduce_norm")
+        return True
+
     # ------------------------------------------------------------------ fused row-parallel linear
     def begin_forward(self):
         self.parity = 0

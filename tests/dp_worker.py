@@ -42,6 +42,8 @@ def main():
     out_path, device = sys.argv[1], sys.argv[2]
     mc = model_cfg(device)
     ec = engine_cfg()
+    if len(sys.argv) > 3:
+        ec.global_.comm_backend = sys.argv[3]          # fused: dispatch / combine over peer memory
     world = int(os.environ.get("WORLD_SIZE", "1"))
     ec.global_.attn_data_para_size = world
     dtype = torch.bfloat16 if device == "cuda" else torch.float32
@@ -60,7 +62,8 @@ def main():
         order = sorted(first)
         moe = llm.model.layers[0].moe
         torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "first": torch.stack([first[k] for k in order]),
-                    "experts": (moe.expert_lo, moe.expert_hi), "gathered_bytes": llm.model.dp.gathered_bytes if llm.model.dp else 0},
+                    "experts": (moe.expert_lo, moe.expert_hi), "gathered_bytes": llm.model.dp.gathered_bytes if llm.model.dp else 0,
+                    "peer_memory": bool(llm.model.dp is not None and llm.model.dp.symm is not None)},
                    out_path)
     import torch.distributed as dist
     llm.shutdown()

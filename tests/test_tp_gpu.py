@@ -107,5 +107,9 @@ def test_attention_dp_with_expert_parallel_over_nccl(tmp_path):
     combine)."""
     single = _launch_worker("dp_worker.py", 1, str(tmp_path / "single.pt"), 29671)
     dp = _launch_worker("dp_worker.py", 2, str(tmp_path / "dp.pt"), 29672)
-    assert dp["experts"] == (0, 4) and dp["gathered_bytes"] > 0
+    assert dp["experts"] == (0, 4) and dp["gathered_bytes"] > 0 and not dp["peer_memory"]
     assert rel(dp["first"], single["first"]) < 4e-2
+    # the same layout with dispatch and combine over peer memory (row pull + fused reduce / residual kernel)
+    fused = _launch_worker("dp_worker.py", 2, str(tmp_path / "dpf.pt"), 29673, "fused")
+    assert fused["peer_memory"] and fused["gathered_bytes"] > 0
+    assert rel(fused["first"], single["first"]) < 4e-2
