@@ -216,11 +216,17 @@ def main():
     s.max_new_tokens, s.ignore_eos, s.topk = S_out, True, 1
     rng = np.random.default_rng(1234)
 
+    latency = {"ttft": [], "tpot": []}
+
     def one_step(i):
         prompts = [rng.integers(0, mc.vocab_size, S_in).tolist() for _ in range(B)] if rank == 0 else []
         reqs = llm.generate(prompts, s)
         if rank == 0:
             assert all(len(r.outputs[0].tokens) == S_out for r in reqs), "short generation"
+            for r in reqs:       # host clock per request: arrival -> first token, then per output token
+                if r.first_token_time and r.finish_time:
+                    latency["ttft"].append((r.first_token_time - r.arrive) * 1000.0)
+                    latency["tpot"].append((r.finish_time - r.first_token_time) * 1000.0 / max(1, S_out - 1))
 
     def barrier():
         if world > 1:
@@ -231,6 +237,8 @@ def main():
     for i in range(args.warmup):
         one_step(i)
     barrier()
+    latency["ttft"].clear()
+    latency["tpot"].clear()
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
     l0, h0, d0 = native.launch_count(), llm.engine.runner.h2d_bytes, llm.engine.sampler.d2h_bytes
@@ -280,6 +288,8 @@ def main():
                        "global_batch": B, "seq_len": S_in, "output_len": S_out, "parallelism": "tp%d" % world,
                        "comm": args.comm, "kv_block_tokens": 16, "weight_scale_mode": args.scale_mode, "cuda_graph_decode": not args.no_graphs,
                        "l2": "inputs larger than L2 (weights 70 GB per pass); no explicit flush"},
+            "p50_ttft_ms": statistics.median(latency["ttft"]) if latency["ttft"] else None,
+            "p50_tpot_ms": statistics.median(latency["tpot"]) if latency["tpot"] else None,
             "clocks": clocks, "gpu_launches": launches,
             "graph_replays": getattr(llm.engine.runner, "graph_replays", 0),
         }

@@ -169,6 +169,9 @@ class LLM:
             layer_range = stage_layers(model_cfg.num_layers, pp, self.pp_rank)
         self.model = build_model(model_cfg, source, self.tp_rank, tp, self.comm, self.device, dtype, quant,
                                  layer_range=layer_range, max_positions=mp)
+        if self.engine_cfg.global_.embed_tokens_use_cpu and self.model.embed is not None and not model_cfg.tie_word_embeddings:
+            host = self.model.embed.to("cpu")
+            self.model.embed = host.pin_memory() if dev_type == "cuda" else host
         if adp > 1:
             from .parallel.data_parallel import AttentionDP
             symm = None

@@ -131,6 +131,17 @@ class CommonModel:
     # ------------------------------------------------------------------ blocks
     def embed_tokens(self, step: StepInput) -> torch.Tensor:
         cfg = self.cfg
+        if self.embed.device != self.device:
+            # embed_tokens_use_cpu: the table stays in (pinned) host memory, rows are looked up there and only the
+            # step's rows travel to the device (src/ksana_llm/layers/cpu/emb_lookup_layer.cpp in the reference)
+            ids = step.input_ids.to("cpu").long()
+            h = (self.embed[ids].float() * cfg.emb_scale).to(self.dtype) if cfg.emb_scale != 1.0 else self.embed[ids]
+            if self.pos_embed is not None:
+                h = h + self.pos_embed.to("cpu")[step.positions.to("cpu").long()]
+            h = h.to(self.device, non_blocking=True)
+            if step.refit_positions is not None and step.refit_positions.numel() > 0:
+                h[step.refit_positions.long()] = step.refit_embeddings.to(h.dtype)
+            return h
         V = self.embed.shape[0]
         lo = self.tp_rank * V if self.embed_sharded else 0
         h = ops.embedding(step.input_ids, self.embed, vocab_lo=lo, vocab_hi=lo + V,

@@ -151,6 +151,8 @@ class ServingModel:
             ne.metrics_start_export(prof.metrics_export_url, prof.export_interval_millis)
         if prof.trace_export_url:
             ne.span_set_sink(prof.trace_export_url)
+        from ..utils import version_reporter
+        version_reporter.init(self.llm.engine_cfg.global_.is_version_report)
         if self.llm.rank == 0:
             self.llm.engine.start()
             self._start_rpc_endpoint()

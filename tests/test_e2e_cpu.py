@@ -132,3 +132,23 @@ def test_nvfp4_weights_cpu():
     want = x @ W.w.t()
     got = linear(x, LinearWeight(w=W.w.clone()).quantize_nvfp4())
     assert float((got - want).norm() / want.norm()) < 0.2
+
+
+def test_embedding_table_on_the_host_gives_the_same_tokens():
+    """embed_tokens_use_cpu keeps the table in host memory; only the looked-up rows reach the model's device."""
+    import torch
+    from helpers import tiny_model_cfg
+    from ksanallm_b200.config import EngineConfig
+    from ksanallm_b200.llm import LLM
+    from ksanallm_b200.utils import native_engine as ne
+    outs = []
+    for on_host in (False, True):
+        ec = EngineConfig()
+        ec.global_.embed_tokens_use_cpu = on_host
+        ec.batch_scheduler.max_token_len = 64
+        ec.block_manager.device_blocks_num = 32
+        llm = LLM(ec, tiny_model_cfg(), weights="random", device="cpu", dtype=torch.float32)
+        s = ne.SamplingConfig()
+        s.max_new_tokens, s.ignore_eos = 5, True
+        outs.append([r.outputs[0].tokens for r in llm.generate([[5, 6, 7, 8], [9, 10]], s)])
+    assert outs[0] == outs[1]
