@@ -389,6 +389,34 @@ extern "C" int ksana_reduce_norm(const unsigned long long* data_ptrs, const unsi
   }
   return 0;
 }
+// The same all-reduce with the sum taken inside the NVSwitch (NVLS): `mc` is the multicast address of the symmetric
+// buffer (every rank's copy of the staged tensor bound to one address); one multimem.ld_reduce returns the sum over
+// all ranks' copies, so a rank receives n bytes instead of size x n. Summation order is the switch's, the result is
+// rounded to bf16 once before the residual is added.
+__global__ void allreduce_nvls_kernel(const CommPeers c, uint32_t* ctrs, const uint8_t* mc, long long off, bf16* out,
+                                      const bf16* residual, long long nvec, int* err) {
+  const uint32_t epoch = begin_epoch(ctrs, 3);
+  if (!signal_and_wait(c, 3, epoch, err, true)) return;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc + off + i * 16)
+                 : "memory");
+    if (residual) {
+      float a[8], b[8];
+      unpack8c(v, a);
+      unpack8c(reinterpret_cast<const uint4*>(residual)[i], b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] += b[e];
+      v = pack8c(a);
+    }
+    reinterpret_cast<uint4*>(out)[i] = v;
+  }
+  end_epoch(ctrs, 3, epoch);
+}
+
 
 extern "C" int ksana_comm_barrier(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank,
                                   int size, void* ctrs, int* err, cudaStream_t st) {
@@ -421,5 +449,22 @@ extern "C" int ksana_allgather_pull(const unsigned long long* data_ptrs, const u
   allgather_pull_kernel<<<static_cast<int>(g), 256, 0, st>>>(make_peers(data_ptrs, flag_ptrs, rank, size),
                                                              static_cast<uint32_t*>(ctrs), off, out, rows, cols,
                                                              src_ld, dst_ld, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// mc_base: multicast address of the symmetric buffer (0: not available -> -10).
+extern "C" int ksana_allreduce_nvls(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank,
+                                    int size, void* ctrs, unsigned long long mc_base, long long off, void* out,
+                                    const void* residual, long long n_elems, int* err, cudaStream_t st) {
+  if (n_elems % 8 || mc_base == 0 || (off & 15)) return -10;
+  const long long nvec = n_elems / 8;
+  long long g = (nvec + 255) / 256;
+  if (g > 148 * 4) g = 148 * 4;
+  if (g < 1) g = 1;
+  allreduce_nvls_kernel<<<static_cast<int>(g), 256, 0, st>>>(make_peers(data_ptrs, flag_ptrs, rank, size),
+                                                             static_cast<uint32_t*>(ctrs),
+                                                             reinterpret_cast<const uint8_t*>(mc_base), off,
+                                                             static_cast<bf16*>(out),
+                                                             static_cast<const bf16*>(residual), nvec, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

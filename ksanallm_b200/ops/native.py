@@ -40,6 +40,7 @@ _SIGS = {
                           i64, i64, i64, i64, vp, vp],
     "ksana_comm_barrier": [vp, vp, i32, i32, vp, vp, vp],
     "ksana_allreduce_pull": [vp, vp, i32, i32, vp, i64, vp, vp, i64, vp, vp],
+    "ksana_allreduce_nvls": [vp, vp, i32, i32, vp, C.c_ulonglong, i64, vp, vp, i64, vp, vp],
     "ksana_allgather_pull": [vp, vp, i32, i32, vp, i64, vp, i32, i32, i32, i32, vp, vp],
     "ksana_norm": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp],
     "ksana_act_mul": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],

@@ -24,6 +24,7 @@ Every wait is bounded in the kernels; a timeout sets the device error word (see 
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -68,6 +69,9 @@ class SymmetricComm:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.data_ptrs = (C.c_ulonglong * 8)(*(ptrs + [0] * (8 - size)))
         self.flag_ptrs = (C.c_ulonglong * 8)(*(ptrs + [0] * (8 - size)))       # flags live at offset 0
+        # NVLS: multicast address of the buffer when the platform bound one (in-switch reductions); opt-in
+        self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.use_nvls = bool(self.mc_ptr) and os.environ.get("KSANA_NVLS", "0") == "1"
         self.ctrs = torch.zeros(16, dtype=torch.int32, device=self.device)
         self.parity = 0
         dist.barrier(group)
@@ -94,11 +98,21 @@ class SymmetricComm:
                                              native.err_flag(self.device).data_ptr(), native._st())
         native._check(rc, "ksana_comm_barrier")
 
-    def all_reduce(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """x (bf16, contiguous) summed over ranks (+ residual); one-shot pull over peer memory."""
+    def all_reduce(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, nvls: Optional[bool] = None) -> torch.Tensor:
+        """x (bf16, contiguous) summed over ranks (+ residual): one-shot pull over peer memory, or - ``nvls`` /
+        KSANA_NVLS=1 and a multicast binding of the buffer - one in-switch reduction per 16 bytes
+        (multimem.ld_reduce)."""
         n = x.numel()
         self.stage[:n].copy_(x.reshape(-1))
         out = torch.empty_like(x)
+        if nvls if nvls is not None else self.use_nvls:
+            rc = native.lib().ksana_allreduce_nvls(self.data_ptrs, self.flag_ptrs, self.rank, self.size,
+                                                   self.ctrs.data_ptr(), self.mc_ptr, self.stage_off, out.data_ptr(),
+                                                   residual.data_ptr() if residual is not None else None, n,
+                                                   native.err_flag(self.device).data_ptr(), native._st())
+            native._check(rc, "ksana_allreduce_nvls")
+            self.barrier()
+            return out
         rc = native.lib().ksana_allreduce_pull(self.data_ptrs, self.flag_ptrs, self.rank, self.size,
                                                self.ctrs.data_ptr(), self.stage_off, out.data_ptr(),
                                                residual.data_ptr() if residual is not None else None, n,

@@ -44,6 +44,15 @@ def main():
     err = float((got.float() - want).abs().max())
     say("all_reduce max err", err)
     assert err < 0.1
+    say("multicast address", hex(comm.mc_ptr))
+    if comm.mc_ptr:
+        res = torch.randn(64, H, device=dev, dtype=torch.bfloat16)
+        got = comm.all_reduce(x, residual=res, nvls=True)       # in-switch reduction (multimem.ld_reduce)
+        torch.cuda.synchronize()
+        native.check_err_flag(dev)
+        err = float((got.float() - (want + res.float())).abs().max())
+        say("nvls all_reduce max err", err)
+        assert err < 0.15
     results = {}
     for M in (4, 16, 64, 200):
         for quant in (False, True):
