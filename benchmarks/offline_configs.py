@@ -73,6 +73,8 @@ def main():
     ap.add_argument("--no-prefix-cache", action="store_true")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--weights", default="", choices=["", "auto", "fp8_block", "nvfp4", "w4a16"],
+                    help="weight format (default: bf16 for config b, fp8_block for d and e)")
     args = ap.parse_args()
     defaults = {"b": (500, 512, 128), "d": (256, 2176, 64), "e": (64, 1024, 64)}[args.config]
     args.requests = args.requests or defaults[0]
@@ -110,7 +112,7 @@ def main():
     ec.batch_scheduler.enable_auto_prefix_cache = args.config == "d" and not args.no_prefix_cache
     ec.block_manager.block_token_num = 16
     ec.block_manager.reserved_device_memory_ratio = 0.08
-    ec.quantization.weight_quant_method = "auto" if (args.config == "b" or not on_gpu) else "fp8_block"
+    ec.quantization.weight_quant_method = args.weights or ("auto" if (args.config == "b" or not on_gpu) else "fp8_block")
     if not on_gpu:
         ec.block_manager.device_blocks_num = 4096
     llm = LLM(ec, mc, weights="random", device="cuda" if on_gpu else "cpu", dtype=torch.bfloat16 if on_gpu else torch.float32,

@@ -141,6 +141,22 @@ def case_mla_prefill():      # 2 sequences x 2048 new tokens, 128 heads (absorbe
     return run
 
 
+def case_w4_gemv():          # 4-bit weight-only decode GEMV: 8 rows x 28672 x 8192 (117 MB of packed weights)
+    N, K, g = 28672, 8192, 128
+    q4 = torch.randint(0, 256, (N, K // 2), device=DEV, dtype=torch.uint8)
+    scale = torch.full((N, K // g), 0.01, device=DEV, dtype=torch.float16)
+    zs = torch.full((N, K // g), 0.08, device=DEV, dtype=torch.float16)
+    x = torch.randn(8, K, device=DEV, dtype=torch.bfloat16)
+    y = torch.empty(8, N, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        native.linear_w4(x, q4, scale, zs, out=y)
+    run.bytes = N * K // 2 + 2 * N * (K // g) * 2
+    for _ in range(2):
+        run()
+    return run
+
+
 def case_norm_quant():       # residual add + RMSNorm + FP8 quantisation of 16384 x 8192 activations (805 MB moved)
     x = torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16)
     r = torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16)
@@ -183,7 +199,7 @@ def time_cases(names):
             if getattr(run, "flops", 0):
                 extra += f", {run.flops / ms / 1e9:.1f} TFLOP/s"
             if getattr(run, "bytes", 0):
-                extra += f", {run.bytes / ms / 1e6:.1f} GB/s of cache rows"
+                extra += f", {run.bytes / ms / 1e6:.1f} GB/s of streamed bytes"
             print(f"{n}: {ms * 1000:.1f} us per launch{extra}")
             continue
         # inputs are re-created inside each case; time only the second half by differencing two call counts
