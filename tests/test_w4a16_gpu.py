@@ -54,3 +54,36 @@ def test_linear_dispatch_w4():
     y = linear(x, W)
     want = x.float() @ W.dense().t()
     assert float((y.float() - want).norm() / want.norm()) < 1e-2
+
+
+def test_w4_model_through_the_engine_matches_cpu():
+    """A small Llama with 4-bit weight-only projections: greedy decoding on the GPU (GEMV kernel for decode steps,
+    expansion + tcgen05 GEMM for the prefill) follows the CPU engine running the same quantised weights."""
+    from ksanallm_b200.config import EngineConfig, ModelConfig
+    from ksanallm_b200.models.weights import RandomSource, build_model
+    from ksanallm_b200.runtime.engine import LLMEngine
+    from ksanallm_b200.utils import native_engine as ne
+    cfg = ModelConfig(model_type="llama", hidden_size=512, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, vocab_size=1000, max_position_embeddings=256, max_token_len=256)
+    outs = {}
+    for dev, dt in (("cpu", torch.float32), ("cuda", torch.bfloat16)):
+        model = build_model(cfg, RandomSource(seed=4, std=0.05), device=dev, dtype=dt, quant="w4a16:128")
+        assert model.layers[0].qkv.w4a16 and model.layers[1].down.w4a16
+        ec = EngineConfig()
+        ec.batch_scheduler.max_token_len = 200
+        ec.global_.enable_cuda_graph = dev == "cuda"
+        eng = LLMEngine(model, cfg, ec, num_blocks=64)
+        s = ne.SamplingConfig()
+        s.max_new_tokens, s.ignore_eos = 5, True
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (50, 9)]
+        logits = []
+        eng.step_hook = lambda plan, lg: logits.append(lg.float().cpu().clone())
+        eng.generate(prompts, s)
+        outs[dev] = logits
+        if dev == "cuda":
+            native.check_err_flag(torch.device("cuda"))
+            eng.runner.release_graphs()
+    a = next(x for x in outs["cpu"] if x.numel())
+    b = next(x for x in outs["cuda"] if x.numel())
+    assert a.shape == b.shape and float((a - b).norm() / a.norm()) < 0.05
