@@ -168,6 +168,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline stages (the GPUs of a stage form its tensor-parallel group)")
+    ap.add_argument("--micro-batches", type=int, default=2, help="micro-batches of a step in flight across the stages")
     ap.add_argument("--scale-mode", default="ue8m0", choices=["ue8m0", "fp32"],
                     help="weight scales: powers of two applied by the tensor cores, or exact amax/448 fp32 scales")
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
@@ -199,6 +201,8 @@ def main():
     B, S_in, S_out = args.batch, args.input_len, args.output_len
     ec = EngineConfig()
     ec.global_.comm_backend = args.comm
+    ec.global_.pipeline_para_size = args.pp
+    ec.global_.pipeline_micro_batches = args.micro_batches
     ec.global_.enable_cuda_graph = not args.no_graphs
     ec.batch_scheduler.max_batch_size = max(B, 8)
     ec.batch_scheduler.max_token_len = S_in + S_out + 16
@@ -273,10 +277,11 @@ def main():
         out_tokens = args.steps * B * S_out
         value = out_tokens / (ms / 1000.0)
         res = {
-            "metric": "output tok/s (offline, max over ranks) at Llama-3-70B fp8 TP%d" % world,
+            "metric": "output tok/s (offline, max over ranks) at Llama-3-70B fp8 " +
+                      ("TP%d" % world if args.pp == 1 else "PP%dxTP%d" % (args.pp, world // args.pp)),
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": (value / BASELINE_TOK_S[world]) if (world in BASELINE_TOK_S and not args.layers and
+            "vs_baseline": (value / BASELINE_TOK_S[world]) if (world in BASELINE_TOK_S and not args.layers and args.pp == 1 and
                                                                (B, S_in, S_out) == (64, 2048, 256)) else None,
             "dtype": ("fp8-e4m3 block-scaled weights (128x128 blocks, fp32 scales holding powers of two so that the tensor "
                       "cores apply them), fp8-e4m3 1x128-scaled GEMM inputs, bf16 activations and KV cache"
@@ -285,7 +290,7 @@ def main():
                       "1x128-scaled GEMM inputs, bf16 activations and KV cache"), "data": "synthetic",
             "impl": "ours",
             "config": {"model": "Llama-3-70B architecture, random-init N(0,0.02)" + (" [DEBUG %d layers: INVALID]" % args.layers if args.layers else ""),
-                       "global_batch": B, "seq_len": S_in, "output_len": S_out, "parallelism": "tp%d" % world,
+                       "global_batch": B, "seq_len": S_in, "output_len": S_out, "parallelism": ("tp%d" % world) if args.pp == 1 else ("pp%d x tp%d, %d micro-batches" % (args.pp, world // args.pp, args.micro_batches)),
                        "comm": args.comm, "kv_block_tokens": 16, "weight_scale_mode": args.scale_mode, "cuda_graph_decode": not args.no_graphs,
                        "l2": "inputs larger than L2 (weights 70 GB per pass); no explicit flush"},
             "p50_ttft_ms": statistics.median(latency["ttft"]) if latency["ttft"] else None,
