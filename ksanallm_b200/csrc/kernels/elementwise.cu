@@ -12,6 +12,7 @@
 //   rotary     : .../rotary_embedding/rotary_embedding.cu:70-197
 //   cache copy : .../paged_attention/cache_copy.cu:21-254
 //   fp8 quant  : 3rdparty/LLM_kernels/csrc/utils/nvidia/cuda_fp8_utils.cu:27-140
+#include "guards.cuh"
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -279,8 +280,10 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const bf16* __rest
 
 // out[r, :] = in[idx[r], :]  (last-token assembly, logits gather)
 __global__ void gather_rows_kernel(const bf16* __restrict__ in, const int* __restrict__ idx, bf16* __restrict__ out,
-                                   int H) {
-  const uint4* src = reinterpret_cast<const uint4*>(in + static_cast<size_t>(idx[blockIdx.x]) * H);
+                                   int H, int in_rows, int* err) {
+  int r = idx[blockIdx.x];
+  if (r < 0 || r >= in_rows) { if (threadIdx.x == 0) guard_report(err, kGuardGatherRow, r); r = 0; }
+  const uint4* src = reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * H);
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(blockIdx.x) * H);
   for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) dst[i] = src[i];
 }
@@ -501,10 +504,11 @@ extern "C" int ksana_embedding(const int* ids, const void* table, const int* pos
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-extern "C" int ksana_gather_rows(const void* in, const int* idx, void* out, int R, int H, cudaStream_t st) {
+extern "C" int ksana_gather_rows(const void* in, const int* idx, void* out, int R, int H, int in_rows, int* err,
+                                 cudaStream_t st) {
   if (R <= 0) return 0;
-  if (H % 8) return -10;
-  gather_rows_kernel<<<R, 256, 0, st>>>((const bf16*)in, idx, (bf16*)out, H);
+  if (H % 8 || in_rows <= 0) return -10;
+  gather_rows_kernel<<<R, 256, 0, st>>>((const bf16*)in, idx, (bf16*)out, H, in_rows, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

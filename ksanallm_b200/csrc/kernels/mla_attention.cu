@@ -27,6 +27,7 @@
 // partial outputs (fp32 O, running maximum, row sum) are merged by mla_merge_kernel.
 // Every wait is bounded; a timeout sets the error word and leaves the output untouched.
 #include "sm100_ptx.cuh"
+#include "guards.cuh"
 #include <cuda_bf16.h>
 #include <math_constants.h>
 
@@ -58,6 +59,7 @@ struct MlaParams {
   const int* cu_q; const int* kv_lens;
   int G, block_tokens, box_rows, nsplit, T;
   long long rows_per_block;                   // cache rows (576 elements each) between consecutive blocks
+  int num_blocks;                             // blocks addressable from the layer base (block-table entries are checked)
   float scale_log2;
   int* err;
 };
@@ -96,6 +98,10 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   const int qtile = nqt - 1 - static_cast<int>(blockIdx.x) / p.nsplit;      // longest rows first
   const int row0 = qtile * kMlaM;
   if (row0 >= q_len * G) return;
+  if (q0 < 0 || q_len < 0 || q0 + q_len > p.T || kv_len < q_len) {     // inconsistent sequence metadata: touch nothing
+    if (threadIdx.x == 0) guard_report(p.err, kGuardQueryRow, q0 + q_len);
+    return;
+  }
   const int past = kv_len - q_len;
   const int last_row = min(row0 + kMlaM - 1, q_len * G - 1);
   const int kv_end = min(kv_len, past + last_row / G + 1);
@@ -171,7 +177,9 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 #pragma unroll
         for (int bx = 0; bx < kMlaMaxBoxes; ++bx) {
           const int t = t0 + bx * br;
-          dst[bx] = (bx < boxes && t < kv_len) ? __ldg(table + t / bt) : 0;
+          int id = (bx < boxes && t < kv_len) ? __ldg(table + t / bt) : 0;
+          if (id < 0 || id >= p.num_blocks) { guard_report(p.err, kGuardBlockId, id); id = 0; }
+          dst[bx] = id;
         }
       };
       fetch(0, blk_next);
@@ -452,12 +460,16 @@ __global__ void mla_rope_append_kernel(const bf16* __restrict__ q, long long q_s
                                        long long kv_stride, const bf16* __restrict__ norm_w, float eps,
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        const float* __restrict__ cos_sin, bf16* __restrict__ qfull, bf16* __restrict__ cache,
-                                       long long rows_per_block, int block_tokens, int G) {
+                                       long long rows_per_block, int block_tokens, int G, int max_pos, long long num_slots,
+                                       int* err) {
   __shared__ float red[4];
   const int t = blockIdx.x, tid = threadIdx.x;                 // 128 threads
   const bf16* row = kv + static_cast<size_t>(t) * kv_stride;
-  const float* cs = cos_sin + static_cast<size_t>(positions[t]) * 64;
-  const int slot = slots[t];
+  int pos = positions[t];
+  if (pos < 0 || pos >= max_pos) { if (tid == 0) guard_report(err, kGuardPosition, pos); pos = 0; }
+  const float* cs = cos_sin + static_cast<size_t>(pos) * 64;
+  int slot = slots[t];
+  if (slot >= num_slots) { if (tid == 0) guard_report(err, kGuardSlot, slot); slot = -1; }
   bf16* crow = nullptr;
   if (slot >= 0 && cache != nullptr)
     crow = cache + (static_cast<size_t>(slot / block_tokens) * rows_per_block + slot % block_tokens) * kMlaDk;
@@ -566,6 +578,7 @@ extern "C" int ksana_mla_attention(const void* q, long long T, void* out, long l
   p.block_table = block_table; p.table_stride = table_stride; p.cu_q = cu_q; p.kv_lens = kv_lens;
   p.G = G; p.block_tokens = bt; p.box_rows = box_rows; p.nsplit = nsplit; p.T = static_cast<int>(T);
   p.rows_per_block = block_stride / kMlaDk;
+  p.num_blocks = static_cast<int>(cache_rows / p.rows_per_block);
   p.scale_log2 = scale * 1.44269504f;
   p.err = err;
   const int nqt = (max_q_len * G + kMlaM - 1) / kMlaM;
@@ -583,12 +596,13 @@ extern "C" int ksana_mla_attention(const void* q, long long T, void* out, long l
 extern "C" int ksana_mla_rope_append(const void* q, long long q_stride, int nope, const void* kv, long long kv_stride,
                                      const void* norm_w, float eps, const int* positions, const int* slots,
                                      const float* cos_sin, void* qfull, void* cache, long long block_stride,
-                                     int block_tokens, int T, int G, cudaStream_t st) {
+                                     int block_tokens, int T, int G, int max_pos, long long num_slots, int* err,
+                                     cudaStream_t st) {
   if (T <= 0) return 0;
   if (block_stride % kMlaDk) return -10;
   mla_rope_append_kernel<<<T, 128, 0, st>>>(static_cast<const bf16*>(q), q_stride, nope, static_cast<const bf16*>(kv),
                                             kv_stride, static_cast<const bf16*>(norm_w), eps, positions, slots, cos_sin,
                                             static_cast<bf16*>(qfull), static_cast<bf16*>(cache), block_stride / kMlaDk,
-                                            block_tokens, G);
+                                            block_tokens, G, max_pos, num_slots, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

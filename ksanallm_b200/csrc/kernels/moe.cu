@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include "guards.cuh"
 
 namespace ksana {
 
@@ -110,13 +111,14 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
 __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int* __restrict__ dst_row,
                                  int* __restrict__ tile_expert, int* __restrict__ expert_offsets,
                                  int* __restrict__ total_rows, int TK, int E, int max_tiles, int expert_lo,
-                                 int expert_hi) {
+                                 int expert_hi, int* err) {
   __shared__ int cnt[kMaxExperts];
   __shared__ int off[kMaxExperts + 1];
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < TK; i += blockDim.x) {
     const int e = topk_ids[i];
+    if (e < 0 || e >= E) { guard_report(err, kGuardExpert, e); continue; }
     if (e >= expert_lo && e < expert_hi) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
@@ -148,18 +150,19 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int* __restri
   __syncthreads();
   for (int i = threadIdx.x; i < TK; i += blockDim.x) {
     const int e = topk_ids[i];
-    dst_row[i] = (e >= expert_lo && e < expert_hi) ? off[e] + atomicAdd(&cnt[e], 1) : -1;
+    dst_row[i] = (e >= 0 && e < E && e >= expert_lo && e < expert_hi) ? off[e] + atomicAdd(&cnt[e], 1) : -1;
   }
 }
 
 // perm[dst_row[t*K+k]] = x[t]; rows of padding stay as they are (their outputs are never read).
 __global__ void moe_permute_kernel(const bf16* __restrict__ x, const int* __restrict__ dst_row, bf16* __restrict__ perm,
-                                   int K, int H) {
+                                   int K, int H, int cap, int* err) {
   const int t = blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
   for (int k = 0; k < K; ++k) {
     const int r = dst_row[t * K + k];
     if (r < 0) continue;
+    if (r >= cap) { if (threadIdx.x == 0) guard_report(err, kGuardDstRow, r); continue; }
     uint4* dst = reinterpret_cast<uint4*>(perm + static_cast<size_t>(r) * H);
     for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) dst[i] = src[i];
   }
@@ -168,7 +171,7 @@ __global__ void moe_permute_kernel(const bf16* __restrict__ x, const int* __rest
 // out[t] = (accumulate ? out[t] : 0) + sum_k w[t,k] * y[dst_row[t,k]]
 __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __restrict__ dst_row,
                                    const float* __restrict__ topk_w, bf16* __restrict__ out, int K, int H,
-                                   int accumulate) {
+                                   int accumulate, int cap, int* err) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) {
     float acc[8];
@@ -184,6 +187,7 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __rest
     for (int k = 0; k < K; ++k) {
       const int r = dst_row[t * K + k];
       if (r < 0) continue;
+      if (r >= cap) { if (i == 0) guard_report(err, kGuardDstRow, r); continue; }
       const float w = topk_w[t * K + k];
       const uint4 v = reinterpret_cast<const uint4*>(y + static_cast<size_t>(r) * H)[i];
       const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -212,25 +216,26 @@ extern "C" int ksana_moe_route(const float* logits, const float* bias, int* topk
 }
 
 extern "C" int ksana_moe_align(const int* topk_ids, int* dst_row, int* tile_expert, int* expert_offsets,
-                               int* total_rows, int TK, int E, int max_tiles, int expert_lo, int expert_hi,
+                               int* total_rows, int TK, int E, int max_tiles, int expert_lo, int expert_hi, int* err,
                                cudaStream_t st) {
   if (E > kMaxExperts) return -10;
   moe_align_kernel<<<1, 1024, 0, st>>>(topk_ids, dst_row, tile_expert, expert_offsets, total_rows, TK, E, max_tiles,
-                                       expert_lo, expert_hi);
+                                       expert_lo, expert_hi, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-extern "C" int ksana_moe_permute(const void* x, const int* dst_row, void* perm, int T, int K, int H, cudaStream_t st) {
+extern "C" int ksana_moe_permute(const void* x, const int* dst_row, void* perm, int T, int K, int H, int cap, int* err,
+                                 cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8) return -10;
-  moe_permute_kernel<<<T, 256, 0, st>>>((const bf16*)x, dst_row, (bf16*)perm, K, H);
+  moe_permute_kernel<<<T, 256, 0, st>>>((const bf16*)x, dst_row, (bf16*)perm, K, H, cap, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int ksana_moe_combine(const void* y, const int* dst_row, const float* topk_w, void* out, int T, int K, int H,
-                                 int accumulate, cudaStream_t st) {
+                                 int accumulate, int cap, int* err, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8) return -10;
-  moe_combine_kernel<<<T, 256, 0, st>>>((const bf16*)y, dst_row, topk_w, (bf16*)out, K, H, accumulate);
+  moe_combine_kernel<<<T, 256, 0, st>>>((const bf16*)y, dst_row, topk_w, (bf16*)out, K, H, accumulate, cap, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

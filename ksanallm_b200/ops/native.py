@@ -30,9 +30,9 @@ _SIGS = {
                           vp, vp],
     "ksana_gemm_grouped": [i32, vp, i32, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp, vp],
     "ksana_moe_route": [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp],
-    "ksana_moe_align": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp],
-    "ksana_moe_permute": [vp, vp, vp, i32, i32, i32, vp],
-    "ksana_moe_combine": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "ksana_moe_align": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
+    "ksana_moe_permute": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
+    "ksana_moe_combine": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_smallm_push": [i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, vp, i64, vp, i32, vp, i32, vp, vp],
     "ksana_gemm_fp8_block_push": [vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_gemm_bf16_push": [vp, i32, vp, i32, i32, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
@@ -46,7 +46,7 @@ _SIGS = {
     "ksana_act_mul": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
     "ksana_quant_fp8": [vp, vp, vp, i32, i32, i32, i32, vp],
     "ksana_embedding": [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
-    "ksana_gather_rows": [vp, vp, vp, i32, i32, vp],
+    "ksana_gather_rows": [vp, vp, vp, i32, i32, i32, vp, vp],
     "ksana_refit_rows": [vp, vp, vp, i32, i32, vp],
     "ksana_rope_kv_append": [vp, vp, i32, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32,
                              i32, vp],
@@ -61,7 +61,7 @@ _SIGS = {
     "ksana_paged_decode": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, f32, f32,
                            i32, vp, vp, i64, vp, vp],
     "ksana_mla_attention": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, f32, i64, i32, vp, vp, vp, vp],
-    "ksana_mla_rope_append": [vp, i64, i32, vp, i64, vp, f32, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
+    "ksana_mla_rope_append": [vp, i64, i32, vp, i64, vp, f32, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i64, vp, vp],
     "ksana_w4_gemv": [vp, i64, vp, vp, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, vp],
     "ksana_w4_dequant": [vp, vp, vp, vp, i64, i32, i32, i32, vp],
     "ksana_sample": [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, vp],
@@ -125,9 +125,15 @@ def err_flag(device) -> torch.Tensor:
 
 def check_err_flag(device) -> None:
     flag = err_flag(device)
-    if int(flag.item()) != 0:
+    code = int(flag.item())
+    if code != 0:
         flag.zero_()
-        raise RuntimeError("a device-side bounded wait timed out (kernel reported an error status)")
+        if code >= 1000000:
+            names = {11: "block-table entry", 12: "sequence row range", 13: "position", 14: "cache slot", 15: "expert id",
+                     16: "expert destination row", 17: "gather row index"}
+            raise RuntimeError(f"a kernel skipped an out-of-range {names.get(code // 1000000, 'index')} "
+                               f"(value mod 1e6 = {code % 1000000}); the step's results are invalid")
+        raise RuntimeError(f"a device-side bounded wait timed out (kernel reported error status {code})")
 
 
 # ------------------------------------------------------------------------------------- GEMM
@@ -369,7 +375,8 @@ def gather_rows(x, idx, out=None):
     R, H = idx.numel(), x.shape[1]
     if out is None:
         out = torch.empty(R, H, dtype=torch.bfloat16, device=x.device)
-    _check(lib().ksana_gather_rows(_p(x), _p(idx), _p(out), R, H, _st()), "ksana_gather_rows")
+    _check(lib().ksana_gather_rows(_p(x), _p(idx), _p(out), R, H, int(x.shape[0]), _p(err_flag(x.device)), _st()),
+           "ksana_gather_rows")
     return out
 
 
@@ -452,7 +459,8 @@ def mla_rope_append(q, nope, kv, norm_w, eps, positions, slots, cos_sin, qfull, 
     T = q.shape[0]
     rc = lib().ksana_mla_rope_append(_p(q), q.stride(0), nope, _p(kv), kv.stride(0), _p(norm_w), float(eps), _p(positions),
                                      _p(slots), _p(cos_sin), _p(qfull), _p(cache_layer), block_stride, block_tokens, T, G,
-                                     _st())
+                                     int(cos_sin.shape[0]), int(cache_layer.shape[0]) * block_tokens,
+                                     _p(err_flag(q.device)), _st())
     _check(rc, "ksana_mla_rope_append")
 
 
@@ -558,7 +566,7 @@ def moe_align(topk_ids, E, expert_lo=0, expert_hi=None):
     offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
     total = torch.empty(1, dtype=torch.int32, device=dev)
     rc = lib().ksana_moe_align(_p(topk_ids), _p(dst_row), _p(tile_expert), _p(offsets), _p(total), TK, E, max_tiles,
-                               expert_lo, hi, _st())
+                               expert_lo, hi, _p(err_flag(dev)), _st())
     _check(rc, "ksana_moe_align")
     return dst_row, tile_expert, offsets, total, max_tiles * 128
 
@@ -566,12 +574,13 @@ def moe_align(topk_ids, E, expert_lo=0, expert_hi=None):
 def moe_permute(x, dst_row, K, cap):
     T, H = x.shape
     perm = torch.empty(cap, H, dtype=torch.bfloat16, device=x.device)
-    _check(lib().ksana_moe_permute(_p(x), _p(dst_row), _p(perm), T, K, H, _st()), "ksana_moe_permute")
+    _check(lib().ksana_moe_permute(_p(x), _p(dst_row), _p(perm), T, K, H, cap, _p(err_flag(x.device)), _st()),
+           "ksana_moe_permute")
     return perm
 
 
 def moe_combine(y, dst_row, topk_w, out, K, accumulate):
     T, H = out.shape
-    _check(lib().ksana_moe_combine(_p(y), _p(dst_row), _p(topk_w), _p(out), T, K, H, int(accumulate), _st()),
-           "ksana_moe_combine")
+    _check(lib().ksana_moe_combine(_p(y), _p(dst_row), _p(topk_w), _p(out), T, K, H, int(accumulate), int(y.shape[0]),
+                                   _p(err_flag(out.device)), _st()), "ksana_moe_combine")
     return out

@@ -48,7 +48,8 @@ def test_image_request_through_serving_model(tmp_path):
     assert out.input_tokens == [1, 20, PAD, PAD, 21, 22] and len(out.output_tokens[0]) == 4     # 1x2 merged patches
     # the picture matters: another image changes the continuation's logits path (same tokens, other embeddings)
     seen = []
-    llm.engine.step_hook = lambda plan, lg: seen.append(lg.float().clone())
+    # prefill steps only: the hook of a request's last decode step may still run after generate() has returned
+    llm.engine.step_hook = lambda plan, lg: seen.append(lg.float().clone()) if plan.num_multi else None
     model.generate(inputs=list(prompt), generation_config=gen, additional_params={"images": [img]})
     a = seen[0]
     seen.clear()
