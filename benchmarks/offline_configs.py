@@ -126,9 +126,12 @@ def main():
                 s = ne.SamplingConfig()
                 s.max_new_tokens, s.ignore_eos, s.topk = o, True, 1
                 handles.append(llm.engine.add_request(p, s))
+            debug = on_gpu and os.environ.get("KSANA_CHECK_INPUTS", "0") not in ("", "0")
             while not all(h.done.is_set() for h in handles):
                 if not llm.engine.step() and llm.engine.scheduler.idle():
                     break
+                if debug:                       # debug runs: surface a kernel's index-guard report at the step it happened
+                    native.check_err_flag(dev)
             if world > 1:
                 import numpy as np
                 from ksanallm_b200.parallel.control import broadcast_plan
