@@ -131,7 +131,7 @@ class CommonModel:
     # ------------------------------------------------------------------ blocks
     def embed_tokens(self, step: StepInput) -> torch.Tensor:
         cfg = self.cfg
-        if self.embed.device != self.device:
+        if self.embed.device.type != self.device.type:
             # embed_tokens_use_cpu: the table stays in (pinned) host memory, rows are looked up there and only the
             # step's rows travel to the device (src/ksana_llm/layers/cpu/emb_lookup_layer.cpp in the reference)
             ids = step.input_ids.to("cpu").long()
