@@ -98,7 +98,9 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   const int qtile = nqt - 1 - static_cast<int>(blockIdx.x) / p.nsplit;      // longest rows first
   const int row0 = qtile * kMlaM;
   if (row0 >= q_len * G) return;
-  if (q0 < 0 || q_len < 0 || q0 + q_len > p.T || kv_len < q_len) {     // inconsistent sequence metadata: touch nothing
+  // inconsistent sequence metadata: touch nothing (kv_len == 0 is the padding row of a captured decode graph: it
+  // takes the empty-range path below)
+  if (q0 < 0 || q_len < 0 || q0 + q_len > p.T || (kv_len != 0 && kv_len < q_len)) {
     if (threadIdx.x == 0) guard_report(p.err, kGuardQueryRow, q0 + q_len);
     return;
   }
