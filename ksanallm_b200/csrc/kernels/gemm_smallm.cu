@@ -22,6 +22,7 @@
 // Same warp roles and bounded waits as gemm_tcgen05.cu. No cluster multicast.
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdio.h>
 
 namespace ksana {
@@ -46,13 +47,16 @@ struct SmallMParams {
   // push mode: the (partial) result is stored into every rank's receive slot for this rank instead of D
   __nv_bfloat16* push[8];
   int push_n;
+  // kind 3 (weight-only 4-bit): packed levels [N, K/2] (even k in the low nibble), fp16 scale and zero*scale [N, K/group]
+  const uint8_t* w4; const __half* w4_scale; const __half* w4_zs; int w4_group;
 };
 
 constexpr int pow2_at_least(int x) { int p = 32; while (p < x) p *= 2; return p; }
 
-template <int MP, int KIND>   // MP: padded token count (16..128); KIND 0 bf16, 1 fp8 fp32 scales, 2 fp8 UE8M0 scales
+template <int MP, int KIND>   // MP: padded token count (16..128); KIND 0 bf16, 1 fp8 fp32 scales, 2 fp8 UE8M0 scales,
+                              // 3 bf16 activations x 4-bit weights expanded to bf16 tiles by four extra warps
 struct SmallMCfg {
-  static constexpr int kThreads = KIND == 2 ? kSmThreads + 32 : kSmThreads;
+  static constexpr int kThreads = KIND == 2 ? kSmThreads + 32 : (KIND == 3 ? kSmThreads + 128 : kSmThreads);
   static constexpr int kSfBytes = KIND == 2 ? kSmSfStages * 1024 : 0;     // per stage: weight chunk + token chunk
   static constexpr int kWBytes = 128 * kSmRowBytes;
   static constexpr int kXBytes = MP * kSmRowBytes;
@@ -63,7 +67,7 @@ struct SmallMCfg {
   static constexpr int kSfBase = kAccStages * MP;                         // kind 2: two sets of 8 scale columns
   static constexpr int kTmemCols = pow2_at_least(kAccStages * MP + (KIND == 2 ? 16 : 0));
   static constexpr int kSmemBytes = kStages * kStageBytes + kSfBytes + 1024 + 512;
-  static constexpr int kElems = KIND == 0 ? 64 : 128;
+  static constexpr int kElems = (KIND == 0 || KIND == 3) ? 64 : 128;
 };
 
 // Work decomposition ("stream-K"): the (tile, k-block) units of the whole GEMM are laid out in one
@@ -117,7 +121,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   const long long u_begin = cut(blockIdx.x, U, P), u_end = cut(blockIdx.x + 1, U, P);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    // kind 3: a stage is full when the activation tile has landed (TMA) and the four expansion warps have arrived
+    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], KIND == 3 ? 5 : 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128); }
     for (int i = 0; i < kSmSfStages; ++i) { mbar_init(&sf_full[i], 1); mbar_init(&sf_empty[i], 1); }
     *abort_flag = 0;
@@ -140,8 +145,12 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sw = smem + stage * Cfg::kStageBytes;
-          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_2d(sw, &tma_w, &full_bar[stage], kb * Cfg::kElems, sg.tile * 128);
+          if constexpr (KIND == 3) {
+            mbar_expect_tx(&full_bar[stage], Cfg::kXBytes);
+          } else {
+            mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+            tma_load_2d(sw, &tma_w, &full_bar[stage], kb * Cfg::kElems, sg.tile * 128);
+          }
           tma_load_2d(sw + Cfg::kWBytes, &tma_x, &full_bar[stage], kb * Cfg::kElems, 0);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
         }
@@ -149,7 +158,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = KIND == 0 ? make_idesc(128, MP, 1, 1) : make_idesc(128, MP, 0, 0);
+      constexpr bool kBf16 = KIND == 0 || KIND == 3;
+      constexpr uint32_t idesc = kBf16 ? make_idesc(128, MP, 1, 1) : make_idesc(128, MP, 0, 0);
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       long long u = u_begin; Segment sg; bool ok = true;
@@ -205,8 +215,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           const uint32_t d_tmem = tmem_base + acc * MP;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint32_t accum = KIND == 0 ? ((kb != sg.kb0) || k != 0) : (k != 0);
-            if (KIND == 0) mma_f16(d_tmem, wdesc + 2 * k, xdesc + 2 * k, idesc, accum);
+            const uint32_t accum = kBf16 ? ((kb != sg.kb0) || k != 0) : (k != 0);
+            if (kBf16) mma_f16(d_tmem, wdesc + 2 * k, xdesc + 2 * k, idesc, accum);
             else mma_f8(d_tmem, wdesc + 2 * k, xdesc + 2 * k, idesc, accum);
           }
           tc_commit(&empty_bar[stage]);
@@ -216,14 +226,69 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
           }
         }
-        if (KIND == 0 && ok) {
+        if (kBf16 && ok) {
           tc_commit(&tfull_bar[acc]);
           if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
         }
       }
     }
     __syncwarp();
-  } else if (warp == 6) {
+  } else if (warp >= 6) {
+    if constexpr (KIND == 3) {
+      // ---------------------------------------------------------- 4-bit weight expansion (kind 3), warps 6..9
+      // Thread r owns weight row r of the tile: per K block it reads its 32 packed bytes (64 levels), turns them
+      // into bf16 (level * scale - zero*scale, one bf16 fma per pair) and stores the 128-byte row into the stage in
+      // the 128-byte-swizzled layout the MMA descriptor expects. The next block's bytes are fetched before the
+      // current one is converted, so the global-memory latency overlaps the arithmetic.
+      const int r = (warp - 6) * 32 + lane;
+      const int ngroups = p.K / p.w4_group;
+      int stage = 0; uint32_t phase = 0;
+      long long u = u_begin; Segment sg; bool ok = true;
+      while (ok && next_segment(u, u_end, num_kb, sg)) {
+        const int n = min(sg.tile * 128 + r, p.N - 1);          // rows past N repeat the last row; never stored
+        const uint8_t* wrow = p.w4 + static_cast<size_t>(n) * (p.K >> 1);
+        const __half* srow = p.w4_scale + static_cast<size_t>(n) * ngroups;
+        const __half* zrow = p.w4_zs + static_cast<size_t>(n) * ngroups;
+        uint4 qa = __ldg(reinterpret_cast<const uint4*>(wrow + sg.kb0 * 32));
+        uint4 qb = __ldg(reinterpret_cast<const uint4*>(wrow + sg.kb0 * 32 + 16));
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+          const int grp = (kb * 64) / p.w4_group;
+          const __nv_bfloat162 sc2 = __float2bfloat162_rn(__half2float(srow[grp]));
+          const __nv_bfloat162 nz2 = __float2bfloat162_rn(-__half2float(zrow[grp]));
+          if (kb + 1 < sg.kb1) {
+            qa = __ldg(reinterpret_cast<const uint4*>(wrow + (kb + 1) * 32));
+            qb = __ldg(reinterpret_cast<const uint4*>(wrow + (kb + 1) * 32 + 16));
+          }
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* dst = smem + stage * Cfg::kStageBytes + r * 128;
+          const __nv_bfloat162 bias128 = __float2bfloat162_rn(128.f);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t w = words[c];
+            // 0x4300 | level = bf16(128 + level) exactly; pairs come out as (0,4) (1,5) (2,6) (3,7)
+            uint32_t t[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t v = ((w >> (4 * j)) & 0x000f000fu) | 0x43004300u;
+              __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&v);
+              h = __hfma2(__hsub2(h, bias128), sc2, nz2);
+              t[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            uint4 o;
+            o.x = __byte_perm(t[0], t[1], 0x5410);     // levels 0, 1
+            o.y = __byte_perm(t[2], t[3], 0x5410);     // levels 2, 3
+            o.z = __byte_perm(t[0], t[1], 0x7632);     // levels 4, 5
+            o.w = __byte_perm(t[2], t[3], 0x7632);     // levels 6, 7
+            *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[stage]);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
     // ------------------------------------------------------------ scale packer (kind 2 only)
     if constexpr (KIND == 2) {
       // One group = up to four K blocks of one segment. The scales of the next group are fetched while the
@@ -507,14 +572,21 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
                        int ldw, const float* w_scale, void* D, void* out_f32, int ldd, const void* bias,
                        const void* residual, int ldr, int M, int N, int K, int ctas_hint, void* scratch,
                        long long scratch_bytes, void* counters, int counters_len, int* err_flag,
-                       cudaStream_t st, const unsigned long long* push_ptrs, int push_n) {
+                       cudaStream_t st, const unsigned long long* push_ptrs, int push_n, const void* w4_scale = nullptr,
+                       const void* w4_zs = nullptr, int w4_group = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (M > 128) return -20;
-  const int esz = kind == 0 ? 2 : 1;
-  if ((K % (kind == 0 ? 8 : 128)) || (ldx % (16 / esz)) || (ldw % (16 / esz))) return -10;
+  const bool w4 = kind == 3;
+  const int esz = (kind == 0 || w4) ? 2 : 1;
+  if (w4) {
+    if ((K % 64) || w4_group < 64 || (w4_group % 64) || (K % w4_group) || (ldx % 8) || !w4_scale || !w4_zs ||
+        (reinterpret_cast<uintptr_t>(W) & 15)) return -10;
+  } else if ((K % (kind == 0 ? 8 : 128)) || (ldx % (16 / esz)) || (ldw % (16 / esz))) {
+    return -10;
+  }
   const int MP = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   const int n_tiles = (N + 127) / 128;
-  const int num_kb = (K + (kind == 0 ? 64 : 128) - 1) / (kind == 0 ? 64 : 128);
+  const int num_kb = (K + (esz == 2 ? 64 : 128) - 1) / (esz == 2 ? 64 : 128);
   int sms = 148;
   {
     int dev = 0;
@@ -541,8 +613,9 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
   }
   if (!can_split && P != 1) P = 1;
   CUtensorMap mw, mx;
-  if (make_map2(&mw, W, N, K, ldw, esz, 128)) return -12;
   if (make_map2(&mx, X, M, K, ldx, esz, MP)) return -13;
+  if (w4) mw = mx;                                   // unused by kind 3: the weight tiles are expanded in the kernel
+  else if (make_map2(&mw, W, N, K, ldw, esz, 128)) return -12;
   SmallMParams p{};
   p.M = M; p.N = N; p.K = K;
   p.D = static_cast<__nv_bfloat16*>(D); p.out_f32 = static_cast<float*>(out_f32); p.ldd = ldd;
@@ -553,10 +626,17 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
   p.err = err_flag;
   for (int i = 0; i < push_n && i < 8; ++i) p.push[i] = reinterpret_cast<__nv_bfloat16*>(push_ptrs[i]);
   p.push_n = push_n;
+  if (w4) {
+    p.w4 = static_cast<const uint8_t*>(W);
+    p.w4_scale = static_cast<const __half*>(w4_scale);
+    p.w4_zs = static_cast<const __half*>(w4_zs);
+    p.w4_group = w4_group;
+  }
   const int ctas = static_cast<int>(P);
 #define KSANA_SM_DISPATCH(MPV)                                                                        \
   case MPV: return kind == 0 ? launch_smallm<MPV, 0>(mw, mx, p, ctas, st)                            \
-                 : (kind == 1 ? launch_smallm<MPV, 1>(mw, mx, p, ctas, st) : launch_smallm<MPV, 2>(mw, mx, p, ctas, st));
+                 : (kind == 1 ? launch_smallm<MPV, 1>(mw, mx, p, ctas, st)                            \
+                 : (kind == 2 ? launch_smallm<MPV, 2>(mw, mx, p, ctas, st) : launch_smallm<MPV, 3>(mw, mx, p, ctas, st)));
   switch (MP) {
     KSANA_SM_DISPATCH(16)
     KSANA_SM_DISPATCH(32)
@@ -574,6 +654,16 @@ extern "C" int ksana_gemm_smallm(int kind, const void* X, int ldx, const float* 
                                  cudaStream_t st) {
   return smallm_impl(kind, X, ldx, a_scale, a_scale_ld, W, ldw, w_scale, D, out_f32, ldd, bias, residual, ldr, M, N, K,
                      ctas_hint, scratch, scratch_bytes, counters, counters_len, err_flag, st, nullptr, 0);
+}
+
+// Weight-only 4-bit weights (kind 3): W = packed levels [N, K/2], fp16 scale and zero*scale [N, K/group], group a multiple
+// of 64. bf16 activations and output; same stream-K decomposition, scratch and counters as the other kinds.
+extern "C" int ksana_gemm_smallm_w4(const void* X, int ldx, const void* qw, const void* scale, const void* zs, int group,
+                                    void* D, int ldd, const void* bias, const void* residual, int ldr, int M, int N, int K,
+                                    void* scratch, long long scratch_bytes, void* counters, int counters_len,
+                                    int* err_flag, cudaStream_t st) {
+  return smallm_impl(3, X, ldx, nullptr, 0, qw, K / 2, nullptr, D, nullptr, ldd, bias, residual, ldr, M, N, K, 0, scratch,
+                     scratch_bytes, counters, counters_len, err_flag, st, nullptr, 0, scale, zs, group);
 }
 
 // Push mode (tensor parallel, decode-sized batches): the partial product is stored into every rank's

@@ -62,6 +62,7 @@ _SIGS = {
                            i32, vp, vp, i64, vp, vp],
     "ksana_mla_attention": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, f32, i64, i32, vp, vp, vp, vp],
     "ksana_mla_rope_append": [vp, i64, i32, vp, i64, vp, f32, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i64, vp, vp],
+    "ksana_gemm_smallm_w4": [vp, i32, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, vp, i64, vp, i32, vp, vp],
     "ksana_w4_gemv": [vp, i64, vp, vp, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, vp],
     "ksana_w4_dequant": [vp, vp, vp, vp, i64, i32, i32, i32, vp],
     "ksana_sample": [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, vp],
@@ -127,7 +128,8 @@ def check_err_flag(device) -> None:
     flag = err_flag(device)
     code = int(flag.item())
     if code != 0:
-        flag.zero_()
+        with torch.inference_mode():          # the word may have been created inside the engine's inference mode
+            flag.zero_()
         if code >= 1000000:
             names = {11: "block-table entry", 12: "sequence row range", 13: "position", 14: "cache slot", 15: "expert id",
                      16: "expert destination row", 17: "gather row index"}
@@ -285,6 +287,7 @@ def gemm_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, out=None, bias=None, residual=Non
     return dst
 
 
+W4_TENSOR_CORE = True        # rows 3..128: expand-in-kernel + tcgen05 (the CUDA-core GEMV is compute bound beyond 2 rows)
 W4_GEMV_MAX_M = 32          # up to this many rows the 4-bit weights are streamed by the GEMV kernel (8 rows per pass)
 _w4_scratch = {}
 
@@ -296,6 +299,16 @@ def linear_w4(x, q4, scale, zs, out=None, bias=None, residual=None):
     g = K // scale.shape[1]
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if W4_TENSOR_CORE and 2 < M <= 128 and g % 64 == 0 and K % 64 == 0:
+        # weight stream on the tensor cores: four warps expand the packed tiles to bf16 in shared memory, the rest is
+        # the stream-K skinny GEMM
+        scratch, counters = gemm_workspace(x.device)
+        rc = lib().ksana_gemm_smallm_w4(_p(x), x.stride(0), _p(q4), _p(scale), _p(zs), g, _p(out), out.stride(0), _p(bias),
+                                        _p(residual), residual.stride(0) if residual is not None else 0, M, N, K,
+                                        _p(scratch), scratch.numel() * 4, _p(counters), counters.numel(),
+                                        _p(err_flag(x.device)), _st())
+        _check(rc, "ksana_gemm_smallm_w4")
+        return out
     if M <= W4_GEMV_MAX_M:
         rc = lib().ksana_w4_gemv(_p(x), x.stride(0), _p(q4), _p(scale), _p(zs), _p(bias), _p(residual),
                                  residual.stride(0) if residual is not None else 0, _p(out), out.stride(0), M, N, K, g, _st())
