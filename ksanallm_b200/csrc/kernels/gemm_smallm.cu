@@ -254,32 +254,30 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
           const int grp = (kb * 64) / p.w4_group;
-          const __nv_bfloat162 sc2 = __float2bfloat162_rn(__half2float(srow[grp]));
-          const __nv_bfloat162 nz2 = __float2bfloat162_rn(-__half2float(zrow[grp]));
+          const float sc = __half2float(srow[grp]);
+          const float c128 = -(__half2float(zrow[grp]) + 128.f * sc);       // folds the +128 of the bit trick below
           if (kb + 1 < sg.kb1) {
             qa = __ldg(reinterpret_cast<const uint4*>(wrow + (kb + 1) * 32));
             qb = __ldg(reinterpret_cast<const uint4*>(wrow + (kb + 1) * 32 + 16));
           }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* dst = smem + stage * Cfg::kStageBytes + r * 128;
-          const __nv_bfloat162 bias128 = __float2bfloat162_rn(128.f);
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             const uint32_t w = words[c];
-            // 0x4300 | level = bf16(128 + level) exactly; pairs come out as (0,4) (1,5) (2,6) (3,7)
-            uint32_t t[4];
+            // 0x4300 | level is bf16(128 + level) exactly, and a bf16 in the high half of a word is that fp32 value;
+            // (128 + level) * scale - (zero*scale + 128 * scale) in fp32, rounded once to bf16
+            float f[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              uint32_t v = ((w >> (4 * j)) & 0x000f000fu) | 0x43004300u;
-              __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&v);
-              h = __hfma2(__hsub2(h, bias128), sc2, nz2);
-              t[j] = *reinterpret_cast<uint32_t*>(&h);
+              const uint32_t v = ((w >> (4 * j)) & 0x000f000fu) | 0x43004300u;        // levels j (low) and j + 4 (high)
+              f[j] = fmaf(__uint_as_float(v << 16), sc, c128);
+              f[j + 4] = fmaf(__uint_as_float(v & 0xffff0000u), sc, c128);
             }
             uint4 o;
-            o.x = __byte_perm(t[0], t[1], 0x5410);     // levels 0, 1
-            o.y = __byte_perm(t[2], t[3], 0x5410);     // levels 2, 3
-            o.z = __byte_perm(t[0], t[1], 0x7632);     // levels 4, 5
-            o.w = __byte_perm(t[2], t[3], 0x7632);     // levels 6, 7
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
             *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
           }
           fence_async_smem();

@@ -213,7 +213,9 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             logits = self.model.forward(step)
-        g = (graph, img, logits, mb)
+        # the captured kernels hold raw pointers to every tensor of `step` (cu_q is not part of `img`): keep the
+        # step alive with the graph, or its memory is handed to later allocations and a replay reads garbage offsets
+        g = (graph, img, logits, mb, step)
         self.graphs[bs] = g
         return g
 
@@ -224,7 +226,7 @@ class ModelRunner:
         if plan.sample_rows.size != nseq or plan.max_blocks > self.graph_max_blocks:
             return None
         bs = next(b for b in self.GRAPH_SIZES if b >= nseq)
-        graph, img, logits, mb = self._graph_for(bs)
+        graph, img, logits, mb, _step = self._graph_for(bs)
         host = np.zeros(4 * bs + bs * mb, dtype=np.int32)
         host[0:nseq] = plan.input_ids
         host[bs:bs + nseq] = plan.positions
