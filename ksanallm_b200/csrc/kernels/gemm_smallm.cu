@@ -60,7 +60,8 @@ struct SmallMCfg {
   static constexpr int kSfBytes = KIND == 2 ? kSmSfStages * 1024 : 0;     // per stage: weight chunk + token chunk
   static constexpr int kWBytes = 128 * kSmRowBytes;
   static constexpr int kXBytes = MP * kSmRowBytes;
-  static constexpr int kStageBytes = kWBytes + kXBytes;
+  static constexpr int kPackedBytes = KIND == 3 ? 128 * 32 : 0;             // kind 3: the 4-bit tile of the stage (TMA)
+  static constexpr int kStageBytes = kWBytes + kXBytes + kPackedBytes;
   static constexpr int kStagesRaw = (kSmSmemBudget - kSfBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
   static constexpr int kAccStages = KIND != 1 ? 2 : ((512 / MP) > 4 ? 4 : (512 / MP));
@@ -95,6 +96,12 @@ __device__ __forceinline__ int owner_of(long long x, long long U, long long P) {
   return static_cast<int>(c);
 }
 
+// element i (0..7) of eight fp16 values held in a uint4, without indexing the registers dynamically
+__device__ __forceinline__ float pick_half(const uint4& v, int i) {
+  const uint32_t w = (i & 4) ? ((i & 2) ? v.w : v.z) : ((i & 2) ? v.y : v.x);
+  return __half2float(__ushort_as_half(static_cast<unsigned short>((i & 1) ? (w >> 16) : (w & 0xffffu))));
+}
+
 template <int MP, int KIND>
 __global__ void __launch_bounds__(SmallMCfg<MP, KIND>::kThreads, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
@@ -110,7 +117,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   uint64_t* tempty_bar = tfull_bar + Cfg::kAccStages;
   uint64_t* sf_full = tempty_bar + Cfg::kAccStages;
   uint64_t* sf_empty = sf_full + kSmSfStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + kSmSfStages);
+  uint64_t* pk_full = sf_empty + kSmSfStages;                                 // kind 3: packed tile landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pk_full + (KIND == 3 ? Cfg::kStages : 0));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint32_t* last_flag = tmem_slot + 2;
 
@@ -123,6 +131,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   if (threadIdx.x == 0) {
     // kind 3: a stage is full when the activation tile has landed (TMA) and the four expansion warps have arrived
     for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], KIND == 3 ? 5 : 1); mbar_init(&empty_bar[i], 1); }
+    if (KIND == 3) { for (int i = 0; i < Cfg::kStages; ++i) mbar_init(&pk_full[i], 1); }
     for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128); }
     for (int i = 0; i < kSmSfStages; ++i) { mbar_init(&sf_full[i], 1); mbar_init(&sf_empty[i], 1); }
     *abort_flag = 0;
@@ -146,6 +155,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sw = smem + stage * Cfg::kStageBytes;
           if constexpr (KIND == 3) {
+            // the packed 4-bit tile (128 rows x 32 bytes) goes to the tail of the stage on its own barrier; the
+            // expansion warps turn it into the bf16 tile at the head of the stage
+            mbar_expect_tx(&pk_full[stage], Cfg::kPackedBytes);
+            tma_load_2d(sw + Cfg::kWBytes + Cfg::kXBytes, &tma_w, &pk_full[stage], kb * 32, sg.tile * 128);
             mbar_expect_tx(&full_bar[stage], Cfg::kXBytes);
           } else {
             mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
@@ -236,32 +249,52 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   } else if (warp >= 6) {
     if constexpr (KIND == 3) {
       // ---------------------------------------------------------- 4-bit weight expansion (kind 3), warps 6..9
-      // Thread r owns weight row r of the tile: per K block it reads its 32 packed bytes (64 levels), turns them
-      // into bf16 (level * scale - zero*scale, one bf16 fma per pair) and stores the 128-byte row into the stage in
-      // the 128-byte-swizzled layout the MMA descriptor expects. The next block's bytes are fetched before the
-      // current one is converted, so the global-memory latency overlaps the arithmetic.
+      // Thread r owns weight row r of the tile: per K block it reads its 32 packed bytes (64 levels) from the
+      // stage's packed area (brought in by TMA, as many K blocks ahead as there are stages), turns them into bf16
+      // (level * scale - zero*scale in fp32, rounded once) and stores the 128-byte row into the stage in the
+      // 128-byte-swizzled layout the MMA descriptor expects.
       const int r = (warp - 6) * 32 + lane;
       const int ngroups = p.K / p.w4_group;
+      const bool vec_scales = (ngroups & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.w4_scale) |
+                                                       reinterpret_cast<uintptr_t>(p.w4_zs)) & 15) == 0;
       int stage = 0; uint32_t phase = 0;
       long long u = u_begin; Segment sg; bool ok = true;
       while (ok && next_segment(u, u_end, num_kb, sg)) {
         const int n = min(sg.tile * 128 + r, p.N - 1);          // rows past N repeat the last row; never stored
-        const uint8_t* wrow = p.w4 + static_cast<size_t>(n) * (p.K >> 1);
         const __half* srow = p.w4_scale + static_cast<size_t>(n) * ngroups;
         const __half* zrow = p.w4_zs + static_cast<size_t>(n) * ngroups;
-        uint4 qa = __ldg(reinterpret_cast<const uint4*>(wrow + sg.kb0 * 32));
-        uint4 qb = __ldg(reinterpret_cast<const uint4*>(wrow + sg.kb0 * 32 + 16));
+        // Scales and zero terms of eight groups at a time (one 16-byte load each), the next eight fetched when the
+        // current eight are first used: a row's scales sit in a sector of their own, so a load per K block would
+        // put a trip to memory on the path of every block.
+        int cur_chunk = -1;
+        uint4 cs = make_uint4(0, 0, 0, 0), cz = cs, ns = cs, nz = cs;
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-          const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
           const int grp = (kb * 64) / p.w4_group;
-          const float sc = __half2float(srow[grp]);
-          const float c128 = -(__half2float(zrow[grp]) + 128.f * sc);       // folds the +128 of the bit trick below
-          if (kb + 1 < sg.kb1) {
-            qa = __ldg(reinterpret_cast<const uint4*>(wrow + (kb + 1) * 32));
-            qb = __ldg(reinterpret_cast<const uint4*>(wrow + (kb + 1) * 32 + 16));
+          float sc, zz;
+          if (vec_scales) {
+            const int ch = grp >> 3;
+            if (ch != cur_chunk) {
+              if (cur_chunk >= 0 && ch == cur_chunk + 1) { cs = ns; cz = nz; }
+              else { cs = __ldg(reinterpret_cast<const uint4*>(srow) + ch); cz = __ldg(reinterpret_cast<const uint4*>(zrow) + ch); }
+              cur_chunk = ch;
+              if ((ch + 1) * 8 < ngroups) {
+                ns = __ldg(reinterpret_cast<const uint4*>(srow) + ch + 1);
+                nz = __ldg(reinterpret_cast<const uint4*>(zrow) + ch + 1);
+              }
+            }
+            sc = pick_half(cs, grp & 7);
+            zz = pick_half(cz, grp & 7);
+          } else {
+            sc = __half2float(srow[grp]);
+            zz = __half2float(zrow[grp]);
           }
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          const float c128 = -(zz + 128.f * sc);                            // folds the +128 of the bit trick below
+          // the TMA for this stage was issued after the stage had been released, so its arrival also means "empty"
+          if (!mbar_wait(&pk_full[stage], phase, abort_flag)) { ok = false; break; }
           uint8_t* dst = smem + stage * Cfg::kStageBytes + r * 128;
+          const uint4* pk = reinterpret_cast<const uint4*>(smem + stage * Cfg::kStageBytes + Cfg::kWBytes + Cfg::kXBytes + r * 32);
+          const uint4 qa = pk[0], qb = pk[1];
+          const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             const uint32_t w = words[c];
@@ -543,6 +576,19 @@ static int make_map2(CUtensorMap* map, const void* base, int rows, int cols, int
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
 }
 
+// 4-bit weights [rows, k / 2 bytes]: one box is the 32 bytes x 128 rows of a K block, stored unswizzled
+static int make_map_packed4(CUtensorMap* map, const void* base, int rows, int k) {
+  EncodeTiledFn2 enc = encode_fn2();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
+  cuuint32_t box[2] = {32, 128};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
+}
+
 template <int MP, int KIND>
 static int launch_smallm(const CUtensorMap& mw, const CUtensorMap& mx, const SmallMParams& p, int ctas,
                          cudaStream_t st) {
@@ -612,8 +658,9 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
   if (!can_split && P != 1) P = 1;
   CUtensorMap mw, mx;
   if (make_map2(&mx, X, M, K, ldx, esz, MP)) return -13;
-  if (w4) mw = mx;                                   // unused by kind 3: the weight tiles are expanded in the kernel
-  else if (make_map2(&mw, W, N, K, ldw, esz, 128)) return -12;
+  if (w4) {
+    if (make_map_packed4(&mw, W, N, K)) return -12;
+  } else if (make_map2(&mw, W, N, K, ldw, esz, 128)) return -12;
   SmallMParams p{};
   p.M = M; p.N = N; p.K = K;
   p.D = static_cast<__nv_bfloat16*>(D); p.out_f32 = static_cast<float*>(out_f32); p.ldd = ldd;

@@ -141,20 +141,29 @@ def case_mla_prefill():      # 2 sequences x 2048 new tokens, 128 heads (absorbe
     return run
 
 
-def case_w4_gemv():          # 4-bit weight-only decode GEMV: 8 rows x 28672 x 8192 (117 MB of packed weights)
+def _w4_case(M):
     N, K, g = 28672, 8192, 128
     q4 = torch.randint(0, 256, (N, K // 2), device=DEV, dtype=torch.uint8)
     scale = torch.full((N, K // g), 0.01, device=DEV, dtype=torch.float16)
     zs = torch.full((N, K // g), 0.08, device=DEV, dtype=torch.float16)
-    x = torch.randn(8, K, device=DEV, dtype=torch.bfloat16)
-    y = torch.empty(8, N, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
 
     def run():
         native.linear_w4(x, q4, scale, zs, out=y)
     run.bytes = N * K // 2 + 2 * N * (K // g) * 2
+    run.flops = 2 * M * N * K
     for _ in range(2):
         run()
     return run
+
+
+def case_w4_gemv():          # 4-bit weight-only decode GEMM: 8 rows x 28672 x 8192 (117 MB of packed weights)
+    return _w4_case(8)
+
+
+def case_w4_m128():          # the same weights at a decode batch of 128
+    return _w4_case(128)
 
 
 def case_norm_quant():       # residual add + RMSNorm + FP8 quantisation of 16384 x 8192 activations (805 MB moved)

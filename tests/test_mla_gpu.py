@@ -124,6 +124,8 @@ def test_deepseek_engine_gpu_uses_latent_kernel():
             outs[dev] = logits
             if dev == "cuda":
                 native.check_err_flag(torch.device("cuda"))
+                # the latent-attention kernel reads cu_q in decode graphs too: every captured graph must own its step
+                assert eng.runner.graphs and all(g[4].cu_q is not None for g in eng.runner.graphs.values())
                 eng.runner.release_graphs()
     finally:
         native.mla_attention = real
