@@ -54,20 +54,23 @@ struct SmallMParams {
 constexpr int pow2_at_least(int x) { int p = 32; while (p < x) p *= 2; return p; }
 
 template <int MP, int KIND>   // MP: padded token count (16..128); KIND 0 bf16, 1 fp8 fp32 scales, 2 fp8 UE8M0 scales,
-                              // 3 bf16 activations x 4-bit weights expanded to bf16 tiles by four extra warps
+                              // 3 bf16 activations x 4-bit weights expanded to bf16 tiles by eight extra warps
 struct SmallMCfg {
-  static constexpr int kThreads = KIND == 2 ? kSmThreads + 32 : (KIND == 3 ? kSmThreads + 128 : kSmThreads);
+  static constexpr int kThreads = KIND == 2 ? kSmThreads + 32 : (KIND == 3 ? kSmThreads + 256 : kSmThreads);
   static constexpr int kSfBytes = KIND == 2 ? kSmSfStages * 1024 : 0;     // per stage: weight chunk + token chunk
   static constexpr int kWBytes = 128 * kSmRowBytes;
   static constexpr int kXBytes = MP * kSmRowBytes;
-  static constexpr int kPackedBytes = KIND == 3 ? 128 * 32 : 0;             // kind 3: the 4-bit tile of the stage (TMA)
-  static constexpr int kStageBytes = kWBytes + kXBytes + kPackedBytes;
-  static constexpr int kStagesRaw = (kSmSmemBudget - kSfBytes) / kStageBytes;
+  // kind 3: ring of packed 4-bit tiles, each 128 rows x 128 bytes = four K blocks (wide rows keep DRAM pages open)
+  static constexpr int kPackedSlots = KIND == 3 ? 3 : 0;
+  static constexpr int kPackedBytes = 128 * 128;
+  static constexpr int kPackedRing = kPackedSlots * kPackedBytes;
+  static constexpr int kStageBytes = kWBytes + kXBytes;
+  static constexpr int kStagesRaw = (kSmSmemBudget - kSfBytes - kPackedRing) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
   static constexpr int kAccStages = KIND != 1 ? 2 : ((512 / MP) > 4 ? 4 : (512 / MP));
   static constexpr int kSfBase = kAccStages * MP;                         // kind 2: two sets of 8 scale columns
   static constexpr int kTmemCols = pow2_at_least(kAccStages * MP + (KIND == 2 ? 16 : 0));
-  static constexpr int kSmemBytes = kStages * kStageBytes + kSfBytes + 1024 + 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kPackedRing + kSfBytes + 1024 + 512;
   static constexpr int kElems = (KIND == 0 || KIND == 3) ? 64 : 128;
 };
 
@@ -109,7 +112,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   using Cfg = SmallMCfg<MP, KIND>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sf_smem = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint8_t* pk_smem = smem + Cfg::kStages * Cfg::kStageBytes;                  // kind 3: packed ring (1024-aligned)
+  uint8_t* sf_smem = pk_smem + Cfg::kPackedRing;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + Cfg::kSfBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Cfg::kStages;
@@ -117,8 +121,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   uint64_t* tempty_bar = tfull_bar + Cfg::kAccStages;
   uint64_t* sf_full = tempty_bar + Cfg::kAccStages;
   uint64_t* sf_empty = sf_full + kSmSfStages;
-  uint64_t* pk_full = sf_empty + kSmSfStages;                                 // kind 3: packed tile landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pk_full + (KIND == 3 ? Cfg::kStages : 0));
+  uint64_t* pk_full = sf_empty + kSmSfStages;                                 // kind 3: packed tile landed / consumed
+  uint64_t* pk_empty = pk_full + Cfg::kPackedSlots;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pk_empty + Cfg::kPackedSlots);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint32_t* last_flag = tmem_slot + 2;
 
@@ -130,8 +135,8 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
 
   if (threadIdx.x == 0) {
     // kind 3: a stage is full when the activation tile has landed (TMA) and the four expansion warps have arrived
-    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], KIND == 3 ? 5 : 1); mbar_init(&empty_bar[i], 1); }
-    if (KIND == 3) { for (int i = 0; i < Cfg::kStages; ++i) mbar_init(&pk_full[i], 1); }
+    for (int i = 0; i < Cfg::kStages; ++i) { mbar_init(&full_bar[i], KIND == 3 ? 9 : 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < Cfg::kPackedSlots; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], 8); }
     for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128); }
     for (int i = 0; i < kSmSfStages; ++i) { mbar_init(&sf_full[i], 1); mbar_init(&sf_empty[i], 1); }
     *abort_flag = 0;
@@ -149,16 +154,23 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       tma_prefetch_desc(&tma_w);
       tma_prefetch_desc(&tma_x);
       int stage = 0; uint32_t phase = 0;
+      [[maybe_unused]] int pslot = 0; [[maybe_unused]] uint32_t pphase = 0;       // kind 3: packed ring
       long long u = u_begin; Segment sg; bool ok = true;
       while (ok && next_segment(u, u_end, num_kb, sg)) {
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if constexpr (KIND == 3) {
+            // every fourth K block of a segment: the packed tile of that block and the next three goes into the
+            // packed ring; the expansion warps turn it into the bf16 tiles of the stages
+            if (((kb - sg.kb0) & 3) == 0) {
+              if (!mbar_wait(&pk_empty[pslot], pphase ^ 1, abort_flag)) { ok = false; break; }
+              mbar_expect_tx(&pk_full[pslot], Cfg::kPackedBytes);
+              tma_load_2d(pk_smem + pslot * Cfg::kPackedBytes, &tma_w, &pk_full[pslot], kb * 32, sg.tile * 128);
+              if (++pslot == Cfg::kPackedSlots) { pslot = 0; pphase ^= 1; }
+            }
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sw = smem + stage * Cfg::kStageBytes;
           if constexpr (KIND == 3) {
-            // the packed 4-bit tile (128 rows x 32 bytes) goes to the tail of the stage on its own barrier; the
-            // expansion warps turn it into the bf16 tile at the head of the stage
-            mbar_expect_tx(&pk_full[stage], Cfg::kPackedBytes);
-            tma_load_2d(sw + Cfg::kWBytes + Cfg::kXBytes, &tma_w, &pk_full[stage], kb * 32, sg.tile * 128);
             mbar_expect_tx(&full_bar[stage], Cfg::kXBytes);
           } else {
             mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
@@ -248,12 +260,17 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     __syncwarp();
   } else if (warp >= 6) {
     if constexpr (KIND == 3) {
-      // ---------------------------------------------------------- 4-bit weight expansion (kind 3), warps 6..9
-      // Thread r owns weight row r of the tile: per K block it reads its 32 packed bytes (64 levels) from the
-      // stage's packed area (brought in by TMA, as many K blocks ahead as there are stages), turns them into bf16
+      // ---------------------------------------------------------- 4-bit weight expansion (kind 3), warps 6..13
+      // Two threads share weight row r of the tile: per K block each reads 16 of its 32 packed bytes (32 levels) from the
+      // packed ring (brought in by TMA four K blocks at a time, 128-byte swizzled), turns them into bf16
       // (level * scale - zero*scale in fp32, rounded once) and stores the 128-byte row into the stage in the
       // 128-byte-swizzled layout the MMA descriptor expects.
-      const int r = (warp - 6) * 32 + lane;
+      const int r = ((warp - 6) & 3) * 32 + lane;           // eight warps: two per 32 rows, each half a row
+      const int half = (warp - 6) >> 2;
+      constexpr int kBatch = Cfg::kStages >= 8 ? 4 : 2;        // K blocks converted per round (at most half the ring)
+      const int gblocks = p.w4_group / 64;                    // K blocks per group; a power of two in practice
+      const int gshift = (gblocks & (gblocks - 1)) == 0 ? 31 - __clz(gblocks) : -1;
+      int pslot = 0; uint32_t pphase = 0;
       const int ngroups = p.K / p.w4_group;
       const bool vec_scales = (ngroups & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.w4_scale) |
                                                        reinterpret_cast<uintptr_t>(p.w4_zs)) & 15) == 0;
@@ -266,57 +283,103 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         // Scales and zero terms of eight groups at a time (one 16-byte load each), the next eight fetched when the
         // current eight are first used: a row's scales sit in a sector of their own, so a load per K block would
         // put a trip to memory on the path of every block.
-        int cur_chunk = -1;
+        int cur_chunk = -1, cur_grp = -1;
         uint4 cs = make_uint4(0, 0, 0, 0), cz = cs, ns = cs, nz = cs;
-        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-          const int grp = (kb * 64) / p.w4_group;
-          float sc, zz;
-          if (vec_scales) {
-            const int ch = grp >> 3;
-            if (ch != cur_chunk) {
-              if (cur_chunk >= 0 && ch == cur_chunk + 1) { cs = ns; cz = nz; }
-              else { cs = __ldg(reinterpret_cast<const uint4*>(srow) + ch); cz = __ldg(reinterpret_cast<const uint4*>(zrow) + ch); }
-              cur_chunk = ch;
-              if ((ch + 1) * 8 < ngroups) {
-                ns = __ldg(reinterpret_cast<const uint4*>(srow) + ch + 1);
-                nz = __ldg(reinterpret_cast<const uint4*>(zrow) + ch + 1);
-              }
+        __nv_bfloat162 sc_hi, sc_lo, neg_zr, off;
+        // Batches of kBatch K blocks: one wait per barrier, one proxy fence and one round of arrivals per batch,
+        // and the conversions of the batch's blocks overlap each other's shared-memory latency.
+        for (int kb = sg.kb0; kb < sg.kb1; kb += kBatch) {
+          const int sub0 = (kb - sg.kb0) & 3;                                // first K block within the packed tile
+          const int nb = min(kBatch, sg.kb1 - kb);
+          if (sub0 == 0) if (!mbar_wait(&pk_full[pslot], pphase, abort_flag)) { ok = false; break; }
+          {
+            int st = stage; uint32_t ph = phase;
+            for (int j = 0; j < nb; ++j) {                                    // the batch's bf16 tiles are no longer read
+              if (!mbar_wait(&empty_bar[st], ph ^ 1, abort_flag)) { ok = false; break; }
+              if (++st == Cfg::kStages) { st = 0; ph ^= 1; }
             }
-            sc = pick_half(cs, grp & 7);
-            zz = pick_half(cz, grp & 7);
-          } else {
-            sc = __half2float(srow[grp]);
-            zz = __half2float(zrow[grp]);
+            if (!ok) break;
           }
-          const float c128 = -(zz + 128.f * sc);                            // folds the +128 of the bit trick below
-          // the TMA for this stage was issued after the stage had been released, so its arrival also means "empty"
-          if (!mbar_wait(&pk_full[stage], phase, abort_flag)) { ok = false; break; }
-          uint8_t* dst = smem + stage * Cfg::kStageBytes + r * 128;
-          const uint4* pk = reinterpret_cast<const uint4*>(smem + stage * Cfg::kStageBytes + Cfg::kWBytes + Cfg::kXBytes + r * 32);
-          const uint4 qa = pk[0], qb = pk[1];
-          const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint32_t w = words[c];
-            // 0x4300 | level is bf16(128 + level) exactly, and a bf16 in the high half of a word is that fp32 value;
-            // (128 + level) * scale - (zero*scale + 128 * scale) in fp32, rounded once to bf16
-            float f[8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t v = ((w >> (4 * j)) & 0x000f000fu) | 0x43004300u;        // levels j (low) and j + 4 (high)
-              f[j] = fmaf(__uint_as_float(v << 16), sc, c128);
-              f[j + 4] = fmaf(__uint_as_float(v & 0xffff0000u), sc, c128);
+          for (int j = 0; j < kBatch; ++j) {
+            if (j >= nb) break;
+            const int grp = gshift >= 0 ? ((kb + j) >> gshift) : ((kb + j) * 64) / p.w4_group;
+            if (grp != cur_grp) {
+              cur_grp = grp;
+              float sc, zz;
+              if (vec_scales) {
+                const int ch = grp >> 3;
+                if (ch != cur_chunk) {
+                  if (cur_chunk >= 0 && ch == cur_chunk + 1) { cs = ns; cz = nz; }
+                  else { cs = __ldg(reinterpret_cast<const uint4*>(srow) + ch); cz = __ldg(reinterpret_cast<const uint4*>(zrow) + ch); }
+                  cur_chunk = ch;
+                  if ((ch + 1) * 8 < ngroups) {
+                    ns = __ldg(reinterpret_cast<const uint4*>(srow) + ch + 1);
+                    nz = __ldg(reinterpret_cast<const uint4*>(zrow) + ch + 1);
+                  }
+                }
+                sc = pick_half(cs, grp & 7);
+                zz = pick_half(cz, grp & 7);
+              } else {
+                sc = __half2float(srow[grp]);
+                zz = __half2float(zrow[grp]);
+              }
+              // w = level * scale - zs in packed bf16 arithmetic (the fp32 -> bf16 pack instruction is too slow for
+              // this path) without losing the fp16 scale's precision: with z0 the integer nearest zs / scale,
+              // d = level - z0 is exact, the scale is split into two bf16 terms and the remainder zs - z0 * scale
+              // is at most half a step, so t = d * scale_lo - remainder and w = d * scale_hi + t round only at
+              // bf16's own resolution of w.
+              float z0 = sc != 0.f ? rintf(zz / sc) : 0.f;
+              z0 = fminf(fmaxf(z0, -64.f), 64.f);
+              const __nv_bfloat16 sh = __float2bfloat16_rn(sc);
+              sc_hi = __bfloat162bfloat162(sh);
+              sc_lo = __float2bfloat162_rn(sc - __bfloat162float(sh));
+              neg_zr = __float2bfloat162_rn(-(zz - z0 * sc));
+              off = __float2bfloat162_rn(128.f + z0);                        // exact: an integer below 256
             }
-            uint4 o;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+            int st = stage + j;
+            if (st >= Cfg::kStages) st -= Cfg::kStages;
+            uint8_t* dst = smem + st * Cfg::kStageBytes + r * 128;
+            const uint4 qa = *reinterpret_cast<const uint4*>(pk_smem + pslot * Cfg::kPackedBytes + r * 128 +
+                                                             ((((sub0 + j) * 2 + half) ^ (r & 7)) << 4));
+            const uint32_t words[4] = {qa.x, qa.y, qa.z, qa.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-            *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
+            for (int cc = 0; cc < 4; ++cc) {
+              const int c = half * 4 + cc;
+              const uint32_t w = words[cc];
+              uint32_t pr[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                // 0x4300 | level is bf16(128 + level) exactly: levels q (low half) and q + 4 (high half)
+                uint32_t v = ((w >> (4 * q)) & 0x000f000fu) | 0x43004300u;
+                const __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), off);     // exact
+                __nv_bfloat162 t = __hfma2(d, sc_lo, neg_zr);
+                t = __hfma2(d, sc_hi, t);
+                pr[q] = *reinterpret_cast<uint32_t*>(&t);
+              }
+              uint4 o;                                         // back to K order: (0,1) (2,3) (4,5) (6,7)
+              o.x = __byte_perm(pr[0], pr[1], 0x5410);
+              o.y = __byte_perm(pr[2], pr[3], 0x5410);
+              o.z = __byte_perm(pr[0], pr[1], 0x7632);
+              o.w = __byte_perm(pr[2], pr[3], 0x7632);
+              *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
+            }
           }
           fence_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&full_bar[stage]);
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+          if (lane == 0) {
+            for (int j = 0; j < nb; ++j) {
+              int st = stage + j;
+              if (st >= Cfg::kStages) st -= Cfg::kStages;
+              mbar_arrive(&full_bar[st]);
+            }
+            if (sub0 + nb == 4 || kb + nb == sg.kb1) mbar_arrive(&pk_empty[pslot]);     // done with this packed tile
+          }
+          if (sub0 + nb == 4 || kb + nb == sg.kb1) {
+            if (++pslot == Cfg::kPackedSlots) { pslot = 0; pphase ^= 1; }
+          }
+          stage += nb;
+          if (stage >= Cfg::kStages) { stage -= Cfg::kStages; phase ^= 1; }
         }
       }
     }
@@ -576,16 +639,16 @@ static int make_map2(CUtensorMap* map, const void* base, int rows, int cols, int
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
 }
 
-// 4-bit weights [rows, k / 2 bytes]: one box is the 32 bytes x 128 rows of a K block, stored unswizzled
+// 4-bit weights [rows, k / 2 bytes]: one box is 128 bytes x 128 rows (four K blocks), 128-byte swizzled
 static int make_map_packed4(CUtensorMap* map, const void* base, int rows, int k) {
   EncodeTiledFn2 enc = encode_fn2();
   if (!enc) return -1;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
-  cuuint32_t box[2] = {32, 128};
+  cuuint32_t box[2] = {128, 128};
   cuuint32_t estr[2] = {1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
 }
 

@@ -177,49 +177,83 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     __syncwarp();
   } else if (warp == 2) {
     // ------------------------------------------------------------- scale packer
+    // The scale values of the next two groups are already on their way (plain loads whose results are not
+    // touched until their turn) while the warp waits for the buffer of the current group: under the load of
+    // the operand stream a group's loads take longer than its four K blocks of MMAs, so fetching on demand
+    // starves the MMA thread. Three register sets rotate by name, not by index, so that no load result is
+    // moved (a move would wait for it).
     int sfs = 0; uint32_t sf_phase = 0;
-    bool ok = true;
     const int n_blocks = (p.N + 127) / 128;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    constexpr int NB = Cfg::kBChunks;
+    struct Raw { float a[16]; float b[NB * 4]; };
+    auto fetch = [&](int tile, int g, Raw& r) {
       int m_blk, n_blk;
       mx_tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
       const int m0 = m_blk * kMxBM;
-      for (int g = 0; g < num_groups; ++g) {
-        if (!mbar_wait(&sf_empty[sfs], sf_phase ^ 1, abort_flag)) { ok = false; break; }
-        uint8_t* buf = sf_smem + sfs * Cfg::kSfStageBytes;
-        uint32_t w[4];
 #pragma unroll
-        for (int r4 = 0; r4 < 4; ++r4) {
-          const int row = m0 + r4 * 32 + lane;
-          uint32_t word = 0;
+      for (int r4 = 0; r4 < 4; ++r4) {
+        const int row = min(m0 + r4 * 32 + lane, p.M - 1);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int kb = g * 4 + j;
-            uint32_t e = 127u;
-            if (row < p.M && kb < num_kb) e = ue8m0_of(p.a_scale[static_cast<size_t>(kb) * p.a_scale_ld + row]);
-            word |= e << (8 * j);
-          }
-          w[r4] = word;
+        for (int j = 0; j < 4; ++j) {
+          const int kb = min(g * 4 + j, num_kb - 1);
+          r.a[r4 * 4 + j] = __ldg(p.a_scale + static_cast<size_t>(kb) * p.a_scale_ld + row);
         }
-        *reinterpret_cast<uint4*>(buf + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-#pragma unroll
-        for (int c = 0; c < Cfg::kBChunks; ++c) {
-          const int nb = n_blk * Cfg::kBChunks + c;
-          uint32_t word = 0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int kb = g * 4 + j;
-            uint32_t e = 127u;
-            if (nb < n_blocks && kb < num_kb) e = ue8m0_of(p.w_scale[static_cast<size_t>(nb) * num_kb + kb]);
-            word |= e << (8 * j);
-          }
-          *reinterpret_cast<uint4*>(buf + 512 * (1 + c) + lane * 16) = make_uint4(word, word, word, word);
-        }
-        fence_async_smem();          // the tensor core reads the chunk through the async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sf_full[sfs]);
-        if (++sfs == kMxSfStages) { sfs = 0; sf_phase ^= 1; }
       }
+#pragma unroll
+      for (int c = 0; c < NB; ++c) {
+        const int nb = min(n_blk * NB + c, n_blocks - 1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kb = min(g * 4 + j, num_kb - 1);
+          r.b[c * 4 + j] = __ldg(p.w_scale + static_cast<size_t>(nb) * num_kb + kb);
+        }
+      }
+    };
+    // rows past M, column blocks past N and K blocks past the end repeat the last valid scale: what they scale
+    // is zero-filled by TMA or never stored
+    auto emit = [&](const Raw& r) -> bool {
+      if (!mbar_wait(&sf_empty[sfs], sf_phase ^ 1, abort_flag)) return false;
+      uint8_t* buf = sf_smem + sfs * Cfg::kSfStageBytes;
+      uint32_t w[4];
+#pragma unroll
+      for (int r4 = 0; r4 < 4; ++r4) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) word |= ue8m0_of(r.a[r4 * 4 + j]) << (8 * j);
+        w[r4] = word;
+      }
+      *reinterpret_cast<uint4*>(buf + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+#pragma unroll
+      for (int c = 0; c < NB; ++c) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) word |= ue8m0_of(r.b[c * 4 + j]) << (8 * j);
+        *reinterpret_cast<uint4*>(buf + 512 * (1 + c) + lane * 16) = make_uint4(word, word, word, word);
+      }
+      fence_async_smem();          // the tensor core reads the chunk through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sf_full[sfs]);
+      if (++sfs == kMxSfStages) { sfs = 0; sf_phase ^= 1; }
+      return true;
+    };
+    // (tile, group) sequence of this CTA; `ahead` runs two steps in front of `cur`
+    int ct = static_cast<int>(blockIdx.x), cg = 0, at = ct, ag = 0;
+    auto advance = [&](int& t, int& g) { if (++g == num_groups) { g = 0; t += static_cast<int>(gridDim.x); } };
+    Raw r0, r1, r2;
+    if (at < num_tiles) { fetch(at, ag, r0); advance(at, ag); }
+    if (at < num_tiles) { fetch(at, ag, r1); advance(at, ag); }
+    while (ct < num_tiles) {
+      if (at < num_tiles) { fetch(at, ag, r2); advance(at, ag); }
+      if (!emit(r0)) break;
+      advance(ct, cg);
+      if (ct >= num_tiles) break;
+      if (at < num_tiles) { fetch(at, ag, r0); advance(at, ag); }
+      if (!emit(r1)) break;
+      advance(ct, cg);
+      if (ct >= num_tiles) break;
+      if (at < num_tiles) { fetch(at, ag, r1); advance(at, ag); }
+      if (!emit(r2)) break;
+      advance(ct, cg);
     }
   } else {
     // ---------------------------------------------------------------- epilogue

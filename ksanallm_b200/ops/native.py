@@ -25,6 +25,7 @@ _SIGS = {
     "ksana_quant_nvfp4": [vp, i32, vp, i32, vp, i32, vp, i32, i32, vp],
     "ksana_gemm_mxfp8": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, vp,
                          vp],
+    "ksana_gemm_mxfp8_pair": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_gemm_fp8_block": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_smallm": [i32, vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i64, vp, i32,
                           vp, vp],
@@ -228,6 +229,24 @@ def gemm_mxfp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None,
     return dst
 
 
+MX_PAIR_MIN_M = 0                  # CTA-pair hardware-scaled kernel from this many rows; 0 disables it
+
+
+def gemm_mxfp8_pair(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, push=None, push_n=0, push_rows=0,
+                    ldd=None):
+    """Hardware-scaled FP8 GEMM on CTA pairs (256 x 256 tiles over two SMs, tcgen05 cta_group::2 block_scale MMA)."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    dst = out if out_f32 is None else out_f32
+    rc = lib().ksana_gemm_mxfp8_pair(_p(xq), xq.stride(0), _p(xs), xs.stride(0), _p(wq), wq.stride(0), _p(ws),
+                                     _p(out) if out_f32 is None else None, _p(out_f32),
+                                     dst.stride(0) if dst is not None else ldd, _p(bias), _p(residual),
+                                     residual.stride(0) if residual is not None else 0, M, N, K, push, push_n,
+                                     push_rows, _p(err_flag(xq.device)), _st())
+    _check(rc, "ksana_gemm_mxfp8_pair")
+    return dst
+
+
 def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0, splits=0,
              hw_scale=False):
     """Block-scaled FP8 GEMM. xq [M,K] e4m3, xs [K/128, ld] fp32; wq [N,K] e4m3, ws [ceil(N/128), K/128] fp32.
@@ -245,6 +264,8 @@ def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, b
         skinny = M <= SMALL_M_FP8 or (M <= 64 and t256 < 100 and K >= 16384)
         if (skinny or splits != 0) and M <= 128 and bn == 0:
             return _gemm_smallm(2, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)
+        if MX_PAIR_MIN_M > 0 and M >= MX_PAIR_MIN_M and bn == 0 and max_ctas == 0 and t256 >= 148:
+            return gemm_mxfp8_pair(xq, xs, wq, ws, out, bias, residual, out_f32)
         if bn == 0 or bn >= 128:
             return gemm_mxfp8(xq, xs, wq, ws, out, bias, residual, out_f32, bn or (256 if t256 >= 100 else 128),
                               max_ctas)

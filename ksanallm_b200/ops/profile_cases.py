@@ -47,6 +47,45 @@ def case_gemm_mxfp8():       # prefill-sized hardware-scaled FP8 GEMM: 4096 x 10
         native.gemm_mxfp8(xq, xs, wq, ws, y)
 
 
+def case_gemm_mxfp8_pair():  # the same GEMM on CTA pairs (256 x 256 tiles over two SMs)
+    wq, ws = _w8(10240, 8192)
+    xq, xs = native.quant_fp8(torch.randn(4096, 8192, device=DEV, dtype=torch.bfloat16))
+    y = torch.empty(4096, 10240, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        native.gemm_mxfp8_pair(xq, xs, wq, ws, y)
+    run.flops = 2 * 4096 * 10240 * 8192
+    for _ in range(2):
+        run()
+    return run
+
+
+def case_gemm_mxfp8_big():   # a prefill step of the 70B model: 16384 x 10240 x 8192
+    wq, ws = _w8(10240, 8192)
+    xq, xs = native.quant_fp8(torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16))
+    y = torch.empty(16384, 10240, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        native.gemm_mxfp8(xq, xs, wq, ws, y, bn=256)
+    run.flops = 2 * 16384 * 10240 * 8192
+    for _ in range(2):
+        run()
+    return run
+
+
+def case_gemm_mxfp8_pair_big():
+    wq, ws = _w8(10240, 8192)
+    xq, xs = native.quant_fp8(torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16))
+    y = torch.empty(16384, 10240, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        native.gemm_mxfp8_pair(xq, xs, wq, ws, y)
+    run.flops = 2 * 16384 * 10240 * 8192
+    for _ in range(2):
+        run()
+    return run
+
+
 def case_skinny_bf16():
     w = torch.randn(14336, 8192, device=DEV, dtype=torch.bfloat16) * 0.05
     x = torch.randn(8, 8192, device=DEV, dtype=torch.bfloat16)

@@ -83,3 +83,25 @@ def test_gemm_smallm_hw_scaled(M, N, K, splits):
     native.check_err_flag(DEV)
     want = ref.gemm_fp8(xq, xs, wq, ws, bias, res, out_dtype=torch.float32)
     assert rel_err(y, want) < 1e-2, rel_err(y, want)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (256, 256, 1024), (300, 1000, 640), (1000, 7168, 3584),
+                                   (4096, 10240, 8192), (2500, 57344, 1024)])
+def test_gemm_mxfp8_pair(M, N, K):
+    """CTA-pair variant (cta_group::2): both CTAs' rows and both weight halves carry their own scales."""
+    x, w = _operands(M, N, K, seed=M + N + K + 1)
+    wq, ws = ref.quant_weight_fp8_block(w)
+    xq, xs = native.quant_fp8(x)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        y = native.gemm_mxfp8_pair(xq, xs, wq, ws, torch.empty(M, N, device=DEV, dtype=torch.bfloat16), bias, res)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    want = ref.gemm_fp8(xq, xs, wq, ws, bias, res, out_dtype=torch.float32)
+    assert rel_err(y, want) < 1e-2, rel_err(y, want)
+    yf = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    native.gemm_mxfp8_pair(xq, xs, wq, ws, None, out_f32=yf)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    assert rel_err(yf, ref.gemm_fp8(xq, xs, wq, ws, out_dtype=torch.float32)) < 2e-3
