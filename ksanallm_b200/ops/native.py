@@ -25,6 +25,8 @@ _SIGS = {
     "ksana_quant_nvfp4": [vp, i32, vp, i32, vp, i32, vp, i32, i32, vp],
     "ksana_gemm_mxfp8": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, vp,
                          vp],
+    "ksana_gemm_mxfp8_tall": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i32, i32, vp,
+                              vp],
     "ksana_gemm_mxfp8_pair": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_gemm_fp8_block": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_smallm": [i32, vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i64, vp, i32,
@@ -229,6 +231,24 @@ def gemm_mxfp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None,
     return dst
 
 
+MX_TALL_MIN_M = 512                # 256 x 224-tile hardware-scaled kernel from this many rows (measured faster); 0 disables it
+
+
+def gemm_mxfp8_tall(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, max_ctas=0, push=None, push_n=0,
+                    push_rows=0, ldd=None):
+    """Hardware-scaled FP8 GEMM with 256 x 224 tiles per CTA (less operand traffic per MMA than 128 x 256)."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    dst = out if out_f32 is None else out_f32
+    rc = lib().ksana_gemm_mxfp8_tall(_p(xq), xq.stride(0), _p(xs), xs.stride(0), _p(wq), wq.stride(0), _p(ws),
+                                     _p(out) if out_f32 is None else None, _p(out_f32),
+                                     dst.stride(0) if dst is not None else ldd, _p(bias), _p(residual),
+                                     residual.stride(0) if residual is not None else 0, M, N, K, max_ctas, push, push_n,
+                                     push_rows, _p(err_flag(xq.device)), _st())
+    _check(rc, "ksana_gemm_mxfp8_tall")
+    return dst
+
+
 MX_PAIR_MIN_M = 0                  # CTA-pair hardware-scaled kernel from this many rows; 0 disables it
 
 
@@ -264,6 +284,8 @@ def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, b
         skinny = M <= SMALL_M_FP8 or (M <= 64 and t256 < 100 and K >= 16384)
         if (skinny or splits != 0) and M <= 128 and bn == 0:
             return _gemm_smallm(2, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)
+        if MX_TALL_MIN_M > 0 and M >= MX_TALL_MIN_M and bn == 0 and ((M + 255) // 256) * ((N + 223) // 224) >= 148:
+            return gemm_mxfp8_tall(xq, xs, wq, ws, out, bias, residual, out_f32, max_ctas)
         if MX_PAIR_MIN_M > 0 and M >= MX_PAIR_MIN_M and bn == 0 and max_ctas == 0 and t256 >= 148:
             return gemm_mxfp8_pair(xq, xs, wq, ws, out, bias, residual, out_f32)
         if bn == 0 or bn >= 128:

@@ -105,3 +105,25 @@ def test_gemm_mxfp8_pair(M, N, K):
     torch.cuda.synchronize()
     native.check_err_flag(DEV)
     assert rel_err(yf, ref.gemm_fp8(xq, xs, wq, ws, out_dtype=torch.float32)) < 2e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 224, 128), (256, 448, 1024), (300, 1000, 640), (1000, 7168, 3584),
+                                   (4096, 10240, 8192), (2500, 57344, 1024), (77, 264, 1024)])
+def test_gemm_mxfp8_tall(M, N, K):
+    """256 x 224 tiles: 224-wide tiles straddle the 128 x 128 weight blocks, so every 32-column run picks its block."""
+    x, w = _operands(M, N, K, seed=M + N + K + 2)
+    wq, ws = ref.quant_weight_fp8_block(w)
+    xq, xs = native.quant_fp8(x)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    for _ in range(2):
+        y = native.gemm_mxfp8_tall(xq, xs, wq, ws, torch.empty(M, N, device=DEV, dtype=torch.bfloat16), bias, res)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    want = ref.gemm_fp8(xq, xs, wq, ws, bias, res, out_dtype=torch.float32)
+    assert rel_err(y, want) < 1e-2, rel_err(y, want)
+    yf = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    native.gemm_mxfp8_tall(xq, xs, wq, ws, None, out_f32=yf)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    assert rel_err(yf, ref.gemm_fp8(xq, xs, wq, ws, out_dtype=torch.float32)) < 2e-3
