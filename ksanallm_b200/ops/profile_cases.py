@@ -60,6 +60,19 @@ def case_gemm_mxfp8_pair():  # the same GEMM on CTA pairs (256 x 256 tiles over 
     return run
 
 
+def case_gemm_mxfp8_tall():  # the same GEMM with 256 x 224 tiles per CTA
+    wq, ws = _w8(10240, 8192)
+    xq, xs = native.quant_fp8(torch.randn(4096, 8192, device=DEV, dtype=torch.bfloat16))
+    y = torch.empty(4096, 10240, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        native.gemm_mxfp8_tall(xq, xs, wq, ws, y)
+    run.flops = 2 * 4096 * 10240 * 8192
+    for _ in range(2):
+        run()
+    return run
+
+
 def case_gemm_mxfp8_big():   # a prefill step of the 70B model: 16384 x 10240 x 8192
     wq, ws = _w8(10240, 8192)
     xq, xs = native.quant_fp8(torch.randn(16384, 8192, device=DEV, dtype=torch.bfloat16))
