@@ -351,6 +351,57 @@ __global__ void rope_kv_append_kernel(bf16* __restrict__ qkv, const int* __restr
   }
 }
 
+// Vector form of the kernel above for the common case (rotate halves over the whole head, one position row):
+// a thread rotates 8 pairs with two 16-byte loads / stores and copies 8 cache elements per 16-byte load.
+template <typename CacheT>
+__global__ void rope_kv_append_vec_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                          const int* __restrict__ slots, const float* __restrict__ cos_sin,
+                                          CacheT* __restrict__ cache, long long block_stride, int block_tokens, int Hq,
+                                          int Hkv, int D, float k_scale_inv, float v_scale_inv, int apply_rope) {
+  const int t = blockIdx.x;
+  bf16* row = qkv + static_cast<size_t>(t) * (Hq + 2 * Hkv) * D;
+  const int half = D >> 1, hv = half >> 3;                   // 16-byte vectors per half head
+  if (apply_rope) {
+    const float* cs = cos_sin + static_cast<size_t>(positions[t]) * D;
+    const int items = (Hq + Hkv) * hv;
+    for (int i = threadIdx.x; i < items; i += blockDim.x) {
+      const int h = i / hv, j0 = (i - h * hv) << 3;
+      bf16* hp = row + static_cast<size_t>(h) * D;
+      float x0[8], x1[8], c[8], sn[8], y0[8], y1[8];
+      unpack8(*reinterpret_cast<const uint4*>(hp + j0), x0);
+      unpack8(*reinterpret_cast<const uint4*>(hp + half + j0), x1);
+      *reinterpret_cast<float4*>(&c[0]) = *reinterpret_cast<const float4*>(cs + j0);
+      *reinterpret_cast<float4*>(&c[4]) = *reinterpret_cast<const float4*>(cs + j0 + 4);
+      *reinterpret_cast<float4*>(&sn[0]) = *reinterpret_cast<const float4*>(cs + half + j0);
+      *reinterpret_cast<float4*>(&sn[4]) = *reinterpret_cast<const float4*>(cs + half + j0 + 4);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { y0[e] = x0[e] * c[e] - x1[e] * sn[e]; y1[e] = x1[e] * c[e] + x0[e] * sn[e]; }
+      *reinterpret_cast<uint4*>(hp + j0) = pack8(y0);
+      *reinterpret_cast<uint4*>(hp + half + j0) = pack8(y1);
+    }
+    __syncthreads();
+  }
+  const int slot = slots[t];
+  if (slot < 0 || cache == nullptr) return;
+  const int blk = slot / block_tokens, off = slot % block_tokens;
+  CacheT* kbase = cache + static_cast<size_t>(blk) * block_stride;
+  const bf16* ksrc = row + static_cast<size_t>(Hq) * D;
+  const int dv = D >> 3, n8 = Hkv * dv;
+  for (int i = threadIdx.x; i < 2 * n8; i += blockDim.x) {
+    const int kv = i / n8, r = i - kv * n8;
+    const int h = r / dv, d = (r - h * dv) << 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(ksrc + (static_cast<size_t>(i) << 3));
+    const size_t dst = ((static_cast<size_t>(kv) * Hkv + h) * block_tokens + off) * D + d;
+    if constexpr (sizeof(CacheT) == 1) {
+      float f[8];
+      unpack8(v, f);
+      *reinterpret_cast<uint2*>(kbase + dst) = pack8_e4m3(f, kv ? v_scale_inv : k_scale_inv);
+    } else {
+      *reinterpret_cast<uint4*>(kbase + dst) = v;
+    }
+  }
+}
+
 // Block-to-block copy inside the paged cache (beam fork, flexible cache, swap staging):
 // pairs[2*i] = source block, pairs[2*i+1] = destination block; copies all layers of a block.
 __global__ void copy_blocks_kernel(uint4* __restrict__ cache, const int* __restrict__ pairs, long long block_vec) {
@@ -523,6 +574,18 @@ extern "C" int ksana_rope_kv_append(void* qkv, const int* positions, int pos_str
                                     int Hq, int Hkv, int D, int rot_dim, int neox, int mrope_s0, int mrope_s1,
                                     int cache_fp8, float k_scale, float v_scale, int apply_rope, cudaStream_t st) {
   if (T <= 0) return 0;
+  if (neox && rot_dim == D && (D % 16) == 0 && pos_stride == 0 && (block_stride % 16) == 0 &&
+      (reinterpret_cast<uintptr_t>(qkv) % 16) == 0 && (reinterpret_cast<uintptr_t>(cache) % 16) == 0 &&
+      (reinterpret_cast<uintptr_t>(cos_sin) % 16) == 0) {
+    if (cache_fp8)
+      rope_kv_append_vec_kernel<uint8_t><<<T, 256, 0, st>>>((bf16*)qkv, positions, slots, cos_sin, (uint8_t*)cache,
+                                                            block_stride, block_tokens, Hq, Hkv, D, 1.f / k_scale,
+                                                            1.f / v_scale, apply_rope);
+    else
+      rope_kv_append_vec_kernel<bf16><<<T, 256, 0, st>>>((bf16*)qkv, positions, slots, cos_sin, (bf16*)cache,
+                                                         block_stride, block_tokens, Hq, Hkv, D, 1.f, 1.f, apply_rope);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   if (cache_fp8)
     rope_kv_append_kernel<uint8_t><<<T, 256, 0, st>>>((bf16*)qkv, positions, pos_stride, slots, cos_sin,
                                                       (uint8_t*)cache, block_stride, block_tokens, Hq, Hkv, D, rot_dim,
