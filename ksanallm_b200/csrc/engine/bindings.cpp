@@ -3,6 +3,7 @@
 // (src/ksana_llm/torch_op/serving_op.cpp:98-245), reduced to the engine-facing objects: the
 // HTTP-facing Python package builds the request/response objects on top of these.
 #include "endpoint_plugin.h"
+#include "stop_checker.h"
 #include "request_packer.h"
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
@@ -93,6 +94,7 @@ PYBIND11_MODULE(_ksana_engine, m) {
   m.doc() = "native host runtime: scheduler, KV cache manager, structured-output FSM, profiler, control plane";
 
   ksana::BindRequestPacker(m);
+  ksana::BindStopChecker(m);
 
   py::class_<PyEndpointPlugin>(m, "EndpointPlugin")
       .def(py::init<const std::string&, const std::string&>(), py::arg("name"), py::arg("search_dir") = "")

@@ -384,6 +384,8 @@ class LLMEngine:
                     ne.report_metric("time_to_first_token_ms", (req.first_token_time - req.arrive) * 1000.0)
             if finished:
                 out.finished = True
+                if code == 0 and req.cfg.stop_strings and self.tokenizer is not None:
+                    self._final_stop_check(out, req.cfg)
                 if code != 0:
                     req.status_code, req.status_message = code, message
                     ne.report_counter({4: "forward_req_aborted_num", 7: "forward_req_timeout_num"}.get(code, "forward_req_error_num"), 1)
@@ -405,20 +407,48 @@ class LLMEngine:
                 ne.report_metric("forward_cost_time_ms", (time.time() - req.arrive) * 1000.0)
                 self._complete(req)
 
+    def _final_stop_check(self, out, cfg):
+        """The last token of a sequence can complete a stop string too (and text held back as half a character is
+        final now): one search over the whole text (src/ksana_llm/batch_scheduler/strategy/continuous_batching.cpp:32-55
+        checks complete stop strings when a request finishes)."""
+        checker = ne.StopChecker(list(cfg.stop_strings))
+        if checker.append(self.tokenizer.decode(out.tokens, skip_special_tokens=True)) >= 0:
+            out.tokens = list(self.tokenizer.encode(checker.kept(), add_special_tokens=False))
+
     def _post_token_hooks(self, req: Request, i: int, seq_id: int):
         """Stop strings and structured output act on decoded text, which needs the tokenizer."""
         out = req.outputs[i]
         cfg = req.cfg
         if cfg.stop_strings and self.tokenizer is not None:
-            text = self.tokenizer.decode(out.tokens, skip_special_tokens=True)
-            for s in cfg.stop_strings:
-                pos = text.find(s)
-                if pos >= 0:
-                    kept = self.tokenizer.encode(text[:pos], add_special_tokens=False)
-                    out.tokens = list(kept)
-                    ev = self.scheduler.finish_sequence(seq_id, -1, 0, "")
-                    out.finished = True
-                    return
+            # incremental detokenisation: only the tokens since the last complete character are decoded again, and
+            # the native checker searches only the tail that the new text can complete. Bytes that never complete a
+            # character (they decode to U+FFFD whatever follows) break the increments: such an output falls back
+            # to decoding and searching its whole text per token.
+            st = getattr(out, "_stop_state", None)
+            if st is None:
+                st = out._stop_state = [ne.StopChecker(list(cfg.stop_strings)), 0, 0, False]   # checker, prefix, read, whole
+            checker, prefix, read, whole = st
+            hit = -1
+            if not whole:
+                before = self.tokenizer.decode(out.tokens[prefix:read], skip_special_tokens=True) if read > prefix else ""
+                now = self.tokenizer.decode(out.tokens[prefix:], skip_special_tokens=True)
+                if not ne.StopChecker.ends_incomplete(now):
+                    if now.startswith(before):
+                        st[1], st[2] = read, len(out.tokens)
+                        hit = checker.append(now[len(before):])
+                    else:
+                        whole = st[3] = True
+                elif len(out.tokens) - read >= 4 or len(out.tokens) >= cfg.max_new_tokens:
+                    whole = st[3] = True
+            if whole:
+                checker.reset()
+                hit = checker.append(self.tokenizer.decode(out.tokens, skip_special_tokens=True))
+            if hit >= 0:
+                kept = self.tokenizer.encode(checker.kept(), add_special_tokens=False)
+                out.tokens = list(kept)
+                self.scheduler.finish_sequence(seq_id, -1, 0, "")
+                out.finished = True
+                return
         if req.structured is not None:
             action = req.structured.after_token(out.tokens)
             if action.final:

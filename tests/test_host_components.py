@@ -323,3 +323,21 @@ def test_native_msgpack_matches_the_python_codec_and_validates_forward_bodies():
                          "slice_pos")):
         with pytest.raises(ValueError, match=why):
             ne.unpack_forward_body(msgpack.packb(broken))
+
+
+def test_stop_checker_incremental_search():
+    """Native stop-string checker: pieces arrive one by one, a stop string may straddle pieces, the earliest
+    match wins, half a UTF-8 character is reported as incomplete."""
+    from ksanallm_b200.utils import native_engine as ne
+    c = ne.StopChecker(["END", "stop here", ""])
+    assert c.append("abc E") == -1 and c.append("N") == -1
+    assert c.append("D tail") == 4 and c.kept() == "abc "
+    assert c.append("more END") == 4                      # stays on the first hit
+    c.reset()
+    assert c.append("x stop") == -1 and c.append(" he") == -1 and c.append("re END") == 2 and c.kept() == "x "
+    c2 = ne.StopChecker(["é!"])
+    assert c2.append("caf") == -1 and c2.append("é") == -1 and c2.append("!") == 3 and c2.kept() == "caf"
+    assert ne.StopChecker.ends_incomplete("ab�") and not ne.StopChecker.ends_incomplete("abé")
+    assert not ne.StopChecker.ends_incomplete("")
+    none = ne.StopChecker([])
+    assert none.append("anything") == -1 and none.kept() == "anything"
