@@ -25,6 +25,7 @@ _SIGS = {
     "ksana_quant_nvfp4": [vp, i32, vp, i32, vp, i32, vp, i32, i32, vp],
     "ksana_gemm_mxfp8": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, vp,
                          vp],
+    "ksana_gemm_bf16_tall": [vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_mxfp8_tall": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i32, i32, vp,
                               vp],
     "ksana_gemm_mxfp8_pair": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
@@ -188,6 +189,22 @@ def gemm_pair(kind, x, xs, w, ws, out, bias=None, residual=None, push=None, push
     return out
 
 
+BF16_TALL_MIN_M = 0                # 256 x 256-tile bf16 kernel from this many rows; 0 disables it
+
+
+def gemm_bf16_tall(x, w, out=None, bias=None, residual=None, out_f32=None, max_ctas=0):
+    """bf16 GEMM with 256 x 256 tiles per CTA (two 128-row MMAs share every weight tile)."""
+    M, K = x.shape
+    N = w.shape[0]
+    dst = out if out_f32 is None else out_f32
+    rc = lib().ksana_gemm_bf16_tall(_p(x), x.stride(0), _p(w), w.stride(0), _p(out) if out_f32 is None else None,
+                                    _p(out_f32), dst.stride(0), _p(bias), _p(residual),
+                                    residual.stride(0) if residual is not None else 0, M, N, K, max_ctas,
+                                    _p(err_flag(x.device)), _st())
+    _check(rc, "ksana_gemm_bf16_tall")
+    return dst
+
+
 def _pair_ok(M, N, K, kind, bn, out_f32, max_ctas):
     return (PAIR_MIN_M > 0 and M >= PAIR_MIN_M and bn == 0 and max_ctas == 0 and out_f32 is None and N % 8 == 0
             and N >= 256 and K % (128 if kind else 8) == 0)
@@ -203,6 +220,9 @@ def gemm_bf16(x, w, out=None, bias=None, residual=None, out_f32=None, bn=0, max_
     dst = out if out_f32 is None else out_f32
     if (M <= SMALL_M_BF16 or splits < 0) and M <= 128 and bn == 0 and K % 8 == 0:
         return _gemm_smallm(0, x, None, w, None, out, out_f32, bias, residual, M, N, K, splits)
+    if (BF16_TALL_MIN_M > 0 and M >= BF16_TALL_MIN_M and bn == 0 and splits == 0 and N % 8 == 0 and K % 8 == 0
+            and ((M + 255) // 256) * ((N + 255) // 256) >= 148):
+        return gemm_bf16_tall(x, w, out, bias, residual, out_f32, max_ctas)
     if _pair_ok(M, N, K, 0, bn, out_f32, max_ctas):
         return gemm_pair(0, x, None, w, None, out, bias, residual)
     rc = lib().ksana_gemm_bf16(_p(x), x.stride(0), _p(w), w.stride(0), _p(out) if out_f32 is None else None,
