@@ -254,6 +254,23 @@ def gemm_mxfp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None,
 MX_TALL_MIN_M = 512                # 256 x 224-tile hardware-scaled kernel from this many rows (measured faster); 0 disables it
 
 
+def _tall_wins(M, N, K, max_ctas=0, sms=148):
+    """256 x 224 tiles against 128 x 256 tiles for one problem, from measured behaviour: the tall tile does 1.75
+    times the MMA work at about 1.18 times the rate but cannot overlap its accumulator drain (about three K
+    blocks of time per tile), so it needs a long K and a tile count that fills its last wave."""
+    if K < 4096:
+        return False
+    ctas = min(sms, max_ctas) if max_ctas > 0 else sms
+    kb = K // 128
+    t_tall = ((M + 255) // 256) * ((N + 223) // 224)
+    t_std = ((M + 127) // 128) * ((N + 255) // 256)
+    if t_tall < ctas:
+        return False
+    tall = -(-t_tall // ctas) * (1.75 * kb + 3.0) / 1.18
+    std = -(-t_std // ctas) * (kb + 0.5)
+    return tall < std
+
+
 def gemm_mxfp8_tall(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, max_ctas=0, push=None, push_n=0,
                     push_rows=0, ldd=None):
     """Hardware-scaled FP8 GEMM with 256 x 224 tiles per CTA (less operand traffic per MMA than 128 x 256)."""
@@ -304,7 +321,7 @@ def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, b
         skinny = M <= SMALL_M_FP8 or (M <= 64 and t256 < 100 and K >= 16384)
         if (skinny or splits != 0) and M <= 128 and bn == 0:
             return _gemm_smallm(2, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)
-        if MX_TALL_MIN_M > 0 and M >= MX_TALL_MIN_M and bn == 0 and ((M + 255) // 256) * ((N + 223) // 224) >= 148:
+        if MX_TALL_MIN_M > 0 and M >= MX_TALL_MIN_M and bn == 0 and _tall_wins(M, N, K, max_ctas):
             return gemm_mxfp8_tall(xq, xs, wq, ws, out, bias, residual, out_f32, max_ctas)
         if MX_PAIR_MIN_M > 0 and M >= MX_PAIR_MIN_M and bn == 0 and max_ctas == 0 and t256 >= 148:
             return gemm_mxfp8_pair(xq, xs, wq, ws, out, bias, residual, out_f32)

@@ -169,3 +169,12 @@ def test_debug_input_checks_catch_bad_indices(monkeypatch):
     bad_slots = dataclasses.replace(good, slots=good.slots.clone())
     bad_slots.slots[1] = bad_slots.slots[0]
     assert any("same cache slot" in v or "says otherwise" in v for v in checks.step_violations(bad_slots, nb, bt, 300, 512))
+
+
+def test_fp8_tile_choice_rule():
+    """The dispatch rule between 256 x 224 and 128 x 256 FP8 tiles reproduces the measured winners."""
+    from ksanallm_b200.ops.native import _tall_wins
+    tall = [(16384, 10240, 8192), (16384, 57344, 8192), (16384, 8192, 28672), (16384, 4096, 14336), (2048, 10240, 8192),
+            (512, 57344, 8192), (16384, 28672, 4096)]
+    std = [(4096, 7168, 2048), (16384, 4096, 1024), (16384, 2048, 7168), (8192, 1280, 8192), (256, 1024, 8192)]
+    assert all(_tall_wins(*s) for s in tall) and not any(_tall_wins(*s) for s in std)
