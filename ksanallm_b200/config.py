@@ -265,7 +265,7 @@ class ModelConfig:
 
 _ARCH_ALIASES = {
     "llama": "llama", "mistral": "llama", "qwen2": "qwen", "qwen": "qwen", "qwen2_vl": "qwen2_vl", "baichuan": "baichuan",
-    "chatglm": "chatglm", "gpt2": "gpt", "openai-gpt": "gpt", "fairseq-transformer": "gpt", "mixtral": "mixtral",
+    "chatglm": "chatglm", "glm": "chatglm", "gpt2": "gpt", "openai-gpt": "gpt", "fairseq-transformer": "gpt", "mixtral": "mixtral",
     "qwen2_moe": "qwen2_moe", "deepseek_v3": "deepseek_v3", "deepseek_v2": "deepseek_v3", "internlm2": "llama",
     "yi": "llama",
 }
@@ -350,10 +350,16 @@ def model_config_from_hf(hf: dict, generation: Optional[dict] = None) -> ModelCo
             c.position_embedding = "alibi"
         c.lm_head_norm = hf.get("vocab_size", 0) == 125696
     if arch == "chatglm":
+        # ChatGLM2/3 (THUDM config names) and GLM-4 in the Hugging Face layout (model_type "glm"): rotary pairs are
+        # interleaved and cover only part of the head, QKV carries a bias, gate and up are one fused matrix
         c.rope_neox = False
-        c.rotary_dim = c.head_dim // 2
-        c.qkv_bias = bool(hf.get("add_qkv_bias", True))
-        c.num_kv_heads = hf.get("multi_query_group_num", c.num_kv_heads) if hf.get("multi_query_attention", True) else c.num_heads
+        prf = hf.get("partial_rotary_factor", (hf.get("rope_parameters") or {}).get("partial_rotary_factor", 0.5))
+        c.rotary_dim = int(c.head_dim * float(prf))
+        c.qkv_bias = bool(hf.get("attention_bias", hf.get("add_qkv_bias", True)))
+        if mt == "glm":
+            c.num_kv_heads = hf.get("num_key_value_heads", c.num_heads) or c.num_heads
+        else:
+            c.num_kv_heads = hf.get("multi_query_group_num", c.num_kv_heads) if hf.get("multi_query_attention", True) else c.num_heads
     if arch in ("mixtral", "qwen2_moe", "deepseek_v3"):
         c.num_experts = hf.get("num_local_experts", hf.get("num_experts", hf.get("n_routed_experts", 8)))
         c.num_experts_per_tok = hf.get("num_experts_per_tok", 2)

@@ -105,3 +105,21 @@ def test_deepseek_v3_mla_and_grouped_sigmoid_routing():
             if n.endswith("e_score_correction_bias"):
                 b.copy_(0.1 * torch.randn(b.shape, generator=torch.Generator().manual_seed(5)))
     _check(m, c.to_dict(), tol=5e-4)
+
+
+def test_glm4_partial_interleaved_rope_fused_gate_up():
+    """GLM-4 in the Hugging Face layout runs on the ChatGLM flags: interleaved rotary pairs over half of the
+    head, QKV bias, one fused gate|up matrix."""
+    from transformers import GlmConfig, GlmForCausalLM
+    c = GlmConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                  vocab_size=200, max_position_embeddings=256, rms_norm_eps=1e-5, head_dim=16, partial_rotary_factor=0.5,
+                  attention_bias=True, tie_word_embeddings=False, pad_token_id=0)
+    _check(_init(GlmForCausalLM(c)), c.to_dict())
+
+
+def test_mistral_runs_as_llama():
+    from transformers import MistralConfig, MistralForCausalLM
+    c = MistralConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                      vocab_size=200, max_position_embeddings=256, rms_norm_eps=1e-5, sliding_window=None,
+                      tie_word_embeddings=False)
+    _check(_init(MistralForCausalLM(c)), c.to_dict())
