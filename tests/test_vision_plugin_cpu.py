@@ -10,11 +10,13 @@ PAD = 290
 
 def test_tower_and_positions():
     tower = VisionTower(hidden_out=64, dim=32, depth=1, heads=2, patch=14, merge=2)
-    emb, grids = tower([torch.rand(3, 56, 84), torch.rand(2, 3, 28, 28)])
+    clip = torch.rand(4, 3, 28, 28)
+    emb, grids = tower([torch.rand(3, 56, 84), clip])
+    # a still image is one temporal patch (its own second frame); four frames are two temporal patches
     assert grids == [(1, 4, 6), (2, 2, 2)] and emb.shape == (1 * 2 * 3 + 2 * 1 * 1, 64)
-    # frames do not attend to each other: the second image's embeddings do not depend on the first image
-    emb2, _ = tower([torch.rand(3, 56, 84), torch.rand(2, 3, 28, 28)])
-    assert emb2.shape == emb.shape
+    # images do not attend to each other: the clip's embeddings do not depend on the first image
+    emb2, _ = tower([torch.rand(3, 56, 84), clip])
+    assert emb2.shape == emb.shape and torch.allclose(emb2[6:], emb[6:], atol=1e-5)
     toks = [5, 6] + [PAD] * 6 + [7, 8]
     pos = mrope_positions(toks, PAD, [(1, 4, 6)], 2)
     assert pos[:, :2].tolist() == [[0, 1]] * 3
@@ -59,3 +61,53 @@ def test_image_request_through_serving_model(tmp_path):
     model.generate(inputs=list(prompt), generation_config=gen, additional_params={"images": [img]})
     assert torch.allclose(seen[0], a, atol=1e-5)
     model.shutdown()
+
+
+def test_tower_matches_hugging_face_visual():
+    """The tower loads the checkpoint's ``visual.*`` tensors by name and reproduces the Hugging Face Qwen2-VL vision
+    transformer: same flattened patches in, same merged embeddings out."""
+    import pytest
+    transformers = pytest.importorskip("transformers")
+    from transformers.models.qwen2_vl import modeling_qwen2_vl as hf
+    from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLVisionConfig
+    vc = Qwen2VLVisionConfig(depth=2, embed_dim=32, hidden_size=48, num_heads=4, mlp_ratio=4, patch_size=14,
+                             spatial_merge_size=2, temporal_patch_size=2, in_channels=3)
+    ref = hf.Qwen2VisionTransformerPretrainedModel(vc).eval()
+    g = torch.Generator().manual_seed(3)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(torch.randn(p.shape, generator=g) * (0.05 if p.dim() > 1 else 0.1) + (1.0 if p.dim() == 1 and p.shape[0] == 32 else 0.0))
+    tower = VisionTower(hidden_out=48, dim=32, depth=2, heads=4, patch=14, merge=2, temporal=2, mlp_ratio=4).eval()
+    missing, unexpected = tower.load_state_dict(ref.state_dict(), strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    images = [torch.rand(3, 56, 84, generator=g), torch.rand(4, 3, 28, 56, generator=g)]
+    flat, grids = tower.patchify(images)
+    with torch.no_grad():
+        got = tower.forward_patches(flat, grids)
+        want = ref(flat, grid_thw=torch.tensor(grids)).pooler_output
+    assert got.shape == want.shape
+    assert float((got - want).abs().max()) < 1e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_mrope_positions_match_hugging_face_rope_index():
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers import Qwen2VLConfig
+    from transformers.models.qwen2_vl import modeling_qwen2_vl as hf
+    cfg = Qwen2VLConfig(
+        text_config=dict(hidden_size=32, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2, intermediate_size=64,
+                         vocab_size=400, rope_parameters={"rope_type": "default", "mrope_section": [2, 3, 3], "rope_theta": 10000.0}),
+        vision_config=dict(depth=1, embed_dim=16, hidden_size=32, num_heads=2, patch_size=14, spatial_merge_size=2,
+                           temporal_patch_size=2),
+        image_token_id=PAD, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    model = hf.Qwen2VLModel(cfg)
+    toks = [5, 6, 292] + [PAD] * 6 + [293, 7, 8, 292] + [PAD] * 4 + [293, 9]
+    ids = torch.tensor([toks])
+    kinds = torch.tensor([[1 if t == PAD else 0 for t in toks]], dtype=torch.int32)
+    try:
+        want, _ = model.get_rope_index(ids, kinds, image_grid_thw=torch.tensor([[1, 4, 6], [1, 4, 4]]),
+                                       attention_mask=torch.ones_like(ids))
+    except TypeError:
+        pytest.skip("this transformers version has another get_rope_index signature")
+    got = mrope_positions(toks, PAD, [(1, 4, 6), (1, 4, 4)], 2)
+    assert torch.equal(want[:, 0].to(torch.int32), got)
