@@ -293,6 +293,16 @@ def parse_model_max_length(hf: dict, max_pos: int) -> int:
 
 
 def model_config_from_hf(hf: dict, generation: Optional[dict] = None) -> ModelConfig:
+    tc = hf.get("text_config")
+    if isinstance(tc, dict):
+        # multimodal config.json files of newer exports keep the language model's fields under text_config
+        merged = dict(tc)
+        merged.update({k: v for k, v in hf.items() if k not in ("text_config",) and (v is not None or k not in merged)})
+        merged["model_type"] = hf.get("model_type", tc.get("model_type", "llama"))
+        for k in ("tie_word_embeddings",):
+            if hf.get(k) is None and tc.get(k) is not None:
+                merged[k] = tc[k]
+        hf = merged
     rp = hf.get("rope_parameters")
     if isinstance(rp, dict):
         # newer config.json files keep rope_theta and the scaling description together under rope_parameters

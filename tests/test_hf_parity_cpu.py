@@ -123,3 +123,51 @@ def test_mistral_runs_as_llama():
                       vocab_size=200, max_position_embeddings=256, rms_norm_eps=1e-5, sliding_window=None,
                       tie_word_embeddings=False)
     _check(_init(MistralForCausalLM(c)), c.to_dict())
+
+
+def test_qwen2_vl_image_tokens_mrope_and_vision_tower():
+    """Whole Qwen2-VL forward: the plug-in's vision tower (loaded from the checkpoint's visual.* tensors) feeds the
+    image tokens' embeddings, its mrope positions drive the 3-axis rotary, and the language model's weights arrive
+    through the ``model.language_model.*`` names of newer exports with their fields under ``text_config``."""
+    from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    from ksanallm_b200.ksana_plugin.qwen2_vl.ksana_plugin import VisionTower, mrope_positions
+    pad = 290
+    cfg = Qwen2VLConfig(
+        text_config=dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                         vocab_size=400, max_position_embeddings=256, rms_norm_eps=1e-6,
+                         rope_parameters={"rope_type": "default", "mrope_section": [2, 3, 3], "rope_theta": 10000.0}),
+        vision_config=dict(depth=1, embed_dim=32, hidden_size=64, num_heads=2, patch_size=14, spatial_merge_size=2,
+                           temporal_patch_size=2),
+        image_token_id=pad, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293, tie_word_embeddings=False)
+    hf = _init(Qwen2VLForConditionalGeneration(cfg)).eval()
+    mc = model_config_from_hf(cfg.to_dict())
+    assert mc.model_type == "qwen2_vl" and mc.position_embedding == "mrope" and mc.mrope_section == [2, 3, 3] and mc.qkv_bias
+    mc.max_token_len = 256
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    model = build_model(mc, DictSource(sd, mc.model_type), device="cpu", dtype=torch.float32)
+    tower = VisionTower(hidden_out=64, dim=32, depth=1, heads=2, patch=14, merge=2, temporal=2).eval()
+    missing, unexpected = tower.load_state_dict({k.split("visual.", 1)[1]: v for k, v in sd.items() if "visual." in k}, strict=False)
+    assert not missing and not unexpected
+    img = torch.rand(3, 56, 84, generator=torch.Generator().manual_seed(5))
+    flat, grids = tower.patchify([img])
+    n_img = grids[0][0] * (grids[0][1] // 2) * (grids[0][2] // 2)
+    toks = [5, 6, 292] + [pad] * n_img + [293, 7, 8, 9, 10]
+    kinds = torch.tensor([[1 if t == pad else 0 for t in toks]], dtype=torch.int32)
+    with torch.no_grad():
+        try:
+            want = hf(input_ids=torch.tensor([toks]), pixel_values=flat, image_grid_thw=torch.tensor(grids),
+                      mm_token_type_ids=kinds).logits[0].float()
+        except TypeError:
+            pytest.skip("this transformers version has another multimodal forward signature")
+        emb = tower.forward_patches(flat, grids)
+    T = len(toks)
+    model.allocate_kv_cache(8, 16)
+    ar = torch.arange(T, dtype=torch.int32)
+    step = StepInput(torch.tensor(toks, dtype=torch.int32), ar, ar.clone(), torch.tensor([0, T], dtype=torch.int32),
+                     torch.tensor([T], dtype=torch.int32), torch.arange(8, dtype=torch.int32).view(1, 8),
+                     num_multi=1, num_single=0, num_tokens=T, num_multi_tokens=T, max_q_len=T, max_kv_len=T)
+    step.mrope_positions = mrope_positions(toks, pad, grids, 2)
+    step.refit_positions = torch.arange(3, 3 + n_img, dtype=torch.int32)
+    step.refit_embeddings = emb.float()
+    got = model.forward(step)
+    assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
