@@ -229,9 +229,15 @@ class KsanaPlugin:
         inp = kwargs["ksana_python_input"]
         params = kwargs.get("additional_params") or {}
         images = params.get("images")
-        if not images:
+        if params.get("pixel_values") is not None and params.get("image_grid_thw") is not None:
+            # output of the Hugging Face image processor: flattened patches and their (t, h, w) grids
+            grids = [tuple(int(v) for v in g) for g in torch.as_tensor(params["image_grid_thw"]).tolist()]
+            with torch.no_grad():
+                emb = self.tower.forward_patches(torch.as_tensor(params["pixel_values"]).float(), grids)
+        elif images:
+            emb, grids = self.tower([torch.as_tensor(im) for im in images])
+        else:
             return
-        emb, grids = self.tower([torch.as_tensor(im) for im in images])
         tokens = list(inp["input_tokens"])
         per = [g[0] * (g[1] // self.tower.merge) * (g[2] // self.tower.merge) for g in grids]
         # a single pad token per image in the prompt stands for the whole image: expand it
