@@ -147,6 +147,7 @@ PYBIND11_MODULE(_ksana_engine, m) {
   py::class_<SchedulerConfig>(m, "SchedulerConfig")
       .def(py::init<>())
       .def_readwrite("schedule_strategy", &SchedulerConfig::schedule_strategy)
+      .def_readwrite("dp_size", &SchedulerConfig::dp_size)
       .def_readwrite("waiting_timeout_in_ms", &SchedulerConfig::waiting_timeout_in_ms)
       .def_readwrite("max_waiting_queue_len", &SchedulerConfig::max_waiting_queue_len)
       .def_readwrite("max_step_tokens", &SchedulerConfig::max_step_tokens)

@@ -31,6 +31,13 @@ struct CacheStats {
   int64_t prefix_hit_requests = 0, prefix_hit_tokens = 0, prefix_hit_blocks = 0;
   int64_t evicted_blocks = 0, swapped_out_blocks = 0, swapped_in_blocks = 0, dedup_blocks = 0;
   int64_t flexible_hit_tokens = 0;
+  CacheStats& operator+=(const CacheStats& o) {
+    prefix_hit_requests += o.prefix_hit_requests; prefix_hit_tokens += o.prefix_hit_tokens;
+    prefix_hit_blocks += o.prefix_hit_blocks; evicted_blocks += o.evicted_blocks;
+    swapped_out_blocks += o.swapped_out_blocks; swapped_in_blocks += o.swapped_in_blocks;
+    dedup_blocks += o.dedup_blocks; flexible_hit_tokens += o.flexible_hit_tokens;
+    return *this;
+  }
 };
 
 class CacheManager {

@@ -76,8 +76,9 @@ bool StepPlan::Unpack(const int32_t* d, size_t n, StepPlan* p) {
 
 // --------------------------------------------------------------------------------- Scheduler
 Scheduler::Scheduler(const SchedulerConfig& cfg, int num_device_blocks, int num_host_blocks)
-    : cfg_(cfg), cache_(num_device_blocks, num_host_blocks, cfg.block_token_num, cfg.enable_prefix_cache),
-      split_fuse_on_(cfg.split_fuse_token_num > 0) {
+    : cfg_(cfg), split_fuse_on_(cfg.split_fuse_token_num > 0) {
+  for (int r = 0; r < std::max(1, cfg.dp_size); ++r)
+    caches_.emplace_back(new CacheManager(num_device_blocks, num_host_blocks, cfg.block_token_num, cfg.enable_prefix_cache));
   if (cfg_.max_step_tokens < cfg_.max_batch_size) cfg_.max_step_tokens = cfg_.max_batch_size;
 }
 
@@ -105,7 +106,9 @@ Status Scheduler::AddRequest(int64_t req_id, const std::vector<int>& prompt, con
   std::vector<SeqPtr> group;
   for (int i = 0; i < n; ++i) {
     auto s = std::make_shared<Sequence>();
-    s->seq_id = next_seq_id_++;
+    // siblings share blocks with the leader, so they live on its rank: ids one rank-stride apart
+    s->seq_id = i == 0 ? next_seq_id_ : group[0]->seq_id + static_cast<int64_t>(i) * static_cast<int64_t>(caches_.size());
+    next_seq_id_ = std::max(next_seq_id_, s->seq_id + 1);
     s->req_id = req_id;
     s->index = i;
     s->tokens = prompt;
@@ -144,9 +147,9 @@ void Scheduler::MergeWaitingBuffer() {
 void Scheduler::FinishLocked(const SeqPtr& s, int code, const std::string& msg, int new_token,
                              std::vector<SeqEvent>* ev) {
   if (s->state == SeqState::FINISHED) return;
-  cache_.Release(s->blocks);
+  CacheOf(*s).Release(s->blocks);
   s->blocks.clear();
-  cache_.ReleaseHost(s->host_blocks);
+  CacheOf(*s).ReleaseHost(s->host_blocks);
   s->host_blocks.clear();
   s->state = SeqState::FINISHED;
   s->finish_status = Status(static_cast<RetCode>(code), msg);
@@ -207,7 +210,9 @@ int Scheduler::StepTokenCap(int num_decodes) const {
 
 void Scheduler::PreemptLocked(const SeqPtr& v, StepPlan* plan) {
   ++v->preempt_count;
-  if (cfg_.preempt_mode == 0 && cache_.SwapOut(&v->blocks, &v->host_blocks, &plan->swap_out)) {
+  const size_t so0 = plan->swap_out.size();
+  if (cfg_.preempt_mode == 0 && CacheOf(*v).SwapOut(&v->blocks, &v->host_blocks, &plan->swap_out)) {
+    for (size_t i = so0; i < plan->swap_out.size(); ++i) plan->swap_out[i].device_block += PoolBase(*v);
     v->promoted = std::min(v->promoted, static_cast<int>(v->blocks.size()));
     v->state = SeqState::SWAPPED;
     swapped_.push_back(v);
@@ -215,7 +220,7 @@ void Scheduler::PreemptLocked(const SeqPtr& v, StepPlan* plan) {
     return;
   }
   // recompute: everything generated so far becomes the prompt of a fresh prefill
-  cache_.Release(v->blocks);
+  CacheOf(*v).Release(v->blocks);
   v->blocks.clear();
   v->kv_cached = 0;
   v->promoted = 0;
@@ -255,6 +260,13 @@ void Scheduler::EmitSequence(const SeqPtr& s, StepPlan* plan) {
   }
 }
 
+bool Scheduler::SwapInQualified(CacheManager& cache, const SeqPtr& s, StepPlan* plan) {
+  const size_t n0 = plan->swap_in.size();
+  if (!cache.SwapIn(&s->blocks, &s->host_blocks, &plan->swap_in)) return false;
+  for (size_t i = n0; i < plan->swap_in.size(); ++i) plan->swap_in[i].device_block += PoolBase(*s);
+  return true;
+}
+
 bool Scheduler::Schedule(StepPlan* plan) {
   std::lock_guard<std::mutex> g(mu_);
   MergeWaitingBuffer();
@@ -276,32 +288,40 @@ bool Scheduler::Schedule(StepPlan* plan) {
     step_tokens += s->chunk;
   }
   // a sequence that got no token budget this step (chunk == 0) simply idles until the next one
-  int total_need = 0;
-  for (auto& s : running_) total_need += BlocksNeeded(*s);
+  // per data-parallel rank: blocks this step needs and sequences running there (one rank in all other layouts)
+  const int R = static_cast<int>(caches_.size());
+  std::vector<int> rank_need(R, 0), rank_bs(R, 0);
+  for (auto& s : running_) { rank_need[RankOf(*s)] += BlocksNeeded(*s); ++rank_bs[RankOf(*s)]; }
   bool step_sched_finish = false;
-  while (!running_.empty()) {
-    const int bs = static_cast<int>(running_.size());
-    const int usable = cache_.usable_blocks();
-    if (total_need + CeilMul(bs, cfg_.swapout_block_threshold) <= usable) break;
-    if (bs == 1) {
-      if (total_need <= usable) break;
-      // a lone request that cannot grow any more can never finish
-      SeqPtr v = running_.back();
-      running_.pop_back();
-      FinishLocked(v, RET_OUT_OF_MEMORY, "not enough KV cache blocks for this request", -1, &plan->events);
-      total_need = 0;
-      break;
+  for (int r = 0; r < R; ++r) {
+    while (rank_bs[r] > 0) {
+      const int usable = caches_[r]->usable_blocks();
+      if (rank_need[r] + CeilMul(rank_bs[r], cfg_.swapout_block_threshold) <= usable) break;
+      // the youngest sequence of this rank goes first
+      int vi = static_cast<int>(running_.size()) - 1;
+      while (vi >= 0 && RankOf(*running_[vi]) != r) --vi;
+      if (vi < 0) break;
+      SeqPtr v = running_[vi];
+      if (rank_bs[r] == 1) {
+        if (rank_need[r] <= usable) break;
+        // a lone request that cannot grow any more can never finish
+        running_.erase(running_.begin() + vi);
+        FinishLocked(v, RET_OUT_OF_MEMORY, "not enough KV cache blocks for this request", -1, &plan->events);
+        rank_need[r] = 0;
+        rank_bs[r] = 0;
+        break;
+      }
+      running_.erase(running_.begin() + vi);
+      rank_need[r] -= BlocksNeeded(*v);
+      --rank_bs[r];
+      step_tokens -= v->chunk;
+      if (split_fuse_on_ && cfg_.split_fuse_token_num > 0) split_fuse_on_ = false;   // memory pressure: stop chunk-mixing
+      PreemptLocked(v, plan);
+      step_sched_finish = true;
     }
-    SeqPtr v = running_.back();
-    running_.pop_back();
-    total_need -= BlocksNeeded(*v);
-    step_tokens -= v->chunk;
-    if (split_fuse_on_ && cfg_.split_fuse_token_num > 0) split_fuse_on_ = false;   // memory pressure: stop chunk-mixing
-    PreemptLocked(v, plan);
-    step_sched_finish = true;
   }
   for (auto& s : running_) {
-    const bool ok = cache_.Allocate(BlocksNeeded(*s), &s->blocks);
+    const bool ok = CacheOf(*s).Allocate(BlocksNeeded(*s), &s->blocks);
     if (!ok) { s->chunk = 0; }   // cannot happen after the check above; keep the step consistent anyway
   }
 
@@ -310,16 +330,19 @@ bool Scheduler::Schedule(StepPlan* plan) {
     while (!swapped_.empty()) {
       SeqPtr s = swapped_.front();
       const int bs = static_cast<int>(running_.size());
+      int bs_rank = 0;                                   // block thresholds count the sequences of the same rank
+      for (auto& o : running_) bs_rank += (RankOf(*o) == RankOf(*s));
+      CacheManager& cache = CacheOf(*s);
       const int remaining = static_cast<int>(s->tokens.size()) - s->kv_cached;
       s->chunk = remaining;
       const int need = static_cast<int>(s->host_blocks.size()) +
                        std::max(0, CeilDiv(s->kv_cached + s->chunk, B) -
                                        static_cast<int>(s->blocks.size() + s->host_blocks.size()));
       if (bs + 1 <= cfg_.max_batch_size && step_tokens + s->chunk <= cap &&
-          need + CeilMul(bs, cfg_.swapin_block_threshold) <= cache_.usable_blocks() &&
-          cache_.SwapIn(&s->blocks, &s->host_blocks, &plan->swap_in)) {
-        cache_.Allocate(BlocksNeeded(*s), &s->blocks);
-        s->promoted = cache_.Promote(s->tokens, &s->blocks, s->kv_cached, s->promoted);
+          need + CeilMul(bs_rank, cfg_.swapin_block_threshold) <= cache.usable_blocks() &&
+          SwapInQualified(cache, s, plan)) {
+        cache.Allocate(BlocksNeeded(*s), &s->blocks);
+        s->promoted = cache.Promote(s->tokens, &s->blocks, s->kv_cached, s->promoted);
         s->state = SeqState::RUNNING;
         running_.push_back(s);
         swapped_.pop_front();
@@ -350,20 +373,23 @@ bool Scheduler::Schedule(StepPlan* plan) {
       for (auto& m : git->second) siblings += (m->forked_pending && m->leader == s->seq_id);
     const int bs = static_cast<int>(running_.size());
     if (bs + 1 + siblings > cfg_.max_batch_size) break;
+    int bs_rank = 0;
+    for (auto& o : running_) bs_rank += (RankOf(*o) == RankOf(*s));
+    CacheManager& cache = CacheOf(*s);
     // cached prefix (re-evaluated at every attempt: the tree may have changed meanwhile)
     std::vector<int> pre_blocks;
     std::vector<BlockCopy> flex_copies;
-    int matched = cache_.AcquirePrefix(s->tokens, &pre_blocks);
+    int matched = cache.AcquirePrefix(s->tokens, &pre_blocks);
     int flex = 0;
     if (cfg_.min_flexible_cache_num > 0)
-      flex = cache_.AcquireFlexible(s->tokens, matched, cfg_.min_flexible_cache_num, &pre_blocks, &flex_copies);
+      flex = cache.AcquireFlexible(s->tokens, matched, cfg_.min_flexible_cache_num, &pre_blocks, &flex_copies);
     const int cached = std::min(matched + flex, len - 1);    // at least the last token is computed
     const int remaining = len - cached;
     int chunk = std::min(remaining, std::max(cap - step_tokens, 0));
     if (chunk < remaining) chunk = ((cached + chunk) / B) * B - cached;
     const int unique = std::max(0, CeilDiv(cached + std::max(chunk, 0), B) - static_cast<int>(pre_blocks.size()));
-    if (chunk <= 0 || unique + CeilMul(bs, cfg_.launch_block_threshold) > cache_.usable_blocks()) {
-      cache_.Release(pre_blocks);
+    if (chunk <= 0 || unique + CeilMul(bs_rank, cfg_.launch_block_threshold) > cache.usable_blocks()) {
+      cache.Release(pre_blocks);
       break;   // FIFO: nobody overtakes the head
     }
     s->blocks = pre_blocks;
@@ -372,8 +398,8 @@ bool Scheduler::Schedule(StepPlan* plan) {
     s->flexible_hit_tokens = flex;
     s->promoted = matched / B;
     s->chunk = chunk;
-    cache_.Allocate(unique, &s->blocks);
-    for (auto& c : flex_copies) plan->copies.push_back(c);
+    cache.Allocate(unique, &s->blocks);
+    for (auto& c : flex_copies) plan->copies.push_back({c.src + PoolBase(*s), c.dst + PoolBase(*s), c.pos_delta});
     s->state = SeqState::RUNNING;
     running_.push_back(s);
     waiting_.pop_front();
@@ -439,7 +465,7 @@ void Scheduler::PostStep(const StepPlan& plan, const std::vector<SampledToken>& 
     if (s->state != SeqState::RUNNING) continue;
     s->kv_cached += plan.q_lens[i];
     s->chunk = 0;
-    s->promoted = cache_.Promote(s->tokens, &s->blocks, s->kv_cached, s->promoted);
+    s->promoted = CacheOf(*s).Promote(s->tokens, &s->blocks, s->kv_cached, s->promoted);
   }
   // 2. beam re-parenting uses the parents' state before any token of this step is appended
   struct Reparent { SeqPtr dst; std::vector<int> tokens; std::vector<int> blocks; int kv; int promoted; };
@@ -452,12 +478,15 @@ void Scheduler::PostStep(const StepPlan& plan, const std::vector<SampledToken>& 
     auto pit = by_id_.find(pid);
     if (dit == by_id_.end() || pit == by_id_.end()) continue;
     Reparent mv{dit->second, pit->second->tokens, {}, pit->second->kv_cached, 0};
-    if (!cache_.Fork(pit->second->blocks, pit->second->kv_cached, &mv.blocks, &fork_copies)) continue;
+    if (RankOf(*dit->second) != RankOf(*pit->second)) continue;          // beams of a group share a rank by construction
+    const size_t fc0 = fork_copies.size();
+    if (!CacheOf(*pit->second).Fork(pit->second->blocks, pit->second->kv_cached, &mv.blocks, &fork_copies)) continue;
+    for (size_t k = fc0; k < fork_copies.size(); ++k) { fork_copies[k].src += PoolBase(*pit->second); fork_copies[k].dst += PoolBase(*pit->second); }
     mv.promoted = std::min(pit->second->promoted, pit->second->kv_cached / cfg_.block_token_num);
     moves.push_back(std::move(mv));
   }
   for (auto& mv : moves) {
-    cache_.Release(mv.dst->blocks);
+    CacheOf(*mv.dst).Release(mv.dst->blocks);
     mv.dst->blocks = std::move(mv.blocks);
     mv.dst->tokens = std::move(mv.tokens);
     mv.dst->kv_cached = mv.kv;
@@ -479,7 +508,8 @@ void Scheduler::PostStep(const StepPlan& plan, const std::vector<SampledToken>& 
         // leader appended its own token already when it precedes us; share only the prompt part
         const int shared_tokens = std::min(l->kv_cached, s->prompt_len);
         std::vector<BlockCopy> cps;
-        if (cache_.Fork(l->blocks, shared_tokens, &s->blocks, &cps)) {
+        if (RankOf(*l) == RankOf(*s) && CacheOf(*l).Fork(l->blocks, shared_tokens, &s->blocks, &cps)) {
+          for (auto& c : cps) { c.src += PoolBase(*l); c.dst += PoolBase(*l); }
           pending_copies_.insert(pending_copies_.end(), cps.begin(), cps.end());
           s->kv_cached = shared_tokens;
           s->promoted = std::min(l->promoted, shared_tokens / cfg_.block_token_num);
@@ -535,7 +565,7 @@ bool Scheduler::ReplaceGenerated(int64_t seq_id, const std::vector<int>& generat
     const int keep_blocks = new_cached / B;   // whole blocks that stay valid
     if (keep_blocks < static_cast<int>(s->blocks.size())) {
       std::vector<int> drop(s->blocks.begin() + keep_blocks, s->blocks.end());
-      cache_.Release(drop);
+      CacheOf(*s).Release(drop);
       s->blocks.resize(keep_blocks);
     }
     s->kv_cached = keep_blocks * B;
@@ -562,17 +592,27 @@ SchedulerStats Scheduler::GetStats() {
   s.waiting = static_cast<int64_t>(waiting_.size() + waiting_buffer_.size());
   s.running = static_cast<int64_t>(running_.size());
   s.swapped = static_cast<int64_t>(swapped_.size());
-  s.free_blocks = cache_.free_blocks();
-  s.usable_blocks = cache_.usable_blocks();
-  s.used_blocks = cache_.used_blocks();
-  s.free_host_blocks = cache_.free_host_blocks();
-  s.cache = cache_.stats();
+  // the tightest rank for the pools, the sum for the counters
+  s.free_blocks = caches_[0]->free_blocks();
+  s.usable_blocks = caches_[0]->usable_blocks();
+  s.used_blocks = caches_[0]->used_blocks();
+  s.free_host_blocks = caches_[0]->free_host_blocks();
+  s.cache = caches_[0]->stats();
+  for (size_t r = 1; r < caches_.size(); ++r) {
+    s.free_blocks = std::min<int64_t>(s.free_blocks, caches_[r]->free_blocks());
+    s.usable_blocks = std::min<int64_t>(s.usable_blocks, caches_[r]->usable_blocks());
+    s.used_blocks = std::max<int64_t>(s.used_blocks, caches_[r]->used_blocks());
+    s.free_host_blocks = std::min<int64_t>(s.free_host_blocks, caches_[r]->free_host_blocks());
+    s.cache += caches_[r]->stats();
+  }
   return s;
 }
 
 bool Scheduler::CheckInvariants(std::string* why) {
   std::lock_guard<std::mutex> g(mu_);
-  return cache_.CheckInvariants(why);
+  for (auto& c : caches_)
+    if (!c->CheckInvariants(why)) return false;
+  return true;
 }
 
 }  // namespace ksana

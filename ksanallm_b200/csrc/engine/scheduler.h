@@ -39,6 +39,9 @@ struct SchedulerConfig {
   bool enable_prefix_cache = false;
   int block_token_num = 16;
   int auto_batch_wait_ms = 100;
+  // attention data parallelism: sequence s lives on rank s % dp_size and only that rank holds its KV blocks, so
+  // every rank gets a block pool (and prefix tree, and host swap pool) of its own; block ids are per rank
+  int dp_size = 1;
   std::vector<int> eos_token_ids;
 };
 
@@ -146,8 +149,15 @@ class Scheduler {
   void EmitSequence(const SeqPtr& s, StepPlan* plan);
   int StepTokenCap(int num_decodes) const;
 
+  CacheManager& CacheOf(const Sequence& s) { return *caches_[static_cast<size_t>(s.seq_id % static_cast<int64_t>(caches_.size()))]; }
+  // Copy and swap lists are executed by the ranks, and block ids are per rank: a device block in those lists is
+  // written as rank * blocks_per_rank + block, so that each rank picks out (and un-offsets) its own entries.
+  int PoolBase(const Sequence& s) const { return RankOf(s) * caches_[0]->num_device_blocks(); }
+  bool SwapInQualified(CacheManager& cache, const SeqPtr& s, StepPlan* plan);
+  int RankOf(const Sequence& s) const { return static_cast<int>(s.seq_id % static_cast<int64_t>(caches_.size())); }
+
   SchedulerConfig cfg_;
-  CacheManager cache_;
+  std::vector<std::unique_ptr<CacheManager>> caches_;   // one per data-parallel rank (one in all other layouts)
   std::mutex mu_;
   std::deque<SeqPtr> waiting_buffer_, waiting_;
   std::vector<SeqPtr> running_;

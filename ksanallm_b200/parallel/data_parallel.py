@@ -12,7 +12,9 @@ disjoint set of sequences for everything except the routed experts:
 
 Sequence ownership is ``seq_id % size``: stable for the lifetime of a sequence and known to every rank from the
 broadcast step plan, as are all ranks' row counts, so no sizes are exchanged at run time. Rank 0 schedules and
-samples; the other ranks send it the logits rows of their sequences each step.
+samples; the other ranks send it the logits rows of their sequences each step. The scheduler keeps one KV block pool
+(with its own prefix tree and host swap pool) per rank, so the group holds ``size`` times the sequences of one GPU;
+block ids in a sequence's table are ids of its owner's pool.
 """
 from __future__ import annotations
 
@@ -29,6 +31,7 @@ class AttentionDP:
         self.rank, self.size, self.group = rank, size, group
         self.symm = symm                             # parallel.symm.SymmetricComm: dispatch / combine over peer memory
         self.counts: List[int] = [0] * size          # rows per rank of the step being executed
+        self.blocks_per_rank = 0                     # device blocks of one rank's pool (set by the engine)
         self.gathered_bytes = 0
 
     # ------------------------------------------------------------------ step plan -> this rank's share
@@ -64,10 +67,23 @@ class AttentionDP:
             sample_rows=new_row[sample_rows[my_samples]].astype(np.int32), sample_seq_ids=sample_seq[my_samples].astype(np.int32),
             num_multi=nm, num_single=len(mine) - nm, num_tokens=int(len(rows)), num_multi_tokens=int(ql[:nm].sum()),
             max_q_len=int(ql.max()) if len(ql) else 0,
-            swap_out=plan.swap_out, swap_in=plan.swap_in, copies=plan.copies)
+            swap_out=self._mine(plan.swap_out, 2, (0,)), swap_in=self._mine(plan.swap_in, 2, (0,)),
+            copies=self._mine(plan.copies, 3, (0, 1)))
         self._sample_owner = sample_owner
         self._sample_counts = [int((sample_owner == r).sum()) for r in range(self.size)]
         return sub
+
+    def _mine(self, flat, width: int, block_cols) -> np.ndarray:
+        """Swap / copy entries of this rank. The scheduler keeps one block pool per rank and writes a device block of
+        these lists as ``rank * blocks_per_rank + block``; entries of other ranks are dropped, ours lose the offset."""
+        a = np.asarray(flat, dtype=np.int32).reshape(-1, width)
+        if a.size == 0 or not self.blocks_per_rank:
+            return np.asarray(flat, dtype=np.int32)
+        keep = (a[:, block_cols[0]] // self.blocks_per_rank) == self.rank
+        a = a[keep].copy()
+        for c in block_cols:
+            a[:, c] -= self.rank * self.blocks_per_rank
+        return a.reshape(-1)
 
     # ------------------------------------------------------------------ logits back to the scheduler rank
     def gather_logits(self, local: Optional[torch.Tensor], vocab: int, device) -> Optional[torch.Tensor]:

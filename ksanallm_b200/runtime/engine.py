@@ -287,6 +287,10 @@ class LLMEngine:
         sc.enable_prefix_cache = bool(bs.enable_auto_prefix_cache)
         sc.block_token_num = cfg.block_manager.block_token_num
         sc.eos_token_ids = list(model_cfg.eos_token_ids)
+        dp = getattr(model, "dp", None)
+        if dp is not None and getattr(dp, "size", 1) > 1:
+            sc.dp_size = int(dp.size)          # every data-parallel rank's cache only holds its own sequences
+            dp.blocks_per_rank = int(num_blocks)
         self.sched_cfg = sc
         if num_blocks * sc.block_token_num < sc.max_token_len:
             raise ValueError(f"{num_blocks} KV blocks of {sc.block_token_num} tokens cannot hold max_token_len "

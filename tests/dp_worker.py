@@ -34,7 +34,11 @@ def engine_cfg():
     ec.batch_scheduler.max_batch_size = 8
     ec.batch_scheduler.max_token_len = 300
     ec.batch_scheduler.max_step_tokens = 512
-    ec.block_manager.device_blocks_num = 128
+    ec.block_manager.device_blocks_num = int(os.environ.get("KSANA_TEST_DP_BLOCKS", "128"))
+    ec.batch_scheduler.max_token_len = min(300, ec.block_manager.device_blocks_num * 16)
+    if os.environ.get("KSANA_TEST_DP_HOST_BLOCKS"):
+        ec.block_manager.host_blocks_num = int(os.environ["KSANA_TEST_DP_HOST_BLOCKS"])
+        ec.batch_scheduler.preempt_mode = 0
     return ec
 
 
@@ -63,7 +67,8 @@ def main():
         moe = llm.model.layers[0].moe
         torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "first": torch.stack([first[k] for k in order]),
                     "experts": (moe.expert_lo, moe.expert_hi), "gathered_bytes": llm.model.dp.gathered_bytes if llm.model.dp else 0,
-                    "peer_memory": bool(llm.model.dp is not None and llm.model.dp.symm is not None)},
+                    "peer_memory": bool(llm.model.dp is not None and llm.model.dp.symm is not None),
+                    "stats": dict(llm.engine.scheduler.stats())},
                    out_path)
     import torch.distributed as dist
     llm.shutdown()

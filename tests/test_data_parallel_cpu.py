@@ -67,3 +67,26 @@ def test_attention_dp_matches_single_process(tmp_path, nproc, port):
     assert got["gathered_bytes"] > 0
     assert float((got["first"] - want_first).abs().max()) < 1e-3
     assert got["tokens"] == want_tokens
+
+
+@pytest.mark.parametrize("blocks,host", [(12, 0)])
+def test_attention_dp_ranks_pool_their_caches(tmp_path, blocks, host):
+    """Two ranks with `blocks` KV blocks each: together they hold what one pool of that size cannot (12 blocks: no
+    preemption although the five sequences need 14); the results stay those of the single process. (Swap lists per
+    rank are checked on the scheduler in tests/test_scheduler.py.)"""
+    want_tokens, want_first = _single()
+    out = str(tmp_path / "dp.pt")
+    env = dict(os.environ, OMP_NUM_THREADS="1", KSANA_TEST_DP_BLOCKS=str(blocks))
+    if host:
+        env["KSANA_TEST_DP_HOST_BLOCKS"] = str(host)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29671 + blocks), os.path.join(ROOT, "tests", "dp_worker.py"), out, "cpu"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    assert got["tokens"] == want_tokens
+    st = got["stats"]
+    if host:
+        assert st["preempt_swap"] > 0 and st["swap_in"] > 0
+    else:
+        assert st["preempt_swap"] == 0 and st["preempt_recompute"] == 0

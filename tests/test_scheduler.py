@@ -263,3 +263,74 @@ def test_static_batching_runs_batches_to_completion():
     s.post_step(plan, [11, 12, 13])
     outs, fin, _ = run_to_completion(s, seeds)
     assert fin[late[0]] == 0
+
+
+def test_data_parallel_ranks_have_block_pools_of_their_own():
+    """dp_size ranks: a sequence's blocks come from the pool of rank seq_id % dp_size, so two ranks hold twice the
+    sequences; slots may repeat across ranks but never inside one; siblings stay on their leader's rank; memory
+    pressure on one rank preempts only that rank's sequences."""
+    B, blocks = 6, 12
+    one = make(num_blocks=blocks, host_blocks=0, preempt_mode=1)
+    two = make(num_blocks=blocks, host_blocks=0, preempt_mode=1, dp_size=2)
+    results = []
+    for s, dp in ((one, 1), (two, 2)):
+        seeds, prompts = {}, {}
+        for r in range(8):
+            p = list(range(40 + r, 40 + r + 10))
+            code, _, ids = s.add_request(r, p, cfg(20))
+            assert code == 0
+            seeds[ids[0]], prompts[ids[0]] = r + 5, len(p)
+
+        def check(plan, dp=dp):
+            per_rank = {}
+            row = 0
+            for k, sid in enumerate(plan.seq_ids.tolist()):
+                q = int(plan.q_lens[k])
+                rank = sid % dp
+                for slot in plan.slots[row:row + q].tolist():
+                    assert slot not in per_rank.setdefault(rank, set()), "two tokens of one rank write the same KV slot"
+                    per_rank[rank].add(slot)
+                    assert 0 <= slot < blocks * B
+                row += q
+
+        outs, fin, steps = run_to_completion(s, seeds, kv_check=check)
+        for sid in seeds:
+            assert fin[sid] == 0 and outs[sid] == expected(prompts[sid], seeds[sid], 20)
+        results.append((steps, s.stats()["preempt_recompute"]))
+    # 8 sequences x 5 blocks at the end do not fit 12 blocks, but fit 2 x 12 better: fewer preemptions and steps
+    assert results[1][1] < results[0][1] and results[1][0] <= results[0][0]
+    # parallel sampling: the siblings share the leader's blocks, hence its rank
+    s = make(num_blocks=40, dp_size=4)
+    code, _, ids = s.add_request(1, list(range(10, 30)), cfg(6, num_return_sequences=3, topk=4))
+    code, _, ids2 = s.add_request(2, list(range(50, 70)), cfg(6))
+    assert len({i % 4 for i in ids}) == 1 and len(set(ids + ids2)) == 4
+    seeds = {i: 3 + k for k, i in enumerate(ids + ids2)}
+    outs, fin, _ = run_to_completion(s, seeds)
+    assert all(fin[i] == 0 and len(outs[i]) == 6 for i in ids + ids2)
+
+
+def test_data_parallel_swap_lists_name_the_owning_pool():
+    """Swap mode under data parallelism: a device block in the swap lists is rank * blocks_per_rank + block, the rank
+    being the owner of the swapped sequence; what goes out comes back; tokens are unaffected."""
+    blocks = 10
+    s = make(num_blocks=blocks, host_blocks=40, preempt_mode=0, dp_size=2)
+    seeds, prompts = {}, {}
+    for r in range(8):
+        p = list(range(60 + r, 60 + r + 9))
+        code, _, ids = s.add_request(r, p, cfg(30))
+        seeds[ids[0]], prompts[ids[0]] = r + 2, len(p)
+    seen = {"out": set(), "in": set()}
+
+    def check(plan):
+        for key, arr in (("out", plan.swap_out), ("in", plan.swap_in)):
+            a = np.asarray(arr).reshape(-1, 2)
+            for dev, host in a.tolist():
+                assert 0 <= dev < 2 * blocks and 0 <= host < 40
+                seen[key].add(dev // blocks)
+
+    outs, fin, _ = run_to_completion(s, seeds, kv_check=check)
+    for sid in seeds:
+        assert fin[sid] == 0 and outs[sid] == expected(prompts[sid], seeds[sid], 30)
+    st = s.stats()
+    assert st["preempt_swap"] > 0 and st["swapped_out_blocks"] == st["swapped_in_blocks"]
+    assert seen["out"] == {0, 1} and seen["in"] == {0, 1}
