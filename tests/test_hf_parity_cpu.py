@@ -171,3 +171,89 @@ def test_qwen2_vl_image_tokens_mrope_and_vision_tower():
     step.refit_embeddings = emb.float()
     got = model.forward(step)
     assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_baichuan_13b_style_alibi_wpack_normhead():
+    """Baichuan has no implementation inside transformers; this restates its published modeling code (13B class):
+    packed W_pack projection, ALiBi bias slope_h * key_position on the attention scores, RMSNorm, SwiGLU, and
+    Baichuan2's NormHead (rows of lm_head normalised). The slopes are also checked against BLOOM's builder."""
+    import math
+    import torch.nn.functional as F
+    from transformers.models.bloom.modeling_bloom import build_alibi_tensor
+    from ksanallm_b200.models.common import alibi_slopes
+    for heads in (8, 32, 40):
+        want = build_alibi_tensor(torch.ones(1, 5), heads, torch.float32).view(heads, 5)[:, 1]     # slope * position 1
+        assert torch.allclose(alibi_slopes(heads), want, rtol=1e-6)
+
+    H, L, heads, inter, V, T = 80, 2, 5, 96, 125696 // 512, 19          # hidden != 4096 -> ALiBi
+    hf_cfg = {"model_type": "baichuan", "hidden_size": H, "num_hidden_layers": L, "num_attention_heads": heads,
+              "intermediate_size": inter, "vocab_size": 125696, "rms_norm_eps": 1e-6, "max_position_embeddings": 128}
+    g = torch.Generator().manual_seed(2)
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.08
+    sd = {"model.embed_tokens.weight": rnd(125696, H) * 0, "model.norm.weight": 1 + rnd(H), "lm_head.weight": rnd(125696, H) * 0}
+    # only the first V rows of the big vocabulary are exercised; the rest stays zero (the size selects Baichuan2's NormHead)
+    sd["model.embed_tokens.weight"][:V] = rnd(V, H)
+    sd["lm_head.weight"][:V] = rnd(V, H)
+    for i in range(L):
+        p = f"model.layers.{i}."
+        sd[p + "self_attn.W_pack.weight"] = rnd(3 * H, H)
+        sd[p + "self_attn.o_proj.weight"] = rnd(H, H)
+        sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"] = rnd(inter, H), rnd(inter, H)
+        sd[p + "mlp.down_proj.weight"] = rnd(H, inter)
+        sd[p + "input_layernorm.weight"], sd[p + "post_attention_layernorm.weight"] = 1 + rnd(H), 1 + rnd(H)
+    tokens = torch.randint(3, V, (T,), generator=g).tolist()
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+
+    h = sd["model.embed_tokens.weight"][tokens]
+    slopes = alibi_slopes(heads)
+    D = H // heads
+    bias = slopes.view(heads, 1, 1) * torch.arange(T).view(1, 1, T).float()
+    causal = torch.full((T, T), float("-inf")).triu(1)
+    for i in range(L):
+        p = f"model.layers.{i}."
+        x = rms(h, sd[p + "input_layernorm.weight"])
+        q, k, v = (x @ sd[p + "self_attn.W_pack.weight"].t()).view(T, 3, heads, D).unbind(1)
+        s = torch.einsum("thd,shd->hts", q, k) / math.sqrt(D) + bias + causal
+        a = torch.einsum("hts,shd->thd", s.softmax(-1), v).reshape(T, H)
+        h = h + a @ sd[p + "self_attn.o_proj.weight"].t()
+        x = rms(h, sd[p + "post_attention_layernorm.weight"])
+        h = h + (F.silu(x @ sd[p + "mlp.gate_proj.weight"].t()) * (x @ sd[p + "mlp.up_proj.weight"].t())) @ sd[p + "mlp.down_proj.weight"].t()
+    want = rms(h, sd["model.norm.weight"]) @ F.normalize(sd["lm_head.weight"][:V], dim=-1).t()
+    got = _ours(hf_cfg, sd, tokens)[:, :V]
+    assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_chatglm3_checkpoint_names_and_config_keys():
+    """The original ChatGLM2/3 layout (fused query_key_value with bias, dense_h_to_4h = gate|up, THUDM config keys)
+    arrives through the weight map: the tensors of a tiny GLM-4 model renamed that way give GLM-4's logits."""
+    from transformers import GlmConfig, GlmForCausalLM
+    c = GlmConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                  vocab_size=200, max_position_embeddings=256, rms_norm_eps=1e-5, head_dim=16, partial_rotary_factor=0.5,
+                  attention_bias=True, tie_word_embeddings=False, pad_token_id=0)
+    hf = _init(GlmForCausalLM(c)).eval()
+    src = hf.state_dict()
+    sd = {"transformer.embedding.word_embeddings.weight": src["model.embed_tokens.weight"],
+          "transformer.encoder.final_layernorm.weight": src["model.norm.weight"],
+          "transformer.output_layer.weight": src["lm_head.weight"],
+          "transformer.rotary_pos_emb.inv_freq": torch.zeros(4)}
+    for i in range(2):
+        p, q = f"model.layers.{i}.", f"transformer.encoder.layers.{i}."
+        sd[q + "input_layernorm.weight"] = src[p + "input_layernorm.weight"]
+        sd[q + "post_attention_layernorm.weight"] = src[p + "post_attention_layernorm.weight"]
+        for kind in ("weight", "bias"):
+            sd[q + f"self_attention.query_key_value.{kind}"] = torch.cat(
+                [src[p + f"self_attn.{n}_proj.{kind}"] for n in ("q", "k", "v")], 0)
+        sd[q + "self_attention.dense.weight"] = src[p + "self_attn.o_proj.weight"]
+        sd[q + "mlp.dense_h_to_4h.weight"] = src[p + "mlp.gate_up_proj.weight"]
+        sd[q + "mlp.dense_4h_to_h.weight"] = src[p + "mlp.down_proj.weight"]
+    thudm = {"model_type": "chatglm", "hidden_size": 64, "num_layers": 2, "num_attention_heads": 4, "kv_channels": 16,
+             "multi_query_attention": True, "multi_query_group_num": 2, "ffn_hidden_size": 128, "padded_vocab_size": 200,
+             "layernorm_epsilon": 1e-5, "add_qkv_bias": True, "seq_length": 256, "rmsnorm": True}
+    torch.manual_seed(0)
+    tokens = torch.randint(3, 200, (23,)).tolist()
+    with torch.no_grad():
+        want = hf(torch.tensor([tokens])).logits[0].float()
+    got = _ours(thudm, sd, tokens)
+    assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
