@@ -350,6 +350,10 @@ def model_config_from_hf(hf: dict, generation: Optional[dict] = None) -> ModelCo
     c.max_token_len = parse_model_max_length(hf, c.max_position_embeddings)
     if arch == "qwen" or arch == "qwen2_vl" or arch == "qwen2_moe":
         c.qkv_bias = True
+    if mt == "qwen":
+        # first-generation Qwen: config.json counts gate and up together (w1 and w2 are intermediate_size / 2 wide each)
+        c.intermediate_size //= 2
+        c.rms_norm_eps = hf.get("layer_norm_epsilon", c.rms_norm_eps)
     if arch == "qwen2_vl":
         c.position_embedding, c.is_visual = "mrope", True
         c.mrope_section = list((hf.get("rope_scaling") or {}).get("mrope_section", [16, 24, 24]))

@@ -257,3 +257,33 @@ def test_chatglm3_checkpoint_names_and_config_keys():
         want = hf(torch.tensor([tokens])).logits[0].float()
     got = _ours(thudm, sd, tokens)
     assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_qwen_first_generation_checkpoint_names():
+    """Qwen-7B/14B (first generation) layout through its weight map: fused c_attn with bias, w2 = gate, w1 = up,
+    intermediate_size counting both. The tensors of a tiny Qwen2 model (no grouped KV heads) renamed that way give
+    Qwen2's logits."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    c = Qwen2Config(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, intermediate_size=96,
+                    vocab_size=200, max_position_embeddings=256, rms_norm_eps=1e-6, rope_theta=10000.0,
+                    tie_word_embeddings=False, use_sliding_window=False)
+    hf = _init(Qwen2ForCausalLM(c)).eval()
+    src = hf.state_dict()
+    sd = {"transformer.wte.weight": src["model.embed_tokens.weight"], "transformer.ln_f.weight": src["model.norm.weight"],
+          "lm_head.weight": src["lm_head.weight"]}
+    for i in range(2):
+        p, q = f"model.layers.{i}.", f"transformer.h.{i}."
+        sd[q + "ln_1.weight"], sd[q + "ln_2.weight"] = src[p + "input_layernorm.weight"], src[p + "post_attention_layernorm.weight"]
+        for kind in ("weight", "bias"):
+            sd[q + f"attn.c_attn.{kind}"] = torch.cat([src[p + f"self_attn.{n}_proj.{kind}"] for n in ("q", "k", "v")], 0)
+        sd[q + "attn.c_proj.weight"] = src[p + "self_attn.o_proj.weight"]
+        sd[q + "mlp.w2.weight"], sd[q + "mlp.w1.weight"] = src[p + "mlp.gate_proj.weight"], src[p + "mlp.up_proj.weight"]
+        sd[q + "mlp.c_proj.weight"] = src[p + "mlp.down_proj.weight"]
+    v1 = {"model_type": "qwen", "hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4, "kv_channels": 16,
+          "intermediate_size": 192, "vocab_size": 200, "layer_norm_epsilon": 1e-6, "rotary_emb_base": 10000, "seq_length": 256}
+    torch.manual_seed(0)
+    tokens = torch.randint(3, 200, (23,)).tolist()
+    with torch.no_grad():
+        want = hf(torch.tensor([tokens])).logits[0].float()
+    got = _ours(v1, sd, tokens)
+    assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
