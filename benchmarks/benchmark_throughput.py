@@ -122,6 +122,25 @@ def read_prompts(path: str, col_idx: int, prompt_num: int, shuffle: bool, seed: 
     return prompts[:prompt_num] if prompt_num > 0 else prompts
 
 
+_TOKENIZER = None
+
+
+def load_tokenizer(args):
+    global _TOKENIZER
+    if _TOKENIZER is None:
+        if not args.tokenizer_path:
+            raise SystemExit("--chat_template needs --tokenizer_path")
+        from transformers import AutoTokenizer
+        _TOKENIZER = AutoTokenizer.from_pretrained(args.tokenizer_path, trust_remote_code=True)
+    return _TOKENIZER
+
+
+def apply_chat_template(args, prompt: str, tokenizer=None) -> str:
+    """The prompt as the single user turn of a conversation, rendered to text with the generation prompt appended."""
+    tok = tokenizer or load_tokenizer(args)
+    return tok.apply_chat_template([{"role": "user", "content": prompt}], tokenize=False, add_generation_prompt=True)
+
+
 def build_payload(args, prompt, max_new_tokens: Optional[int] = None) -> dict:
     sampling = {
         "temperature": args.temperature, "topk": args.topk, "topp": args.topp,
@@ -131,7 +150,11 @@ def build_payload(args, prompt, max_new_tokens: Optional[int] = None) -> dict:
         "num_return_sequences": args.num_return_sequences, "logprobs": args.logprobs, "ignore_eos": args.ignore_eos,
         "stop_token_ids": args.stop_token_ids or [],
     }
+    if args.stop_strings:
+        sampling["stop_strings"] = list(args.stop_strings)
     body = {"sampling_config": sampling, "stream": bool(args.stream)}
+    if args.structured_output_regex:
+        body["structured_output_regex"] = args.structured_output_regex
     if isinstance(prompt, str):
         body["prompt"] = prompt
     else:
@@ -272,6 +295,13 @@ def args_config(argv=None):
     p.add_argument("--num_return_sequences", type=int, default=1)
     p.add_argument("--logprobs", type=int, default=0)
     p.add_argument("--stop_token_ids", type=int, nargs="*", default=None)
+    p.add_argument("--stop_strings", type=str, nargs="*", default=None, help="strings that end a generation")
+    p.add_argument("--structured_output_regex", type=str, default=None, help="regular expression the outputs must match")
+    p.add_argument("--structured_output_file", type=str, default=None, help="file holding that regular expression")
+    p.add_argument("--tokenizer_path", type=str, default=None,
+                   help="Hugging Face tokenizer: needed by --chat_template, and used to count tokens of text-only answers")
+    p.add_argument("--chat_template", action="store_true",
+                   help="wrap every prompt as one user message with the tokenizer's chat template")
     p.add_argument("--ignore_eos", action="store_true")
     p.add_argument("--client_timeout", type=float, default=3600.0)
     return p.parse_args(argv)
@@ -279,11 +309,16 @@ def args_config(argv=None):
 
 def run_benchmark(args) -> List[dict]:
     url = f"http://{args.host}:{args.port}/generate"
+    if args.structured_output_file:
+        with open(args.structured_output_file, "r", encoding="utf-8") as f:
+            args.structured_output_regex = f.read().strip()
     if args.synthetic:
         work = synthetic_prompts(args.synthetic, args.vocab_size, args.seed)
         args.ignore_eos = True
     elif args.input_csv:
         work = [(p, None) for p in read_prompts(args.input_csv, args.col_idx, args.prompt_num, args.shuffle, args.seed)]
+        if args.chat_template:
+            work = [(apply_chat_template(args, p), n) for p, n in work]
     else:
         raise SystemExit("give --input_csv or --synthetic")
     pct = sorted(set([50.0] + list(args.percentiles)))

@@ -21,8 +21,8 @@ class ByteTokenizer:
         return bs.decode("utf-8", errors="replace")
 
     def apply_chat_template(self, messages, tokenize=True, add_generation_prompt=True):
-        text = "".join(f"<{m['role']}>{m['content']}" for m in messages) + "<assistant>"
-        return self.encode(text)
+        text = "".join(f"<{m['role']}>{m['content']}" for m in messages) + ("<assistant>" if add_generation_prompt else "")
+        return self.encode(text) if tokenize else text
 
 
 def tiny_model_cfg(vocab=300, **kw):

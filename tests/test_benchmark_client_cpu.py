@@ -79,3 +79,26 @@ def test_client_against_live_server(server, tmp_path, extra):
     if "--stream" in extra:
         assert s["avg_ttft_s"] > 0 and s["p99_ttft_s"] >= s["p50_ttft_s"] and "avg_tpot_s" in s
     assert perf.exists() and (tmp_path / "out.csv").read_text().count("\n") == 7
+
+
+def test_client_text_prompts_chat_template_stop_strings_and_regex(server, tmp_path):
+    """Text prompts from a CSV file wrapped by the tokenizer's chat template, a stop string and a structured-output
+    expression read from a file: all reach the server in the request body and the run completes."""
+    csv_path = tmp_path / "prompts.csv"
+    csv_path.write_text("id,prompt\n1,hello there\n2,second prompt\n3,third\n", encoding="utf-8")
+    regex_path = tmp_path / "regex.txt"
+    regex_path.write_text("[a-c]{3}\n", encoding="utf-8")
+    args = bt.args_config(["--port", str(server), "--input_csv", str(csv_path), "--col_idx", "1", "--max_new_tokens", "6",
+                           "--mode", "sync", "--concurrency", "2", "--client_timeout", "60", "--stop_strings", "zzzz",
+                           "--structured_output_file", str(regex_path), "--chat_template", "--tokenizer_path", "unused"])
+    bt._TOKENIZER = ByteTokenizer()                       # stands in for AutoTokenizer.from_pretrained
+    try:
+        wrapped = bt.apply_chat_template(args, "hello there")
+        assert wrapped == "<user>hello there<assistant>"
+        res = bt.run_benchmark(args)
+    finally:
+        bt._TOKENIZER = None
+    assert args.structured_output_regex == "[a-c]{3}"
+    body = bt.build_payload(args, wrapped)
+    assert body["structured_output_regex"] == "[a-c]{3}" and body["sampling_config"]["stop_strings"] == ["zzzz"]
+    assert res[0]["finished"] == 3 and res[0]["failed"] == 0
