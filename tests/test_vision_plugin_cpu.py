@@ -111,3 +111,43 @@ def test_mrope_positions_match_hugging_face_rope_index():
         pytest.skip("this transformers version has another get_rope_index signature")
     got = mrope_positions(toks, PAD, [(1, 4, 6), (1, 4, 4)], 2)
     assert torch.equal(want[:, 0].to(torch.int32), got)
+
+
+def test_qwen_vl_first_generation_tower_and_spans():
+    """First-generation Qwen-VL: the tower's parameters carry the checkpoint's names, a picture of any size becomes a
+    fixed number of embeddings, and the <img>path</img> spans of the token stream are found and filled."""
+    from ksanallm_b200.ksana_plugin.qwen_vl.ksana_plugin import KsanaPlugin as QwenVLPlugin, VisionTower as Tower1, image_spans
+    from ksanallm_b200.ksana_plugin.qwen_vl.ksana_plugin import resize_positions, sincos_2d
+    tower = Tower1(image_size=56, patch=14, width=32, depth=1, heads=2, mlp_ratio=2.0, queries=4, out_dim=128, trained_grid=2).eval()
+    names = set(tower.state_dict().keys())
+    expected = {"conv1.weight", "positional_embedding", "ln_pre.weight", "ln_pre.bias", "proj", "ln_post.weight", "ln_post.bias",
+                "attn_pool.pos_embed", "attn_pool.query", "attn_pool.kv_proj.weight", "attn_pool.attn.in_proj_weight",
+                "attn_pool.attn.in_proj_bias", "attn_pool.attn.out_proj.weight", "attn_pool.attn.out_proj.bias",
+                "attn_pool.ln_q.weight", "attn_pool.ln_q.bias", "attn_pool.ln_kv.weight", "attn_pool.ln_kv.bias"}
+    expected |= {f"transformer.resblocks.0.{n}" for n in (
+        "ln_1.weight", "ln_1.bias", "ln_2.weight", "ln_2.bias", "attn.in_proj.weight", "attn.in_proj.bias",
+        "attn.out_proj.weight", "attn.out_proj.bias", "mlp.c_fc.weight", "mlp.c_fc.bias", "mlp.c_proj.weight", "mlp.c_proj.bias")}
+    assert names == expected
+    g = torch.Generator().manual_seed(0)
+    img = torch.rand(3, 40, 70, generator=g)
+    px = tower.preprocess(img)
+    assert px.shape == (3, 56, 56)
+    out = tower(torch.stack([px, tower.preprocess(1.0 - img)]))
+    assert out.shape == (2, 4, 128) and float((out[0] - out[1]).abs().max()) > 1e-6
+    # position tables: identity when the grid matches, smooth resize otherwise; sine/cosine table is bounded
+    t = torch.arange(8.0).view(4, 2)
+    assert torch.equal(resize_positions(t, 4), t) and resize_positions(t, 16).shape == (16, 2)
+    assert sincos_2d(16, 3).shape == (9, 16) and float(sincos_2d(16, 3).abs().max()) <= 1.0
+    # spans: <img> = 500, </img> = 501, pad = 502; the path is spelled in bytes
+    path = "a/b.pt"
+    toks = [1, 2, 500] + list(path.encode()) + [502] * (6 - len(path)) + [501, 9, 500] + list(b"zz") + [502, 502, 502, 502] + [501]
+    spans = image_spans(toks, 500)
+    assert [(p, n, s) for p, n, s in spans] == [(3, 6, path), (12, 6, "zz")]
+    plugin = QwenVLPlugin()
+    plugin.init_plugin(model_path="", visual={"image_start_id": 500, "image_size": 56, "width": 32, "layers": 1, "heads": 2,
+                                              "mlp_ratio": 2.0, "n_queries": 4, "output_dim": 128})
+    plugin.tower.float().cpu()
+    inp = {"input_tokens": toks}
+    plugin.preprocess(ksana_python_input=inp, additional_params={"images": [img, 1.0 - img]})
+    assert inp["input_refit_embedding"]["pos"] == [3, 12]
+    assert [tuple(e.shape) for e in inp["input_refit_embedding"]["embeddings"]] == [(4, 128), (4, 128)]
