@@ -1,6 +1,7 @@
 """Request-level features through the real engine on CPU: parallel sampling, beam search, log-probs,
 penalties, n-gram bans, stop strings, structured output, streaming + abort, /forward targets, swap."""
 import math
+import pytest
 import threading
 
 import torch
@@ -178,3 +179,26 @@ def test_fp8_tile_choice_rule():
             (512, 57344, 8192), (16384, 28672, 4096)]
     std = [(4096, 7168, 2048), (16384, 4096, 1024), (16384, 2048, 7168), (8192, 1280, 8192), (256, 1024, 8192)]
     assert all(_tall_wins(*s) for s in tall) and not any(_tall_wins(*s) for s in std)
+
+
+def test_kv_scale_calibration_writes_the_reference_file_format(tmp_path):
+    """The calibration tool's file is read back by the config loader, and its scales are the cache's largest
+    magnitudes over the e4m3 range."""
+    from ksanallm_b200.config import EngineConfig, load_kv_scales
+    from ksanallm_b200.llm import LLM
+    from ksanallm_b200.utils.kv_scale_calibration import calibrate_kv_scales, layer_amax, write_kv_scales
+    cfg = tiny_model_cfg()
+    ec = EngineConfig()
+    ec.batch_scheduler.max_token_len = 128
+    ec.block_manager.device_blocks_num = 64
+    llm = LLM(ec, cfg, weights="random", device="cpu", dtype=torch.float32)
+    prompts = [[5 + i, 9, 11, 13 + i, 17, 19] for i in range(5)]
+    scales = calibrate_kv_scales(llm, prompts, max_new_tokens=3, batch=2)
+    assert len(scales) == cfg.num_layers and all(s > 0 for s in scales)
+    want = layer_amax(llm.model.kv_cache).amax(dim=1) / 448.0
+    assert all(s >= float(w) - 1e-9 for s, w in zip(scales, want))        # the running maximum covers the last batch
+    out = tmp_path / "kv_cache_scales.json"
+    write_kv_scales(str(out), scales)
+    back = load_kv_scales(str(out), cfg.num_layers)
+    assert [b[0] for b in back] == pytest.approx(scales) and all(b[0] == b[1] for b in back)
+    llm.shutdown()
