@@ -287,3 +287,14 @@ def test_qwen_first_generation_checkpoint_names():
         want = hf(torch.tensor([tokens])).logits[0].float()
     got = _ours(v1, sd, tokens)
     assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("scaling", [{"rope_type": "linear", "factor": 4.0},
+                                     {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 16,
+                                      "beta_fast": 32.0, "beta_slow": 1.0}])
+def test_llama_rope_scaling_variants(scaling):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    c = LlamaConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                    vocab_size=200, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0,
+                    rope_scaling=dict(scaling), tie_word_embeddings=False)
+    _check(_init(LlamaForCausalLM(c)), c.to_dict())
