@@ -143,7 +143,7 @@ def build_deepseek(cfg: ModelConfig, source, tp_rank, tp_size, comm, device, dty
     """MLA attention weights + dense / MoE feed-forward, canonical names as in the HF checkpoint
     (q_a_proj, q_a_layernorm, q_b_proj, kv_a_proj_with_mqa, kv_a_layernorm, kv_b_proj, o_proj)."""
     from .moe import load_moe
-    from .weights import RandomSource, _cols, _make_linear, _rows
+    from .weights import RandomSource, _cat0, _cols, _dense, _make_linear, _rows
     m = DeepseekModel(cfg, tp_rank, tp_size, comm, device, dtype, layer_range, max_positions=max_positions)
     H, Hq_all = cfg.hidden_size, cfg.num_heads
     nope, rope, vdim, lora = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
@@ -165,7 +165,7 @@ def build_deepseek(cfg: ModelConfig, source, tp_rank, tp_size, comm, device, dty
         q_b = _make_linear(_rows(q_b_full, tp_rank, tp_size), None, device, dtype, quant)
         kv_a = _make_linear(get(p + "kv_a_proj_with_mqa.weight", (lora + rope, H)), None, device, dtype, quant)
         kv_a_norm = get(p + "kv_a_layernorm.weight", (lora,), "ones").to(device=device, dtype=dtype)
-        kv_b = _rows(get(p + "kv_b_proj.weight", (Hq_all * (nope + vdim), lora)), tp_rank, tp_size).to(device)
+        kv_b = _dense(_rows(get(p + "kv_b_proj.weight", (Hq_all * (nope + vdim), lora)), tp_rank, tp_size)).to(device)
         kv_b = kv_b.float().view(Hq, nope + vdim, lora)
         mla = MLAWeights(q_a, q_a_norm, q_b, kv_a, kv_a_norm, kv_b[:, :nope].contiguous().to(dtype),
                          kv_b[:, nope:].contiguous().to(dtype))
@@ -185,7 +185,7 @@ def build_deepseek(cfg: ModelConfig, source, tp_rank, tp_size, comm, device, dty
             g = _rows(get(lp + "mlp.gate_proj.weight", (inter, H)), tp_rank, tp_size)
             u = _rows(get(lp + "mlp.up_proj.weight", (inter, H)), tp_rank, tp_size)
             d = _cols(get(lp + "mlp.down_proj.weight", (H, inter)), tp_rank, tp_size)
-            lw.gate_up = _make_linear(torch.cat([g, u], 0), None, device, dtype, quant)
+            lw.gate_up = _make_linear(_cat0([g, u]), None, device, dtype, quant)
             lw.down = _make_linear(d, None, device, dtype, quant)
         m.layers.append(lw)
     m.final_norm = get("model.norm.weight", (H,), "ones").to(device=device, dtype=dtype)

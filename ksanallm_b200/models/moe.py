@@ -53,20 +53,20 @@ class MoEWeights:
 
 
 def _rows(t, rank, size):
-    n = (t.shape[0] + size - 1) // size
-    return t[rank * n:(rank + 1) * n]
+    from .weights import _rows as rows          # FP8 checkpoint pairs are sliced with their block scales
+    return rows(t, rank, size)
 
 
 def _cols(t, rank, size):
-    n = (t.shape[1] + size - 1) // size
-    return t[:, rank * n:(rank + 1) * n]
+    from .weights import _cols as cols
+    return cols(t, rank, size)
 
 
 def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dtype, quant, ep_rank=0, ep_size=1):
     """Expert parallelism (``ep_size`` > 1, over the tensor-parallel group whose ranks all hold every token):
     each rank keeps whole experts ``[lo, hi)`` (no intermediate-dimension slicing) and computes only their
     contributions; the block's all-reduce is the combine. The shared expert stays tensor-parallel."""
-    from .weights import RandomSource, _make_linear
+    from .weights import Fp8Pair, RandomSource, _cat0, _dense, _make_linear
     sh_rank, sh_size = tp_rank, tp_size
     if ep_size > 1:
         tp_rank, tp_size = 0, 1
@@ -94,7 +94,7 @@ def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dt
         ep = f"{prefix}mlp.experts.{e}."
         if fused:
             g, u = gu_all[e, :I_full], gu_all[e, I_full:]
-            g_u = torch.cat([_rows(g, tp_rank, tp_size), _rows(u, tp_rank, tp_size)], 0)
+            g_u = _cat0([_rows(g, tp_rank, tp_size), _rows(u, tp_rank, tp_size)])
             d = _cols(d_all[e], tp_rank, tp_size)
         elif rnd and source.on_device:
             g_u = source.get(ep + f"gate_up_proj.weight.tp{tp_rank}", (2 * I, H), device=device)
@@ -102,19 +102,24 @@ def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dt
         else:
             g = _rows(source.get(ep + "gate_proj.weight", (I_full, H), device=device), tp_rank, tp_size)
             u = _rows(source.get(ep + "up_proj.weight", (I_full, H), device=device), tp_rank, tp_size)
-            g_u = torch.cat([g, u], 0)
+            g_u = _cat0([g, u])
             d = _cols(source.get(ep + "down_proj.weight", (H, I_full), device=device), tp_rank, tp_size)
         w13_parts.append(g_u.to(device))
         w2_parts.append(d.to(device))
     n_local = hi - lo
-    w13 = torch.cat(w13_parts, 0)
-    w2 = torch.cat(w2_parts, 0)
+    w13 = _cat0(w13_parts)
+    w2 = _cat0(w2_parts)
     w13_s = w2_s = None
-    if quant in ("fp8_block", "nvfp4") and H % 128 == 0 and I % 128 == 0:     # grouped experts: FP8 blocks
+    if isinstance(w13, Fp8Pair) and isinstance(w2, Fp8Pair) and quant in (None, "fp8_block") and H % 128 == 0 and I % 128 == 0:
+        # an FP8 checkpoint's expert stacks: its own values and block scales, bit for bit
+        w13, w13_s = w13.q.contiguous(), w13.s.float().contiguous()
+        w2, w2_s = w2.q.contiguous(), w2.s.float().contiguous()
+    elif quant in ("fp8_block", "nvfp4") and H % 128 == 0 and I % 128 == 0:     # grouped experts: FP8 blocks
+        w13, w2 = _dense(w13), _dense(w2)
         w13, w13_s = ref.quant_weight_fp8_block(w13)
         w2, w2_s = ref.quant_weight_fp8_block(w2)
     else:
-        w13, w2 = w13.to(dtype).contiguous(), w2.to(dtype).contiguous()
+        w13, w2 = _dense(w13).to(dtype).contiguous(), _dense(w2).to(dtype).contiguous()
     mw = MoEWeights(router, rbias, w13, w13_s, w2, w2_s, E, I, H, expert_lo=lo, expert_hi=hi)
     sI_full = cfg.shared_expert_intermediate_size
     if sI_full:
@@ -122,7 +127,7 @@ def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dt
         g = _rows(source.get(sp + "gate_proj.weight", (sI_full, H), device=device), sh_rank, sh_size)
         u = _rows(source.get(sp + "up_proj.weight", (sI_full, H), device=device), sh_rank, sh_size)
         d = _cols(source.get(sp + "down_proj.weight", (H, sI_full), device=device), sh_rank, sh_size)
-        mw.shared_gate_up = _make_linear(torch.cat([g, u], 0), None, device, dtype, quant)
+        mw.shared_gate_up = _make_linear(_cat0([g, u]), None, device, dtype, quant)
         mw.shared_down = _make_linear(d, None, device, dtype, quant)
         if cfg.shared_expert_gate:
             mw.shared_gate = source.get(prefix + "mlp.shared_expert_gate.weight", (1, H), device=device).to(device=device, dtype=dtype)

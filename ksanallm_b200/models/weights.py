@@ -74,6 +74,96 @@ def apply_weight_map(name: str, rules: List[tuple]) -> str:
     return name
 
 
+# ------------------------------------------------------------------------------------- FP8 checkpoints
+class Fp8Pair:
+    """A projection weight as an FP8 checkpoint stores it: e4m3 values [N, K] and one fp32 scale per 128 x 128
+    block [ceil(N/128), ceil(K/128)] (DeepSeek-V3 style ``weight_scale_inv``; a per-tensor ``weight_scale`` is
+    spread over the blocks). Slicing for tensor parallelism and packing (QKV, gate|up, expert stacks) act on values
+    and scales together as long as the cuts fall on block boundaries, so the checkpoint's own quantisation reaches
+    the GEMMs unchanged (src/ksana_llm/models/quant/quant_weight.cpp:729-896 binds checkpoint scales per layer);
+    a cut inside a block falls back to the dense fp32 values."""
+    BLOCK = 128
+
+    def __init__(self, q: torch.Tensor, s: torch.Tensor):
+        self.q, self.s = q, s
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def to(self, device=None, dtype=None, **kw):
+        return Fp8Pair(self.q.to(device), self.s.to(device)) if device is not None else self
+
+    def dense(self, dtype=torch.float32) -> torch.Tensor:
+        N, K = self.q.shape
+        full = self.s.float().repeat_interleave(self.BLOCK, 0)[:N].repeat_interleave(self.BLOCK, 1)[:, :K]
+        return (self.q.float() * full.to(self.q.device)).to(dtype)
+
+    def rows(self, lo: int, hi: int):
+        hi = min(hi, self.q.shape[0])
+        if lo % self.BLOCK or (hi % self.BLOCK and hi != self.q.shape[0]):
+            return self.dense()[lo:hi]
+        return Fp8Pair(self.q[lo:hi], self.s[lo // self.BLOCK:(hi + self.BLOCK - 1) // self.BLOCK])
+
+    def cols(self, lo: int, hi: int):
+        hi = min(hi, self.q.shape[1])
+        if lo % self.BLOCK or (hi % self.BLOCK and hi != self.q.shape[1]):
+            return self.dense()[:, lo:hi]
+        return Fp8Pair(self.q[:, lo:hi], self.s[:, lo // self.BLOCK:(hi + self.BLOCK - 1) // self.BLOCK])
+
+    def split(self, sizes, dim=0):
+        assert dim == 0
+        out, lo = [], 0
+        for n in sizes:
+            out.append(self.rows(lo, lo + n))
+            lo += n
+        return out
+
+    def chunk(self, n, dim=0):
+        assert dim == 0
+        step = (self.q.shape[0] + n - 1) // n
+        return self.split([min(step, self.q.shape[0] - i * step) for i in range(n)], 0)
+
+
+def _dense(t, dtype=None):
+    """Plain tensor of a weight (FP8 pairs are expanded exactly)."""
+    if isinstance(t, Fp8Pair):
+        return t.dense(dtype or torch.float32)
+    return t
+
+
+def _cat0(parts):
+    """Row-wise concatenation of weights; FP8 pairs stay pairs when every part but the last ends on a block row."""
+    if any(isinstance(p, Fp8Pair) for p in parts):
+        if all(isinstance(p, Fp8Pair) for p in parts) and all(p.q.shape[0] % Fp8Pair.BLOCK == 0 for p in parts[:-1]):
+            return Fp8Pair(torch.cat([p.q for p in parts], 0), torch.cat([p.s for p in parts], 0))
+        return torch.cat([_dense(p) for p in parts], 0)
+    return torch.cat(parts, 0)
+
+
+class _Fp8Mixin:
+    """``<layer>.weight`` stored as float8_e4m3fn with ``<layer>.weight_scale_inv`` (block scales) or a scalar
+    ``<layer>.weight_scale`` is served as an Fp8Pair."""
+
+    def _fp8_pair(self, name: str, t: torch.Tensor):
+        if t.dtype != torch.float8_e4m3fn or t.dim() != 2 or not name.endswith(".weight"):
+            return t
+        nb, kb = (t.shape[0] + 127) // 128, (t.shape[1] + 127) // 128
+        if self._has_raw(name + "_scale_inv"):
+            s = self._get_raw(name + "_scale_inv").float()
+            if tuple(s.shape) == (nb, kb):
+                return Fp8Pair(t, s)
+            return t.float() * s if s.numel() == 1 else t.float()
+        if self._has_raw(name + "_scale"):
+            s = self._get_raw(name + "_scale").float()
+            if s.numel() == 1:
+                return Fp8Pair(t, s.reshape(1, 1).expand(nb, kb).contiguous())
+            if s.numel() == t.shape[0]:                       # one scale per output channel: no block form
+                return t.float() * s.reshape(-1, 1)
+        return t.float()
+
+
+
 class _PackedW4Mixin:
     """``<layer>.weight`` of a GPTQ / AWQ layer (stored as qweight / qzeros / scales [/ g_idx]) is served as its exact
     dense expansion; see models/quant_w4.py."""
@@ -92,7 +182,7 @@ class _PackedW4Mixin:
                            g_idx)
 
 
-class CheckpointSource(_PackedW4Mixin):
+class CheckpointSource(_PackedW4Mixin, _Fp8Mixin):
     """Tensors of a Hugging Face checkpoint directory (``*.safetensors`` preferred, then ``*.bin`` /
     ``*.pt``), renamed to canonical names through the optional regex weight map."""
 
@@ -139,7 +229,7 @@ class CheckpointSource(_PackedW4Mixin):
             base = self._packed(name)
             if base is not None:
                 return self._dense_from_packed(base)
-        return self._get_raw(name)
+        return self._fp8_pair(name, self._get_raw(name))
 
     def _get_raw(self, name: str) -> torch.Tensor:
         kind_, f, k, transpose = self.index[name]
@@ -152,7 +242,7 @@ class CheckpointSource(_PackedW4Mixin):
         return t.t().contiguous() if transpose else t
 
 
-class DictSource(_PackedW4Mixin):
+class DictSource(_PackedW4Mixin, _Fp8Mixin):
     def __init__(self, tensors: Dict[str, torch.Tensor], model_type: str = "llama"):
         rules = load_weight_map(model_type)
         self.t = {}
@@ -179,23 +269,32 @@ class DictSource(_PackedW4Mixin):
             base = self._packed(name)
             if base is not None:
                 return self._dense_from_packed(base)
-        return self.t[name]
+        return self._fp8_pair(name, self.t[name])
 
 
 # ------------------------------------------------------------------------------------- loader
-def _rows(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+def _rows(t, rank: int, size: int):
     n = (t.shape[0] + size - 1) // size
+    if isinstance(t, Fp8Pair):
+        return t.rows(rank * n, (rank + 1) * n)
     return t[rank * n:(rank + 1) * n]
 
 
-def _cols(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+def _cols(t, rank: int, size: int):
     n = (t.shape[1] + size - 1) // size
+    if isinstance(t, Fp8Pair):
+        return t.cols(rank * n, (rank + 1) * n)
     return t[:, rank * n:(rank + 1) * n]
 
 
-def _make_linear(w: torch.Tensor, bias, device, dtype, quant: Optional[str]) -> LinearWeight:
-    w = w.to(device)
+def _make_linear(w, bias, device, dtype, quant: Optional[str]) -> LinearWeight:
     b = bias.to(device=device, dtype=dtype) if bias is not None else None
+    if isinstance(w, Fp8Pair):
+        if (quant is None or quant == "fp8_block") and w.shape[1] % 128 == 0:
+            # the checkpoint's own FP8 values and block scales, bit for bit
+            return LinearWeight(bias=b, wq=w.q.to(device).contiguous(), ws=w.s.float().to(device).contiguous())
+        w = w.dense()
+    w = w.to(device)
     if quant and quant.startswith("w4a16") and w.shape[1] % 32 == 0:
         group = int(quant.split(":")[1]) if ":" in quant else 128
         while w.shape[1] % group:
@@ -261,7 +360,7 @@ def build_model(cfg: ModelConfig, source, tp_rank: int = 0, tp_size: int = 1, co
                 k_b = get(p + "self_attn.k_proj.bias", (Hkv_all * D,)) if has_b else None
                 v_b = get(p + "self_attn.v_proj.bias", (Hkv_all * D,)) if has_b else None
             kv_rank, kv_size = (tp_rank // kv_rep, tp_size // kv_rep) if tp_size > 1 else (0, 1)
-            qkv_w = torch.cat([_rows(q_w, tp_rank, tp_size), _rows(k_w, kv_rank, kv_size), _rows(v_w, kv_rank, kv_size)], 0)
+            qkv_w = _cat0([_rows(q_w, tp_rank, tp_size), _rows(k_w, kv_rank, kv_size), _rows(v_w, kv_rank, kv_size)])
             qkv_b = None
             if q_b is not None:
                 qkv_b = torch.cat([_rows(q_b, tp_rank, tp_size), _rows(k_b, kv_rank, kv_size), _rows(v_b, kv_rank, kv_size)], 0)
@@ -298,7 +397,7 @@ def build_model(cfg: ModelConfig, source, tp_rank: int = 0, tp_size: int = 1, co
                     else:
                         g_w = get(p + "mlp.gate_proj.weight", (inter, H))
                         u_w = get(p + "mlp.up_proj.weight", (inter, H))
-                    gu_w = torch.cat([_rows(g_w, tp_rank, tp_size), _rows(u_w, tp_rank, tp_size)], 0)
+                    gu_w = _cat0([_rows(g_w, tp_rank, tp_size), _rows(u_w, tp_rank, tp_size)])
                 else:
                     gu_w = _rows(get(p + "mlp.up_proj.weight", (inter, H)), tp_rank, tp_size)
                 d_w = _cols(get(p + "mlp.down_proj.weight", (H, inter)), tp_rank, tp_size)
