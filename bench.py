@@ -26,10 +26,10 @@ import time
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 # Output tok/s of the library-only measuring stick (``--impl baseline``: per-tensor FP8 cuBLASLt GEMMs, SDPA, NCCL,
-# unfused ops) on the same batch, by GPU count; the numbers BASELINE.md lists. ``vs_baseline`` divides by them.
+# unfused ops) on the same batch, by GPU count, measured on one B200. ``vs_baseline`` divides by them.
 BASELINE_TOK_S = {1: 576.2}
 
-REFERENCE_UNAVAILABLE = ("refused by a safety check: installing the reference (pip install of /root/reference, which "
+REFERENCE_UNAVAILABLE = ("refused by a safety check: installing the reference (a pip install of its source tree, which "
                          "runs its setup.py / CMake build) was denied in this environment, so baseline/_ref does not exist")
 
 
