@@ -25,8 +25,9 @@ static int g_failures = 0;
     if (!(cond)) { std::fprintf(stderr, "FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond); ++g_failures; } \
   } while (0)
 
-static void SchedulerStress(int preempt_mode) {
+static void SchedulerStress(int preempt_mode, int dp_size = 1) {
   SchedulerConfig cfg;
+  cfg.dp_size = dp_size;                  // > 1: one block pool per data-parallel rank
   cfg.max_batch_size = 16;
   cfg.max_step_tokens = 256;
   cfg.max_token_len = 224;
@@ -142,6 +143,8 @@ static void ControlPlaneStress() {
 int main() {
   SchedulerStress(0);
   SchedulerStress(1);
+  SchedulerStress(0, 3);
+  SchedulerStress(1, 2);
   ControlPlaneStress();
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);
