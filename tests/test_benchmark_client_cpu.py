@@ -102,3 +102,21 @@ def test_client_text_prompts_chat_template_stop_strings_and_regex(server, tmp_pa
     body = bt.build_payload(args, wrapped)
     assert body["structured_output_regex"] == "[a-c]{3}" and body["sampling_config"]["stop_strings"] == ["zzzz"]
     assert res[0]["finished"] == 3 and res[0]["failed"] == 0
+
+
+@pytest.mark.parametrize("config,extra", [("b", ["--requests", "8", "--input-len", "24", "--output-len", "6"]),
+                                          ("d", ["--requests", "5", "--output-len", "4"]),
+                                          ("e", ["--requests", "6", "--input-len", "40", "--output-len", "8"])])
+def test_offline_configurations_toy_mode(config, extra):
+    """The offline configuration script end to end on the CPU (toy-sized models of the named architectures): every
+    request finishes, the shared-prefix load hits the prefix cache."""
+    import json
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "benchmarks", "offline_configs.py"), "--config", config] + extra,
+                       capture_output=True, text=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    res = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+    assert res["config"] == config and res["finished_ok"] == res["requests"] and res["output_tokens"] > 0
+    if config == "d":
+        assert res["prefix_hit_tokens"] > 0
