@@ -360,3 +360,12 @@ def test_example_configurations_load():
     assert seen["ksana_llm_pipeline.yaml"].global_.pipeline_para_size == 2
     assert seen["ksana_llm_deepseek_v3_ep8.yaml"].global_.attn_data_para_size == 8
     assert seen["ksana_llm_deepseek_v3_ep8.yaml"].global_.expert_para_size == 8
+
+
+def test_import_compatibility_package():
+    """`import ksana_llm` exposes the serving surface of the reference's Python package."""
+    import ksana_llm
+    from ksanallm_b200.serving.auto_model import AutoModel
+    assert ksana_llm.AutoModel is AutoModel
+    assert {"AutoModel", "EndpointConfig", "PluginConfig"} <= set(ksana_llm.__all__)
+    assert ksana_llm.EndpointConfig().type in ("python", "PYTHON", "python ") or hasattr(ksana_llm.EndpointConfig(), "type")
