@@ -120,3 +120,25 @@ def test_offline_configurations_toy_mode(config, extra):
     assert res["config"] == config and res["finished_ok"] == res["requests"] and res["output_tokens"] > 0
     if config == "d":
         assert res["prefix_hit_tokens"] > 0
+
+
+def test_command_line_clients_against_live_server(server, capsys):
+    """serving_generate_client.py and serving_forward_client.py (the reference's client script names) against the
+    live server: blocking and streaming generation, a logits target with perplexity, a hidden-state target."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    import serving_forward_client
+    import serving_generate_client
+    res = serving_generate_client.main(["--port", str(server), "--host", "127.0.0.1", "--prompt", "hello", "--max_new_tokens", "5"])
+    assert len(res["output_token_ids"][0]) == 5
+    res = serving_generate_client.main(["--port", str(server), "--host", "127.0.0.1", "--input_tokens", "5", "6", "7",
+                                        "--max_new_tokens", "4", "--stream"])
+    assert res["chunks"] and len(res["chunks"][-1]["output_token_ids"][0]) == 4
+    doc = serving_forward_client.main(["--port", str(server), "--host", "127.0.0.1", "--input_tokens", "5", "6", "7", "8", "9",
+                                       "--target", "logits", "--reduce", "GATHER_TOKEN_ID", "--slice", "0", "3"])
+    t = doc["responses"][0]["response"][0]
+    assert t["target_name"] == "logits" and t["tensor"].shape[0] == 4
+    doc = serving_forward_client.main(["--port", str(server), "--host", "127.0.0.1", "--prompt", "abcdef", "--target", "layernorm",
+                                       "--slice", "0", "1"])
+    assert doc["responses"][0]["response"][0]["tensor"].shape[0] == 2
+    assert "perplexity" in capsys.readouterr().out
