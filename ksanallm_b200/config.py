@@ -406,7 +406,7 @@ def model_config_from_hf(hf: dict, generation: Optional[dict] = None) -> ModelCo
         if c.quant_method == "fp8":
             c.fp8_checkpoint = True
             c.weight_block_size = q.get("weight_block_size")
-    td = hf.get("torch_dtype", "bfloat16")
+    td = hf.get("torch_dtype") or hf.get("dtype") or "bfloat16"          # newer exports write "dtype"
     c.dtype = {"float16": "float16", "bfloat16": "bfloat16", "float32": "float32"}.get(str(td).replace("torch.", ""), "bfloat16")
     eos = (generation or {}).get("eos_token_id", hf.get("eos_token_id"))
     if eos is not None:

@@ -98,7 +98,7 @@ def auto_host_blocks(cfg: EngineConfig, num_device_blocks: int, block_bytes: int
 class LLM:
     def __init__(self, engine_cfg: Optional[EngineConfig] = None, model_cfg: Optional[ModelConfig] = None,
                  config_file: Optional[str] = None, weights="checkpoint", device: Optional[str] = None,
-                 dtype=torch.bfloat16, tokenizer=None, seed: int = 0, max_positions: Optional[int] = None):
+                 dtype=None, tokenizer=None, seed: int = 0, max_positions: Optional[int] = None):
         if config_file is not None:
             engine_cfg = load_yaml_config(config_file)
         self.engine_cfg = engine_cfg or EngineConfig()
@@ -110,6 +110,10 @@ class LLM:
         self.rank, self.world, dev_group, ctl_group, world_group = init_distributed(dev_type, pp)
         local = _dist_env()[2]
         self.device = torch.device("cuda", local) if dev_type == "cuda" else torch.device("cpu")
+        if dtype is None:
+            # the kernels compute in bf16 (fp16 checkpoints are converted on load); on the CPU path a float32 checkpoint
+            # keeps its precision
+            dtype = torch.float32 if (dev_type == "cpu" and getattr(model_cfg, "dtype", "") == "float32") else torch.bfloat16
         if dev_type == "cuda":
             torch.cuda.set_device(self.device)
         tp = self.world // pp

@@ -1,0 +1,137 @@
+"""Stand-alone server process end to end (the shape of the reference's tests/integration_test.py): a tiny Hugging
+Face Llama checkpoint and tokenizer are written to disk, ``python serving_server.py --config_file X.yaml --port P`` is
+started as a child process, and the answers of /generate (blocking and streaming) are compared token by token with
+Hugging Face's own greedy generation from the same files."""
+import json
+import os
+import signal
+import socket
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+tokenizers = pytest.importorskip("tokenizers")
+requests = pytest.importorskip("requests")
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _write_model(path: str):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import LlamaConfig, LlamaForCausalLM, PreTrainedTokenizerFast
+    words = ["<unk>", "<s>", "</s>"] + [f"w{i}" for i in range(60)] + ["the", "cat", "sat", "on", "mat", "hello", "world"]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", bos_token="<s>", eos_token="</s>")
+    fast.save_pretrained(path)
+    cfg = LlamaConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                      vocab_size=len(words), max_position_embeddings=128, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                      bos_token_id=1, eos_token_id=2, torch_dtype="float32")
+    torch.manual_seed(3)
+    model = LlamaForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() > 1:
+                p.normal_(0.0, 0.3)
+    model.save_pretrained(path, safe_serialization=True)
+    return model, fast
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.fixture(scope="module")
+def served(tmp_path_factory):
+    d = tmp_path_factory.mktemp("served")
+    model_dir = str(d / "model")
+    os.makedirs(model_dir)
+    model, tok = _write_model(model_dir)
+    yaml_path = str(d / "ksana_llm.yaml")
+    with open(yaml_path, "w", encoding="utf-8") as f:
+        f.write(f"""setting:
+  global:
+    tensor_para_size: 1
+    enable_cuda_graph: false
+  batch_scheduler:
+    max_batch_size: 8
+    max_token_len: 96
+    max_step_tokens: 256
+    enable_auto_prefix_cache: true
+  block_manager:
+    block_token_num: 16
+    device_blocks_num: 64
+  endpoint_type: python
+model_spec:
+  base_model:
+    model_dir: {model_dir}
+""")
+    port = _free_port()
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", PYTHONPATH=ROOT)
+    proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "serving_server.py"), "--config_file", yaml_path, "--host",
+                             "127.0.0.1", "--port", str(port)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env,
+                            start_new_session=True)
+    deadline = time.time() + 120
+    up = False
+    while time.time() < deadline and proc.poll() is None:
+        try:
+            if requests.get(f"http://127.0.0.1:{port}/health", timeout=1).status_code == 200:
+                up = True
+                break
+        except Exception:
+            time.sleep(0.5)
+    if not up:
+        out = proc.stdout.read().decode(errors="replace")[-3000:] if proc.poll() is not None else ""
+        try:
+            os.killpg(proc.pid, signal.SIGKILL)
+        except ProcessLookupError:
+            pass
+        pytest.fail("server did not come up: " + out)
+    yield f"http://127.0.0.1:{port}", model, tok
+    try:
+        os.killpg(proc.pid, signal.SIGTERM)
+        proc.wait(timeout=20)
+    except Exception:
+        try:
+            os.killpg(proc.pid, signal.SIGKILL)
+        except ProcessLookupError:
+            pass
+
+
+def _hf_greedy(model, tok, prompt, n):
+    ids = tok(prompt, return_tensors="pt").input_ids
+    with torch.no_grad():
+        out = model.generate(ids, max_new_tokens=n, do_sample=False, eos_token_id=None, pad_token_id=0)
+    return ids[0].tolist(), out[0, ids.shape[1]:].tolist()
+
+
+def test_generate_matches_hugging_face_greedy(served):
+    url, model, tok = served
+    for prompt in ("the cat sat on the mat", "hello world w1 w2 w3 w4 w5"):
+        ids, want = _hf_greedy(model, tok, prompt, 12)
+        r = requests.post(url + "/generate", json={"prompt": prompt, "stream": False,
+                                                   "sampling_config": {"max_new_tokens": 12, "topk": 1, "ignore_eos": True}})
+        assert r.status_code == 200, r.text
+        body = r.json()
+        assert body["input_token_ids"] == ids
+        assert body["output_token_ids"][0] == want
+        assert body["texts"][0].split() == tok.decode(want).split()
+
+
+def test_streaming_and_token_input(served):
+    url, model, tok = served
+    ids, want = _hf_greedy(model, tok, "w7 w8 w9 the cat", 8)
+    r = requests.post(url + "/generate", json={"input_tokens": ids, "stream": True,
+                                               "sampling_config": {"max_new_tokens": 8, "topk": 1, "ignore_eos": True}}, stream=True)
+    chunks = [json.loads(c) for c in r.content.split(b"\0") if c]
+    assert chunks and chunks[-1]["output_token_ids"][0] == want
+    lens = [len(c["output_token_ids"][0]) for c in chunks]
+    assert lens == sorted(lens) and lens[-1] == 8
+    m = requests.get(url + "/metrics").text
+    assert "forward_req_total_num" in m or "metric_" in m
