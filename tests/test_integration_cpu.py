@@ -1,7 +1,8 @@
 """Stand-alone server process end to end (the shape of the reference's tests/integration_test.py): a tiny Hugging
 Face Llama checkpoint and tokenizer are written to disk, ``python serving_server.py --config_file X.yaml --port P`` is
-started as a child process, and the answers of /generate (blocking and streaming) are compared token by token with
-Hugging Face's own greedy generation from the same files."""
+started as a child process - alone, and as two tensor-parallel ranks under torchrun (rank 0 serves, rank 1 follows the
+broadcast step plans) - and the answers of /generate (blocking and streaming) are compared token by token with Hugging
+Face's own greedy generation from the same files."""
 import json
 import os
 import signal
@@ -47,8 +48,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.fixture(scope="module")
-def served(tmp_path_factory):
+@pytest.fixture(scope="module", params=[1, 2], ids=["one-process", "two-tensor-parallel-ranks"])
+def served(request, tmp_path_factory):
+    nproc = request.param
     d = tmp_path_factory.mktemp("served")
     model_dir = str(d / "model")
     os.makedirs(model_dir)
@@ -57,8 +59,9 @@ def served(tmp_path_factory):
     with open(yaml_path, "w", encoding="utf-8") as f:
         f.write(f"""setting:
   global:
-    tensor_para_size: 1
+    tensor_para_size: {nproc}
     enable_cuda_graph: false
+    comm_backend: nccl
   batch_scheduler:
     max_batch_size: 8
     max_token_len: 96
@@ -74,9 +77,12 @@ model_spec:
 """)
     port = _free_port()
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", PYTHONPATH=ROOT)
-    proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "serving_server.py"), "--config_file", yaml_path, "--host",
-                             "127.0.0.1", "--port", str(port)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env,
-                            start_new_session=True)
+    launcher = [sys.executable] if nproc == 1 else [
+        sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+        "--master-port", str(_free_port())]
+    proc = subprocess.Popen(launcher + [os.path.join(ROOT, "serving_server.py"), "--config_file", yaml_path, "--host",
+                                        "127.0.0.1", "--port", str(port)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                            env=env, start_new_session=True)
     deadline = time.time() + 120
     up = False
     while time.time() < deadline and proc.poll() is None:
