@@ -298,3 +298,40 @@ def test_llama_rope_scaling_variants(scaling):
                     vocab_size=200, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0,
                     rope_scaling=dict(scaling), tie_word_embeddings=False)
     _check(_init(LlamaForCausalLM(c)), c.to_dict())
+
+
+@pytest.mark.parametrize("layout", ["sharded-safetensors", "pytorch-bin"])
+def test_checkpoint_directories_on_disk(tmp_path, layout):
+    """A checkpoint directory as users have it (config.json + sharded safetensors with an index, or a pickled
+    pytorch_model.bin; tied embeddings) loads through CheckpointSource and reproduces Hugging Face's logits."""
+    import os
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    from ksanallm_b200.config import load_model_config
+    from ksanallm_b200.models.weights import CheckpointSource
+    c = Qwen2Config(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                    vocab_size=200, max_position_embeddings=128, rms_norm_eps=1e-6, tie_word_embeddings=True, dtype="float32")
+    hf = _init(Qwen2ForCausalLM(c)).eval()
+    hf.tie_weights()
+    d = str(tmp_path)
+    if layout == "sharded-safetensors":
+        hf.save_pretrained(d, safe_serialization=True, max_shard_size="60KB")
+        assert len([f for f in os.listdir(d) if f.endswith(".safetensors")]) > 1
+    else:
+        hf.config.save_pretrained(d)
+        torch.save(dict(hf.state_dict()), os.path.join(d, "pytorch_model.bin"))
+    mc = load_model_config(d)
+    assert mc.tie_word_embeddings and mc.qkv_bias and mc.dtype == "float32"
+    mc.max_token_len = 128
+    model = build_model(mc, CheckpointSource(d, mc.model_type), device="cpu", dtype=torch.float32)
+    torch.manual_seed(0)
+    tokens = torch.randint(3, 200, (19,)).tolist()
+    T = len(tokens)
+    model.allocate_kv_cache(8, 16)
+    ar = torch.arange(T, dtype=torch.int32)
+    step = StepInput(torch.tensor(tokens, dtype=torch.int32), ar, ar.clone(), torch.tensor([0, T], dtype=torch.int32),
+                     torch.tensor([T], dtype=torch.int32), torch.arange(8, dtype=torch.int32).view(1, 8),
+                     num_multi=1, num_single=0, num_tokens=T, num_multi_tokens=T, max_q_len=T, max_kv_len=T)
+    with torch.no_grad():
+        want = hf(torch.tensor([tokens])).logits[0].float()
+    got = model.forward(step)
+    assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
