@@ -117,7 +117,12 @@ def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExec
     def render_messages(messages) -> Optional[List[int]]:
         if tokenizer is None or not hasattr(tokenizer, "apply_chat_template"):
             return None
-        return tokenizer.apply_chat_template(messages, tokenize=True, add_generation_prompt=True)
+        ids = tokenizer.apply_chat_template(messages, tokenize=True, add_generation_prompt=True)
+        if hasattr(ids, "keys"):                       # newer tokenizers return an encoding object, not a list
+            ids = ids["input_ids"]
+        if len(ids) and isinstance(ids[0], (list, tuple)):
+            ids = ids[0]
+        return [int(t) for t in ids]
 
     async def process_request(request_dict: Dict[str, Any], req_ctx: Dict[str, str]):
         model_name = request_dict.pop("model_name", "")

@@ -28,6 +28,8 @@ def _write_model(path: str):
     tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
     tok.pre_tokenizer = pre_tokenizers.Whitespace()
     fast = PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", bos_token="<s>", eos_token="</s>")
+    fast.chat_template = ("{% for m in messages %}{{ 'w1 ' if m['role'] == 'user' else 'w2 ' }}{{ m['content'] }} {% endfor %}"
+                          "{% if add_generation_prompt %}w3{% endif %}")
     fast.save_pretrained(path)
     cfg = LlamaConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
                       vocab_size=len(words), max_position_embeddings=128, rms_norm_eps=1e-5, tie_word_embeddings=False,
@@ -141,3 +143,29 @@ def test_streaming_and_token_input(served):
     assert lens == sorted(lens) and lens[-1] == 8
     m = requests.get(url + "/metrics").text
     assert "forward_req_total_num" in m or "metric_" in m
+
+
+def test_chat_messages_and_stop_strings(served):
+    """OpenAI-style messages go through the tokenizer's chat template on the server; a stop string cuts the answer
+    where Hugging Face's text has it."""
+    url, model, tok = served
+    messages = [{"role": "user", "content": "the cat sat"}, {"role": "assistant", "content": "on the mat"},
+                {"role": "user", "content": "hello world"}]
+    ids = tok.apply_chat_template(messages, tokenize=True, add_generation_prompt=True)
+    ids = list(ids["input_ids"]) if hasattr(ids, "keys") else list(ids)
+    with torch.no_grad():
+        out = model.generate(torch.tensor([ids]), max_new_tokens=10, do_sample=False, eos_token_id=None, pad_token_id=0)
+    want = out[0, len(ids):].tolist()
+    r = requests.post(url + "/generate", json={"messages": messages, "stream": False,
+                                               "sampling_config": {"max_new_tokens": 10, "topk": 1, "ignore_eos": True}})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    assert body["input_token_ids"] == ids and body["output_token_ids"][0] == want
+    words = tok.decode(want, skip_special_tokens=True).split()      # the server's text leaves special tokens out
+    stop = words[4]
+    cut = words.index(stop)
+    r = requests.post(url + "/generate", json={"messages": messages, "stream": False,
+                                               "sampling_config": {"max_new_tokens": 10, "topk": 1, "ignore_eos": True,
+                                                                   "stop_strings": [stop]}})
+    got = r.json()["output_token_ids"][0]
+    assert tok.decode(got, skip_special_tokens=True).split() == words[:cut]
