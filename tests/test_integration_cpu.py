@@ -169,3 +169,25 @@ def test_chat_messages_and_stop_strings(served):
                                                                    "stop_strings": [stop]}})
     got = r.json()["output_token_ids"][0]
     assert tok.decode(got, skip_special_tokens=True).split() == words[:cut]
+
+
+def test_parallel_sampling_beams_and_logprobs(served):
+    url, model, tok = served
+    prompt = "the cat sat on"
+    r = requests.post(url + "/generate", json={"prompt": prompt, "stream": False,
+                                               "sampling_config": {"max_new_tokens": 6, "topk": 5, "temperature": 0.9,
+                                                                   "num_return_sequences": 3, "ignore_eos": True, "logprobs": 2}})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    assert len(body["output_token_ids"]) == 3 and all(len(o) == 6 for o in body["output_token_ids"])
+    assert len(body["logprobs"]) == 3 and all(len(lp) == 6 for lp in body["logprobs"])
+    # greedy first token must be among the top-2 log-probabilities reported for step 0
+    ids, want = _hf_greedy(model, tok, prompt, 1)
+    top_ids = {int(t) for t, _ in body["logprobs"][0][0]}
+    assert want[0] in top_ids
+    r = requests.post(url + "/generate", json={"prompt": prompt, "stream": False,
+                                               "sampling_config": {"max_new_tokens": 5, "num_beams": 3, "num_return_sequences": 2,
+                                                                   "logprobs": 3, "ignore_eos": True}})
+    assert r.status_code == 200, r.text
+    beams = r.json()["output_token_ids"]
+    assert len(beams) == 2 and all(len(b) == 5 for b in beams) and beams[0] != beams[1]
