@@ -11,6 +11,8 @@ the cumulative outputs after every step and aborts the request when it is droppe
 from __future__ import annotations
 
 import asyncio
+import logging
+import os
 import threading
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
@@ -24,6 +26,8 @@ from ..utils import native_engine as ne
 from .forward_api import verify_request_target
 from .plugin import KsanaPlugin, PluginConfig
 from .request_packer import pack_responses, unpack_requests
+
+logger = logging.getLogger(__name__)
 
 
 @dataclass
@@ -139,6 +143,17 @@ class ServingModel:
             self.endpoint_config = endpoint_config
         if self.llm is None:
             cfg = load_yaml_config(self._config_file)
+            if self.tokenizer is None:
+                # AutoModel.from_config(yaml) users pass no tokenizer: take the one beside the checkpoint (stop strings,
+                # structured output and text prompts of /forward need it)
+                tdir = getattr(cfg, "tokenizer_dir", "") or getattr(cfg, "model_dir", "")
+                if tdir and os.path.isdir(tdir) and any(os.path.exists(os.path.join(tdir, f)) for f in
+                                                        ("tokenizer.json", "tokenizer.model", "tokenizer_config.json", "vocab.json")):
+                    try:
+                        from transformers import AutoTokenizer
+                        self.tokenizer = AutoTokenizer.from_pretrained(tdir, trust_remote_code=True)
+                    except Exception as e:          # noqa: BLE001 - a broken tokenizer directory must not stop token-id serving
+                        logger.warning("tokenizer in %s could not be loaded: %s", tdir, e)
             self.llm = LLM(cfg, None, weights=weights, device=device, tokenizer=self.tokenizer)
             self.model_cfg = self.llm.model_cfg
         self.llm.engine.tokenizer = self.tokenizer

@@ -191,3 +191,34 @@ def test_parallel_sampling_beams_and_logprobs(served):
     assert r.status_code == 200, r.text
     beams = r.json()["output_token_ids"]
     assert len(beams) == 2 and all(len(b) == 5 for b in beams) and beams[0] != beams[1]
+
+
+def test_auto_model_from_config_loads_the_tokenizer_beside_the_checkpoint(tmp_path):
+    """`ksana_llm.AutoModel.from_config(yaml)` (the package API of the reference) without an explicit tokenizer: the one
+    in the model directory is used, so stop strings work on a model created that way."""
+    import ksana_llm
+    model_dir = str(tmp_path / "model")
+    os.makedirs(model_dir)
+    hf, tok = _write_model(model_dir)
+    yaml_path = str(tmp_path / "k.yaml")
+    with open(yaml_path, "w", encoding="utf-8") as f:
+        f.write(f"""setting:
+  global: {{tensor_para_size: 1, enable_cuda_graph: false}}
+  batch_scheduler: {{max_batch_size: 4, max_token_len: 96, max_step_tokens: 256}}
+  block_manager: {{block_token_num: 16, device_blocks_num: 32}}
+  endpoint_type: python
+model_spec:
+  base_model: {{model_dir: {model_dir}}}
+""")
+    sm = ksana_llm.AutoModel.from_config(yaml_path)
+    sm.init_serving(device="cpu")
+    try:
+        assert sm.tokenizer is not None and sm.llm.engine.tokenizer is sm.tokenizer
+        ids, want = _hf_greedy(hf, tok, "the cat sat on the mat", 8)
+        st, out = sm.generate(inputs=ids, generation_config={"max_new_tokens": 8, "ignore_eos": True})
+        assert st.OK() and out.output_tokens[0] == want
+        words = tok.decode(want, skip_special_tokens=True).split()
+        st, out = sm.generate(inputs=ids, generation_config={"max_new_tokens": 8, "ignore_eos": True, "stop_strings": [words[3]]})
+        assert st.OK() and tok.decode(out.output_tokens[0], skip_special_tokens=True).split() == words[:words.index(words[3])]
+    finally:
+        sm.shutdown()
