@@ -220,15 +220,15 @@ class LLM:
 
     def follow(self):
         """Worker ranks: execute broadcast step plans until the end-of-batch (empty image) or stop (None) signal."""
-        from .parallel.control import broadcast_plan
+        from .parallel.control import broadcast_plan, unpack_extras
         while True:
-            img = broadcast_plan(self.engine.control_group, None)
+            img, blob = broadcast_plan(self.engine.control_group, None, with_extras=True)
             if img is None:
                 return False
             if img.size == 0:
                 return True
             plan = ne.StepPlan.unpack(img)
-            self.engine.runner.execute(plan, None)
+            self.engine.run_with_extras(plan, unpack_extras(blob))
 
     def shutdown(self, stop_followers: bool = False):
         """Stops the engine loop. ``stop_followers`` additionally releases worker ranks blocked in ``follow``."""

@@ -464,9 +464,12 @@ class LLMEngine:
                 self.scheduler.replace_generated(seq_id, action.tokens)
 
     def _gather_extras(self, plan) -> Optional[dict]:
-        """Per-step optional inputs: plugin embeddings to splice in, multimodal rotary positions."""
+        """Per-step optional inputs, as host tensors: plugin embeddings to splice in, multimodal rotary positions,
+        and for /forward targets the flag that keeps the hidden states plus the row ranges [first row, rows] whose
+        logits are computed for every position after the forward (a collective under tensor parallelism, so the
+        worker ranks get the same list and run it too)."""
         extra = {}
-        refit_pos, refit_emb, want_hidden = [], [], False
+        refit_pos, refit_emb, want_hidden, full_logits = [], [], False, []
         mrope = None
         row0 = 0
         for k, sid in enumerate(plan.seq_ids.tolist()):
@@ -498,16 +501,32 @@ class LLMEngine:
                         mrope[:, row0 + s2 - start:row0 + ql] = torch.arange(s2, start + ql, dtype=torch.int32) + base
                 if req.request_target:
                     want_hidden = True
+                    if "logits" in req.request_target:
+                        full_logits.append([row0, ql])
             row0 += ql
-        dev = self.model.device
         if refit_pos:
-            extra["refit_positions"] = torch.tensor(refit_pos, dtype=torch.int32, device=dev)
-            extra["refit_embeddings"] = torch.stack(refit_emb).float().to(dev)
+            extra["refit_positions"] = torch.tensor(refit_pos, dtype=torch.int32)
+            extra["refit_embeddings"] = torch.stack(refit_emb).float().cpu()
         if mrope is not None:
-            extra["mrope_positions"] = mrope.to(dev)
+            extra["mrope_positions"] = mrope
         if want_hidden:
             extra["want_hidden"] = True
+        if full_logits:
+            extra["full_logits"] = full_logits
         return extra or None
+
+    def run_with_extras(self, plan, extra: Optional[dict]):
+        """The forward of one step with its optional inputs moved to the device; returns (logits, the all-position
+        logits of the ``full_logits`` row ranges in order). Every rank of the engine calls this with the same plan
+        and extras, so the collectives inside line up."""
+        step_extra = None
+        if extra:
+            dev = self.model.device
+            step_extra = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in extra.items() if k != "full_logits"}
+        logits = self.runner.execute(plan, step_extra or None)
+        full = [self.model.compute_logits(self.model.step_normed[r0:r0 + n])
+                for r0, n in (extra or {}).get("full_logits", [])]
+        return logits, full
 
     def step(self) -> bool:
         """Runs one engine step. Returns False when there was nothing to run."""
@@ -521,12 +540,12 @@ class LLMEngine:
         ne.trace_record("SchedBegin", "i", 0, float(plan.num_tokens))
         ne.report_metric("batch_scheduler_batch_size", float(len(plan.seq_ids)))
         ne.report_metric("token_num_in_batch", float(plan.num_tokens))
+        extra = self._gather_extras(plan)
         if self.world_size > 1:
-            self._broadcast_plan(plan)
+            self._broadcast_plan(plan, extra)
         phase = "Prefill" if plan.num_multi else "Decode"
         ne.trace_record(phase, "B", 0, float(plan.num_tokens))
-        extra = self._gather_extras(plan)
-        logits = self.runner.execute(plan, extra)
+        logits, self._step_full_logits = self.run_with_extras(plan, extra)
         self.last_logits = logits
         tokens, parents, lp_by_seq = self._sample(plan, logits)
         ne.trace_record(phase, "E", 0, float(plan.num_tokens))
@@ -558,12 +577,13 @@ class LLMEngine:
         extract_targets(self, plan, logits)
 
     def full_logits_for(self, req, row0: int, ql: int) -> torch.Tensor:
-        """Logits of every position of one sequence of the current step (perplexity-style targets)."""
-        return self.model.compute_logits(self.model.step_normed[row0:row0 + ql])
+        """Logits of every position of one sequence of the current step (perplexity-style targets): computed right
+        after the forward, in plan order, by ``run_with_extras``."""
+        return self._step_full_logits.pop(0)
 
-    def _broadcast_plan(self, plan):
-        from ..parallel.control import broadcast_plan
-        broadcast_plan(self.control_group, plan.pack())
+    def _broadcast_plan(self, plan, extra: Optional[dict] = None):
+        from ..parallel.control import broadcast_plan, pack_extras
+        broadcast_plan(self.control_group, plan.pack(), extras=pack_extras(extra))
 
     # ------------------------------------------------------------------ loop
     def start(self):

@@ -270,6 +270,10 @@ class ServingModel:
         except Exception as e:  # noqa: BLE001
             return Status(1, f"failed to parse request: {e}"), None
         engine = self.llm.engine
+        if getattr(engine.model, "dp", None) is not None:
+            # attention data parallelism spreads the rows of a step over the ranks; request targets address rows of
+            # the whole step, so they are served by tensor- or pipeline-parallel deployments only
+            return Status(1, "request targets are not supported with attention data parallelism"), None
         pending = []
         for r in reqs_in:
             code, msg = verify_request_target(r["request_target"], len(r["input_tokens"]))

@@ -202,3 +202,17 @@ def test_kv_scale_calibration_writes_the_reference_file_format(tmp_path):
     back = load_kv_scales(str(out), cfg.num_layers)
     assert [b[0] for b in back] == pytest.approx(scales) and all(b[0] == b[1] for b in back)
     llm.shutdown()
+
+
+def test_step_extras_survive_the_wire_format():
+    """The optional inputs of a step (spliced embeddings, multimodal positions, /forward flags and row ranges)
+    reach worker ranks as a byte image: tensors keep dtype and values, plain values stay plain."""
+    from ksanallm_b200.parallel.control import pack_extras, unpack_extras
+    assert pack_extras(None) is None and pack_extras({}) is None and unpack_extras(None) is None
+    extra = {"refit_positions": torch.tensor([3, 4], dtype=torch.int32), "refit_embeddings": torch.randn(2, 8),
+             "mrope_positions": torch.arange(12, dtype=torch.int32).view(3, 4), "want_hidden": True,
+             "full_logits": [[0, 5], [9, 2]]}
+    back = unpack_extras(pack_extras(extra))
+    assert set(back) == set(extra) and back["want_hidden"] is True and back["full_logits"] == [[0, 5], [9, 2]]
+    for k in ("refit_positions", "refit_embeddings", "mrope_positions"):
+        assert back[k].dtype == extra[k].dtype and torch.equal(back[k], extra[k])

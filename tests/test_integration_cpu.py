@@ -222,3 +222,21 @@ model_spec:
         assert st.OK() and tok.decode(out.output_tokens[0], skip_special_tokens=True).split() == words[:words.index(words[3])]
     finally:
         sm.shutdown()
+
+
+def test_forward_perplexity_matches_hugging_face(served):
+    """/forward with a logits GATHER_TOKEN_ID target returns the probabilities of the prompt's own next tokens; the
+    perplexity computed from them equals the one from Hugging Face's logits (the check of the reference's
+    src/ksana_llm/python/tests/test_models.py)."""
+    import math
+    from ksanallm_b200.serving import clients
+    url, model, tok = served
+    prompt = "the cat sat on the mat hello world w1 w2"
+    ids = tok(prompt).input_ids
+    doc = clients.forward(url, [{"prompt": prompt, "request_target": [{"target_name": "logits", "token_reduce_mode": "GATHER_TOKEN_ID",
+                                                                      "slice_pos": [[0, len(ids) - 2]]}]}])
+    got = clients.perplexity_from_forward(doc)[0]
+    with torch.no_grad():
+        logp = torch.log_softmax(model(torch.tensor([ids])).logits[0].float(), -1)
+    nll = -sum(float(logp[i, ids[i + 1]]) for i in range(len(ids) - 1)) / (len(ids) - 1)
+    assert math.isclose(got, math.exp(nll), rel_tol=2e-3)
