@@ -131,3 +131,39 @@ class PipelineRunner:
             logits = torch.empty(rows, model.cfg.vocab_size, dtype=torch.float32, device=dev)
             dist.recv(logits, src=self.logits_src, group=self.group)
         return logits
+
+    def collect_targets(self, full_ranges) -> list:
+        """Collective over the engine's ranks after a step that kept its hidden states (request targets). Only the
+        last stage has the final hidden states, the final norm and the lm_head, while rank 0 answers the requests:
+        the last stage computes the all-position logits of the row ranges ``full_ranges`` ([first row, rows] each)
+        and its tensor-parallel rank 0 sends hidden states, normed states and those logits to rank 0, which keeps
+        the states on its model object and returns the logits list (other ranks return [])."""
+        model = self.model
+        if self.pp_size == 1:
+            return [model.compute_logits(model.step_normed[r0:r0 + n]) for r0, n in full_ranges]
+        full = []
+        if self.last:
+            full = [model.compute_logits(model.step_normed[r0:r0 + n]).contiguous() for r0, n in full_ranges]
+            if self.tp_rank == 0:
+                shape = torch.tensor(list(model.step_hidden.shape), dtype=torch.int64, device=model.step_hidden.device)
+                dist.send(shape, dst=0, group=self.group)
+                for t in (model.step_hidden, model.step_normed):
+                    dist.send(t.contiguous(), dst=0, group=self.group)
+                for t in full:
+                    dist.send(t, dst=0, group=self.group)
+        if self.first and self.tp_rank == 0:
+            dev = model.device
+            shape = torch.zeros(2, dtype=torch.int64, device=dev)
+            dist.recv(shape, src=self.logits_src, group=self.group)
+            T, H = int(shape[0]), int(shape[1])
+            model.step_hidden = torch.empty(T, H, dtype=model.dtype, device=dev)
+            model.step_normed = torch.empty(T, H, dtype=model.dtype, device=dev)
+            dist.recv(model.step_hidden, src=self.logits_src, group=self.group)
+            dist.recv(model.step_normed, src=self.logits_src, group=self.group)
+            full = []
+            for _r0, n in full_ranges:
+                t = torch.empty(n, model.cfg.vocab_size, dtype=torch.float32, device=dev)
+                dist.recv(t, src=self.logits_src, group=self.group)
+                full.append(t)
+        return full
+

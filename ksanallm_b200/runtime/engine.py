@@ -524,8 +524,11 @@ class LLMEngine:
             dev = self.model.device
             step_extra = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in extra.items() if k != "full_logits"}
         logits = self.runner.execute(plan, step_extra or None)
-        full = [self.model.compute_logits(self.model.step_normed[r0:r0 + n])
-                for r0, n in (extra or {}).get("full_logits", [])]
+        ranges = (extra or {}).get("full_logits", [])
+        pipe = self.runner.pipeline
+        if pipe is not None and extra and extra.get("want_hidden"):
+            return logits, pipe.collect_targets(ranges)       # the states live on the last stage
+        full = [self.model.compute_logits(self.model.step_normed[r0:r0 + n]) for r0, n in ranges]
         return logits, full
 
     def step(self) -> bool:

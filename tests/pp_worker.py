@@ -29,6 +29,39 @@ def prompts_for(vocab):
     return [torch.randint(3, vocab, (n,), generator=g).tolist() for n in (70, 5, 33, 128)]
 
 
+TARGETS = {"transformer": {"slice_pos": [[0, 3]], "token_reduce_mode": "GATHER_ALL"},
+           "layernorm": {"slice_pos": [[2, 2]], "token_reduce_mode": "GATHER_ALL"},
+           "logits": {"slice_pos": [[0, 10]], "token_reduce_mode": "GATHER_TOKEN_ID"}}
+
+
+def refit_for(mc):
+    """Embeddings spliced over prompt positions 1..2 and 7 (what a vision plug-in hands to the engine)."""
+    g = torch.Generator().manual_seed(5)
+    return [1, 7], [torch.randn(2, mc.hidden_size, generator=g), torch.randn(mc.hidden_size, generator=g)]
+
+
+def run_targets(llm):
+    """Two prefill-only requests with request targets (hidden states, normed states, next-token probabilities) in one
+    batch, through the engine of every rank; rank 0 returns their responses."""
+    import copy
+    import numpy as np
+    from ksanallm_b200.parallel.control import broadcast_plan
+    if llm.rank != 0:
+        llm.follow()
+        return None
+    s = ne.SamplingConfig()
+    s.max_new_tokens = 1
+    prompts = prompts_for(llm.engine.model_cfg.vocab_size)[2:]
+    reqs = [llm.engine.add_request(p, s, request_target=copy.deepcopy(TARGETS)) for p in prompts]
+    reqs.append(llm.engine.add_request(prompts[0], s, request_target=copy.deepcopy(TARGETS), refit=refit_for(llm.engine.model_cfg)))
+    while not all(r.done.is_set() for r in reqs):
+        if not llm.engine.step() and llm.engine.scheduler.idle():
+            break
+    if llm.world > 1:
+        broadcast_plan(llm.engine.control_group, np.zeros(0, dtype=np.int32))
+    return [{k: v.clone() for k, v in r.response.items()} for r in reqs]
+
+
 def main():
     out_path, device, pp, mb = sys.argv[1], sys.argv[2], int(sys.argv[3]), int(sys.argv[4])
     mc = model_cfg(device)
@@ -52,9 +85,11 @@ def main():
     s = ne.SamplingConfig()
     s.max_new_tokens, s.ignore_eos = 5, True
     reqs = llm.generate(prompts_for(mc.vocab_size) if llm.rank == 0 else [], s)
+    targets = run_targets(llm) if os.environ.get("PP_TARGETS") else None
     if llm.rank == 0:
         order = sorted(first)
         torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "first": torch.stack([first[k] for k in order]),
+                    "targets": targets,
                     "layers": (llm.model.layer_lo, llm.model.layer_hi),
                     "sent_bytes": llm.engine.runner.pipeline.sent_bytes if llm.engine.runner.pipeline else 0}, out_path)
     import torch.distributed as dist

@@ -30,10 +30,10 @@ def test_split_sequences_balances_tokens():
     assert len(split_sequences(np.ones(8, dtype=np.int64), 4)) == 4
 
 
-def _launch(nproc, out, pp, mb, port):
+def _launch(nproc, out, pp, mb, port, **env):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "pp_worker.py"), out, "cpu", str(pp), str(mb)]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1", **env))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return torch.load(out)
 
@@ -73,3 +73,37 @@ def test_pipeline_matches_single_process(tmp_path, nproc, pp, mb, port):
     assert got["sent_bytes"] > 0
     assert float((got["first"] - want_first).abs().max()) < 1e-3
     assert got["tokens"] == want_tokens
+
+
+@pytest.mark.parametrize("nproc,pp,mb,port", [(2, 2, 2, 29714), (4, 2, 2, 29715)])
+def test_request_targets_over_pipeline_stages(tmp_path, nproc, pp, mb, port):
+    """/forward style targets under pipeline (and pipeline x tensor) parallelism: the last stage owns the final
+    hidden states and the lm_head, rank 0 answers the request - same tensors as one process."""
+    import copy
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from pp_worker import TARGETS, model_cfg, prompts_for, refit_for
+    from ksanallm_b200.config import EngineConfig
+    from ksanallm_b200.models.weights import RandomSource, build_model
+    from ksanallm_b200.runtime.engine import LLMEngine
+    from ksanallm_b200.utils import native_engine as ne
+    mc = model_cfg("cpu")
+    model = build_model(mc, RandomSource(seed=11, std=0.2), device="cpu", dtype=torch.float32)
+    ec = EngineConfig()
+    ec.batch_scheduler.max_batch_size, ec.batch_scheduler.max_token_len, ec.batch_scheduler.max_step_tokens = 8, 300, 512
+    eng = LLMEngine(model, mc, ec, num_blocks=128)
+    s = ne.SamplingConfig()
+    s.max_new_tokens = 1
+    want = [eng.add_request(p, s, request_target=copy.deepcopy(TARGETS)) for p in prompts_for(mc.vocab_size)[2:]]
+    want.append(eng.add_request(prompts_for(mc.vocab_size)[2], s, request_target=copy.deepcopy(TARGETS), refit=refit_for(mc)))
+    while not all(r.done.is_set() for r in want):
+        eng.step()
+    got = _launch(nproc, str(tmp_path / "pp.pt"), pp, mb, port, PP_TARGETS="1")["targets"]
+    assert len(got) == len(want) == 3
+    # the spliced embeddings change the states of the third request (same prompt as the first)
+    assert float((want[2].response["transformer"] - want[0].response["transformer"]).abs().max()) > 1e-2
+    for g, w in zip(got, want):
+        assert set(g) == set(w.response) == set(TARGETS)
+        assert g["transformer"].shape == (4, mc.hidden_size) and g["logits"].shape == (11,)
+        for k in TARGETS:
+            assert float((g[k] - w.response[k]).abs().max()) < 1e-3, k
+
