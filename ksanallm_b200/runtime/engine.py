@@ -328,7 +328,12 @@ class LLMEngine:
             req.structured = StructuredOutput(self.fsm_controller.get_or_create(structured_regex), self.tokenizer)
         if cfg.seed == 0:
             cfg.seed = int.from_bytes(os.urandom(7), "little") | 1
-        code, msg, seq_ids = self.scheduler.add_request(req_id, list(prompt), cfg)
+        if getattr(self.model, "dp", None) is not None and (request_target or refit is not None or mrope_positions is not None):
+            # attention data parallelism hands each rank the rows of its own sequences; per-row extras address the
+            # rows of the whole step and are not re-indexed per rank
+            code, msg, seq_ids = 1, "request targets and spliced embeddings are not supported with attention data parallelism", []
+        else:
+            code, msg, seq_ids = self.scheduler.add_request(req_id, list(prompt), cfg)
         ne.report_counter("forward_req_total_num", 1)
         if code != 0:
             req.status_code, req.status_message = code, msg
