@@ -65,10 +65,14 @@ def main():
     if llm.rank == 0:
         order = sorted(first)
         moe = llm.model.layers[0].moe
+        # a request with per-row extras is answered with a status at admission: nothing is scheduled for it
+        refused = (llm.engine.add_request([5, 6, 7], s, request_target={"transformer": {"token_reduce_mode": "GATHER_ALL"}})
+                   if llm.model.dp is not None else None)
         torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "first": torch.stack([first[k] for k in order]),
                     "experts": (moe.expert_lo, moe.expert_hi), "gathered_bytes": llm.model.dp.gathered_bytes if llm.model.dp else 0,
                     "peer_memory": bool(llm.model.dp is not None and llm.model.dp.symm is not None),
-                    "stats": dict(llm.engine.scheduler.stats())},
+                    "stats": dict(llm.engine.scheduler.stats()) if llm.engine.scheduler else {},
+                    "refused": (refused.status_code, refused.done.is_set()) if llm.model.dp is not None else None},
                    out_path)
     import torch.distributed as dist
     llm.shutdown()

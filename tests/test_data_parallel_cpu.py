@@ -85,6 +85,7 @@ def test_attention_dp_ranks_pool_their_caches(tmp_path, blocks, host):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     got = torch.load(out)
     assert got["tokens"] == want_tokens
+    assert got["refused"] == (1, True)
     st = got["stats"]
     if host:
         assert st["preempt_swap"] > 0 and st["swap_in"] > 0
