@@ -26,6 +26,7 @@ import csv
 import json
 import math
 import random
+import os
 import sys
 import time
 from dataclasses import dataclass, field
@@ -262,6 +263,9 @@ def args_config(argv=None):
     p.add_argument("--port", type=int, default=8080)
     p.add_argument("--input_csv", default=None)
     p.add_argument("--col_idx", type=int, default=0)
+    p.add_argument("--prefix_cache_csv", default=None,
+                   help="prompt set with a shared preamble (see prefix_cache_reader.py); the shared token count is "
+                        "reported when --tokenizer_path is given")
     p.add_argument("--output_csv", default=None, help="per-request outputs (prompt length, output length, latency, text)")
     p.add_argument("--perf_csv", default=None, help="one row of summary statistics per iteration")
     p.add_argument("--request_rate", type=float, default=float("inf"), help="requests per second; inf = all at once")
@@ -319,8 +323,15 @@ def run_benchmark(args) -> List[dict]:
         work = [(p, None) for p in read_prompts(args.input_csv, args.col_idx, args.prompt_num, args.shuffle, args.seed)]
         if args.chat_template:
             work = [(apply_chat_template(args, p), n) for p, n in work]
+    elif args.prefix_cache_csv:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from prefix_cache_reader import load_prompts
+        shared, prompts = load_prompts(args.prefix_cache_csv, getattr(args, "tokenizer_path", None) or None,
+                                       args.prompt_num or 220)
+        print(f"prefix-cache prompt set: {len(prompts)} prompts, {shared} shared prefix tokens")
+        work = [(p, None) for p in prompts]
     else:
-        raise SystemExit("give --input_csv or --synthetic")
+        raise SystemExit("give --input_csv, --prefix_cache_csv or --synthetic")
     pct = sorted(set([50.0] + list(args.percentiles)))
     results = []
     rate = args.request_rate

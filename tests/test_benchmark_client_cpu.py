@@ -142,3 +142,29 @@ def test_command_line_clients_against_live_server(server, capsys):
                                        "--slice", "0", "1"])
     assert doc["responses"][0]["response"][0]["tensor"].shape[0] == 2
     assert "perplexity" in capsys.readouterr().out
+
+
+def test_prompt_sets_and_prefix_cache_reader(tmp_path):
+    """The shipped prompt sets load through the client's CSV reader; the prefix-cache set shares its preamble token
+    for token, and its engine configuration parses."""
+    import importlib.util
+    from ksanallm_b200.config import load_yaml_config
+    bench_dir = os.path.dirname(os.path.abspath(bt.__file__))
+    spec = importlib.util.spec_from_file_location("prefix_cache_reader", os.path.join(bench_dir, "prefix_cache_reader.py"))
+    reader = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(reader)
+    assert reader.common_prefix_len([[1, 2, 3, 4], [1, 2, 9], [1, 2, 3]]) == 2
+    assert reader.common_prefix_len([]) == 0 and reader.common_prefix_len([[5, 6]]) == 2
+    path = os.path.join(bench_dir, "prefix_cache_input.csv")
+    shared, prompts = reader.load_prompts(path, tokenizer=ByteTokenizer(), count=50)
+    assert len(prompts) == 50 and len(set(prompts)) == 24 and prompts[24] == prompts[0]
+    assert shared > 700 and all(p.startswith("[INST]You are the assistant") and p.endswith("[/INST]") for p in prompts)
+    assert reader.load_prompts(path, count=0)[0] == 0                       # no tokenizer: nothing measured
+    bad = tmp_path / "bad.csv"
+    bad.write_text("description\nid,text\n0,hello\n")
+    with pytest.raises(ValueError):
+        reader.load_prompts(str(bad))
+    qs = bt.read_prompts(os.path.join(bench_dir, "benchmark_input.csv"), 0, 0, False, 0)
+    assert len(qs) == 32 and all(q.startswith("Think about") for q in qs)
+    ec = load_yaml_config(os.path.join(bench_dir, "prefix_cache_config.yaml"))
+    assert ec.batch_scheduler.enable_auto_prefix_cache and ec.batch_scheduler.max_batch_size == 256
