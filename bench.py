@@ -246,6 +246,7 @@ def main():
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
     l0, h0, d0 = native.launch_count(), llm.engine.runner.h2d_bytes, llm.engine.sampler.d2h_bytes
+    llm.engine.host_ms.clear()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
@@ -255,6 +256,7 @@ def main():
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
     launches = native.launch_count() - l0
+    host_ms = dict(llm.engine.host_ms)
     h2d = (llm.engine.runner.h2d_bytes - h0) / max(args.steps, 1)
     d2h = (llm.engine.sampler.d2h_bytes - d0) / max(args.steps, 1)
     # end-to-end arm: host clock around the public API (inputs are host lists -> pinned staging -> H2D each
@@ -297,6 +299,8 @@ def main():
             "p50_tpot_ms": statistics.median(latency["tpot"]) if latency["tpot"] else None,
             "clocks": clocks, "gpu_launches": launches,
             "graph_replays": getattr(llm.engine.runner, "graph_replays", 0),
+            "host_ms_per_engine_step": {k: round(v / max(1, host_ms.get("steps", 1)), 3) for k, v in host_ms.items() if k != "steps"},
+            "engine_steps": host_ms.get("steps", 0),
         }
         if e2e_ms is not None:
             res["e2e"] = {"value": out_tokens / (e2e_ms / 1000.0), "unit": "tok/s", "h2d_bytes_per_step": h2d,

@@ -1,7 +1,7 @@
 """Small, self-contained launches of the hot kernels for profiling (each case runs its kernel twice).
 
-  python -m ksanallm_b200.ops.profile_cases [case ...]
-  ncu --set full --clock-control none -k regex:<kernel> -c <n> -o prof python -m ksanallm_b200.ops.profile_cases <case>
+  python benchmarks/kernel_cases.py [case ...]
+  ncu --set full --clock-control none -k regex:<kernel> -c <n> -o prof python benchmarks/kernel_cases.py <case>
 
 Cases keep a few hundred MB on the device: larger than L2 where DRAM figures matter, small enough for a
 multi-pass capture to finish in a minute or two.
@@ -9,11 +9,14 @@ multi-pass capture to finish in a minute or two.
 from __future__ import annotations
 
 import math
+import os
 import sys
 
 import torch
 
-from . import native, reference as ref
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ksanallm_b200.ops import native, reference as ref  # noqa: E402
 
 DEV = "cuda"
 

@@ -185,6 +185,10 @@ PYBIND11_MODULE(_ksana_engine, m) {
       .def_property_readonly("copies", [](const StepPlan& p) {
         std::vector<int> v; for (auto& c : p.copies) { v.push_back(c.src); v.push_back(c.dst); v.push_back(c.pos_delta); }
         return ToArray(v); })
+      .def_property_readonly("pre_copies", [](const StepPlan& p) {
+        std::vector<int> v; for (auto& c : p.pre_copies) { v.push_back(c.src); v.push_back(c.dst); v.push_back(c.pos_delta); }
+        return ToArray(v); })
+      .def("has_block_ops", &StepPlan::has_block_ops)
       .def_property_readonly("events", [](const StepPlan& p) { return EventsToList(p.events); })
       .def_readonly("max_blocks", &StepPlan::max_blocks)
       .def_readonly("num_multi", &StepPlan::num_multi)
@@ -192,6 +196,8 @@ PYBIND11_MODULE(_ksana_engine, m) {
       .def_readonly("num_tokens", &StepPlan::num_tokens)
       .def_readonly("num_multi_tokens", &StepPlan::num_multi_tokens)
       .def_readonly("max_q_len", &StepPlan::max_q_len)
+      .def_readonly("sample_k", &StepPlan::sample_k)
+      .def_readwrite("sample_full", &StepPlan::sample_full)
       .def("empty", &StepPlan::empty)
       .def("pack", [](const StepPlan& p) { return ToArray(p.Pack()); })
       .def_static("unpack", [](py::array_t<int32_t, py::array::c_style | py::array::forcecast> a) {

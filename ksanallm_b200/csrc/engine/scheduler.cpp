@@ -14,7 +14,7 @@ inline int CeilMul(int bs, float thr) { return static_cast<int>(std::ceil(static
 // ---------------------------------------------------------------------------------- StepPlan
 std::vector<int32_t> StepPlan::Pack() const {
   // header: magic, nseq, ntok, num_multi, num_single, num_multi_tokens, max_q_len, max_blocks,
-  //         nsample, nswap_out, nswap_in, ncopies, reserved x4
+  //         nsample, nswap_out, nswap_in, ncopies, npre_copies, sample_k, sample_full, reserved
   std::vector<int32_t> out;
   const int nseq = static_cast<int>(seq_ids.size());
   out.reserve(16 + nseq * (4 + max_blocks) + num_tokens * 3 + 64);
@@ -30,7 +30,10 @@ std::vector<int32_t> StepPlan::Pack() const {
   out.push_back(static_cast<int>(swap_out.size()));
   out.push_back(static_cast<int>(swap_in.size()));
   out.push_back(static_cast<int>(copies.size()));
-  for (int i = 0; i < 4; ++i) out.push_back(0);
+  out.push_back(static_cast<int>(pre_copies.size()));
+  out.push_back(sample_k);
+  out.push_back(sample_full ? 1 : 0);
+  out.push_back(0);
   auto put = [&](const std::vector<int>& v) { out.insert(out.end(), v.begin(), v.end()); };
   auto put64 = [&](const std::vector<int64_t>& v) {
     for (int64_t x : v) { out.push_back(static_cast<int32_t>(x & 0xffffffff)); out.push_back(static_cast<int32_t>(x >> 32)); }
@@ -41,6 +44,7 @@ std::vector<int32_t> StepPlan::Pack() const {
   for (auto& s : swap_out) { out.push_back(s.device_block); out.push_back(s.host_block); }
   for (auto& s : swap_in) { out.push_back(s.device_block); out.push_back(s.host_block); }
   for (auto& c : copies) { out.push_back(c.src); out.push_back(c.dst); out.push_back(c.pos_delta); }
+  for (auto& c : pre_copies) { out.push_back(c.src); out.push_back(c.dst); out.push_back(c.pos_delta); }
   return out;
 }
 
@@ -50,9 +54,14 @@ bool StepPlan::Unpack(const int32_t* d, size_t n, StepPlan* p) {
   const int nseq = d[1];
   p->num_tokens = d[2]; p->num_multi = d[3]; p->num_single = d[4]; p->num_multi_tokens = d[5];
   p->max_q_len = d[6]; p->max_blocks = d[7];
-  const int nsample = d[8], nso = d[9], nsi = d[10], ncp = d[11];
+  const int nsample = d[8], nso = d[9], nsi = d[10], ncp = d[11], npre = d[12];
+  p->sample_k = d[13];
+  p->sample_full = d[14] != 0;
+  if (nseq < 0 || p->num_tokens < 0 || p->max_blocks < 0 || nsample < 0 || nso < 0 || nsi < 0 || ncp < 0 || npre < 0)
+    return false;
   size_t need = 16 + static_cast<size_t>(p->num_tokens) * 3 + (nseq + 1) + nseq * 2 +
-                static_cast<size_t>(nseq) * p->max_blocks + nsample + 2 * nseq + 2 * nsample + 2 * nso + 2 * nsi + 3 * ncp;
+                static_cast<size_t>(nseq) * p->max_blocks + nsample + 2 * nseq + 2 * nsample + 2 * nso + 2 * nsi +
+                3 * ncp + 3 * npre;
   if (n < need) return false;
   const int32_t* c = d + 16;
   auto get = [&](std::vector<int>* v, size_t cnt) { v->assign(c, c + cnt); c += cnt; };
@@ -71,6 +80,7 @@ bool StepPlan::Unpack(const int32_t* d, size_t n, StepPlan* p) {
   for (int i = 0; i < nso; ++i) { p->swap_out.push_back({c[0], c[1]}); c += 2; }
   for (int i = 0; i < nsi; ++i) { p->swap_in.push_back({c[0], c[1]}); c += 2; }
   for (int i = 0; i < ncp; ++i) { p->copies.push_back({c[0], c[1], c[2]}); c += 3; }
+  for (int i = 0; i < npre; ++i) { p->pre_copies.push_back({c[0], c[1], c[2]}); c += 3; }
   return true;
 }
 
@@ -247,6 +257,10 @@ void Scheduler::EmitSequence(const SeqPtr& s, StepPlan* plan) {
     const int row = plan->num_tokens - 1;
     plan->sample_seq_ids.push_back(s->seq_id);
     plan->sample_rows.push_back(row);
+    const SamplingConfig& c = *s->cfg;
+    plan->sample_k = std::max(plan->sample_k, std::max(c.topk, c.logprobs_num));
+    if (c.repetition_penalty != 1.0f || c.no_repeat_ngram_size > 0 || c.encoder_no_repeat_ngram_size > 0)
+      plan->sample_full = true;
     // siblings waiting for this prefill draw their first token from the same logits row
     auto git = groups_.find(s->req_id);
     if (git != groups_.end()) {
@@ -431,14 +445,16 @@ bool Scheduler::Schedule(StepPlan* plan) {
   for (auto& s : multi) fill(s);
   for (auto& s : single) fill(s);
 
-  if (!plan->empty() && !pending_copies_.empty()) {
-    // forks decided after the previous step: their tail-block copies run before this forward
-    plan->copies.insert(plan->copies.begin(), pending_copies_.begin(), pending_copies_.end());
+  if (!pending_copies_.empty()) {
+    // Forks decided after the previous step: their tail-block copies run first, before this step's swap-outs,
+    // swap-ins and copies. A fork's destination block may be swapped out (its owner is the youngest sequence, the
+    // first victim) or freed and handed out again by this very plan, so it has to be filled before any of that.
+    plan->pre_copies.swap(pending_copies_);
     pending_copies_.clear();
   }
   ++stats_.steps;
   stats_.step_tokens += plan->num_tokens;
-  return !plan->empty();
+  return !plan->empty() || plan->has_block_ops();
 }
 
 bool Scheduler::CheckFinishLocked(const SeqPtr& s, int token, std::vector<SeqEvent>* ev) {

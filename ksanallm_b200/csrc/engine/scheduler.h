@@ -85,11 +85,19 @@ struct StepPlan {
   std::vector<int> block_table; int max_blocks = 0;
   std::vector<int64_t> sample_seq_ids;     // sequences that sample this step ...
   std::vector<int> sample_rows;            // ... and the token row whose logits they use
+  std::vector<BlockCopy> pre_copies;       // tail-block copies of forks decided after the previous step: they run
+                                           // first, before this step's swap-outs can touch their destinations
   std::vector<SwapCopy> swap_out, swap_in;
   std::vector<BlockCopy> copies;
   int num_multi = 0, num_single = 0, num_tokens = 0, num_multi_tokens = 0, max_q_len = 0;
+  // What this step's sampling needs from the logits: the largest candidate count of any sampling row
+  // (max(topk, logprobs_num)), and whether a row edits the whole logits row first (repetition penalty, n-gram
+  // bans). Tensor-parallel ranks use it to exchange per-shard top-k candidates instead of whole vocabulary shards.
+  int sample_k = 0;
+  bool sample_full = false;
   std::vector<SeqEvent> events;            // timeouts / aborts / rejections decided while planning
   bool empty() const { return seq_ids.empty(); }
+  bool has_block_ops() const { return !pre_copies.empty() || !swap_out.empty() || !swap_in.empty() || !copies.empty(); }
   void Clear() { *this = StepPlan(); }
   // Flat int32 image (header + arrays) used for the single host->device upload and for
   // broadcasting the step to the other ranks / nodes.

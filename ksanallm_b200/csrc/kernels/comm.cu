@@ -103,16 +103,36 @@ __device__ __forceinline__ uint2 pack8_e4m3c(const float (&f)[8], float inv_scal
 __device__ __forceinline__ uint32_t begin_epoch(const uint32_t* ctrs, int kind) {
   return *reinterpret_cast<const volatile uint32_t*>(ctrs + kind) + 1;
 }
-__device__ __forceinline__ void end_epoch(uint32_t* ctrs, int kind, uint32_t epoch) {
+// Returns true (to every thread of the block) in the last block of the grid to get here. `sys`: the block's stores
+// to peers are made visible system-wide before it is counted, so that the last block may tell the peers about them.
+__device__ __forceinline__ bool end_epoch(uint32_t* ctrs, int kind, uint32_t epoch, bool sys = false) {
+  __shared__ int s_last;
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(ctrs + 8 + kind, 1u) == gridDim.x - 1) {
+    if (sys) __threadfence_system(); else __threadfence();
+    const bool last = atomicAdd(ctrs + 8 + kind, 1u) == gridDim.x - 1;
+    if (last) {
       ctrs[8 + kind] = 0;
       __threadfence();
       *reinterpret_cast<volatile uint32_t*>(ctrs + kind) = epoch;
     }
+    s_last = last ? 1 : 0;
   }
+  __syncthreads();
+  return s_last != 0;
+}
+
+// "My rows are delivered": the last block of a kernel that pushed rows to the peers raises flag `kind` at every
+// peer with the next epoch of that kind; the consumer's wait (gather_wait_kernel, or a GEMM that waits itself)
+// reads the same counter after this kernel has finished.
+__device__ __forceinline__ void signal_delivered(const CommPeers& c, uint32_t* ctrs, int kind) {
+  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(ctrs + kind) + 1;
+  if (threadIdx.x < c.size) {
+    __threadfence_system();
+    st_release_sys(c.flags[threadIdx.x] + kind * kFlagStride + c.rank, epoch);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(ctrs + kind) = epoch;
 }
 
 struct ReduceNormParams {
@@ -132,26 +152,52 @@ struct ReduceNormParams {
                                   // product [M, H] sits at slots_off in its own buffer and the row owner reads
                                   // its rows from all peers (coalesced peer loads) instead of receiving pushes
   long long h_sym_off, y_sym_off, yq_sym_off, ys_sym_off;   // offsets of h / y / yq / yscale inside the symmetric buffer (gather mode: those tensors live there)
+  // NVLS: multicast address of the symmetric buffer (null: plain peer loads / stores). With it, pull mode takes the
+  // sum over all ranks' partial rows from the switch (one multimem.ld_reduce per 16 bytes instead of one load per
+  // rank) and the gather pushes go out once (multimem.st, replicated by the switch, own copy included).
+  uint8_t* mc;
   int* err;
 };
 
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const uint8_t* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st16(uint8_t* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               :: "l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void multimem_st8(uint8_t* mc_addr, const uint2& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" :: "l"(mc_addr), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void multimem_st4(uint8_t* mc_addr, float v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" :: "l"(mc_addr), "f"(v) : "memory");
+}
+
 constexpr int kRnMaxVec = 4;
 
-// grid = row_count blocks; block handles one row (up to kRnMaxVec * blockDim vectors of 8).
-__global__ void reduce_norm_kernel(const ReduceNormParams p) {
+// grid = row_count blocks; block handles one row (up to NV * blockDim vectors of 8). NV = 1 runs 1024 threads per row
+// (decode-sized batches: all of a row's peer loads are in flight at once), NV = kRnMaxVec 256 threads.
+template <int NV>
+__device__ __forceinline__ void reduce_norm_body(const ReduceNormParams& p) {
   __shared__ float red[32];
   const CommPeers& c = p.peers;
   const uint32_t epoch = begin_epoch(p.ctrs, 0);
   if (!signal_and_wait(c, 0, epoch, p.err, true)) return;
   const int lrow = blockIdx.x;                  // row inside this rank's slice
-  if (lrow >= p.row_count) { end_epoch(p.ctrs, 0, epoch); return; }   // a rank without rows only exchanges flags
+  if (lrow >= p.row_count) {          // a rank without rows only exchanges flags
+    if (end_epoch(p.ctrs, 0, epoch, (p.gather & 1) != 0) && (p.gather & 1)) signal_delivered(c, p.ctrs, 1);
+    return;
+  }
   const int row = p.row_begin + lrow;
   const int nvec = p.H >> 3;
   const uint8_t* base = static_cast<const uint8_t*>(c.data[c.rank]) + p.slots_off;
-  float v[kRnMaxVec][8];
+  float v[NV][8];
   float s = 0.f, s2 = 0.f;
 #pragma unroll
-  for (int j = 0; j < kRnMaxVec; ++j) {
+  for (int j = 0; j < NV; ++j) {
     const int i = threadIdx.x + j * blockDim.x;
     if (i < nvec) {
       float acc[8];
@@ -162,10 +208,19 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
       }
       // all loads first (peer loads in pull mode: one NVLink round trip, not one per rank), then a fixed summation
       // order so that every rank produces the same bits
+      const bool in_switch = p.mc != nullptr && (p.gather & 4);
+      if (in_switch) {
+        // every rank's partial row sits at the same offset of its symmetric buffer: the switch returns their sum
+        // (fp32 accumulation, rounded to bf16 once)
+        float f[8];
+        unpack8c(multimem_ld_reduce_bf16x8(p.mc + p.slots_off + (static_cast<size_t>(row) * p.H + static_cast<size_t>(i) * 8) * 2), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      }
       uint4 pv[kMaxRanks];
 #pragma unroll
       for (int r = 0; r < kMaxRanks; ++r) {
-        if (r < c.size) {
+        if (r < c.size && !in_switch) {
           const uint8_t* src = (p.gather & 4)
               ? static_cast<const uint8_t*>(c.data[r]) + p.slots_off + (static_cast<size_t>(row) * p.H) * 2
               : base + r * p.slot_stride + (static_cast<size_t>(lrow) * p.H) * 2;
@@ -174,7 +229,7 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
       }
 #pragma unroll
       for (int r = 0; r < kMaxRanks; ++r) {
-        if (r < c.size) {
+        if (r < c.size && !in_switch) {
           float f[8];
           unpack8c(pv[r], f);
 #pragma unroll
@@ -183,7 +238,9 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
       }
       const uint4 packed = pack8c(acc);
       if (p.h) reinterpret_cast<uint4*>(p.h + static_cast<size_t>(row) * p.H)[i] = packed;
-      if ((p.gather & 2) && p.h) {
+      if ((p.gather & 2) && p.h && p.mc) {
+        multimem_st16(p.mc + p.h_sym_off + (static_cast<size_t>(row) * p.H + static_cast<size_t>(i) * 8) * 2, packed);
+      } else if ((p.gather & 2) && p.h) {
         for (int r = 0; r < c.size; ++r) {
           if (r == c.rank) continue;
           bf16* ph = reinterpret_cast<bf16*>(static_cast<uint8_t*>(c.data[r]) + p.h_sym_off);
@@ -214,7 +271,7 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
       mean = block_sum(s) / p.H;
       float var = 0.f;
 #pragma unroll
-      for (int j = 0; j < kRnMaxVec; ++j) {
+      for (int j = 0; j < NV; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nvec) {
 #pragma unroll
@@ -226,7 +283,7 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
       rstd = rsqrtf(block_sum(s2) / p.H + p.eps);
     }
 #pragma unroll
-    for (int j = 0; j < kRnMaxVec; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       const bool on = i < nvec;
       float o[8];
@@ -246,7 +303,9 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
         const uint4 packed = pack8c(o);
         if (p.y) {
           reinterpret_cast<uint4*>(p.y + static_cast<size_t>(row) * p.H)[i] = packed;
-          if (p.gather & 1) {
+          if ((p.gather & 1) && p.mc) {
+            multimem_st16(p.mc + p.y_sym_off + (static_cast<size_t>(row) * p.H + static_cast<size_t>(i) * 8) * 2, packed);
+          } else if (p.gather & 1) {
             for (int r = 0; r < c.size; ++r) {
               if (r == c.rank) continue;
               bf16* py = reinterpret_cast<bf16*>(static_cast<uint8_t*>(c.data[r]) + p.y_sym_off);
@@ -267,7 +326,11 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
           const uint2 q = pack8_e4m3c(o, 1.f / scale);
           reinterpret_cast<uint2*>(p.yq + static_cast<size_t>(row) * p.H)[i] = q;
           if ((i & 15) == 0) p.yscale[static_cast<size_t>(i >> 4) * p.scale_ld + row] = scale;
-          if (p.gather & 1) {
+          if ((p.gather & 1) && p.mc) {
+            multimem_st8(p.mc + p.yq_sym_off + static_cast<size_t>(row) * p.H + static_cast<size_t>(i) * 8, q);
+            if ((i & 15) == 0)
+              multimem_st4(p.mc + p.ys_sym_off + (static_cast<size_t>(i >> 4) * p.scale_ld + row) * 4, scale);
+          } else if (p.gather & 1) {
             for (int r = 0; r < c.size; ++r) {
               if (r == c.rank) continue;
               uint8_t* pq = static_cast<uint8_t*>(c.data[r]) + p.yq_sym_off;
@@ -282,14 +345,19 @@ __global__ void reduce_norm_kernel(const ReduceNormParams p) {
       }
     }
   }
-  end_epoch(p.ctrs, 0, epoch);
+  // gather mode: once every block's pushes are visible, the last block tells the peers that this rank's slice is there
+  if (end_epoch(p.ctrs, 0, epoch, (p.gather & 1) != 0) && (p.gather & 1)) signal_delivered(c, p.ctrs, 1);
 }
 
-// Second half of the gather mode: flag "my slice is delivered" and wait for every peer's slice.
-// Runs as its own small launch after reduce_norm_kernel so that all blocks' pushes are complete.
-__global__ void gather_fence_kernel(const CommPeers c, uint32_t* ctrs, int* err) {
-  const uint32_t epoch = begin_epoch(ctrs, 1);
-  if (signal_and_wait(c, 1, epoch, err, true)) end_epoch(ctrs, 1, epoch);
+__global__ void __launch_bounds__(1024) reduce_norm_kernel_v1(const ReduceNormParams p) { reduce_norm_body<1>(p); }
+__global__ void reduce_norm_kernel_v4(const ReduceNormParams p) { reduce_norm_body<kRnMaxVec>(p); }
+
+// Second half of the gather mode: wait until every peer has flagged its slice as delivered (the flag is raised by
+// the last block of the peer's reduce_norm_kernel). Stream-ordered after this rank's own reduce_norm_kernel, so the
+// epoch to wait for is the counter's current value.
+__global__ void gather_wait_kernel(const CommPeers c, const uint32_t* ctrs, int* err) {
+  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(ctrs + 1);
+  signal_and_wait(c, 1, epoch, err, false);
 }
 
 // Plain barrier across ranks (bounded).
@@ -364,8 +432,10 @@ extern "C" int ksana_reduce_norm(const unsigned long long* data_ptrs, const unsi
                                  int row_begin, int row_count, int M, int H, void* h, const void* norm_w,
                                  const void* norm_b, float eps, int layernorm, void* y, void* yq, float* yscale,
                                  int scale_ld, int gather, long long h_sym_off, long long y_sym_off,
-                                 long long yq_sym_off, long long ys_sym_off, int* err, cudaStream_t st) {
+                                 long long yq_sym_off, long long ys_sym_off, unsigned long long mc_base, int* err,
+                                 cudaStream_t st) {
   if (size > kMaxRanks || H % 8 || H > 8 * kRnMaxVec * 1024) return -10;
+  if (mc_base && ((slots_off | h_sym_off | y_sym_off | yq_sym_off | ys_sym_off) & 15)) return -12;
   if (yq && H % 128) return -11;
   ReduceNormParams p{};
   p.peers = make_peers(data_ptrs, flag_ptrs, rank, size);
@@ -376,15 +446,20 @@ extern "C" int ksana_reduce_norm(const unsigned long long* data_ptrs, const unsi
   p.eps = eps; p.layernorm = layernorm;
   p.y = static_cast<bf16*>(y); p.yq = static_cast<uint8_t*>(yq); p.yscale = yscale; p.scale_ld = scale_ld;
   p.gather = gather; p.h_sym_off = h_sym_off; p.y_sym_off = y_sym_off; p.yq_sym_off = yq_sym_off; p.ys_sym_off = ys_sym_off;
+  p.mc = reinterpret_cast<uint8_t*>(mc_base);
   p.err = err;
-  int threads = (((H >> 3) + kRnMaxVec - 1) / kRnMaxVec + 31) / 32 * 32;
+  // few rows (decode): one 16-byte vector per thread, so that a row's loads from all peers are in flight together;
+  // many rows: up to kRnMaxVec vectors per thread
+  const int per_thread = (row_count <= 64 && H <= 8192) ? 1 : kRnMaxVec;
+  int threads = (((H >> 3) + per_thread - 1) / per_thread + 31) / 32 * 32;
   if (threads < 32) threads = 32;
   if (threads > 1024) threads = 1024;
   // a rank with no rows still takes part in the flag exchange
-  reduce_norm_kernel<<<row_count > 0 ? row_count : 1, threads, 0, st>>>(p);
+  if (per_thread == 1) reduce_norm_kernel_v1<<<row_count > 0 ? row_count : 1, threads, 0, st>>>(p);
+  else reduce_norm_kernel_v4<<<row_count > 0 ? row_count : 1, threads, 0, st>>>(p);
   if (cudaGetLastError() != cudaSuccess) return -4;
   if (gather & 1) {
-    gather_fence_kernel<<<1, 32, 0, st>>>(p.peers, p.ctrs, err);
+    gather_wait_kernel<<<1, 32, 0, st>>>(p.peers, p.ctrs, err);
     if (cudaGetLastError() != cudaSuccess) return -5;
   }
   return 0;

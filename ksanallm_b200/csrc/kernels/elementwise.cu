@@ -412,20 +412,34 @@ __global__ void rope_kv_append_vec_kernel(bf16* __restrict__ qkv, const int* __r
 
 // Block-to-block copy inside the paged cache (beam fork, flexible cache, swap staging):
 // pairs[2*i] = source block, pairs[2*i+1] = destination block; copies all layers of a block.
-__global__ void copy_blocks_kernel(uint4* __restrict__ cache, const int* __restrict__ pairs, long long block_vec) {
-  const uint4* src = cache + static_cast<size_t>(pairs[2 * blockIdx.x]) * block_vec;
-  uint4* dst = cache + static_cast<size_t>(pairs[2 * blockIdx.x + 1]) * block_vec;
+// A block id outside [0, num_blocks) is recorded in the error word and its copy is skipped.
+__global__ void copy_blocks_kernel(uint4* __restrict__ cache, const int* __restrict__ pairs, long long block_vec,
+                                   int num_blocks, int* err) {
+  const int sb = pairs[2 * blockIdx.x], db = pairs[2 * blockIdx.x + 1];
+  if (sb < 0 || sb >= num_blocks || db < 0 || db >= num_blocks) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) guard_report(err, kGuardBlockId, (sb < 0 || sb >= num_blocks) ? sb : db);
+    return;
+  }
+  const uint4* src = cache + static_cast<size_t>(sb) * block_vec;
+  uint4* dst = cache + static_cast<size_t>(db) * block_vec;
   for (long long i = blockIdx.y * static_cast<long long>(blockDim.x) + threadIdx.x; i < block_vec;
        i += static_cast<long long>(gridDim.y) * blockDim.x)
     dst[i] = src[i];
 }
 
-// Gather / scatter of whole cache blocks between the device cache and a pinned host staging
-// area (one launch per swap instead of one memcpy per block). dir 0: cache->stage, 1: stage->cache.
-__global__ void swap_blocks_kernel(uint4* __restrict__ cache, uint4* __restrict__ stage, const int* __restrict__ ids,
-                                   long long block_vec, int dir) {
-  uint4* c = cache + static_cast<size_t>(ids[blockIdx.x]) * block_vec;
-  uint4* s = stage + static_cast<size_t>(blockIdx.x) * block_vec;
+// Whole cache blocks between the device cache and a pool of host blocks in pinned (device-visible) host memory:
+// pairs[2*i] = device block, pairs[2*i+1] = host block; dir 0: cache -> host pool, 1: host pool -> cache. One launch
+// per swap list; the kernel moves the bytes over PCIe itself, so no staging copy and no host synchronisation is
+// needed. Ids outside their pools are recorded in the error word and skipped.
+__global__ void swap_blocks_kernel(uint4* __restrict__ cache, uint4* __restrict__ pool, const int* __restrict__ pairs,
+                                   long long block_vec, int dir, int num_blocks, int num_pool_blocks, int* err) {
+  const int b = pairs[2 * blockIdx.x], hb = pairs[2 * blockIdx.x + 1];
+  if (b < 0 || b >= num_blocks || hb < 0 || hb >= num_pool_blocks) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) guard_report(err, kGuardBlockId, (b < 0 || b >= num_blocks) ? b : hb);
+    return;
+  }
+  uint4* c = cache + static_cast<size_t>(b) * block_vec;
+  uint4* s = pool + static_cast<size_t>(hb) * block_vec;
   for (long long i = blockIdx.y * static_cast<long long>(blockDim.x) + threadIdx.x; i < block_vec;
        i += static_cast<long long>(gridDim.y) * blockDim.x) {
     if (dir == 0) s[i] = c[i]; else c[i] = s[i];
@@ -606,18 +620,20 @@ extern "C" int ksana_rope_kv_append(void* qkv, const int* positions, int pos_str
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-extern "C" int ksana_copy_blocks(void* cache, const int* pairs, int npairs, long long block_bytes, cudaStream_t st) {
+extern "C" int ksana_copy_blocks(void* cache, const int* pairs, int npairs, long long block_bytes, int num_blocks,
+                                 int* err, cudaStream_t st) {
   if (npairs <= 0) return 0;
   if (block_bytes % 16) return -10;
-  copy_blocks_kernel<<<dim3(npairs, 16), 256, 0, st>>>((uint4*)cache, pairs, block_bytes / 16);
+  copy_blocks_kernel<<<dim3(npairs, 16), 256, 0, st>>>((uint4*)cache, pairs, block_bytes / 16, num_blocks, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-extern "C" int ksana_swap_blocks(void* cache, void* stage, const int* ids, int n, long long block_bytes, int dir,
-                                 cudaStream_t st) {
+extern "C" int ksana_swap_blocks(void* cache, void* pool, const int* pairs, int n, long long block_bytes, int dir,
+                                 int num_blocks, int num_pool_blocks, int* err, cudaStream_t st) {
   if (n <= 0) return 0;
   if (block_bytes % 16) return -10;
-  swap_blocks_kernel<<<dim3(n, 16), 256, 0, st>>>((uint4*)cache, (uint4*)stage, ids, block_bytes / 16, dir);
+  swap_blocks_kernel<<<dim3(n, 16), 256, 0, st>>>((uint4*)cache, (uint4*)pool, pairs, block_bytes / 16, dir, num_blocks,
+                                                  num_pool_blocks, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -24,14 +24,17 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdio.h>
+#include <atomic>
+#include <mutex>
+#include <type_traits>
 
 namespace ksana {
 
 constexpr int kSmThreads = 192;        // + one scale-packer warp (warp 6) for kind 2
 constexpr int kSmSfStages = 4;        // scale-chunk buffers
-constexpr int kSmSfBatch = 1;
 constexpr int kSmRowBytes = 128;
-constexpr int kSmSmemBudget = 200 * 1024;
+constexpr int kSmSmemBudget = 226 * 1024;   // all shared memory of a CTA: operand ring + scale buffers + staging + barriers
+constexpr int kSmXsKb = 256;          // kind 2: K blocks whose activation-scale exponents fit the shared-memory table
 
 struct SmallMParams {
   int M, N, K;
@@ -42,14 +45,27 @@ struct SmallMParams {
   const float* w_scale;                   // [ceil(N/128)][K/128]
   int seg_cap;                            // scratch slots per output tile
   float* scratch;                         // [n_tiles][seg_cap][MP][128] fp32 partial tiles
-  unsigned int* counters;                 // [n_tiles], zero before the first launch
+  unsigned int* counters;                 // [2 * n_tiles] (pieces written, pieces reduced), zero before the first launch
+  int vec_out;                            // D (and the residual) allow 16-byte row accesses
   int* err;
   // push mode: the (partial) result is stored into every rank's receive slot for this rank instead of D
   __nv_bfloat16* push[8];
   int push_n;
   // kind 3 (weight-only 4-bit): packed levels [N, K/2] (even k in the low nibble), fp16 scale and zero*scale [N, K/group]
   const uint8_t* w4; const __half* w4_scale; const __half* w4_zs; int w4_group;
+  // optional cycle counters per CTA and role (16 words per CTA), see ksana_smallm_set_profile
+  long long* prof;
 };
+
+__device__ __forceinline__ long long prof_clock() { return clock64(); }
+// adds the cycles since t0 to counter k of this CTA when profiling is on
+#define KSANA_PROF_ADD(k, t0) do { if (p.prof) p.prof[blockIdx.x * 16 + (k)] += prof_clock() - (t0); } while (0)
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 constexpr int pow2_at_least(int x) { int p = 32; while (p < x) p *= 2; return p; }
 
@@ -58,6 +74,9 @@ template <int MP, int KIND>   // MP: padded token count (16..128); KIND 0 bf16, 
 struct SmallMCfg {
   static constexpr int kThreads = KIND == 2 ? kSmThreads + 32 : (KIND == 3 ? kSmThreads + 256 : kSmThreads);
   static constexpr int kSfBytes = KIND == 2 ? kSmSfStages * 1024 : 0;     // per stage: weight chunk + token chunk
+  // kind 2: exponent bytes of the activation scales of every K block ([kb][MP]), filled once per CTA so that the
+  // scale packer never waits for a global load in the steady state
+  static constexpr int kXsBytes = KIND == 2 ? kSmXsKb * MP : 0;
   static constexpr int kWBytes = 128 * kSmRowBytes;
   static constexpr int kXBytes = MP * kSmRowBytes;
   // kind 3: ring of packed 4-bit tiles, each 128 rows x 128 bytes = four K blocks (wide rows keep DRAM pages open)
@@ -65,12 +84,14 @@ struct SmallMCfg {
   static constexpr int kPackedBytes = 128 * 128;
   static constexpr int kPackedRing = kPackedSlots * kPackedBytes;
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kStagesRaw = (kSmSmemBudget - kSfBytes - kPackedRing) / kStageBytes;
+  // epilogue staging tile [MP tokens][128 features] bf16: results leave (and residual rows enter) as 16-byte vectors
+  static constexpr int kOutBytes = MP * 256;
+  static constexpr int kStagesRaw = (kSmSmemBudget - kSfBytes - kXsBytes - kPackedRing - kOutBytes - 1536) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
   static constexpr int kAccStages = KIND != 1 ? 2 : ((512 / MP) > 4 ? 4 : (512 / MP));
   static constexpr int kSfBase = kAccStages * MP;                         // kind 2: two sets of 8 scale columns
   static constexpr int kTmemCols = pow2_at_least(kAccStages * MP + (KIND == 2 ? 16 : 0));
-  static constexpr int kSmemBytes = kStages * kStageBytes + kPackedRing + kSfBytes + 1024 + 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kPackedRing + kSfBytes + kXsBytes + kOutBytes + 1024 + 512;
   static constexpr int kElems = (KIND == 0 || KIND == 3) ? 64 : 128;
 };
 
@@ -105,6 +126,88 @@ __device__ __forceinline__ float pick_half(const uint4& v, int i) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>((i & 1) ? (w >> 16) : (w & 0xffffu))));
 }
 
+// ---- epilogue output. A thread of the four epilogue warps owns one output feature (column tile * 128 + nrow) and
+// holds NR consecutive token rows of it in registers (v[r] = row row0 + r); the output matrix is [token][feature].
+// Staged form: the residual rows come in as 16-byte vectors, every thread adds its column in shared memory (one
+// rounding of acc + bias + residual, as in the scalar form), and the rows leave as 16-byte vectors.
+template <int NR>
+__device__ __forceinline__ void store_rows_staged(const SmallMParams& p, uint8_t* out_stage, int tile, int nrow, int row0,
+                                                  int nrows, const float (&v)[NR]) {
+  const int t = static_cast<int>(threadIdx.x) - 64;
+  const int n0 = tile * 128, n = n0 + nrow;
+  uint4* st4 = reinterpret_cast<uint4*>(out_stage);
+  __nv_bfloat16* stb = reinterpret_cast<__nv_bfloat16*>(out_stage);
+  if (p.residual) {
+    for (int i = t; i < nrows * 16; i += 128) {
+      const int r = i >> 4, c = i & 15;
+      const __nv_bfloat16* src = p.residual + static_cast<size_t>(row0 + r) * p.ldr + n0 + c * 8;
+      if (n0 + c * 8 + 8 <= p.N) st4[i] = *reinterpret_cast<const uint4*>(src);
+      else
+        for (int e = 0; e < 8; ++e) stb[i * 8 + e] = (n0 + c * 8 + e < p.N) ? src[e] : __float2bfloat16(0.f);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+  }
+  const float b = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    if (r < nrows) {
+      float o = v[r] + b;
+      if (p.residual) o += __bfloat162float(stb[r * 128 + nrow]);
+      stb[r * 128 + nrow] = __float2bfloat16(o);
+    }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  for (int i = t; i < nrows * 16; i += 128) {
+    const int r = i >> 4, c = i & 15;
+    __nv_bfloat16* dst = p.D + static_cast<size_t>(row0 + r) * p.ldd + n0 + c * 8;
+    if (n0 + c * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(dst) = st4[i];
+    else
+      for (int e = 0; e < 8; ++e)
+        if (n0 + c * 8 + e < p.N) dst[e] = stb[i * 8 + e];
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");      // the staging tile is reused by the next caller
+}
+
+// Scalar form (fp32 output, push mode, unaligned outputs): two-byte / four-byte accesses, eight rows at a time so
+// that the residual loads of a batch are in flight together (the output may alias the residual).
+template <int NR>
+__device__ __forceinline__ void store_rows_scalar(const SmallMParams& p, int tile, int nrow, int row0, int nrows,
+                                                  const float (&v)[NR]) {
+  const int n = tile * 128 + nrow;
+  if (n >= p.N) return;
+  const float b = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+  for (int r0 = 0; r0 < NR; r0 += 8) {
+    if (r0 >= nrows) break;
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = r0 + i;
+      o[i] = v[r < NR ? r : NR - 1] + b;
+      if (p.residual && r < nrows) o[i] += __bfloat162float(p.residual[static_cast<size_t>(row0 + r) * p.ldr + n]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = r0 + i;
+      if (r >= nrows) continue;
+      const size_t m = static_cast<size_t>(row0 + r);
+      if (p.push_n) {
+        const __nv_bfloat16 ob = __float2bfloat16(o[i]);
+        for (int q = 0; q < p.push_n; ++q) p.push[q][m * p.ldd + n] = ob;
+      } else if (p.out_f32) p.out_f32[m * p.ldd + n] = o[i];
+      else p.D[m * p.ldd + n] = __float2bfloat16(o[i]);
+    }
+  }
+}
+
+template <int NR>
+__device__ __forceinline__ void store_rows(const SmallMParams& p, uint8_t* out_stage, int tile, int nrow, int row0,
+                                           int nrows, const float (&v)[NR]) {
+  if (nrows <= 0) return;
+  if (p.vec_out && !p.out_f32 && !p.push_n) store_rows_staged<NR>(p, out_stage, tile, nrow, row0, nrows, v);
+  else store_rows_scalar<NR>(p, tile, nrow, row0, nrows, v);
+}
+
 template <int MP, int KIND>
 __global__ void __launch_bounds__(SmallMCfg<MP, KIND>::kThreads, 1)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
@@ -114,7 +217,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* pk_smem = smem + Cfg::kStages * Cfg::kStageBytes;                  // kind 3: packed ring (1024-aligned)
   uint8_t* sf_smem = pk_smem + Cfg::kPackedRing;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + Cfg::kSfBytes);
+  uint8_t* xs_tab = sf_smem + Cfg::kSfBytes;                                  // kind 2: [kb][MP] exponent bytes
+  uint8_t* out_stage = xs_tab + Cfg::kXsBytes;                                // epilogue staging tile (16-byte aligned)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + Cfg::kOutBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Cfg::kStages;
   uint64_t* tfull_bar = bars + 2 * Cfg::kStages;
@@ -123,11 +228,18 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   uint64_t* sf_empty = sf_full + kSmSfStages;
   uint64_t* pk_full = sf_empty + kSmSfStages;                                 // kind 3: packed tile landed / consumed
   uint64_t* pk_empty = pk_full + Cfg::kPackedSlots;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pk_empty + Cfg::kPackedSlots);
+  uint64_t* xs_ready = pk_empty + Cfg::kPackedSlots;                          // kind 2: exponent table filled
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xs_ready + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint32_t* last_flag = tmem_slot + 2;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long prof_t0 = prof_clock();
+  if (p.prof && threadIdx.x == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    p.prof[blockIdx.x * 16 + 14] = static_cast<long long>(gt);
+  }
   const int n_tiles = (p.N + 127) / 128;
   const int num_kb = (p.K + Cfg::kElems - 1) / Cfg::kElems;
   const long long U = static_cast<long long>(n_tiles) * num_kb, P = gridDim.x;
@@ -139,6 +251,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     for (int i = 0; i < Cfg::kPackedSlots; ++i) { mbar_init(&pk_full[i], 1); mbar_init(&pk_empty[i], 8); }
     for (int i = 0; i < Cfg::kAccStages; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 128); }
     for (int i = 0; i < kSmSfStages; ++i) { mbar_init(&sf_full[i], 1); mbar_init(&sf_empty[i], 1); }
+    mbar_init(xs_ready, 128);
     *abort_flag = 0;
     *last_flag = 0;
     mbar_fence_init();
@@ -168,7 +281,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
               if (++pslot == Cfg::kPackedSlots) { pslot = 0; pphase ^= 1; }
             }
           }
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          { const long long pt_ = prof_clock(); if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; } KSANA_PROF_ADD(0, pt_); }
           uint8_t* sw = smem + stage * Cfg::kStageBytes;
           if constexpr (KIND == 3) {
             mbar_expect_tx(&full_bar[stage], Cfg::kXBytes);
@@ -191,14 +304,14 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       int sfs = 0; uint32_t sf_phase = 0, set = 0;
       while (ok && next_segment(u, u_end, num_kb, sg)) {
         if (KIND != 1) {
-          if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+          { const long long pt_ = prof_clock(); if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; } KSANA_PROF_ADD(1, pt_); }
           tc_fence_after();
         }
         if constexpr (KIND == 2) {
           // groups of up to four K blocks share one pair of scale chunks (byte j of a chunk = block kb0 + 4g + j)
           const uint32_t d_tmem = tmem_base + acc * MP;
           for (int g0 = sg.kb0; g0 < sg.kb1 && ok; g0 += 4) {
-            if (!mbar_wait(&sf_full[sfs], sf_phase, abort_flag)) { ok = false; break; }
+            { const long long pt_ = prof_clock(); if (!mbar_wait(&sf_full[sfs], sf_phase, abort_flag)) { ok = false; break; } KSANA_PROF_ADD(2, pt_); }
             tc_fence_after();
             const uint32_t tsfa = tmem_base + Cfg::kSfBase + set * 8;
             const uint32_t tsfb = tsfa + 4;
@@ -206,7 +319,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
             tmem_cp_sf(tsfa, make_sf_desc(sf_addr));
             tmem_cp_sf(tsfb, make_sf_desc(sf_addr + 512));
             for (int j = 0; j < 4 && g0 + j < sg.kb1; ++j) {
-              if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+              { const long long pt_ = prof_clock(); if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; } KSANA_PROF_ADD(3, pt_); }
               tc_fence_after();
               const uint32_t sw = smem_u32(smem + stage * Cfg::kStageBytes);
               const uint64_t wdesc = make_smem_desc_sw128(sw);
@@ -385,55 +498,49 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
     // ------------------------------------------------------------ scale packer (kind 2 only)
     if constexpr (KIND == 2) {
-      // One group = up to four K blocks of one segment. The scales of the next group are fetched while the
-      // current one waits for its buffer, so the L2 latency of the loads stays off the packer's critical path.
-      struct GroupIter { long long u; Segment sg; int g0; bool valid; };
-      auto next_group = [&](GroupIter& it) {
-        if (it.valid && it.g0 + 4 < it.sg.kb1) { it.g0 += 4; return true; }
-        it.valid = next_segment(it.u, u_end, num_kb, it.sg);
-        it.g0 = it.sg.kb0;
-        return it.valid;
-      };
-      auto load_group = [&](const GroupIter& it, uint32_t (&w)[5]) {   // w[0]: weight chunk word, w[1..4]: token words
-        const float* ws = p.w_scale + static_cast<size_t>(it.sg.tile) * num_kb;
-        w[0] = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) w[0] |= (it.g0 + j < it.sg.kb1 ? ue8m0_of(ws[it.g0 + j]) : 127u) << (8 * j);
-#pragma unroll
-        for (int r4 = 0; r4 < 4; ++r4) {
-          const int tok = r4 * 32 + lane;
-          uint32_t word = 0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t e = 127u;
-            if (tok < p.M && it.g0 + j < it.sg.kb1)
-              e = ue8m0_of(p.a_scale[static_cast<size_t>(it.g0 + j) * p.a_scale_ld + tok]);
-            word |= e << (8 * j);
-          }
-          w[1 + r4] = word;
-        }
-      };
-      // Four groups per round (half of the buffers): their loads are all in flight together, so the packer exposes
-      // one L2 round trip per four groups, and the MMA issuer works through the other half meanwhile.
+      // One group = up to four K blocks of one segment; the MMA issuer copies a group's two 512-byte chunks (weight
+      // exponents, token exponents) into TMEM. Token exponents come from the shared-memory table the epilogue warps
+      // fill once per CTA; weight exponents are fetched 32 K blocks at a time (one float per lane), so in the
+      // steady state the packer waits for no global load. When K has more blocks than the table holds, the token
+      // exponents are read from global memory per group instead.
+      const bool tab = num_kb <= kSmXsKb;
       int sfs = 0; uint32_t sf_phase = 0;
-      GroupIter it{u_begin, Segment{0, 0, 0}, 0, false};
-      bool more = true, ok = true;
-      while (more && ok) {
-        uint32_t w[kSmSfBatch][5];
-        bool have[kSmSfBatch];
+      long long u = u_begin; Segment sg;
+      bool ok = true;
+      bool tab_ok = false;        // the first groups do not wait for the table: they read their scales themselves
+      while (ok && next_segment(u, u_end, num_kb, sg)) {
+        const float* ws = p.w_scale + static_cast<size_t>(sg.tile) * num_kb;
+        uint32_t wexp = 127u;                   // exponent of block (wbase + lane)
+        int wbase = -1000000;
+        for (int g0 = sg.kb0; g0 < sg.kb1 && ok; g0 += 4) {
+          if (tab && !tab_ok) tab_ok = mbar_test_wait(xs_ready, 0);
+          if (g0 + 4 > wbase + 32) {
+            wbase = g0;
+            wexp = (g0 + lane < sg.kb1) ? ue8m0_of(ws[g0 + lane]) : 127u;
+          }
+          uint32_t w0 = 0;
 #pragma unroll
-        for (int i = 0; i < kSmSfBatch; ++i) {
-          have[i] = more && next_group(it);
-          more = have[i];
-          if (have[i]) load_group(it, w[i]);
-        }
+          for (int j = 0; j < 4; ++j) w0 |= __shfl_sync(0xffffffffu, wexp, g0 - wbase + j) << (8 * j);
+          uint32_t w[4];
 #pragma unroll
-        for (int i = 0; i < kSmSfBatch; ++i) {
-          if (!have[i] || !ok) continue;
-          if (!mbar_wait(&sf_empty[sfs], sf_phase ^ 1, abort_flag)) { ok = false; continue; }
+          for (int r4 = 0; r4 < 4; ++r4) {
+            const int tok = r4 * 32 + lane;
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t e = 127u;
+              if (tok < MP && g0 + j < sg.kb1) {
+                if (tab_ok) e = xs_tab[(g0 + j) * MP + tok];
+                else if (tok < p.M) e = ue8m0_of(p.a_scale[static_cast<size_t>(g0 + j) * p.a_scale_ld + tok]);
+              }
+              word |= e << (8 * j);
+            }
+            w[r4] = word;
+          }
+          { const long long pt_ = prof_clock(); if (!mbar_wait(&sf_empty[sfs], sf_phase ^ 1, abort_flag)) { ok = false; break; } KSANA_PROF_ADD(4, pt_); }
           uint8_t* buf = sf_smem + sfs * 1024;
-          *reinterpret_cast<uint4*>(buf + lane * 16) = make_uint4(w[i][0], w[i][0], w[i][0], w[i][0]);
-          *reinterpret_cast<uint4*>(buf + 512 + lane * 16) = make_uint4(w[i][1], w[i][2], w[i][3], w[i][4]);
+          *reinterpret_cast<uint4*>(buf + lane * 16) = make_uint4(w0, w0, w0, w0);
+          *reinterpret_cast<uint4*>(buf + 512 + lane * 16) = make_uint4(w[0], w[1], w[2], w[3]);
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sf_full[sfs]);
@@ -448,14 +555,48 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     const int nrow = q * 32 + lane;          // output feature inside the tile
     int acc = 0; uint32_t acc_phase = 0;
     const int nkb_scale = (p.K + 127) / 128;
+    if constexpr (KIND == 2) {
+      // Exponent table for the scale packer: the K blocks this CTA's piece touches (all of them when the piece
+      // spans more than one tile), tokens past M get the neutral exponent. The weight ring fills meanwhile.
+      if (num_kb <= kSmXsKb) {
+        int lo = 0, hi = num_kb;
+        if (u_end > u_begin && u_begin / num_kb == (u_end - 1) / num_kb) {
+          lo = static_cast<int>(u_begin % num_kb);
+          hi = static_cast<int>((u_end - 1) % num_kb) + 1;
+        }
+        const int t = threadIdx.x - 64;                          // 0..127 over the four epilogue warps
+        constexpr int Q = MP / 4;                                 // four tokens (one 16-byte load) per table word
+        const bool vec = (reinterpret_cast<uintptr_t>(p.a_scale) & 15) == 0 && (p.a_scale_ld & 3) == 0;
+        uint32_t* tab32 = reinterpret_cast<uint32_t*>(xs_tab);
+#pragma unroll 4
+        for (int i = lo * Q + t; i < hi * Q; i += 128) {
+          const int kb = i / Q, tok = (i % Q) * 4;
+          const float* src = p.a_scale + static_cast<size_t>(kb) * p.a_scale_ld + tok;
+          float4 v = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (vec && tok + 3 < p.a_scale_ld) v = *reinterpret_cast<const float4*>(src);
+          else {
+            if (tok < p.M) v.x = src[0];
+            if (tok + 1 < p.M) v.y = src[1];
+            if (tok + 2 < p.M) v.z = src[2];
+            if (tok + 3 < p.M) v.w = src[3];
+          }
+          const uint32_t e0 = tok < p.M ? ue8m0_of(v.x) : 127u, e1 = tok + 1 < p.M ? ue8m0_of(v.y) : 127u;
+          const uint32_t e2 = tok + 2 < p.M ? ue8m0_of(v.z) : 127u, e3 = tok + 3 < p.M ? ue8m0_of(v.w) : 127u;
+          tab32[i] = e0 | (e1 << 8) | (e2 << 16) | (e3 << 24);
+        }
+        mbar_arrive(xs_ready);
+        if (threadIdx.x == 64) KSANA_PROF_ADD(6, prof_t0);
+      }
+    }
     long long u = u_begin; Segment sg; bool ok = true;
+    int pend_tile[2], pend_nseg[2], pend_my[2], npend = 0;      // a piece starts and ends with at most one cut tile each
     while (ok && next_segment(u, u_end, num_kb, sg)) {
       const int n = sg.tile * 128 + nrow;
       float accv[MP];
 #pragma unroll
       for (int i = 0; i < MP; ++i) accv[i] = 0.f;
       if (KIND != 1) {
-        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+        { const long long pt_ = prof_clock(); if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; } KSANA_PROF_ADD(5, pt_); }
         tc_fence_after();
         if constexpr (MP >= 32) {
 #pragma unroll
@@ -529,80 +670,99 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         if (!ok) break;
       }
 
-      auto finish = [&](const float (&v)[MP]) {
-        if (n >= p.N) return;
-        const float b = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
-        // eight tokens at a time: the residual loads of a batch are issued together before its stores (the output
-        // may alias the residual, so the compiler cannot move a load above an earlier store by itself)
-#pragma unroll
-        for (int m0 = 0; m0 < MP; m0 += 8) {
-          if (m0 >= p.M) break;
-          float o[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = m0 + i;
-            o[i] = v[m] + b;
-            if (p.residual && m < p.M) o[i] += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n]);
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = m0 + i;
-            if (m >= p.M) continue;
-            if (p.push_n) {
-              const __nv_bfloat16 ob = __float2bfloat16(o[i]);
-              for (int r = 0; r < p.push_n; ++r) p.push[r][static_cast<size_t>(m) * p.ldd + n] = ob;
-            } else if (p.out_f32) p.out_f32[static_cast<size_t>(m) * p.ldd + n] = o[i];
-            else p.D[static_cast<size_t>(m) * p.ldd + n] = __float2bfloat16(o[i]);
-          }
-        }
-      };
-
       if (sg.kb0 == 0 && sg.kb1 == num_kb) {
-        finish(accv);                        // this CTA covered the whole K range of the tile
+        const long long pt10 = prof_clock();
+        store_rows<MP>(p, out_stage, sg.tile, nrow, 0, p.M < MP ? p.M : MP, accv);   // the whole K range of the tile
+        if (threadIdx.x == 64) KSANA_PROF_ADD(10, pt10);
       } else {
+        // A tile cut across CTAs: this piece goes to the scratch slot of its position; the sum is taken after the
+        // last segment (below), when every CTA of the tile reduces its own share of the tokens.
         const long long t0 = static_cast<long long>(sg.tile) * num_kb;
         const int first = owner_of(t0, U, P), lastc = owner_of(t0 + num_kb - 1, U, P);
-        const int nseg = lastc - first + 1;
         const int my = static_cast<int>(blockIdx.x) - first;
-        float* tile_scratch = p.scratch + static_cast<size_t>(sg.tile) * p.seg_cap * MP * 128;
-        float* mine = tile_scratch + static_cast<size_t>(my) * MP * 128;
+        float* mine = p.scratch + (static_cast<size_t>(sg.tile) * p.seg_cap + my) * MP * 128;
+        const long long pt7 = prof_clock();
 #pragma unroll
         for (int m4 = 0; m4 < MP / 4; ++m4)       // [MP/4][128 features][4 tokens]: 16-byte stores, coalesced over lanes
           reinterpret_cast<float4*>(mine)[m4 * 128 + nrow] =
               make_float4(accv[4 * m4], accv[4 * m4 + 1], accv[4 * m4 + 2], accv[4 * m4 + 3]);
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          const unsigned int prev = atomicAdd(&p.counters[sg.tile], 1u);
-          const bool last = prev == static_cast<unsigned int>(nseg - 1);
-          if (last) p.counters[sg.tile] = 0;   // ready for the next launch
-          *last_flag = last ? 1u : 0u;
-          __threadfence();
+        if (threadIdx.x == 64) atomicAdd(&p.counters[sg.tile], 1u);
+        if (npend < 2) { pend_tile[npend] = sg.tile; pend_nseg[npend] = lastc - first + 1; pend_my[npend] = my; ++npend; }
+        if (threadIdx.x == 64) KSANA_PROF_ADD(7, pt7);
+      }
+    }
+
+    // ---- tiles cut across CTAs: every CTA of such a tile sums a share of the tokens over all pieces (fixed order,
+    // so the result does not depend on arrival order) once all pieces are written. The waits come after all of this
+    // CTA's own pieces are published, so no CTA's progress depends on another CTA's wait; all CTAs of the grid are
+    // resident together (one per SM), and the wait is bounded all the same.
+    for (int i = 0; i < npend && ok; ++i) {
+      const int tile = pend_tile[i], nseg = pend_nseg[i], my = pend_my[i];
+      const long long pt9 = prof_clock();
+      if (threadIdx.x == 64) {
+        int it = 0;
+        while (ld_acquire_gpu_u32(&p.counters[tile]) < static_cast<unsigned int>(nseg)) {
+          if (++it > (1 << 22) || *abort_flag) { *abort_flag = 1; break; }
+          __nanosleep(20);
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*last_flag) {
-          __threadfence();
-          float sum[MP];
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abort_flag) { ok = false; break; }
+      constexpr int G = MP / 4;                         // token groups of four (one 16-byte word of a partial tile)
+      constexpr int NG = G / 2;                         // a tile is cut at least in two: at most half the groups here
+      const int g0 = my * G / nseg, g1 = (my + 1) * G / nseg;
+      const int ng = g1 - g0;
+      const float4* base = reinterpret_cast<const float4*>(p.scratch + static_cast<size_t>(tile) * p.seg_cap * MP * 128);
+      float sum[4 * NG];
 #pragma unroll
-          for (int m = 0; m < MP; ++m) sum[m] = 0.f;
-          for (int sgi = 0; sgi < nseg; ++sgi) {       // fixed order: deterministic sums
-            // written by other SMs: read through L2 (ld.global.cg), never through this SM's L1
-            const float4* src = reinterpret_cast<const float4*>(tile_scratch + static_cast<size_t>(sgi) * MP * 128);
+      for (int r = 0; r < 4 * NG; ++r) sum[r] = 0.f;
+      // pieces in position order (the result does not depend on arrival order); the loads of up to eight pieces (few
+      // groups) or two pieces (many groups) are in flight together. Written by other SMs: read through L2.
+      auto add_pieces = [&](auto batch_tag) {
+        constexpr int SB = decltype(batch_tag)::value;
+        for (int s0 = 0; s0 < nseg; s0 += SB) {
+          float4 buf[SB][NG];
 #pragma unroll
-            for (int m4 = 0; m4 < MP / 4; ++m4) {
-              const float4 v = __ldcg(src + m4 * 128 + nrow);
-              sum[4 * m4] += v.x; sum[4 * m4 + 1] += v.y; sum[4 * m4 + 2] += v.z; sum[4 * m4 + 3] += v.w;
-            }
-          }
-          finish(sum);
+          for (int q = 0; q < SB; ++q)
+#pragma unroll
+            for (int gi = 0; gi < NG; ++gi)
+              if (s0 + q < nseg && gi < ng && (SB <= 2 || gi < 2))
+                buf[q][gi] = __ldcg(base + static_cast<size_t>(s0 + q) * (MP * 32) + (g0 + gi) * 128 + nrow);
+#pragma unroll
+          for (int q = 0; q < SB; ++q)
+#pragma unroll
+            for (int gi = 0; gi < NG; ++gi)
+              if (s0 + q < nseg && gi < ng && (SB <= 2 || gi < 2)) {
+                sum[4 * gi] += buf[q][gi].x; sum[4 * gi + 1] += buf[q][gi].y;
+                sum[4 * gi + 2] += buf[q][gi].z; sum[4 * gi + 3] += buf[q][gi].w;
+              }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is reused by the next segment
+      };
+      if (ng <= 2) add_pieces(std::integral_constant<int, 8>{});
+      else add_pieces(std::integral_constant<int, (NG >= 16 ? 1 : 2)>{});
+      int nrows = 4 * ng;
+      if (4 * g0 + nrows > p.M) nrows = p.M - 4 * g0;
+      store_rows<4 * NG>(p, out_stage, tile, nrow, 4 * g0, nrows, sum);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        // the last CTA to finish reading leaves both counters of the tile at zero for the next launch
+        const unsigned int prev = atomicAdd(&p.counters[n_tiles + tile], 1u);
+        if (prev == static_cast<unsigned int>(nseg - 1)) { p.counters[tile] = 0; p.counters[n_tiles + tile] = 0; }
+        KSANA_PROF_ADD(9, pt9);
       }
     }
   }
 
+  if (p.prof && lane == 0 && (warp <= 2 || warp == 6)) p.prof[blockIdx.x * 16 + (warp == 6 ? 8 : 11 + warp)] += prof_clock() - prof_t0;
   tc_fence_before();
   __syncthreads();
+  if (p.prof && threadIdx.x == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    p.prof[blockIdx.x * 16 + 15] = static_cast<long long>(gt);
+  }
   if (*abort_flag) {
     if (threadIdx.x == 0 && p.err) atomicExch(p.err, 2);
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -656,19 +816,30 @@ template <int MP, int KIND>
 static int launch_smallm(const CUtensorMap& mw, const CUtensorMap& mx, const SmallMParams& p, int ctas,
                          cudaStream_t st) {
   using Cfg = SmallMCfg<MP, KIND>;
-  static bool set = false;
-  if (!set) {
+  // the opt-in to large dynamic shared memory is a per-device attribute of the function
+  static std::atomic<bool> set[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -3;
+  if (!set[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(gemm_smallm_kernel<MP, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg::kSmemBytes) != cudaSuccess) return -3;
-    set = true;
+    set[dev].store(true, std::memory_order_release);
   }
   gemm_smallm_kernel<MP, KIND><<<ctas, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mw, mx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+static long long* g_smallm_prof = nullptr;
+
 }  // namespace ksana
 
 using namespace ksana;
+
+// Profiling aid: with a device buffer of 16 x 148 64-bit words set here, every launch adds per-CTA cycle counts to it
+// (waits of the producer / MMA / packer / epilogue roles, epilogue phases, role run times, start and end of the CTA
+// on the global timer). nullptr switches it off (the default).
+extern "C" void ksana_smallm_set_profile(void* buf) { g_smallm_prof = static_cast<long long*>(buf); }
 
 // Scratch needed: n_tiles * seg_cap * MP * 128 * 4 bytes (seg_cap = pieces a tile can be cut into);
 // counters: n_tiles words, zero before the first launch (the kernel leaves them zero).
@@ -683,6 +854,7 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
                        const void* w4_zs = nullptr, int w4_group = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (M > 128) return -20;
+  if (kind < 0 || kind > 3) return -10;
   const bool w4 = kind == 3;
   const int esz = (kind == 0 || w4) ? 2 : 1;
   if (w4) {
@@ -710,7 +882,7 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
     return static_cast<int>((num_kb + per - 1) / per + 1);
   };
   int seg_cap = seg_cap_for(P);
-  const bool can_split = scratch != nullptr && counters != nullptr && counters_len >= n_tiles;
+  const bool can_split = scratch != nullptr && counters != nullptr && counters_len >= 2 * n_tiles;
   while (P > 1 && (!can_split || static_cast<long long>(n_tiles) * seg_cap * MP * 128 * 4 > scratch_bytes)) {
     // fall back to whole tiles per CTA: pieces end on tile boundaries when P divides n_tiles evenly
     P = can_split ? P / 2 : 1;
@@ -732,6 +904,9 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
   p.a_scale = a_scale; p.a_scale_ld = a_scale_ld; p.w_scale = w_scale;
   p.seg_cap = seg_cap; p.scratch = static_cast<float*>(scratch); p.counters = static_cast<unsigned int*>(counters);
   p.err = err_flag;
+  p.vec_out = D != nullptr && (reinterpret_cast<uintptr_t>(D) & 15) == 0 && (ldd % 8) == 0 &&
+              (residual == nullptr || ((reinterpret_cast<uintptr_t>(residual) & 15) == 0 && (ldr % 8) == 0));
+  p.prof = g_smallm_prof;
   for (int i = 0; i < push_n && i < 8; ++i) p.push[i] = reinterpret_cast<__nv_bfloat16*>(push_ptrs[i]);
   p.push_n = push_n;
   if (w4) {
@@ -793,13 +968,14 @@ extern "C" int ksana_gemm_smallm_push(int kind, const void* X, int ldx, const fl
 #include <stdio.h>
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kKsanaNoAllocScratchBytes];
-static __device__ __align__(256) unsigned int g_noalloc_counters[kKsanaNoAllocMaxTiles];
+static __device__ __align__(256) unsigned int g_noalloc_counters[2 * kKsanaNoAllocMaxTiles];   // written + reduced, per tile
 
 namespace {
 constexpr int kMaxDevices = 64;
 void* g_noalloc_scratch_addr[kMaxDevices];      // device addresses, filled on first use per device
 void* g_noalloc_counter_addr[kMaxDevices];
-bool g_noalloc_ready[kMaxDevices];
+cudaError_t g_noalloc_setup_err[kMaxDevices];
+std::once_flag g_noalloc_once[kMaxDevices];
 thread_local char g_noalloc_msg[256] = "";
 }  // namespace
 
@@ -815,21 +991,28 @@ extern "C" int ksana_gemm_smallm_noalloc(int kind, const void* X, int ldx, const
     snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ksana_gemm_smallm_noalloc: cannot query the current device");
     return KSANA_NOALLOC_SETUP_FAILED;
   }
-  if (!g_noalloc_ready[dev]) {
-    // In host code the array names are host-side stand-ins, not device pointers: ask the runtime for the
-    // device addresses, with this device current, and check that it worked.
+  if (kind != 0 && kind != 1) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ksana_gemm_smallm_noalloc: kind %d is not served here (0: bf16, 1: e4m3 "
+             "with fp32 scales)", kind);
+    return KSANA_NOALLOC_BAD_ARGUMENT;
+  }
+  // In host code the array names are host-side stand-ins, not device pointers: ask the runtime for the device
+  // addresses, with this device current, exactly once per device (threads that arrive together wait for the one
+  // that does it), and keep the outcome.
+  std::call_once(g_noalloc_once[dev], [dev]() {
     void* s = nullptr;
     void* c = nullptr;
-    const cudaError_t e1 = cudaGetSymbolAddress(&s, g_noalloc_scratch);
-    const cudaError_t e2 = cudaGetSymbolAddress(&c, g_noalloc_counters);
-    if (e1 != cudaSuccess || e2 != cudaSuccess || s == nullptr || c == nullptr) {
-      snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ksana_gemm_smallm_noalloc: cudaGetSymbolAddress failed on device %d: %s",
-               dev, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
-      return KSANA_NOALLOC_SETUP_FAILED;
-    }
+    cudaError_t e = cudaGetSymbolAddress(&s, g_noalloc_scratch);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&c, g_noalloc_counters);
+    if (e == cudaSuccess && (s == nullptr || c == nullptr)) e = cudaErrorInvalidSymbol;
     g_noalloc_scratch_addr[dev] = s;
     g_noalloc_counter_addr[dev] = c;
-    g_noalloc_ready[dev] = true;
+    g_noalloc_setup_err[dev] = e;
+  });
+  if (g_noalloc_setup_err[dev] != cudaSuccess) {
+    snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ksana_gemm_smallm_noalloc: cudaGetSymbolAddress failed on device %d: %s",
+             dev, cudaGetErrorString(g_noalloc_setup_err[dev]));
+    return KSANA_NOALLOC_SETUP_FAILED;
   }
   if (M <= 0 || N <= 0 || K <= 0) return KSANA_NOALLOC_OK;
   const int n_tiles = (N + 127) / 128;
@@ -850,11 +1033,11 @@ extern "C" int ksana_gemm_smallm_noalloc(int kind, const void* X, int ldx, const
     return KSANA_NOALLOC_TOO_LARGE;
   }
   // Counters must start at zero; an earlier call that gave up half-way may have left some behind.
-  if (cudaMemsetAsync(g_noalloc_counter_addr[dev], 0, sizeof(unsigned int) * n_tiles, stream) != cudaSuccess) {
+  if (cudaMemsetAsync(g_noalloc_counter_addr[dev], 0, sizeof(unsigned int) * 2 * n_tiles, stream) != cudaSuccess) {
     snprintf(g_noalloc_msg, sizeof(g_noalloc_msg), "ksana_gemm_smallm_noalloc: clearing the tile counters failed");
     return KSANA_NOALLOC_SETUP_FAILED;
   }
   return smallm_impl(kind, X, ldx, a_scale, a_scale_ld, W, ldw, w_scale, D, nullptr, ldd, bias, residual, ldr, M, N, K,
                      0, g_noalloc_scratch_addr[dev], kKsanaNoAllocScratchBytes, g_noalloc_counter_addr[dev],
-                     kKsanaNoAllocMaxTiles, err_flag, stream, nullptr, 0);
+                     2 * kKsanaNoAllocMaxTiles, err_flag, stream, nullptr, 0);
 }

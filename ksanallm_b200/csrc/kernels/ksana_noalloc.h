@@ -19,8 +19,10 @@
 //     problems are rejected with KSANA_NOALLOC_TOO_LARGE and a message from
 //     ksana_noalloc_last_error(); nothing is launched.
 //   * First call on a device: resolves the device address of the built-in scratch with
-//     cudaGetSymbolAddress while that device is current (checked), once per device. Make this
-//     first call outside of any stream capture.
+//     cudaGetSymbolAddress while that device is current (checked), once per device; host threads
+//     that make their first call together are serialised on that step. Make this first call
+//     outside of any stream capture.
+//   * kind must be 0 or 1; anything else is rejected with KSANA_NOALLOC_BAD_ARGUMENT before any launch.
 //   * All calls on one device share the one scratch array, which keeps whatever the previous call
 //     left in it. The counters that must start at zero are cleared on the caller's stream before
 //     each launch. Two calls that overlap on the GPU (different streams without ordering) race on
@@ -33,7 +35,8 @@ extern "C" {
 #endif
 
 enum { kKsanaNoAllocScratchBytes = 8 << 20, kKsanaNoAllocMaxTiles = 1024 };
-enum { KSANA_NOALLOC_OK = 0, KSANA_NOALLOC_TOO_LARGE = -30, KSANA_NOALLOC_SETUP_FAILED = -31 };
+enum { KSANA_NOALLOC_OK = 0, KSANA_NOALLOC_TOO_LARGE = -30, KSANA_NOALLOC_SETUP_FAILED = -31,
+       KSANA_NOALLOC_BAD_ARGUMENT = -32 };
 
 // kind 0: X and W are bf16. kind 1: X and W are e4m3 with a_scale [K/128][a_scale_ld] and
 // w_scale [ceil(N/128)][K/128] (fp32). D is bf16 with row stride ldd. bias / residual may be null.

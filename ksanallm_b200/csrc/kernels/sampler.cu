@@ -54,6 +54,13 @@ struct SampleParams {
   int num_logprobs;                    // N (0 = none), same for the launch
   int* lp_ids; float* lp_vals;         // [B][N]
   int vocab;
+  // Vocabulary-sharded sampling (tensor parallel). Candidate mode (cand_val != null): nothing is drawn; the row's
+  // cand_k largest logits (sorted: value descending, index ascending) are written to cand_val / cand_idx
+  // [B][cand_k] with idx_offset added to the indices (this shard's first token id); short rows are padded with
+  // -inf. Merge mode (col_ids != null): `logits` rows are candidate lists gathered from all shards and
+  // col_ids [rows][col_ld] holds the token id of every column; drawn tokens and log-prob ids are mapped through it.
+  float* cand_val; int* cand_idx; int cand_k; int idx_offset;
+  const int* col_ids; long long col_ld;
 };
 
 __global__ void __launch_bounds__(kSampThreads)
@@ -66,10 +73,13 @@ sample_kernel(const SampleParams p) {
   __shared__ uint32_t sh_prefix, sh_remaining, sh_count, sh_ties;
 
   const int b = blockIdx.x;
-  const float* row = p.logits + static_cast<long long>(p.row_idx ? p.row_idx[b] : b) * p.ld;
+  const long long src_row = p.row_idx ? p.row_idx[b] : b;
+  const float* row = p.logits + src_row * p.ld;
+  const int* ids = p.col_ids ? p.col_ids + src_row * p.col_ld : nullptr;
   const int V = p.vocab;
-  const int k_req = max(1, min(p.top_k[b], kMaxK));
-  const int N = p.num_logprobs;
+  const bool cand_mode = p.cand_val != nullptr;
+  const int k_req = cand_mode ? max(1, min(p.cand_k, kMaxK)) : max(1, min(p.top_k[b], kMaxK));
+  const int N = cand_mode ? 0 : p.num_logprobs;
   const int tid = threadIdx.x;
 
   if (k_req == 1 && N == 0) {
@@ -95,7 +105,15 @@ sample_kernel(const SampleParams p) {
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
         if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
       }
-      if (tid == 0) p.out_tokens[b] = bi == 0x7fffffff ? 0 : bi;
+      if (tid == 0) {
+        if (cand_mode) {
+          p.cand_val[b] = bv;
+          p.cand_idx[b] = bi == 0x7fffffff ? 0x7fffffff : bi + p.idx_offset;
+        } else {
+          const int pick = bi == 0x7fffffff ? 0 : bi;
+          p.out_tokens[b] = ids ? ids[pick] : pick;
+        }
+      }
     }
     return;
   }
@@ -160,6 +178,14 @@ sample_kernel(const SampleParams p) {
       __syncthreads();
     }
   }
+  if (cand_mode) {
+    for (int i = tid; i < p.cand_k; i += kSampThreads) {
+      const bool has = i < K && cand_idx[i] != 0x7fffffff;
+      p.cand_val[static_cast<long long>(b) * p.cand_k + i] = has ? cand_val[i] : -INFINITY;
+      p.cand_idx[static_cast<long long>(b) * p.cand_k + i] = has ? cand_idx[i] + p.idx_offset : 0x7fffffff;
+    }
+    return;
+  }
   const float temp = p.temperature[b] > 0.f ? p.temperature[b] : 1.f;
   const float inv_t = 1.f / temp;
 
@@ -171,7 +197,7 @@ sample_kernel(const SampleParams p) {
     for (int i = 0; i < n; ++i) sum += __expf(cand_val[i] * inv_t - mx);
     const float lse = mx + __logf(sum);
     for (int i = 0; i < N; ++i) {
-      p.lp_ids[static_cast<long long>(b) * N + i] = i < n ? cand_idx[i] : -1;
+      p.lp_ids[static_cast<long long>(b) * N + i] = i < n ? (ids ? ids[cand_idx[i]] : cand_idx[i]) : -1;
       p.lp_vals[static_cast<long long>(b) * N + i] = i < n ? cand_val[i] * inv_t - lse : -INFINITY;
     }
   }
@@ -201,7 +227,7 @@ sample_kernel(const SampleParams p) {
         if (u < acc) { choice = cand_idx[i]; break; }
       }
     }
-    p.out_tokens[b] = choice;
+    p.out_tokens[b] = ids ? ids[choice] : choice;
   }
 }
 
@@ -241,7 +267,33 @@ extern "C" int ksana_sample(const float* logits, long long ld, const int* row_id
   if (B <= 0) return 0;
   if (num_logprobs > kMaxK) return -10;
   SampleParams p{logits, ld, row_idx, temperature, top_k, top_p, seeds, steps, out_tokens, num_logprobs, lp_ids,
-                 lp_vals, vocab};
+                 lp_vals, vocab, nullptr, nullptr, 0, 0, nullptr, 0};
+  sample_kernel<<<B, kSampThreads, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Sampling over candidate lists gathered from the vocabulary shards: logits [rows][ld] holds `ncols` candidate
+// values per row and col_ids [rows][col_ld] their token ids; everything else as ksana_sample.
+extern "C" int ksana_sample_merged(const float* logits, long long ld, const int* col_ids, long long col_ld,
+                                   const int* row_idx, const float* temperature, const int* top_k, const float* top_p,
+                                   const unsigned long long* seeds, const int* steps, int* out_tokens, int num_logprobs,
+                                   int* lp_ids, float* lp_vals, int B, int ncols, cudaStream_t st) {
+  if (B <= 0) return 0;
+  if (num_logprobs > kMaxK || !col_ids) return -10;
+  SampleParams p{logits, ld, row_idx, temperature, top_k, top_p, seeds, steps, out_tokens, num_logprobs, lp_ids,
+                 lp_vals, ncols, nullptr, nullptr, 0, 0, col_ids, col_ld};
+  sample_kernel<<<B, kSampThreads, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// This shard's k largest logits per row (value descending, index ascending) with their token ids
+// (column + idx_offset): cand_val / cand_idx [B][k]. k <= 1024.
+extern "C" int ksana_shard_topk(const float* logits, long long ld, const int* row_idx, int B, int vocab, int k,
+                                int idx_offset, float* cand_val, int* cand_idx, cudaStream_t st) {
+  if (B <= 0) return 0;
+  if (k < 1 || k > kMaxK || !cand_val || !cand_idx) return -10;
+  SampleParams p{logits, ld, row_idx, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, vocab,
+                 cand_val, cand_idx, k, idx_offset, nullptr, 0};
   sample_kernel<<<B, kSampThreads, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -45,7 +45,17 @@ class StepInput:
     refit_embeddings: Optional[torch.Tensor] = None     # [R, hidden] fp32
     decode_splits: int = 1
     decode_workspace: Optional[tuple] = None
+    sample_k: int = 0                    # > 0: tensor-parallel ranks return merged per-shard top-k candidates, not logits
     want_hidden: bool = False            # keep final hidden states / post-norm states for /forward
+
+
+@dataclass
+class LogitCandidates:
+    """What a tensor-parallel forward returns instead of whole logits rows when the step's sampling only needs the k
+    largest logits of every row: each vocabulary shard's top k, gathered from all ranks. values [rows, tp * k] fp32,
+    ids [rows, tp * k] int32 (token ids; padding columns carry -inf / 0x7fffffff)."""
+    values: torch.Tensor
+    ids: torch.Tensor
 
 
 @dataclass
@@ -218,6 +228,32 @@ class CommonModel:
             logits = self.comm.all_gather_last_dim(logits, valid=self.vocab_shard)
         return logits[:, : self.cfg.vocab_size] if logits.shape[1] != self.cfg.vocab_size else logits
 
+    def compute_candidates(self, normed: torch.Tensor, k: int):
+        """Vocabulary-sharded sampling: the lm_head shard's logits stay on this rank; only each row's k largest
+        (value, token id) pairs cross NVLink, k x 8 bytes per row and rank instead of the row's whole fp32 shard
+        (the reference gathers the shards in full: src/ksana_llm/models/common/common_model.cpp:905-980). Every
+        sampling choice the engine offers - greedy, top-k, top-p within the top k, top-N log-probs - depends on the
+        k largest logits only, and the global top k is contained in the union of the shards' top k, so the merged
+        lists give exactly the tokens the full rows would. Returns None when the lists do not fit the exchange area."""
+        symm = getattr(self.comm, "symm", None) if self.comm is not None else None
+        B = normed.shape[0]
+        stage = symm.candidate_stage(B, k) if (symm is not None and normed.is_cuda) else None
+        if stage is None:
+            return None
+        logits = ops.linear(normed, self.lm_head, out_f32=True)
+        lo = self.tp_rank * self.vocab_shard
+        valid = max(0, min(self.vocab_shard, self.cfg.vocab_size - lo))
+        ops.native.shard_topk(logits, valid, k, lo, stage[0], stage[1])
+        vals, ids = symm.gather_candidates(B, k)
+        return LogitCandidates(vals, ids)
+
+    def logits_or_candidates(self, hn: torch.Tensor, step: StepInput):
+        if step.sample_k > 0 and self.tp_size > 1:
+            cand = self.compute_candidates(hn, step.sample_k)
+            if cand is not None:
+                return cand
+        return self.compute_logits(hn)
+
     def lm_head_forward(self, h: torch.Tensor, step: StepInput) -> torch.Tensor:
         """final norm -> rows that need logits -> lm_head. With ``want_hidden`` the hidden states of every
         row (before and after the final norm) are kept for /forward request targets."""
@@ -230,7 +266,7 @@ class CommonModel:
             if rows is not None:
                 h = ops.gather_rows(h, rows)
             hn = self._final_norm(h)
-        return self.compute_logits(hn)
+        return self.logits_or_candidates(hn, step)
 
     def rerotate_blocks(self, triples) -> None:
         """Flexible-cache copies land at another position: rotate the copied K by the position delta
@@ -293,12 +329,11 @@ class CommonModel:
         """Row-parallel GEMMs push their partial tiles into peer memory from the epilogue; one kernel then
         reduces, adds the residual and applies the following norm (and FP8 quantisation), so a layer has
         no stand-alone all-reduce, add or norm launches."""
-        from ..parallel.symm import ONE_SHOT_ROWS
         cfg, symm = self.cfg, self.comm.symm
         ln = cfg.norm_type == "layernorm"
         symm.begin_forward()
         T = h0.shape[0]
-        if T > ONE_SHOT_ROWS:
+        if not symm.one_shot(T):
             h = symm.h[:T]
             h.copy_(h0)
         else:
@@ -329,7 +364,7 @@ class CommonModel:
         if step.want_hidden:
             self.step_hidden, self.step_normed = h, x
         hn = ops.gather_rows(x, step.logits_rows) if step.logits_rows is not None else x
-        return self.compute_logits(hn)
+        return self.logits_or_candidates(hn, step)
 
     # ------------------------------------------------------------------ misc
     embed_sharded = False

@@ -3,7 +3,7 @@
 The kernels trust the step metadata (block tables, cache slots, token ids, row indices). With
 ``KSANA_CHECK_INPUTS=1`` the runner validates it on the host before every forward pass and raises with the first
 violation, so that a scheduler or plug-in bug surfaces as a Python exception instead of an out-of-range device
-access. (``compute-sanitizer`` cannot be used on the shared GPUs; this is the bounds-check mode of the engine.)
+access. This is the engine's own bounds-check mode, for runs where no device-side sanitizer is at hand.
 The checks synchronise with the device and are meant for tests and debugging, not for serving.
 """
 from __future__ import annotations

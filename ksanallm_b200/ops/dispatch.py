@@ -236,10 +236,24 @@ def rope_kv_append(qkv, positions, slots, cos_sin, cache_layer, block_tokens, Hq
                            mrope_sections, k_scale, v_scale, apply_rope)
 
 
-def decode_splits(batch: int, hkv: int, max_kv_len: int, sms: int = 148) -> int:
-    """Split-KV factor: enough CTAs for two waves, at least two 64-token tiles per split."""
-    want = math.ceil(2 * sms / max(1, batch * hkv))
-    return max(1, min(want, 32, max(1, max_kv_len // 128)))
+def decode_splits(batch: int, hkv: int, max_kv_len: int, sms: int = 148, ctas_per_sm: int = 2) -> int:
+    """Split-KV factor of the decode attention kernel. One CTA serves one (sequence, kv head, split) and two CTAs
+    fit an SM (shared memory), so the time is about waves x (64-token tiles per split + a fixed set-up cost of about
+    two tiles); the factor minimising that is chosen, with at least two tiles per split."""
+    import os
+    forced = int(os.environ.get("KSANA_DECODE_SPLITS", "0"))
+    tiles = max(1, (max_kv_len + 63) // 64)
+    most = max(1, min(32, tiles // 2))
+    if forced > 0:
+        return min(forced, most)
+    slots = sms * ctas_per_sm
+    best, best_cost = 1, None
+    for n in range(1, most + 1):
+        waves = (batch * hkv * n + slots - 1) // slots
+        cost = waves * ((tiles + n - 1) // n + 2)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = n, cost
+    return best
 
 
 def paged_attention(qkv, out, cache_layer, block_tokens, block_table, cu_q, kv_lens, num_multi, num_single,

@@ -41,7 +41,7 @@ _SIGS = {
     "ksana_gemm_fp8_block_push": [vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_gemm_bf16_push": [vp, i32, vp, i32, i32, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_reduce_norm": [vp, vp, i32, i32, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp, f32, i32, vp, vp, vp, i32, i32,
-                          i64, i64, i64, i64, vp, vp],
+                          i64, i64, i64, i64, C.c_ulonglong, vp, vp],
     "ksana_comm_barrier": [vp, vp, i32, i32, vp, vp, vp],
     "ksana_allreduce_pull": [vp, vp, i32, i32, vp, i64, vp, vp, i64, vp, vp],
     "ksana_allreduce_nvls": [vp, vp, i32, i32, vp, C.c_ulonglong, i64, vp, vp, i64, vp, vp],
@@ -54,8 +54,8 @@ _SIGS = {
     "ksana_refit_rows": [vp, vp, vp, i32, i32, vp],
     "ksana_rope_kv_append": [vp, vp, i32, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32,
                              i32, vp],
-    "ksana_copy_blocks": [vp, vp, i32, i64, vp],
-    "ksana_swap_blocks": [vp, vp, vp, i32, i64, i32, vp],
+    "ksana_copy_blocks": [vp, vp, i32, i64, i32, vp, vp],
+    "ksana_swap_blocks": [vp, vp, vp, i32, i64, i32, i32, i32, vp, vp],
     "ksana_add": [vp, vp, vp, vp, i64, i32, vp],
     "ksana_cast_f32": [vp, vp, i64, vp],
     "ksana_paged_prefill_tc": [vp, i64, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i64,
@@ -70,6 +70,8 @@ _SIGS = {
     "ksana_w4_gemv": [vp, i64, vp, vp, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, vp],
     "ksana_w4_dequant": [vp, vp, vp, vp, i64, i32, i32, i32, vp],
     "ksana_sample": [vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, vp],
+    "ksana_sample_merged": [vp, i64, vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i32, i32, vp],
+    "ksana_shard_topk": [vp, i64, vp, i32, i32, i32, i32, vp, vp, vp],
     "ksana_repetition_penalty": [vp, i64, vp, vp, vp, vp, i32, i32, vp],
     "ksana_ban_tokens": [vp, i64, vp, vp, vp, i32, i32, vp],
 }
@@ -86,7 +88,51 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
+_recorder = None
+
+
+class _RecordingLib:
+    """Stand-in for the library handle while a launch recorder is installed: every entry point called through it
+    is appended to the recorder as (name, function, arguments) before it runs."""
+
+    def __init__(self, real, rec):
+        self._real, self._rec = real, rec
+
+    def __getattr__(self, name):
+        fn = getattr(self._real, name)
+        rec = self._rec
+
+        def call(*args):
+            rec.append((name, fn, args))
+            return fn(*args)
+        return call
+
+
+class recording:
+    """Context manager: collects every native launch issued inside it into ``calls`` (used by the step breakdown
+    in benchmarks/step_breakdown.py, which replays subsets of a step's launches in graphs of their own)."""
+
+    def __init__(self, calls: list):
+        self.calls = calls
+
+    def __enter__(self):
+        global _recorder
+        _recorder = self.calls
+        return self.calls
+
+    def __exit__(self, *exc):
+        global _recorder
+        _recorder = None
+        return False
+
+
 def lib():
+    if _recorder is not None:
+        return _RecordingLib(_load(), _recorder)
+    return _load()
+
+
+def _load():
     global _LIB
     if _LIB is None:
         if not _LIB_PATH.exists():
@@ -122,28 +168,41 @@ _err_flags = {}
 
 def err_flag(device) -> torch.Tensor:
     """Per-device int32 word that kernels with bounded waits set when a wait gave up."""
-    key = torch.device(device).index or 0
+    d = torch.device(device)
+    key = (d.type, d.index or 0)
     if key not in _err_flags:
         _err_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _err_flags[key]
 
 
+def describe_err_code(code: int) -> str:
+    if code >= 1000000:
+        names = {11: "block-table entry", 12: "sequence row range", 13: "position", 14: "cache slot", 15: "expert id",
+                 16: "expert destination row", 17: "gather row index"}
+        return (f"a kernel skipped an out-of-range {names.get(code // 1000000, 'index')} "
+                f"(value mod 1e6 = {code % 1000000}); the step's results are invalid")
+    what = {2: "a tensor-core GEMM gave up waiting for its operands", 3: "a wait for a peer GPU's flag ran out",
+            4: "an attention kernel gave up waiting for its K/V tiles"}.get(code, "a device-side bounded wait timed out")
+    return f"{what} (kernel reported error status {code})"
+
+
+def clear_err_flag(device) -> None:
+    with torch.inference_mode():              # the word may have been created inside the engine's inference mode
+        err_flag(device).zero_()
+
+
 def check_err_flag(device) -> None:
-    flag = err_flag(device)
-    code = int(flag.item())
+    """Reads the device error word (synchronises the stream); raises and clears it when a kernel reported."""
+    code = int(err_flag(device).item())
     if code != 0:
-        with torch.inference_mode():          # the word may have been created inside the engine's inference mode
-            flag.zero_()
-        if code >= 1000000:
-            names = {11: "block-table entry", 12: "sequence row range", 13: "position", 14: "cache slot", 15: "expert id",
-                     16: "expert destination row", 17: "gather row index"}
-            raise RuntimeError(f"a kernel skipped an out-of-range {names.get(code // 1000000, 'index')} "
-                               f"(value mod 1e6 = {code % 1000000}); the step's results are invalid")
-        raise RuntimeError(f"a device-side bounded wait timed out (kernel reported error status {code})")
+        clear_err_flag(device)
+        raise RuntimeError(describe_err_code(code))
 
 
 # ------------------------------------------------------------------------------------- GEMM
-SMALL_M_FP8 = 32                   # FP8: per-k-block promotion costs grow with the row count (measured crossover)
+import os as _os
+
+SMALL_M_FP8 = int(_os.environ.get("KSANA_SKINNY_MAX_M", "32"))   # FP8: rows up to which the skinny stream-K kernel always runs
 SMALL_M_BF16 = 128                 # bf16: no per-K-block promotion, the skinny kernel wins up to a full token tile
 _SCRATCH_BYTES = 64 << 20
 _COUNTERS = 4096
@@ -593,12 +652,19 @@ def mla_attention(qfull, out, cache_layer, block_stride, block_tokens, block_tab
 
 
 def copy_blocks(cache, pairs, block_bytes):
-    _check(lib().ksana_copy_blocks(_p(cache), _p(pairs), pairs.numel() // 2, block_bytes, _st()), "ksana_copy_blocks")
+    """pairs: int32 [n, 2] (source block, destination block) on the device; ids outside the cache are skipped and
+    recorded in the error word."""
+    _check(lib().ksana_copy_blocks(_p(cache), _p(pairs), pairs.numel() // 2, block_bytes, int(cache.shape[0]),
+                                   _p(err_flag(cache.device)), _st()), "ksana_copy_blocks")
 
 
-def swap_blocks(cache, stage, ids, block_bytes, to_host: bool):
-    _check(lib().ksana_swap_blocks(_p(cache), _p(stage), _p(ids), ids.numel(), block_bytes, 0 if to_host else 1, _st()),
-           "ksana_swap_blocks")
+def swap_blocks(cache, host_pool, pairs, block_bytes, to_host: bool):
+    """Whole cache blocks between the device cache and the pinned host block pool, one launch per list. ``pairs``:
+    int32 [n, 2] (device block, host block) on the device; ``host_pool``: pinned uint8 [host_blocks, block_bytes]
+    (the kernel reads / writes it over PCIe, no staging copy). Bad ids are skipped and recorded in the error word."""
+    _check(lib().ksana_swap_blocks(_p(cache), host_pool.data_ptr(), _p(pairs), pairs.numel() // 2, block_bytes,
+                                   0 if to_host else 1, int(cache.shape[0]), int(host_pool.shape[0]),
+                                   _p(err_flag(cache.device)), _st()), "ksana_swap_blocks")
 
 
 # ----------------------------------------------------------------------------------- sampler
@@ -609,6 +675,26 @@ def sample(logits, temperature, top_k, top_p, seeds, steps, out_tokens, row_idx=
                             _p(seeds), _p(steps), _p(out_tokens), num_logprobs, _p(lp_ids), _p(lp_vals), B,
                             logits.shape[1], _st())
     _check(rc, "ksana_sample")
+
+
+def sample_merged(cand_vals, cand_ids, temperature, top_k, top_p, seeds, steps, out_tokens, num_logprobs=0, lp_ids=None,
+                  lp_vals=None):
+    """The sampler over candidate lists gathered from the vocabulary shards: cand_vals [B, C] fp32 logits and
+    cand_ids [B, C] int32 token ids of the same columns."""
+    B = out_tokens.numel()
+    rc = lib().ksana_sample_merged(_p(cand_vals), cand_vals.stride(0), _p(cand_ids), cand_ids.stride(0), None,
+                                   _p(temperature), _p(top_k), _p(top_p), _p(seeds), _p(steps), _p(out_tokens),
+                                   num_logprobs, _p(lp_ids), _p(lp_vals), B, cand_vals.shape[1], _st())
+    _check(rc, "ksana_sample_merged")
+
+
+def shard_topk(logits, vocab, k, idx_offset, out_vals, out_ids):
+    """This vocabulary shard's k largest logits per row and their token ids (column + idx_offset):
+    out_vals fp32 [B, k], out_ids int32 [B, k], sorted by value (descending) then id."""
+    B = logits.shape[0]
+    rc = lib().ksana_shard_topk(_p(logits), logits.stride(0), None, B, vocab, k, idx_offset, _p(out_vals), _p(out_ids),
+                                _st())
+    _check(rc, "ksana_shard_topk")
 
 
 def repetition_penalty(logits, offsets, ids, penalty, row_idx=None):

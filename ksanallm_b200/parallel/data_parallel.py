@@ -68,7 +68,7 @@ class AttentionDP:
             num_multi=nm, num_single=len(mine) - nm, num_tokens=int(len(rows)), num_multi_tokens=int(ql[:nm].sum()),
             max_q_len=int(ql.max()) if len(ql) else 0,
             swap_out=self._mine(plan.swap_out, 2, (0,)), swap_in=self._mine(plan.swap_in, 2, (0,)),
-            copies=self._mine(plan.copies, 3, (0, 1)))
+            copies=self._mine(plan.copies, 3, (0, 1)), pre_copies=self._mine(getattr(plan, "pre_copies", ()), 3, (0, 1)))
         self._sample_owner = sample_owner
         self._sample_counts = [int((sample_owner == r).sum()) for r in range(self.size)]
         return sub

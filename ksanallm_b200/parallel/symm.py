@@ -34,7 +34,11 @@ from ..ops import native
 from ..ops.dispatch import LinearWeight, QTensor, linear, quantize
 
 FLAG_BYTES = 4096
-ONE_SHOT_ROWS = 64             # up to this many rows every rank reduces all rows itself (one flag exchange)
+ONE_SHOT_ROWS = 64             # at most this many rows are reduced by every rank itself (one flag exchange) ...
+ONE_SHOT_PULL_BYTES = 1 << 20  # ... and only while a rank then pulls no more than this from its peers: beyond it the
+                               # rows are split over the ranks (reduce-scatter, norm, all-gather), which moves
+                               # 2/size of the bytes at the price of a second flag exchange
+CAND_MAX_K = 64                # sampling candidates exchanged per row and shard at most (beyond: whole shards)
 PUSH_EPILOGUE = False          # large batches: reduce-scatter by GEMM-epilogue pushes instead of owner pulls
 
 
@@ -61,6 +65,11 @@ class SymmetricComm:
         self.stage_off = off
         self.stage_bytes = _align(max_tokens * hidden * 2)
         off += self.stage_bytes
+        # sampling candidates of the vocabulary shards (values and token ids, fp32 / int32 words): a region of its
+        # own, so that nothing else ever writes it between a step's exchange and the next step's
+        self.cand_off = off
+        self.cand_words = 2 * min(max_tokens, 1024) * CAND_MAX_K
+        off += _align(self.cand_words * 4)
         self.total = off
         self.buf = symm_mem.empty(self.total, dtype=torch.uint8, device=self.device)
         self.buf.zero_()
@@ -71,7 +80,10 @@ class SymmetricComm:
         self.flag_ptrs = (C.c_ulonglong * 8)(*(ptrs + [0] * (8 - size)))       # flags live at offset 0
         # NVLS: multicast address of the buffer when the platform bound one (in-switch reductions); opt-in
         self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
-        self.use_nvls = bool(self.mc_ptr) and os.environ.get("KSANA_NVLS", "0") == "1"
+        # in-switch reduction / replication pays from four ranks on (with two there is nothing to save); KSANA_NVLS=0 / 1
+        # overrides
+        want = os.environ.get("KSANA_NVLS")
+        self.use_nvls = bool(self.mc_ptr) and (want == "1" or (want is None and size >= 4))
         self.ctrs = torch.zeros(16, dtype=torch.int32, device=self.device)
         self.parity = 0
         dist.barrier(group)
@@ -81,6 +93,14 @@ class SymmetricComm:
         self.yq = self._view(self.yq_off, (max_tokens, hidden), torch.float8_e4m3fn)
         self.ys = self._view(self.ys_off, (hidden // 128 + 1, self.scale_ld), torch.float32)
         self.stage = self._view(self.stage_off, (self.stage_bytes // 2,), torch.bfloat16)
+
+    def one_shot(self, M: int) -> bool:
+        """Whether a row-parallel result of M rows is reduced by every rank itself (all rows pulled from every peer)
+        instead of reduce-scatter + all-gather."""
+        forced = os.environ.get("KSANA_ONE_SHOT_ROWS")
+        if forced is not None:
+            return M <= int(forced)
+        return M <= ONE_SHOT_ROWS and M * (self.size - 1) * self.hidden * 2 <= ONE_SHOT_PULL_BYTES
 
     def _view(self, off: int, shape, dtype):
         n = 1
@@ -137,6 +157,26 @@ class SymmetricComm:
         self.barrier()          # peers are done reading the stage before it is written again
         return out
 
+    def candidate_stage(self, B: int, k: int):
+        """Where this rank writes its shard's sampling candidates: (values fp32 [B, k], token ids int32 [B, k]),
+        views of the symmetric buffer. None if B x k does not fit the region."""
+        if 2 * B * k > self.cand_words or k > CAND_MAX_K:
+            return None
+        words = self.buf[self.cand_off: self.cand_off + 2 * B * k * 4]
+        return words[: B * k * 4].view(torch.float32).view(B, k), words[B * k * 4:].view(torch.int32).view(B, k)
+
+    def gather_candidates(self, B: int, k: int):
+        """Collective: every rank's staged candidates -> (values [B, size * k], token ids [B, size * k]) on every rank,
+        rank r's candidates in columns [r * k, (r + 1) * k). One pull kernel (its flag exchange makes the peers'
+        staged rows visible); the region is written once per forward pass, and the flag exchanges of the next pass's
+        layers lie between two uses, so no trailing barrier is needed."""
+        out = torch.empty(2 * B, self.size * k, dtype=torch.float32, device=self.device)
+        rc = native.lib().ksana_allgather_pull(self.data_ptrs, self.flag_ptrs, self.rank, self.size,
+                                               self.ctrs.data_ptr(), self.cand_off, out.data_ptr(), 2 * B, k, k,
+                                               self.size * k, native.err_flag(self.device).data_ptr(), native._st())
+        native._check(rc, "ksana_allgather_pull")
+        return out[:B], out[B:].view(torch.int32)
+
     def all_gather_rows(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """[rows, H] bf16 (the same ``rows`` on every rank) -> [size * rows, H]: rank r's rows at r * rows, pulled
         from the peers' staging areas (raw 32-bit copies). None if it does not fit the staging area."""
@@ -171,7 +211,8 @@ class SymmetricComm:
         rc = native.lib().ksana_reduce_norm(self.data_ptrs, self.flag_ptrs, self.rank, self.size, self.ctrs.data_ptr(),
                                             self.slots_off[parity], self.slot_bytes, row_begin, n, M, H, h_base or None,
                                             None, None, 0.0, 0, None, None, None, 0, 4, self.h_off, self.y_off,
-                                            self.yq_off, self.ys_off, native.err_flag(self.device).data_ptr(), native._st())
+                                            self.yq_off, self.ys_off, self.mc_ptr if self.use_nvls else 0,
+                                            native.err_flag(self.device).data_ptr(), native._st())
         native._check(rc, "ksana_reduce_norm")
         return True
 
@@ -212,7 +253,7 @@ class SymmetricComm:
         lib = native.lib()
         if writer is None and W.fp8 and not isinstance(x, QTensor):
             x = quantize(x)
-        one_shot = M <= ONE_SHOT_ROWS
+        one_shot = self.one_shot(M)
         rows_per = M if one_shot else (M + self.size - 1) // self.size
         bias = W.bias.data_ptr() if (writer is None and W.bias is not None and self.rank == 0) else None
         if writer is not None:
@@ -271,7 +312,7 @@ class SymmetricComm:
                                    norm_b.data_ptr() if norm_b is not None else None, float(eps), int(layernorm),
                                    y.data_ptr() if y is not None else None, yq.data_ptr() if yq is not None else None,
                                    ys.data_ptr() if ys is not None else None, scale_ld, gather, self.h_off, self.y_off,
-                                   self.yq_off, self.ys_off, err, st)
+                                   self.yq_off, self.ys_off, self.mc_ptr if self.use_nvls else 0, err, st)
         native._check(rc, "ksana_reduce_norm")
         if norm_w is None:
             return h, None

@@ -21,12 +21,12 @@ import numpy as np
 import torch
 
 from ..config import EngineConfig, ModelConfig
-from ..models.common import StepInput
+from ..models.common import LogitCandidates, StepInput
 from ..ops import dispatch as ops
 from ..ops import checks as _checks
 from ..ops import native
 from ..utils import native_engine as ne
-from .sampler import Sampler, SamplingParams
+from .sampler import DeviceStepError, Sampler, SamplingParams
 from .structured import StructuredOutput
 
 
@@ -82,64 +82,102 @@ class ModelRunner:
         if num_host_blocks > 0:
             self.host_cache = torch.zeros(num_host_blocks, self.block_bytes, dtype=torch.uint8,
                                           pin_memory=self.cuda)
-        self._pinned = None
-        self._pinned_cap = 0
+        self._ring: list = []
+        self._ring_pos = 0
+        self._swap_stream = None
+        self.exchange_candidates = os.environ.get("KSANA_SHARD_SAMPLING", "1") != "0"
         self.pipeline = None             # parallel.pipeline.PipelineRunner when the job has several stages
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
-    def _stage(self, arr: np.ndarray) -> torch.Tensor:
-        """One pinned staging buffer -> one H2D copy."""
+    STAGE_RING = 4
+
+    def _stage_buffer(self, n: int):
+        """Next pinned staging buffer of the ring with room for ``n`` int32 words. A buffer is rewritten only after
+        the copy that last read it has completed (its event), so several asynchronous uploads of one step - block
+        lists, the step image, sampler parameters - never share host memory that a DMA may still be reading."""
+        ring = self._ring
+        if not ring:
+            ring.extend([None, 0, None] for _ in range(self.STAGE_RING))        # [buffer, capacity, event]
+        self._ring_pos = (self._ring_pos + 1) % self.STAGE_RING
+        slot = ring[self._ring_pos]
+        if slot[2] is not None:
+            slot[2].synchronize()
+        if n > slot[1]:
+            slot[1] = max(n * 2, 1 << 16)
+            slot[0] = torch.empty(slot[1], dtype=torch.int32, pin_memory=True)
+            slot[2] = torch.cuda.Event()
+        return slot
+
+    def _stage(self, arr: np.ndarray, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """int32 host array -> device through a pinned staging buffer, one asynchronous H2D copy. ``out``: device
+        tensor to fill (CUDA-graph inputs); otherwise a new device tensor is returned."""
         n = int(arr.size)
         if not self.cuda:
             return torch.from_numpy(arr.copy())
-        if n > self._pinned_cap:
-            self._pinned_cap = max(n * 2, 1 << 16)
-            self._pinned = torch.empty(self._pinned_cap, dtype=torch.int32, pin_memory=True)
-        self._pinned[:n].copy_(torch.from_numpy(arr))
+        slot = self._stage_buffer(n)
+        host = slot[0][:n]
+        host.numpy()[:] = arr.reshape(-1)
         self.h2d_bytes += n * 4
-        return self._pinned[:n].to(self.device, non_blocking=True)
+        if out is None:
+            out = host.to(self.device, non_blocking=True)
+        else:
+            out.copy_(host, non_blocking=True)
+        slot[2].record()
+        return out
 
     def apply_block_ops(self, plan) -> None:
-        """Swap-outs, swap-ins and block copies decided by the scheduler, in that order, on the compute stream."""
-        so, si, cp = plan.swap_out, plan.swap_in, plan.copies
+        """Block copies of forks decided after the previous step, then swap-outs, swap-ins and the copies decided by
+        this plan, in that order. On a GPU the four lists travel in one staged upload; a swap is one kernel per
+        direction that moves the blocks between the cache and the pinned host pool over PCIe (no staging copy, no
+        host synchronisation), issued on a side stream that the compute stream joins before the forward."""
+        pre = np.asarray(getattr(plan, "pre_copies", ()), dtype=np.int32)
+        so, si, cp = np.asarray(plan.swap_out, dtype=np.int32), np.asarray(plan.swap_in, dtype=np.int32), \
+            np.asarray(plan.copies, dtype=np.int32)
+        if not (pre.size or so.size or si.size or cp.size):
+            return
         cache = self.model.kv_cache
         flat = cache.view(cache.shape[0], -1)
-        if so.size:
-            pairs = so.reshape(-1, 2)
-            self._swap(flat, pairs, to_host=True)
-        if si.size:
-            pairs = si.reshape(-1, 2)
-            self._swap(flat, pairs, to_host=False)
-        if cp.size:
-            triples = cp.reshape(-1, 3)
-            if self.cuda:
-                t = self._stage(np.ascontiguousarray(triples[:, :2]).reshape(-1).astype(np.int32))
-                native.copy_blocks(cache, t, self.block_bytes)
-            else:
-                for s, d, _ in triples:
-                    flat[int(d)].copy_(flat[int(s)])
-            if (triples[:, 2] != 0).any():
-                self.model.rerotate_blocks(triples)
-
-    def _swap(self, flat, pairs, to_host: bool):
-        if self.host_cache is None:
+        if (so.size or si.size) and self.host_cache is None:
             raise RuntimeError("swap requested without a host block pool")
-        dev_ids = pairs[:, 0].astype(np.int64)
-        host_ids = pairs[:, 1].astype(np.int64)
-        raw = flat.view(torch.uint8) if flat.dtype != torch.uint8 else flat
+        pre3, cp3 = pre.reshape(-1, 3), cp.reshape(-1, 3)
         if self.cuda:
-            # pinned host blocks are written / read by the copy engine in one batched index copy per direction
-            if to_host:
-                gathered = raw[torch.from_numpy(dev_ids).to(self.device)]
-                self.host_cache[torch.from_numpy(host_ids)] = gathered.cpu()
-            else:
-                raw[torch.from_numpy(dev_ids).to(self.device)] = self.host_cache[torch.from_numpy(host_ids)].to(self.device, non_blocking=True)
+            pre2 = np.ascontiguousarray(pre3[:, :2]).reshape(-1)
+            cp2 = np.ascontiguousarray(cp3[:, :2]).reshape(-1)
+            dev = self._stage(np.concatenate([pre2, so.reshape(-1), si.reshape(-1), cp2]))
+            o = pre2.size
+            if pre2.size:
+                native.copy_blocks(cache, dev[:o], self.block_bytes)
+            if so.size or si.size:
+                if self._swap_stream is None:
+                    self._swap_stream = torch.cuda.Stream(device=self.device)
+                main = torch.cuda.current_stream()
+                self._swap_stream.wait_stream(main)
+                with torch.cuda.stream(self._swap_stream):
+                    if so.size:
+                        native.swap_blocks(cache, self.host_cache, dev[o:o + so.size], self.block_bytes, to_host=True)
+                    if si.size:
+                        native.swap_blocks(cache, self.host_cache, dev[o + so.size:o + so.size + si.size],
+                                           self.block_bytes, to_host=False)
+                dev.record_stream(self._swap_stream)
+                main.wait_stream(self._swap_stream)
+            if cp2.size:
+                native.copy_blocks(cache, dev[o + so.size + si.size:], self.block_bytes)
         else:
-            if to_host:
-                self.host_cache[torch.from_numpy(host_ids)] = raw[torch.from_numpy(dev_ids)]
-            else:
-                raw[torch.from_numpy(dev_ids)] = self.host_cache[torch.from_numpy(host_ids)]
+            raw = flat.view(torch.uint8) if flat.dtype != torch.uint8 else flat
+            for sblk, dblk, _ in pre3:
+                flat[int(dblk)].copy_(flat[int(sblk)])
+            if so.size:
+                p2 = so.reshape(-1, 2).astype(np.int64)
+                self.host_cache[torch.from_numpy(p2[:, 1])] = raw[torch.from_numpy(p2[:, 0])]
+            if si.size:
+                p2 = si.reshape(-1, 2).astype(np.int64)
+                raw[torch.from_numpy(p2[:, 0])] = self.host_cache[torch.from_numpy(p2[:, 1])]
+            for sblk, dblk, _ in cp3:
+                flat[int(dblk)].copy_(flat[int(sblk)])
+        for t3 in (pre3, cp3):
+            if t3.size and (t3[:, 2] != 0).any():
+                self.model.rerotate_blocks(t3)
 
     def build_step(self, plan, extra: Optional[dict] = None) -> StepInput:
         T, nseq = plan.num_tokens, len(plan.seq_ids)
@@ -162,6 +200,7 @@ class ModelRunner:
         step = StepInput(input_ids, positions, slots, cu_q, kv_lens, table, plan.num_multi, plan.num_single, T,
                          plan.num_multi_tokens, plan.max_q_len, logits_rows=rows)
         step.max_kv_len = int(np.max(plan.kv_lens)) if nseq else 0
+        step.sample_k = self.candidate_k(plan, extra)
         if plan.num_single:
             max_kv = int(plan.kv_lens[plan.num_multi:].max())
             step.decode_splits = ops.decode_splits(plan.num_single, self.model.Hkv, max_kv)
@@ -169,6 +208,22 @@ class ModelRunner:
             for k, v in extra.items():
                 setattr(step, k, v)
         return step
+
+    CANDIDATE_KS = (1, 8, 64)
+
+    def candidate_k(self, plan, extra) -> int:
+        """How many per-shard sampling candidates a tensor-parallel step exchanges instead of whole logits rows
+        (0: whole rows). Needs the peer-memory path, a step whose sampling looks only at the largest logits (no
+        penalties or bans, which edit whole rows) and nobody else reading the logits (request targets, hooks)."""
+        model = self.model
+        symm = getattr(getattr(model, "comm", None), "symm", None)
+        if (not self.cuda or symm is None or getattr(model, "tp_size", 1) <= 1 or extra or self.pipeline is not None
+                or not self.exchange_candidates or plan.sample_full or plan.sample_k <= 0):
+            return 0
+        for k in self.CANDIDATE_KS:
+            if plan.sample_k <= k:
+                return k
+        return 0
 
     # ------------------------------------------------------------------ CUDA-graph decode
     GRAPH_SIZES = (1, 2, 4, 8, 16, 32, 64, 128, 256)
@@ -190,8 +245,8 @@ class ModelRunner:
             if self.cuda:
                 torch.cuda.synchronize(self.device)
 
-    def _graph_for(self, bs: int):
-        g = self.graphs.get(bs)
+    def _graph_for(self, bs: int, kx: int = 0):
+        g = self.graphs.get((bs, kx))
         if g is not None:
             return g
         mb = self.graph_max_blocks
@@ -204,6 +259,7 @@ class ModelRunner:
         step = StepInput(ids, pos, slots, cu_q, kvl, table, 0, bs, bs, 0, 1, logits_rows=None)
         step.decode_splits = ops.decode_splits(bs, self.model.Hkv, self.graph_max_kv)
         step.max_kv_len = self.graph_max_kv
+        step.sample_k = kx
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -216,7 +272,7 @@ class ModelRunner:
         # the captured kernels hold raw pointers to every tensor of `step` (cu_q is not part of `img`): keep the
         # step alive with the graph, or its memory is handed to later allocations and a replay reads garbage offsets
         g = (graph, img, logits, mb, step)
-        self.graphs[bs] = g
+        self.graphs[(bs, kx)] = g
         return g
 
     def _try_graph(self, plan) -> Optional[torch.Tensor]:
@@ -226,7 +282,7 @@ class ModelRunner:
         if plan.sample_rows.size != nseq or plan.max_blocks > self.graph_max_blocks:
             return None
         bs = next(b for b in self.GRAPH_SIZES if b >= nseq)
-        graph, img, logits, mb, _step = self._graph_for(bs)
+        graph, img, logits, mb, _step = self._graph_for(bs, self.candidate_k(plan, None))
         host = np.zeros(4 * bs + bs * mb, dtype=np.int32)
         host[0:nseq] = plan.input_ids
         host[bs:bs + nseq] = plan.positions
@@ -235,30 +291,32 @@ class ModelRunner:
         host[3 * bs:3 * bs + nseq] = plan.kv_lens
         tbl = host[4 * bs:].reshape(bs, mb)
         tbl[:nseq, :plan.max_blocks] = np.asarray(plan.block_table).reshape(nseq, plan.max_blocks)
-        n = host.size
-        if n > self._pinned_cap:
-            self._pinned_cap = max(n * 2, 1 << 16)
-            self._pinned = torch.empty(self._pinned_cap, dtype=torch.int32, pin_memory=True)
-        self._pinned[:n].copy_(torch.from_numpy(host))
-        img.copy_(self._pinned[:n], non_blocking=True)
-        self.h2d_bytes += n * 4
+        self._stage(host, out=img)
         graph.replay()
         self.graph_replays = getattr(self, "graph_replays", 0) + 1
+        if isinstance(logits, LogitCandidates):
+            return LogitCandidates(logits.values[:nseq], logits.ids[:nseq])
         return logits[:nseq]
 
     @torch.inference_mode()
     def execute(self, plan, extra: Optional[dict] = None) -> torch.Tensor:
-        self.apply_block_ops(plan)
         dp = getattr(self.model, "dp", None)
         if dp is not None:
-            # attention data parallelism: this rank runs only its own sequences; rank 0 collects the logits rows
+            # attention data parallelism: this rank runs only its own sequences and only its own pool's swap / copy
+            # entries (the plan names device blocks as rank * blocks_per_rank + block); rank 0 collects the logits rows
             sub = dp.sub_plan(plan)
+            self.apply_block_ops(sub)
+            if plan.empty():
+                return None
             local = None
             if sub.num_tokens:
                 local = self.model.forward(self.build_step(sub, None))
             else:
                 self.model.forward_empty_dp()
             return dp.gather_logits(local, self.model.cfg.vocab_size, self.device)
+        self.apply_block_ops(plan)
+        if plan.empty():
+            return None                      # a plan may carry block operations only (everything else was preempted)
         if extra is None:
             out = self._try_graph(plan)
             if out is not None:
@@ -300,7 +358,7 @@ class LLMEngine:
         self.runner.pipeline = pipeline
         if cfg.global_.enable_cuda_graph:
             self.runner.enable_graphs(bs.max_batch_size, sc.max_token_len)
-        self.sampler = Sampler(model.device, model_cfg.vocab_size)
+        self.sampler = Sampler(model.device, model_cfg.vocab_size, stage=self.runner._stage)
         self.requests: Dict[int, Request] = {}
         self.seq_to_req: Dict[int, tuple] = {}
         self._next_req = 1
@@ -312,6 +370,8 @@ class LLMEngine:
         self.fsm_controller = ne.FsmController()
         self.step_hook: Optional[Callable] = None
         self.last_logits: Optional[torch.Tensor] = None
+        self.fatal: Optional[str] = None          # set when the tensor-parallel group can no longer serve (see _device_fault)
+        self.host_ms: Dict[str, float] = {}      # host wall time of the step loop by phase (milliseconds, summed)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: List[int], sampling=None, stream: bool = False, structured_regex: str = "",
@@ -328,7 +388,9 @@ class LLMEngine:
             req.structured = StructuredOutput(self.fsm_controller.get_or_create(structured_regex), self.tokenizer)
         if cfg.seed == 0:
             cfg.seed = int.from_bytes(os.urandom(7), "little") | 1
-        if getattr(self.model, "dp", None) is not None and (request_target or refit is not None or mrope_positions is not None):
+        if self.fatal is not None:
+            code, msg, seq_ids = 12, f"engine stopped after a device error: {self.fatal}", []
+        elif getattr(self.model, "dp", None) is not None and (request_target or refit is not None or mrope_positions is not None):
             # attention data parallelism hands each rank the rows of its own sequences; per-row extras address the
             # rows of the whole step and are not re-indexed per rank
             code, msg, seq_ids = 1, "request targets and spliced embeddings are not supported with attention data parallelism", []
@@ -538,31 +600,54 @@ class LLMEngine:
 
     def step(self) -> bool:
         """Runs one engine step. Returns False when there was nothing to run."""
-        t0 = time.time()
+        tm = self.host_ms
+        t0 = time.perf_counter()
         plan = self.scheduler.schedule()
-        ne.report_metric("batch_manager_schedule_ms", (time.time() - t0) * 1000.0)
+        t1 = time.perf_counter()
+        ne.report_metric("batch_manager_schedule_ms", (t1 - t0) * 1000.0)
         if plan.events:
             self._handle_events(plan.events)
         if plan.empty():
+            if plan.has_block_ops():         # copies / swaps decided without a forward to run: execute them alone
+                if self.world_size > 1:
+                    self._broadcast_plan(plan, None)
+                self.runner.execute(plan, None)
+                return True
             return False
         ne.trace_record("SchedBegin", "i", 0, float(plan.num_tokens))
         ne.report_metric("batch_scheduler_batch_size", float(len(plan.seq_ids)))
         ne.report_metric("token_num_in_batch", float(plan.num_tokens))
         extra = self._gather_extras(plan)
+        if self.step_hook is not None:
+            plan.sample_full = True          # a hook reads whole logits rows: every rank gathers them (the flag travels with the plan)
+        t2 = time.perf_counter()
         if self.world_size > 1:
             self._broadcast_plan(plan, extra)
+        t3 = time.perf_counter()
         phase = "Prefill" if plan.num_multi else "Decode"
         ne.trace_record(phase, "B", 0, float(plan.num_tokens))
         logits, self._step_full_logits = self.run_with_extras(plan, extra)
+        t4 = time.perf_counter()
         self.last_logits = logits
-        tokens, parents, lp_by_seq = self._sample(plan, logits)
+        try:
+            tokens, parents, lp_by_seq = self._sample(plan, logits)
+        except DeviceStepError as e:
+            self._device_fault(e)
+            return True
+        t5 = time.perf_counter()
         ne.trace_record(phase, "E", 0, float(plan.num_tokens))
         self._extract_targets(plan, logits)
         events = self.scheduler.post_step(plan, tokens, parents)
+        t6 = time.perf_counter()
         self._handle_events(events, lp_by_seq)
         self.steps += 1
         if self.step_hook:
             self.step_hook(plan, logits)
+        t7 = time.perf_counter()
+        for k, v in (("schedule", t1 - t0), ("extras", t2 - t1), ("broadcast", t3 - t2), ("launch", t4 - t3),
+                     ("sample_and_wait", t5 - t4), ("post_step", t6 - t5), ("events", t7 - t6)):
+            tm[k] = tm.get(k, 0.0) + v * 1000.0
+        tm["steps"] = tm.get("steps", 0) + 1
         return True
 
     def _sample(self, plan, logits):
@@ -616,6 +701,23 @@ class LLMEngine:
                         self._wake.wait(timeout=0.05)
                     else:
                         self._wake.wait(timeout=0.001)
+
+    def _device_fault(self, err: DeviceStepError):
+        """A kernel of the step reported through the device error word (read back with the sampled tokens): the
+        step's logits are not trustworthy, so every request in flight ends with RET_RUNTIME instead of sampled
+        garbage (the reference turns a failed forward into an error status for the batch the same way:
+        src/ksana_llm/runtime/llm_runtime.cpp:387-445). With several ranks a wait on a peer that ran out leaves the
+        ranks' collective epochs out of step, so the engine also refuses new requests and releases the workers."""
+        ne.report_counter("forward_req_error_num", len(self.requests))
+        self._fail_all(12, f"device error during the step: {err}")
+        if self.world_size > 1 or err.code == 3:
+            self.fatal = str(err)
+            if self.world_size > 1:
+                from ..parallel.control import broadcast_plan
+                try:
+                    broadcast_plan(self.control_group, None)
+                except Exception:  # noqa: BLE001 - the workers may be gone already
+                    pass
 
     def _fail_all(self, code: int, message: str):
         for req in list(self.requests.values()):

@@ -74,13 +74,64 @@ def banned_encoder_ngram_tokens(prompt: List[int], generated: List[int], n: int)
     return list(banned)
 
 
+class DeviceStepError(RuntimeError):
+    """A kernel of the step reported through the device error word: a bounded wait ran out (a peer or a copy never
+    arrived) or an index guard skipped an out-of-range access. The step's results are invalid."""
+
+    def __init__(self, code: int):
+        self.code = int(code)
+        super().__init__(native.describe_err_code(self.code))
+
+
 class Sampler:
-    def __init__(self, device, vocab_size: int):
+    def __init__(self, device, vocab_size: int, stage=None):
         self.device = torch.device(device)
         self.cuda = self.device.type == "cuda"
         self.vocab = vocab_size
         self.d2h_bytes = 0
         self._cpu_rng = torch.Generator().manual_seed(1234)
+        self._stage = stage                  # int32 host array -> device through pinned staging (ModelRunner._stage)
+        self._host_out = None                # pinned read-back area: tokens, then the device error word
+        self._host_cap = 0
+        self._done = None
+
+    def _upload_params(self, params: List[SamplingParams]):
+        """temperature / top-k / top-p / step counters / seeds of all rows in one staged host->device copy."""
+        B = len(params)
+        img = np.empty(6 * B + (B & 1), dtype=np.int32)
+        img[0:B] = np.array([p.temperature for p in params], dtype=np.float32).view(np.int32)
+        img[B:2 * B] = [p.topk for p in params]
+        img[2 * B:3 * B] = np.array([p.topp for p in params], dtype=np.float32).view(np.int32)
+        img[3 * B:4 * B] = [p.step for p in params]
+        o = 4 * B + (B & 1)                                   # seeds are 64-bit: keep them 8-byte aligned
+        img[o:o + 2 * B] = np.array([p.seed for p in params], dtype=np.int64).view(np.int32)
+        if self._stage is not None:
+            dev = self._stage(img)
+        else:
+            dev = torch.from_numpy(img).to(self.device)
+        return (dev[0:B].view(torch.float32), dev[B:2 * B], dev[2 * B:3 * B].view(torch.float32), dev[3 * B:4 * B],
+                dev[o:o + 2 * B].view(torch.int64))
+
+    def _read_back(self, out: torch.Tensor):
+        """Sampled tokens and the device error word through pinned memory: two asynchronous copies and one event
+        wait (the step's only host synchronisation). Raises DeviceStepError when a kernel of the step reported."""
+        B = out.numel()
+        if self._host_out is None or self._host_cap < B + 1:
+            self._host_cap = max(2 * (B + 1), 1024)
+            self._host_out = torch.empty(self._host_cap, dtype=torch.int32, pin_memory=True)
+            self._done = torch.cuda.Event()
+        host = self._host_out
+        host[:B].copy_(out, non_blocking=True)
+        host[B:B + 1].copy_(native.err_flag(self.device), non_blocking=True)
+        self._done.record()
+        self._done.synchronize()
+        self.d2h_bytes += (B + 1) * 4
+        arr = host[:B + 1].numpy()
+        code = int(arr[B])
+        if code != 0:
+            native.clear_err_flag(self.device)
+            raise DeviceStepError(code)
+        return arr[:B].tolist()
 
     def _csr(self, lists: List[List[int]]):
         offs = np.zeros(len(lists) + 1, dtype=np.int32)
@@ -90,11 +141,16 @@ class Sampler:
         return (torch.from_numpy(offs).to(self.device), torch.from_numpy(ids).to(self.device))
 
     @torch.inference_mode()
-    def sample(self, logits: torch.Tensor, params: List[SamplingParams], reqs, seq_ids: List[int]):
+    def sample(self, logits, params: List[SamplingParams], reqs, seq_ids: List[int]):
         B = len(params)
+        merged = None
+        if not torch.is_tensor(logits):
+            # per-shard top-k candidates gathered from the tensor-parallel ranks (models.common.LogitCandidates): the
+            # engine only asks for them when no row edits its logits first, so the penalty / ban passes are skipped
+            merged, logits = logits, logits.values
         logits = logits[:B]
         # 1. repetition penalty over the distinct tokens seen so far
-        if any(p.repetition_penalty != 1.0 for p in params):
+        if merged is None and any(p.repetition_penalty != 1.0 for p in params):
             lists = []
             for p, (req, i) in zip(params, reqs):
                 seen = set(req.prompt) | set(req.outputs[i].tokens) if (req is not None and p.repetition_penalty != 1.0) else set()
@@ -108,7 +164,7 @@ class Sampler:
                     if l:
                         logits[b, torch.tensor(l)] *= 1.0 / params[b].repetition_penalty
         # 2. n-gram bans
-        if any(p.no_repeat_ngram_size > 0 or p.encoder_no_repeat_ngram_size > 0 for p in params):
+        if merged is None and any(p.no_repeat_ngram_size > 0 or p.encoder_no_repeat_ngram_size > 0 for p in params):
             lists = []
             for p, (req, i) in zip(params, reqs):
                 ban = []
@@ -128,27 +184,31 @@ class Sampler:
                         logits[b, torch.tensor(l)] = float("-inf")
         # 3. fused temperature / top-k / top-p / draw (+ top-N log-probs)
         N = max(p.logprobs_num for p in params)
-        temp = torch.tensor([p.temperature for p in params], dtype=torch.float32)
-        topk = torch.tensor([p.topk for p in params], dtype=torch.int32)
-        topp = torch.tensor([p.topp for p in params], dtype=torch.float32)
         if self.cuda:
-            seeds = torch.tensor([p.seed for p in params], dtype=torch.int64)
-            steps = torch.tensor([p.step for p in params], dtype=torch.int32)
+            temp, topk, topp, steps, seeds = self._upload_params(params)
             out = torch.empty(B, dtype=torch.int32, device=self.device)
             lp_ids = torch.empty(B, max(N, 1), dtype=torch.int32, device=self.device) if N else None
             lp_vals = torch.empty(B, max(N, 1), dtype=torch.float32, device=self.device) if N else None
-            native.sample(logits, temp.to(self.device), topk.to(self.device), topp.to(self.device),
-                          seeds.to(self.device), steps.to(self.device), out, num_logprobs=N, lp_ids=lp_ids,
-                          lp_vals=lp_vals)
-            tokens = out.cpu().tolist()        # the step's device->host result read (synchronises the stream)
-            self.d2h_bytes += B * 4
+            if merged is not None:
+                native.sample_merged(logits, merged.ids[:B], temp, topk, topp, seeds, steps, out, num_logprobs=N,
+                                     lp_ids=lp_ids, lp_vals=lp_vals)
+            else:
+                native.sample(logits, temp, topk, topp, seeds, steps, out, num_logprobs=N, lp_ids=lp_ids, lp_vals=lp_vals)
+            tokens = self._read_back(out)      # the step's device->host result read (the only host synchronisation)
             if N:
                 lp_ids_h, lp_vals_h = lp_ids.cpu(), lp_vals.cpu()
                 self.d2h_bytes += B * N * 8
         else:
+            temp = torch.tensor([p.temperature for p in params], dtype=torch.float32)
+            topk = torch.tensor([p.topk for p in params], dtype=torch.int32)
+            topp = torch.tensor([p.topp for p in params], dtype=torch.float32)
             u = torch.rand(B, generator=self._cpu_rng)
             tok, lp_ids_h, lp_vals_h = ref.sample(logits.float(), temp, topk, topp, u, N)
             tokens = tok.tolist()
+            code = int(native.err_flag(self.device).item())      # same contract as the device path
+            if code != 0:
+                native.clear_err_flag(self.device)
+                raise DeviceStepError(code)
         parents = [-1] * B
         lp_by_seq: Dict[int, list] = {}
         if N:

@@ -60,7 +60,7 @@ def main():
 
     llm.engine.step_hook = hook
     s = ne.SamplingConfig()
-    s.max_new_tokens, s.ignore_eos = 5, True
+    s.max_new_tokens, s.ignore_eos = int(os.environ.get("KSANA_TEST_DP_NEW", "5")), True
     reqs = llm.generate(prompts_for(mc.vocab_size) if llm.rank == 0 else [], s)
     if llm.rank == 0:
         order = sorted(first)

@@ -32,7 +32,7 @@ def test_sub_plan_selects_own_sequences():
     assert sub1.seq_ids.tolist() == [7, 9] and sub1.sample_rows.tolist() == [4, 5] and sub1.num_multi == 1
 
 
-def _single():
+def _single(new_tokens=5):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from dp_worker import engine_cfg, model_cfg, prompts_for
     from ksanallm_b200.models.weights import RandomSource, build_model
@@ -49,7 +49,7 @@ def _single():
 
     eng.step_hook = hook
     s = ne.SamplingConfig()
-    s.max_new_tokens, s.ignore_eos = 5, True
+    s.max_new_tokens, s.ignore_eos = new_tokens, True
     reqs = eng.generate(prompts_for(mc.vocab_size), s)
     return [r.outputs[0].tokens for r in reqs], torch.stack([first[k] for k in sorted(first)])
 
@@ -69,14 +69,16 @@ def test_attention_dp_matches_single_process(tmp_path, nproc, port):
     assert got["tokens"] == want_tokens
 
 
-@pytest.mark.parametrize("blocks,host", [(12, 0)])
+@pytest.mark.parametrize("blocks,host", [(12, 0), (8, 32)])
 def test_attention_dp_ranks_pool_their_caches(tmp_path, blocks, host):
     """Two ranks with `blocks` KV blocks each: together they hold what one pool of that size cannot (12 blocks: no
-    preemption although the five sequences need 14); the results stay those of the single process. (Swap lists per
-    rank are checked on the scheduler in tests/test_scheduler.py.)"""
-    want_tokens, want_first = _single()
+    preemption although the five sequences need 14); the results stay those of the single process. With 8 blocks per
+    rank and a host pool the ranks swap: every rank executes only its own pool's entries of the plan's swap lists
+    (device blocks are written as rank * blocks_per_rank + block there), and the tokens still match."""
+    new_tokens = 40 if host else 5
+    want_tokens, want_first = _single(new_tokens)
     out = str(tmp_path / "dp.pt")
-    env = dict(os.environ, OMP_NUM_THREADS="1", KSANA_TEST_DP_BLOCKS=str(blocks))
+    env = dict(os.environ, OMP_NUM_THREADS="1", KSANA_TEST_DP_BLOCKS=str(blocks), KSANA_TEST_DP_NEW=str(new_tokens))
     if host:
         env["KSANA_TEST_DP_HOST_BLOCKS"] = str(host)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",

@@ -216,3 +216,40 @@ def test_step_extras_survive_the_wire_format():
     assert set(back) == set(extra) and back["want_hidden"] is True and back["full_logits"] == [[0, 5], [9, 2]]
     for k in ("refit_positions", "refit_embeddings", "mrope_positions"):
         assert back[k].dtype == extra[k].dtype and torch.equal(back[k], extra[k])
+
+
+def test_device_error_word_fails_requests_in_flight():
+    """A non-zero device error word read back with the sampled tokens ends the step's requests with RET_RUNTIME
+    instead of returning tokens sampled from invalid logits; a peer wait that ran out also stops admission."""
+    from ksanallm_b200.ops import native
+    eng = tiny_engine(num_blocks=64, max_token_len=64)
+    s = sampling(max_new_tokens=8, ignore_eos=True)
+    req = eng.add_request(list(range(5, 25)), s)
+    assert eng.step()                                   # prefill step, fine
+    with torch.inference_mode():
+        native.err_flag(eng.model.device).fill_(3)
+    assert eng.step()                                   # the read-back sees the word
+    assert req.done.is_set() and req.status_code == 12 and "peer" in req.status_message
+    assert int(native.err_flag(eng.model.device).item()) == 0
+    r2 = eng.add_request(list(range(5, 25)), s)         # the group's collective epochs are out of step: refuse
+    assert r2.done.is_set() and r2.status_code == 12
+    eng.fatal = None
+    r3 = eng.generate([list(range(5, 25))], s)[0]
+    assert r3.status_code == 0 and len(r3.outputs[0].tokens) == 8
+
+
+def test_forked_siblings_survive_swap_preemption():
+    """Parallel sampling forks the partly filled tail block of the shared prompt, and under memory pressure the
+    freshly forked (youngest) sibling is the first to be swapped out: the fork's copy has to land before the swap
+    reads its destination. Greedy siblings under pressure produce the tokens of the unconstrained run."""
+    prompts = [[40 + i, 41 + i, 42 + i, 43 + i, 44 + i] for i in range(3)]
+    s = sampling(max_new_tokens=40, ignore_eos=True, num_return_sequences=3)
+    calm = tiny_engine(num_blocks=256, max_token_len=64).generate(prompts, s)
+    tight = tiny_engine(num_blocks=14, host_blocks=128, max_token_len=64)
+    pressed = tight.generate(prompts, s)
+    for a, b in zip(pressed, calm):
+        assert a.status_code == 0 and b.status_code == 0
+        assert [o.tokens for o in a.outputs] == [o.tokens for o in b.outputs]
+        assert a.outputs[0].tokens == a.outputs[1].tokens == a.outputs[2].tokens
+    st = tight.scheduler.stats()
+    assert st["preempt_swap"] > 0 and st["swap_in"] > 0

@@ -316,7 +316,21 @@ def test_penalties_and_blocks():
     want[6], want[7] = want[1], want[2]
     native.copy_blocks(cache, torch.tensor([1, 6, 2, 7], device=DEV, dtype=torch.int32), 4096 * 2)
     assert torch.equal(cache, want)
-    stage = torch.zeros(2, 4096, dtype=torch.bfloat16).pin_memory()
-    native.swap_blocks(cache, stage, torch.tensor([3, 5], device=DEV, dtype=torch.int32), 4096 * 2, True)
+    # swaps: (device block, host block) pairs against a pinned host pool, moved by the kernel itself
+    pool = torch.zeros(4, 4096 * 2, dtype=torch.uint8).pin_memory()
+    native.swap_blocks(cache, pool, torch.tensor([3, 2, 5, 0], device=DEV, dtype=torch.int32), 4096 * 2, True)
     torch.cuda.synchronize()
-    assert torch.equal(stage, cache[[3, 5]].cpu())
+    assert torch.equal(pool[2].view(torch.bfloat16), cache[3].cpu()) and torch.equal(pool[0].view(torch.bfloat16), cache[5].cpu())
+    before = cache.clone()
+    native.swap_blocks(cache, pool, torch.tensor([1, 2, 4, 0], device=DEV, dtype=torch.int32), 4096 * 2, False)
+    torch.cuda.synchronize()
+    assert torch.equal(cache[1], before[3]) and torch.equal(cache[4], before[5]) and torch.equal(cache[0], before[0])
+    # block ids outside the cache or the pool are skipped and reported through the error word
+    native.check_err_flag(DEV)
+    native.copy_blocks(cache, torch.tensor([1, 99], device=DEV, dtype=torch.int32), 4096 * 2)
+    with pytest.raises(RuntimeError, match="block-table entry"):
+        native.check_err_flag(DEV)
+    native.swap_blocks(cache, pool, torch.tensor([2, 7], device=DEV, dtype=torch.int32), 4096 * 2, True)
+    with pytest.raises(RuntimeError, match="block-table entry"):
+        native.check_err_flag(DEV)
+    assert torch.equal(cache[1], before[3])

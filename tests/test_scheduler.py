@@ -205,7 +205,8 @@ def test_parallel_sampling_shares_prefill_and_forks():
     s.post_step(plan, [100, 101, 102])
     plan = s.schedule()
     assert sorted(plan.seq_ids.tolist()) == ids and plan.num_tokens == 3
-    assert plan.copies.size == 2 * 3                                 # two siblings copy the partial tail block
+    assert plan.pre_copies.size == 2 * 3 and plan.copies.size == 0   # two siblings copy the partial tail block, before
+                                                                     # anything else this plan does to the cache
     tbl = plan.block_table.reshape(3, plan.max_blocks)
     assert (tbl[:, :3] == tbl[0, :3]).all() and len(set(tbl[:, 3].tolist())) == 3   # shared full blocks, private tails
     toks = {sid: s.get_tokens(sid) for sid in ids}
@@ -222,7 +223,7 @@ def test_beam_reparenting_shares_history():
     s.post_step(plan, [20, 21], [ids[1], -1])
     assert s.get_tokens(ids[0])[-3:] == [12, 8, 20] and s.get_tokens(ids[1])[-3:] == [12, 8, 21]
     plan = s.schedule()
-    assert plan.copies.size == 3
+    assert plan.pre_copies.size == 3
     assert s.check_invariants()[0]
 
 

@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _launch(nproc, out, backend, quant, port, graphs=None, arch=None):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _launch(nproc, out, backend, quant, port, graphs=None, arch=None, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py"),
            out, backend, quant]
@@ -54,6 +54,24 @@ def test_tp2_fused_matches_nccl_and_single(tmp_path, quant, tol):
     assert rel(fused["first"], single["first"]) < tol
     assert rel(fused["first"], nccl["first"]) < tol
     assert fused["graph_replays"] > 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("sampling", ["greedy", "topk"])
+def test_tp2_shard_sampling_matches_whole_logits(tmp_path, sampling):
+    """Vocabulary-sharded sampling: when nothing needs whole logits rows the ranks exchange each shard's top-k
+    (value, token id) pairs and sample from the merged lists. The tokens (and top-N log-probs) are those of the run
+    that gathers whole rows: same kernels up to the lm_head, exact merge, counter-based random draws."""
+    n = 2
+    env = {"KSANA_TP_SAMPLING": sampling}
+    whole = _launch(n, str(tmp_path / "whole.pt"), "fused", "auto", 29681, **env)                      # the hook reads logits
+    cand = _launch(n, str(tmp_path / "cand.pt"), "fused", "auto", 29682, KSANA_TP_TEST_NOHOOK="1", **env)
+    assert cand["tokens"] == whole["tokens"]
+    assert cand["graph_replays"] > 0
+    if sampling == "topk":
+        for a, b in zip(cand["logprobs"], whole["logprobs"]):
+            assert [[t for t, _ in step] for step in a] == [[t for t, _ in step] for step in b]
+            assert all(abs(x[1] - y[1]) < 1e-4 for sa, sb in zip(a, b) for x, y in zip(sa, sb))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")

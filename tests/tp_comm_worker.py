@@ -70,7 +70,7 @@ def main():
             nxt = LinearWeight(wq=torch.empty(8, H, device=dev, dtype=torch.float8_e4m3fn), ws=torch.empty(1, 8, device=dev)) if quant else None
             for rep in range(3):
                 comm.begin_forward()
-                if M > ONE_SHOT_ROWS:
+                if not comm.one_shot(M):
                     h = comm.h[:M]
                     h.copy_(h0)
                 else:
@@ -110,7 +110,7 @@ def main():
         xs = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         nw = torch.ones(H, device=dev, dtype=torch.bfloat16)
         W = LinearWeight(w=w)
-        hbuf = comm.h[:M] if M > ONE_SHOT_ROWS else torch.zeros(M, H, device=dev, dtype=torch.bfloat16)
+        hbuf = comm.h[:M] if not comm.one_shot(M) else torch.zeros(M, H, device=dev, dtype=torch.bfloat16)
 
         def fused():
             comm.begin_forward()

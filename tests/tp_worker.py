@@ -68,11 +68,14 @@ def main():
             first.setdefault(sid, row)
             last[sid] = row
 
-    llm.engine.step_hook = hook
+    if os.environ.get("KSANA_TP_TEST_NOHOOK") != "1":     # without the hook nothing reads whole logits rows: the ranks
+        llm.engine.step_hook = hook                        # then exchange per-shard sampling candidates only
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in (70, 5, 33, 128)]
     s = ne.SamplingConfig()
     s.max_new_tokens, s.ignore_eos = 5, True
+    if os.environ.get("KSANA_TP_SAMPLING") == "topk":
+        s.topk, s.topp, s.temperature, s.seed, s.logprobs_num, s.max_new_tokens = 20, 0.9, 0.8, 1234, 3, 12
     reqs = llm.generate(prompts if llm.rank == 0 else [], s)
     say("generate returned")
     torch.cuda.synchronize()
@@ -80,8 +83,11 @@ def main():
     native.check_err_flag(llm.device)
     if llm.rank == 0:
         order = sorted(first)
-        torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "first": torch.stack([first[k] for k in order]),
-                    "last": torch.stack([last[k] for k in order]),
+        zero = torch.zeros(1, 1)
+        torch.save({"tokens": [r.outputs[0].tokens for r in reqs],
+                    "logprobs": [r.outputs[0].logprobs for r in reqs],
+                    "first": torch.stack([first[k] for k in order]) if first else zero,
+                    "last": torch.stack([last[k] for k in order]) if last else zero,
                     "graph_replays": getattr(llm.engine.runner, "graph_replays", 0)}, out_path)
     import torch.distributed as dist
     llm.shutdown()
