@@ -87,6 +87,44 @@ def llama3_70b():
                        max_position_embeddings=8192, max_token_len=8192, eos_token_ids=[128001])
 
 
+def tp_check(rank, world, dev):
+    """Numerics of the tensor-parallel paths at this GPU count, on the real layer shapes: a 2-layer model of the
+    headline architecture runs one prefill step (4 x 256 tokens) and one decode step (64 sequences) through the fused
+    peer-memory path and through the NCCL path; returns the relative error of the logits of the fused path against
+    the NCCL path (both bf16, so rounding differs between them by design)."""
+    import torch
+    import torch.distributed as dist
+    from benchmarks.step_breakdown import build_step
+    from ksanallm_b200.models.weights import RandomSource, build_model
+    from ksanallm_b200.ops import native
+    from ksanallm_b200.parallel.comm import TPComm
+    mc = llama3_70b()
+    mc.num_layers = 2
+    out = {}
+    logits = {}
+    for backend in ("fused", "nccl"):
+        comm = TPComm(dist.group.WORLD, rank, world, backend, dev, max_tokens=2048, hidden=mc.hidden_size)
+        model = build_model(mc, RandomSource(seed=5, on_device=True), rank, world, comm, dev, torch.bfloat16, "fp8_block",
+                            max_positions=1024)
+        model.allocate_kv_cache(64 * 16 + 64, 16)
+        with torch.inference_mode():
+            for phase, batch in (("prefill", 4), ("decode", 64)):
+                step, _ = build_step(torch, model, phase, batch, 200, 256, 16)
+                torch.manual_seed(7)
+                step.input_ids.copy_(torch.randint(0, mc.vocab_size, step.input_ids.shape, device=dev, dtype=torch.int32))
+                lg = model.forward(step)
+                logits[(backend, phase)] = lg.float().clone()
+        torch.cuda.synchronize()
+        native.check_err_flag(dev)
+        del model, comm
+        torch.cuda.empty_cache()
+        dist.barrier()
+    for phase in ("prefill", "decode"):
+        a, b = logits[("fused", phase)], logits[("nccl", phase)]
+        out[phase] = float((a - b).norm() / b.norm().clamp_min(1e-12))
+    return out
+
+
 def run_library_baseline(args):
     """Same model shape, batch and timing protocol, executed by baseline/library_engine.py."""
     import torch
@@ -173,6 +211,7 @@ def main():
     ap.add_argument("--scale-mode", default="ue8m0", choices=["ue8m0", "fp32"],
                     help="weight scales: powers of two applied by the tensor cores, or exact amax/448 fp32 scales")
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--no-tp-check", action="store_true", help="skip the fused-vs-NCCL numerics check that precedes a multi-GPU run")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -214,6 +253,21 @@ def main():
     ec.block_manager.device_blocks_num = B * blocks_per_seq + 4 * max(B, 8) + 64
     ec.quantization.weight_quant_method = "fp8_block"
     ec.quantization.fp8_scale_mode = args.scale_mode
+    tp_numerics = None
+    if world > 1 and args.pp == 1 and not args.no_tp_check:
+        from ksanallm_b200.llm import init_distributed
+        import torch.distributed as dist
+        init_distributed("cuda", 1)
+        tp_dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(tp_dev)
+        tp_numerics = tp_check(rank, world, tp_dev)
+        worst = max(tp_numerics.values())
+        if worst > 3e-2:
+            if rank == 0:
+                print(json.dumps({"error": "tensor-parallel numerics check failed", "tp_check": tp_numerics}))
+            sys.stdout.flush()
+            dist.barrier()
+            os._exit(3)
     llm = LLM(ec, mc, weights="random", device="cuda", max_positions=S_in + S_out + 64)
     dev = llm.device
     s = ne.SamplingConfig()
@@ -298,6 +352,7 @@ def main():
             "p50_ttft_ms": statistics.median(latency["ttft"]) if latency["ttft"] else None,
             "p50_tpot_ms": statistics.median(latency["tpot"]) if latency["tpot"] else None,
             "clocks": clocks, "gpu_launches": launches,
+            "tp_check": ({"rel_err_fused_vs_nccl": tp_numerics, "limit": 3e-2} if tp_numerics is not None else None),
             "graph_replays": getattr(llm.engine.runner, "graph_replays", 0),
             "host_ms_per_engine_step": {k: round(v / max(1, host_ms.get("steps", 1)), 3) for k, v in host_ms.items() if k != "steps"},
             "engine_steps": host_ms.get("steps", 0),

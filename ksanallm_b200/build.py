@@ -114,11 +114,22 @@ def build_host_stress(sanitizer: str = "thread") -> Path:
     compiled with -fsanitize=<thread|address|undefined>; run the returned binary, it exits 0 when clean."""
     OBJ.mkdir(exist_ok=True)
     edir = CSRC / "engine"
-    srcs = [edir / n for n in ("host_stress.cpp", "scheduler.cpp", "cache_manager.cpp", "control_channel.cpp")]
+    srcs = [edir / n for n in ("host_stress.cpp", "scheduler.cpp", "cache_manager.cpp", "control_channel.cpp", "logger.cpp")]
     out = OBJ / f"host_stress_{sanitizer}"
     if _newer(out, [*srcs, *sorted(edir.glob("*.h"))]):
         _run(["g++", "-O1", "-g", "-std=c++17", "-pthread", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer",
               "-DKSANA_NO_PYBIND", "-I", str(edir), *map(str, srcs), "-o", str(out)])
+    return out
+
+
+def build_client() -> Path:
+    """The stand-alone C++ /forward client (csrc/client/serving_forward_client.cpp) -> lib/serving_forward_client."""
+    LIB.mkdir(exist_ok=True)
+    src = CSRC / "client" / "serving_forward_client.cpp"
+    codec = CSRC / "engine" / "request_packer.cpp"
+    out = LIB / "serving_forward_client"
+    if _newer(out, [src, codec, CSRC / "engine" / "request_packer.h"]):
+        _run(["g++", "-O2", "-std=c++17", "-Wall", "-DKSANA_NO_PYBIND", str(src), str(codec), "-o", str(out)])
     return out
 
 
@@ -127,6 +138,9 @@ def build_all(force: bool = False, verbose: bool = False):
 
 
 if __name__ == "__main__":
+    if "--client" in sys.argv:
+        print(build_client())
+        sys.exit(0)
     if "--sanitizer" in sys.argv:
         print(build_host_stress(sys.argv[sys.argv.index("--sanitizer") + 1]))
         sys.exit(0)

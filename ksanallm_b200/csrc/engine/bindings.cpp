@@ -13,6 +13,7 @@
 #include "common.h"
 #include "control_channel.h"
 #include "fsm.h"
+#include "logger.h"
 #include "profiler.h"
 #include "scheduler.h"
 
@@ -95,6 +96,19 @@ PYBIND11_MODULE(_ksana_engine, m) {
 
   ksana::BindRequestPacker(m);
   ksana::BindStopChecker(m);
+
+  // process-wide logger (KLLM_LOG_LEVEL / KLLM_LOG_FILE); the Python side writes through the same sink
+  m.def("log_message", [](int level, const std::string& file, int line, const std::string& text) {
+    ksana::Logger::Get().Write(level, file.c_str(), line, text);
+  });
+  m.def("log_enabled", [](int level) { return ksana::Logger::Get().Enabled(level); });
+  m.def("log_level", []() { return ksana::Logger::Get().level(); });
+  m.def("set_log_level", [](const std::string& name) {
+    auto& lg = ksana::Logger::Get();
+    lg.SetLevel(ksana::Logger::ParseLevel(name, lg.level()));
+  });
+  m.def("set_log_file", [](const std::string& path) { ksana::Logger::Get().SetFile(path); });
+  m.def("log_file", []() { return ksana::Logger::Get().file(); });
 
   py::class_<PyEndpointPlugin>(m, "EndpointPlugin")
       .def(py::init<const std::string&, const std::string&>(), py::arg("name"), py::arg("search_dir") = "")
@@ -200,6 +214,22 @@ PYBIND11_MODULE(_ksana_engine, m) {
       .def_readwrite("sample_full", &StepPlan::sample_full)
       .def("empty", &StepPlan::empty)
       .def("pack", [](const StepPlan& p) { return ToArray(p.Pack()); })
+      .def("step_image_words", &StepPlan::StepImageWords)
+      .def("write_step_image", [](const StepPlan& p, uintptr_t dst, size_t capacity_words) {
+        if (capacity_words < p.StepImageWords()) throw std::runtime_error("step image does not fit its buffer");
+        return p.WriteStepImage(reinterpret_cast<int32_t*>(dst));
+      })
+      .def("write_decode_image", [](const StepPlan& p, uintptr_t dst, size_t capacity_words, int bs, int mb) {
+        if (capacity_words < static_cast<size_t>(4) * bs + static_cast<size_t>(bs) * mb)
+          throw std::runtime_error("decode image does not fit its buffer");
+        return p.WriteDecodeImage(reinterpret_cast<int32_t*>(dst), bs, mb);
+      })
+      .def_property_readonly("num_seqs", [](const StepPlan& p) { return p.seq_ids.size(); })
+      .def_property_readonly("num_samples", [](const StepPlan& p) { return p.sample_rows.size(); })
+      .def_property_readonly("max_kv_len", [](const StepPlan& p) {
+        int m = 0; for (int v : p.kv_lens) m = std::max(m, v); return m; })
+      .def_property_readonly("max_single_kv_len", [](const StepPlan& p) {
+        int m = 0; for (size_t i = p.num_multi; i < p.kv_lens.size(); ++i) m = std::max(m, p.kv_lens[i]); return m; })
       .def_static("unpack", [](py::array_t<int32_t, py::array::c_style | py::array::forcecast> a) {
         StepPlan p;
         if (!StepPlan::Unpack(a.data(), static_cast<size_t>(a.size()), &p)) throw std::runtime_error("bad step plan image");

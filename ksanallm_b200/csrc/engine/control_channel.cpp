@@ -1,4 +1,5 @@
 #include "control_channel.h"
+#include "logger.h"
 
 #include <arpa/inet.h>
 #include <netdb.h>
@@ -199,6 +200,7 @@ void ControlMaster::MarkFailed(Peer* p) {
   if (!p->failed) {
     p->failed = true;
     alive_ = false;   // one lost node stops the cluster (no elastic re-sharding)
+    KLLM_LOG_ERROR << "control channel: connection to node " << p->rank << " closed; the cluster is no longer alive";
   }
   cv_.notify_all();
 }
@@ -232,6 +234,8 @@ void ControlMaster::HeartbeatLoop() {
       if (!p->failed && now - p->last_seen_ms > hb_timeout_ms_) {
         p->failed = true;
         alive_ = false;
+        KLLM_LOG_ERROR << "control channel: no heartbeat from node " << p->rank << " for " << (now - p->last_seen_ms)
+                       << " ms; the cluster is no longer alive";
         cv_.notify_all();
       }
     }
@@ -349,6 +353,7 @@ void ControlWorker::ReaderLoop() {
     Packet pkt;
     if (!RecvPacket(fd_, &pkt, -1)) {
       alive_ = false;   // EOF: the master is gone
+      if (!stop_) KLLM_LOG_ERROR << "control channel: the master closed the connection";
       cv_.notify_all();
       return;
     }

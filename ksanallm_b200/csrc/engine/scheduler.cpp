@@ -4,6 +4,8 @@
 #include <cmath>
 #include <cstring>
 
+#include "logger.h"
+
 namespace ksana {
 
 namespace {
@@ -84,6 +86,33 @@ bool StepPlan::Unpack(const int32_t* d, size_t n, StepPlan* p) {
   return true;
 }
 
+size_t StepPlan::StepImageWords() const {
+  return static_cast<size_t>(num_tokens) * 3 + cu_q.size() + kv_lens.size() + block_table.size() + sample_rows.size();
+}
+
+size_t StepPlan::WriteStepImage(int32_t* dst) const {
+  int32_t* c = dst;
+  auto put = [&](const std::vector<int>& v) { if (!v.empty()) std::memcpy(c, v.data(), v.size() * sizeof(int32_t)); c += v.size(); };
+  put(input_ids); put(positions); put(slots); put(cu_q); put(kv_lens); put(block_table); put(sample_rows);
+  return static_cast<size_t>(c - dst);
+}
+
+size_t StepPlan::WriteDecodeImage(int32_t* dst, int bs, int mb) const {
+  const int nseq = static_cast<int>(seq_ids.size());
+  if (num_multi != 0 || nseq > bs || max_blocks > mb || num_tokens != nseq) return 0;
+  const size_t total = static_cast<size_t>(4) * bs + static_cast<size_t>(bs) * mb;
+  std::memset(dst, 0, total * sizeof(int32_t));
+  std::memcpy(dst, input_ids.data(), nseq * sizeof(int32_t));
+  std::memcpy(dst + bs, positions.data(), nseq * sizeof(int32_t));
+  for (int i = 0; i < bs; ++i) dst[2 * bs + i] = i < nseq ? slots[i] : -1;
+  std::memcpy(dst + 3 * bs, kv_lens.data(), nseq * sizeof(int32_t));
+  int32_t* tbl = dst + 4 * bs;
+  for (int i = 0; i < nseq; ++i)
+    std::memcpy(tbl + static_cast<size_t>(i) * mb, block_table.data() + static_cast<size_t>(i) * max_blocks,
+                max_blocks * sizeof(int32_t));
+  return total;
+}
+
 // --------------------------------------------------------------------------------- Scheduler
 Scheduler::Scheduler(const SchedulerConfig& cfg, int num_device_blocks, int num_host_blocks)
     : cfg_(cfg), split_fuse_on_(cfg.split_fuse_token_num > 0) {
@@ -108,6 +137,7 @@ Status Scheduler::AddRequest(int64_t req_id, const std::vector<int>& prompt, con
   std::lock_guard<std::mutex> g(mu_);
   if (static_cast<int>(waiting_buffer_.size() + waiting_.size()) >= cfg_.max_waiting_queue_len) {
     ++stats_.rejected;
+    KLLM_LOG_WARNING << "req " << req_id << " rejected: waiting queue is full (" << cfg_.max_waiting_queue_len << ")";
     return Status(RET_EXCEED_CAPACITY, "waiting queue is full");
   }
   ++stats_.total_requests;
@@ -189,6 +219,7 @@ void Scheduler::ExpireAndAbort(int64_t now, std::vector<SeqEvent>* ev) {
     }
     if (queued && now >= s->arrive_ms + cfg_.waiting_timeout_in_ms) {
       ++stats_.timeouts;
+      KLLM_LOG_WARNING << "req " << s->req_id << " waited " << (now - s->arrive_ms) << " ms in the queue: timeout";
       auto git = groups_.find(s->req_id);
       std::vector<SeqPtr> sibs;
       if (git != groups_.end()) sibs = git->second;
@@ -220,6 +251,8 @@ int Scheduler::StepTokenCap(int num_decodes) const {
 
 void Scheduler::PreemptLocked(const SeqPtr& v, StepPlan* plan) {
   ++v->preempt_count;
+  KLLM_LOG_DEBUG << "preempt seq " << v->seq_id << " (req " << v->req_id << ", " << v->blocks.size() << " blocks, mode "
+                 << (cfg_.preempt_mode == 0 ? "swap" : "recompute") << ")";
   const size_t so0 = plan->swap_out.size();
   if (cfg_.preempt_mode == 0 && CacheOf(*v).SwapOut(&v->blocks, &v->host_blocks, &plan->swap_out)) {
     for (size_t i = so0; i < plan->swap_out.size(); ++i) plan->swap_out[i].device_block += PoolBase(*v);
@@ -320,6 +353,8 @@ bool Scheduler::Schedule(StepPlan* plan) {
         if (rank_need[r] <= usable) break;
         // a lone request that cannot grow any more can never finish
         running_.erase(running_.begin() + vi);
+        KLLM_LOG_WARNING << "req " << v->req_id << ": not enough KV cache blocks for a single sequence of "
+                         << v->tokens.size() << " tokens; finishing it with RET_OUT_OF_MEMORY";
         FinishLocked(v, RET_OUT_OF_MEMORY, "not enough KV cache blocks for this request", -1, &plan->events);
         rank_need[r] = 0;
         rank_bs[r] = 0;

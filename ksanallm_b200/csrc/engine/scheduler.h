@@ -103,6 +103,15 @@ struct StepPlan {
   // broadcasting the step to the other ranks / nodes.
   std::vector<int32_t> Pack() const;
   static bool Unpack(const int32_t* data, size_t n, StepPlan* out);
+  // Device images written straight into (pinned) host memory, no intermediate arrays.
+  // Step image: input_ids, positions, slots [num_tokens each], cu_q [nseq + 1], kv_lens [nseq],
+  // block_table [nseq * max_blocks], sample_rows. Returns the number of words (StepImageWords()).
+  size_t StepImageWords() const;
+  size_t WriteStepImage(int32_t* dst) const;
+  // Image of a pure decode step padded to `bs` sequences and `mb` blocks per sequence (the layout a captured
+  // decode graph reads): ids, positions, slots (-1 padding), kv_lens [bs each], block_table [bs * mb].
+  // Returns the number of words, or 0 if the plan does not fit.
+  size_t WriteDecodeImage(int32_t* dst, int bs, int mb) const;
 };
 
 struct SampledToken {

@@ -23,6 +23,7 @@
 // and of its FlashAttention-2 call (src/ksana_llm/kernels/nvidia/kernel_wrapper.cpp:437-588),
 // without the reverse cache copy the latter needs.
 #include "sm100_ptx.cuh"
+#include "pdl.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
@@ -386,6 +387,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams
   bf16* vs = ks + kKvStages * kTileTok * D;
   float* merge = reinterpret_cast<float*>(ks);              // 4 warps x 16 rows x (D + 2), reuses the K ring after the loop
 
+  pdl_trigger();
+  pdl_wait();
   const int g = blockIdx.x, s = blockIdx.y, split = blockIdx.z;
   const int G = p.Hq / p.Hkv;
   const int kv_len = p.kv_lens[s];
@@ -512,6 +515,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams
 // grid (Hq, B): combine the per-split partials.
 template <int D>
 __global__ void decode_reduce_kernel(const AttnParams p) {
+  pdl_trigger();
+  pdl_wait();
   const int head = blockIdx.x, s = blockIdx.y;
   const size_t base = (static_cast<size_t>(s) * p.Hq + head) * p.num_splits;
   float mm = -INFINITY;
@@ -589,11 +594,10 @@ static int launch_decode(const AttnParams& p, const CUtensorMap& map, long long 
     set = true;
   }
   dim3 grid(p.Hkv, B, p.num_splits);
-  paged_decode_kernel<D, MODE><<<grid, kAttnThreads, smem, st>>>(map, p, rows_per_block);
-  if (cudaGetLastError() != cudaSuccess) return -4;
+  if (launch_pdl(paged_decode_kernel<D, MODE>, grid, dim3(kAttnThreads), smem, st, map, p, rows_per_block) != cudaSuccess)
+    return -4;
   if (p.num_splits > 1) {
-    decode_reduce_kernel<D><<<dim3(p.Hq, B), D < 128 ? 64 : 128, 0, st>>>(p);
-    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (launch_pdl(decode_reduce_kernel<D>, dim3(p.Hq, B), dim3(D < 128 ? 64 : 128), 0, st, p) != cudaSuccess) return -5;
   }
   return 0;
 }

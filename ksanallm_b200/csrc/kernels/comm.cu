@@ -26,6 +26,7 @@
 #include <cuda_fp8.h>
 #include <stdint.h>
 #include "fp8_scale.cuh"
+#include "pdl.cuh"
 
 namespace ksana {
 
@@ -183,6 +184,8 @@ constexpr int kRnMaxVec = 4;
 template <int NV>
 __device__ __forceinline__ void reduce_norm_body(const ReduceNormParams& p) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   const CommPeers& c = p.peers;
   const uint32_t epoch = begin_epoch(p.ctrs, 0);
   if (!signal_and_wait(c, 0, epoch, p.err, true)) return;
@@ -356,6 +359,8 @@ __global__ void reduce_norm_kernel_v4(const ReduceNormParams p) { reduce_norm_bo
 // the last block of the peer's reduce_norm_kernel). Stream-ordered after this rank's own reduce_norm_kernel, so the
 // epoch to wait for is the counter's current value.
 __global__ void gather_wait_kernel(const CommPeers c, const uint32_t* ctrs, int* err) {
+  pdl_trigger();
+  pdl_wait();
   const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(ctrs + 1);
   signal_and_wait(c, 1, epoch, err, false);
 }
@@ -455,12 +460,13 @@ extern "C" int ksana_reduce_norm(const unsigned long long* data_ptrs, const unsi
   if (threads < 32) threads = 32;
   if (threads > 1024) threads = 1024;
   // a rank with no rows still takes part in the flag exchange
-  if (per_thread == 1) reduce_norm_kernel_v1<<<row_count > 0 ? row_count : 1, threads, 0, st>>>(p);
-  else reduce_norm_kernel_v4<<<row_count > 0 ? row_count : 1, threads, 0, st>>>(p);
-  if (cudaGetLastError() != cudaSuccess) return -4;
+  const dim3 grid(row_count > 0 ? row_count : 1);
+  const cudaError_t e = per_thread == 1 ? launch_pdl(reduce_norm_kernel_v1, grid, dim3(threads), 0, st, p)
+                                        : launch_pdl(reduce_norm_kernel_v4, grid, dim3(threads), 0, st, p);
+  if (e != cudaSuccess) return -4;
   if (gather & 1) {
-    gather_wait_kernel<<<1, 32, 0, st>>>(p.peers, p.ctrs, err);
-    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (launch_pdl(gather_wait_kernel, dim3(1), dim3(32), 0, st, p.peers, static_cast<const uint32_t*>(p.ctrs), err) !=
+        cudaSuccess) return -5;
   }
   return 0;
 }

@@ -13,6 +13,7 @@
 //   cache copy : .../paged_attention/cache_copy.cu:21-254
 //   fp8 quant  : 3rdparty/LLM_kernels/csrc/utils/nvidia/cuda_fp8_utils.cu:27-140
 #include "guards.cuh"
+#include "pdl.cuh"
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -85,6 +86,8 @@ template <int MODE>
 __global__ void norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ residual, const bf16* __restrict__ w,
                             const bf16* __restrict__ beta, bf16* __restrict__ y, uint8_t* __restrict__ yq,
                             float* __restrict__ yscale, int scale_ld, int H, float eps) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nvec = H >> 3;
@@ -184,6 +187,8 @@ __device__ __forceinline__ float act_fn(float x, int act) {
 
 __global__ void act_mul_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, uint8_t* __restrict__ outq,
                                float* __restrict__ oscale, int scale_ld, int M, int I, int in_ld, int act, int gated) {
+  pdl_trigger();
+  pdl_wait();
   const int nvec = I >> 3;
   const long long total = static_cast<long long>(M) * nvec;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -228,6 +233,8 @@ __global__ void act_mul_kernel(const bf16* __restrict__ in, bf16* __restrict__ o
 // x[M,K] bf16 -> e4m3 + one scale per (row, 128 columns); scales stored [K/128][scale_ld].
 __global__ void quant_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
                                  int scale_ld, int M, int K, int x_ld) {
+  pdl_trigger();
+  pdl_wait();
   const int nvec = K >> 3;                                    // a multiple of 16
   const long long total = static_cast<long long>(M) * nvec;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -257,6 +264,8 @@ __global__ void quant_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restrict
 __global__ void embedding_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
                                  const int* __restrict__ positions, const bf16* __restrict__ pos_table,
                                  bf16* __restrict__ out, int H, int vocab_lo, int vocab_hi, float scale) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool mine = id >= vocab_lo && id < vocab_hi;
@@ -289,6 +298,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const bf16* __rest
 // out[r, :] = in[idx[r], :]  (last-token assembly, logits gather)
 __global__ void gather_rows_kernel(const bf16* __restrict__ in, const int* __restrict__ idx, bf16* __restrict__ out,
                                    int H, int in_rows, int* err) {
+  pdl_trigger();
+  pdl_wait();
   int r = idx[blockIdx.x];
   if (r < 0 || r >= in_rows) { if (threadIdx.x == 0) guard_report(err, kGuardGatherRow, r); r = 0; }
   const uint4* src = reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * H);
@@ -366,6 +377,8 @@ __global__ void rope_kv_append_vec_kernel(bf16* __restrict__ qkv, const int* __r
                                           const int* __restrict__ slots, const float* __restrict__ cos_sin,
                                           CacheT* __restrict__ cache, long long block_stride, int block_tokens, int Hq,
                                           int Hkv, int D, float k_scale_inv, float v_scale_inv, int apply_rope) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   bf16* row = qkv + static_cast<size_t>(t) * (Hq + 2 * Hkv) * D;
   const int half = D >> 1, hv = half >> 3;                   // 16-byte vectors per half head
@@ -529,10 +542,10 @@ extern "C" int ksana_norm(const void* x, void* residual, const void* w, const vo
   if (yq && (H % 128)) return -11;
   const int threads = norm_threads(H);
   if (layernorm)
-    norm_kernel<1><<<M, threads, 0, st>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, (const bf16*)beta, (bf16*)y,
+    launch_pdl(norm_kernel<1>, dim3(M), dim3(threads), 0, st, (const bf16*)x, (bf16*)residual, (const bf16*)w, (const bf16*)beta, (bf16*)y,
                                           (uint8_t*)yq, yscale, scale_ld, H, eps);
   else
-    norm_kernel<0><<<M, threads, 0, st>>>((const bf16*)x, (bf16*)residual, (const bf16*)w, (const bf16*)beta, (bf16*)y,
+    launch_pdl(norm_kernel<0>, dim3(M), dim3(threads), 0, st, (const bf16*)x, (bf16*)residual, (const bf16*)w, (const bf16*)beta, (bf16*)y,
                                           (uint8_t*)yq, yscale, scale_ld, H, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -543,7 +556,7 @@ extern "C" int ksana_act_mul(const void* in, void* out, void* outq, float* oscal
   if (I % 8 || in_ld % 8) return -10;
   if (outq && (I % 128)) return -11;
   const long long total = static_cast<long long>(M) * (I >> 3);
-  act_mul_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)in, (bf16*)out, (uint8_t*)outq, oscale, scale_ld, M,
+  launch_pdl(act_mul_kernel, dim3(grid_for(total, 256)), dim3(256), 0, st, (const bf16*)in, (bf16*)out, (uint8_t*)outq, oscale, scale_ld, M,
                                                        I, in_ld, act, gated);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -553,7 +566,7 @@ extern "C" int ksana_quant_fp8(const void* x, void* q, float* scale, int scale_l
   if (M <= 0) return 0;
   if (K % 128 || x_ld % 8) return -10;
   const long long total = static_cast<long long>(M) * (K >> 3);
-  quant_fp8_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (uint8_t*)q, scale, scale_ld, M, K, x_ld);
+  launch_pdl(quant_fp8_kernel, dim3(grid_for(total, 256)), dim3(256), 0, st, (const bf16*)x, (uint8_t*)q, scale, scale_ld, M, K, x_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -572,7 +585,7 @@ extern "C" int ksana_embedding(const int* ids, const void* table, const int* pos
                                void* out, int T, int H, int vocab_lo, int vocab_hi, float scale, cudaStream_t st) {
   if (T <= 0) return 0;
   if (H % 8) return -10;
-  embedding_kernel<<<T, 256, 0, st>>>(ids, (const bf16*)table, positions, (const bf16*)pos_table, (bf16*)out, H,
+  launch_pdl(embedding_kernel, dim3(T), dim3(256), 0, st, ids, (const bf16*)table, positions, (const bf16*)pos_table, (bf16*)out, H,
                                       vocab_lo, vocab_hi, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -581,7 +594,7 @@ extern "C" int ksana_gather_rows(const void* in, const int* idx, void* out, int 
                                  cudaStream_t st) {
   if (R <= 0) return 0;
   if (H % 8 || in_rows <= 0) return -10;
-  gather_rows_kernel<<<R, 256, 0, st>>>((const bf16*)in, idx, (bf16*)out, H, in_rows, err);
+  launch_pdl(gather_rows_kernel, dim3(R), dim3(256), 0, st, (const bf16*)in, idx, (bf16*)out, H, in_rows, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -600,11 +613,11 @@ extern "C" int ksana_rope_kv_append(void* qkv, const int* positions, int pos_str
       (reinterpret_cast<uintptr_t>(qkv) % 16) == 0 && (reinterpret_cast<uintptr_t>(cache) % 16) == 0 &&
       (reinterpret_cast<uintptr_t>(cos_sin) % 16) == 0) {
     if (cache_fp8)
-      rope_kv_append_vec_kernel<uint8_t><<<T, 256, 0, st>>>((bf16*)qkv, positions, slots, cos_sin, (uint8_t*)cache,
+      launch_pdl(rope_kv_append_vec_kernel<uint8_t>, dim3(T), dim3(256), 0, st, (bf16*)qkv, positions, slots, cos_sin, (uint8_t*)cache,
                                                             block_stride, block_tokens, Hq, Hkv, D, 1.f / k_scale,
                                                             1.f / v_scale, apply_rope);
     else
-      rope_kv_append_vec_kernel<bf16><<<T, 256, 0, st>>>((bf16*)qkv, positions, slots, cos_sin, (bf16*)cache,
+      launch_pdl(rope_kv_append_vec_kernel<bf16>, dim3(T), dim3(256), 0, st, (bf16*)qkv, positions, slots, cos_sin, (bf16*)cache,
                                                          block_stride, block_tokens, Hq, Hkv, D, 1.f, 1.f, apply_rope);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }

@@ -21,6 +21,7 @@
 //     segment accumulates in TMEM and the epilogue runs once per segment, as for bf16.
 // Same warp roles and bounded waits as gemm_tcgen05.cu. No cluster multicast.
 #include "sm100_ptx.cuh"
+#include "pdl.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdio.h>
@@ -233,6 +234,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint32_t* last_flag = tmem_slot + 2;
 
+  pdl_trigger();                      // the next kernel of the stream may set itself up while this one runs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long prof_t0 = prof_clock();
   if (p.prof && threadIdx.x == 0) {
@@ -261,6 +263,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, TMEM and the launch itself overlapped the previous kernel's tail; its results (activations, scales,
+  // residual, the split-K counters) are read only from here on
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -826,8 +831,8 @@ static int launch_smallm(const CUtensorMap& mw, const CUtensorMap& mx, const Sma
                              Cfg::kSmemBytes) != cudaSuccess) return -3;
     set[dev].store(true, std::memory_order_release);
   }
-  gemm_smallm_kernel<MP, KIND><<<ctas, Cfg::kThreads, Cfg::kSmemBytes, st>>>(mw, mx, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(gemm_smallm_kernel<MP, KIND>, dim3(ctas), dim3(Cfg::kThreads), Cfg::kSmemBytes, st, mw, mx, p) ==
+                 cudaSuccess ? 0 : -4;
 }
 
 static long long* g_smallm_prof = nullptr;

@@ -22,6 +22,7 @@
 // The reference has no counterpart of the hardware-scaled path: its FP8 GEMMs are cuBLASLt per-tensor
 // (src/ksana_llm/kernels/nvidia/kernel_wrapper.cpp:1014-1048) or DeepGEMM block-wise on Hopper.
 #include "sm100_ptx.cuh"
+#include "pdl.cuh"
 #include <cuda_bf16.h>
 #include <stdio.h>
 
@@ -73,6 +74,7 @@ __device__ __forceinline__ void mx_tile_coords(int tile, int m_tiles, int n_tile
 template <int BN>
 __global__ void __launch_bounds__(kMxThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const MxParams p) {
+  pdl_trigger();
   using Cfg = MxCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -106,6 +108,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                         // set-up overlapped the previous kernel; its results are read from here on
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -377,7 +380,7 @@ static int launch_mx(const CUtensorMap& ma, const CUtensorMap& mb, const MxParam
   const int tiles = ((p.M + kMxBM - 1) / kMxBM) * ((p.N + BN - 1) / BN);
   int grid = tiles < sms ? tiles : sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  gemm_mxfp8_kernel<BN><<<grid, kMxThreads, Cfg::kSmemBytes, st>>>(ma, mb, p);
+  launch_pdl(gemm_mxfp8_kernel<BN>, dim3(grid), dim3(kMxThreads), Cfg::kSmemBytes, st, ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

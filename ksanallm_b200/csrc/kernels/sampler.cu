@@ -13,6 +13,7 @@
 // samplingTopKKernels.cu:55-300, decodingCommon.cu:95-207, repetition_penalty.cu:19}.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "pdl.cuh"
 
 namespace ksana {
 
@@ -72,6 +73,8 @@ sample_kernel(const SampleParams p) {
   __shared__ int red_idx[32];
   __shared__ uint32_t sh_prefix, sh_remaining, sh_count, sh_ties;
 
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   const long long src_row = p.row_idx ? p.row_idx[b] : b;
   const float* row = p.logits + src_row * p.ld;
@@ -268,8 +271,7 @@ extern "C" int ksana_sample(const float* logits, long long ld, const int* row_id
   if (num_logprobs > kMaxK) return -10;
   SampleParams p{logits, ld, row_idx, temperature, top_k, top_p, seeds, steps, out_tokens, num_logprobs, lp_ids,
                  lp_vals, vocab, nullptr, nullptr, 0, 0, nullptr, 0};
-  sample_kernel<<<B, kSampThreads, 0, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(sample_kernel, dim3(B), dim3(kSampThreads), 0, st, p) == cudaSuccess ? 0 : -4;
 }
 
 // Sampling over candidate lists gathered from the vocabulary shards: logits [rows][ld] holds `ncols` candidate
@@ -282,8 +284,7 @@ extern "C" int ksana_sample_merged(const float* logits, long long ld, const int*
   if (num_logprobs > kMaxK || !col_ids) return -10;
   SampleParams p{logits, ld, row_idx, temperature, top_k, top_p, seeds, steps, out_tokens, num_logprobs, lp_ids,
                  lp_vals, ncols, nullptr, nullptr, 0, 0, col_ids, col_ld};
-  sample_kernel<<<B, kSampThreads, 0, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(sample_kernel, dim3(B), dim3(kSampThreads), 0, st, p) == cudaSuccess ? 0 : -4;
 }
 
 // This shard's k largest logits per row (value descending, index ascending) with their token ids
@@ -294,8 +295,7 @@ extern "C" int ksana_shard_topk(const float* logits, long long ld, const int* ro
   if (k < 1 || k > kMaxK || !cand_val || !cand_idx) return -10;
   SampleParams p{logits, ld, row_idx, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, vocab,
                  cand_val, cand_idx, k, idx_offset, nullptr, 0};
-  sample_kernel<<<B, kSampThreads, 0, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(sample_kernel, dim3(B), dim3(kSampThreads), 0, st, p) == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int ksana_repetition_penalty(float* logits, long long ld, const int* row_idx, const int* offsets,

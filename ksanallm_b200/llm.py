@@ -204,7 +204,41 @@ class LLM:
                                       micro_batches=self.engine_cfg.global_.pipeline_micro_batches)
         self.engine = LLMEngine(self.model, model_cfg, self.engine_cfg, nblocks, nhost, tokenizer, kv_dtype,
                                 self.rank, self.world, ctl_group, pipeline=pipeline)
+        # liveness of the other ranks: a lost peer ends this rank's service instead of leaving it in a collective
+        from .parallel.coordinator import DistributedCoordinator, register_stop_hook
+        self.coordinator = DistributedCoordinator.from_env(self.rank, self.world)
+        if self.coordinator is not None:
+            self.coordinator.start()
+            register_stop_hook(self.engine.on_service_stop)
         self.tokenizer = tokenizer
+        from .utils import logger
+        logger.info(f"engine ready: model {model_cfg.model_type} ({model_cfg.num_layers} layers, hidden "
+                    f"{model_cfg.hidden_size}), rank {self.rank}/{self.world} tp {tp} pp {pp} attention-dp {adp}, "
+                    f"{nblocks} device KV blocks of {bt} tokens, {nhost} host blocks, weights {quant or 'dense'}")
+        self.warmup()
+
+    def warmup(self):
+        """One short request through the whole engine before serving (kernel modules loaded, workspaces and the
+        first decode graph created, collectives' first-call set-up done), as the reference does at start-up unless
+        ``DISABLE_WARMUP`` is set (src/ksana_llm/service/inference_engine.cpp:218-247). Collective: every rank of the
+        engine runs it from its constructor."""
+        if os.environ.get("DISABLE_WARMUP", "").lower() in ("1", "true", "yes", "on"):
+            return
+        from .utils import logger
+        limit = min(self.model_cfg.max_token_len or 64, self.engine_cfg.batch_scheduler.max_token_len)
+        if limit < 4:
+            return
+        s = ne.SamplingConfig()
+        s.max_new_tokens, s.ignore_eos = 2, True
+        tok = min(1, self.model_cfg.vocab_size - 1)
+        import time
+        t0 = time.time()
+        reqs = self.generate([[tok] * min(8, limit - 2)] if self.rank == 0 else [], s)
+        if self.rank == 0:
+            ok = bool(reqs) and reqs[0].status_code == 0
+            logger.info(f"warm-up request {'finished' if ok else 'FAILED'} in {(time.time() - t0) * 1000.0:.0f} ms")
+            if not ok:
+                raise RuntimeError(f"warm-up request failed: {reqs[0].status_message if reqs else 'no result'}")
 
     # ------------------------------------------------------------------ API
     def generate(self, prompt_token_ids: List[List[int]], sampling=None, timeout: Optional[float] = None):
@@ -233,6 +267,8 @@ class LLM:
     def shutdown(self, stop_followers: bool = False):
         """Stops the engine loop. ``stop_followers`` additionally releases worker ranks blocked in ``follow``."""
         self.engine.runner.release_graphs()
+        if getattr(self, "coordinator", None) is not None:
+            self.coordinator.close()
         if self.rank == 0:
             self.engine.stop()
             if stop_followers and self.world > 1:

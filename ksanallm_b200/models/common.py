@@ -22,6 +22,7 @@ from ..config import ModelConfig
 from ..ops import dispatch as ops
 from ..ops import reference as ref
 from ..ops.dispatch import LinearWeight
+from ..utils import nvtx
 
 
 @dataclass
@@ -206,14 +207,17 @@ class CommonModel:
             h = self.mlp(lw, h, h)
             return ops.norm(h, lw.post_norm, cfg.rms_norm_eps, beta=lw.post_norm_bias, layernorm=ln)
         x = ops.norm(h, lw.input_norm, cfg.rms_norm_eps, beta=lw.input_norm_bias, layernorm=ln, quant_for=lw.qkv)
-        a = self.attention(li, lw, x, step)
-        h = self.row_parallel(a, lw.o_proj, h)
+        with nvtx.annotate("attention"):
+            a = self.attention(li, lw, x, step)
+        with nvtx.annotate("o_proj"):
+            h = self.row_parallel(a, lw.o_proj, h)
         if lw.moe is not None:
             from .moe import moe_forward
             x = ops.norm(h, lw.post_norm, cfg.rms_norm_eps, beta=lw.post_norm_bias, layernorm=ln)
             return moe_forward(self, lw.moe, x, h)
         x = ops.norm(h, lw.post_norm, cfg.rms_norm_eps, beta=lw.post_norm_bias, layernorm=ln, quant_for=lw.gate_up)
-        return self.mlp(lw, x, h)
+        with nvtx.annotate("mlp"):
+            return self.mlp(lw, x, h)
 
     def _final_norm(self, h: torch.Tensor) -> torch.Tensor:
         if self.final_norm is None:
@@ -342,9 +346,11 @@ class CommonModel:
         x = ops.norm(h, first.input_norm, cfg.rms_norm_eps, beta=first.input_norm_bias, layernorm=ln, quant_for=first.qkv)
         n = len(self.layers)
         for i, lw in enumerate(self.layers):
-            a = self.attention(self.layer_lo + i, lw, x, step)
-            h, x = symm.row_parallel_norm(a, lw.o_proj, h, lw.post_norm, lw.post_norm_bias, cfg.rms_norm_eps, ln,
-                                          quant_for=lw.gate_up if lw.moe is None else None)
+            with nvtx.annotate("attention"):
+                a = self.attention(self.layer_lo + i, lw, x, step)
+            with nvtx.annotate("o_proj+reduce+norm"):
+                h, x = symm.row_parallel_norm(a, lw.o_proj, h, lw.post_norm, lw.post_norm_bias, cfg.rms_norm_eps, ln,
+                                              quant_for=lw.gate_up if lw.moe is None else None)
             if i + 1 < n:
                 nw, nb, nq = self.layers[i + 1].input_norm, self.layers[i + 1].input_norm_bias, self.layers[i + 1].qkv
             else:
@@ -357,10 +363,12 @@ class CommonModel:
                 h, x = symm.partial_norm(lambda part, _m=lw.moe, _x=x: moe_partial(self, _m, _x, into=part), T, h, nw, nb,
                                          cfg.rms_norm_eps, ln, quant_for=nq, gather_h=last_h)
                 continue
-            gu = ops.linear(x, lw.gate_up)
-            act = ops.act_mul(gu, cfg.activation, cfg.gated_mlp, quant_for=lw.down)
-            h, x = symm.row_parallel_norm(act, lw.down, h, nw, nb, cfg.rms_norm_eps, ln, quant_for=nq,
-                                          gather_h=last_h)
+            with nvtx.annotate("gate_up+act"):
+                gu = ops.linear(x, lw.gate_up)
+                act = ops.act_mul(gu, cfg.activation, cfg.gated_mlp, quant_for=lw.down)
+            with nvtx.annotate("down+reduce+norm"):
+                h, x = symm.row_parallel_norm(act, lw.down, h, nw, nb, cfg.rms_norm_eps, ln, quant_for=nq,
+                                              gather_h=last_h)
         if step.want_hidden:
             self.step_hidden, self.step_normed = h, x
         hn = ops.gather_rows(x, step.logits_rows) if step.logits_rows is not None else x

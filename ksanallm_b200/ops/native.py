@@ -363,6 +363,27 @@ def gemm_mxfp8_pair(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=
     return dst
 
 
+def _skinny_wins_mx(M, N, K, sms=148):
+    """Rows 33..128 with tensor-core-applied scales: skinny stream-K kernel or tiled kernel, from their measured
+    behaviour in CUDA graphs of decode steps (microseconds). Tiled: about 6.5 + 0.37 per 128-deep K block and wave of
+    128 x 128 tiles (0.69 with 128 x 256 tiles); one CTA walks the whole K range of its tile, so few tiles leave
+    SMs idle. Skinny: the (tile, K block) units are spread evenly over the SMs at about 0.62 per K block and CTA for 64
+    rows (0.9 for 128), plus a higher fixed cost and the cross-CTA reduction of cut tiles."""
+    kb = K // 128
+    t128 = (N + 127) // 128
+    t256 = (N + 255) // 256
+    if t256 >= 100:
+        tiled = 6.5 + -(-t256 // sms) * kb * 0.69
+    else:
+        tiled = 6.5 + -(-t128 // sms) * kb * 0.37
+    units = t128 * kb
+    ctas = min(sms, max(1, units // 4))
+    per_cta = -(-units // ctas)
+    pieces = -(-kb // max(1, per_cta)) + 1 if per_cta < kb else 1
+    skinny = 11.5 + 0.15 * pieces + per_cta * (0.62 if M <= 64 else 0.9)
+    return skinny < tiled
+
+
 def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, bn=0, max_ctas=0, splits=0,
              hw_scale=False):
     """Block-scaled FP8 GEMM. xq [M,K] e4m3, xs [K/128, ld] fp32; wq [N,K] e4m3, ws [ceil(N/128), K/128] fp32.
@@ -374,10 +395,10 @@ def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, b
     dst = out if out_f32 is None else out_f32
     if hw_scale:
         # power-of-two scales: both kernels let the tensor cores apply them. Skinny stream-K kernel for decode-sized
-        # M, and for mid-sized M when the output has too few tiles to fill the SMs and K is long; tiled kernel
-        # otherwise (256-wide tiles when they fill the SMs). Crossovers are measured.
+        # M and wherever the tiled kernel would leave most SMs idle; tiled kernel otherwise (256-wide tiles when
+        # they fill the SMs).
         t256 = ((M + 127) // 128) * ((N + 255) // 256)
-        skinny = M <= SMALL_M_FP8 or (M <= 64 and t256 < 100 and K >= 16384)
+        skinny = M <= SMALL_M_FP8 or (M <= 128 and _skinny_wins_mx(M, N, K))
         if (skinny or splits != 0) and M <= 128 and bn == 0:
             return _gemm_smallm(2, xq, xs, wq, ws, out, out_f32, bias, residual, M, N, K, splits)
         if MX_TALL_MIN_M > 0 and M >= MX_TALL_MIN_M and bn == 0 and _tall_wins(M, N, K, max_ctas):

@@ -25,6 +25,7 @@ from ..models.common import LogitCandidates, StepInput
 from ..ops import dispatch as ops
 from ..ops import checks as _checks
 from ..ops import native
+from ..utils import logger, nvtx
 from ..utils import native_engine as ne
 from .sampler import DeviceStepError, Sampler, SamplingParams
 from .structured import StructuredOutput
@@ -179,12 +180,24 @@ class ModelRunner:
             if t3.size and (t3[:, 2] != 0).any():
                 self.model.rerotate_blocks(t3)
 
+    def _stage_plan(self, plan) -> torch.Tensor:
+        """The step's device metadata (ids, positions, slots, sequence offsets, lengths, block table, sample rows) in
+        one upload. A scheduler plan writes its image straight into the pinned staging buffer."""
+        if self.cuda and hasattr(plan, "write_step_image"):
+            n = int(plan.step_image_words())
+            slot = self._stage_buffer(n)
+            plan.write_step_image(slot[0].data_ptr(), slot[1])
+            self.h2d_bytes += n * 4
+            dev = slot[0][:n].to(self.device, non_blocking=True)
+            slot[2].record()
+            return dev
+        parts = [plan.input_ids, plan.positions, plan.slots, plan.cu_q, plan.kv_lens, plan.block_table, plan.sample_rows]
+        return self._stage(np.concatenate([np.asarray(p, dtype=np.int32).reshape(-1) for p in parts]))
+
     def build_step(self, plan, extra: Optional[dict] = None) -> StepInput:
         T, nseq = plan.num_tokens, len(plan.seq_ids)
         nsamp = plan.sample_rows.size
-        parts = [plan.input_ids, plan.positions, plan.slots, plan.cu_q, plan.kv_lens, plan.block_table, plan.sample_rows]
-        img = np.concatenate([np.asarray(p, dtype=np.int32).reshape(-1) for p in parts])
-        dev = self._stage(img)
+        dev = self._stage_plan(plan)
         o = 0
 
         def take(n):
@@ -199,10 +212,11 @@ class ModelRunner:
         rows = take(nsamp)
         step = StepInput(input_ids, positions, slots, cu_q, kv_lens, table, plan.num_multi, plan.num_single, T,
                          plan.num_multi_tokens, plan.max_q_len, logits_rows=rows)
-        step.max_kv_len = int(np.max(plan.kv_lens)) if nseq else 0
+        kv_lens = np.asarray(plan.kv_lens)
+        step.max_kv_len = int(kv_lens.max()) if nseq else 0
         step.sample_k = self.candidate_k(plan, extra)
         if plan.num_single:
-            max_kv = int(plan.kv_lens[plan.num_multi:].max())
+            max_kv = int(kv_lens[plan.num_multi:].max())
             step.decode_splits = ops.decode_splits(plan.num_single, self.model.Hkv, max_kv)
         if extra:
             for k, v in extra.items():
@@ -283,15 +297,23 @@ class ModelRunner:
             return None
         bs = next(b for b in self.GRAPH_SIZES if b >= nseq)
         graph, img, logits, mb, _step = self._graph_for(bs, self.candidate_k(plan, None))
-        host = np.zeros(4 * bs + bs * mb, dtype=np.int32)
-        host[0:nseq] = plan.input_ids
-        host[bs:bs + nseq] = plan.positions
-        host[2 * bs:3 * bs] = -1
-        host[2 * bs:2 * bs + nseq] = plan.slots
-        host[3 * bs:3 * bs + nseq] = plan.kv_lens
-        tbl = host[4 * bs:].reshape(bs, mb)
-        tbl[:nseq, :plan.max_blocks] = np.asarray(plan.block_table).reshape(nseq, plan.max_blocks)
-        self._stage(host, out=img)
+        n = 4 * bs + bs * mb
+        if hasattr(plan, "write_decode_image"):
+            slot = self._stage_buffer(n)                  # the plan writes the padded image into pinned memory itself
+            plan.write_decode_image(slot[0].data_ptr(), slot[1], bs, mb)
+            self.h2d_bytes += n * 4
+            img.copy_(slot[0][:n], non_blocking=True)
+            slot[2].record()
+        else:
+            host = np.zeros(n, dtype=np.int32)
+            host[0:nseq] = plan.input_ids
+            host[bs:bs + nseq] = plan.positions
+            host[2 * bs:3 * bs] = -1
+            host[2 * bs:2 * bs + nseq] = plan.slots
+            host[3 * bs:3 * bs + nseq] = plan.kv_lens
+            tbl = host[4 * bs:].reshape(bs, mb)
+            tbl[:nseq, :plan.max_blocks] = np.asarray(plan.block_table).reshape(nseq, plan.max_blocks)
+            self._stage(host, out=img)
         graph.replay()
         self.graph_replays = getattr(self, "graph_replays", 0) + 1
         if isinstance(logits, LogitCandidates):
@@ -602,7 +624,8 @@ class LLMEngine:
         """Runs one engine step. Returns False when there was nothing to run."""
         tm = self.host_ms
         t0 = time.perf_counter()
-        plan = self.scheduler.schedule()
+        with nvtx.annotate("schedule"):
+            plan = self.scheduler.schedule()
         t1 = time.perf_counter()
         ne.report_metric("batch_manager_schedule_ms", (t1 - t0) * 1000.0)
         if plan.events:
@@ -626,11 +649,13 @@ class LLMEngine:
         t3 = time.perf_counter()
         phase = "Prefill" if plan.num_multi else "Decode"
         ne.trace_record(phase, "B", 0, float(plan.num_tokens))
-        logits, self._step_full_logits = self.run_with_extras(plan, extra)
+        with nvtx.annotate(phase):
+            logits, self._step_full_logits = self.run_with_extras(plan, extra)
         t4 = time.perf_counter()
         self.last_logits = logits
         try:
-            tokens, parents, lp_by_seq = self._sample(plan, logits)
+            with nvtx.annotate("sample"):
+                tokens, parents, lp_by_seq = self._sample(plan, logits)
         except DeviceStepError as e:
             self._device_fault(e)
             return True
@@ -693,6 +718,7 @@ class LLMEngine:
             except Exception as e:  # noqa: BLE001 - the loop must survive and fail the affected requests
                 import traceback
                 traceback.print_exc()
+                logger.error(f"engine step failed: {e!r}")
                 self._fail_all(12, f"engine step failed: {e}")
                 ran = False
             if not ran:
@@ -709,6 +735,7 @@ class LLMEngine:
         src/ksana_llm/runtime/llm_runtime.cpp:387-445). With several ranks a wait on a peer that ran out leaves the
         ranks' collective epochs out of step, so the engine also refuses new requests and releases the workers."""
         ne.report_counter("forward_req_error_num", len(self.requests))
+        logger.error(f"device error during an engine step ({len(self.requests)} requests in flight): {err}")
         self._fail_all(12, f"device error during the step: {err}")
         if self.world_size > 1 or err.code == 3:
             self.fatal = str(err)
@@ -718,6 +745,14 @@ class LLMEngine:
                     broadcast_plan(self.control_group, None)
                 except Exception:  # noqa: BLE001 - the workers may be gone already
                     pass
+
+    def on_service_stop(self, reason: str):
+        """Stop hook of the service lifetime (parallel.coordinator): a peer rank is gone, so no step can complete any
+        more. Every request in flight is answered with RET_RUNTIME and new ones are refused."""
+        self.fatal = reason
+        self._stop = True
+        if self.scheduler is not None:
+            self._fail_all(12, f"service stopped: {reason}")
 
     def _fail_all(self, code: int, message: str):
         for req in list(self.requests.values()):

@@ -98,12 +98,12 @@ class Sampler:
     def _upload_params(self, params: List[SamplingParams]):
         """temperature / top-k / top-p / step counters / seeds of all rows in one staged host->device copy."""
         B = len(params)
-        img = np.empty(6 * B + (B & 1), dtype=np.int32)
+        img = np.empty(6 * B, dtype=np.int32)
         img[0:B] = np.array([p.temperature for p in params], dtype=np.float32).view(np.int32)
         img[B:2 * B] = [p.topk for p in params]
         img[2 * B:3 * B] = np.array([p.topp for p in params], dtype=np.float32).view(np.int32)
         img[3 * B:4 * B] = [p.step for p in params]
-        o = 4 * B + (B & 1)                                   # seeds are 64-bit: keep them 8-byte aligned
+        o = 4 * B                                             # seeds are 64-bit: an even word offset keeps them 8-byte aligned
         img[o:o + 2 * B] = np.array([p.seed for p in params], dtype=np.int64).view(np.int32)
         if self._stage is not None:
             dev = self._stage(img)

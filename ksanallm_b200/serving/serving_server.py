@@ -199,6 +199,9 @@ def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExec
 
 def main(argv=None):
     args = args_config(argv)
+    from ..utils import logger
+    logger.install_logging_handler()          # uvicorn / serving records go to the engine's log sink (KLLM_LOG_FILE)
+    logger.info(f"serving_server starting: config {args.config_file}, endpoint {args.endpoint} on {args.host}:{args.port}")
     tokenizer = load_tokenizer(args.tokenizer_dir) if args.tokenizer_dir and os.path.isdir(args.tokenizer_dir) else None
     model = ServingModel(args.config_file, tokenizer=tokenizer)
     plugin_config = PluginConfig(model_dir=args.model_dir, config_file=args.config_file, plugin_name=args.model_type,
@@ -210,6 +213,8 @@ def main(argv=None):
     if rank != 0 or node_rank != 0:
         while model.llm.follow():      # worker ranks: execute broadcast step plans until the stop signal
             pass
+        if getattr(model.llm, "coordinator", None) is not None:
+            model.llm.coordinator.close()
         return
     import uvicorn
     app = create_app(model, tokenizer)

@@ -142,6 +142,16 @@ def test_command_line_clients_against_live_server(server, capsys):
                                        "--slice", "0", "1"])
     assert doc["responses"][0]["response"][0]["tensor"].shape[0] == 2
     assert "perplexity" in capsys.readouterr().out
+    # the example clients (examples/api_client.py, examples/streaming_client.py)
+    import importlib.util
+    for name in ("api_client", "streaming_client"):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(root, "examples", name + ".py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        for extra in ([], ["--stream"]):
+            assert mod.main(["--host", "127.0.0.1", "--port", str(server), "--prompt", "hello there"] + extra) == 0
+        out = capsys.readouterr().out
+        assert ("Answer 0" in out) if name == "api_client" else ("[" in out)
 
 
 def test_prompt_sets_and_prefix_cache_reader(tmp_path):

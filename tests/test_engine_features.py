@@ -253,3 +253,25 @@ def test_forked_siblings_survive_swap_preemption():
         assert a.outputs[0].tokens == a.outputs[1].tokens == a.outputs[2].tokens
     st = tight.scheduler.stats()
     assert st["preempt_swap"] > 0 and st["swap_in"] > 0
+
+
+def test_warmup_request_runs_at_start_unless_disabled(monkeypatch):
+    """The engine answers one short request from its constructor (kernels, workspaces and collectives set up before
+    the first user request); DISABLE_WARMUP=1 skips it."""
+    from ksanallm_b200.config import EngineConfig
+    from ksanallm_b200.llm import LLM
+    from ksanallm_b200.models.weights import RandomSource
+
+    def build():
+        ec = EngineConfig()
+        ec.batch_scheduler.max_token_len = 64
+        ec.block_manager.device_blocks_num = 32
+        return LLM(ec, tiny_model_cfg(), weights=RandomSource(seed=0, std=0.2), device="cpu", dtype=torch.float32)
+
+    monkeypatch.setenv("DISABLE_WARMUP", "1")
+    assert build().engine.steps == 0
+    monkeypatch.delenv("DISABLE_WARMUP")
+    llm = build()
+    assert llm.engine.steps == 2 and llm.engine.scheduler.idle()
+    st = llm.engine.scheduler.stats()
+    assert st["total_requests"] == 1 and st["finished"] == 1

@@ -369,3 +369,64 @@ def test_import_compatibility_package():
     assert ksana_llm.AutoModel is AutoModel
     assert {"AutoModel", "EndpointConfig", "PluginConfig"} <= set(ksana_llm.__all__)
     assert ksana_llm.EndpointConfig().type in ("python", "PYTHON", "python ") or hasattr(ksana_llm.EndpointConfig(), "type")
+
+
+def test_lost_worker_rank_ends_the_service(tmp_path):
+    """Failure detection reaches the engine (host only): rank 1 of a two-rank CPU engine exits between two steps; rank
+    0's liveness monitor sees the closed control connection, the requests in flight are answered with RET_RUNTIME and
+    the process leaves with a non-zero code instead of waiting forever in the step-plan broadcast."""
+    import json
+    import socket
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    out = str(tmp_path / "lifetime.json")
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), KSANA_CONTROL_PORT=str(port + 1), KSANA_HEARTBEAT_INTERVAL_MS="100",
+                   KSANA_HEARTBEAT_TIMEOUT_MS="2000", OMP_NUM_THREADS="1", DISABLE_WARMUP="1", KLLM_LOG_FILE="stderr")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(root, "tests", "lifetime_worker.py"), out], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    assert procs[1].returncode == 0, outs[1][-2000:]
+    assert procs[0].returncode == 1, outs[0][-3000:]
+    got = json.load(open(out))
+    assert "lost" in got["reason"] and got["fatal"]
+    assert all(code == 12 and done for code, done, _ in got["statuses"]), got
+    assert "service shutdown" in outs[0]
+
+
+def test_native_logger_levels_file_and_python_bridge(tmp_path):
+    """KLLM_LOG_LEVEL / KLLM_LOG_FILE semantics of the native logger and the Python bridge on top of it."""
+    import logging
+    from ksanallm_b200.utils import logger
+    path = str(tmp_path / "logs" / "engine.log")          # the directory is created on demand
+    old_file, old_level = logger.log_file(), ne.log_level()
+    try:
+        logger.set_file(path)
+        logger.set_level("WARNING")
+        logger.info("not written")
+        logger.warning("disk almost full")
+        logger.error("step failed")
+        assert not ne.log_enabled(logger.INFO) and ne.log_enabled(logger.ERROR)
+        logger.set_level("DEBUG")
+        logger.debug("details")
+        h = logger.NativeLogHandler()
+        lg = logging.getLogger("ksana-test")
+        lg.addHandler(h)
+        lg.setLevel(logging.INFO)
+        lg.info("from python logging %d", 7)
+        lg.removeHandler(h)
+        logger.set_file("stderr")
+        text = open(path).read().splitlines()
+    finally:
+        logger.set_file(old_file)
+        ne.set_log_level(["DEBUG", "INFO", "WARNING", "ERROR", "FATAL"][old_level])
+    assert len(text) == 4 and "not written" not in "".join(text)
+    assert " WARNING " in text[0] and text[0].endswith("] disk almost full") and "test_host_components.py:" in text[0]
+    assert " ERROR " in text[1] and " DEBUG " in text[2]
+    assert "from python logging 7" in text[3] and "ksana-test" in text[3]

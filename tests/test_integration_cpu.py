@@ -240,3 +240,26 @@ def test_forward_perplexity_matches_hugging_face(served):
         logp = torch.log_softmax(model(torch.tensor([ids])).logits[0].float(), -1)
     nll = -sum(float(logp[i, ids[i + 1]]) for i in range(len(ids) - 1)) / (len(ids) - 1)
     assert math.isclose(got, math.exp(nll), rel_tol=2e-3)
+
+
+def test_cpp_forward_client_against_the_live_server(served):
+    """The stand-alone C++ /forward client (own msgpack codec, plain sockets) posts its two-request batch - a text
+    prompt and a token list, each with a logits GATHER_TOKEN_ID target - and prints the probabilities it got back."""
+    import re
+    from urllib.parse import urlparse
+    from ksanallm_b200.build import build_client
+    url, model, tok = served
+    u = urlparse(url)
+    exe = str(build_client())
+    r = subprocess.run([exe, "-s", u.hostname, "-p", str(u.port), "-a", "forward"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0, r.stdout + r.stderr
+    blocks = re.findall(r"input_token_ids : \[ ([\d ]+)\], target_name : logits, tensor : \n\[ ([-\d. e]+)\]", r.stdout)
+    assert len(blocks) == 2, r.stdout
+    second_ids = [int(x) for x in blocks[1][0].split()]
+    assert second_ids == [1, 22, 13]
+    # slice (-3, -2) of a three-token input = positions 0 and 1: the probabilities of tokens 22 and 13 given their prefixes
+    probs = [float(x) for x in blocks[1][1].split()]
+    with torch.no_grad():
+        p = torch.softmax(model(torch.tensor([second_ids])).logits[0].float(), -1)
+    assert len(probs) == 2 and abs(probs[0] - float(p[0, 22])) < 2e-3 and abs(probs[1] - float(p[1, 13])) < 2e-3
+    assert "request duration:" in r.stdout
