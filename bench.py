@@ -40,13 +40,18 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.idx, self.proc, self.lines = gpu_index, None, []
+    def __init__(self, gpu_index: int, enabled: bool = True):
+        """``enabled`` False (every rank but 0 in a multi-GPU run): no sampler process. One nvidia-smi per rank would
+        query the driver eight times every 200 ms and show up as launch latency in the very region it observes; rank 0
+        samples its own GPU, which runs the same kernels as the others."""
+        self.idx, self.proc, self.lines, self.enabled = gpu_index, None, [], enabled
 
     def start(self):
+        if not self.enabled:
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "250"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:  # noqa: BLE001
@@ -90,8 +95,10 @@ def llama3_70b():
 def tp_check(rank, world, dev):
     """Numerics of the tensor-parallel paths at this GPU count, on the real layer shapes: a 2-layer model of the
     headline architecture runs one prefill step (4 x 256 tokens) and one decode step (64 sequences) through the fused
-    peer-memory path and through the NCCL path; returns the relative error of the logits of the fused path against
-    the NCCL path (both bf16, so rounding differs between them by design)."""
+    peer-memory path and through the NCCL path; returns the relative errors of the fused path's logits against the
+    NCCL path's, with bf16 weights (the two paths differ only in where sums are rounded) and with the block-FP8
+    weights of the benchmark (every e4m3 rounding that flips between the paths moves an activation by up to 6 %, so
+    two correct paths sit several per cent apart)."""
     import torch
     import torch.distributed as dist
     from benchmarks.step_breakdown import build_step
@@ -101,28 +108,31 @@ def tp_check(rank, world, dev):
     mc = llama3_70b()
     mc.num_layers = 2
     out = {}
-    logits = {}
-    for backend in ("fused", "nccl"):
-        comm = TPComm(dist.group.WORLD, rank, world, backend, dev, max_tokens=2048, hidden=mc.hidden_size)
-        model = build_model(mc, RandomSource(seed=5, on_device=True), rank, world, comm, dev, torch.bfloat16, "fp8_block",
-                            max_positions=1024)
-        model.allocate_kv_cache(64 * 16 + 64, 16)
-        with torch.inference_mode():
-            for phase, batch in (("prefill", 4), ("decode", 64)):
-                step, _ = build_step(torch, model, phase, batch, 200, 256, 16)
-                torch.manual_seed(7)
-                step.input_ids.copy_(torch.randint(0, mc.vocab_size, step.input_ids.shape, device=dev, dtype=torch.int32))
-                lg = model.forward(step)
-                logits[(backend, phase)] = lg.float().clone()
-        torch.cuda.synchronize()
-        native.check_err_flag(dev)
-        del model, comm
-        torch.cuda.empty_cache()
-        dist.barrier()
-    for phase in ("prefill", "decode"):
-        a, b = logits[("fused", phase)], logits[("nccl", phase)]
-        out[phase] = float((a - b).norm() / b.norm().clamp_min(1e-12))
+    for quant in ("bf16", "fp8_block"):
+        logits = {}
+        for backend in ("fused", "nccl"):
+            comm = TPComm(dist.group.WORLD, rank, world, backend, dev, max_tokens=2048, hidden=mc.hidden_size)
+            model = build_model(mc, RandomSource(seed=5, on_device=True), rank, world, comm, dev, torch.bfloat16,
+                                None if quant == "bf16" else quant, max_positions=1024)
+            model.allocate_kv_cache(64 * 16 + 64, 16)
+            with torch.inference_mode():
+                for phase, batch in (("prefill", 4), ("decode", 64)):
+                    step, _ = build_step(torch, model, phase, batch, 200, 256, 16)
+                    torch.manual_seed(7)
+                    step.input_ids.copy_(torch.randint(0, mc.vocab_size, step.input_ids.shape, device=dev, dtype=torch.int32))
+                    logits[(backend, phase)] = model.forward(step).float().clone()
+            torch.cuda.synchronize()
+            native.check_err_flag(dev)
+            del model, comm
+            torch.cuda.empty_cache()
+            dist.barrier()
+        for phase in ("prefill", "decode"):
+            a, b = logits[("fused", phase)], logits[("nccl", phase)]
+            out[f"{quant}_{phase}"] = round(float((a - b).norm() / b.norm().clamp_min(1e-12)), 5)
     return out
+
+
+TP_CHECK_LIMITS = {"bf16": 3e-2, "fp8_block": 0.15}
 
 
 def run_library_baseline(args):
@@ -161,7 +171,7 @@ def run_library_baseline(args):
     for _ in range(args.warmup):
         one_step()
     barrier()
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, enabled=rank == 0)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -261,8 +271,7 @@ def main():
         tp_dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(tp_dev)
         tp_numerics = tp_check(rank, world, tp_dev)
-        worst = max(tp_numerics.values())
-        if worst > 3e-2:
+        if any(v > TP_CHECK_LIMITS[k.rsplit("_", 1)[0]] for k, v in tp_numerics.items()):
             if rank == 0:
                 print(json.dumps({"error": "tensor-parallel numerics check failed", "tp_check": tp_numerics}))
             sys.stdout.flush()
@@ -297,7 +306,7 @@ def main():
     barrier()
     latency["ttft"].clear()
     latency["tpot"].clear()
-    sampler = ClockSampler(dev.index or 0)
+    sampler = ClockSampler(dev.index or 0, enabled=rank == 0)
     sampler.start()
     l0, h0, d0 = native.launch_count(), llm.engine.runner.h2d_bytes, llm.engine.sampler.d2h_bytes
     llm.engine.host_ms.clear()
@@ -352,7 +361,7 @@ def main():
             "p50_ttft_ms": statistics.median(latency["ttft"]) if latency["ttft"] else None,
             "p50_tpot_ms": statistics.median(latency["tpot"]) if latency["tpot"] else None,
             "clocks": clocks, "gpu_launches": launches,
-            "tp_check": ({"rel_err_fused_vs_nccl": tp_numerics, "limit": 3e-2} if tp_numerics is not None else None),
+            "tp_check": ({"rel_err_fused_vs_nccl": tp_numerics, "limits": TP_CHECK_LIMITS} if tp_numerics is not None else None),
             "graph_replays": getattr(llm.engine.runner, "graph_replays", 0),
             "host_ms_per_engine_step": {k: round(v / max(1, host_ms.get("steps", 1)), 3) for k, v in host_ms.items() if k != "steps"},
             "engine_steps": host_ms.get("steps", 0),

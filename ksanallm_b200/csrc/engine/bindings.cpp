@@ -268,6 +268,19 @@ PYBIND11_MODULE(_ksana_engine, m) {
         }
         return EventsToList(ev);
       }, py::arg("plan"), py::arg("tokens"), py::arg("parents") = std::vector<int64_t>())
+      .def("can_pipeline", &Scheduler::CanPipeline)
+      .def("advance", [](Scheduler& s, const StepPlan& plan) {
+        py::gil_scoped_release rel;
+        s.Advance(plan);
+      })
+      .def("resolve", [](Scheduler& s, const StepPlan& plan, const std::vector<int>& tokens) {
+        std::vector<SeqEvent> ev;
+        {
+          py::gil_scoped_release rel;
+          s.Resolve(plan, tokens, &ev);
+        }
+        return EventsToList(ev);
+      })
       .def("finish_sequence", [](Scheduler& s, int64_t seq_id, int keep, int code, const std::string& msg) {
         std::vector<SeqEvent> ev;
         s.FinishSequence(seq_id, keep, code, msg, &ev);

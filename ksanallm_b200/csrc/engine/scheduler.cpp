@@ -324,10 +324,11 @@ bool Scheduler::Schedule(StepPlan* plan) {
 
   // ------------------------------------------------------------------ running queue
   int num_decodes = 0;
-  for (auto& s : running_) num_decodes += (static_cast<int>(s->tokens.size()) - s->kv_cached == 1);
+  for (auto& s : running_) num_decodes += (!s->draining && static_cast<int>(s->tokens.size()) - s->kv_cached == 1);
   int cap = StepTokenCap(num_decodes);
   int step_tokens = 0;
   for (auto& s : running_) {
+    if (s->draining) { s->chunk = 0; continue; }     // its last token is still on the device: nothing more to run
     const int remaining = static_cast<int>(s->tokens.size()) - s->kv_cached;
     int chunk = std::min(remaining, std::max(cap - step_tokens, 0));
     if (chunk < remaining) chunk = ((s->kv_cached + chunk) / B) * B - s->kv_cached;   // chunks end on block boundaries
@@ -577,6 +578,64 @@ void Scheduler::PostStep(const StepPlan& plan, const std::vector<SampledToken>& 
     if (!CheckFinishLocked(s, sampled[i].token, ev)) {
       ev->push_back({s->seq_id, s->req_id, s->index, sampled[i].token, false, 0, ""});
     }
+  }
+  running_.erase(std::remove_if(running_.begin(), running_.end(),
+                                [](const SeqPtr& s) { return s->state == SeqState::FINISHED; }),
+                 running_.end());
+}
+
+bool Scheduler::CanPipeline(const StepPlan& plan) {
+  std::lock_guard<std::mutex> g(mu_);
+  for (int64_t id : plan.sample_seq_ids) {
+    auto it = by_id_.find(id);
+    if (it == by_id_.end()) continue;
+    const Sequence& s = *it->second;
+    if (s.forked_pending || s.cfg->num_beams > 1) return false;
+    auto git = groups_.find(s.req_id);
+    if (git != groups_.end() && git->second.size() > 1) return false;      // siblings fork on sampled results
+  }
+  return true;
+}
+
+void Scheduler::Advance(const StepPlan& plan) {
+  std::lock_guard<std::mutex> g(mu_);
+  for (size_t i = 0; i < plan.seq_ids.size(); ++i) {
+    auto it = by_id_.find(plan.seq_ids[i]);
+    if (it == by_id_.end()) continue;
+    SeqPtr s = it->second;
+    if (s->state != SeqState::RUNNING) continue;
+    s->kv_cached += plan.q_lens[i];
+    s->chunk = 0;
+    // every token up to kv_cached is a real one here (the previous step was resolved before this call)
+    s->promoted = CacheOf(*s).Promote(s->tokens, &s->blocks, s->kv_cached, s->promoted);
+  }
+  for (int64_t id : plan.sample_seq_ids) {
+    auto it = by_id_.find(id);
+    if (it == by_id_.end()) continue;
+    SeqPtr s = it->second;
+    if (s->state == SeqState::FINISHED || s->token_pending) continue;
+    s->tokens.push_back(-1);
+    s->token_pending = true;
+    const int generated = static_cast<int>(s->tokens.size()) - s->prompt_len;
+    s->draining = generated >= s->cfg->max_new_tokens || static_cast<int>(s->tokens.size()) >= cfg_.max_token_len;
+  }
+}
+
+void Scheduler::Resolve(const StepPlan& plan, const std::vector<int>& tokens, std::vector<SeqEvent>* ev) {
+  std::lock_guard<std::mutex> g(mu_);
+  const int64_t now = NowMs();
+  for (size_t i = 0; i < plan.sample_seq_ids.size() && i < tokens.size(); ++i) {
+    auto it = by_id_.find(plan.sample_seq_ids[i]);
+    if (it == by_id_.end()) continue;                 // finished or aborted meanwhile: the row was wasted work
+    SeqPtr s = it->second;
+    if (s->state == SeqState::FINISHED || !s->token_pending || s->tokens.empty()) continue;
+    s->tokens.back() = tokens[i];
+    s->token_pending = false;
+    s->draining = false;
+    if (s->sampled == 0) s->first_token_ms = now;
+    ++s->sampled;
+    ++stats_.output_tokens;
+    if (!CheckFinishLocked(s, tokens[i], ev)) ev->push_back({s->seq_id, s->req_id, s->index, tokens[i], false, 0, ""});
   }
   running_.erase(std::remove_if(running_.begin(), running_.end(),
                                 [](const SeqPtr& s) { return s->state == SeqState::FINISHED; }),

@@ -65,6 +65,11 @@ struct Sequence {
   int64_t arrive_ms = 0;
   int64_t first_token_ms = 0;
   bool aborted = false;
+  // Pipelined stepping (see Scheduler::Advance / Resolve): the last element of `tokens` is a placeholder (-1) for a
+  // token that was sampled on the device by a step whose results the host has not read yet; `draining`: that token
+  // is certainly the sequence's last one (length limits), so it is not scheduled again while it is outstanding
+  bool token_pending = false;
+  bool draining = false;
   bool forked_pending = false;   // sibling that waits for its leader's prefill
   int64_t leader = -1;
   SeqState state = SeqState::WAITING;
@@ -143,6 +148,18 @@ class Scheduler {
   bool Schedule(StepPlan* plan);
   // Consumes the step's sampled tokens (one per plan.sample_seq_ids entry, same order).
   void PostStep(const StepPlan& plan, const std::vector<SampledToken>& sampled, std::vector<SeqEvent>* events);
+
+  // Pipelined stepping: PostStep in two halves, so that the next step can be planned and launched while the device
+  // still runs this one. Advance(plan) - right after the step is launched - moves the cached lengths forward and
+  // gives every sampling sequence a placeholder token (the real one is taken from the sampler's device buffer by the
+  // next step); the following Schedule() then plans those sequences' next decode row. Resolve(plan, tokens) - when
+  // the step's tokens have reached the host - puts the real tokens in place, runs the finish checks and reports the
+  // events PostStep would have. A sequence that turns out to be finished may already be part of the step in flight;
+  // its row there is wasted and its result ignored. Only for plans whose sampling sequences are all plain (one
+  // sequence per request, no beams): CanPipeline(plan) says so.
+  bool CanPipeline(const StepPlan& plan);
+  void Advance(const StepPlan& plan);
+  void Resolve(const StepPlan& plan, const std::vector<int>& tokens, std::vector<SeqEvent>* events);
 
   // Runtime hooks: stop strings and structured output need the tokenizer, which lives outside.
   void FinishSequence(int64_t seq_id, int keep_tokens, int code, const std::string& message,

@@ -24,6 +24,8 @@
 // without the reverse cache copy the latter needs.
 #include "sm100_ptx.cuh"
 #include "pdl.cuh"
+#include "fp8_scale.cuh"
+#include <cuda_fp8.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
@@ -56,7 +58,30 @@ struct AttnParams {
   // decode split workspace
   float* part_o; float* part_ml; int num_splits;
   int* err;                              // device word set when a bounded wait gave up
+  // decode, head dim 128: also emit the output as the FP8 operand of the next GEMM (e4m3 values [T][Hq*D] and one
+  // power-of-two scale per row and head, [Hq][oscale_ld]), quantised from the bf16-rounded values exactly as the
+  // stand-alone quantiser would
+  uint8_t* outq; float* oscale; int oscale_ld;
 };
+
+// One head row of D = 128 outputs held one per thread of a 128-thread block: rounds to bf16, stores it (if `out`),
+// and stores the row's e4m3 values and scale. Every thread of the block must call it.
+__device__ __forceinline__ void store_head_row_q(const AttnParams& p, int s, int head, int d, float v, float* red4) {
+  const __nv_bfloat16 b = __float2bfloat16(v);
+  const float fb = __bfloat162float(b);
+  if (p.out) p.out[static_cast<size_t>(s) * p.out_stride + head * 128 + d] = b;
+  float am = fabsf(fb);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  __syncthreads();                                   // red4 may still be read from the previous row
+  if ((threadIdx.x & 31) == 0) red4[threadIdx.x >> 5] = am;
+  __syncthreads();
+  am = fmaxf(fmaxf(red4[0], red4[1]), fmaxf(red4[2], red4[3]));
+  const float sc = fp8_group_scale(am);
+  const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(fb * (1.f / sc), __NV_SATFINITE, __NV_E4M3);
+  p.outq[(static_cast<size_t>(s) * p.Hq + head) * 128 + d] = q;
+  if (d == 0) p.oscale[static_cast<size_t>(head) * p.oscale_ld + s] = sc;
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -382,6 +407,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams
   uint8_t* smem_attn = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_attn_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t full_bar[kKvStages];
   __shared__ uint32_t abort_word;
+  __shared__ float red4[4];
   bf16* qs = reinterpret_cast<bf16*>(smem_attn);            // 16 x D
   bf16* ks = qs + 16 * D;                                   // kKvStages x (64 x D)
   bf16* vs = ks + kKvStages * kTileTok * D;
@@ -503,7 +529,11 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams
     }
     const int head = g * G + r;
     if (p.num_splits == 1) {
-      p.out[static_cast<size_t>(s) * p.out_stride + head * D + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+      const float v = ll > 0.f ? acc / ll : 0.f;
+      if constexpr (D == 128) {
+        if (p.outq) { store_head_row_q(p, s, head, d, v, red4); continue; }   // (D == blockDim: r is uniform per pass)
+      }
+      p.out[static_cast<size_t>(s) * p.out_stride + head * D + d] = __float2bfloat16(v);
     } else {
       const size_t base = (static_cast<size_t>(s) * p.Hq + head) * p.num_splits + split;
       p.part_o[base * D + d] = acc;
@@ -517,6 +547,7 @@ template <int D>
 __global__ void decode_reduce_kernel(const AttnParams p) {
   pdl_trigger();
   pdl_wait();
+  __shared__ float red4[4];
   const int head = blockIdx.x, s = blockIdx.y;
   const size_t base = (static_cast<size_t>(s) * p.Hq + head) * p.num_splits;
   float mm = -INFINITY;
@@ -529,7 +560,11 @@ __global__ void decode_reduce_kernel(const AttnParams p) {
       acc += p.part_o[(base + k) * D + d] * f;
       ll += p.part_ml[(base + k) * 2 + 1] * f;
     }
-    p.out[static_cast<size_t>(s) * p.out_stride + head * D + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+    const float v = ll > 0.f ? acc / ll : 0.f;
+    if constexpr (D == 128) {
+      if (p.outq) { store_head_row_q(p, s, head, d, v, red4); continue; }     // 128 threads: one pass, every thread in it
+    }
+    p.out[static_cast<size_t>(s) * p.out_stride + head * D + d] = __float2bfloat16(v);
   }
 }
 
@@ -651,8 +686,10 @@ extern "C" int ksana_paged_decode(const void* q, long long q_stride, void* out, 
                                   const void* cache, long long block_stride, int block_tokens, const int* block_table,
                                   int table_stride, const int* kv_lens, const float* alibi, int B, int Hq, int Hkv,
                                   int D, float scale, int cache_fp8, float k_scale, float v_scale, int num_splits,
-                                  float* part_o, float* part_ml, long long cache_rows, int* err, cudaStream_t st) {
+                                  float* part_o, float* part_ml, long long cache_rows, void* outq, float* oscale,
+                                  int oscale_ld, int* err, cudaStream_t st) {
   if (B <= 0) return 0;
+  if (outq && (D != 128 || !oscale)) return -13;
   if (Hq % Hkv || Hq / Hkv > 16) return -10;
   if (num_splits < 1) num_splits = 1;
   if (num_splits > 1 && (!part_o || !part_ml)) return -12;
@@ -662,6 +699,7 @@ extern "C" int ksana_paged_decode(const void* q, long long q_stride, void* out, 
   p.block_table = block_table; p.table_stride = table_stride; p.cu_q = nullptr; p.kv_lens = kv_lens; p.alibi = alibi;
   p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.44269504f; p.k_scale = k_scale; p.v_scale = v_scale;
   p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml; p.err = err;
+  p.outq = static_cast<uint8_t*>(outq); p.oscale = oscale; p.oscale_ld = oscale_ld;
   if (D == 128) return dispatch_decode<128>(p, cache_fp8, cache_rows, B, st);
   if (D == 64) return dispatch_decode<64>(p, cache_fp8, cache_rows, B, st);
   return -11;

@@ -38,6 +38,7 @@ struct CommPeers {
   void* data[kMaxRanks];          // peers' symmetric data buffers (same layout on every rank)
   uint32_t* flags[kMaxRanks];     // peers' flag pads
   int rank, size;
+  int spin_limit;                 // polls a wait on a peer's flag may take before it gives up (see kSpinLimit)
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -67,7 +68,7 @@ __device__ __forceinline__ bool signal_and_wait(const CommPeers& c, int kind, ui
     int it = 0;
     // signed distance handles wrap-around of the 32-bit epoch
     while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
-      if (++it > kSpinLimit) { s_ok = 0; if (err) atomicExch(err, 3); break; }
+      if (++it > c.spin_limit) { s_ok = 0; if (err) atomicExch(err, 3); break; }
       __nanosleep(64);
     }
   }
@@ -199,6 +200,18 @@ __device__ __forceinline__ void reduce_norm_body(const ReduceNormParams& p) {
   const uint8_t* base = static_cast<const uint8_t*>(c.data[c.rank]) + p.slots_off;
   float v[NV][8];
   float s = 0.f, s2 = 0.f;
+  const bool in_switch = p.mc != nullptr && (p.gather & 4);
+  // in-switch sums of all of this thread's vectors are requested up front: one round trip through the switch for
+  // the row instead of one per vector (the requests are what keeps the links busy)
+  uint4 sw[NV];
+  if (in_switch) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < nvec)
+        sw[j] = multimem_ld_reduce_bf16x8(p.mc + p.slots_off + (static_cast<size_t>(row) * p.H + static_cast<size_t>(i) * 8) * 2);
+    }
+  }
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int i = threadIdx.x + j * blockDim.x;
@@ -211,12 +224,11 @@ __device__ __forceinline__ void reduce_norm_body(const ReduceNormParams& p) {
       }
       // all loads first (peer loads in pull mode: one NVLink round trip, not one per rank), then a fixed summation
       // order so that every rank produces the same bits
-      const bool in_switch = p.mc != nullptr && (p.gather & 4);
       if (in_switch) {
-        // every rank's partial row sits at the same offset of its symmetric buffer: the switch returns their sum
+        // every rank's partial row sits at the same offset of its symmetric buffer: the switch returned their sum
         // (fp32 accumulation, rounded to bf16 once)
         float f[8];
-        unpack8c(multimem_ld_reduce_bf16x8(p.mc + p.slots_off + (static_cast<size_t>(row) * p.H + static_cast<size_t>(i) * 8) * 2), f);
+        unpack8c(sw[j], f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] += f[e];
       }
@@ -415,8 +427,11 @@ __global__ void allgather_pull_kernel(const CommPeers c, uint32_t* ctrs, long lo
   end_epoch(ctrs, 3, epoch);
 }
 
+static int g_spin_limit = kSpinLimit;
+
 static CommPeers make_peers(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs, int rank, int size) {
   CommPeers c{};
+  c.spin_limit = g_spin_limit;
   for (int i = 0; i < size && i < kMaxRanks; ++i) {
     c.data[i] = reinterpret_cast<void*>(data_ptrs[i]);
     c.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
@@ -429,6 +444,11 @@ static CommPeers make_peers(const unsigned long long* data_ptrs, const unsigned 
 }  // namespace ksana
 
 using namespace ksana;
+
+// Budget of every wait on a peer's flag, in polls of about 0.1 us each (default 2^20, about a second; <= 0 restores
+// the default). A wait that runs out sets the device error word to 3 and the kernel returns without touching the
+// data that depended on the peer; the context stays usable. Failure-detection tests use a budget of a millisecond.
+extern "C" void ksana_comm_set_spin_limit(int polls) { g_spin_limit = polls > 0 ? polls : kSpinLimit; }
 
 // Reduce the partial slots that the peers' GEMM epilogues pushed, add the residual, normalise, optionally
 // quantise and all-gather. See ReduceNormParams. Launches 1 kernel (2 in gather mode).

@@ -459,6 +459,19 @@ __global__ void swap_blocks_kernel(uint4* __restrict__ cache, uint4* __restrict_
   }
 }
 
+// ids[rows[i]] = prev_tokens[src[i]]: a pipelined step takes the input ids of its decode rows straight from the
+// previous step's sampler output on the device (the host has not read those tokens yet).
+__global__ void patch_ids_kernel(int* __restrict__ ids, const int* __restrict__ rows, const int* __restrict__ src,
+                                 const int* __restrict__ prev_tokens, int n, int n_ids, int n_prev, int* err) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int r = rows[i], sidx = src[i];
+  if (r < 0 || r >= n_ids || sidx < 0 || sidx >= n_prev) { guard_report(err, kGuardGatherRow, r < 0 || r >= n_ids ? r : sidx); return; }
+  ids[r] = prev_tokens[sidx];
+}
+
 // out = a + b (+ bias), bf16 (used for unfused residual paths and the baseline backend)
 __global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, const bf16* __restrict__ bias,
                            bf16* __restrict__ out, long long nvec_total, int nvec_row) {
@@ -648,6 +661,13 @@ extern "C" int ksana_swap_blocks(void* cache, void* pool, const int* pairs, int 
   swap_blocks_kernel<<<dim3(n, 16), 256, 0, st>>>((uint4*)cache, (uint4*)pool, pairs, block_bytes / 16, dir, num_blocks,
                                                   num_pool_blocks, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int ksana_patch_ids(int* ids, const int* rows, const int* src, const int* prev_tokens, int n, int n_ids,
+                               int n_prev, int* err, cudaStream_t st) {
+  if (n <= 0) return 0;
+  return launch_pdl(patch_ids_kernel, dim3((n + 127) / 128), dim3(128), 0, st, ids, rows, src, prev_tokens, n, n_ids,
+                    n_prev, err) == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int ksana_add(const void* a, const void* b, const void* bias, void* out, long long M, int H,

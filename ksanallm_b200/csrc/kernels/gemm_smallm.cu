@@ -158,6 +158,25 @@ __device__ __forceinline__ void store_rows_staged(const SmallMParams& p, uint8_t
     }
   }
   asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (p.push_n) {
+    // tensor-parallel push mode: the rows go to this rank's receive slot in every rank's memory (its own included),
+    // 256 contiguous bytes per row and tile, written as 16-byte vectors by 16 neighbouring threads: posted stores
+    // over NVLink that overlap with the tiles still being computed
+    for (int i = t; i < nrows * 16; i += 128) {
+      const int r = i >> 4, c = i & 15;
+      const size_t off = static_cast<size_t>(row0 + r) * p.ldd + n0 + c * 8;
+      const uint4 v = st4[i];
+      if (n0 + c * 8 + 8 <= p.N) {
+        for (int q = 0; q < p.push_n; ++q) *reinterpret_cast<uint4*>(p.push[q] + off) = v;
+      } else {
+        for (int q = 0; q < p.push_n; ++q)
+          for (int e = 0; e < 8; ++e)
+            if (n0 + c * 8 + e < p.N) p.push[q][off + e] = stb[i * 8 + e];
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    return;
+  }
   for (int i = t; i < nrows * 16; i += 128) {
     const int r = i >> 4, c = i & 15;
     __nv_bfloat16* dst = p.D + static_cast<size_t>(row0 + r) * p.ldd + n0 + c * 8;
@@ -205,7 +224,7 @@ template <int NR>
 __device__ __forceinline__ void store_rows(const SmallMParams& p, uint8_t* out_stage, int tile, int nrow, int row0,
                                            int nrows, const float (&v)[NR]) {
   if (nrows <= 0) return;
-  if (p.vec_out && !p.out_f32 && !p.push_n) store_rows_staged<NR>(p, out_stage, tile, nrow, row0, nrows, v);
+  if (p.vec_out && !p.out_f32) store_rows_staged<NR>(p, out_stage, tile, nrow, row0, nrows, v);
   else store_rows_scalar<NR>(p, tile, nrow, row0, nrows, v);
 }
 
@@ -263,9 +282,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // barriers, TMEM and the launch itself overlapped the previous kernel's tail; its results (activations, scales,
-  // residual, the split-K counters) are read only from here on
-  pdl_wait();
+  // Barriers, TMEM and the launch itself overlapped the previous kernel's tail (programmatic dependent launch). What
+  // the previous kernel produced - activations, their scales, the residual, the split-K counters - is read only
+  // after pdl_wait(); every role calls it before its first such access. The weights are never written while the
+  // engine runs, so the producer fills the ring with weight tiles before it waits: when the activations arrive
+  // (for instance from the cross-GPU reduction that precedes this GEMM), the first MMAs find their weights loaded.
 
   if (warp == 0) {
     if (lane == 0) {
@@ -273,9 +294,27 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       tma_prefetch_desc(&tma_x);
       int stage = 0; uint32_t phase = 0;
       [[maybe_unused]] int pslot = 0; [[maybe_unused]] uint32_t pphase = 0;       // kind 3: packed ring
+      int pre = 0;                            // K blocks whose weight tile is already on its way
+      if constexpr (KIND != 3) {
+        long long u2 = u_begin; Segment s2;
+        while (pre < Cfg::kStages && next_segment(u2, u_end, num_kb, s2)) {
+          for (int kb = s2.kb0; kb < s2.kb1 && pre < Cfg::kStages; ++kb, ++pre) {
+            mbar_expect_tx(&full_bar[pre], Cfg::kStageBytes);
+            tma_load_2d(smem + pre * Cfg::kStageBytes, &tma_w, &full_bar[pre], kb * Cfg::kElems, s2.tile * 128);
+          }
+        }
+      }
+      pdl_wait();
+      tma_prefetch_desc(&tma_x);
+      int issued = 0;
       long long u = u_begin; Segment sg; bool ok = true;
       while (ok && next_segment(u, u_end, num_kb, sg)) {
-        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++issued) {
+          if (issued < pre) {                 // first round of the ring: the weight tile was requested above
+            tma_load_2d(smem + stage * Cfg::kStageBytes + Cfg::kWBytes, &tma_x, &full_bar[stage], kb * Cfg::kElems, 0);
+            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if constexpr (KIND == 3) {
             // every fourth K block of a segment: the packed tile of that block and the next three goes into the
             // packed ring; the expansion warps turn it into the bf16 tiles of the stages
@@ -300,6 +339,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       }
     }
   } else if (warp == 1) {
+    pdl_wait();
     if (lane == 0) {
       constexpr bool kBf16 = KIND == 0 || KIND == 3;
       constexpr uint32_t idesc = kBf16 ? make_idesc(128, MP, 1, 1) : make_idesc(128, MP, 0, 0);
@@ -377,6 +417,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
     __syncwarp();
   } else if (warp >= 6) {
+    pdl_wait();
     if constexpr (KIND == 3) {
       // ---------------------------------------------------------- 4-bit weight expansion (kind 3), warps 6..13
       // Two threads share weight row r of the tile: per K block each reads 16 of its 32 packed bytes (32 levels) from the
@@ -555,6 +596,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
+    pdl_wait();
     const int q = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     const int nrow = q * 32 + lane;          // output feature inside the tile
@@ -911,6 +953,10 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
   p.err = err_flag;
   p.vec_out = D != nullptr && (reinterpret_cast<uintptr_t>(D) & 15) == 0 && (ldd % 8) == 0 &&
               (residual == nullptr || ((reinterpret_cast<uintptr_t>(residual) & 15) == 0 && (ldr % 8) == 0));
+  if (push_n > 0) {
+    p.vec_out = (ldd % 8) == 0 && residual == nullptr;
+    for (int i = 0; i < push_n && i < 8; ++i) p.vec_out = p.vec_out && (push_ptrs[i] & 15) == 0;
+  }
   p.prof = g_smallm_prof;
   for (int i = 0; i < push_n && i < 8; ++i) p.push[i] = reinterpret_cast<__nv_bfloat16*>(push_ptrs[i]);
   p.push_n = push_n;

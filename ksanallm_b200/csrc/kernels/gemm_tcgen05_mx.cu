@@ -108,7 +108,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait();                         // set-up overlapped the previous kernel; its results are read from here on
+  // Set-up overlapped the previous kernel (programmatic dependent launch); what that kernel produced is read only
+  // after pdl_wait(), which every role calls first - except that the producer requests the weight tiles (B, never
+  // written while the engine runs) of its first K blocks before it waits.
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -117,10 +119,26 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       tma_prefetch_desc(&tma_b);
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      int pre = 0;
+      if (static_cast<int>(blockIdx.x) < num_tiles) {
+        int m_blk, n_blk;
+        mx_tile_coords(blockIdx.x, m_tiles, n_tiles, m_blk, n_blk);
+        for (; pre < Cfg::kStages && pre < num_kb; ++pre) {
+          mbar_expect_tx(&full_bar[pre], Cfg::kStageBytes);
+          tma_load_2d(smem + pre * Cfg::kStageBytes + Cfg::kABytes, &tma_b, &full_bar[pre], pre * 128, n_blk * BN);
+        }
+      }
+      pdl_wait();
+      int issued = 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
         mx_tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb; ++kb, ++issued) {
+          if (issued < pre) {                 // first round of the ring: the weight tile was requested above
+            tma_load_2d(smem + stage * Cfg::kStageBytes, &tma_a, &full_bar[stage], kb * 128, m_blk * kMxBM);
+            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
@@ -133,6 +151,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     __syncwarp();
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
+    pdl_wait();
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       int sfs = 0; uint32_t sf_phase = 0;
@@ -179,6 +198,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
     __syncwarp();
   } else if (warp == 2) {
+    pdl_wait();
     // ------------------------------------------------------------- scale packer
     // The scale values of the next two groups are already on their way (plain loads whose results are not
     // touched until their turn) while the warp waits for the buffer of the current group: under the load of
@@ -260,6 +280,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    pdl_wait();                       // the residual / output may still be in use by the previous kernel
     const int q = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     const int wg = (warp - 3) >> 2;

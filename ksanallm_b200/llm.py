@@ -261,8 +261,10 @@ class LLM:
                 return False
             if img.size == 0:
                 return True
-            plan = ne.StepPlan.unpack(img)
-            self.engine.run_with_extras(plan, unpack_extras(blob))
+            n_aux = int(img[-1])                         # the image ends with the pipelined-step data and its length
+            aux = img[img.size - 1 - n_aux:img.size - 1] if n_aux > 0 else None
+            plan = ne.StepPlan.unpack(img[:img.size - 1 - n_aux])
+            self.engine.follow_step(plan, unpack_extras(blob), aux)
 
     def shutdown(self, stop_followers: bool = False):
         """Stops the engine loop. ``stop_followers`` additionally releases worker ranks blocked in ``follow``."""

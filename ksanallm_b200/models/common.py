@@ -178,11 +178,11 @@ class CommonModel:
         ops.rope_kv_append(qkv, pos, step.slots, self.cos_sin if use_rope else _dummy_cs(qkv), cache_layer,
                            self.block_tokens, self.Hq, self.Hkv, self.D, self.rot_dim, cfg.rope_neox, sections, ks, vs,
                            apply_rope=use_rope)
-        out = torch.empty(qkv.shape[0], self.Hq * self.D, dtype=qkv.dtype, device=qkv.device)
-        ops.paged_attention(qkv, out, cache_layer, self.block_tokens, step.block_table, step.cu_q, step.kv_lens,
-                            step.num_multi, step.num_single, step.num_multi_tokens, step.max_q_len, self.Hq, self.Hkv,
-                            self.D, self.scale, self.alibi, ks, vs, step.decode_splits, step.decode_workspace)
-        return out
+        # pure decode steps hand the o_proj GEMM its FP8 operand straight from the attention kernels
+        return ops.paged_attention(qkv, None, cache_layer, self.block_tokens, step.block_table, step.cu_q, step.kv_lens,
+                                   step.num_multi, step.num_single, step.num_multi_tokens, step.max_q_len, self.Hq,
+                                   self.Hkv, self.D, self.scale, self.alibi, ks, vs, step.decode_splits,
+                                   step.decode_workspace, quant_for=lw.o_proj)
 
     def row_parallel(self, x, W: LinearWeight, h: torch.Tensor) -> torch.Tensor:
         """h += x W^T, reduced over the tensor-parallel group. Single rank: the add is the GEMM's epilogue."""

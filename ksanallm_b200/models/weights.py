@@ -58,12 +58,22 @@ class RandomSource:
         return torch.randn(shape, generator=self._gen(name, "cpu"), dtype=torch.float32) * self.std
 
 
-def load_weight_map(model_type: str) -> List[tuple]:
-    path = os.path.join(WEIGHT_MAP_DIR, f"{model_type}_weight_map.json")
+def _python_replacement(repl: str) -> str:
+    """Replacement strings may name groups the ECMAScript way the reference's maps do (``$1``, ``$2`` ...;
+    src/ksana_llm/utils/get_custom_weight_name.cpp:47 uses std::regex_replace) or the Python way (``\\1``): both are
+    accepted, ``$$`` stands for a literal dollar sign."""
+    out = re.sub(r"\$(\d+)", r"\\g<\1>", repl.replace("$$", "\0"))
+    return out.replace("\0", "$")
+
+
+def load_weight_map(model_type: str, path: Optional[str] = None) -> List[tuple]:
+    """Rules of ``<model_type>_weight_map.json`` (or of an explicit file, e.g. one written for the reference engine):
+    an ordered list of (compiled pattern, replacement)."""
+    path = path or os.path.join(WEIGHT_MAP_DIR, f"{model_type}_weight_map.json")
     if not os.path.exists(path):
         return []
     with open(path, "r", encoding="utf-8") as f:
-        return [(re.compile(k), v) for k, v in json.load(f).items()]
+        return [(re.compile(k), _python_replacement(v)) for k, v in json.load(f).items()]
 
 
 def apply_weight_map(name: str, rules: List[tuple]) -> str:

@@ -258,9 +258,25 @@ def decode_splits(batch: int, hkv: int, max_kv_len: int, sms: int = 148, ctas_pe
 
 def paged_attention(qkv, out, cache_layer, block_tokens, block_table, cu_q, kv_lens, num_multi, num_single,
                     num_multi_tokens, max_q_len, Hq, Hkv, D, scale, alibi=None, k_scale=1.0, v_scale=1.0,
-                    num_splits=1, workspace=None):
+                    num_splits=1, workspace=None, quant_for: Optional[LinearWeight] = None):
     """Attention of this step's new tokens (rows of ``qkv``: multi-token sequences first, then one row per
-    single-token sequence) against the paged cache, which already holds their K/V."""
+    single-token sequence) against the paged cache, which already holds their K/V. ``out`` None allocates the
+    result; with ``quant_for`` (the FP8 linear that consumes it) a pure decode step returns the QTensor that linear
+    wants, quantised inside the attention kernels."""
+    T = qkv.shape[0]
+    if qkv.is_cuda and quant_for is not None and quant_for.fp8 and num_multi == 0 and num_single and D == 128 and out is None:
+        po, pml = workspace if workspace is not None else (None, None)
+        if num_splits > 1 and po is None:
+            po = torch.empty(num_single * Hq * num_splits * D, dtype=torch.float32, device=qkv.device)
+            pml = torch.empty(num_single * Hq * num_splits * 2, dtype=torch.float32, device=qkv.device)
+        oq = torch.empty(T, Hq * D, dtype=torch.float8_e4m3fn, device=qkv.device)
+        osc = torch.empty(Hq, max(4, (T + 3) // 4 * 4), dtype=torch.float32, device=qkv.device)
+        native.paged_decode(qkv, qkv.stride(0), None, cache_layer, cache_layer.stride(0), block_tokens, block_table,
+                            kv_lens, num_single, Hq, Hkv, D, scale, alibi, k_scale, v_scale, num_splits, po, pml,
+                            out_q=oq, out_scale=osc)
+        return QTensor(oq, osc)
+    if out is None:
+        out = torch.empty(T, Hq * D, dtype=qkv.dtype, device=qkv.device)
     if qkv.is_cuda:
         if num_multi:
             native.paged_prefill(qkv, qkv.stride(0), out, cache_layer, cache_layer.stride(0), block_tokens, block_table,

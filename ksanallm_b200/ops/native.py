@@ -57,13 +57,14 @@ _SIGS = {
     "ksana_copy_blocks": [vp, vp, i32, i64, i32, vp, vp],
     "ksana_swap_blocks": [vp, vp, vp, i32, i64, i32, i32, i32, vp, vp],
     "ksana_add": [vp, vp, vp, vp, i64, i32, vp],
+    "ksana_patch_ids": [vp, vp, vp, vp, i32, i32, i32, vp, vp],
     "ksana_cast_f32": [vp, vp, i64, vp],
     "ksana_paged_prefill_tc": [vp, i64, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i64,
                                vp, vp],
     "ksana_paged_prefill": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32,
                             f32, f32, i64, vp, vp],
     "ksana_paged_decode": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, f32, f32,
-                           i32, vp, vp, i64, vp, vp],
+                           i32, vp, vp, i64, vp, vp, i32, vp, vp],
     "ksana_mla_attention": [vp, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, i32, i32, i32, f32, i64, i32, vp, vp, vp, vp],
     "ksana_mla_rope_append": [vp, i64, i32, vp, i64, vp, f32, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i64, vp, vp],
     "ksana_gemm_smallm_w4": [vp, i32, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, vp, i64, vp, i32, vp, vp],
@@ -558,6 +559,12 @@ def refit_rows(hidden, pos, emb):
            "ksana_refit_rows")
 
 
+def patch_ids(ids, rows, src, prev_tokens):
+    """ids[rows[i]] = prev_tokens[src[i]] on the device (all int32)."""
+    _check(lib().ksana_patch_ids(_p(ids), _p(rows), _p(src), _p(prev_tokens), rows.numel(), ids.numel(),
+                                 prev_tokens.numel(), _p(err_flag(ids.device)), _st()), "ksana_patch_ids")
+
+
 def add(a, b=None, bias=None, out=None):
     if out is None:
         out = torch.empty_like(a)
@@ -617,12 +624,17 @@ def paged_prefill(q, q_stride, out, cache_layer, block_stride, block_tokens, blo
 
 
 def paged_decode(q, q_stride, out, cache_layer, block_stride, block_tokens, block_table, kv_lens, B, Hq, Hkv, D, scale,
-                 alibi=None, k_scale=1.0, v_scale=1.0, num_splits=1, part_o=None, part_ml=None):
+                 alibi=None, k_scale=1.0, v_scale=1.0, num_splits=1, part_o=None, part_ml=None, out_q=None,
+                 out_scale=None):
+    """``out_q`` / ``out_scale`` (head dim 128): the output also (or, with ``out`` None, only) as the FP8 operand of the
+    next GEMM: e4m3 [B, Hq * D] and scales [Hq, ld]."""
     fp8 = cache_layer.dtype != torch.bfloat16
-    rc = lib().ksana_paged_decode(_p(q), q_stride, _p(out), out.stride(0), _p(cache_layer), block_stride, block_tokens,
+    rc = lib().ksana_paged_decode(_p(q), q_stride, _p(out), out.stride(0) if out is not None else Hq * D, _p(cache_layer),
+                                  block_stride, block_tokens,
                                   _p(block_table), block_table.stride(0), _p(kv_lens), _p(alibi), B, Hq, Hkv, D,
                                   float(scale), int(fp8), float(k_scale), float(v_scale), num_splits, _p(part_o),
-                                  _p(part_ml), _cache_rows(cache_layer, block_stride, D), _p(err_flag(q.device)), _st())
+                                  _p(part_ml), _cache_rows(cache_layer, block_stride, D), _p(out_q), _p(out_scale),
+                                  out_scale.stride(0) if out_scale is not None else 0, _p(err_flag(q.device)), _st())
     _check(rc, "ksana_paged_decode")
 
 

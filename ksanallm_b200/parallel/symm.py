@@ -35,10 +35,17 @@ from ..ops.dispatch import LinearWeight, QTensor, linear, quantize
 
 FLAG_BYTES = 4096
 ONE_SHOT_ROWS = 64             # at most this many rows are reduced by every rank itself (one flag exchange) ...
-ONE_SHOT_PULL_BYTES = 1 << 20  # ... and only while a rank then pulls no more than this from its peers: beyond it the
+ONE_SHOT_PULL_BYTES = 8 << 20  # ... and only while a rank then pulls no more than this from its peers: beyond it the
                                # rows are split over the ranks (reduce-scatter, norm, all-gather), which moves
-                               # 2/size of the bytes at the price of a second flag exchange
+                               # 2/size of the bytes at the price of a second flag exchange and a second launch.
+                               # Measured on 8 GPUs at 64 rows x 8192 (7 MB pulled per rank): one-shot 23.6 us per
+                               # reduce and the fastest whole step; split 22.8 us (in-switch sums) / 23.9 us (peer
+                               # loads) per reduce but a slower step
 CAND_MAX_K = 64                # sampling candidates exchanged per row and shard at most (beyond: whole shards)
+PUSH_MIN_RANKS = 4             # decode-sized batches on this many ranks or more: the row-parallel GEMM's epilogue
+                               # pushes its partial rows into every rank's receive slot (posted NVLink stores that
+                               # overlap with the tiles still being computed) and the reduce kernel reads local
+                               # memory only; below, every rank pulls the partial rows from its peers instead
 PUSH_EPILOGUE = False          # large batches: reduce-scatter by GEMM-epilogue pushes instead of owner pulls
 
 
@@ -254,12 +261,15 @@ class SymmetricComm:
         if writer is None and W.fp8 and not isinstance(x, QTensor):
             x = quantize(x)
         one_shot = self.one_shot(M)
+        want_push = os.environ.get("KSANA_PUSH")
+        push_mode = PUSH_EPILOGUE or (one_shot and writer is None and not W.nvfp4 and not W.w4a16 and
+                                      (want_push == "1" or (want_push is None and self.size >= PUSH_MIN_RANKS)))
         rows_per = M if one_shot else (M + self.size - 1) // self.size
         bias = W.bias.data_ptr() if (writer is None and W.bias is not None and self.rank == 0) else None
         if writer is not None:
             part = self.buf[self.slots_off[parity]: self.slots_off[parity] + M * H * 2].view(torch.bfloat16).view(M, H)
             writer(part)
-        elif not PUSH_EPILOGUE:
+        elif not push_mode:
             # partial product [M, H] into this rank's own symmetric buffer (the slot area of this parity); the
             # reduce kernel of every row owner (one-shot: of every rank) pulls it from there
             part = self.buf[self.slots_off[parity]: self.slots_off[parity] + M * H * 2].view(torch.bfloat16).view(M, H)
@@ -292,7 +302,7 @@ class SymmetricComm:
             native._check(rc, "ksana_gemm_push")
         want_q = quant_for is not None and quant_for.fp8 and H % 128 == 0 and norm_w is not None
         if one_shot:
-            row_begin, row_count, gather = 0, M, (4 if (writer is not None or not PUSH_EPILOGUE) else 0)
+            row_begin, row_count, gather = 0, M, (4 if (writer is not None or not push_mode) else 0)
             y = torch.empty(M, H, dtype=torch.bfloat16, device=self.device) if (norm_w is not None and not want_q) else None
             yq = torch.empty(M, H, dtype=torch.float8_e4m3fn, device=self.device) if want_q else None
             scale_ld = (M + 3) // 4 * 4
@@ -300,7 +310,7 @@ class SymmetricComm:
         else:
             row_begin = min(self.rank * rows_per, M)
             row_count = max(0, min(rows_per, M - row_begin))
-            gather = 1 | (2 if gather_h else 0) | (4 if (writer is not None or not PUSH_EPILOGUE) else 0)
+            gather = 1 | (2 if gather_h else 0) | (4 if (writer is not None or not push_mode) else 0)
             assert h.data_ptr() == self.h.data_ptr(), "large-batch row-parallel linear needs the symmetric residual view"
             y = self.y[:M] if (norm_w is not None and not want_q) else None
             yq = self.yq[:M] if want_q else None

@@ -91,7 +91,7 @@ class ModelRunner:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
-    STAGE_RING = 4
+    STAGE_RING = 16       # several steps of uploads may be queued behind the step in flight (pipelined stepping)
 
     def _stage_buffer(self, n: int):
         """Next pinned staging buffer of the ring with room for ``n`` int32 words. A buffer is rewritten only after
@@ -194,10 +194,24 @@ class ModelRunner:
         parts = [plan.input_ids, plan.positions, plan.slots, plan.cu_q, plan.kv_lens, plan.block_table, plan.sample_rows]
         return self._stage(np.concatenate([np.asarray(p, dtype=np.int32).reshape(-1) for p in parts]))
 
-    def build_step(self, plan, extra: Optional[dict] = None) -> StepInput:
+    def _patch_ids(self, ids: torch.Tensor, patch) -> None:
+        """Pipelined steps: rows whose input token the host does not know yet (sampled by the step still in flight)
+        take it from that step's sampler output on the device. ``patch`` = (rows, src, previous tokens)."""
+        rows, src, prev = patch
+        if rows.size == 0:
+            return
+        if self.cuda:
+            idx = self._stage(np.concatenate([rows, src]).astype(np.int32))
+            native.patch_ids(ids, idx[:rows.size], idx[rows.size:], prev)
+        else:
+            ids[torch.from_numpy(rows.astype(np.int64))] = prev[torch.from_numpy(src.astype(np.int64))].to(ids.dtype)
+
+    def build_step(self, plan, extra: Optional[dict] = None, patch=None) -> StepInput:
         T, nseq = plan.num_tokens, len(plan.seq_ids)
         nsamp = plan.sample_rows.size
         dev = self._stage_plan(plan)
+        if patch is not None:
+            self._patch_ids(dev[:T], patch)
         o = 0
 
         def take(n):
@@ -289,7 +303,7 @@ class ModelRunner:
         self.graphs[(bs, kx)] = g
         return g
 
-    def _try_graph(self, plan) -> Optional[torch.Tensor]:
+    def _try_graph(self, plan, patch=None) -> Optional[torch.Tensor]:
         nseq = len(plan.seq_ids)
         if getattr(self, "graphs", None) is None or plan.num_multi or nseq == 0 or nseq > self.graph_max_batch:
             return None
@@ -314,6 +328,8 @@ class ModelRunner:
             tbl = host[4 * bs:].reshape(bs, mb)
             tbl[:nseq, :plan.max_blocks] = np.asarray(plan.block_table).reshape(nseq, plan.max_blocks)
             self._stage(host, out=img)
+        if patch is not None:
+            self._patch_ids(img[:bs], patch)
         graph.replay()
         self.graph_replays = getattr(self, "graph_replays", 0) + 1
         if isinstance(logits, LogitCandidates):
@@ -321,7 +337,7 @@ class ModelRunner:
         return logits[:nseq]
 
     @torch.inference_mode()
-    def execute(self, plan, extra: Optional[dict] = None) -> torch.Tensor:
+    def execute(self, plan, extra: Optional[dict] = None, patch=None) -> torch.Tensor:
         dp = getattr(self.model, "dp", None)
         if dp is not None:
             # attention data parallelism: this rank runs only its own sequences and only its own pool's swap / copy
@@ -340,10 +356,10 @@ class ModelRunner:
         if plan.empty():
             return None                      # a plan may carry block operations only (everything else was preempted)
         if extra is None:
-            out = self._try_graph(plan)
+            out = self._try_graph(plan, patch)
             if out is not None:
                 return out
-        step = self.build_step(plan, extra)
+        step = self.build_step(plan, extra, patch)
         if _checks.enabled():
             _checks.check_step(step, self.model)
         if self.pipeline is not None:
@@ -393,6 +409,11 @@ class LLMEngine:
         self.step_hook: Optional[Callable] = None
         self.last_logits: Optional[torch.Tensor] = None
         self.fatal: Optional[str] = None          # set when the tensor-parallel group can no longer serve (see _device_fault)
+        # pipelined stepping (see _step_pipelined): the step whose tokens the host has not read yet, and how many
+        # active requests need synchronous steps
+        self.pipelined = os.environ.get("KSANA_PIPELINED_STEPS", "1") != "0"
+        self._flight: Optional[dict] = None
+        self._nonplain = 0
         self.host_ms: Dict[str, float] = {}      # host wall time of the step loop by phase (milliseconds, summed)
 
     # ------------------------------------------------------------------ requests
@@ -406,6 +427,11 @@ class LLMEngine:
         n = max(cfg.num_beams, cfg.num_return_sequences, 1)
         req = Request(req_id, prompt, cfg, n, stream)
         req.request_target, req.refit, req.mrope_positions = request_target, refit, mrope_positions
+        # plain = nothing needs the host between a step's sampling and the next forward (see _step_pipelined)
+        req.plain = (n == 1 and cfg.num_beams == 1 and not cfg.stop_strings and not structured_regex and
+                     cfg.repetition_penalty == 1.0 and cfg.no_repeat_ngram_size == 0 and
+                     cfg.encoder_no_repeat_ngram_size == 0 and cfg.logprobs_num == 0 and not request_target and
+                     refit is None and mrope_positions is None)
         if structured_regex:
             req.structured = StructuredOutput(self.fsm_controller.get_or_create(structured_regex), self.tokenizer)
         if cfg.seed == 0:
@@ -431,6 +457,8 @@ class LLMEngine:
             self.requests[req_id] = req
             for i, sid in enumerate(seq_ids):
                 self.seq_to_req[sid] = (req, i)
+            if not req.plain:
+                self._nonplain += 1
         if req.structured is not None:
             init = req.structured.initial_tokens()
             if init:
@@ -455,7 +483,8 @@ class LLMEngine:
         if req.span_id:
             ne.span_end(req.span_id, {"code": str(req.status_code)})
         with self._lock:
-            self.requests.pop(req.req_id, None)
+            if self.requests.pop(req.req_id, None) is not None and not getattr(req, "plain", True):
+                self._nonplain -= 1
             for sid in req.seq_ids:
                 self.seq_to_req.pop(sid, None)
 
@@ -604,7 +633,7 @@ class LLMEngine:
             extra["full_logits"] = full_logits
         return extra or None
 
-    def run_with_extras(self, plan, extra: Optional[dict]):
+    def run_with_extras(self, plan, extra: Optional[dict], patch=None):
         """The forward of one step with its optional inputs moved to the device; returns (logits, the all-position
         logits of the ``full_logits`` row ranges in order). Every rank of the engine calls this with the same plan
         and extras, so the collectives inside line up."""
@@ -612,7 +641,7 @@ class LLMEngine:
         if extra:
             dev = self.model.device
             step_extra = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in extra.items() if k != "full_logits"}
-        logits = self.runner.execute(plan, step_extra or None)
+        logits = self.runner.execute(plan, step_extra or None, patch)
         ranges = (extra or {}).get("full_logits", [])
         pipe = self.runner.pipeline
         if pipe is not None and extra and extra.get("want_hidden"):
@@ -620,8 +649,180 @@ class LLMEngine:
         full = [self.model.compute_logits(self.model.step_normed[r0:r0 + n]) for r0, n in ranges]
         return logits, full
 
+    # ------------------------------------------------------------------ pipelined stepping
+    # The host work between two steps (read the tokens, post-process, schedule, pack, broadcast, launch) is off the
+    # device's critical path whenever the running requests are plain: the next step is planned and launched while the
+    # device still runs the current one. The scheduler gives every sampling sequence a placeholder token
+    # (Scheduler::Advance), the next step's decode rows take their input ids from the sampler's device buffer, and the
+    # tokens are read and post-processed (Scheduler::Resolve) while that next step executes. Counterpart of the
+    # reference's separate scheduling / execution threads (src/ksana_llm/batch_manager/batch_manager.cpp:111-241) with
+    # one thread and one step of look-ahead. Anything that needs the host between sampling and the next forward
+    # (beams, parallel sampling forks, stop strings, structured output, penalties, log-probs, request targets, hooks)
+    # drains the pipeline and steps synchronously.
+    AUX_MAGIC = 0x4B535058
+
+    def _pipelining_possible(self) -> bool:
+        return (self.pipelined and self.runner.pipeline is None and getattr(self.model, "dp", None) is None
+                and self.step_hook is None and self._nonplain == 0)
+
+    def _resolve_flight(self) -> None:
+        """Second half of a pipelined step: its tokens reach the host, the scheduler puts them in place of the
+        placeholders and the requests hear about them."""
+        fl, self._flight = self._flight, None
+        if fl is None:
+            return
+        t0 = time.perf_counter()
+        try:
+            tokens = self.sampler.finish_plain(fl["handle"])
+        except DeviceStepError as e:
+            self._device_fault(e)
+            return
+        t1 = time.perf_counter()
+        events = self.scheduler.resolve(fl["plan"], tokens)
+        self._handle_events(events, None)
+        self.steps += 1
+        tm = self.host_ms
+        tm["sample_and_wait"] = tm.get("sample_and_wait", 0.0) + (t1 - t0) * 1000.0
+        tm["post_step"] = tm.get("post_step", 0.0) + (time.perf_counter() - t1) * 1000.0
+        tm["steps"] = tm.get("steps", 0) + 1
+
+    def _plain_params(self, plan, pending: set):
+        params = []
+        for sid in plan.sample_seq_ids.tolist():
+            ent = self.seq_to_req.get(sid)
+            req, i = ent if ent else (None, 0)
+            sp = SamplingParams.from_request(req, i)
+            if sid in pending:
+                sp.step += 1                 # its previous token is still on the device: not in the request's list yet
+            params.append(sp)
+        return params
+
+    def _patch_for(self, plan, fl):
+        """(rows, src, previous tokens) for the rows of ``plan`` whose input id is a placeholder, or None."""
+        ids = np.asarray(plan.input_ids)
+        rows = np.nonzero(ids < 0)[0].astype(np.int32)
+        if rows.size == 0:
+            return None
+        if fl is None:
+            raise RuntimeError("a step plan carries placeholder tokens but no step is in flight")
+        where = {sid: k for k, sid in enumerate(fl["plan"].sample_seq_ids.tolist())}
+        cu = np.asarray(plan.cu_q)
+        seq_of_row = np.searchsorted(cu, rows, side="right") - 1
+        seq_ids = np.asarray(plan.seq_ids)
+        src = np.array([where[int(seq_ids[k])] for k in seq_of_row], dtype=np.int32)
+        return rows, src, fl["handle"]["tokens_dev"]
+
+    def _step_pipelined(self) -> bool:
+        tm = self.host_ms
+        t0 = time.perf_counter()
+        fl = self._flight
+        with nvtx.annotate("schedule"):
+            plan = self.scheduler.schedule()
+        t1 = time.perf_counter()
+        if plan.events:
+            self._handle_events(plan.events)
+        if plan.empty():
+            if plan.has_block_ops():
+                if self.world_size > 1:
+                    self._broadcast_plan(plan, None)
+                self.runner.execute(plan, None)
+            if fl is not None:
+                self._resolve_flight()
+                return True
+            return plan.has_block_ops()
+        extra = self._gather_extras(plan)
+        plain = (not extra and self.scheduler.can_pipeline(plan) and self._pipelining_possible())
+        patch = self._patch_for(plan, fl)
+        image = None
+        if plain:
+            pending = set(fl["plan"].sample_seq_ids.tolist()) if fl is not None else set()
+            image = Sampler.params_image(self._plain_params(plan, pending))
+        t2 = time.perf_counter()
+        if self.world_size > 1:
+            self._broadcast_plan(plan, extra, self._pack_aux(patch, image))
+        t3 = time.perf_counter()
+        phase = "Prefill" if plan.num_multi else "Decode"
+        with nvtx.annotate(phase):
+            logits, self._step_full_logits = self.run_with_extras(plan, extra, patch)
+        self.last_logits = logits
+        nsamp = int(plan.sample_rows.size)
+        if plain:
+            handle = self.sampler.launch_plain(logits, image, nsamp) if nsamp else {"tokens_dev": None, "B": 0, "code": 0}
+            t4 = time.perf_counter()
+            if fl is not None:
+                self._resolve_flight()                   # overlaps with the step just launched
+            if self.fatal is None:
+                self.scheduler.advance(plan)
+                self._flight = {"plan": plan, "handle": handle}
+            t5 = time.perf_counter()
+            for k, v in (("schedule", t1 - t0), ("extras", t2 - t1), ("broadcast", t3 - t2), ("launch", t4 - t3)):
+                tm[k] = tm.get(k, 0.0) + v * 1000.0
+            return True
+        # a step that needs the host between sampling and the next forward: finish what is in flight, then the
+        # synchronous second half
+        t4 = time.perf_counter()
+        if fl is not None:
+            self._resolve_flight()
+            if self.fatal is not None:
+                return True
+        try:
+            tokens, parents, lp_by_seq = self._sample(plan, logits)
+        except DeviceStepError as e:
+            self._device_fault(e)
+            return True
+        t5 = time.perf_counter()
+        self._extract_targets(plan, logits)
+        events = self.scheduler.post_step(plan, tokens, parents)
+        t6 = time.perf_counter()
+        self._handle_events(events, lp_by_seq)
+        self.steps += 1
+        if self.step_hook:
+            self.step_hook(plan, logits)
+        for k, v in (("schedule", t1 - t0), ("extras", t2 - t1), ("broadcast", t3 - t2), ("launch", t4 - t3),
+                     ("sample_and_wait", t5 - t4), ("post_step", t6 - t5), ("events", time.perf_counter() - t6)):
+            tm[k] = tm.get(k, 0.0) + v * 1000.0
+        tm["steps"] = tm.get("steps", 0) + 1
+        return True
+
+    def _pack_aux(self, patch, image) -> Optional[np.ndarray]:
+        """What the worker ranks need beside the plan in a pipelined step: the rows to patch from their own copy of
+        the previous step's tokens, and the sampler's parameters (they run the same sampler on the same logits, so
+        every rank holds the tokens the next step reads). Layout: magic, n_patch, n_sample_words, rows, src, image."""
+        if patch is None and image is None:
+            return None
+        rows, src = (patch[0], patch[1]) if patch is not None else (np.zeros(0, np.int32), np.zeros(0, np.int32))
+        img = image if image is not None else np.zeros(0, np.int32)
+        return np.concatenate([np.array([self.AUX_MAGIC, rows.size, img.size], dtype=np.int32), rows, src, img])
+
+    def follow_step(self, plan, extra: Optional[dict], aux: Optional[np.ndarray]):
+        """Worker ranks: one broadcast step. Pipelined steps also sample (no read-back) so that the next step can take
+        its input ids from this rank's own device buffer."""
+        patch, image = None, None
+        if aux is not None and aux.size >= 3 and int(aux[0]) == self.AUX_MAGIC:
+            n_patch, n_img = int(aux[1]), int(aux[2])
+            if n_patch:
+                prev = self._flight["handle"]["tokens_dev"] if self._flight else None
+                if prev is None:
+                    raise RuntimeError("worker rank: a pipelined step refers to tokens this rank never sampled")
+                patch = (aux[3:3 + n_patch].copy(), aux[3 + n_patch:3 + 2 * n_patch].copy(), prev)
+            if n_img:
+                image = aux[3 + 2 * n_patch:3 + 2 * n_patch + n_img].copy()
+        out = self.run_with_extras(plan, extra, patch)
+        if image is not None:
+            nsamp = int(plan.sample_rows.size)
+            self._flight = {"plan": None, "handle": self.sampler.launch_plain(out[0], image, nsamp, read_back=False)
+                            if nsamp else {"tokens_dev": None, "B": 0}}
+        else:
+            self._flight = None
+        return out
+
     def step(self) -> bool:
         """Runs one engine step. Returns False when there was nothing to run."""
+        if self._flight is not None or self._pipelining_possible():
+            if self._flight is not None and not self._pipelining_possible():
+                self._resolve_flight()       # something that needs synchronous steps arrived: drain first
+            else:
+                return self._step_pipelined()
         tm = self.host_ms
         t0 = time.perf_counter()
         with nvtx.annotate("schedule"):
@@ -699,9 +900,13 @@ class LLMEngine:
         after the forward, in plan order, by ``run_with_extras``."""
         return self._step_full_logits.pop(0)
 
-    def _broadcast_plan(self, plan, extra: Optional[dict] = None):
+    def _broadcast_plan(self, plan, extra: Optional[dict] = None, aux: Optional[np.ndarray] = None):
+        """The plan image for the worker ranks; ``aux`` (pipelined steps) rides behind it in the same message, followed
+        by its length, and a plan without one ends with a zero."""
         from ..parallel.control import broadcast_plan, pack_extras
-        broadcast_plan(self.control_group, plan.pack(), extras=pack_extras(extra))
+        img = plan.pack()
+        tail = np.concatenate([aux, [aux.size]]).astype(np.int32) if aux is not None else np.zeros(1, dtype=np.int32)
+        broadcast_plan(self.control_group, np.concatenate([img, tail]), extras=pack_extras(extra))
 
     # ------------------------------------------------------------------ loop
     def start(self):
@@ -781,6 +986,8 @@ class LLMEngine:
                     break
                 if deadline and time.time() > deadline:
                     break
+            if self._flight is not None:          # a last step of rows that turned out to be finished: collect it
+                self._resolve_flight()
         else:
             for r in reqs:
                 r.done.wait(timeout)

@@ -94,6 +94,85 @@ class Sampler:
         self._host_out = None                # pinned read-back area: tokens, then the device error word
         self._host_cap = 0
         self._done = None
+        self._plain_slots = [[None, None], [None, None]]     # two read-back areas: a step in flight and the next one
+        self._plain_next = 0
+
+    @staticmethod
+    def params_image(params: List[SamplingParams]) -> np.ndarray:
+        """The sampler kernel's per-row parameters as 6 int32 words per row: temperature, top-k, top-p, draw counter
+        (all rows of one kind together), then the 64-bit seeds."""
+        B = len(params)
+        img = np.empty(6 * B, dtype=np.int32)
+        img[0:B] = np.array([p.temperature for p in params], dtype=np.float32).view(np.int32)
+        img[B:2 * B] = [p.topk for p in params]
+        img[2 * B:3 * B] = np.array([p.topp for p in params], dtype=np.float32).view(np.int32)
+        img[3 * B:4 * B] = [p.step for p in params]
+        img[4 * B:6 * B] = np.array([p.seed for p in params], dtype=np.int64).view(np.int32)
+        return img
+
+    def _image_views(self, dev: torch.Tensor, B: int):
+        o = 4 * B                                             # seeds are 64-bit: an even word offset keeps them aligned
+        return (dev[0:B].view(torch.float32), dev[B:2 * B], dev[2 * B:3 * B].view(torch.float32), dev[3 * B:4 * B],
+                dev[o:o + 2 * B].view(torch.int64))
+
+    # ------------------------------------------------------------------ plain rows, in two halves (pipelined steps)
+    def launch_plain(self, logits, image: np.ndarray, B: int, read_back: bool = True) -> dict:
+        """Sampling of rows that need nothing but the kernel (no penalties, bans, log-probs or beams), without waiting
+        for the result: returns a handle whose ``tokens_dev`` (int32 [B] on the device) the next step can read its
+        input ids from, and which ``finish_plain`` turns into host tokens later. ``read_back`` False (worker ranks):
+        nothing is copied to the host."""
+        merged = None
+        if not torch.is_tensor(logits):
+            merged, logits = logits, logits.values
+        logits = logits[:B]
+        if not self.cuda:
+            view = torch.from_numpy(image)
+            temp, topk, topp = view[0:B].view(torch.float32), view[B:2 * B], view[2 * B:3 * B].view(torch.float32)
+            u = torch.rand(B, generator=self._cpu_rng)
+            tok, _, _ = ref.sample(logits.float(), temp, topk, topp, u, 0)
+            code = int(native.err_flag(self.device).item())
+            return {"tokens_dev": tok.to(torch.int32), "B": B, "code": code}
+        dev = self._stage(image) if self._stage is not None else torch.from_numpy(image).to(self.device)
+        temp, topk, topp, steps, seeds = self._image_views(dev, B)
+        out = torch.empty(B, dtype=torch.int32, device=self.device)
+        if merged is not None:
+            native.sample_merged(logits, merged.ids[:B], temp, topk, topp, seeds, steps, out)
+        else:
+            native.sample(logits, temp, topk, topp, seeds, steps, out)
+        handle = {"tokens_dev": out, "B": B}
+        if read_back:
+            slot = self._plain_slots[self._plain_next]
+            self._plain_next ^= 1
+            if slot[0] is None or slot[0].numel() < B + 1:
+                slot[0] = torch.empty(max(2 * (B + 1), 1024), dtype=torch.int32, pin_memory=True)
+                slot[1] = torch.cuda.Event()
+            slot[0][:B].copy_(out, non_blocking=True)
+            slot[0][B:B + 1].copy_(native.err_flag(self.device), non_blocking=True)
+            slot[1].record()
+            handle["slot"] = slot
+            self.d2h_bytes += (B + 1) * 4
+        return handle
+
+    def finish_plain(self, handle: dict) -> List[int]:
+        """Waits for a ``launch_plain`` result (the step's only host synchronisation); raises DeviceStepError when a
+        kernel of that step reported through the error word."""
+        B = handle["B"]
+        if B == 0 or handle.get("tokens_dev") is None:
+            return []
+        if "slot" not in handle:
+            code = handle.get("code", 0)
+            if code:
+                native.clear_err_flag(self.device)
+                raise DeviceStepError(code)
+            return handle["tokens_dev"].tolist()
+        host, ev = handle["slot"]
+        ev.synchronize()
+        arr = host[:B + 1].numpy()
+        code = int(arr[B])
+        if code != 0:
+            native.clear_err_flag(self.device)
+            raise DeviceStepError(code)
+        return arr[:B].tolist()
 
     def _upload_params(self, params: List[SamplingParams]):
         """temperature / top-k / top-p / step counters / seeds of all rows in one staged host->device copy."""

@@ -34,8 +34,8 @@ def main():
         inner = llm.engine.run_with_extras
         seen = {"n": 0}
 
-        def counted(plan, extra):
-            out = inner(plan, extra)
+        def counted(plan, extra, patch=None):
+            out = inner(plan, extra, patch)
             seen["n"] += 1
             if seen["n"] == 4:
                 os._exit(0)

@@ -146,8 +146,8 @@ def test_debug_input_checks_catch_bad_indices(monkeypatch):
     steps = []
     real = eng.runner.build_step
 
-    def spy(plan, extra=None):
-        st = real(plan, extra)
+    def spy(plan, extra=None, patch=None):
+        st = real(plan, extra, patch)
         steps.append(st)
         return st
 
@@ -228,7 +228,10 @@ def test_device_error_word_fails_requests_in_flight():
     assert eng.step()                                   # prefill step, fine
     with torch.inference_mode():
         native.err_flag(eng.model.device).fill_(3)
-    assert eng.step()                                   # the read-back sees the word
+    for _ in range(3):                                  # the word is read back with a step's tokens; with pipelined
+        if req.done.is_set():                           # stepping that is one step after the step that set it
+            break
+        assert eng.step()
     assert req.done.is_set() and req.status_code == 12 and "peer" in req.status_message
     assert int(native.err_flag(eng.model.device).item()) == 0
     r2 = eng.add_request(list(range(5, 25)), s)         # the group's collective epochs are out of step: refuse
@@ -275,3 +278,31 @@ def test_warmup_request_runs_at_start_unless_disabled(monkeypatch):
     assert llm.engine.steps == 2 and llm.engine.scheduler.idle()
     st = llm.engine.scheduler.stats()
     assert st["total_requests"] == 1 and st["finished"] == 1
+
+
+def test_pipelined_steps_give_the_tokens_of_synchronous_steps():
+    """Pipelined stepping (next step planned and launched before the current step's tokens reach the host) against
+    synchronous stepping: same tokens for every request, with sequences that stop on EOS while their next row is
+    already in flight, a length limit that is known in advance, chunked prefill, the prefix cache and preemption."""
+    from ksanallm_b200.utils import native_engine as ne
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, 300, (n,), generator=g).tolist() for n in (40, 7, 23, 61, 5, 33)]
+    prompts.append(list(prompts[0][:32]) + [9, 8, 7])                 # shares two cache blocks with the first prompt
+    probe = tiny_engine(max_token_len=120)
+    probe.pipelined = False
+    seqs = [set(r.outputs[0].tokens) for r in probe.generate(prompts, sampling(max_new_tokens=30, ignore_eos=True))]
+    # a token that some sequences produce and others do not serves as EOS: some stop early, some run to their limit
+    eos = next(t for t in sorted(set().union(*seqs)) if 2 <= sum(t in q for q in seqs) <= len(seqs) - 2)
+    for pressure in (dict(num_blocks=128, host_blocks=0), dict(num_blocks=14, host_blocks=0, preempt_mode=1)):
+        outs = []
+        for pipelined in (False, True):
+            eng = tiny_engine(enable_auto_prefix_cache=True, split_fuse_token_num=32, max_token_len=120, **pressure)
+            eng.pipelined = pipelined
+            eng.sched_cfg.eos_token_ids = [int(eos)]
+            eng.scheduler = ne.Scheduler(eng.sched_cfg, pressure["num_blocks"], pressure["host_blocks"])
+            reqs = eng.generate(prompts, sampling(max_new_tokens=30))
+            outs.append([(r.outputs[0].tokens, r.status_code) for r in reqs])
+            assert eng.scheduler.idle() and eng.scheduler.check_invariants()[0]
+            assert eng._flight is None
+        assert outs[0] == outs[1]
+        assert any(len(t) < 30 for t, _ in outs[1]) and any(len(t) == 30 for t, _ in outs[1])

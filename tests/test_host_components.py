@@ -430,3 +430,18 @@ def test_native_logger_levels_file_and_python_bridge(tmp_path):
     assert " WARNING " in text[0] and text[0].endswith("] disk almost full") and "test_host_components.py:" in text[0]
     assert " ERROR " in text[1] and " DEBUG " in text[2]
     assert "from python logging 7" in text[3] and "ksana-test" in text[3]
+
+
+def test_weight_maps_accept_dollar_groups(tmp_path):
+    """A weight map written for the reference engine names capture groups as $1 (std::regex_replace); such a file
+    loads and renames like the same map written with Python's \\1."""
+    from ksanallm_b200.models.weights import apply_weight_map, load_weight_map
+    ref_style = {"transformer.h.(\\d+).ln_(\\d).weight": "model.layers.$1.norm$2.weight", "transformer.wte.weight": "model.embed_tokens.weight"}
+    py_style = {"transformer.h.(\\d+).ln_(\\d).weight": "model.layers.\\1.norm\\2.weight", "transformer.wte.weight": "model.embed_tokens.weight"}
+    pa, pb = tmp_path / "a.json", tmp_path / "b.json"
+    pa.write_text(json.dumps(ref_style))
+    pb.write_text(json.dumps(py_style))
+    ra, rb = load_weight_map("x", str(pa)), load_weight_map("x", str(pb))
+    for name in ("transformer.h.12.ln_2.weight", "transformer.wte.weight", "lm_head.weight"):
+        assert apply_weight_map(name, ra) == apply_weight_map(name, rb)
+    assert apply_weight_map("transformer.h.12.ln_2.weight", ra) == "model.layers.12.norm2.weight"

@@ -237,6 +237,15 @@ def test_paged_decode(Hq, Hkv, D, splits, fp8):
                         alibi=alibi, num_splits=splits, part_o=po, part_ml=pml)
     want = ref.paged_attention(q, cache, table, cu_q, kvl, Hq, Hkv, D, 1 / math.sqrt(D), alibi=alibi)
     assert rel_err(out, want) < 2e-2, rel_err(out, want)
+    if D == 128:
+        # the same launch can emit the FP8 operand of the next GEMM: bit-identical to quantising its bf16 output
+        oq = torch.zeros(B, Hq * D, device=DEV, dtype=torch.float8_e4m3fn)
+        osc = torch.zeros(Hq, 8, device=DEV, dtype=torch.float32)
+        native.paged_decode(q, q.stride(0), None, cache, cache.stride(0), bt, table, kvl, B, Hq, Hkv, D, 1 / math.sqrt(D),
+                            alibi=alibi, num_splits=splits, part_o=po, part_ml=pml, out_q=oq, out_scale=osc)
+        wq, ws = native.quant_fp8(out)
+        assert torch.equal(oq.view(torch.uint8), wq.view(torch.uint8))
+        assert torch.equal(osc[:, :B], ws[:, :B])
 
 
 @pytest.mark.parametrize("neox", [True, False])
@@ -334,3 +343,43 @@ def test_penalties_and_blocks():
     with pytest.raises(RuntimeError, match="block-table entry"):
         native.check_err_flag(DEV)
     assert torch.equal(cache[1], before[3])
+
+
+def test_peer_wait_runs_out_and_reports_through_the_error_word():
+    """Failure detection on the device without a fault: a barrier over two "ranks" whose buffers are both plain local
+    allocations; the second rank never signals, the wait's budget is about a millisecond, the kernel returns, the error
+    word reads 3 (peer wait ran out), and the next launch on the same context works."""
+    import ctypes as C
+    lib = native.lib()
+    lib.ksana_comm_set_spin_limit.argtypes = [C.c_int]
+    lib.ksana_comm_set_spin_limit.restype = None
+    native.check_err_flag(DEV)
+    pads = [torch.zeros(4096, dtype=torch.uint8, device=DEV) for _ in range(2)]     # flag pad of rank 0 and of the absent rank 1
+    ptrs = (C.c_ulonglong * 8)(*([p.data_ptr() for p in pads] + [0] * 6))
+    ctrs = torch.zeros(16, dtype=torch.int32, device=DEV)
+    err = native.err_flag(DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    lib.ksana_comm_set_spin_limit(5000)
+    try:
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        rc = lib.ksana_comm_barrier(ptrs, ptrs, 0, 2, ctrs.data_ptr(), err.data_ptr(), st)
+        t1.record()
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 200.0                       # gave up within its budget (milliseconds, not a second)
+        assert int(err.item()) == 3
+        with pytest.raises(RuntimeError, match="peer"):
+            native.check_err_flag(DEV)                            # the host side turns the word into an error and clears it
+        assert int(ctrs[2].item()) == 0                           # the barrier's epoch did not advance
+        # the context is intact: a one-rank barrier and an ordinary kernel run afterwards
+        rc = lib.ksana_comm_barrier(ptrs, ptrs, 0, 1, ctrs.data_ptr(), err.data_ptr(), st)
+        assert rc == 0
+        x = torch.randn(4, 256, device=DEV, dtype=torch.bfloat16)
+        y = native.add(x, x)
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0 and int(ctrs[2].item()) == 1
+        assert torch.equal(y, (x.float() * 2).to(torch.bfloat16))
+    finally:
+        lib.ksana_comm_set_spin_limit(0)
