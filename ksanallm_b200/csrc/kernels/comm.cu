@@ -189,7 +189,9 @@ __device__ __forceinline__ void reduce_norm_body(const ReduceNormParams& p) {
   pdl_wait();
   const CommPeers& c = p.peers;
   const uint32_t epoch = begin_epoch(p.ctrs, 0);
-  if (!signal_and_wait(c, 0, epoch, p.err, true)) return;
+  // gather bit 4: the GEMM that pushed the partial rows already raised this rank's flag at the peers (its last CTA,
+  // after a system-wide fence): only wait for theirs
+  if (!signal_and_wait(c, 0, epoch, p.err, (p.gather & 16) == 0)) return;
   const int lrow = blockIdx.x;                  // row inside this rank's slice
   if (lrow >= p.row_count) {          // a rank without rows only exchanges flags
     if (end_epoch(p.ctrs, 0, epoch, (p.gather & 1) != 0) && (p.gather & 1)) signal_delivered(c, p.ctrs, 1);

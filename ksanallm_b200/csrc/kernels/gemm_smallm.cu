@@ -52,6 +52,13 @@ struct SmallMParams {
   // push mode: the (partial) result is stored into every rank's receive slot for this rank instead of D
   __nv_bfloat16* push[8];
   int push_n;
+  // push mode, optional: once every CTA's pushes are out (system-wide), the last CTA raises this rank's "partial rows
+  // delivered" flag at every peer (sig_flags[r], epoch = *sig_epoch + 1), so that the reduce kernel that follows only
+  // has to wait for the peers' flags instead of exchanging them itself
+  uint32_t* sig_flags[8];
+  const uint32_t* sig_epoch;
+  unsigned int* sig_done;
+  int sig_n;
   // kind 3 (weight-only 4-bit): packed levels [N, K/2] (even k in the low nibble), fp16 scale and zero*scale [N, K/group]
   const uint8_t* w4; const __half* w4_scale; const __half* w4_zs; int w4_group;
   // optional cycle counters per CTA and role (16 words per CTA), see ksana_smallm_set_profile
@@ -800,6 +807,20 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
         KSANA_PROF_ADD(9, pt9);
       }
     }
+    if (p.sig_n > 0) {
+      // every store_rows call ended with a barrier of the four epilogue warps: all of this CTA's pushes precede it
+      if (threadIdx.x == 64) {
+        __threadfence_system();
+        const unsigned int prev = atomicAdd(p.sig_done, 1u);
+        if (prev == gridDim.x - 1) {
+          *p.sig_done = 0;
+          const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(p.sig_epoch) + 1;
+          __threadfence_system();
+          for (int r = 0; r < p.sig_n; ++r)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sig_flags[r]), "r"(epoch) : "memory");
+        }
+      }
+    }
   }
 
   if (p.prof && lane == 0 && (warp <= 2 || warp == 6)) p.prof[blockIdx.x * 16 + (warp == 6 ? 8 : 11 + warp)] += prof_clock() - prof_t0;
@@ -879,6 +900,13 @@ static int launch_smallm(const CUtensorMap& mw, const CUtensorMap& mx, const Sma
 
 static long long* g_smallm_prof = nullptr;
 
+struct PushSignal {            // filled by ksana_gemm_smallm_push_signal for the launch it makes
+  unsigned long long flags[8];
+  const void* epoch;
+  void* done;
+  int n;
+};
+
 }  // namespace ksana
 
 using namespace ksana;
@@ -898,7 +926,7 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
                        const void* residual, int ldr, int M, int N, int K, int ctas_hint, void* scratch,
                        long long scratch_bytes, void* counters, int counters_len, int* err_flag,
                        cudaStream_t st, const unsigned long long* push_ptrs, int push_n, const void* w4_scale = nullptr,
-                       const void* w4_zs = nullptr, int w4_group = 0) {
+                       const void* w4_zs = nullptr, int w4_group = 0, const PushSignal* sig = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (M > 128) return -20;
   if (kind < 0 || kind > 3) return -10;
@@ -960,6 +988,12 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
   p.prof = g_smallm_prof;
   for (int i = 0; i < push_n && i < 8; ++i) p.push[i] = reinterpret_cast<__nv_bfloat16*>(push_ptrs[i]);
   p.push_n = push_n;
+  if (sig && sig->n > 0 && push_n > 0) {
+    for (int i = 0; i < sig->n && i < 8; ++i) p.sig_flags[i] = reinterpret_cast<uint32_t*>(sig->flags[i]);
+    p.sig_epoch = static_cast<const uint32_t*>(sig->epoch);
+    p.sig_done = static_cast<unsigned int*>(sig->done);
+    p.sig_n = sig->n;
+  }
   if (w4) {
     p.w4 = static_cast<const uint8_t*>(W);
     p.w4_scale = static_cast<const __half*>(w4_scale);
@@ -1009,6 +1043,23 @@ extern "C" int ksana_gemm_smallm_push(int kind, const void* X, int ldx, const fl
                                       cudaStream_t st) {
   return smallm_impl(kind, X, ldx, a_scale, a_scale_ld, W, ldw, w_scale, nullptr, nullptr, ldd, bias, nullptr, 0, M, N,
                      K, 0, scratch, scratch_bytes, counters, counters_len, err_flag, st, push_ptrs, push_n);
+}
+
+// Push mode with the delivery flag raised by the GEMM itself: sig_flags[r] = address of this rank's flag word in rank
+// r's flag pad, sig_epoch = the device counter of completed exchanges (the flag value is that counter + 1),
+// sig_done = a zeroed device word counting finished CTAs (left at zero).
+extern "C" int ksana_gemm_smallm_push_signal(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld,
+                                             const void* W, int ldw, const float* w_scale, int ldd, const void* bias,
+                                             int M, int N, int K, void* scratch, long long scratch_bytes, void* counters,
+                                             int counters_len, const unsigned long long* push_ptrs, int push_n,
+                                             const unsigned long long* sig_flags, const void* sig_epoch, void* sig_done,
+                                             int* err_flag, cudaStream_t st) {
+  PushSignal sig{};
+  for (int i = 0; i < push_n && i < 8; ++i) sig.flags[i] = sig_flags[i];
+  sig.epoch = sig_epoch; sig.done = sig_done; sig.n = push_n;
+  return smallm_impl(kind, X, ldx, a_scale, a_scale_ld, W, ldw, w_scale, nullptr, nullptr, ldd, bias, nullptr, 0, M, N,
+                     K, 0, scratch, scratch_bytes, counters, counters_len, err_flag, st, push_ptrs, push_n, nullptr,
+                     nullptr, 0, &sig);
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -38,6 +38,8 @@ _SIGS = {
     "ksana_moe_permute": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
     "ksana_moe_combine": [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_smallm_push": [i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, vp, i64, vp, i32, vp, i32, vp, vp],
+    "ksana_gemm_smallm_push_signal": [i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, vp, i64, vp, i32, vp, i32,
+                                      vp, vp, vp, vp, vp],
     "ksana_gemm_fp8_block_push": [vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_gemm_bf16_push": [vp, i32, vp, i32, i32, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_reduce_norm": [vp, vp, i32, i32, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp, f32, i32, vp, vp, vp, i32, i32,

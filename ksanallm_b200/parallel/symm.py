@@ -92,6 +92,9 @@ class SymmetricComm:
         want = os.environ.get("KSANA_NVLS")
         self.use_nvls = bool(self.mc_ptr) and (want == "1" or (want is None and size >= 4))
         self.ctrs = torch.zeros(16, dtype=torch.int32, device=self.device)
+        # address of this rank's "partial rows delivered" flag (kind 0) in every rank's flag pad
+        self.sig_flag_ptrs = (C.c_ulonglong * 8)(*[(ptrs[r] + 4 * rank if r < size else 0) for r in range(8)])
+        self.push_signal = os.environ.get("KSANA_PUSH_SIGNAL", "0") == "1"
         self.parity = 0
         dist.barrier(group)
         # local views
@@ -276,16 +279,21 @@ class SymmetricComm:
             linear(x, W if self.rank == 0 else W.without_bias(), out=part)
         elif one_shot:
             scratch, counters = native.gemm_workspace(self.device)
+            gemm_signals = self.push_signal
             if W.fp8:
-                rc = lib.ksana_gemm_smallm_push(2 if W.ue8m0 else 1, x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0),
-                                                W.wq.data_ptr(), W.wq.stride(0), W.ws.data_ptr(), H, bias, M, H,
-                                                W.in_features, scratch.data_ptr(), scratch.numel() * 4,
-                                                counters.data_ptr(), counters.numel(), push, self.size, err, st)
+                head = (2 if W.ue8m0 else 1, x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0), W.wq.data_ptr(),
+                        W.wq.stride(0), W.ws.data_ptr())
             else:
-                rc = lib.ksana_gemm_smallm_push(0, x.data_ptr(), x.stride(0), None, 0, W.w.data_ptr(), W.w.stride(0),
-                                                None, H, bias, M, H, W.in_features, scratch.data_ptr(),
-                                                scratch.numel() * 4, counters.data_ptr(), counters.numel(), push,
-                                                self.size, err, st)
+                head = (0, x.data_ptr(), x.stride(0), None, 0, W.w.data_ptr(), W.w.stride(0), None)
+            tail = (H, bias, M, H, W.in_features, scratch.data_ptr(), scratch.numel() * 4, counters.data_ptr(),
+                    counters.numel(), push, self.size)
+            if gemm_signals:
+                # the GEMM's last CTA raises this rank's flag at the peers once its pushes are out: the reduce kernel
+                # below then only waits (gather bit 4)
+                rc = lib.ksana_gemm_smallm_push_signal(*head, *tail, self.sig_flag_ptrs, self.ctrs.data_ptr(),
+                                                       self.ctrs[12:13].data_ptr(), err, st)
+            else:
+                rc = lib.ksana_gemm_smallm_push(*head, *tail, err, st)
             native._check(rc, "ksana_gemm_smallm_push")
         else:
             if W.fp8 and W.ue8m0 and M >= native.MX_MIN_M:
@@ -303,6 +311,8 @@ class SymmetricComm:
         want_q = quant_for is not None and quant_for.fp8 and H % 128 == 0 and norm_w is not None
         if one_shot:
             row_begin, row_count, gather = 0, M, (4 if (writer is not None or not push_mode) else 0)
+            if push_mode and writer is None and self.push_signal:
+                gather |= 16
             y = torch.empty(M, H, dtype=torch.bfloat16, device=self.device) if (norm_w is not None and not want_q) else None
             yq = torch.empty(M, H, dtype=torch.float8_e4m3fn, device=self.device) if want_q else None
             scale_ld = (M + 3) // 4 * 4

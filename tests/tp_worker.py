@@ -53,9 +53,9 @@ def main():
     say("llm ready")
     inner = llm.engine.runner.execute
 
-    def traced(plan, extra=None):
+    def traced(plan, extra=None, patch=None):
         say("execute: seqs", len(plan.seq_ids), "tokens", plan.num_tokens, "multi", plan.num_multi)
-        out = inner(plan, extra)
+        out = inner(plan, extra, patch)
         say("launched")
         return out
 
