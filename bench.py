@@ -363,7 +363,11 @@ def main():
             "clocks": clocks, "gpu_launches": launches,
             "tp_check": ({"rel_err_fused_vs_nccl": tp_numerics, "limits": TP_CHECK_LIMITS} if tp_numerics is not None else None),
             "graph_replays": getattr(llm.engine.runner, "graph_replays", 0),
-            "host_ms_per_engine_step": {k: round(v / max(1, host_ms.get("steps", 1)), 3) for k, v in host_ms.items() if k != "steps"},
+            "host_ms_per_engine_step": {k: round(v / max(1, host_ms.get("steps", 1)), 3) for k, v in host_ms.items()
+                                        if k != "steps" and not k.endswith(("_wall", "_n"))},
+            "loop_ms_per_iteration": {ph.lower(): round(host_ms[ph + "_wall"] / max(1, host_ms.get(ph + "_n", 1)), 3)
+                                      for ph in ("Prefill", "Decode") if ph + "_wall" in host_ms},
+            "loop_iterations": {ph.lower(): host_ms.get(ph + "_n", 0) for ph in ("Prefill", "Decode")},
             "engine_steps": host_ms.get("steps", 0),
         }
         if e2e_ms is not None:

@@ -14,7 +14,10 @@ dependency chain itself costs.
   torchrun --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/step_breakdown.py --phase decode   (real TP ranks;
         communication kernels appear as classes of their own, every rank replays the same graphs in the same order)
 
-Prints one JSON line (rank 0) with the table; ``bench.py --breakdown`` calls the same function.
+``--phase both`` times a decode and a prefill step of the same model; ``--variants`` repeats the measurement under
+several settings of the environment switches (read per call by the communication layer) without starting over.
+
+Prints one JSON line per table (rank 0); ``bench.py --breakdown`` calls the same function.
 """
 from __future__ import annotations
 
@@ -87,7 +90,10 @@ def build_step(torch, model, phase, batch, ctx, q_len, block_tokens):
     return step, batch * bps
 
 
-def run_breakdown(model, phase="decode", batch=64, ctx=2176, q_len=2048, reps=10, block_tokens=16, sync_all=None):
+def run_breakdown(model, phase="decode", batch=64, ctx=2176, q_len=2048, reps=10, block_tokens=16, sync_all=None,
+                  classes=True):
+    """``classes=False`` times the whole step only: needed when a kernel of one class waits for a flag that a kernel of
+    another class raises (a graph of one class alone would wait until its limit)."""
     import torch
     from ksanallm_b200.ops import native
     step, nblocks = build_step(torch, model, phase, batch, ctx, q_len, block_tokens)
@@ -110,7 +116,7 @@ def run_breakdown(model, phase="decode", batch=64, ctx=2176, q_len=2048, reps=10
         for name, fn, args in calls:
             groups.setdefault(_class_key(name, args), []).append((fn, args))
         rows = []
-        for key, lst in groups.items():
+        for key, lst in (groups.items() if classes else ()):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 st = torch.cuda.current_stream().cuda_stream
@@ -127,8 +133,11 @@ def run_breakdown(model, phase="decode", batch=64, ctx=2176, q_len=2048, reps=10
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--phase", default="decode", choices=["decode", "prefill"])
-    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--phase", default="decode", choices=["decode", "prefill", "both"])
+    ap.add_argument("--batch", type=int, default=64, help="sequences of the decode step")
+    ap.add_argument("--prefill-batch", type=int, default=None, help="sequences of the prefill step (default: --batch)")
+    ap.add_argument("--variants", default="", help="settings to time one after the other in this process, e.g. "
+                    "'base:;nopush:KSANA_PUSH=0;sig:KSANA_PUSH=1,KSANA_PUSH_SIGNAL=1' (name:VAR=value,...)")
     ap.add_argument("--ctx", type=int, default=2176)
     ap.add_argument("--q-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=80)
@@ -156,7 +165,9 @@ def main():
                      vocab_size=128256 // e, rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8192,
                      max_token_len=8192, eos_token_ids=[1])
     ref.WEIGHT_SCALE_POW2 = args.scale_mode != "fp32"
-    tokens = args.batch if args.phase == "decode" else args.batch * args.q_len
+    phases = ["decode", "prefill"] if args.phase == "both" else [args.phase]
+    pbatch = args.prefill_batch if args.prefill_batch is not None else args.batch
+    tokens = max(args.batch if "decode" in phases else 0, pbatch * args.q_len if "prefill" in phases else 0)
     comm = TPComm(dev_group, rank, world, args.comm, dev, max_tokens=max(tokens, 64), hidden=mc.hidden_size) if world > 1 else None
     model = build_model(mc, RandomSource(seed=0, on_device=True), rank, world, comm, dev, torch.bfloat16, "fp8_block",
                         max_positions=max(args.ctx, args.q_len) + 64)
@@ -166,17 +177,31 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    res = run_breakdown(model, args.phase, args.batch, args.ctx, args.q_len, args.reps, sync_all=sync_all)
-    res["world"] = world
-    res["emulate_tp"] = e
-    res["comm"] = args.comm if world > 1 else None
-    if rank == 0:
-        print(json.dumps(res))
-        print("%-58s %6s %10s %8s" % ("class", "n", "us total", "us each"), file=sys.stderr)
-        for r in res["classes"]:
-            print("%-58s %6d %10.1f %8.2f" % (r["class"][:58], r["launches"], r["us_total"], r["us_each"]), file=sys.stderr)
-        print("full graph %.1f us; sum of classes %.1f us; %d launches" %
-              (res["full_graph_us"], res["sum_of_classes_us"], res["native_launches"]), file=sys.stderr)
+    variants = []
+    for item in (args.variants.split(";") if args.variants else [":"]):
+        name, _, sets = item.partition(":")
+        variants.append((name or "default", dict(kv.split("=", 1) for kv in sets.split(",") if kv)))
+    base_env = {k: os.environ.get(k) for _, env in variants for k in env}
+    # phase by phase (a prefill step leaves the GPU at the power cap, which would slow the decode step timed after it)
+    for phase in phases:
+        for name, env in variants:
+            for k, v in base_env.items():          # every variant starts from the environment the process was given
+                if v is None:
+                    os.environ.pop(k, None)
+                else:
+                    os.environ[k] = v
+            os.environ.update(env)
+            res = run_breakdown(model, phase, args.batch if phase == "decode" else pbatch, args.ctx, args.q_len, args.reps,
+                                sync_all=sync_all, classes=os.environ.get("KSANA_PUSH_SIGNAL", "0") != "1")
+            res.update(world=world, emulate_tp=e, comm=args.comm if world > 1 else None, variant=name, env=env)
+            if rank == 0:
+                print(json.dumps(res))
+                print("== %s / %s %s" % (name, phase, env), file=sys.stderr)
+                print("%-58s %6s %10s %8s" % ("class", "n", "us total", "us each"), file=sys.stderr)
+                for r in res["classes"]:
+                    print("%-58s %6d %10.1f %8.2f" % (r["class"][:58], r["launches"], r["us_total"], r["us_each"]), file=sys.stderr)
+                print("full graph %.1f us; sum of classes %.1f us; %d launches" %
+                      (res["full_graph_us"], res["sum_of_classes_us"], res["native_launches"]), file=sys.stderr)
     sys.stdout.flush()
     if world > 1:
         dist.barrier()

@@ -125,7 +125,7 @@ __device__ __forceinline__ bool end_epoch(uint32_t* ctrs, int kind, uint32_t epo
 }
 
 // "My rows are delivered": the last block of a kernel that pushed rows to the peers raises flag `kind` at every
-// peer with the next epoch of that kind; the consumer's wait (gather_wait_kernel, or a GEMM that waits itself)
+// peer with the next epoch of that kind; the consumer's wait (the last block of gather_finish_kernel)
 // reads the same counter after this kernel has finished.
 __device__ __forceinline__ void signal_delivered(const CommPeers& c, uint32_t* ctrs, int kind) {
   const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(ctrs + kind) + 1;
@@ -194,7 +194,7 @@ __device__ __forceinline__ void reduce_norm_body(const ReduceNormParams& p) {
   if (!signal_and_wait(c, 0, epoch, p.err, (p.gather & 16) == 0)) return;
   const int lrow = blockIdx.x;                  // row inside this rank's slice
   if (lrow >= p.row_count) {          // a rank without rows only exchanges flags
-    if (end_epoch(p.ctrs, 0, epoch, (p.gather & 1) != 0) && (p.gather & 1)) signal_delivered(c, p.ctrs, 1);
+    end_epoch(p.ctrs, 0, epoch);
     return;
   }
   const int row = p.row_begin + lrow;
@@ -339,22 +339,24 @@ __device__ __forceinline__ void reduce_norm_body(const ReduceNormParams& p) {
 #pragma unroll
         for (int off = 8; off > 0; off >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, off));
         const float scale = fp8_group_scale(am);
+        // two neighbouring threads' eight bytes leave as one 16-byte store (local copy and peers alike); the scales
+        // stay local here: a scale per row and K block is four bytes in a column of its own, and pushed one by one
+        // they cost a link packet each - the finishing kernel sends this rank's slice of every scale row in one piece
+        uint2 q = make_uint2(0u, 0u);
+        if (on) q = pack8_e4m3c(o, 1.f / scale);
+        const uint32_t nx = __shfl_down_sync(0xffffffffu, q.x, 1), ny = __shfl_down_sync(0xffffffffu, q.y, 1);
         if (on) {
-          const uint2 q = pack8_e4m3c(o, 1.f / scale);
-          reinterpret_cast<uint2*>(p.yq + static_cast<size_t>(row) * p.H)[i] = q;
           if ((i & 15) == 0) p.yscale[static_cast<size_t>(i >> 4) * p.scale_ld + row] = scale;
-          if ((p.gather & 1) && p.mc) {
-            multimem_st8(p.mc + p.yq_sym_off + static_cast<size_t>(row) * p.H + static_cast<size_t>(i) * 8, q);
-            if ((i & 15) == 0)
-              multimem_st4(p.mc + p.ys_sym_off + (static_cast<size_t>(i >> 4) * p.scale_ld + row) * 4, scale);
-          } else if (p.gather & 1) {
-            for (int r = 0; r < c.size; ++r) {
-              if (r == c.rank) continue;
-              uint8_t* pq = static_cast<uint8_t*>(c.data[r]) + p.yq_sym_off;
-              reinterpret_cast<uint2*>(pq + static_cast<size_t>(row) * p.H)[i] = q;
-              if ((i & 15) == 0) {
-                float* ps = reinterpret_cast<float*>(static_cast<uint8_t*>(c.data[r]) + p.ys_sym_off);
-                ps[static_cast<size_t>(i >> 4) * p.scale_ld + row] = scale;
+          if ((threadIdx.x & 1) == 0) {
+            const uint4 qq = make_uint4(q.x, q.y, nx, ny);
+            const size_t at = static_cast<size_t>(row) * p.H + static_cast<size_t>(i) * 8;
+            *reinterpret_cast<uint4*>(p.yq + at) = qq;
+            if ((p.gather & 1) && p.mc) {
+              multimem_st16(p.mc + p.yq_sym_off + at, qq);
+            } else if (p.gather & 1) {
+              for (int r = 0; r < c.size; ++r) {
+                if (r == c.rank) continue;
+                *reinterpret_cast<uint4*>(static_cast<uint8_t*>(c.data[r]) + p.yq_sym_off + at) = qq;
               }
             }
           }
@@ -362,19 +364,58 @@ __device__ __forceinline__ void reduce_norm_body(const ReduceNormParams& p) {
       }
     }
   }
-  // gather mode: once every block's pushes are visible, the last block tells the peers that this rank's slice is there
-  if (end_epoch(p.ctrs, 0, epoch, (p.gather & 1) != 0) && (p.gather & 1)) signal_delivered(c, p.ctrs, 1);
+  // gather mode: gather_finish_kernel, next in the stream, tells the peers that this rank's slice is there
+  end_epoch(p.ctrs, 0, epoch);
 }
 
 __global__ void __launch_bounds__(1024) reduce_norm_kernel_v1(const ReduceNormParams p) { reduce_norm_body<1>(p); }
 __global__ void reduce_norm_kernel_v4(const ReduceNormParams p) { reduce_norm_body<kRnMaxVec>(p); }
 
-// Second half of the gather mode: wait until every peer has flagged its slice as delivered (the flag is raised by
-// the last block of the peer's reduce_norm_kernel). Stream-ordered after this rank's own reduce_norm_kernel, so the
-// epoch to wait for is the counter's current value.
-__global__ void gather_wait_kernel(const CommPeers c, const uint32_t* ctrs, int* err) {
+// Second half of the gather mode, stream-ordered after reduce_norm_kernel. (1) The FP8 scales of this rank's rows go
+// to the peers: scale row kb holds one float per token, so this rank's slice [row_begin, row_begin + row_count) is
+// contiguous and leaves as 16-byte stores (one multimem.st each with a multicast binding). (2) Once every block's
+// stores are out (system-wide fence, block count in ctrs[9]), the last block raises this rank's "slice delivered"
+// flag (kind 1) at every peer - the reduce kernel's pushes are covered by the same release, since that kernel has
+// finished - and (3) waits, bounded, until every peer has raised its own.
+__global__ void gather_finish_kernel(const CommPeers c, uint32_t* ctrs, const float* ys_local, long long ys_sym_off,
+                                     uint8_t* mc, int scale_ld, int row_begin, int row_count, int nkb, int* err) {
+  __shared__ int s_last;
   pdl_trigger();
   pdl_wait();
+  if (ys_local != nullptr && row_count > 0) {
+    for (int kb = blockIdx.x; kb < nkb; kb += gridDim.x) {
+      const size_t first = static_cast<size_t>(kb) * scale_ld + row_begin;       // in floats
+      const float* src = ys_local + first;
+      const int head = min(row_count, static_cast<int>((4 - (first & 3)) & 3));     // floats before a 16-byte boundary
+      const int nvec = (row_count - head) >> 2;
+      const int tail0 = head + nvec * 4;
+      auto put4 = [&](size_t elem, float v) {
+        if (mc) { multimem_st4(mc + ys_sym_off + elem * 4, v); return; }
+        for (int r = 0; r < c.size; ++r)
+          if (r != c.rank) reinterpret_cast<float*>(static_cast<uint8_t*>(c.data[r]) + ys_sym_off)[elem] = v;
+      };
+      for (int t = threadIdx.x; t < head; t += blockDim.x) put4(first + t, src[t]);
+      for (int t = tail0 + threadIdx.x; t < row_count; t += blockDim.x) put4(first + t, src[t]);
+      for (int t = threadIdx.x; t < nvec; t += blockDim.x) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + head + static_cast<size_t>(t) * 4);
+        const size_t at = (first + head + static_cast<size_t>(t) * 4) * 4;
+        if (mc) { multimem_st16(mc + ys_sym_off + at, v); continue; }
+        for (int r = 0; r < c.size; ++r)
+          if (r != c.rank) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(c.data[r]) + ys_sym_off + at) = v;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const bool last = atomicAdd(ctrs + 9, 1u) == gridDim.x - 1;
+    if (last) ctrs[9] = 0;
+    s_last = last ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  signal_delivered(c, ctrs, 1);
+  __syncthreads();
   const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(ctrs + 1);
   signal_and_wait(c, 1, epoch, err, false);
 }
@@ -487,8 +528,10 @@ extern "C" int ksana_reduce_norm(const unsigned long long* data_ptrs, const unsi
                                         : launch_pdl(reduce_norm_kernel_v4, grid, dim3(threads), 0, st, p);
   if (e != cudaSuccess) return -4;
   if (gather & 1) {
-    if (launch_pdl(gather_wait_kernel, dim3(1), dim3(32), 0, st, p.peers, static_cast<const uint32_t*>(p.ctrs), err) !=
-        cudaSuccess) return -5;
+    const int nkb = yq ? H / 128 : 0;
+    if (launch_pdl(gather_finish_kernel, dim3(nkb > 0 ? (nkb < 64 ? nkb : 64) : 1), dim3(256), 0, st, p.peers, p.ctrs,
+                   static_cast<const float*>(yq ? yscale : nullptr), ys_sym_off, p.mc, scale_ld, row_begin, row_count,
+                   nkb, err) != cudaSuccess) return -5;
   }
   return 0;
 }

@@ -459,6 +459,60 @@ __global__ void swap_blocks_kernel(uint4* __restrict__ cache, uint4* __restrict_
   }
 }
 
+// Flexible-cache copies land at another position of the sequence: the K rows of the destination block are rotated by
+// the position delta (rotary rotations add, so one rotation by |delta| with the sign on the sine does it), in place,
+// for every layer and KV head of the block. triples[3*i] = source block (unused here), [3*i+1] = destination block,
+// [3*i+2] = position delta. Cache layout [blocks][layers][2][kv heads][block tokens][head dim], K panel first;
+// cos_sin [max_pos][rot_dim] = cos | sin (fp32). FP8 caches are rotated on their raw values (the tensor scale is
+// a common factor). Bad block ids and deltas beyond the table are recorded in the error word and skipped.
+template <typename T>
+__device__ __forceinline__ float kv_to_float(T v);
+template <> __device__ __forceinline__ float kv_to_float<bf16>(bf16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float kv_to_float<uint8_t>(uint8_t v) {
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(v, __NV_E4M3)));
+}
+template <typename T>
+__device__ __forceinline__ T kv_from_float(float v);
+template <> __device__ __forceinline__ bf16 kv_from_float<bf16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ uint8_t kv_from_float<uint8_t>(float v) {
+  return __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+template <typename T>
+__global__ void rerotate_blocks_kernel(T* __restrict__ cache, const int* __restrict__ triples, const float* __restrict__ cos_sin,
+                                       int max_pos, int layers, int hkv, int bt, int D, int rot_dim, int neox,
+                                       int num_blocks, int* err) {
+  const int db = triples[3 * blockIdx.x + 1], delta = triples[3 * blockIdx.x + 2];
+  if (delta == 0) return;
+  const int ad = delta < 0 ? -delta : delta;
+  if (db < 0 || db >= num_blocks || ad >= max_pos) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) guard_report(err, db < 0 || db >= num_blocks ? kGuardBlockId : kGuardPosition,
+                                                          db < 0 || db >= num_blocks ? db : ad);
+    return;
+  }
+  const int half = rot_dim >> 1;
+  const float* cs = cos_sin + static_cast<size_t>(ad) * rot_dim;
+  const float sgn = delta > 0 ? 1.f : -1.f;
+  const long long panel = static_cast<long long>(bt) * D;                 // one head's K panel
+  const long long layer_stride = 2LL * hkv * panel, block_stride = layers * layer_stride;
+  T* blk = cache + static_cast<size_t>(db) * block_stride;
+  const long long pairs = static_cast<long long>(layers) * hkv * bt * half;
+  for (long long i = blockIdx.y * static_cast<long long>(blockDim.x) + threadIdx.x; i < pairs;
+       i += static_cast<long long>(gridDim.y) * blockDim.x) {
+    const int j = static_cast<int>(i % half);
+    long long t = i / half;
+    const int tok = static_cast<int>(t % bt); t /= bt;
+    const int head = static_cast<int>(t % hkv);
+    const int layer = static_cast<int>(t / hkv);
+    T* row = blk + layer * layer_stride + head * panel + static_cast<long long>(tok) * D;
+    const int i0 = neox ? j : 2 * j, i1 = neox ? j + half : 2 * j + 1;
+    const float c = cs[j], sn = cs[half + j] * sgn;
+    const float x0 = kv_to_float<T>(row[i0]), x1 = kv_to_float<T>(row[i1]);
+    row[i0] = kv_from_float<T>(x0 * c - x1 * sn);
+    row[i1] = kv_from_float<T>(x1 * c + x0 * sn);
+  }
+}
+
 // ids[rows[i]] = prev_tokens[src[i]]: a pipelined step takes the input ids of its decode rows straight from the
 // previous step's sampler output on the device (the host has not read those tokens yet).
 __global__ void patch_ids_kernel(int* __restrict__ ids, const int* __restrict__ rows, const int* __restrict__ src,
@@ -660,6 +714,21 @@ extern "C" int ksana_swap_blocks(void* cache, void* pool, const int* pairs, int 
   if (block_bytes % 16) return -10;
   swap_blocks_kernel<<<dim3(n, 16), 256, 0, st>>>((uint4*)cache, (uint4*)pool, pairs, block_bytes / 16, dir, num_blocks,
                                                   num_pool_blocks, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// kv_bytes: 2 (bf16 cache) or 1 (e4m3 cache).
+extern "C" int ksana_rerotate_blocks(void* cache, const int* triples, int n, const float* cos_sin, int max_pos, int layers,
+                                     int hkv, int bt, int D, int rot_dim, int neox, int kv_bytes, int num_blocks,
+                                     int* err, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (rot_dim <= 0 || rot_dim > D || (rot_dim & 1) || (kv_bytes != 1 && kv_bytes != 2)) return -10;
+  if (kv_bytes == 2)
+    rerotate_blocks_kernel<bf16><<<dim3(n, 8), 256, 0, st>>>((bf16*)cache, triples, cos_sin, max_pos, layers, hkv, bt, D,
+                                                            rot_dim, neox, num_blocks, err);
+  else
+    rerotate_blocks_kernel<uint8_t><<<dim3(n, 8), 256, 0, st>>>((uint8_t*)cache, triples, cos_sin, max_pos, layers, hkv,
+                                                                bt, D, rot_dim, neox, num_blocks, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -23,6 +23,7 @@
 // (src/ksana_llm/kernels/nvidia/kernel_wrapper.cpp:1014-1048) or DeepGEMM block-wise on Hopper.
 #include "sm100_ptx.cuh"
 #include "pdl.cuh"
+#include "push_epilogue.cuh"
 #include <cuda_bf16.h>
 #include <stdio.h>
 
@@ -45,7 +46,8 @@ struct MxCfg {
   static constexpr int kSfCols = 4 * (1 + kBChunks);          // TMEM columns of one scale set
   static constexpr int kSfBase = kAccStages * BN;             // first scale column
   static constexpr int kTmemCols = 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kMxSfStages * kSfStageBytes + 1024 + 512;
+  static constexpr int kEpiStageBytes = 8 * kPushStageBytes;   // push epilogue: one transposition buffer per epilogue warp
+  static constexpr int kSmemBytes = kStages * kStageBytes + kMxSfStages * kSfStageBytes + 1024 + 512 + kEpiStageBytes;
   static constexpr int kEpiCols = BN / 2;
 };
 
@@ -88,6 +90,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   uint64_t* tempty_bar = tfull_bar + Cfg::kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + Cfg::kAccStages);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint8_t* epi_stage = reinterpret_cast<uint8_t*>(bars) + 512;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + kMxBM - 1) / kMxBM;
@@ -304,6 +307,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);     // the accumulator is in registers: the next tile may start
       if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
+      if (p.push_n && !p.out_f32) {
+        // rows for the peers: contiguous runs of EC columns per row (see push_epilogue.cuh)
+        push_rows_staged<EC>(epi_stage + (warp - 3) * kPushStageBytes, r, p.bias, lane, m_blk * kMxBM + q * 32, n0, p.M,
+                             p.N, p.push, p.push_n, p.push_rows, p.ldd);
+        continue;
+      }
       if (!row_ok) continue;
 #pragma unroll
       for (int c0 = 0; c0 < EC; c0 += 8) {
@@ -333,12 +342,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
           for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
-          if (p.push_n) {
-            const int owner = min(row / p.push_rows, p.push_n - 1);
-            *reinterpret_cast<uint4*>(p.push[owner] + static_cast<size_t>(row - owner * p.push_rows) * p.ldd + col) = ov;
-          } else {
-            *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(row) * p.ldd + col) = ov;
-          }
+          *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(row) * p.ldd + col) = ov;
         }
       }
     }

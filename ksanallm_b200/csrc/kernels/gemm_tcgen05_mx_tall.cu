@@ -21,6 +21,7 @@
 // The reference has no counterpart (its FP8 GEMMs are cuBLASLt per-tensor or DeepGEMM on Hopper:
 // src/ksana_llm/kernels/nvidia/kernel_wrapper.cpp:1014-1048).
 #include "sm100_ptx.cuh"
+#include "push_epilogue.cuh"
 #include <cuda_bf16.h>
 #include <stdio.h>
 
@@ -39,7 +40,7 @@ constexpr int kTlSfStageBytes = 4 * 512;
 constexpr int kTlSfCols = 16;                 // TMEM columns of one scale set: 2 x 4 (rows) + 2 x 4 (columns)
 constexpr int kTlSfBase = 2 * kTlBN;          // first scale column
 constexpr int kTlTmemCols = 512;
-constexpr int kTlSmemBytes = kTlStages * kTlStageBytes + kTlSfStages * kTlSfStageBytes + 1024 + 512;
+constexpr int kTlSmemBytes = kTlStages * kTlStageBytes + kTlSfStages * kTlSfStageBytes + 1024 + 512 + 8 * kPushStageBytes;
 constexpr int kTlGroupM = 8;                  // 256-row tiles per raster group
 constexpr int kTlPass = kTlBN / 2;            // columns per epilogue pass
 
@@ -79,6 +80,7 @@ gemm_mxfp8_tall_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   uint64_t* tempty_bar = tfull_bar + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint8_t* epi_stage = reinterpret_cast<uint8_t*>(bars) + 512;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + kTlBM - 1) / kTlBM;
@@ -294,6 +296,12 @@ gemm_mxfp8_tall_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar);       // the accumulator is in registers: the next tile may start
         }
+        if (p.push_n && !p.out_f32) {
+          // rows for the peers: one contiguous run of kTlPass columns (224 bytes) per row (see push_epilogue.cuh)
+          push_rows_staged<kTlPass>(epi_stage + (warp - 3) * kPushStageBytes, r, p.bias, lane,
+                                    m_blk * kTlBM + h * 128 + q * 32, n0, p.M, p.N, p.push, p.push_n, p.push_rows, p.ldd);
+          continue;
+        }
         if (!row_ok) continue;
 #pragma unroll
         for (int c0 = 0; c0 < kTlPass; c0 += 8) {
@@ -323,12 +331,7 @@ gemm_mxfp8_tall_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
             for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
-            if (p.push_n) {
-              const int owner = min(row / p.push_rows, p.push_n - 1);
-              *reinterpret_cast<uint4*>(p.push[owner] + static_cast<size_t>(row - owner * p.push_rows) * p.ldd + col) = ov;
-            } else {
-              *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(row) * p.ldd + col) = ov;
-            }
+            *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(row) * p.ldd + col) = ov;
           }
         }
       }

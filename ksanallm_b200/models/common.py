@@ -16,10 +16,12 @@ import math
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 from ..config import ModelConfig
 from ..ops import dispatch as ops
+from ..ops import native
 from ..ops import reference as ref
 from ..ops.dispatch import LinearWeight
 from ..utils import nvtx
@@ -274,8 +276,15 @@ class CommonModel:
 
     def rerotate_blocks(self, triples) -> None:
         """Flexible-cache copies land at another position: rotate the copied K by the position delta
-        (RoPE rotations add), layer by layer. Rare path, plain tensor ops."""
+        (RoPE rotations add), every layer and KV head of the destination blocks. One kernel on the GPU
+        (``ksana_rerotate_blocks``); plain tensor ops elsewhere."""
         if self.cos_sin is None:
+            return
+        kv = self.kv_cache
+        if (kv.is_cuda and native.available() and kv.dim() == 6 and self.cos_sin.dtype == torch.float32 and
+                kv.dtype in (torch.bfloat16, torch.float8_e4m3fn)):
+            t3 = torch.as_tensor(np.ascontiguousarray(triples, dtype=np.int32)).to(kv.device, non_blocking=False)
+            native.rerotate_blocks(kv, t3, self.cos_sin, self.rot_dim, self.cfg.rope_neox)
             return
         half = self.rot_dim // 2
         for src, dst, delta in triples:

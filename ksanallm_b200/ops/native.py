@@ -60,6 +60,7 @@ _SIGS = {
     "ksana_swap_blocks": [vp, vp, vp, i32, i64, i32, i32, i32, vp, vp],
     "ksana_add": [vp, vp, vp, vp, i64, i32, vp],
     "ksana_patch_ids": [vp, vp, vp, vp, i32, i32, i32, vp, vp],
+    "ksana_rerotate_blocks": [vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_cast_f32": [vp, vp, i64, vp],
     "ksana_paged_prefill_tc": [vp, i64, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i64,
                                vp, vp],
@@ -565,6 +566,16 @@ def patch_ids(ids, rows, src, prev_tokens):
     """ids[rows[i]] = prev_tokens[src[i]] on the device (all int32)."""
     _check(lib().ksana_patch_ids(_p(ids), _p(rows), _p(src), _p(prev_tokens), rows.numel(), ids.numel(),
                                  prev_tokens.numel(), _p(err_flag(ids.device)), _st()), "ksana_patch_ids")
+
+
+def rerotate_blocks(cache, triples, cos_sin, rot_dim, neox):
+    """Rotate the K rows of the destination blocks of ``triples`` (int32 [n, 3] on the device: source block,
+    destination block, position delta) by their position deltas, in place. ``cache``: [blocks, layers, 2, kv heads,
+    block tokens, head dim], bf16 or e4m3; ``cos_sin``: [max_pos, rot_dim] fp32."""
+    nb, layers, _, hkv, bt, D = cache.shape
+    _check(lib().ksana_rerotate_blocks(_p(cache), _p(triples), triples.shape[0], _p(cos_sin), cos_sin.shape[0], layers,
+                                       hkv, bt, D, rot_dim, int(bool(neox)), cache.element_size(), nb,
+                                       _p(err_flag(cache.device)), _st()), "ksana_rerotate_blocks")
 
 
 def add(a, b=None, bias=None, out=None):

@@ -16,9 +16,11 @@ Row-parallel linear:
   * more rows: the GEMM writes its partial product into its own symmetric buffer; one kernel per rank then
     pulls the rows it owns from every peer (coalesced peer loads: reduce-scatter), adds the residual,
     normalises (+ FP8 quantises) and pushes the result rows to every peer (all-gather), followed by one more
-    flag exchange. The residual stream stays sharded by rows: only its owner ever reads it. (Pushing partial
-    tiles from the GEMM epilogue, one 16-byte store per row and thread, ran NVLink at a fraction of its rate;
-    ``PUSH_EPILOGUE`` keeps that variant selectable.)
+    flag exchange. The residual stream stays sharded by rows: only its owner ever reads it. With ``PUSH_EPILOGUE``
+    (KSANA_PUSH_PREFILL=1) the GEMM's epilogue stores each partial row piece straight into the receive slot of the
+    rank that owns the row (64 contiguous bytes per row and store, turned through shared memory; one 16-byte piece
+    per row and thread ran NVLink at a fraction of its rate), so the reduce-scatter traffic overlaps the tiles still
+    being computed and the reduce kernel reads local memory only.
 Every wait is bounded in the kernels; a timeout sets the device error word (see native.check_err_flag).
 """
 from __future__ import annotations
@@ -46,7 +48,8 @@ PUSH_MIN_RANKS = 4             # decode-sized batches on this many ranks or more
                                # pushes its partial rows into every rank's receive slot (posted NVLink stores that
                                # overlap with the tiles still being computed) and the reduce kernel reads local
                                # memory only; below, every rank pulls the partial rows from its peers instead
-PUSH_EPILOGUE = False          # large batches: reduce-scatter by GEMM-epilogue pushes instead of owner pulls
+PUSH_EPILOGUE = False          # large batches: reduce-scatter by GEMM-epilogue pushes (64 contiguous bytes per row
+                               # and store) instead of owner pulls; KSANA_PUSH_PREFILL=0 / 1 overrides
 
 
 def _align(x: int, a: int = 256) -> int:
@@ -89,12 +92,9 @@ class SymmetricComm:
         self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         # in-switch reduction / replication pays from four ranks on (with two there is nothing to save); KSANA_NVLS=0 / 1
         # overrides
-        want = os.environ.get("KSANA_NVLS")
-        self.use_nvls = bool(self.mc_ptr) and (want == "1" or (want is None and size >= 4))
         self.ctrs = torch.zeros(16, dtype=torch.int32, device=self.device)
         # address of this rank's "partial rows delivered" flag (kind 0) in every rank's flag pad
         self.sig_flag_ptrs = (C.c_ulonglong * 8)(*[(ptrs[r] + 4 * rank if r < size else 0) for r in range(8)])
-        self.push_signal = os.environ.get("KSANA_PUSH_SIGNAL", "0") == "1"
         self.parity = 0
         dist.barrier(group)
         # local views
@@ -103,6 +103,22 @@ class SymmetricComm:
         self.yq = self._view(self.yq_off, (max_tokens, hidden), torch.float8_e4m3fn)
         self.ys = self._view(self.ys_off, (hidden // 128 + 1, self.scale_ld), torch.float32)
         self.stage = self._view(self.stage_off, (self.stage_bytes // 2,), torch.bfloat16)
+
+    # The switches below are read from the environment at every call (a dictionary lookup), so that one process can
+    # time several settings; all ranks must hold the same values.
+    @property
+    def use_nvls(self) -> bool:
+        want = os.environ.get("KSANA_NVLS")
+        return bool(self.mc_ptr) and (want == "1" or (want is None and self.size >= 4))
+
+    @property
+    def push_signal(self) -> bool:
+        return os.environ.get("KSANA_PUSH_SIGNAL", "0") == "1"
+
+    @property
+    def push_prefill(self) -> bool:
+        want = os.environ.get("KSANA_PUSH_PREFILL")
+        return PUSH_EPILOGUE if want is None else want == "1"
 
     def one_shot(self, M: int) -> bool:
         """Whether a row-parallel result of M rows is reduced by every rank itself (all rows pulled from every peer)
@@ -265,8 +281,11 @@ class SymmetricComm:
             x = quantize(x)
         one_shot = self.one_shot(M)
         want_push = os.environ.get("KSANA_PUSH")
-        push_mode = PUSH_EPILOGUE or (one_shot and writer is None and not W.nvfp4 and not W.w4a16 and
-                                      (want_push == "1" or (want_push is None and self.size >= PUSH_MIN_RANKS)))
+        plain_w = writer is None and not W.nvfp4 and not W.w4a16
+        if one_shot:
+            push_mode = plain_w and (want_push == "1" or (want_push is None and self.size >= PUSH_MIN_RANKS))
+        else:
+            push_mode = self.push_prefill and plain_w
         rows_per = M if one_shot else (M + self.size - 1) // self.size
         bias = W.bias.data_ptr() if (writer is None and W.bias is not None and self.rank == 0) else None
         if writer is not None:
@@ -297,8 +316,11 @@ class SymmetricComm:
             native._check(rc, "ksana_gemm_smallm_push")
         else:
             if W.fp8 and W.ue8m0 and M >= native.MX_MIN_M:
-                native.gemm_mxfp8(x.q, x.s, W.wq, W.ws, bias=W.bias if self.rank == 0 else None, push=push,
-                                  push_n=self.size, push_rows=rows_per, ldd=H)
+                tall = (native.MX_TALL_MIN_M > 0 and M >= native.MX_TALL_MIN_M and
+                        native._tall_wins(M, H, W.in_features))
+                (native.gemm_mxfp8_tall if tall else native.gemm_mxfp8)(
+                    x.q, x.s, W.wq, W.ws, bias=W.bias if self.rank == 0 else None, push=push, push_n=self.size,
+                    push_rows=rows_per, ldd=H)
                 rc = 0
             elif W.fp8:
                 rc = lib.ksana_gemm_fp8_block_push(x.q.data_ptr(), x.q.stride(0), x.s.data_ptr(), x.s.stride(0),

@@ -753,10 +753,11 @@ class LLMEngine:
                 self._resolve_flight()                   # overlaps with the step just launched
             if self.fatal is None:
                 self.scheduler.advance(plan)
-                self._flight = {"plan": plan, "handle": handle}
-            t5 = time.perf_counter()
+                self._flight = {"plan": plan, "handle": handle, "phase": phase}
             for k, v in (("schedule", t1 - t0), ("extras", t2 - t1), ("broadcast", t3 - t2), ("launch", t4 - t3)):
                 tm[k] = tm.get(k, 0.0) + v * 1000.0
+            # most of this iteration was spent waiting for the step launched by the previous one
+            self._phase_wall(fl["phase"] if fl is not None else phase, t0)
             return True
         # a step that needs the host between sampling and the next forward: finish what is in flight, then the
         # synchronous second half
@@ -782,7 +783,14 @@ class LLMEngine:
                      ("sample_and_wait", t5 - t4), ("post_step", t6 - t5), ("events", time.perf_counter() - t6)):
             tm[k] = tm.get(k, 0.0) + v * 1000.0
         tm["steps"] = tm.get("steps", 0) + 1
+        self._phase_wall(phase, t0)
         return True
+
+    def _phase_wall(self, phase: str, t0: float):
+        """Wall time of one loop iteration, booked to the phase (Prefill / Decode) it mostly served."""
+        tm = self.host_ms
+        tm[phase + "_wall"] = tm.get(phase + "_wall", 0.0) + (time.perf_counter() - t0) * 1000.0
+        tm[phase + "_n"] = tm.get(phase + "_n", 0) + 1
 
     def _pack_aux(self, patch, image) -> Optional[np.ndarray]:
         """What the worker ranks need beside the plan in a pipelined step: the rows to patch from their own copy of
@@ -874,6 +882,7 @@ class LLMEngine:
                      ("sample_and_wait", t5 - t4), ("post_step", t6 - t5), ("events", t7 - t6)):
             tm[k] = tm.get(k, 0.0) + v * 1000.0
         tm["steps"] = tm.get("steps", 0) + 1
+        self._phase_wall(phase, t0)
         return True
 
     def _sample(self, plan, logits):

@@ -50,6 +50,34 @@ def test_gemm_mxfp8(M, N, K, bn):
     assert rel_err(yf, ref.gemm_fp8(xq, xs, wq, ws, out_dtype=torch.float32)) < 2e-3
 
 
+@pytest.mark.parametrize("M,N,K,bn,ranks", [(1024, 512, 512, 256, 4), (1000, 264, 256, 128, 3), (2048, 8192, 1024, 0, 8),
+                                            (1024, 1000, 512, "tall", 4), (3000, 8192, 256, "tall", 8)])
+def test_gemm_mxfp8_push_epilogue(M, N, K, bn, ranks):
+    """Push mode: rows leave for the receive slot of the rank that reduces them (here every slot is local memory),
+    64 contiguous bytes per row and store; bits must equal the plain epilogue's."""
+    import ctypes as C
+    x, w = _operands(M, N, K, seed=M + N + K + ranks)
+    wq, ws = ref.quant_weight_fp8_block(w)
+    xq, xs = native.quant_fp8(x)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    if bn == "tall":
+        def gemm(*a, **kw):
+            kw.pop("bn")
+            return native.gemm_mxfp8_tall(*a, **kw)
+    else:
+        gemm = native.gemm_mxfp8
+    plain = gemm(xq, xs, wq, ws, torch.empty(M, N, device=DEV, dtype=torch.bfloat16), bias, bn=bn)
+    rows_per = (M + ranks - 1) // ranks
+    slots = torch.full((ranks, rows_per, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ptrs = (C.c_ulonglong * 8)(*([slots[r].data_ptr() for r in range(ranks)] + [0] * (8 - ranks)))
+    gemm(xq, xs, wq, ws, bias=bias, bn=bn, push=ptrs, push_n=ranks, push_rows=rows_per, ldd=N)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    got = slots.reshape(ranks * rows_per, N)[:M]
+    assert torch.equal(got, plain)
+    assert torch.isnan(slots.reshape(ranks * rows_per, N)[M:].float()).all()      # nothing written past the last row
+
+
 def test_gemm_fp8_exact_scales_still_served():
     """Weights whose scales are not powers of two (a checkpoint's own) stay on the exact-fp32-scale kernel."""
     from ksanallm_b200.ops.dispatch import LinearWeight, linear

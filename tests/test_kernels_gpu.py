@@ -383,3 +383,50 @@ def test_peer_wait_runs_out_and_reports_through_the_error_word():
         assert torch.equal(y, (x.float() * 2).to(torch.bfloat16))
     finally:
         lib.ksana_comm_set_spin_limit(0)
+
+
+@pytest.mark.parametrize("kv_dtype", [torch.bfloat16, torch.float8_e4m3fn])
+@pytest.mark.parametrize("neox", [True, False])
+def test_rerotate_blocks_matches_tensor_ops(kv_dtype, neox):
+    """Flexible-cache copies: K rows of the destination blocks rotated by the position delta, kernel against the
+    fp32 tensor statement (rotation by |delta| with the sign on the sine); V and other blocks untouched; a block id
+    outside the pool is recorded and skipped."""
+    from ksanallm_b200.ops import reference as ref
+    nb, layers, hkv, bt, D, rot = 12, 3, 2, 16, 128, 64
+    cache = (torch.randn(nb, layers, 2, hkv, bt, D, device=DEV) * 2).to(kv_dtype)
+    before = cache.clone()
+    cs = ref.build_cos_sin_cache(rot, 512, 10000.0, None, DEV)
+    triples = torch.tensor([[0, 3, 37], [1, 5, -120], [2, 7, 0], [4, 9, 511]], dtype=torch.int32, device=DEV)
+    native.rerotate_blocks(cache, triples, cs, rot, neox)
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    half = rot // 2
+    for _, dst, delta in triples.tolist():
+        k = before[dst, :, 0].float()
+        if delta != 0:
+            c, s = cs[abs(delta)][:half], cs[abs(delta)][half:] * (1.0 if delta > 0 else -1.0)
+            r = k[..., :rot]
+            if neox:
+                x0, x1 = r[..., :half], r[..., half:]
+                out = torch.cat([x0 * c - x1 * s, x1 * c + x0 * s], -1)
+            else:
+                x0, x1 = r[..., 0::2], r[..., 1::2]
+                out = torch.stack([x0 * c - x1 * s, x1 * c + x0 * s], -1).flatten(-2)
+            k = k.clone()
+            k[..., :rot] = out
+        got, want = cache[dst, :, 0].float(), k.to(kv_dtype).float()
+        # one rounding step apart at most (the kernel may contract the multiply-adds)
+        step = 0.008 if kv_dtype == torch.bfloat16 else 0.13
+        assert bool(((got - want).abs() <= step * want.abs() + 2e-3).all())
+        assert float((got - want).norm() / want.norm()) < (1e-3 if kv_dtype == torch.bfloat16 else 2e-2)
+        if delta == 0:
+            assert torch.equal(got, want)
+        assert torch.equal(cache[dst, :, 1].view(torch.uint8), before[dst, :, 1].view(torch.uint8))
+    untouched = [b for b in range(nb) if b not in (3, 5, 7, 9)]
+    assert torch.equal(cache[untouched].view(torch.uint8), before[untouched].view(torch.uint8))
+    bad = torch.tensor([[0, nb + 4, 5]], dtype=torch.int32, device=DEV)
+    native.rerotate_blocks(cache, bad, cs, rot, neox)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError):
+        native.check_err_flag(DEV)
+    native.clear_err_flag(DEV)

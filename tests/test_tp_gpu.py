@@ -28,10 +28,10 @@ def _launch(nproc, out, backend, quant, port, graphs=None, arch=None, **extra_en
 @pytest.mark.parametrize("push", ["0", "1"], ids=["pull", "epilogue-push"])
 def test_peer_memory_primitives(tmp_path, push):
     """The peer-memory collectives and the fused row-parallel linear against NCCL / fp32 references; once with the
-    reduce kernel pulling the partial rows from the peers and once with the GEMM epilogue pushing them (the default
-    from four ranks on)."""
+    reduce kernel pulling the partial rows from the peers and once with the GEMM epilogue pushing them (small batches:
+    the default from four ranks on; large batches: KSANA_PUSH_PREFILL)."""
     out_dir = os.environ.get("KSANA_TP_LOG_DIR", str(tmp_path))
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", KSANA_PUSH=push)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", KSANA_PUSH=push, KSANA_PUSH_PREFILL=push)
     n = min(torch.cuda.device_count(), 8)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", "29621", os.path.join(ROOT, "tests", "tp_comm_worker.py"), out_dir]

@@ -54,7 +54,7 @@ def main():
         say("nvls all_reduce max err", err)
         assert err < 0.15
     results = {}
-    for M in (4, 16, 64, 200):
+    for M in (4, 16, 64, 200, 500):
         for quant in (False, True):
             torch.manual_seed(7)
             K = 2048
