@@ -49,6 +49,9 @@ struct F4Params {
   const float* a_ts; const float* w_ts;    // per-tensor scales (device scalars)
   int* err;
   __nv_bfloat16* push[8]; int push_n; int push_rows;
+  // grouped (mixture-of-experts) mode: row tile i multiplies with expert tile_expert[i] (< 0: tile unused); W, w_bs
+  // are the experts' matrices stacked along N (expert_rows rows each) and w_ts holds one tensor scale per expert
+  const int* tile_expert; int expert_rows;
 };
 
 constexpr int kF4GroupM = 16;
@@ -108,12 +111,18 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
         f4_tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
+        int b_row = n_blk * BN;
+        if (p.tile_expert) {
+          const int e = p.tile_expert[m_blk];
+          if (e < 0) continue;                 // every role skips the tiles of unused row blocks
+          b_row += e * p.expert_rows;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           tma_load_2d(sa, &tma_a, &full_bar[stage], kb * 128, m_blk * kF4BM);
-          tma_load_2d(sa + Cfg::kABytes, &tma_b, &full_bar[stage], kb * 128, n_blk * BN);
+          tma_load_2d(sa + Cfg::kABytes, &tma_b, &full_bar[stage], kb * 128, b_row);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -128,6 +137,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       uint32_t set = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (p.tile_expert) {
+          int m_blk, n_blk;
+          f4_tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
+          if (p.tile_expert[m_blk] < 0) continue;
+        }
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -169,6 +183,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_blk, n_blk;
       f4_tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
+      size_t w_row0 = 0;
+      if (p.tile_expert) {
+        const int e = p.tile_expert[m_blk];
+        if (e < 0) continue;
+        w_row0 = static_cast<size_t>(e) * p.expert_rows;
+      }
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!mbar_wait(&sf_empty[sfs], sf_phase ^ 1, abort_flag)) { ok = false; break; }
         uint8_t* buf = sf_smem + sfs * Cfg::kSfStageBytes;
@@ -186,7 +206,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
 #pragma unroll
           for (int r4 = 0; r4 < 4; ++r4) {
             const int n = n_blk * BN + c * 128 + r4 * 32 + lane;
-            rb[c][r4] = n < p.N ? *reinterpret_cast<const uint4*>(p.w_bs + static_cast<size_t>(n) * p.w_bs_ld + kb * 16)
+            rb[c][r4] = n < p.N ? *reinterpret_cast<const uint4*>(p.w_bs + (w_row0 + n) * p.w_bs_ld + kb * 16)
                                 : make_uint4(0, 0, 0, 0);
           }
         }
@@ -221,6 +241,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       const int row = m_blk * kF4BM + q * 32 + lane;
       const int n0 = n_blk * BN + col_off;
       const bool row_ok = row < p.M;
+      int expert = 0;
+      if (p.tile_expert) {
+        expert = p.tile_expert[m_blk];
+        if (expert < 0) continue;
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       uint32_t r[EC];
@@ -232,7 +257,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);     // the accumulator is in registers: the next tile may start
       if (++acc == Cfg::kAccStages) { acc = 0; acc_phase ^= 1; }
       if (!row_ok) continue;
-      const float alpha = (p.a_ts ? *p.a_ts : 1.f) * (p.w_ts ? *p.w_ts : 1.f);
+      const float alpha = (p.a_ts ? *p.a_ts : 1.f) * (p.w_ts ? p.w_ts[expert] : 1.f);
 #pragma unroll
       for (int c0 = 0; c0 < EC; c0 += 8) {
         const int col = n0 + c0;
@@ -367,4 +392,32 @@ extern "C" int ksana_gemm_nvfp4(const void* Aq, int lda, const void* a_bs, int a
   p.a_ts = a_ts; p.w_ts = w_ts;
   p.err = err_flag;
   return bn == 256 ? launch_f4<256>(ma, mb, p, max_ctas, st) : launch_f4<128>(ma, mb, p, max_ctas, st);
+}
+
+// Grouped (mixture-of-experts) form: A_q [cap, K/2] holds expert-major rows in 128-row tiles, tile_expert[cap / 128]
+// names the expert of every tile (-1: unused, nothing is computed or stored for it). W_q [E * N, K/2], w_bs
+// [E * N, K/16] are the experts' matrices stacked along N, w_ts [E] their tensor scales. N must be a multiple of 128.
+extern "C" int ksana_gemm_grouped_nvfp4(const void* Aq, int lda, const void* a_bs, int a_bs_ld, const float* a_ts,
+                                        const void* Wq, int ldw, const void* w_bs, int w_bs_ld, const float* w_ts,
+                                        void* D, int ldd, int cap, int N, int K, int num_experts, const int* tile_expert,
+                                        int bn_hint, int* err_flag, cudaStream_t st) {
+  if (cap <= 0 || N <= 0 || K <= 0 || num_experts <= 0) return 0;
+  if ((cap % 128) || (N % 128) || (K % 256) || (lda % 16) || (ldw % 16) || (a_bs_ld % 16) || (w_bs_ld % 16) || (ldd % 8) ||
+      tile_expert == nullptr || w_ts == nullptr) return -10;
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Wq) | reinterpret_cast<uintptr_t>(a_bs) |
+       reinterpret_cast<uintptr_t>(w_bs)) & 15) return -11;
+  // a weight tile must not reach into the next expert's rows
+  int bn = (bn_hint == 128 || (N % 256)) ? 128 : 256;
+  CUtensorMap ma, mb;
+  if (f4_map(&ma, Aq, cap, K / 2, lda, kF4BM)) return -12;
+  if (f4_map(&mb, Wq, num_experts * N, K / 2, ldw, bn)) return -13;
+  F4Params p{};
+  p.M = cap; p.N = N; p.K = K;
+  p.D = static_cast<__nv_bfloat16*>(D); p.ldd = ldd;
+  p.a_bs = static_cast<const uint8_t*>(a_bs); p.a_bs_ld = a_bs_ld;
+  p.w_bs = static_cast<const uint8_t*>(w_bs); p.w_bs_ld = w_bs_ld;
+  p.a_ts = a_ts; p.w_ts = w_ts;
+  p.err = err_flag;
+  p.tile_expert = tile_expert; p.expert_rows = N;
+  return bn == 256 ? launch_f4<256>(ma, mb, p, 0, st) : launch_f4<128>(ma, mb, p, 0, st);
 }

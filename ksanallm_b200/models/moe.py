@@ -40,10 +40,21 @@ class MoEWeights:
     shared_gate: Optional[torch.Tensor] = None       # [1, H] sigmoid gate of the shared expert (Qwen2-MoE)
     expert_lo: int = 0
     expert_hi: int = 0
+    # NVFP4 experts: w13 / w2 hold packed e2m1 pairs ([rows, K/2] bytes), *_bs the e4m3 scales per 16 elements
+    # ([rows, K/16]) and *_ts one fp32 tensor scale per local expert
+    w13_bs: Optional[torch.Tensor] = None
+    w13_ts: Optional[torch.Tensor] = None
+    w2_bs: Optional[torch.Tensor] = None
+    w2_ts: Optional[torch.Tensor] = None
+
+    @property
+    def nvfp4(self) -> bool:
+        return self.w13_bs is not None
 
     def nbytes(self) -> int:
         n = 0
-        for t in (self.router, self.w13, self.w13_scale, self.w2, self.w2_scale, self.shared_gate):
+        for t in (self.router, self.w13, self.w13_scale, self.w2, self.w2_scale, self.shared_gate, self.w13_bs,
+                  self.w13_ts, self.w2_bs, self.w2_ts):
             if t is not None:
                 n += t.numel() * t.element_size()
         for w in (self.shared_gate_up, self.shared_down):
@@ -110,17 +121,27 @@ def load_moe(cfg: ModelConfig, source, prefix: str, tp_rank, tp_size, device, dt
     w13 = _cat0(w13_parts)
     w2 = _cat0(w2_parts)
     w13_s = w2_s = None
+    nv = {}
     if isinstance(w13, Fp8Pair) and isinstance(w2, Fp8Pair) and quant in (None, "fp8_block") and H % 128 == 0 and I % 128 == 0:
         # an FP8 checkpoint's expert stacks: its own values and block scales, bit for bit
         w13, w13_s = w13.q.contiguous(), w13.s.float().contiguous()
         w2, w2_s = w2.q.contiguous(), w2.s.float().contiguous()
+    elif quant == "nvfp4" and H % 256 == 0 and I % 256 == 0 and n_local > 0:
+        # NVFP4 experts: every expert's two matrices quantised on their own (e2m1 values, e4m3 scales per 16
+        # elements, one fp32 tensor scale per expert and matrix), stacked for the grouped block-scaled GEMM
+        w13, w2 = _dense(w13), _dense(w2)
+        q13 = [ref.quant_nvfp4(w13[e * 2 * I:(e + 1) * 2 * I]) for e in range(n_local)]
+        q2 = [ref.quant_nvfp4(w2[e * H:(e + 1) * H]) for e in range(n_local)]
+        nv = dict(w13_bs=torch.cat([q[1] for q in q13]).contiguous(), w13_ts=torch.stack([q[2] for q in q13]).float().contiguous(),
+                  w2_bs=torch.cat([q[1] for q in q2]).contiguous(), w2_ts=torch.stack([q[2] for q in q2]).float().contiguous())
+        w13, w2 = torch.cat([q[0] for q in q13]).contiguous(), torch.cat([q[0] for q in q2]).contiguous()
     elif quant in ("fp8_block", "nvfp4") and H % 128 == 0 and I % 128 == 0:     # grouped experts: FP8 blocks
         w13, w2 = _dense(w13), _dense(w2)
         w13, w13_s = ref.quant_weight_fp8_block(w13)
         w2, w2_s = ref.quant_weight_fp8_block(w2)
     else:
         w13, w2 = _dense(w13).to(dtype).contiguous(), _dense(w2).to(dtype).contiguous()
-    mw = MoEWeights(router, rbias, w13, w13_s, w2, w2_s, E, I, H, expert_lo=lo, expert_hi=hi)
+    mw = MoEWeights(router, rbias, w13, w13_s, w2, w2_s, E, I, H, expert_lo=lo, expert_hi=hi, **nv)
     sI_full = cfg.shared_expert_intermediate_size
     if sI_full:
         sp = prefix + "mlp.shared_expert."
@@ -203,8 +224,18 @@ def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Ten
         dst_row, tile_expert, _, _, cap = native.moe_align(ids, E, mw.expert_lo, mw.expert_hi)
         if mw.expert_lo:
             tile_expert = torch.where(tile_expert >= 0, tile_expert - mw.expert_lo, tile_expert)
-        perm = native.moe_permute(x, dst_row, K, cap)
-        if mw.w13_scale is not None:
+        perm = native.moe_permute(x, dst_row, K, cap, zero=mw.nvfp4)
+        if mw.nvfp4:
+            # activations go to NVFP4 too: one tensor scale per GEMM input from its own maximum (no host sync);
+            # padding rows are zero so that they do not enter the maximum
+            a_ts = (x.float().abs().amax() / (448.0 * 6.0)).clamp_min(1e-12).reshape(())
+            pq, pbs, _ = native.quant_nvfp4(perm, a_ts)
+            g = native.gemm_grouped_nvfp4(pq, pbs, a_ts, mw.w13, mw.w13_bs, mw.w13_ts, tile_expert, n_local, 2 * mw.inter)
+            a = native.act_mul(g, cfg.activation, True)
+            a_ts2 = (a.float().abs().amax() / (448.0 * 6.0)).clamp_min(1e-12).reshape(())
+            aq, abs_, _ = native.quant_nvfp4(a, a_ts2)
+            y = native.gemm_grouped_nvfp4(aq, abs_, a_ts2, mw.w2, mw.w2_bs, mw.w2_ts, tile_expert, n_local, H)
+        elif mw.w13_scale is not None:
             pq, ps = native.quant_fp8(perm)
             g = native.gemm_grouped(pq, mw.w13, tile_expert, n_local, 2 * mw.inter, a_scale=ps, w_scale=mw.w13_scale)
             _, aq, as_ = native.act_mul(g, cfg.activation, True, quant=True, want_out=False)
@@ -228,17 +259,32 @@ def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Ten
         logits = x.float() @ mw.router.float().t()
         ids, w = route_reference(logits, cfg, mw.router_bias)
         out = torch.zeros(T, H, dtype=torch.float32)
-        w13 = ref.dequant_weight_fp8_block(mw.w13, mw.w13_scale) if mw.w13_scale is not None else mw.w13.float()
-        w2 = ref.dequant_weight_fp8_block(mw.w2, mw.w2_scale) if mw.w2_scale is not None else mw.w2.float()
+        if mw.nvfp4:
+            I2 = 2 * mw.inter
+            w13 = torch.cat([ref.dequant_nvfp4(mw.w13[e * I2:(e + 1) * I2], mw.w13_bs[e * I2:(e + 1) * I2], mw.w13_ts[e])
+                             for e in range(n_local)])
+            w2 = torch.cat([ref.dequant_nvfp4(mw.w2[e * H:(e + 1) * H], mw.w2_bs[e * H:(e + 1) * H], mw.w2_ts[e])
+                            for e in range(n_local)])
+        else:
+            w13 = ref.dequant_weight_fp8_block(mw.w13, mw.w13_scale) if mw.w13_scale is not None else mw.w13.float()
+            w2 = ref.dequant_weight_fp8_block(mw.w2, mw.w2_scale) if mw.w2_scale is not None else mw.w2.float()
+        fq = (lambda t, ts: ref.dequant_nvfp4(*ref.quant_nvfp4(t, ts))) if mw.nvfp4 else (lambda t, ts: t)
+        a_ts = (x.float().abs().amax() / (448.0 * 6.0)).clamp_min(1e-12) if mw.nvfp4 else None
+        acts = []
         for e in range(mw.expert_lo, mw.expert_hi):
             tok, slot = (ids == e).nonzero(as_tuple=True)
             if tok.numel() == 0:
                 continue
             le = e - mw.expert_lo
-            xe = x[tok].float()
-            gu = xe @ w13[le * 2 * mw.inter:(le + 1) * 2 * mw.inter].t()
-            a = ref.act(gu[:, :mw.inter], cfg.activation) * gu[:, mw.inter:]
-            ye = a @ w2[le * H:(le + 1) * H].t()
+            xe = fq(x[tok].float(), a_ts)
+            gu = (xe @ w13[le * 2 * mw.inter:(le + 1) * 2 * mw.inter].t()).to(x.dtype).float()
+            a = (ref.act(gu[:, :mw.inter], cfg.activation) * gu[:, mw.inter:]).to(x.dtype).float()
+            acts.append((le, tok, slot, a))
+        a_ts2 = None
+        if mw.nvfp4 and acts:
+            a_ts2 = (torch.stack([a.abs().amax() for _, _, _, a in acts]).amax() / (448.0 * 6.0)).clamp_min(1e-12)
+        for le, tok, slot, a in acts:
+            ye = (fq(a, a_ts2) @ w2[le * H:(le + 1) * H].t()).to(x.dtype).float()
             out.index_add_(0, tok, ye * w[tok, slot].unsqueeze(-1))
         if shared and mw.shared_gate_up is not None:
             sg = ops.linear(x, mw.shared_gate_up)

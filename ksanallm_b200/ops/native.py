@@ -22,6 +22,7 @@ _SIGS = {
     "ksana_gemm_bf16": [vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_pair": [i32, vp, i32, vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_gemm_nvfp4": [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+    "ksana_gemm_grouped_nvfp4": [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp, vp],
     "ksana_quant_nvfp4": [vp, i32, vp, i32, vp, i32, vp, i32, i32, vp],
     "ksana_gemm_mxfp8": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, vp,
                          vp],
@@ -451,6 +452,20 @@ def gemm_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, out=None, bias=None, residual=Non
     return dst
 
 
+def gemm_grouped_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, tile_expert, E, N, out=None, bn=0):
+    """Expert-major NVFP4 rows ``aq`` [cap, K/2] (128-row tiles, one expert each, ``tile_expert`` < 0: unused) times
+    the experts' stacked NVFP4 matrices ``wq`` [E * N, K/2] with block scales ``w_bs`` [E * N, K/16] and one tensor
+    scale per expert ``w_ts`` [E]. Rows of unused tiles are left untouched."""
+    cap, K = aq.shape[0], aq.shape[1] * 2
+    if out is None:
+        out = torch.zeros(cap, N, dtype=torch.bfloat16, device=aq.device)
+    rc = lib().ksana_gemm_grouped_nvfp4(_p(aq), aq.stride(0), _p(a_bs), a_bs.stride(0), _p(a_ts), _p(wq), wq.stride(0),
+                                        _p(w_bs), w_bs.stride(0), _p(w_ts), _p(out), out.stride(0), cap, N, K, E,
+                                        _p(tile_expert), bn, _p(err_flag(aq.device)), _st())
+    _check(rc, "ksana_gemm_grouped_nvfp4")
+    return out
+
+
 W4_TENSOR_CORE = True        # rows 3..128: expand-in-kernel + tcgen05 (the CUDA-core GEMV is compute bound beyond 2 rows)
 W4_GEMV_MAX_M = 32          # up to this many rows the 4-bit weights are streamed by the GEMV kernel (8 rows per pass)
 _w4_scratch = {}
@@ -796,9 +811,10 @@ def moe_align(topk_ids, E, expert_lo=0, expert_hi=None):
     return dst_row, tile_expert, offsets, total, max_tiles * 128
 
 
-def moe_permute(x, dst_row, K, cap):
+def moe_permute(x, dst_row, K, cap, zero=False):
+    """``zero``: padding rows are zero instead of undefined (for consumers that reduce over the whole tensor)."""
     T, H = x.shape
-    perm = torch.empty(cap, H, dtype=torch.bfloat16, device=x.device)
+    perm = (torch.zeros if zero else torch.empty)(cap, H, dtype=torch.bfloat16, device=x.device)
     _check(lib().ksana_moe_permute(_p(x), _p(dst_row), _p(perm), T, K, H, cap, _p(err_flag(x.device)), _st()),
            "ksana_moe_permute")
     return perm

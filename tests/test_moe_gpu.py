@@ -77,3 +77,52 @@ def test_grouped_moe_pipeline(quant):
         a = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
         want.index_add_(0, tok, (a @ w2d[e * H:(e + 1) * H].t()) * w[tok, slot].unsqueeze(-1))
     assert rel_err(out, want) < tol, rel_err(out, want)
+
+
+def test_grouped_nvfp4_gemm_against_fp32_statement():
+    """Grouped NVFP4 GEMM: every 128-row tile of expert-major rows times its expert's e2m1 matrix (e4m3 block scales,
+    one tensor scale per expert) against the dequantised fp32 product; rows of unused tiles are not touched."""
+    torch.manual_seed(2)
+    E, N, K, cap = 5, 384, 512, 128 * 7
+    tile_expert = torch.tensor([0, 0, 2, -1, 4, 4, 3], dtype=torch.int32, device=DEV)
+    a = torch.randn(cap, K, device=DEV, dtype=torch.bfloat16)
+    a_ts = (a.float().abs().amax() / (448.0 * 6.0)).reshape(())
+    aq, abs_, _ = native.quant_nvfp4(a, a_ts)
+    ws = [torch.randn(N, K, device=DEV) * (0.02 * (e + 1)) for e in range(E)]
+    qs = [ref.quant_nvfp4(w) for w in ws]
+    wq, wbs = torch.cat([q[0] for q in qs]).contiguous(), torch.cat([q[1] for q in qs]).contiguous()
+    wts = torch.stack([q[2] for q in qs]).float().contiguous()
+    out = torch.full((cap, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    for bn in (0, 128):
+        native.gemm_grouped_nvfp4(aq, abs_, a_ts, wq, wbs, wts, tile_expert, E, N, out=out, bn=bn)
+        torch.cuda.synchronize()
+        native.check_err_flag(DEV)
+        ad = ref.dequant_nvfp4(aq, abs_, a_ts)
+        for t, e in enumerate(tile_expert.tolist()):
+            rows = slice(128 * t, 128 * (t + 1))
+            if e < 0:
+                assert bool((out[rows] == 7.0).all())
+                continue
+            want = ad[rows] @ ref.dequant_nvfp4(qs[e][0], qs[e][1], qs[e][2]).t()
+            assert rel_err(out[rows], want) < 1e-2, (t, e, rel_err(out[rows], want))
+
+
+def test_moe_block_with_nvfp4_experts_matches_cpu_statement():
+    """An MoE block whose routed experts are NVFP4 (weights and activations) on the GPU against the same block
+    restated with dequantised operands on the CPU."""
+    from ksanallm_b200.models.weights import RandomSource, build_model
+    cfg = ModelConfig(model_type="mixtral", hidden_size=512, num_layers=1, num_heads=4, num_kv_heads=2, head_dim=128,
+                      intermediate_size=512, moe_intermediate_size=512, vocab_size=1000, num_experts=8,
+                      num_experts_per_tok=2, max_position_embeddings=256, max_token_len=256)
+    from ksanallm_b200.models.moe import moe_partial
+    gpu = build_model(cfg, RandomSource(seed=4, std=0.05), device=DEV, dtype=torch.bfloat16, quant="nvfp4")
+    cpu = build_model(cfg, RandomSource(seed=4, std=0.05), device="cpu", dtype=torch.bfloat16, quant="nvfp4")
+    mw_g, mw_c = gpu.layers[0].moe, cpu.layers[0].moe
+    assert mw_g.nvfp4 and mw_c.nvfp4
+    assert torch.equal(mw_g.w13.cpu(), mw_c.w13) and torch.equal(mw_g.w2_bs.cpu().view(torch.uint8), mw_c.w2_bs.view(torch.uint8))
+    x = torch.randn(200, 512, dtype=torch.bfloat16) * 0.5
+    got = moe_partial(gpu, mw_g, x.to(DEV)).float().cpu()
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    want = moe_partial(cpu, mw_c, x).float()
+    assert rel_err(got, want) < 0.12, rel_err(got, want)      # e2m1 bucket flips of the second GEMM's input
