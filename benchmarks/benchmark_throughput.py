@@ -143,6 +143,11 @@ def apply_chat_template(args, prompt: str, tokenizer=None) -> str:
 
 
 def build_payload(args, prompt, max_new_tokens: Optional[int] = None) -> dict:
+    builder = BACKENDS[getattr(args, "backend", "ksana")][1]
+    if builder is not None:
+        if not isinstance(prompt, str):
+            raise SystemExit("--synthetic token-id prompts need --backend ksana (other servers take text)")
+        return builder(args, prompt, max_new_tokens or args.max_new_tokens)
     sampling = {
         "temperature": args.temperature, "topk": args.topk, "topp": args.topp,
         "max_new_tokens": max_new_tokens or args.max_new_tokens, "repetition_penalty": args.repetition_penalty,
@@ -163,8 +168,129 @@ def build_payload(args, prompt, max_new_tokens: Optional[int] = None) -> dict:
     return body
 
 
-def _finish(rec: RequestRecord, body: Optional[dict]):
+# ---------------------------------------------------------------------------------------------------------------
+# Other servers behind the same load generator (the reference's --backend values, benchmarks/benchmark_throughput.py
+# :390-470 request bodies and :565-605 answers). An adapter names the URL path, builds the request body from the
+# common flags and reads prompt / output token counts and the text out of the last JSON object of the answer. Token
+# counts the server does not report are taken from --tokenizer_path when one is given, else they stay zero.
+def _body_vllm(args, prompt, n_new):
+    return {"prompt": prompt, "n": 1, "temperature": args.temperature, "max_tokens": n_new, "logprobs": args.logprobs or None,
+            "repetition_penalty": args.repetition_penalty, "stop_token_ids": args.stop_token_ids or [],
+            "ignore_eos": args.ignore_eos, "min_tokens": n_new if args.ignore_eos else 0, "skip_special_tokens": False,
+            "spaces_between_special_tokens": False, "top_p": args.topp, "top_k": args.topk, "stream": bool(args.stream)}
+
+
+def _body_trt(args, prompt, n_new):
+    return {"accumulate_tokens": True, "text_input": prompt, "max_tokens": n_new, "temperature": args.temperature,
+            "min_tokens": n_new if args.ignore_eos else 0, "bad_words": "", "stop_words": "", "top_p": args.topp,
+            "top_k": args.topk, "stream": bool(args.stream)}
+
+
+def _body_sglang(args, prompt, n_new):
+    return {"text": prompt, "stream": bool(args.stream),
+            "sampling_params": {"n": 1, "temperature": args.temperature, "max_new_tokens": n_new,
+                                "stop_token_ids": args.stop_token_ids or [], "ignore_eos": args.ignore_eos,
+                                "top_p": args.topp, "top_k": args.topk, "skip_special_tokens": False,
+                                "spaces_between_special_tokens": False, "repetition_penalty": args.repetition_penalty}}
+
+
+def _body_chat_server(args, prompt, n_new):
+    return {"model": "default_model", "prompt": prompt, "messages": [{"role": "user", "content": prompt}],
+            "top_p": args.topp, "temperature": args.temperature, "top_k": args.topk,
+            "repetition_penalty": args.repetition_penalty, "logprobs": args.logprobs, "n": 1, "task_id": time.time(),
+            "delete_prompt_from_output": 1, "stream": bool(args.stream), "stop_token_ids": args.stop_token_ids or [],
+            "max_new_tokens": n_new, "max_tokens": n_new, "ignore_eos": args.ignore_eos,
+            "structured_output_regex": args.structured_output_regex or None}
+
+
+def _count(tok, text):
+    return len(tok.encode(text)) if (tok is not None and text) else 0
+
+
+def _read_prompt_echo(body, prompt, tok, strip_prompt):
+    text = (body.get("text") or [""])
+    text = text[0] if isinstance(text, list) else text
+    if strip_prompt and isinstance(prompt, str) and text.startswith(prompt):
+        text = text[len(prompt):]
+    outs = body.get("output_token_ids")
+    n_out = len(outs[0]) if outs else _count(tok, text)
+    return _count(tok, prompt if isinstance(prompt, str) else ""), n_out, text.strip()
+
+
+def _read_trt(body, prompt, tok, _):
+    text = (body.get("text_output") or "").strip()
+    return _count(tok, prompt if isinstance(prompt, str) else ""), _count(tok, text), text
+
+
+def _read_sglang(body, prompt, tok, _):
+    meta = body.get("meta_info") or {}
+    return int(meta.get("prompt_tokens", 0)), int(meta.get("completion_tokens", 0)), (body.get("text") or "").strip()
+
+
+def _read_chat_server(body, prompt, tok, streamed_text):
+    usage = body.get("usage") or {}
+    choice = (body.get("choices") or [{}])[0]
+    text = streamed_text if streamed_text else ((choice.get("message") or choice.get("delta") or {}).get("content")
+                                                or choice.get("text") or "")
+    n_out = int(usage.get("completion_tokens", 0)) or _count(tok, text)
+    return int(usage.get("prompt_tokens", 0)), n_out, text
+
+
+BACKENDS = {
+    # name: (url path; "+_stream" marks a path that gets that suffix for streaming), body builder, answer reader,
+    #        strip the echoed prompt from the text
+    "ksana": ("/generate", None, None, False),
+    "vllm": ("/generate", _body_vllm, _read_prompt_echo, True),
+    "mindie-service": ("/generate", _body_vllm, _read_prompt_echo, True),
+    "evart": ("/generate", _body_vllm, _read_prompt_echo, False),
+    "trt-llm": ("/v2/models/ensemble/generate+_stream", _body_trt, _read_trt, False),
+    "sglang": ("/generate", _body_sglang, _read_sglang, False),
+    "ksana-server": ("/v1/chat", _body_chat_server, _read_chat_server, False),
+    "vllm-server": ("/v1/chat", _body_chat_server, _read_chat_server, False),
+}
+
+
+def backend_url(args) -> str:
+    path = BACKENDS[args.backend][0]
+    if path.endswith("+_stream"):
+        path = path[:-len("+_stream")] + ("_stream" if args.stream else "")
+    return f"http://{args.host}:{args.port}{path}"
+
+
+def iter_json_objects(buf: bytes):
+    """Splits what has arrived of a streamed answer into complete JSON objects and the unfinished rest. Servers frame
+    their objects with zero bytes (this engine), with "data: " lines (server-sent events) or with new lines."""
+    out = []
+    while True:
+        hits = [(i, len(sep)) for sep in (b"\0", b"\n\n", b"\n") for i in [buf.find(sep)] if i >= 0]
+        if not hits:
+            break
+        at, width = min(hits)
+        piece, rest = buf[:at].strip(), buf[at + width:]
+        if piece.startswith(b"data:"):
+            piece = piece[5:].strip()
+        if piece and piece != b"[DONE]":
+            try:
+                out.append(json.loads(piece))
+            except ValueError:
+                break                  # a separator inside an unfinished object: wait for more bytes
+        buf = rest
+    return out, buf
+
+
+def _finish(rec: RequestRecord, body: Optional[dict], args=None, prompt=None, tok=None, streamed_text=""):
     if body is None:
+        return
+    reader = BACKENDS[getattr(args, "backend", "ksana")][2] if args is not None else None
+    if reader is not None:
+        if "error" in body:
+            rec.ok, rec.error = False, str(body["error"])[:200]
+            return
+        extra = streamed_text if reader is _read_chat_server else BACKENDS[args.backend][3]
+        n_in, n_out, rec.text = reader(body, prompt, tok, extra)
+        rec.output_len = n_out
+        if rec.prompt_len == 0:
+            rec.prompt_len = n_in
         return
     outs = body.get("output_token_ids") or []
     rec.output_len = sum(len(o) for o in outs)
@@ -174,16 +300,41 @@ def _finish(rec: RequestRecord, body: Optional[dict]):
     rec.text = texts[0] if texts else ""
 
 
-async def send_async(session, url: str, payload: dict, rec: RequestRecord):
-    """One request; streaming responses are JSON objects separated by a zero byte (one per engine step)."""
+async def send_async(session, url: str, payload: dict, rec: RequestRecord, args=None, prompt=None, tok=None):
+    """One request. This engine streams JSON objects separated by a zero byte (one per engine step); the other
+    backends' framings are handled by ``iter_json_objects``."""
     rec.start = time.perf_counter()
+    foreign = args is not None and BACKENDS[args.backend][1] is not None
     try:
         async with session.post(url, json=payload) as resp:
             if resp.status != 200:
                 rec.ok, rec.error = False, f"HTTP {resp.status}: {(await resp.text())[:200]}"
                 rec.end = time.perf_counter()
                 return
-            if payload.get("stream"):
+            if payload.get("stream") and foreign:
+                buf, last, text = b"", None, ""
+                async for chunk in resp.content.iter_any():
+                    buf += chunk
+                    objs, buf = iter_json_objects(buf)
+                    now = time.perf_counter()
+                    for obj in objs:
+                        last = obj
+                        delta = ((obj.get("choices") or [{}])[0].get("delta") or {}).get("content") if "choices" in obj else None
+                        if delta:
+                            text += delta
+                        if rec.first_token is None:
+                            rec.first_token = now
+                        rec.chunk_times.append(now)
+                tail = buf.strip(b"\0 \n")
+                if tail.startswith(b"data:"):
+                    tail = tail[5:].strip()
+                if tail and tail != b"[DONE]":
+                    try:
+                        last = json.loads(tail)
+                    except ValueError:
+                        pass
+                _finish(rec, last, args, prompt, tok, text)
+            elif payload.get("stream"):
                 buf, last = b"", None
                 async for chunk in resp.content.iter_any():
                     buf += chunk
@@ -201,7 +352,7 @@ async def send_async(session, url: str, payload: dict, rec: RequestRecord):
                     last = json.loads(buf.strip(b"\0"))
                 _finish(rec, last)
             else:
-                _finish(rec, await resp.json(content_type=None))
+                _finish(rec, await resp.json(content_type=None), args, prompt, tok)
     except Exception as e:  # noqa: BLE001 - a failed request is a data point, not a crash
         rec.ok, rec.error = False, repr(e)
     rec.end = time.perf_counter()
@@ -214,13 +365,15 @@ async def run_async(args, url: str, work: list) -> List[RequestRecord]:
     rng = random.Random(args.seed)
     timeout = aiohttp.ClientTimeout(total=args.client_timeout)
     async with aiohttp.ClientSession(timeout=timeout) as session:
+        tok = _counting_tokenizer(args)
+
         async def one(i):
             payload = build_payload(args, work[i][0], work[i][1])
             if sem is None:
-                await send_async(session, url, payload, records[i])
+                await send_async(session, url, payload, records[i], args, work[i][0], tok)
             else:
                 async with sem:
-                    await send_async(session, url, payload, records[i])
+                    await send_async(session, url, payload, records[i], args, work[i][0], tok)
 
         tasks = []
         for i in range(len(work)):
@@ -232,10 +385,18 @@ async def run_async(args, url: str, work: list) -> List[RequestRecord]:
     return records
 
 
+def _counting_tokenizer(args):
+    """Tokenizer for the token counts of servers that do not report them (None without --tokenizer_path)."""
+    if BACKENDS[args.backend][1] is None or not getattr(args, "tokenizer_path", None):
+        return None
+    return load_tokenizer(args)
+
+
 def run_sync(args, url: str, work: list) -> List[RequestRecord]:
     import requests
     from concurrent.futures import ThreadPoolExecutor
     records = [RequestRecord(prompt_len=0 if isinstance(p, str) else len(p)) for p, _ in work]
+    tok = _counting_tokenizer(args)
 
     def one(i):
         rec = records[i]
@@ -247,7 +408,7 @@ def run_sync(args, url: str, work: list) -> List[RequestRecord]:
             if r.status_code != 200:
                 rec.ok, rec.error = False, f"HTTP {r.status_code}"
             else:
-                _finish(rec, r.json())
+                _finish(rec, r.json(), args, work[i][0], tok)
         except Exception as e:  # noqa: BLE001
             rec.ok, rec.error = False, repr(e)
         rec.end = time.perf_counter()
@@ -282,7 +443,9 @@ def args_config(argv=None):
     p.add_argument("--repeat_num_iters", type=int, default=1)
     p.add_argument("--mode", default="async", choices=["async", "sync"])
     p.add_argument("--stream", action="store_true")
-    p.add_argument("--backend", default="ksana", choices=["ksana"])
+    p.add_argument("--backend", default="ksana", choices=sorted(BACKENDS),
+                   help="server to load: this engine's /generate (default), or vllm / trt-llm / sglang / evart / "
+                        "mindie-service / ksana-server / vllm-server with their own request and answer formats")
     p.add_argument("--prompt_num", type=int, default=0)
     p.add_argument("--model_type", default="llama")
     p.add_argument("--synthetic", default=None, help="N:IN_LEN:OUT_LEN[:SIGMA] synthetic token-id prompts")
@@ -312,7 +475,7 @@ def args_config(argv=None):
 
 
 def run_benchmark(args) -> List[dict]:
-    url = f"http://{args.host}:{args.port}/generate"
+    url = backend_url(args)
     if args.structured_output_file:
         with open(args.structured_output_file, "r", encoding="utf-8") as f:
             args.structured_output_regex = f.read().strip()

@@ -178,3 +178,96 @@ def test_prompt_sets_and_prefix_cache_reader(tmp_path):
     assert len(qs) == 32 and all(q.startswith("Think about") for q in qs)
     ec = load_yaml_config(os.path.join(bench_dir, "prefix_cache_config.yaml"))
     assert ec.batch_scheduler.enable_auto_prefix_cache and ec.batch_scheduler.max_batch_size == 256
+
+
+@pytest.fixture(scope="module")
+def foreign_servers():
+    """Stand-ins for other serving stacks: each answers in that stack's own request / answer format."""
+    import json
+    import uvicorn
+    from fastapi import FastAPI, Request
+    from fastapi.responses import JSONResponse, StreamingResponse
+    app = FastAPI()
+    seen = {}
+
+    @app.post("/generate")
+    async def generate(req: Request):
+        body = await req.json()
+        if "sampling_params" in body:                       # sglang
+            seen["sglang"] = body
+            return JSONResponse({"text": " four words of text", "meta_info": {"prompt_tokens": 7, "completion_tokens": 4}})
+        seen["vllm"] = body                                  # vllm: the prompt is echoed, chunks end with a zero byte
+        words = [" one", " two", " three"]
+        if body.get("stream"):
+            async def chunks():
+                text = body["prompt"]
+                for w in words:
+                    text += w
+                    yield json.dumps({"text": [text]}).encode() + b"\0"
+            return StreamingResponse(chunks())
+        return JSONResponse({"text": [body["prompt"] + "".join(words)]})
+
+    @app.post("/v2/models/ensemble/generate_stream")
+    async def trt(req: Request):
+        seen["trt-llm"] = await req.json()
+
+        async def events():
+            for i in range(1, 4):
+                yield ("data: " + json.dumps({"text_output": "tok " * i}) + "\n\n").encode()
+        return StreamingResponse(events(), media_type="text/event-stream")
+
+    @app.post("/v1/chat")
+    async def chat(req: Request):
+        seen["chat"] = await req.json()
+
+        async def events():
+            for w in ("Hel", "lo ", "you"):
+                yield ("data: " + json.dumps({"choices": [{"delta": {"content": w}}]}) + "\n\n").encode()
+            yield ("data: " + json.dumps({"choices": [{"delta": {"content": ""}}],
+                                          "usage": {"prompt_tokens": 5, "completion_tokens": 3}}) + "\n\n").encode()
+            yield b"data: [DONE]\n\n"
+        return StreamingResponse(events(), media_type="text/event-stream")
+
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    srv = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="warning"))
+    th = threading.Thread(target=srv.run, daemon=True)
+    th.start()
+    for _ in range(200):
+        if srv.started:
+            break
+        time.sleep(0.05)
+    assert srv.started
+    yield port, seen
+    srv.should_exit = True
+    th.join(timeout=10)
+
+
+@pytest.mark.parametrize("backend,stream,n_in,n_out", [("vllm", True, 0, 0), ("vllm", False, 0, 0), ("sglang", False, 7, 4),
+                                                       ("trt-llm", True, 0, 0), ("vllm-server", True, 5, 3)])
+def test_client_speaks_other_backends(foreign_servers, tmp_path, backend, stream, n_in, n_out):
+    """--backend picks the URL, the request body and the answer format of another serving stack; latency statistics
+    come out the same way, token counts from the answer where the stack reports them."""
+    port, seen = foreign_servers
+    csv_path = tmp_path / "prompts.csv"
+    csv_path.write_text("question\nwhat is this\nand that\n", encoding="utf-8")
+    out_csv = tmp_path / "out.csv"
+    argv = ["--port", str(port), "--backend", backend, "--input_csv", str(csv_path), "--max_new_tokens", "9",
+            "--client_timeout", "30", "--output_csv", str(out_csv)] + (["--stream"] if stream else [])
+    res = bt.run_benchmark(bt.args_config(argv))
+    s = res[0]
+    assert s["finished"] == 2 and s["failed"] == 0
+    assert s["avg_input_tokens"] == n_in and s["avg_output_tokens"] == n_out
+    if stream:
+        assert s["avg_ttft_s"] > 0
+    text = out_csv.read_text()
+    if backend == "vllm":
+        assert seen["vllm"]["max_tokens"] == 9 and "one two three" in text and "what is this one" not in text
+    elif backend == "sglang":
+        assert seen["sglang"]["sampling_params"]["max_new_tokens"] == 9 and "four words of text" in text
+    elif backend == "trt-llm":
+        assert seen["trt-llm"]["text_input"] in ("what is this", "and that") and "tok tok tok" in text
+    else:
+        assert seen["chat"]["messages"][0]["role"] == "user" and "Hello you" in text
