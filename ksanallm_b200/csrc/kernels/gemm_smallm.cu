@@ -22,6 +22,7 @@
 // Same warp roles and bounded waits as gemm_tcgen05.cu. No cluster multicast.
 #include "sm100_ptx.cuh"
 #include "pdl.cuh"
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdio.h>
@@ -898,6 +899,67 @@ static int launch_smallm(const CUtensorMap& mw, const CUtensorMap& mx, const Sma
                  cudaSuccess ? 0 : -4;
 }
 
+// How many persistent CTAs share the n_tiles x num_kb (tile, K block) units. Measured on 64-row FP8 problems (graphs
+// of back-to-back launches): a launch costs about 9 us plus 0.5 us per unit of its longest CTA; when the even cut of
+// the units leaves pieces that straddle tile boundaries, every CTA completes two cut tiles instead of one and the
+// launch takes about 6.4 us longer; when no tile is cut at all, the partial-tile exchange disappears (about 3 us
+// less). So beside the even cut over all SMs the candidates are cuts whose pieces end on tile boundaries: s equal
+// pieces per tile (s divides num_kb, n_tiles * s CTAs) and j whole tiles per CTA (j divides n_tiles). Returns the CTA
+// count; est_us (optional) receives the modelled time.
+static long long smallm_pick_ctas(int n_tiles, int num_kb, int sms, int ctas_hint, double* est_us) {
+  const long long U = static_cast<long long>(n_tiles) * num_kb;
+  auto clamp_min_units = [&](long long P) {            // at least four K blocks per CTA
+    if (P > sms) P = sms;
+    if (P > U / 4) P = U / 4 > 0 ? U / 4 : 1;
+    return P;
+  };
+  auto cost = [&](long long P, bool aligned, bool whole_tiles) {
+    const double units = static_cast<double>((U + P - 1) / P);
+    return 9.0 + 0.5 * units + (aligned ? 0.0 : 6.4) - (whole_tiles ? 3.0 : 0.0);
+  };
+  auto classify = [&](long long P, bool& aligned, bool& whole) {
+    aligned = whole = false;
+    if (U % P) return;
+    const long long per = U / P;
+    whole = per % num_kb == 0;
+    aligned = whole || num_kb % per == 0;
+  };
+  if (ctas_hint > 0) {
+    const long long P = clamp_min_units(ctas_hint);
+    bool a, w;
+    classify(P, a, w);
+    if (est_us) *est_us = cost(P, a, w);
+    return P;
+  }
+  long long best_p = clamp_min_units(sms);
+  bool a, w;
+  classify(best_p, a, w);
+  double best = cost(best_p, a, w);
+  // The tile-aligned cuts below win when launches of one GEMM are timed back to back (64 x 1280 x 8192: 13.4 against
+  // 18.6 us, 64 x 8192 x 8192: 25.9 against 29.1 us), but whole decode steps did not get faster with them (one GPU,
+  // 80 layers: 29.20 against 29.03 ms per step; two GPUs: 2240 against 2229 us for 8 layers), so the even cut over all
+  // SMs stays the default and KSANA_SMALLM_ALIGNED_CUT=1 selects by the model.
+  const char* al = std::getenv("KSANA_SMALLM_ALIGNED_CUT");
+  if (!(al && al[0] == '1')) {
+    if (est_us) *est_us = best;
+    return best_p;
+  }
+  for (int sp = 1; sp <= num_kb && static_cast<long long>(n_tiles) * sp <= sms; ++sp) {
+    if (num_kb % sp || (sp > 1 && num_kb / sp < 4)) continue;
+    const long long P = static_cast<long long>(n_tiles) * sp;
+    const double c = cost(P, true, sp == 1);
+    if (c < best) { best = c; best_p = P; }
+  }
+  for (int j = 2; j <= 32; ++j) {
+    if (n_tiles % j || n_tiles / j > sms) continue;
+    const long long P = n_tiles / j;
+    const double c = cost(P, true, true);
+    if (c < best) { best = c; best_p = P; }
+  }
+  if (est_us) *est_us = best;
+  return best_p;
+}
+
 static long long* g_smallm_prof = nullptr;
 
 struct PushSignal {            // filled by ksana_gemm_smallm_push_signal for the launch it makes
@@ -948,9 +1010,7 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const long long U = static_cast<long long>(n_tiles) * num_kb;
-  long long P = ctas_hint > 0 ? ctas_hint : sms;
-  if (P > sms) P = sms;
-  if (P > U / 4) P = U / 4 > 0 ? U / 4 : 1;      // at least four k-blocks per CTA
+  long long P = smallm_pick_ctas(n_tiles, num_kb, sms, ctas_hint, nullptr);
   // a tile may be cut only if scratch and counters can hold the pieces
   auto seg_cap_for = [&](long long ctas) {
     const long long per = U / ctas;               // smallest piece
@@ -1013,6 +1073,23 @@ static int smallm_impl(int kind, const void* X, int ldx, const float* a_scale, i
   }
 #undef KSANA_SM_DISPATCH
   return -21;
+}
+
+// Modelled time of one launch in nanoseconds (see smallm_pick_ctas) and, through ctas_out, the CTA count it would
+// use: what the dispatcher compares with the tiled kernel's model for 33..128 rows. No GPU work.
+extern "C" int ksana_smallm_estimate(int kind, int M, int N, int K, int* ctas_out) {
+  if (M <= 0 || N <= 0 || K <= 0 || M > 128) return -1;
+  const int esz = (kind == 0 || kind == 3) ? 2 : 1;
+  const int kelems = esz == 2 ? 64 : 128;
+  const int n_tiles = (N + 127) / 128, num_kb = (K + kelems - 1) / kelems;
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  double us = 0.0;
+  const long long P = smallm_pick_ctas(n_tiles, num_kb, sms, 0, &us);
+  if (M > 64) us += 0.28 * static_cast<double>((static_cast<long long>(n_tiles) * num_kb + P - 1) / P);   // 128-row activation tiles
+  if (ctas_out) *ctas_out = static_cast<int>(P);
+  return static_cast<int>(us * 1000.0);
 }
 
 extern "C" int ksana_gemm_smallm(int kind, const void* X, int ldx, const float* a_scale, int a_scale_ld, const void* W,

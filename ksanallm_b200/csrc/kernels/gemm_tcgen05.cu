@@ -56,6 +56,11 @@ struct GemmParams {
   __nv_bfloat16* push[8];
   int push_n;
   int push_rows;
+  // batched mode (bf16 only, batch > 0): `batch` independent products D_b = A_b W_b^T; the tensor maps are three-dimensional
+  // (K, rows, batch), so a tile never reads another batch entry's rows, and D_b starts d_batch_stride elements
+  // after D_{b-1} (any layout in which a row of D_b is contiguous: e.g. head-interleaved [rows, batch, N])
+  int batch;
+  long long d_batch_stride;
 };
 
 template <int BN, int KIND>
@@ -109,7 +114,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int lane = threadIdx.x & 31;
   const int m_tiles = (p.M + kBM - 1) / kBM;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
+  const int tiles_per_batch = m_tiles * n_tiles;
+  const int num_tiles = tiles_per_batch * ((KIND == kBf16 && p.batch > 0) ? p.batch : 1);
   const int num_kb = (p.K + Cfg::kElemsPerRow - 1) / Cfg::kElemsPerRow;
 
   if (threadIdx.x == 0) {
@@ -136,7 +142,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
+        const int b = (KIND == kBf16) ? tile / tiles_per_batch : 0;
+        tile_coords(tile - b * tiles_per_batch, m_tiles, n_tiles, m_blk, n_blk);
         const int m0 = m_blk * kBM;
         const int n0 = n_blk * BN;
         int w_row0 = n0;
@@ -150,8 +157,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          tma_load_2d(sa, &tma_a, &full_bar[stage], kb * Cfg::kElemsPerRow, m0);
-          tma_load_2d(sb, &tma_b, &full_bar[stage], kb * Cfg::kElemsPerRow, w_row0);
+          if (KIND == kBf16 && p.batch > 0) {
+            tma_load_3d(sa, &tma_a, &full_bar[stage], kb * Cfg::kElemsPerRow, m0, b);
+            tma_load_3d(sb, &tma_b, &full_bar[stage], kb * Cfg::kElemsPerRow, n0, b);
+          } else {
+            tma_load_2d(sa, &tma_a, &full_bar[stage], kb * Cfg::kElemsPerRow, m0);
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * Cfg::kElemsPerRow, w_row0);
+          }
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -215,7 +227,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
+      const int b = (KIND == kBf16) ? tile / tiles_per_batch : 0;
+      tile_coords(tile - b * tiles_per_batch, m_tiles, n_tiles, m_blk, n_blk);
       const int m0 = m_blk * kBM;
       const int n0 = n_blk * BN + col_off;
       int expert = 0;
@@ -261,7 +274,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
               const int owner = min(row / p.push_rows, p.push_n - 1);
               *reinterpret_cast<uint4*>(p.push[owner] + static_cast<size_t>(row - owner * p.push_rows) * p.ldd + col) = ov;
             } else {
-              *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(row) * p.ldd + col) = ov;
+              *reinterpret_cast<uint4*>(p.D + static_cast<size_t>(b) * p.d_batch_stride + static_cast<size_t>(row) * p.ldd + col) = ov;
             }
           }
         }
@@ -389,7 +402,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     if (e != cudaSuccess) return -3;
     attr_set = true;
   }
-  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * (p.batch > 0 ? p.batch : 1);
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   gemm_tcgen05_kernel<BN, KIND><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(ma, mb, p);
@@ -449,6 +462,53 @@ extern "C" int ksana_gemm_bf16(const void* A, int lda, const void* W, int ldw, v
                                int max_ctas, int* err_flag, cudaStream_t stream) {
   return gemm_bf16_impl(A, lda, W, ldw, D, out_f32, ldd, bias, residual, ldr, M, N, K, bn_hint, max_ctas, err_flag,
                         stream, nullptr, 0, 0);
+}
+
+// Batched bf16 product: D_b[M, N] = A_b[M, K] W_b[N, K]^T for b < batch. Operand b starts a_batch / w_batch elements
+// after operand b - 1 and its rows are lda / ldw elements apart (so A may be a head-interleaved [M, batch, K] tensor);
+// D likewise with d_batch and ldd. All strides in elements, multiples of 8; K a multiple of 8. One launch, tiles of all
+// batch entries in one persistent grid.
+static int make_batched_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, long long batch_stride,
+                            int batch, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kRowBytes / 2), static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+extern "C" int ksana_gemm_bf16_batched(const void* A, long long lda, long long a_batch, const void* W, long long ldw,
+                                       long long w_batch, void* D, long long ldd, long long d_batch, int batch, int M,
+                                       int N, int K, int* err_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if ((N % 8) || (K % 8) || (lda % 8) || (ldw % 8) || (ldd % 8) || (a_batch % 8) || (w_batch % 8) || (d_batch % 8) ||
+      ldd > 0x7fffffffLL) return -10;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(D)) & 15) return -11;
+  const int m_tiles = (M + kBM - 1) / kBM;
+  int bn = 32;
+  for (int c : {256, 128, 64, 32}) {
+    if (c <= N || c == 32) { bn = c; if (batch * m_tiles * ((N + c - 1) / c) >= num_sms() / 2 || c == 32) break; }
+  }
+  CUtensorMap ma, mb;
+  if (make_batched_map(&ma, A, M, K, lda, a_batch, batch, kBM)) return -12;
+  if (make_batched_map(&mb, W, N, K, ldw, w_batch, batch, bn)) return -13;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.D = static_cast<__nv_bfloat16*>(D); p.ldd = static_cast<int>(ldd);
+  p.err = err_flag;
+  p.batch = batch;
+  p.d_batch_stride = d_batch;
+  switch (bn) {
+    case 256: return launch_gemm<256, kBf16>(ma, mb, p, 0, stream);
+    case 128: return launch_gemm<128, kBf16>(ma, mb, p, 0, stream);
+    case 64: return launch_gemm<64, kBf16>(ma, mb, p, 0, stream);
+    default: return launch_gemm<32, kBf16>(ma, mb, p, 0, stream);
+  }
 }
 
 // Push mode: partial rows go to the peers' receive slots (push_ptrs[r] = slot of this rank inside rank r's

@@ -39,6 +39,7 @@ class MLAWeights:
     kv_a_norm: torch.Tensor
     w_uk: torch.Tensor                   # [Hq, nope, kv_lora_rank]
     w_uv: torch.Tensor                   # [Hq, v_dim, kv_lora_rank]
+    w_uk_t: Optional[torch.Tensor] = None    # [Hq, kv_lora_rank, nope]: W_uk as the K-major operand of the batched GEMM (built on first use)
 
 
 def yarn_mscale(scale: float, mscale: float) -> float:
@@ -127,16 +128,21 @@ class DeepseekModel(CommonModel):
         qfull = torch.empty(T, Hq, self.lora + self.rope, dtype=q.dtype, device=q.device)
         native.mla_rope_append(q, self.nope, kv, mw.kv_a_norm, self.cfg.rms_norm_eps, step.positions, step.slots,
                                self.cos_sin, qfull, cache, cache.stride(0), self.block_tokens, Hq)
+        # absorbed query: per head q_nope W_uk straight into the packed query rows (one batched tcgen05 GEMM whose
+        # operand and result views are head-interleaved: no transposes, no copy)
         q_nope = q.view(T, Hq, self.nope + self.rope)[..., : self.nope].transpose(0, 1)          # [Hq, T, nope]
-        qfull[..., : self.lora].copy_(torch.bmm(q_nope, mw.w_uk).transpose(0, 1))
+        if mw.w_uk_t is None:
+            mw.w_uk_t = mw.w_uk.transpose(1, 2).contiguous()                                      # [Hq, lora, nope]
+        native.gemm_bf16_batched(q_nope, mw.w_uk_t, qfull[..., : self.lora].transpose(0, 1))
         o_lat = torch.empty(T, Hq, self.lora, dtype=q.dtype, device=q.device)
         B = step.num_multi + step.num_single
         nsplit = native.mla_splits(B, step.max_q_len, step.max_kv_len) if step.num_multi == 0 else 1
         if not native.mla_attention(qfull, o_lat, cache, cache.stride(0), self.block_tokens, step.block_table, step.cu_q,
                                     step.kv_lens, B, max(step.max_q_len, 1), Hq, self.scale, nsplit):
             raise RuntimeError("latent-attention kernel rejected a configuration that _mla_native_ok accepted")
-        o = torch.bmm(o_lat.transpose(0, 1), mw.w_uv.transpose(1, 2))                            # [Hq, T, v]
-        return o.transpose(0, 1).reshape(T, Hq * self.vdim)
+        o = torch.empty(T, Hq, self.vdim, dtype=q.dtype, device=q.device)
+        native.gemm_bf16_batched(o_lat.transpose(0, 1), mw.w_uv, o.transpose(0, 1))              # per head o_lat W_uv^T
+        return o.view(T, Hq * self.vdim)
 
 
 def build_deepseek(cfg: ModelConfig, source, tp_rank, tp_size, comm, device, dtype, quant, layer_range, max_positions):

@@ -22,6 +22,7 @@ _SIGS = {
     "ksana_gemm_bf16": [vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_pair": [i32, vp, i32, vp, i32, vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, i32, vp, vp],
     "ksana_gemm_nvfp4": [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+    "ksana_gemm_bf16_batched": [vp, i64, i64, vp, i64, i64, vp, i64, i64, i32, i32, i32, i32, vp, vp],
     "ksana_gemm_grouped_nvfp4": [vp, i32, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp, vp],
     "ksana_quant_nvfp4": [vp, i32, vp, i32, vp, i32, vp, i32, i32, vp],
     "ksana_gemm_mxfp8": [vp, i32, vp, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, i32, i32, vp,
@@ -61,6 +62,7 @@ _SIGS = {
     "ksana_swap_blocks": [vp, vp, vp, i32, i64, i32, i32, i32, vp, vp],
     "ksana_add": [vp, vp, vp, vp, i64, i32, vp],
     "ksana_patch_ids": [vp, vp, vp, vp, i32, i32, i32, vp, vp],
+    "ksana_smallm_estimate": [i32, i32, i32, i32, vp],
     "ksana_rerotate_blocks": [vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_cast_f32": [vp, vp, i64, vp],
     "ksana_paged_prefill_tc": [vp, i64, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i64,
@@ -450,6 +452,20 @@ def gemm_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, out=None, bias=None, residual=Non
                                 M, N, K, bn, max_ctas, _p(err_flag(aq.device)), _st())
     _check(rc, "ksana_gemm_nvfp4")
     return dst
+
+
+def gemm_bf16_batched(a, w, out):
+    """out[b] = a[b] @ w[b]^T for every b: a [B, M, K], w [B, N, K], out [B, M, N], bf16 views with unit stride in the
+    last dimension and any (16-byte aligned) strides in the others, e.g. head-interleaved activations
+    ``x.view(T, H, D).transpose(0, 1)``. One launch of the tcgen05 GEMM over all batch entries' tiles."""
+    B, M, K = a.shape
+    N = w.shape[1]
+    assert w.shape[0] == B and w.shape[2] == K and tuple(out.shape) == (B, M, N)
+    assert a.stride(2) == 1 and w.stride(2) == 1 and out.stride(2) == 1
+    rc = lib().ksana_gemm_bf16_batched(_p(a), a.stride(1), a.stride(0), _p(w), w.stride(1), w.stride(0), _p(out),
+                                       out.stride(1), out.stride(0), B, M, N, K, _p(err_flag(a.device)), _st())
+    _check(rc, "ksana_gemm_bf16_batched")
+    return out
 
 
 def gemm_grouped_nvfp4(aq, a_bs, a_ts, wq, w_bs, w_ts, tile_expert, E, N, out=None, bn=0):

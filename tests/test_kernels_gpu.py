@@ -30,6 +30,25 @@ def test_gemm_bf16(M, N, K, bn):
     assert rel_err(y, want) < 1e-2, (M, N, K, bn, rel_err(y, want))
 
 
+@pytest.mark.parametrize("B,M,N,K", [(16, 64, 512, 128), (128, 300, 128, 512), (3, 1000, 264, 72), (1, 130, 512, 128)])
+def test_gemm_bf16_batched_head_interleaved(B, M, N, K):
+    """Batched tcgen05 GEMM on head-interleaved views (the absorbed-query and value projections of latent attention):
+    operand [M, B, Kpad] read per head through a three-dimensional tensor map, result written into a slice of a
+    wider [M, B, Npad] tensor; against the fp32 batched product. Columns outside the slice stay untouched."""
+    torch.manual_seed(B + M)
+    kpad, npad = K + 64, N + 64
+    x = torch.randn(M, B, kpad, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(B, N, K, device=DEV, dtype=torch.bfloat16) * 0.1
+    out = torch.full((M, B, npad), 3.0, device=DEV, dtype=torch.bfloat16)
+    a = x[..., :K].transpose(0, 1)
+    native.gemm_bf16_batched(a, w, out[..., :N].transpose(0, 1))
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    want = torch.bmm(a.float(), w.float().transpose(1, 2)).transpose(0, 1)
+    assert rel_err(out[..., :N], want) < 1e-2
+    assert bool((out[..., N:] == 3.0).all())
+
+
 def test_gemm_bf16_epilogue():
     torch.manual_seed(1)
     M, N, K = 300, 1024, 768
