@@ -12,6 +12,7 @@
 //
 // Row `grow` of the result belongs to rank `min(grow / push_rows, push_n - 1)` and lands at row
 // `grow - owner * push_rows` of that rank's receive slot (`push[owner]`, leading dimension ldd, bf16).
+// push_rows <= 0: broadcast - every rank receives every row (at row `grow` of `push[q]` for all q).
 #pragma once
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -62,8 +63,14 @@ __device__ __forceinline__ void push_rows_staged(uint8_t* stg, const uint32_t* r
       const int gcol = col + 8 * jc;
       if (jc < C && grow < M && gcol < N) {
         const uint4 ov = *reinterpret_cast<const uint4*>(stg + rr * (CP * 16) + ((jc ^ (rr & 7)) << 4));
-        const int owner = min(grow / push_rows, push_n - 1);
-        *reinterpret_cast<uint4*>(push[owner] + static_cast<size_t>(grow - owner * push_rows) * ldd + gcol) = ov;
+        if (push_rows > 0) {
+          const int owner = min(grow / push_rows, push_n - 1);
+          *reinterpret_cast<uint4*>(push[owner] + static_cast<size_t>(grow - owner * push_rows) * ldd + gcol) = ov;
+        } else {
+          // every rank reduces all rows itself (decode-sized batches): the row goes to this rank's slot in all of them
+          for (int q = 0; q < push_n; ++q)
+            *reinterpret_cast<uint4*>(push[q] + static_cast<size_t>(grow) * ldd + gcol) = ov;
+        }
       }
     }
     __syncwarp();

@@ -280,6 +280,7 @@ class SymmetricComm:
         if writer is None and W.fp8 and not isinstance(x, QTensor):
             x = quantize(x)
         one_shot = self.one_shot(M)
+        gemm_signals = False
         want_push = os.environ.get("KSANA_PUSH")
         plain_w = writer is None and not W.nvfp4 and not W.w4a16
         if one_shot:
@@ -296,6 +297,11 @@ class SymmetricComm:
             # reduce kernel of every row owner (one-shot: of every rank) pulls it from there
             part = self.buf[self.slots_off[parity]: self.slots_off[parity] + M * H * 2].view(torch.bfloat16).view(M, H)
             linear(x, W if self.rank == 0 else W.without_bias(), out=part)
+        elif one_shot and W.fp8 and W.ue8m0 and M >= native.MX_MIN_M and not native._skinny_wins_mx(M, H, W.in_features):
+            # the tiled kernel is the faster GEMM for this shape: its epilogue broadcasts the rows (push_rows = 0)
+            native.gemm_mxfp8(x.q, x.s, W.wq, W.ws, bias=W.bias if self.rank == 0 else None, push=push,
+                              push_n=self.size, push_rows=0, ldd=H)
+            rc = 0
         elif one_shot:
             scratch, counters = native.gemm_workspace(self.device)
             gemm_signals = self.push_signal
@@ -333,7 +339,7 @@ class SymmetricComm:
         want_q = quant_for is not None and quant_for.fp8 and H % 128 == 0 and norm_w is not None
         if one_shot:
             row_begin, row_count, gather = 0, M, (4 if (writer is not None or not push_mode) else 0)
-            if push_mode and writer is None and self.push_signal:
+            if push_mode and writer is None and self.push_signal and gemm_signals:
                 gather |= 16
             y = torch.empty(M, H, dtype=torch.bfloat16, device=self.device) if (norm_w is not None and not want_q) else None
             yq = torch.empty(M, H, dtype=torch.float8_e4m3fn, device=self.device) if want_q else None

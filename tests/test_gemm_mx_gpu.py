@@ -76,6 +76,15 @@ def test_gemm_mxfp8_push_epilogue(M, N, K, bn, ranks):
     got = slots.reshape(ranks * rows_per, N)[:M]
     assert torch.equal(got, plain)
     assert torch.isnan(slots.reshape(ranks * rows_per, N)[M:].float()).all()      # nothing written past the last row
+    if bn != "tall" and M <= 1024:
+        # broadcast form (push_rows = 0): every rank's slot receives every row
+        every = torch.full((ranks, M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ptrs = (C.c_ulonglong * 8)(*([every[r].data_ptr() for r in range(ranks)] + [0] * (8 - ranks)))
+        gemm(xq, xs, wq, ws, bias=bias, bn=bn, push=ptrs, push_n=ranks, push_rows=0, ldd=N)
+        torch.cuda.synchronize()
+        native.check_err_flag(DEV)
+        for r in range(ranks):
+            assert torch.equal(every[r], plain)
 
 
 def test_gemm_fp8_exact_scales_still_served():
