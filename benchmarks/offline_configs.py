@@ -181,7 +181,7 @@ def main():
                getattr(llm.engine.runner, "graph_replays", 0)}
         print(json.dumps(res))
     sys.stdout.flush()
-    llm.shutdown(stop_followers=True)
+    llm.shutdown()             # the worker ranks have left ``follow`` with the end-of-batch signal: nobody to release
     if world > 1:
         import torch.distributed as dist
         dist.barrier()

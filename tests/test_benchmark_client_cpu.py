@@ -180,6 +180,23 @@ def test_prompt_sets_and_prefix_cache_reader(tmp_path):
     assert ec.batch_scheduler.enable_auto_prefix_cache and ec.batch_scheduler.max_batch_size == 256
 
 
+@pytest.mark.parametrize("config,extra", [("b", ["--requests", "6", "--input-len", "20", "--output-len", "5"]),
+                                          ("e", ["--requests", "4", "--input-len", "24", "--output-len", "4"])])
+def test_offline_configurations_two_ranks_exit(config, extra):
+    """Two tensor-parallel ranks of the offline configuration script (CPU, gloo): the result line is printed and both
+    processes leave on their own (the worker rank is released by the end-of-batch signal, not by a stop signal)."""
+    import json
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    port = 29750 + (0 if config == "b" else 1)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(root, "benchmarks", "offline_configs.py"), "--config", config] + extra
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    res = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+    assert res["n_gpus"] == 2 and res["finished_ok"] == res["requests"]
+
+
 @pytest.fixture(scope="module")
 def foreign_servers():
     """Stand-ins for other serving stacks: each answers in that stack's own request / answer format."""
