@@ -1,4 +1,5 @@
 #include "profiler.h"
+#include "otlp_export.h"
 
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
@@ -36,13 +37,21 @@ std::string JsonEscape(const std::string& in) {
   }
   return o;
 }
+bool IsHttp(const std::string& target) { return target.compare(0, 7, "http://") == 0; }
 void EmitLine(const std::string& target, const std::string& line) {
-  if (target.empty()) return;
+  if (target.empty() || IsHttp(target)) return;
   if (target == "debug") { std::cout << line << std::endl; return; }
   std::ofstream f(target, std::ios::app);
   f << line << "\n";
 }
 }  // namespace
+
+Profiler::Profiler() {
+  const int64_t wall_us = std::chrono::duration_cast<std::chrono::microseconds>(
+      std::chrono::system_clock::now().time_since_epoch()).count();
+  epoch_offset_us_ = wall_us - NowUs();
+  start_unix_nano_ = wall_us * 1000;
+}
 
 Profiler& Profiler::Instance() {
   static Profiler p;
@@ -62,8 +71,11 @@ const std::vector<std::string>& Profiler::MetricNames() {
 }
 
 void Profiler::SetAttributes(const std::map<std::string, std::string>& attrs) {
-  std::lock_guard<std::mutex> g(mu_);
-  attrs_ = attrs;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    attrs_ = attrs;
+  }
+  OtlpExporter::Instance().Configure(attrs, 0);
 }
 
 void Profiler::ReportMetric(const std::string& name, double value) {
@@ -83,6 +95,7 @@ void Profiler::ReportCounter(const std::string& name, int64_t delta) {
   m.sum += static_cast<double>(delta);
   m.last = m.sum;
   m.max = m.sum;
+  m.counter = true;
   ++m.count;
 }
 
@@ -145,7 +158,19 @@ void Profiler::StartExport(const std::string& target, int interval_ms) {
     while (!export_stop_) {
       export_cv_.wait_for(lk, std::chrono::milliseconds(interval_ms));
       if (export_stop_) break;
-      EmitLine(target, JsonLine());
+      if (IsHttp(target)) {
+        std::vector<OtlpMetricPoint> points;
+        for (const auto& kv : Snapshot()) {
+          OtlpMetricPoint p;
+          p.name = "ksana_" + kv.first;
+          p.counter = kv.second.counter;
+          p.count = kv.second.count; p.sum = kv.second.sum; p.min = kv.second.min; p.max = kv.second.max;
+          points.push_back(std::move(p));
+        }
+        OtlpExporter::Instance().EnqueueMetrics(target, std::move(points), start_unix_nano_);
+      } else {
+        EmitLine(target, JsonLine());
+      }
     }
   });
 }
@@ -195,8 +220,18 @@ void Profiler::EndSpan(const std::string& span_id, const std::map<std::string, s
     line = o.str();
     finished_spans_.push_back(line);
     while (finished_spans_.size() > 4096) finished_spans_.pop_front();
-    open_spans_.erase(it);
     sink = span_sink_;
+    if (IsHttp(sink)) {
+      OtlpSpan os;
+      os.name = s.name; os.trace_id = s.trace_id; os.span_id = s.span_id; os.parent_id = s.parent_id;
+      os.start_us = s.start_us + epoch_offset_us_;
+      os.end_us = NowUs() + epoch_offset_us_;
+      os.attrs = attrs;
+      open_spans_.erase(it);
+      OtlpExporter::Instance().EnqueueSpan(sink, std::move(os));
+      return;
+    }
+    open_spans_.erase(it);
   }
   EmitLine(sink, line);
 }
@@ -320,6 +355,21 @@ void BindProfiler(pybind11::module_& m) {
   m.def("span_end", [](const std::string& id, const std::map<std::string, std::string>& a) { Profiler::Instance().EndSpan(id, a); },
         py::arg("span_id"), py::arg("attributes") = std::map<std::string, std::string>());
   m.def("span_set_sink", [](const std::string& t) { Profiler::Instance().SetSpanSink(t); });
+  m.def("otlp_configure", [](const std::map<std::string, std::string>& resource, int timeout_ms) {
+    OtlpExporter::Instance().Configure(resource, timeout_ms);
+  }, py::arg("resource"), py::arg("timeout_ms") = 1000);
+  m.def("otlp_flush", [](int wait_ms) { py::gil_scoped_release r; OtlpExporter::Instance().Flush(wait_ms); },
+        py::arg("wait_ms") = 2000);
+  m.def("otlp_stats", []() { return std::make_pair(OtlpExporter::Instance().sent(), OtlpExporter::Instance().dropped()); });
+  m.def("otlp_trace_request_json", [](const std::string& name, const std::string& trace_id, const std::string& span_id,
+                                      const std::string& parent_id, int64_t start_us, int64_t end_us,
+                                      const std::map<std::string, std::string>& attrs,
+                                      const std::map<std::string, std::string>& resource) {
+    OtlpSpan s;
+    s.name = name; s.trace_id = trace_id; s.span_id = span_id; s.parent_id = parent_id;
+    s.start_us = start_us; s.end_us = end_us; s.attrs = attrs;
+    return OtlpTraceRequestJson({s}, resource);
+  });
   m.def("spans_finished", []() { return Profiler::Instance().FinishedSpans(); });
   m.def("trace_enable", [](const std::string& p) { TraceEventRecorder::Instance().Enable(p); }, py::arg("path") = "");
   m.def("trace_disable", []() { py::gil_scoped_release r; TraceEventRecorder::Instance().Disable(); });

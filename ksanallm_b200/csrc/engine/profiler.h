@@ -24,6 +24,7 @@ namespace ksana {
 struct MetricValue {
   int64_t count = 0;
   double sum = 0, min = 0, max = 0, last = 0;
+  bool counter = false;      // reported through ReportCounter (a monotonic sum)
 };
 
 class Profiler {
@@ -39,20 +40,23 @@ class Profiler {
   std::string JsonLine();
   void Reset();
 
-  // Periodic export of JsonLine() to a file ("debug" = stdout); stops with StopExport / destruction.
+  // Periodic export: JsonLine() to a file ("debug" = stdout), or an OTLP/HTTP metrics request when the target is an
+  // http:// URL (see otlp_export.h); stops with StopExport / destruction.
   void StartExport(const std::string& target, int interval_ms);
   void StopExport();
 
   // Spans. `traceparent` (may be empty) continues a caller's trace; returns the span id.
   std::string StartSpan(const std::string& name, const std::string& traceparent);
   void EndSpan(const std::string& span_id, const std::map<std::string, std::string>& attrs);
-  void SetSpanSink(const std::string& target);   // file path, "debug" (stdout) or "" (off)
+  void SetSpanSink(const std::string& target);   // file path, "debug" (stdout), an http:// URL (OTLP/HTTP) or "" (off)
   std::vector<std::string> FinishedSpans();      // JSON objects of spans ended so far (kept in memory, bounded)
 
   ~Profiler();
 
  private:
-  Profiler() = default;
+  Profiler();
+  int64_t epoch_offset_us_ = 0;      // wall clock minus the monotonic clock spans are timed with
+  int64_t start_unix_nano_ = 0;
   struct Span { std::string name, trace_id, span_id, parent_id; int64_t start_us; };
   std::mutex mu_;
   std::map<std::string, MetricValue> metrics_;

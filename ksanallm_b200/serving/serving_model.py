@@ -162,6 +162,8 @@ class ServingModel:
         prof = self.llm.engine_cfg.profiler
         if prof.attributes:
             ne.metrics_set_attributes(dict(prof.attributes))
+        # http:// export targets speak OTLP/HTTP with JSON bodies to a collector (/v1/traces, /v1/metrics)
+        ne.otlp_configure({str(k): str(v) for k, v in (prof.attributes or {}).items()}, int(prof.export_timeout_millis))
         if prof.metrics_export_url:
             ne.metrics_start_export(prof.metrics_export_url, prof.export_interval_millis)
         if prof.trace_export_url:

@@ -445,3 +445,92 @@ def test_weight_maps_accept_dollar_groups(tmp_path):
     for name in ("transformer.h.12.ln_2.weight", "transformer.wte.weight", "lm_head.weight"):
         assert apply_weight_map(name, ra) == apply_weight_map(name, rb)
     assert apply_weight_map("transformer.h.12.ln_2.weight", ra) == "model.layers.12.norm2.weight"
+
+
+def test_otlp_http_export_of_spans_and_metrics():
+    """Export targets that are http:// URLs speak OTLP/HTTP with JSON bodies: finished spans arrive at /v1/traces as
+    one ExportTraceServiceRequest (resource attributes, ids, parent from the traceparent header, unix-nanosecond times,
+    span attributes) and the periodic metrics export at /v1/metrics (counters as cumulative monotonic sums,
+    distributions as histograms with count / sum / min / max). A collector that is away costs dropped requests,
+    never a blocked caller."""
+    import json
+    import socket
+    import threading
+    import time
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+
+    got = {"/v1/traces": [], "/v1/metrics": []}
+
+    class Collector(BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = self.rfile.read(int(self.headers["Content-Length"]))
+            assert self.headers["Content-Type"] == "application/json"
+            got[self.path].append(json.loads(body))
+            self.send_response(200)
+            self.send_header("Content-Length", "2")
+            self.end_headers()
+            self.wfile.write(b"{}")
+
+        def log_message(self, *a):
+            pass
+
+    srv = HTTPServer(("127.0.0.1", 0), Collector)
+    port = srv.server_address[1]
+    th = threading.Thread(target=srv.serve_forever, daemon=True)
+    th.start()
+    try:
+        ne.metrics_reset()
+        ne.metrics_set_attributes({"instance": "node-7"})
+        ne.otlp_configure({"instance": "node-7"}, 500)
+        ne.span_set_sink(f"http://127.0.0.1:{port}/v1/traces")
+        parent = "00-0af7651916cd43dd8448eb211c80319c-b7ad6b7169203331-01"
+        t_before = time.time_ns()
+        sid = ne.span_start("generate", parent)
+        time.sleep(0.01)
+        ne.span_end(sid, {"output_tokens": "5"})
+        sid2 = ne.span_start("forward", "")
+        ne.span_end(sid2)
+        ne.report_counter("forward_req_total_num", 3)
+        ne.report_metric("time_to_first_token_ms", 12.5)
+        ne.report_metric("time_to_first_token_ms", 7.5)
+        ne.metrics_start_export(f"http://127.0.0.1:{port}/v1/metrics", 50)
+        deadline = time.time() + 10
+        while time.time() < deadline and not (got["/v1/traces"] and got["/v1/metrics"]):
+            ne.otlp_flush(200)
+            time.sleep(0.05)
+        ne.metrics_stop_export()
+        ne.otlp_flush(2000)
+    finally:
+        ne.span_set_sink("")
+        srv.shutdown()
+    spans = [s for req in got["/v1/traces"] for rs in req["resourceSpans"] for ss in rs["scopeSpans"] for s in ss["spans"]]
+    res_attrs = {a["key"]: a["value"]["stringValue"] for a in got["/v1/traces"][0]["resourceSpans"][0]["resource"]["attributes"]}
+    assert res_attrs["instance"] == "node-7" and res_attrs["service.name"] == "ksana_llm"
+    gen = next(s for s in spans if s["name"] == "generate")
+    assert gen["traceId"] == "0af7651916cd43dd8448eb211c80319c" and gen["parentSpanId"] == "b7ad6b7169203331"
+    assert gen["spanId"] == sid and len(gen["spanId"]) == 16
+    assert int(gen["endTimeUnixNano"]) - int(gen["startTimeUnixNano"]) >= 9_000_000
+    assert abs(int(gen["startTimeUnixNano"]) - t_before) < 5_000_000_000          # wall-clock time, not a monotonic one
+    assert {a["key"]: a["value"]["stringValue"] for a in gen["attributes"]} == {"output_tokens": "5"}
+    fwd = next(s for s in spans if s["name"] == "forward")
+    assert "parentSpanId" not in fwd and len(fwd["traceId"]) == 32
+    metrics = {m["name"]: m for req in got["/v1/metrics"] for rm in req["resourceMetrics"] for sm in rm["scopeMetrics"]
+               for m in sm["metrics"]}
+    c = metrics["ksana_forward_req_total_num"]["sum"]
+    assert c["isMonotonic"] and c["aggregationTemporality"] == 2 and c["dataPoints"][0]["asDouble"] == 3
+    h = metrics["ksana_time_to_first_token_ms"]["histogram"]["dataPoints"][0]
+    assert h["count"] == "2" and h["sum"] == 20 and h["min"] == 7.5 and h["max"] == 12.5
+    # nobody listens: the request is dropped after the timeout and counted, the caller never waits
+    sent0, dropped0 = ne.otlp_stats()
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    dead_port = sock.getsockname()[1]
+    sock.close()
+    ne.span_set_sink(f"http://127.0.0.1:{dead_port}/v1/traces")
+    t0 = time.perf_counter()
+    ne.span_end(ne.span_start("lost", ""))
+    assert time.perf_counter() - t0 < 0.05
+    ne.otlp_flush(3000)
+    ne.span_set_sink("")
+    sent1, dropped1 = ne.otlp_stats()
+    assert dropped1 == dropped0 + 1 and sent1 == sent0
