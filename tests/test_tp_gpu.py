@@ -24,12 +24,12 @@ def _launch(nproc, out, backend, quant, port, graphs=None, arch=None, **extra_en
     return torch.load(out)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("push", ["0", "1"], ids=["pull", "epilogue-push"])
 def test_peer_memory_primitives(tmp_path, push):
     """The peer-memory collectives and the fused row-parallel linear against NCCL / fp32 references; once with the
     reduce kernel pulling the partial rows from the peers and once with the GEMM epilogue pushing them (small batches:
-    the default from four ranks on; large batches: KSANA_PUSH_PREFILL)."""
+    the default from four ranks on; large batches: KSANA_PUSH_PREFILL). One rank per visible GPU; on a one-GPU box
+    the same kernels run as a group of one (flags raised to and awaited from the rank itself)."""
     out_dir = os.environ.get("KSANA_TP_LOG_DIR", str(tmp_path))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", KSANA_PUSH=push, KSANA_PUSH_PREFILL=push)
     n = min(torch.cuda.device_count(), 8)
