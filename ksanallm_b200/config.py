@@ -411,7 +411,8 @@ def model_config_from_hf(hf: dict, generation: Optional[dict] = None) -> ModelCo
     eos = (generation or {}).get("eos_token_id", hf.get("eos_token_id"))
     if eos is not None:
         c.eos_token_ids = [int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos])]
-    c.pad_token_id = int(hf.get("pad_token_id") or 0)
+    pad = hf.get("pad_token_id")
+    c.pad_token_id = int(pad) if pad is not None else (1 if mt == "fairseq-transformer" else 0)   # fairseq dictionaries put <pad> at 1
     if c.num_heads % max(c.num_kv_heads, 1):
         raise ValueError("num_attention_heads must be a multiple of num_key_value_heads")
     return c

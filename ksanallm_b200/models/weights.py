@@ -447,12 +447,15 @@ def build_model(cfg: ModelConfig, source, tp_rank: int = 0, tp_size: int = 1, co
 
 
 def _sinusoidal_table(n: int, dim: int, padding_idx: int) -> torch.Tensor:
-    """fairseq-style sinusoidal positions (sin | cos halves), offset by the padding index."""
+    """fairseq-style sinusoidal positions (sin | cos halves). fairseq numbers the positions of a sequence from
+    ``padding_idx + 1`` on, so row p of this table (looked up with the engine's positions 0, 1, ...) holds the
+    embedding of fairseq position ``p + padding_idx + 1``."""
     import math
     half = dim // 2
     emb = math.log(10000) / (half - 1)
     emb = torch.exp(torch.arange(half, dtype=torch.float32) * -emb)
-    emb = torch.arange(n, dtype=torch.float32).unsqueeze(1) * emb.unsqueeze(0)
+    pos = torch.arange(n, dtype=torch.float32) + float(padding_idx + 1)
+    emb = pos.unsqueeze(1) * emb.unsqueeze(0)
     emb = torch.cat([torch.sin(emb), torch.cos(emb)], dim=1)
     if dim % 2 == 1:
         emb = torch.cat([emb, torch.zeros(n, 1)], dim=1)

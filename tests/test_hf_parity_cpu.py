@@ -71,6 +71,38 @@ def test_gpt2_learned_positions_layernorm_gelu_conv1d():
     _check(_init(GPT2LMHeadModel(c)), c.to_dict(), tol=5e-4)
 
 
+def test_gpt1_post_norm_blocks():
+    """GPT-1 (`openai-gpt`): learned positions, blocks that normalise after the residual add, Conv1D weights, tied head."""
+    from transformers import OpenAIGPTConfig, OpenAIGPTLMHeadModel
+    c = OpenAIGPTConfig(n_embd=64, n_layer=2, n_head=4, vocab_size=200, n_positions=128, afn="gelu",
+                        resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+    _check(_init(OpenAIGPTLMHeadModel(c)), c.to_dict(), tol=5e-4)
+
+
+def test_fairseq_style_decoder_sinusoidal_positions_scaled_embeddings():
+    """A fairseq-style decoder (XGLM is the Hugging Face export of that family): sinusoidal positions offset by the
+    padding index, embeddings scaled by sqrt(d), pre-norm blocks with self_attn_layer_norm / fc1 / fc2 /
+    final_layer_norm names and a closing layer_norm, through the `fairseq-transformer` model type and the
+    GPT-family weight map."""
+    from transformers import XGLMConfig, XGLMForCausalLM
+    c = XGLMConfig(vocab_size=200, max_position_embeddings=128, d_model=64, ffn_dim=160, num_layers=2, attention_heads=4,
+                   activation_function="gelu", dropout=0.0, attention_dropout=0.0, activation_dropout=0.0, layerdrop=0.0,
+                   scale_embedding=True, pad_token_id=1, bos_token_id=0, eos_token_id=2)
+    m = _init(XGLMForCausalLM(c))
+    hf_cfg = {"model_type": "fairseq-transformer", "decoder_embed_dim": 64, "decoder_layers": 2, "decoder_attention_heads": 4,
+              "decoder_ffn_embed_dim": 160, "vocab_size": 200, "max_target_positions": 128, "activation_function": "gelu",
+              "decoder_normalize_before": True, "no_scale_embedding": False, "pad_token_id": 1,
+              "tie_word_embeddings": True}
+    torch.manual_seed(0)
+    tokens = torch.randint(3, 200, (23,)).tolist()
+    m.eval()
+    with torch.no_grad():
+        want = m(torch.tensor([tokens])).logits[0].float()
+        got = _ours(hf_cfg, m.state_dict(), tokens)
+    err = float((got - want).abs().max())
+    assert err < 5e-4 * max(1.0, float(want.abs().max())), err
+
+
 def test_mixtral_softmax_top2_experts():
     from transformers import MixtralConfig, MixtralForCausalLM
     c = MixtralConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=96,
