@@ -265,6 +265,20 @@ def time_cases(names):
             if getattr(run, "bytes", 0):
                 extra += f", {run.bytes / ms / 1e6:.1f} GB/s of streamed bytes"
             print(f"{n}: {ms * 1000:.1f} us per launch{extra}")
+            # clock record: the same launch repeated for about three quarters of a second while nvidia-smi samples
+            # the SM clock and the throttle reasons (a burst of ten launches is over before the first sample)
+            from ksanallm_b200.utils.clocks import ClockSampler
+            sampler = ClockSampler(torch.cuda.current_device())
+            sampler.start()
+            loops = max(10, int(0.75 / max(ms * 1e-3, 1e-6)))
+            e0.record()
+            for _ in range(loops):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            clocks = sampler.stop()
+            print(f"{n}: sustained {e0.elapsed_time(e1) / loops * 1000:.1f} us per launch over {loops} launches; "
+                  f"SM clock median {clocks.get('sm_mhz')} of {clocks.get('sm_max_mhz')} MHz, reasons {clocks.get('reasons')}")
             continue
         # inputs are re-created inside each case; time only the second half by differencing two call counts
         reps = 3

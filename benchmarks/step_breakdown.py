@@ -191,17 +191,21 @@ def main():
                 else:
                     os.environ[k] = v
             os.environ.update(env)
+            from ksanallm_b200.utils.clocks import ClockSampler
+            sampler = ClockSampler(local, enabled=rank == 0)       # clock record of this table's measurements
+            sampler.start()
             res = run_breakdown(model, phase, args.batch if phase == "decode" else pbatch, args.ctx, args.q_len, args.reps,
                                 sync_all=sync_all, classes=os.environ.get("KSANA_PUSH_SIGNAL", "0") != "1")
-            res.update(world=world, emulate_tp=e, comm=args.comm if world > 1 else None, variant=name, env=env)
+            res.update(world=world, emulate_tp=e, comm=args.comm if world > 1 else None, variant=name, env=env,
+                       clocks=sampler.stop() if rank == 0 else None)
             if rank == 0:
                 print(json.dumps(res))
                 print("== %s / %s %s" % (name, phase, env), file=sys.stderr)
                 print("%-58s %6s %10s %8s" % ("class", "n", "us total", "us each"), file=sys.stderr)
                 for r in res["classes"]:
                     print("%-58s %6d %10.1f %8.2f" % (r["class"][:58], r["launches"], r["us_total"], r["us_each"]), file=sys.stderr)
-                print("full graph %.1f us; sum of classes %.1f us; %d launches" %
-                      (res["full_graph_us"], res["sum_of_classes_us"], res["native_launches"]), file=sys.stderr)
+                print("full graph %.1f us; sum of classes %.1f us; %d launches; clocks %s" %
+                      (res["full_graph_us"], res["sum_of_classes_us"], res["native_launches"], res["clocks"]), file=sys.stderr)
     sys.stdout.flush()
     if world > 1:
         dist.barrier()

@@ -513,6 +513,43 @@ __global__ void rerotate_blocks_kernel(T* __restrict__ cache, const int* __restr
   }
 }
 
+// Largest magnitude of a bf16 matrix as a quantisation scale on the device: scale = max(|x|) / divisor (at least
+// `floor`), without a host round trip and without a widened copy of x. `acc` is a zeroed 32-bit word; magnitudes are
+// non-negative, so their bit patterns order like integers and atomicMax works on them. The finishing kernel writes the
+// scale and leaves `acc` at zero for the next call.
+__global__ void absmax_kernel(const bf16* __restrict__ x, int rows, int cols, long long ldx, unsigned int* acc) {
+  __shared__ float red[32];
+  const int vec_per_row = cols >> 3;
+  const long long nvec = static_cast<long long>(rows) * vec_per_row;
+  float m = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row);
+    const uint4 v = *reinterpret_cast<const uint4*>(x + r * ldx + c * 8);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(p[k]);
+      m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    m = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (threadIdx.x == 0 && m > 0.f && m == m) atomicMax(acc, __float_as_uint(m));
+  }
+}
+__global__ void absmax_finish_kernel(unsigned int* acc, float* scale, float inv_divisor, float floor_value) {
+  *scale = fmaxf(__uint_as_float(*acc) * inv_divisor, floor_value);
+  *acc = 0u;
+}
+
 // ids[rows[i]] = prev_tokens[src[i]]: a pipelined step takes the input ids of its decode rows straight from the
 // previous step's sampler output on the device (the host has not read those tokens yet).
 __global__ void patch_ids_kernel(int* __restrict__ ids, const int* __restrict__ rows, const int* __restrict__ src,
@@ -729,6 +766,18 @@ extern "C" int ksana_rerotate_blocks(void* cache, const int* triples, int n, con
   else
     rerotate_blocks_kernel<uint8_t><<<dim3(n, 8), 256, 0, st>>>((uint8_t*)cache, triples, cos_sin, max_pos, layers, hkv,
                                                                 bt, D, rot_dim, neox, num_blocks, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// scale[0] = max(max |x| / divisor, floor) for x [rows, cols] bf16 (row stride ldx, cols a multiple of 8); acc: one
+// zeroed 32-bit word of device scratch that the call leaves zeroed.
+extern "C" int ksana_absmax_scale(const void* x, int rows, int cols, long long ldx, float divisor, float floor_value,
+                                  void* acc, float* scale, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if ((cols % 8) || (ldx % 8) || divisor <= 0.f || (reinterpret_cast<uintptr_t>(x) & 15)) return -10;
+  const long long nvec = static_cast<long long>(rows) * (cols >> 3);
+  absmax_kernel<<<grid_for(nvec, 256), 256, 0, st>>>((const bf16*)x, rows, cols, ldx, (unsigned int*)acc);
+  absmax_finish_kernel<<<1, 1, 0, st>>>((unsigned int*)acc, scale, 1.f / divisor, floor_value);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

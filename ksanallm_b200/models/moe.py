@@ -228,11 +228,11 @@ def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Ten
         if mw.nvfp4:
             # activations go to NVFP4 too: one tensor scale per GEMM input from its own maximum (no host sync);
             # padding rows are zero so that they do not enter the maximum
-            a_ts = (x.float().abs().amax() / (448.0 * 6.0)).clamp_min(1e-12).reshape(())
+            a_ts = native.absmax_scale(x, 448.0 * 6.0)
             pq, pbs, _ = native.quant_nvfp4(perm, a_ts)
             g = native.gemm_grouped_nvfp4(pq, pbs, a_ts, mw.w13, mw.w13_bs, mw.w13_ts, tile_expert, n_local, 2 * mw.inter)
             a = native.act_mul(g, cfg.activation, True)
-            a_ts2 = (a.float().abs().amax() / (448.0 * 6.0)).clamp_min(1e-12).reshape(())
+            a_ts2 = native.absmax_scale(a, 448.0 * 6.0)
             aq, abs_, _ = native.quant_nvfp4(a, a_ts2)
             y = native.gemm_grouped_nvfp4(aq, abs_, a_ts2, mw.w2, mw.w2_bs, mw.w2_ts, tile_expert, n_local, H)
         elif mw.w13_scale is not None:

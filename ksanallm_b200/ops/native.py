@@ -63,6 +63,7 @@ _SIGS = {
     "ksana_add": [vp, vp, vp, vp, i64, i32, vp],
     "ksana_patch_ids": [vp, vp, vp, vp, i32, i32, i32, vp, vp],
     "ksana_smallm_estimate": [i32, i32, i32, i32, vp],
+    "ksana_absmax_scale": [vp, i32, i32, i64, f32, f32, vp, vp, vp],
     "ksana_rerotate_blocks": [vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "ksana_cast_f32": [vp, vp, i64, vp],
     "ksana_paged_prefill_tc": [vp, i64, i64, vp, i64, vp, i64, i32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, i64,
@@ -426,6 +427,23 @@ def gemm_fp8(xq, xs, wq, ws, out=None, bias=None, residual=None, out_f32=None, b
                                     max_ctas, _p(err_flag(xq.device)), _st())
     _check(rc, "ksana_gemm_fp8_block")
     return dst
+
+
+_absmax_acc = {}
+
+
+def absmax_scale(x, divisor: float, floor: float = 1e-12):
+    """max(|x|) / divisor (at least ``floor``) of a bf16 matrix as an fp32 scalar tensor on the device: the tensor
+    scale of an NVFP4 activation, without a host round trip or a widened copy of ``x``."""
+    rows, cols = x.shape
+    key = (x.device.type, x.device.index)
+    acc = _absmax_acc.get(key)
+    if acc is None:
+        acc = _absmax_acc[key] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    scale = torch.empty((), dtype=torch.float32, device=x.device)
+    _check(lib().ksana_absmax_scale(_p(x), rows, cols, x.stride(0), float(divisor), float(floor), _p(acc), _p(scale),
+                                    _st()), "ksana_absmax_scale")
+    return scale
 
 
 def quant_nvfp4(x, tensor_scale):

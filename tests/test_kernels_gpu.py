@@ -449,3 +449,20 @@ def test_rerotate_blocks_matches_tensor_ops(kv_dtype, neox):
     with pytest.raises(RuntimeError):
         native.check_err_flag(DEV)
     native.clear_err_flag(DEV)
+
+
+def test_absmax_scale_on_device():
+    """Tensor scale of an NVFP4 activation computed on the device: max |x| / divisor with a floor, strided rows, and the
+    scratch word left at zero so that back-to-back calls are independent."""
+    torch.manual_seed(3)
+    big = torch.randn(300, 1024 + 64, device=DEV, dtype=torch.bfloat16) * 3
+    x = big[:, :1024]                                    # rows 1088 elements apart
+    x[17, 400] = -77.5
+    s = native.absmax_scale(x, 448.0 * 6.0)
+    torch.cuda.synchronize()
+    assert s.shape == () and abs(float(s) - 77.5 / (448.0 * 6.0)) < 1e-7
+    y = torch.randn(8, 64, device=DEV, dtype=torch.bfloat16) * 0.01
+    s2 = native.absmax_scale(y, 448.0 * 6.0)
+    assert abs(float(s2) - float(y.float().abs().amax()) / (448.0 * 6.0)) < 1e-9      # not the larger value of the first call
+    z = torch.zeros(4, 16, device=DEV, dtype=torch.bfloat16)
+    assert float(native.absmax_scale(z, 6.0, floor=1e-12)) == pytest.approx(1e-12)
