@@ -306,3 +306,92 @@ def test_pipelined_steps_give_the_tokens_of_synchronous_steps():
             assert eng._flight is None
         assert outs[0] == outs[1]
         assert any(len(t) < 30 for t, _ in outs[1]) and any(len(t) == 30 for t, _ in outs[1])
+
+
+def test_abort_while_a_pipelined_step_is_in_flight():
+    """A request is aborted after its next token has been launched but before that step's tokens reached the host: the
+    request ends with the abort status, the other request's tokens equal a run without the abort, nothing leaks."""
+    prompts = [[40, 41, 42, 43], [7, 8, 9]]
+    ref = tiny_engine()
+    ref.pipelined = True
+    want = ref.generate([prompts[1]], sampling(max_new_tokens=12, ignore_eos=True))[0].outputs[0].tokens
+    eng = tiny_engine()
+    eng.pipelined = True
+    a = eng.add_request(prompts[0], sampling(max_new_tokens=50, ignore_eos=True))
+    b = eng.add_request(prompts[1], sampling(max_new_tokens=12, ignore_eos=True))
+    for _ in range(4):
+        assert eng.step()
+    assert eng._flight is not None                      # a step is in flight: its tokens are still on the device
+    eng.abort(a)
+    for _ in range(200):
+        if a.done.is_set() and b.done.is_set():
+            break
+        eng.step()
+    assert a.done.is_set() and a.status_code == 4 and 0 < len(a.outputs[0].tokens) < 50
+    assert b.done.is_set() and b.status_code == 0 and b.outputs[0].tokens == want
+    while eng.step():
+        pass
+    assert eng._flight is None and eng.scheduler.idle() and eng.scheduler.check_invariants()[0]
+
+
+def test_request_that_needs_the_host_joins_pipelined_requests():
+    """A request with log-probabilities (the host looks at every step's logits) arrives while plain requests are being
+    stepped in pipelined mode: the step in flight is drained, stepping goes synchronous while that request lives and
+    pipelined again afterwards; every request's tokens equal a fully synchronous run."""
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(3, 300, (n,), generator=g).tolist() for n in (9, 21, 5)]
+
+    def run(pipelined):
+        eng = tiny_engine()
+        eng.pipelined = pipelined
+        plain = [eng.add_request(p, sampling(max_new_tokens=24, ignore_eos=True)) for p in prompts[:2]]
+        modes = []
+        for _ in range(5):
+            eng.step()
+            modes.append(eng._flight is not None)
+        probe = eng.add_request(prompts[2], sampling(max_new_tokens=6, ignore_eos=True, logprobs_num=2))
+        for _ in range(300):
+            if all(r.done.is_set() for r in plain + [probe]):
+                break
+            eng.step()
+            modes.append(eng._flight is not None)
+        while eng.step():
+            pass
+        assert eng._flight is None and eng.scheduler.idle()
+        assert len(probe.outputs[0].logprobs) == 6
+        return [r.outputs[0].tokens for r in plain + [probe]], modes
+
+    want, sync_modes = run(False)
+    got, modes = run(True)
+    assert got == want
+    assert not any(sync_modes)
+    assert modes[0] or modes[1]                       # pipelined before the probe arrives ...
+    assert not all(modes[5:11])                       # ... synchronous while it lives ...
+    assert modes[-1] or any(modes[11:])               # ... and pipelined again for the rest of the plain requests
+
+
+def test_streaming_under_pipelined_steps_delivers_every_token_in_order():
+    """Streamed pieces of a pipelined run (tokens reach the host one step late) add up to the tokens of a blocking,
+    synchronous run, in order, and the stream ends with its end marker."""
+    prompt = [5, 6, 7, 8, 9]
+    base = tiny_engine()
+    base.pipelined = False
+    want = base.generate([prompt], sampling(max_new_tokens=15, ignore_eos=True))[0].outputs[0].tokens
+    eng = tiny_engine()
+    eng.pipelined = True
+    eng.start()
+    try:
+        req = eng.add_request(prompt, sampling(max_new_tokens=15, ignore_eos=True), stream=True)
+        seen = []
+        while True:
+            item = req.stream_queue.get(timeout=30)
+            if item is None:
+                break
+            assert item[0] == "step"
+            seen.append(list(item[1][0]))
+        assert req.done.wait(30) and req.status_code == 0
+    finally:
+        eng.stop()
+    # every piece carries the tokens so far (or the new ones): the last piece, or their concatenation, is the answer
+    flat = seen[-1] if len(seen[-1]) == len(want) else [t for piece in seen for t in piece]
+    assert flat == want and req.outputs[0].tokens == want
