@@ -173,7 +173,17 @@ def main():
                     help="weight scales: powers of two applied by the tensor cores, or exact amax/448 fp32 scales")
     ap.add_argument("--no-graphs", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
     ap.add_argument("--no-tp-check", action="store_true", help="skip the fused-vs-NCCL numerics check that precedes a multi-GPU run")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="instead of the benchmark: device time of one decode step and one prefill step of this model by "
+                         "kernel class (benchmarks/step_breakdown.py; --layers limits the depth, --comm picks the path)")
     args = ap.parse_args()
+
+    if args.breakdown:
+        from benchmarks import step_breakdown
+        sys.argv = [sys.argv[0], "--phase", "both", "--batch", str(args.batch), "--prefill-batch", "8", "--q-len",
+                    str(args.input_len), "--ctx", str(args.input_len + args.output_len // 2), "--layers",
+                    str(args.layers or 80), "--comm", args.comm, "--scale-mode", args.scale_mode]
+        return step_breakdown.main()
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
