@@ -207,20 +207,33 @@ def shared_expert(model, mw: MoEWeights, x: torch.Tensor) -> torch.Tensor:
     return so
 
 
+def route(model, mw: MoEWeights, x: torch.Tensor):
+    """Expert choice of every row of ``x``: (ids [T, K] int32, weights [T, K] fp32), by the router of this block."""
+    cfg = model.cfg
+    T = x.shape[0]
+    K, E = cfg.num_experts_per_tok, mw.num_experts
+    if x.is_cuda:
+        logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
+        native.gemm_bf16(x, mw.router.to(torch.bfloat16) if mw.router.dtype != torch.bfloat16 else mw.router, out_f32=logits)
+        return native.moe_route(logits, K, cfg.moe_scoring, cfg.norm_topk_prob, cfg.routed_scaling_factor,
+                                mw.router_bias, cfg.n_group, cfg.topk_group)
+    ids, w = route_reference(x.float() @ mw.router.float().t(), cfg, mw.router_bias)
+    return ids.to(torch.int32), w.float()
+
+
 def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Tensor] = None,
-                shared: bool = True) -> torch.Tensor:
+                shared: bool = True, routing=None) -> torch.Tensor:
     """This rank's share of MoE(x): the weighted outputs of the experts (or expert slices) it holds plus its slice
     of the shared expert, before any reduction over ranks. ``into`` ([T, H], e.g. a peer-visible buffer that a
-    reduce kernel pulls from) receives the result when given."""
+    reduce kernel pulls from) receives the result when given. ``routing`` = (ids [T, K] int32, weights [T, K] fp32)
+    decided elsewhere (the row's home rank under expert-parallel all-to-all dispatch; choices of experts this rank
+    does not hold carry id -1) replaces this block's own router."""
     cfg = model.cfg
     T, H = x.shape
     K, E = cfg.num_experts_per_tok, mw.num_experts
     n_local = mw.expert_hi - mw.expert_lo
     if x.is_cuda:
-        logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
-        native.gemm_bf16(x, mw.router.to(torch.bfloat16) if mw.router.dtype != torch.bfloat16 else mw.router, out_f32=logits)
-        ids, w = native.moe_route(logits, K, cfg.moe_scoring, cfg.norm_topk_prob, cfg.routed_scaling_factor,
-                                  mw.router_bias, cfg.n_group, cfg.topk_group)
+        ids, w = routing if routing is not None else route(model, mw, x)
         dst_row, tile_expert, _, _, cap = native.moe_align(ids, E, mw.expert_lo, mw.expert_hi)
         if mw.expert_lo:
             tile_expert = torch.where(tile_expert >= 0, tile_expert - mw.expert_lo, tile_expert)
@@ -256,8 +269,10 @@ def moe_partial(model, mw: MoEWeights, x: torch.Tensor, into: Optional[torch.Ten
         native.moe_combine(y, dst_row, w, out, K, accumulate=have_shared)
         return out
     else:
-        logits = x.float() @ mw.router.float().t()
-        ids, w = route_reference(logits, cfg, mw.router_bias)
+        if routing is not None:
+            ids, w = routing[0].long(), routing[1].float()
+        else:
+            ids, w = route_reference(x.float() @ mw.router.float().t(), cfg, mw.router_bias)
         out = torch.zeros(T, H, dtype=torch.float32)
         if mw.nvfp4:
             I2 = 2 * mw.inter

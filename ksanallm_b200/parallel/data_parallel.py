@@ -33,6 +33,12 @@ class AttentionDP:
         self.counts: List[int] = [0] * size          # rows per rank of the step being executed
         self.blocks_per_rank = 0                     # device blocks of one rank's pool (set by the engine)
         self.gathered_bytes = 0
+        # "allgather": every rank sees every row (dispatch = all-gather, combine = reduce-scatter; over peer memory with
+        # the fused backend). "alltoall": a row travels only to the ranks that hold one of its experts and only their
+        # weighted outputs travel back (library all-to-all collectives with per-step sizes; KSANA_EP_DISPATCH=alltoall)
+        import os
+        self.dispatch = os.environ.get("KSANA_EP_DISPATCH", "allgather")
+        self.dispatched_rows = 0                     # rows sent to other ranks (all-to-all) since the start
 
     # ------------------------------------------------------------------ step plan -> this rank's share
     def owner(self, seq_ids: np.ndarray) -> np.ndarray:
@@ -115,6 +121,8 @@ class AttentionDP:
         T, H = x.shape
         if t_max == 0:
             return h
+        if self.dispatch == "alltoall":
+            return self._moe_alltoall(model, mw, x, h)
         pad = x if T == t_max else torch.cat([x, x.new_zeros(t_max - T, H)], 0)
         if self.symm is not None and x.is_cuda:
             # peer-memory path: rows pulled from the peers' staging areas (dispatch), this rank's experts run over
@@ -145,3 +153,61 @@ class AttentionDP:
         if mw.shared_gate_up is not None and T:
             out = out + shared_expert(model, mw, x)
         return ops.add(h, out.contiguous()) if T else h
+
+    def _moe_alltoall(self, model, mw, x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        """Expert-parallel block as an all-to-all. Every rank routes its own rows, sends a row once to each rank that
+        holds at least one of the row's chosen experts (with the choices restricted to that rank's experts), the
+        owners run their experts on what they received and send one weighted sum per received row back, and the home
+        rank adds up what returns. With group-limited routing a row reaches at most ``topk_group`` ranks instead of
+        all of them. Sizes differ per step, so the row counts are exchanged first (one small all-to-all and a host
+        read); every rank takes part in every collective, also with no rows of its own."""
+        from ..models.moe import moe_partial, route, shared_expert
+        from ..ops import dispatch as ops
+        T, H = x.shape
+        K = model.cfg.num_experts_per_tok
+        dev = x.device
+        per = mw.expert_hi - mw.expert_lo                     # experts per rank (whole experts, equal shares)
+        if T:
+            ids, w = route(model, mw, x)
+            dest = (ids.long() // per).clamp_(0, self.size - 1)                  # [T, K] owner rank of every choice
+        send_idx, send_counts = [], []
+        for d in range(self.size):
+            idx = (dest == d).any(dim=1).nonzero(as_tuple=True)[0] if T else torch.zeros(0, dtype=torch.long, device=dev)
+            send_idx.append(idx)
+            send_counts.append(int(idx.numel()))
+        order = torch.cat(send_idx) if T else torch.zeros(0, dtype=torch.long, device=dev)
+        n_send = int(order.numel())
+        rows = x[order].contiguous() if n_send else x.new_zeros(0, H)
+        if n_send:
+            to = torch.repeat_interleave(torch.arange(self.size, device=dev), torch.tensor(send_counts, device=dev))
+            here = dest[order] == to.unsqueeze(1)                                 # choices that live on the target rank
+            s_ids = torch.where(here, ids[order].to(torch.int32), torch.full_like(ids[order], -1, dtype=torch.int32)).contiguous()
+            s_w = torch.where(here, w[order], torch.zeros_like(w[order])).contiguous()
+        else:
+            s_ids = torch.zeros(0, K, dtype=torch.int32, device=dev)
+            s_w = torch.zeros(0, K, dtype=torch.float32, device=dev)
+        cnt_out = torch.tensor(send_counts, dtype=torch.int64, device=dev)
+        cnt_in = torch.empty(self.size, dtype=torch.int64, device=dev)
+        dist.all_to_all_single(cnt_in, cnt_out, group=self.group)
+        recv_counts = [int(c) for c in cnt_in.tolist()]
+        n_recv = sum(recv_counts)
+        r_rows = torch.empty(n_recv, H, dtype=x.dtype, device=dev)
+        r_ids = torch.empty(n_recv, K, dtype=torch.int32, device=dev)
+        r_w = torch.empty(n_recv, K, dtype=torch.float32, device=dev)
+        for out_t, in_t in ((r_rows, rows), (r_ids, s_ids), (r_w, s_w)):
+            dist.all_to_all_single(out_t, in_t, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=self.group)
+        self.dispatched_rows += n_send - send_counts[self.rank]
+        self.gathered_bytes += (n_recv - recv_counts[self.rank]) * H * x.element_size()
+        if n_recv:
+            part = moe_partial(model, mw, r_rows, shared=False, routing=(r_ids, r_w)).contiguous()
+        else:
+            part = x.new_zeros(0, H)
+        back = torch.empty(n_send, H, dtype=x.dtype, device=dev)
+        dist.all_to_all_single(back, part, output_split_sizes=send_counts, input_split_sizes=recv_counts, group=self.group)
+        if not T:
+            return h
+        out = torch.zeros(T, H, dtype=torch.float32, device=dev)
+        out.index_add_(0, order, back.float())
+        if mw.shared_gate_up is not None:
+            out = out + shared_expert(model, mw, x).float()
+        return ops.add(h, out.to(x.dtype).contiguous())

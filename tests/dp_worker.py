@@ -70,6 +70,7 @@ def main():
                    if llm.model.dp is not None else None)
         torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "first": torch.stack([first[k] for k in order]),
                     "experts": (moe.expert_lo, moe.expert_hi), "gathered_bytes": llm.model.dp.gathered_bytes if llm.model.dp else 0,
+                    "dispatched_rows": llm.model.dp.dispatched_rows if llm.model.dp else 0,
                     "peer_memory": bool(llm.model.dp is not None and llm.model.dp.symm is not None),
                     "stats": dict(llm.engine.scheduler.stats()) if llm.engine.scheduler else {},
                     "refused": (refused.status_code, refused.done.is_set()) if llm.model.dp is not None else None},

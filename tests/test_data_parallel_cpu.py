@@ -54,17 +54,25 @@ def _single(new_tokens=5):
     return [r.outputs[0].tokens for r in reqs], torch.stack([first[k] for k in sorted(first)])
 
 
-@pytest.mark.parametrize("nproc,port", [(2, 29721), (4, 29722)])
-def test_attention_dp_matches_single_process(tmp_path, nproc, port):
+@pytest.mark.parametrize("nproc,port,dispatch", [(2, 29721, "allgather"), (4, 29722, "allgather"),
+                                                 (2, 29723, "alltoall"), (4, 29724, "alltoall")])
+def test_attention_dp_matches_single_process(tmp_path, nproc, port, dispatch):
+    """Attention data parallelism + expert parallelism on CPU ranks against one process, with both forms of the
+    expert dispatch: all-gather of every rank's rows, and the all-to-all that sends a row only to the ranks holding
+    one of its experts (fewer bytes received than with the all-gather)."""
     want_tokens, want_first = _single()
     out = str(tmp_path / "dp.pt")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "dp_worker.py"), out, "cpu"]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, OMP_NUM_THREADS="1", KSANA_EP_DISPATCH=dispatch))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     got = torch.load(out)
     assert got["experts"] == (0, 8 // nproc)                    # rank 0 holds whole experts, a 1/nproc share
     assert got["gathered_bytes"] > 0
+    if dispatch == "alltoall":
+        assert got["dispatched_rows"] > 0
+
     assert float((got["first"] - want_first).abs().max()) < 1e-3
     assert got["tokens"] == want_tokens
 
@@ -93,3 +101,19 @@ def test_attention_dp_ranks_pool_their_caches(tmp_path, blocks, host):
         assert st["preempt_swap"] > 0 and st["swap_in"] > 0
     else:
         assert st["preempt_swap"] == 0 and st["preempt_recompute"] == 0
+
+
+def test_alltoall_dispatch_moves_fewer_rows_than_allgather(tmp_path):
+    """Four CPU ranks, top-2 of 8 experts (two experts per rank): with the all-to-all a row reaches at most two
+    ranks, with the all-gather every rank receives every row; same tokens either way."""
+    res = {}
+    for i, dispatch in enumerate(("allgather", "alltoall")):
+        out = str(tmp_path / f"dp_{dispatch}.pt")
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+               "127.0.0.1", "--master-port", str(29731 + i), os.path.join(ROOT, "tests", "dp_worker.py"), out, "cpu"]
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=300,
+                           env=dict(os.environ, OMP_NUM_THREADS="1", KSANA_EP_DISPATCH=dispatch))
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+        res[dispatch] = torch.load(out)
+    assert res["alltoall"]["tokens"] == res["allgather"]["tokens"]
+    assert 0 < res["alltoall"]["gathered_bytes"] < 0.75 * res["allgather"]["gathered_bytes"]
