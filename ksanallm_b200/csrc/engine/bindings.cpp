@@ -9,6 +9,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "batch_loop.h"
 #include "cache_manager.h"
 #include "common.h"
 #include "control_channel.h"
@@ -353,6 +354,45 @@ PYBIND11_MODULE(_ksana_engine, m) {
         return py::make_tuple(ok, why);
       });
 
+  {
+    // python callables for the native loop thread: entered with the interpreter lock, released with it, and an
+    // exception that escapes one becomes a plain C++ exception carrying its text
+    auto hold = [](py::function f) {
+      return std::shared_ptr<py::function>(new py::function(std::move(f)), [](py::function* p) {
+        py::gil_scoped_acquire g;
+        delete p;
+      });
+    };
+    py::class_<BatchLoop>(m, "BatchLoop")
+        .def(py::init<>())
+        .def("start", [hold](BatchLoop& self, py::function step, py::function idle, py::function on_error) {
+          auto s = hold(std::move(step)), i = hold(std::move(idle)), e = hold(std::move(on_error));
+          auto call_bool = [](const std::shared_ptr<py::function>& f) {
+            py::gil_scoped_acquire g;
+            try {
+              return (*f)().cast<bool>();
+            } catch (py::error_already_set& err) {
+              const std::string msg = err.what();
+              throw std::runtime_error(msg);
+            }
+          };
+          py::gil_scoped_release rel;        // Start() may join a previous thread that needs the lock
+          self.Start([s, call_bool]() { return call_bool(s); }, [i, call_bool]() { return call_bool(i); },
+                     [e](const std::string& msg) {
+                       py::gil_scoped_acquire g;
+                       try {
+                         (*e)(msg);
+                       } catch (py::error_already_set& err) {
+                         throw std::runtime_error(std::string(err.what()));
+                       }
+                     });
+        }, py::arg("step"), py::arg("idle"), py::arg("on_error"))
+        .def("notify", &BatchLoop::Notify)
+        .def("stop", [](BatchLoop& self) { py::gil_scoped_release rel; self.Stop(); })
+        .def_property_readonly("running", &BatchLoop::running)
+        .def_property_readonly("steps", &BatchLoop::steps)
+        .def_property_readonly("sleeps", &BatchLoop::sleeps);
+  }
   BindFsm(m);
   BindProfiler(m);
   BindControlChannel(m);

@@ -402,6 +402,7 @@ class LLMEngine:
         self._next_req = 1
         self._lock = threading.Lock()
         self._wake = threading.Condition()
+        self._native_loop = None
         self._thread: Optional[threading.Thread] = None
         self._stop = False
         self.steps = 0
@@ -465,15 +466,13 @@ class LLMEngine:
                 req.outputs[0].tokens = list(init)
                 self.scheduler.replace_generated(seq_ids[0], list(init))
         ne.report_counter("metric_input_tokens_num", len(prompt))
-        with self._wake:
-            self._wake.notify_all()
+        self._notify_loop()
         return req
 
     def abort(self, req: Request):
         req.aborted = True
         self.scheduler.abort(req.req_id)
-        with self._wake:
-            self._wake.notify_all()
+        self._notify_loop()
 
     def _complete(self, req: Request):
         req.finish_time = time.time()
@@ -919,11 +918,33 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ loop
     def start(self):
-        if self._thread is not None:
+        """Starts the step loop: a native thread (``BatchLoop``: sleeps on a condition variable while idle, woken by
+        ``add_request`` / ``abort``), or a Python thread with ``KSANA_NATIVE_LOOP=0``."""
+        if self._thread is not None or self._native_loop is not None:
             return
         self._stop = False
+        if os.environ.get("KSANA_NATIVE_LOOP", "1") != "0" and hasattr(ne, "BatchLoop"):
+            self._native_loop = ne.BatchLoop()
+            self._native_loop.start(self._loop_step, self._loop_idle, self._loop_error)
+            return
         self._thread = threading.Thread(target=self._loop, name="ksana-engine", daemon=True)
         self._thread.start()
+
+    def _loop_step(self) -> bool:
+        return False if self._stop else bool(self.step())
+
+    def _loop_idle(self) -> bool:
+        return bool(self.scheduler.idle()) and not self._stop
+
+    def _loop_error(self, message: str):
+        logger.error(f"engine step failed: {message}")
+        self._fail_all(12, f"engine step failed: {message}")
+
+    def _notify_loop(self):
+        with self._wake:
+            self._wake.notify_all()
+        if self._native_loop is not None:
+            self._native_loop.notify()
 
     def _loop(self):
         while not self._stop:
@@ -978,8 +999,10 @@ class LLMEngine:
 
     def stop(self):
         self._stop = True
-        with self._wake:
-            self._wake.notify_all()
+        self._notify_loop()
+        if self._native_loop is not None:
+            self._native_loop.stop()
+            self._native_loop = None
         if self._thread is not None:
             self._thread.join(timeout=10)
             self._thread = None

@@ -534,3 +534,47 @@ def test_otlp_http_export_of_spans_and_metrics():
     ne.span_set_sink("")
     sent1, dropped1 = ne.otlp_stats()
     assert dropped1 == dropped0 + 1 and sent1 == sent0
+
+
+def test_native_batch_loop_sleeps_wakes_and_survives_errors():
+    """The engine's loop thread in C++: runs the step callable while it reports work, sleeps on its condition variable
+    while the idle callable says so (no spinning), wakes within milliseconds of `notify`, hands an exception that
+    escapes a step to the error callable and keeps going, and stops promptly."""
+    import threading
+    import time
+    work = {"n": 0, "pending": 0, "errors": []}
+    lock = threading.Lock()
+    woke = threading.Event()
+
+    def step():
+        with lock:
+            if work["pending"] == 0:
+                return False
+            work["pending"] -= 1
+            work["n"] += 1
+            if work["n"] == 3:
+                raise ValueError("third step fails")
+        woke.set()
+        return True
+
+    loop = ne.BatchLoop()
+    loop.start(step, lambda: work["pending"] == 0, lambda msg: work["errors"].append(msg))
+    try:
+        time.sleep(0.3)
+        assert loop.running and loop.steps == 0 and loop.sleeps <= 4          # idle: asleep, not polling
+        with lock:
+            work["pending"] = 5
+        t0 = time.perf_counter()
+        loop.notify()
+        assert woke.wait(2.0) and time.perf_counter() - t0 < 0.1
+        deadline = time.time() + 5
+        while time.time() < deadline and work["pending"]:
+            time.sleep(0.01)
+        assert work["pending"] == 0 and work["n"] == 5
+        assert loop.steps == 4                                              # the failing step does not count as run
+        assert len(work["errors"]) == 1 and "third step fails" in work["errors"][0]
+    finally:
+        t0 = time.perf_counter()
+        loop.stop()
+        assert time.perf_counter() - t0 < 1.0 and not loop.running
+    loop.stop()                                                             # twice is fine
