@@ -114,7 +114,8 @@ def build_host_stress(sanitizer: str = "thread") -> Path:
     compiled with -fsanitize=<thread|address|undefined>; run the returned binary, it exits 0 when clean."""
     OBJ.mkdir(exist_ok=True)
     edir = CSRC / "engine"
-    srcs = [edir / n for n in ("host_stress.cpp", "scheduler.cpp", "cache_manager.cpp", "control_channel.cpp", "logger.cpp")]
+    srcs = [edir / n for n in ("host_stress.cpp", "scheduler.cpp", "cache_manager.cpp", "control_channel.cpp", "logger.cpp", "batch_loop.cpp",
+                                 "otlp_export.cpp")]
     out = OBJ / f"host_stress_{sanitizer}"
     if _newer(out, [*srcs, *sorted(edir.glob("*.h"))]):
         _run(["g++", "-O1", "-g", "-std=c++17", "-pthread", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer",

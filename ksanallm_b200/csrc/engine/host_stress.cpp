@@ -5,16 +5,22 @@
 //    sharing. At the end every request is finished and the block accounting invariants hold.
 // 2. Control plane: a master and two workers over localhost TCP (registration, barrier, layer assignment,
 //    block-number consensus, step-plan broadcast, heartbeats, cluster shutdown), each on its own thread.
+// 3. Loop thread: several producers hand work to a BatchLoop and wake it while it sleeps, a failing step goes through
+//    the error callable, Stop() joins. 4. OTLP exporter: spans and metric snapshots enqueued from several threads for a
+//    collector that is not there (connection refused): everything is dropped and counted, nothing blocks.
 // The reference ships no sanitizer configuration (only gcov flags: CMakeLists.txt WITH_TESTING); its scheduler is
 // guarded by two hand-placed mutexes (src/ksana_llm/batch_scheduler/state/batch_state.h).
 #include <atomic>
 #include <cstdio>
 #include <random>
+#include <stdexcept>
 #include <string>
 #include <thread>
 #include <vector>
 
+#include "batch_loop.h"
 #include "control_channel.h"
+#include "otlp_export.h"
 #include "scheduler.h"
 
 using namespace ksana;
@@ -140,12 +146,68 @@ static void ControlPlaneStress() {
   std::printf("control plane stress: %d broadcasts received\n", got.load());
 }
 
+static void BatchLoopStress() {
+  std::atomic<int> pending{0}, done{0}, errors{0};
+  BatchLoop loop;
+  loop.Start(
+      [&]() {
+        int p = pending.load();
+        while (p > 0 && !pending.compare_exchange_weak(p, p - 1)) {}
+        if (p <= 0) return false;
+        if (done.fetch_add(1) % 97 == 96) throw std::runtime_error("a failing step");
+        return true;
+      },
+      [&]() { return pending.load() == 0; }, [&](const std::string&) { ++errors; });
+  std::vector<std::thread> producers;
+  for (int t = 0; t < 4; ++t) {
+    producers.emplace_back([&] {
+      for (int i = 0; i < 500; ++i) {
+        pending.fetch_add(1);
+        loop.Notify();
+        if (i % 50 == 0) std::this_thread::sleep_for(std::chrono::milliseconds(2));     // let the loop fall asleep
+      }
+    });
+  }
+  for (auto& t : producers) t.join();
+  for (int i = 0; i < 500 && pending.load() > 0; ++i) std::this_thread::sleep_for(std::chrono::milliseconds(10));
+  EXPECT(pending.load() == 0 && done.load() == 2000);
+  EXPECT(errors.load() == 2000 / 97);
+  loop.Stop();
+  EXPECT(!loop.running());
+  std::printf("batch loop stress: %d steps, %d errors handled, %lld sleeps\n", done.load(), errors.load(),
+              static_cast<long long>(loop.sleeps()));
+}
+
+static void OtlpStress() {
+  OtlpExporter& ex = OtlpExporter::Instance();
+  ex.Configure({{"instance", "stress"}}, 200);
+  const int64_t dropped0 = ex.dropped();
+  std::vector<std::thread> threads;
+  for (int t = 0; t < 4; ++t) {
+    threads.emplace_back([&ex, t] {
+      for (int i = 0; i < 100; ++i) {
+        OtlpSpan s;
+        s.name = "span"; s.trace_id = std::string(32, 'a'); s.span_id = std::string(16, static_cast<char>('0' + t));
+        s.start_us = 1; s.end_us = 2; s.attrs = {{"i", std::to_string(i)}};
+        ex.EnqueueSpan("http://127.0.0.1:9/v1/traces", std::move(s));          // the discard port: nobody listens
+      }
+      ex.EnqueueMetrics("http://127.0.0.1:9/v1/metrics", {{"ksana_x", true, 1, 1.0, 0, 0}}, 1);
+    });
+  }
+  for (auto& t : threads) t.join();
+  ex.Flush(10000);
+  EXPECT(ex.dropped() > dropped0 && ex.sent() == 0);
+  std::printf("otlp stress: %lld requests dropped for an absent collector\n", static_cast<long long>(ex.dropped() - dropped0));
+}
+
 int main() {
   SchedulerStress(0);
   SchedulerStress(1);
   SchedulerStress(0, 3);
   SchedulerStress(1, 2);
   ControlPlaneStress();
+  BatchLoopStress();
+  OtlpStress();
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);
     return 1;
