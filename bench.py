@@ -231,8 +231,19 @@ def main():
         init_distributed("cuda", 1)
         tp_dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(tp_dev)
+        def beyond(errs):
+            return any(v > TP_CHECK_LIMITS[k.rsplit("_", 1)[0]] for k, v in errs.items())
+
         tp_numerics = tp_check(rank, world, tp_dev)
-        if any(v > TP_CHECK_LIMITS[k.rsplit("_", 1)[0]] for k, v in tp_numerics.items()):
+        if beyond(tp_numerics) and args.comm == "fused" and os.environ.get("KSANA_PUSH") != "0":
+            # every rank computed the same errors, so every rank takes this branch: once more with the reduce kernels
+            # pulling the partial rows instead of the GEMM epilogues pushing them, and the run goes on in that form
+            # (reported in the result line) if the check then passes
+            first = dict(tp_numerics)
+            os.environ["KSANA_PUSH"] = "0"
+            tp_numerics = tp_check(rank, world, tp_dev)
+            tp_numerics["with_epilogue_push"] = first
+        if beyond({k: v for k, v in tp_numerics.items() if not isinstance(v, dict)}):
             if rank == 0:
                 print(json.dumps({"error": "tensor-parallel numerics check failed", "tp_check": tp_numerics}))
             sys.stdout.flush()
@@ -317,7 +328,7 @@ def main():
             "impl": "ours",
             "config": {"model": "Llama-3-70B architecture, random-init N(0,0.02)" + (" [DEBUG %d layers: INVALID]" % args.layers if args.layers else ""),
                        "global_batch": B, "seq_len": S_in, "output_len": S_out, "parallelism": ("tp%d" % world) if args.pp == 1 else ("pp%d x tp%d, %d micro-batches" % (args.pp, world // args.pp, args.micro_batches)),
-                       "comm": args.comm, "kv_block_tokens": 16, "weight_scale_mode": args.scale_mode, "cuda_graph_decode": not args.no_graphs,
+                       "comm": args.comm, "decode_epilogue_push": os.environ.get("KSANA_PUSH", "auto (4+ ranks)"), "kv_block_tokens": 16, "weight_scale_mode": args.scale_mode, "cuda_graph_decode": not args.no_graphs,
                        "l2": "inputs larger than L2 (weights 70 GB per pass); no explicit flush"},
             "p50_ttft_ms": statistics.median(latency["ttft"]) if latency["ttft"] else None,
             "p50_tpot_ms": statistics.median(latency["tpot"]) if latency["tpot"] else None,
