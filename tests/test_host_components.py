@@ -578,3 +578,28 @@ def test_native_batch_loop_sleeps_wakes_and_survives_errors():
         loop.stop()
         assert time.perf_counter() - t0 < 1.0 and not loop.running
     loop.stop()                                                             # twice is fine
+
+
+def test_clock_record_parser_and_breakdown_helpers():
+    """The nvidia-smi clock record (median SM clock, maximum, throttle reasons that were active in any sample; absent
+    tool reported as such) and the launch-class key of the step breakdown tool."""
+    import importlib.util
+    import os
+    from ksanallm_b200.utils.clocks import ClockSampler
+    c = ClockSampler(0)
+    c.lines = ["0, 1965, 1965, 410.5, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active",
+               "0, 1470, 1965, 998.2, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+               "0, 1455, 1965, 1001.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+               "garbage line"]
+    c.proc = type("P", (), {"terminate": lambda s: None, "wait": lambda s, timeout=0: None, "kill": lambda s: None})()
+    rec = c.stop()
+    assert rec == {"sm_mhz": 1470.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"], "samples": 3}
+    off = ClockSampler(0, enabled=False)
+    off.start()
+    assert off.stop()["sm_mhz"] is None
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("step_breakdown", os.path.join(root, "benchmarks", "step_breakdown.py"))
+    sb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sb)
+    key = sb._class_key("ksana_gemm_smallm", (2, 140737488355328, 8192, None, 64, True, 1280, 0.5, 9999999999))
+    assert key == "gemm_smallm(2,8192,64,1280)"          # pointers, floats, flags and huge values do not split classes
