@@ -403,6 +403,7 @@ class LLMEngine:
         self._lock = threading.Lock()
         self._wake = threading.Condition()
         self._native_loop = None
+        self._loop_bound = False
         self._thread: Optional[threading.Thread] = None
         self._stop = False
         self.steps = 0
@@ -931,7 +932,18 @@ class LLMEngine:
         self._thread.start()
 
     def _loop_step(self) -> bool:
-        return False if self._stop else bool(self.step())
+        if self._stop:
+            return False
+        self._bind_loop_thread()
+        return bool(self.step())
+
+    def _bind_loop_thread(self):
+        """The current CUDA device is a per-thread setting: the loop thread adopts the model's device once."""
+        if not self._loop_bound:
+            self._loop_bound = True
+            dev = getattr(self.runner, "device", None)
+            if dev is not None and torch.device(dev).type == "cuda":
+                torch.cuda.set_device(dev)
 
     def _loop_idle(self) -> bool:
         return bool(self.scheduler.idle()) and not self._stop
@@ -949,6 +961,7 @@ class LLMEngine:
     def _loop(self):
         while not self._stop:
             try:
+                self._bind_loop_thread()
                 ran = self.step()
             except Exception as e:  # noqa: BLE001 - the loop must survive and fail the affected requests
                 import traceback
