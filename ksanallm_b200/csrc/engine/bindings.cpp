@@ -4,6 +4,7 @@
 // HTTP-facing Python package builds the request/response objects on top of these.
 #include "endpoint_plugin.h"
 #include "stop_checker.h"
+#include "waiter.h"
 #include "request_packer.h"
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
@@ -392,6 +393,46 @@ PYBIND11_MODULE(_ksana_engine, m) {
         .def_property_readonly("running", &BatchLoop::running)
         .def_property_readonly("steps", &BatchLoop::steps)
         .def_property_readonly("sleeps", &BatchLoop::sleeps);
+  }
+  {
+    // same surface as threading.Event / queue.Queue (set, is_set, wait(timeout seconds) / put, get(timeout seconds)
+    // raising queue.Empty), so the request objects use them in place of the interpreter's own primitives
+    py::class_<Waiter>(m, "Waiter")
+        .def(py::init<>())
+        .def("set", &Waiter::Set)
+        .def("clear", &Waiter::Clear)
+        .def("is_set", &Waiter::IsSet)
+        .def("wait", [](Waiter& self, py::object timeout) {
+          const long long ms = timeout.is_none() ? -1 : static_cast<long long>(timeout.cast<double>() * 1000.0);
+          py::gil_scoped_release rel;
+          return self.Wait(ms);
+        }, py::arg("timeout") = py::none());
+    using Channel = StreamChannel<std::shared_ptr<py::object>>;
+    py::class_<Channel>(m, "StreamChannel")
+        .def(py::init<>())
+        .def("put", [](Channel& self, py::object item) {
+          // the handle dies with the interpreter lock held wherever the last reference goes away
+          self.Put(std::shared_ptr<py::object>(new py::object(std::move(item)), [](py::object* p) {
+            py::gil_scoped_acquire g;
+            delete p;
+          }));
+        })
+        .def("get", [](Channel& self, py::object timeout) -> py::object {
+          const long long ms = timeout.is_none() ? -1 : static_cast<long long>(timeout.cast<double>() * 1000.0);
+          std::shared_ptr<py::object> item;
+          bool ok;
+          {
+            py::gil_scoped_release rel;
+            ok = self.Get(&item, ms);
+          }
+          if (!ok) {
+            PyErr_SetNone(py::module_::import("queue").attr("Empty").ptr());
+            throw py::error_already_set();
+          }
+          return *item;
+        }, py::arg("timeout") = py::none())
+        .def("qsize", &Channel::Size)
+        .def("empty", [](Channel& self) { return self.Size() == 0; });
   }
   BindFsm(m);
   BindProfiler(m);

@@ -22,6 +22,7 @@
 #include "control_channel.h"
 #include "otlp_export.h"
 #include "scheduler.h"
+#include "waiter.h"
 
 using namespace ksana;
 
@@ -178,6 +179,28 @@ static void BatchLoopStress() {
               static_cast<long long>(loop.sleeps()));
 }
 
+static void WaiterStress() {
+  StreamChannel<int> ch;
+  Waiter done;
+  std::atomic<long long> sum{0};
+  std::thread consumer([&] {
+    int v = 0, n = 0;
+    while (n < 4000) {
+      if (ch.Get(&v, 1000)) { sum += v; ++n; }
+    }
+    done.Set();
+  });
+  std::vector<std::thread> producers;
+  for (int t = 0; t < 4; ++t) producers.emplace_back([&ch] { for (int i = 1; i <= 1000; ++i) ch.Put(i); });
+  for (auto& t : producers) t.join();
+  EXPECT(done.Wait(10000));
+  consumer.join();
+  EXPECT(sum.load() == 4LL * 1000 * 1001 / 2 && ch.Size() == 0);
+  int v = 0;
+  EXPECT(!ch.Get(&v, 10));                       // empty: the time runs out
+  std::printf("waiter / channel stress: sum %lld\n", sum.load());
+}
+
 static void OtlpStress() {
   OtlpExporter& ex = OtlpExporter::Instance();
   ex.Configure({{"instance", "stress"}}, 200);
@@ -207,6 +230,7 @@ int main() {
   SchedulerStress(1, 2);
   ControlPlaneStress();
   BatchLoopStress();
+  WaiterStress();
   OtlpStress();
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);

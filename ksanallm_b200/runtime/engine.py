@@ -50,8 +50,10 @@ class Request:
         self.seq_ids: List[int] = []
         self.status_code = 0
         self.status_message = ""
-        self.done = threading.Event()
-        self.stream_queue: Optional[queue.Queue] = queue.Queue() if stream else None
+        # native waiter / channel (condition variables outside the interpreter; same methods as threading.Event and
+        # queue.Queue), the interpreter's own primitives when the runtime library lacks them
+        self.done = ne.Waiter() if hasattr(ne, "Waiter") else threading.Event()
+        self.stream_queue = (ne.StreamChannel() if hasattr(ne, "StreamChannel") else queue.Queue()) if stream else None
         self.arrive = time.time()
         self.first_token_time: Optional[float] = None
         self.finish_time: Optional[float] = None

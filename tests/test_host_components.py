@@ -603,3 +603,42 @@ def test_clock_record_parser_and_breakdown_helpers():
     spec.loader.exec_module(sb)
     key = sb._class_key("ksana_gemm_smallm", (2, 140737488355328, 8192, None, 64, True, 1280, 0.5, 9999999999))
     assert key == "gemm_smallm(2,8192,64,1280)"          # pointers, floats, flags and huge values do not split classes
+
+
+def test_native_waiter_and_stream_channel_behave_like_event_and_queue():
+    """The request path's blocking primitives in C++: `Waiter` (set / is_set / wait with a timeout in seconds) and
+    `StreamChannel` (put / get with a timeout raising queue.Empty, FIFO order, any Python object as an item); a waiting
+    thread holds no interpreter lock, so other threads keep running meanwhile."""
+    import queue
+    import threading
+    import time
+    w = ne.Waiter()
+    assert not w.is_set()
+    t0 = time.perf_counter()
+    assert w.wait(0.05) is False and 0.04 < time.perf_counter() - t0 < 0.5
+    ticks = []
+    stop = threading.Event()
+
+    def spin():
+        while not stop.is_set():
+            ticks.append(1)
+            time.sleep(0.001)
+
+    th = threading.Thread(target=spin)
+    th.start()
+    threading.Timer(0.1, w.set).start()
+    assert w.wait(5.0) and w.is_set() and w.wait() is True
+    stop.set()
+    th.join()
+    assert len(ticks) > 20                      # the spinner ran while the main thread was blocked in wait()
+    w.clear()
+    assert not w.is_set()
+    c = ne.StreamChannel()
+    with pytest.raises(queue.Empty):
+        c.get(timeout=0.05)
+    items = [("step", [[1, 2], [3]]), {"k": "v"}, None, 7]
+    for it in items:
+        c.put(it)
+    assert c.qsize() == 4 and [c.get(timeout=1) for _ in items] == items and c.empty()
+    threading.Timer(0.05, lambda: c.put("late")).start()
+    assert c.get(timeout=5) == "late"
