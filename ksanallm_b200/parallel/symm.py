@@ -57,30 +57,42 @@ def _align(x: int, a: int = 256) -> int:
 
 
 class SymmetricComm:
+    @staticmethod
+    def layout(size: int, max_tokens: int, hidden: int) -> dict:
+        """Byte offsets of the regions of the symmetric buffer (identical on every rank) for a group of ``size`` ranks:
+        pure arithmetic, no device involved."""
+        rows_rs = (max_tokens + size - 1) // size
+        slot_rows = max(rows_rs, ONE_SHOT_ROWS)
+        slot_bytes = _align(slot_rows * hidden * 2)
+        off = FLAG_BYTES
+        slots_off = [off, off + size * slot_bytes]
+        off += 2 * size * slot_bytes
+        h_off = off; off += _align(max_tokens * hidden * 2)
+        y_off = off; off += _align(max_tokens * hidden * 2)
+        yq_off = off; off += _align(max_tokens * hidden)
+        scale_ld = _align(max_tokens, 4)
+        ys_off = off; off += _align((hidden // 128 + 1) * scale_ld * 4)
+        stage_off = off
+        stage_bytes = _align(max_tokens * hidden * 2)
+        off += stage_bytes
+        # sampling candidates of the vocabulary shards (values and token ids, fp32 / int32 words): a region of its
+        # own, so that nothing else ever writes it between a step's exchange and the next step's
+        cand_off = off
+        cand_words = 2 * min(max_tokens, 1024) * CAND_MAX_K
+        off += _align(cand_words * 4)
+        return dict(slot_rows=slot_rows, slot_bytes=slot_bytes, slots_off=slots_off, h_off=h_off, y_off=y_off, yq_off=yq_off,
+                    scale_ld=scale_ld, ys_off=ys_off, stage_off=stage_off, stage_bytes=stage_bytes, cand_off=cand_off,
+                    cand_words=cand_words, total=off)
+
     def __init__(self, group, rank: int, size: int, device, max_tokens: int = 16384, hidden: int = 8192):
         import torch.distributed._symmetric_memory as symm_mem
         self.group, self.rank, self.size, self.device = group, rank, size, torch.device(device)
         self.max_tokens, self.hidden = max_tokens, hidden
-        rows_rs = (max_tokens + size - 1) // size
-        self.slot_rows = max(rows_rs, ONE_SHOT_ROWS)
-        self.slot_bytes = _align(self.slot_rows * hidden * 2)
-        off = FLAG_BYTES
-        self.slots_off = [off, off + size * self.slot_bytes]
-        off += 2 * size * self.slot_bytes
-        self.h_off = off; off += _align(max_tokens * hidden * 2)
-        self.y_off = off; off += _align(max_tokens * hidden * 2)
-        self.yq_off = off; off += _align(max_tokens * hidden)
-        self.scale_ld = _align(max_tokens, 4)
-        self.ys_off = off; off += _align((hidden // 128 + 1) * self.scale_ld * 4)
-        self.stage_off = off
-        self.stage_bytes = _align(max_tokens * hidden * 2)
-        off += self.stage_bytes
-        # sampling candidates of the vocabulary shards (values and token ids, fp32 / int32 words): a region of its
-        # own, so that nothing else ever writes it between a step's exchange and the next step's
-        self.cand_off = off
-        self.cand_words = 2 * min(max_tokens, 1024) * CAND_MAX_K
-        off += _align(self.cand_words * 4)
-        self.total = off
+        lay = self.layout(size, max_tokens, hidden)
+        self.slot_rows, self.slot_bytes, self.slots_off = lay["slot_rows"], lay["slot_bytes"], lay["slots_off"]
+        self.h_off, self.y_off, self.yq_off, self.ys_off = lay["h_off"], lay["y_off"], lay["yq_off"], lay["ys_off"]
+        self.scale_ld, self.stage_off, self.stage_bytes = lay["scale_ld"], lay["stage_off"], lay["stage_bytes"]
+        self.cand_off, self.cand_words, self.total = lay["cand_off"], lay["cand_words"], lay["total"]
         self.buf = symm_mem.empty(self.total, dtype=torch.uint8, device=self.device)
         self.buf.zero_()
         torch.cuda.synchronize(self.device)

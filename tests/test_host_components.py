@@ -642,3 +642,31 @@ def test_native_waiter_and_stream_channel_behave_like_event_and_queue():
     assert c.qsize() == 4 and [c.get(timeout=1) for _ in items] == items and c.empty()
     threading.Timer(0.05, lambda: c.put("late")).start()
     assert c.get(timeout=5) == "late"
+
+
+@pytest.mark.parametrize("size,max_tokens,hidden", [(1, 512, 1024), (2, 512, 1024), (4, 16384, 8192), (8, 16384, 8192),
+                                                    (8, 64, 8192), (3, 1000, 5120)])
+def test_symmetric_buffer_layout_for_every_group_size(size, max_tokens, hidden):
+    """Layout arithmetic of the peer-mapped buffer (no device needed): regions do not overlap, every region starts on
+    a 256-byte boundary (16-byte vector and multimem accesses), a receive slot holds a rank's share of a large batch
+    and every row of a decode-sized one, and the two slot sets hold one slot per rank each."""
+    from ksanallm_b200.parallel.symm import CAND_MAX_K, FLAG_BYTES, ONE_SHOT_ROWS, SymmetricComm
+    lay = SymmetricComm.layout(size, max_tokens, hidden)
+    row = hidden * 2
+    assert lay["slot_rows"] >= ONE_SHOT_ROWS and lay["slot_rows"] * size >= max_tokens
+    assert lay["slot_bytes"] >= lay["slot_rows"] * row
+    regions = [(0, FLAG_BYTES)]
+    for base in lay["slots_off"]:
+        regions += [(base + r * lay["slot_bytes"], lay["slot_bytes"]) for r in range(size)]
+    regions += [(lay["h_off"], max_tokens * row), (lay["y_off"], max_tokens * row), (lay["yq_off"], max_tokens * hidden),
+                (lay["ys_off"], (hidden // 128 + 1) * lay["scale_ld"] * 4), (lay["stage_off"], lay["stage_bytes"]),
+                (lay["cand_off"], lay["cand_words"] * 4)]
+    regions.sort()
+    for (a, n), (b, _) in zip(regions, regions[1:]):
+        assert a + n <= b, (a, n, b)
+    assert regions[-1][0] + regions[-1][1] <= lay["total"]
+    assert all(start % 256 == 0 for start, _ in regions)
+    assert lay["scale_ld"] >= max_tokens and lay["scale_ld"] % 4 == 0
+    assert lay["cand_words"] >= 2 * min(max_tokens, 1024) * CAND_MAX_K
+    # a partial product of all rows fits the slot area of one parity (pull mode writes it there in one piece)
+    assert size * lay["slot_bytes"] >= max_tokens * row
