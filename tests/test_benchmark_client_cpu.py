@@ -152,6 +152,19 @@ def test_command_line_clients_against_live_server(server, capsys):
             assert mod.main(["--host", "127.0.0.1", "--port", str(server), "--prompt", "hello there"] + extra) == 0
         out = capsys.readouterr().out
         assert ("Answer 0" in out) if name == "api_client" else ("[" in out)
+    # the concurrent example client beside the 7B sample configuration (examples/llama7b/serving_client.py)
+    spec = importlib.util.spec_from_file_location("llama7b_client", os.path.join(root, "examples", "llama7b", "serving_client.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    for extra in ([], ["--stream"]):
+        old_argv = sys.argv
+        sys.argv = ["serving_client.py", "--port", str(server), "--max_new_tokens", "4", "--prompt", "hello", "--prompt", "abc"] + extra
+        try:
+            mod.main()
+        finally:
+            sys.argv = old_argv
+        out = capsys.readouterr().out
+        assert "2 requests in" in out and "request failed" not in out and "HTTP " not in out
 
 
 def test_prompt_sets_and_prefix_cache_reader(tmp_path):

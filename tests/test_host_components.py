@@ -348,13 +348,14 @@ def test_example_configurations_load():
     import glob
     import os
     root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
-    files = sorted(glob.glob(os.path.join(root, "*.yaml")))
-    assert len(files) >= 5
+    files = sorted(glob.glob(os.path.join(root, "*.yaml")) + glob.glob(os.path.join(root, "*", "*.yaml")))
+    assert len(files) >= 6
     seen = {}
     for f in files:
         c = cfgmod.load_yaml_config(f)
         seen[os.path.basename(f)] = c
         assert c.batch_scheduler.max_batch_size >= 1 and c.block_manager.block_token_num in (16, 32, 64, 128)
+    assert seen["ksana_llm.yaml"].batch_scheduler.max_batch_size >= 1
     assert seen["ksana_llm_70b_fp8_tp8.yaml"].global_.tensor_para_size == 8
     assert seen["ksana_llm_70b_fp8_tp8.yaml"].quantization.weight_quant_method == "fp8_block"
     assert seen["ksana_llm_pipeline.yaml"].global_.pipeline_para_size == 2
