@@ -291,6 +291,9 @@ def time_cases(names):
 
 
 def main(argv):
+    unknown = [a for a in argv if a != "--time" and a not in CASES]
+    if unknown:
+        raise SystemExit(f"unknown case(s) {unknown}; cases: {' '.join(CASES)}")
     if argv and argv[0] == "--time":
         return time_cases(argv[1:] or list(CASES))
     names = argv or list(CASES)

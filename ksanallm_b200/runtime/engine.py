@@ -405,6 +405,7 @@ class LLMEngine:
         self._lock = threading.Lock()
         self._wake = threading.Condition()
         self._native_loop = None
+        self._exit_hook = False
         self._loop_bound = False
         self._thread: Optional[threading.Thread] = None
         self._stop = False
@@ -929,6 +930,14 @@ class LLMEngine:
         if os.environ.get("KSANA_NATIVE_LOOP", "1") != "0" and hasattr(ne, "BatchLoop"):
             self._native_loop = ne.BatchLoop()
             self._native_loop.start(self._loop_step, self._loop_idle, self._loop_error)
+            if not self._exit_hook:
+                # a native thread must not ask for the interpreter lock while the interpreter shuts down: a process
+                # that ends without stop() joins the loop first
+                import atexit
+                import weakref
+                ref = weakref.ref(self)
+                atexit.register(lambda: ref() is not None and ref().stop())
+                self._exit_hook = True
             return
         self._thread = threading.Thread(target=self._loop, name="ksana-engine", daemon=True)
         self._thread.start()
@@ -1024,9 +1033,9 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ conveniences
     def generate(self, prompts: List[List[int]], sampling=None, timeout: Optional[float] = None) -> List[Request]:
-        """Offline batch generation on the calling thread (no background loop needed)."""
+        """Offline batch generation: steps on the calling thread, or waits for the background loop where one runs."""
         reqs = [self.add_request(p, _clone_cfg(sampling)) for p in prompts]
-        if self._thread is None:
+        if self._thread is None and self._native_loop is None:
             deadline = time.time() + timeout if timeout else None
             while not all(r.done.is_set() for r in reqs):
                 if not self.step() and self.scheduler.idle():

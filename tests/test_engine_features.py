@@ -395,3 +395,28 @@ def test_streaming_under_pipelined_steps_delivers_every_token_in_order():
     # every piece carries the tokens so far (or the new ones): the last piece, or their concatenation, is the answer
     flat = seen[-1] if len(seen[-1]) == len(want) else [t for piece in seen for t in piece]
     assert flat == want and req.outputs[0].tokens == want
+
+
+@pytest.mark.parametrize("native_loop", ["1", "0"])
+def test_generate_on_a_started_engine_waits_for_the_loop(monkeypatch, native_loop):
+    """``generate`` on an engine whose background loop runs (native thread or Python thread) hands its requests to that
+    loop instead of stepping on the calling thread beside it; tokens equal those of an engine stepped by the caller."""
+    monkeypatch.setenv("KSANA_NATIVE_LOOP", native_loop)
+    prompts = [[5, 6, 7, 8, 9], [3, 1, 4, 1, 5, 9, 2, 6]]
+    want = [r.outputs[0].tokens for r in tiny_engine().generate(prompts, sampling(max_new_tokens=12, ignore_eos=True))]
+    eng = tiny_engine()
+    eng.start()
+    try:
+        assert (eng._native_loop is not None) == (native_loop == "1")
+        stepped_by = set()
+        real_step = eng.step
+
+        def step():
+            stepped_by.add(threading.get_ident())
+            return real_step()
+        eng.step = step
+        got = [r.outputs[0].tokens for r in eng.generate(prompts, sampling(max_new_tokens=12, ignore_eos=True), timeout=60)]
+    finally:
+        eng.stop()
+    assert got == want
+    assert threading.get_ident() not in stepped_by and len(stepped_by) == 1
