@@ -118,6 +118,7 @@ __global__ void moe_align_kernel(const int* __restrict__ topk_ids, int* __restri
   __syncthreads();
   for (int i = threadIdx.x; i < TK; i += blockDim.x) {
     const int e = topk_ids[i];
+    if (e == -1) continue;      // a choice that lives on another rank (all-to-all dispatch sends restricted choices)
     if (e < 0 || e >= E) { guard_report(err, kGuardExpert, e); continue; }
     if (e >= expert_lo && e < expert_hi) atomicAdd(&cnt[e], 1);
   }
