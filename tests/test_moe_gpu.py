@@ -126,3 +126,29 @@ def test_moe_block_with_nvfp4_experts_matches_cpu_statement():
     native.check_err_flag(DEV)
     want = moe_partial(cpu, mw_c, x).float()
     assert rel_err(got, want) < 0.12, rel_err(got, want)      # e2m1 bucket flips of the second GEMM's input
+
+
+def test_moe_block_with_restricted_choices_matches_cpu_statement():
+    """Routing decided elsewhere with some choices struck out (id -1, weight 0: held by another rank under all-to-all
+    dispatch): the GPU block computes only the remaining ones, raises no guard, and agrees with the CPU statement."""
+    from ksanallm_b200.models.moe import moe_partial, route
+    from ksanallm_b200.models.weights import RandomSource, build_model
+    cfg = ModelConfig(model_type="mixtral", hidden_size=512, num_layers=1, num_heads=4, num_kv_heads=2, head_dim=128,
+                      intermediate_size=512, moe_intermediate_size=256, vocab_size=1000, num_experts=8,
+                      num_experts_per_tok=2, max_position_embeddings=256, max_token_len=256)
+    gpu = build_model(cfg, RandomSource(seed=5, std=0.05), device=DEV, dtype=torch.bfloat16)
+    cpu = build_model(cfg, RandomSource(seed=5, std=0.05), device="cpu", dtype=torch.bfloat16)
+    mw_g, mw_c = gpu.layers[0].moe, cpu.layers[0].moe
+    x = torch.randn(150, 512, dtype=torch.bfloat16) * 0.5
+    ids, w = route(gpu, mw_g, x.to(DEV))
+    keep = ids < 4                                   # as if experts 4..7 lived on another rank
+    ids_r = torch.where(keep, ids, torch.full_like(ids, -1)).contiguous()
+    w_r = torch.where(keep, w, torch.zeros_like(w)).contiguous()
+    assert bool((ids_r == -1).any()) and bool(keep.any())
+    got = moe_partial(gpu, mw_g, x.to(DEV), shared=False, routing=(ids_r, w_r)).float().cpu()
+    torch.cuda.synchronize()
+    native.check_err_flag(DEV)
+    want = moe_partial(cpu, mw_c, x, shared=False, routing=(ids_r.cpu(), w_r.cpu())).float()
+    assert rel_err(got, want) < 2e-2, rel_err(got, want)
+    rows_without = (~keep).all(dim=1).cpu()
+    assert float(got[rows_without].abs().max()) == 0.0 if bool(rows_without.any()) else True
