@@ -79,8 +79,12 @@ def tp_check(rank, world, dev):
             dist.barrier()
         for phase in ("prefill", "decode"):
             a, b = logits[("fused", phase)], logits[("nccl", phase)]
-            out[f"{quant}_{phase}"] = round(float((a - b).norm() / b.norm().clamp_min(1e-12)), 5)
-    return out
+            out[f"{quant}_{phase}"] = float((a - b).norm() / b.norm().clamp_min(1e-12))
+    # the largest error over the ranks, so that every rank reads the same numbers and decides alike
+    keys = sorted(out)
+    worst = torch.nan_to_num(torch.tensor([out[k] for k in keys], dtype=torch.float32, device=dev), nan=1e30, posinf=1e30)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    return {k: round(float(v), 5) for k, v in zip(keys, worst.tolist())}
 
 
 TP_CHECK_LIMITS = {"bf16": 3e-2, "fp8_block": 0.15}
@@ -232,7 +236,7 @@ def main():
         tp_dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         torch.cuda.set_device(tp_dev)
         def beyond(errs):
-            return any(v > TP_CHECK_LIMITS[k.rsplit("_", 1)[0]] for k, v in errs.items())
+            return any(not (v <= TP_CHECK_LIMITS[k.rsplit("_", 1)[0]]) for k, v in errs.items())
 
         tp_numerics = tp_check(rank, world, tp_dev)
         if beyond(tp_numerics) and args.comm == "fused" and os.environ.get("KSANA_PUSH") != "0":
