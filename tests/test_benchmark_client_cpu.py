@@ -189,6 +189,14 @@ def test_prompt_sets_and_prefix_cache_reader(tmp_path):
         reader.load_prompts(str(bad))
     qs = bt.read_prompts(os.path.join(bench_dir, "benchmark_input.csv"), 0, 0, False, 0)
     assert len(qs) == 32 and all(q.startswith("Think about") for q in qs)
+    # the chat-style set is what its generator produces (same seed, bit for bit), long-tailed in length
+    spec = importlib.util.spec_from_file_location("make_chat_prompts", os.path.join(bench_dir, "make_chat_prompts.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    chat = bt.read_prompts(os.path.join(bench_dir, "chat_prompts_500.csv"), 0, 0, False, 0)
+    assert chat == gen.build(500, 0)
+    lens = sorted(len(q) for q in chat)
+    assert lens[250] < 400 and lens[-1] > 3000 and lens[0] > 10
     ec = load_yaml_config(os.path.join(bench_dir, "prefix_cache_config.yaml"))
     assert ec.batch_scheduler.enable_auto_prefix_cache and ec.batch_scheduler.max_batch_size == 256
 
