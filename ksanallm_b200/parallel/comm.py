@@ -54,9 +54,11 @@ class TPComm:
     # ---- fused-with-compute entry points used by the model code
     def row_parallel_linear(self, x, W, h: torch.Tensor) -> torch.Tensor:
         """h += all_reduce(x W^T). Baseline: GEMM, library all-reduce, add. Fused backend: the partial
-        product is written into the symmetric buffer and one kernel reduces over peers and adds the residual."""
-        if self.symm is not None:
-            return self.symm.row_parallel_norm(x, W, h, None)[0] if h.shape[0] <= 16 else self._rp_nccl(x, W, h)
+        product is written into the symmetric buffer (or pushed to the peers by the GEMM's epilogue) and one kernel
+        reduces over the ranks and adds the residual, for the batch sizes that every rank reduces itself; larger
+        batches outside the fused forward (whose residual stream lives in the symmetric buffer) use the library."""
+        if self.symm is not None and self.symm.one_shot(h.shape[0]) and h.is_contiguous():
+            return self.symm.row_parallel_norm(x, W, h, None)[0]
         return self._rp_nccl(x, W, h)
 
     def _rp_nccl(self, x, W, h):
