@@ -194,6 +194,7 @@ def load_yaml_config(path_or_dict) -> EngineConfig:
 @dataclass
 class ModelConfig:
     model_type: str = "llama"
+    hf_model_type: str = ""        # model_type as config.json spells it (names the optional weight map file)
     hidden_size: int = 4096
     num_layers: int = 32
     num_heads: int = 32
@@ -292,7 +293,36 @@ def parse_model_max_length(hf: dict, max_pos: int) -> int:
     return max_pos
 
 
-def model_config_from_hf(hf: dict, generation: Optional[dict] = None) -> ModelConfig:
+def resolve_architecture(model_type: str, model_dir: Optional[str] = None) -> str:
+    """Model family that serves a config.json ``model_type``: a known name, else a family whose name the type
+    contains (case-insensitive, e.g. "codellama" -> llama), else Llama when a weight map
+    ``<model_type>_weight_map.json`` exists for it (next to the checkpoint or in the package: a Llama-shaped model
+    whose tensors only carry other names), else an error (src/ksana_llm/runtime/model_instance.cpp:42-86)."""
+    if model_type in _ARCH_ALIASES:
+        return _ARCH_ALIASES[model_type]
+    low = model_type.lower()
+    for part, arch in (("llama", "llama"), ("qwen2_moe", "qwen2_moe"), ("qwen2_vl", "qwen2_vl"), ("qwen", "qwen"),
+                       ("baichuan", "baichuan"), ("chatglm", "chatglm"), ("gpt", "gpt"), ("fairseq-transformer", "gpt"),
+                       ("mixtral", "mixtral"), ("deepseek", "deepseek_v3")):
+        if part in low:
+            return arch
+    if find_weight_map(low, model_dir) or find_weight_map(model_type, model_dir):
+        return "llama"
+    raise ValueError(f"Model type {model_type} is not supported (no <model_type>_weight_map.json found for it either).")
+
+
+def find_weight_map(model_type: str, model_dir: Optional[str] = None) -> Optional[str]:
+    """Path of ``<model_type>_weight_map.json``: the checkpoint directory first, then the package's weight_map folder
+    (src/ksana_llm/utils/optional_file.h:23-61)."""
+    name = f"{model_type}_weight_map.json"
+    for folder in ([model_dir] if model_dir else []) + [os.path.join(os.path.dirname(os.path.abspath(__file__)), "weight_map")]:
+        path = os.path.join(folder, name)
+        if os.path.exists(path):
+            return path
+    return None
+
+
+def model_config_from_hf(hf: dict, generation: Optional[dict] = None, model_dir: Optional[str] = None) -> ModelConfig:
     tc = hf.get("text_config")
     if isinstance(tc, dict):
         # multimodal config.json files of newer exports keep the language model's fields under text_config
@@ -314,8 +344,8 @@ def model_config_from_hf(hf: dict, generation: Optional[dict] = None) -> ModelCo
         elif hf.get("rope_scaling") is None and rp.get("mrope_section"):
             hf["rope_scaling"] = {"mrope_section": rp["mrope_section"]}
     mt = hf.get("model_type", "llama")
-    arch = _ARCH_ALIASES.get(mt, mt)
-    c = ModelConfig(model_type=arch)
+    arch = resolve_architecture(mt, model_dir)
+    c = ModelConfig(model_type=arch, hf_model_type=mt)
     if arch == "gpt":
         c.hidden_size = hf.get("n_embd", hf.get("hidden_size", hf.get("decoder_embed_dim", 768)))
         c.num_layers = hf.get("n_layer", hf.get("num_hidden_layers", hf.get("decoder_layers", 12)))
@@ -426,7 +456,7 @@ def load_model_config(model_dir: str) -> ModelConfig:
     if os.path.exists(gpath):
         with open(gpath, "r", encoding="utf-8") as f:
             gen = json.load(f)
-    return model_config_from_hf(hf, gen)
+    return model_config_from_hf(hf, gen, model_dir)
 
 
 def load_kv_scales(path: str, num_layers: int) -> List[List[float]]:

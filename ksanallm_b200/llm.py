@@ -160,7 +160,7 @@ class LLM:
                 from .models.gguf import GGUFSource
                 source = GGUFSource(ggufs[0])
             else:
-                source = CheckpointSource(self.engine_cfg.model_dir, model_cfg.model_type)
+                source = CheckpointSource(self.engine_cfg.model_dir, model_cfg.model_type, model_cfg.hf_model_type)
         else:
             source = weights
         kv_path = os.path.join(self.engine_cfg.model_dir or ".", "kv_cache_scales.json")

@@ -66,11 +66,20 @@ def _python_replacement(repl: str) -> str:
     return out.replace("\0", "$")
 
 
-def load_weight_map(model_type: str, path: Optional[str] = None) -> List[tuple]:
-    """Rules of ``<model_type>_weight_map.json`` (or of an explicit file, e.g. one written for the reference engine):
-    an ordered list of (compiled pattern, replacement)."""
-    path = path or os.path.join(WEIGHT_MAP_DIR, f"{model_type}_weight_map.json")
-    if not os.path.exists(path):
+def load_weight_map(model_type: str, path: Optional[str] = None, model_dir: Optional[str] = None,
+                    hf_model_type: str = "") -> List[tuple]:
+    """Rules of a weight map: an ordered list of (compiled pattern, replacement). ``path`` names a file outright (e.g.
+    one written for the reference engine); otherwise the first of ``<hf_model_type>_weight_map.json`` (config.json's
+    own spelling of the type) and ``<model_type>_weight_map.json`` (the family) that exists, looked for next to the
+    checkpoint before the package's folder, so that a map shipped with a model wins
+    (src/ksana_llm/utils/optional_file.h:23-61)."""
+    from ..config import find_weight_map
+    if path is None:
+        for name in ([hf_model_type] if hf_model_type and hf_model_type != model_type else []) + [model_type]:
+            path = find_weight_map(name, model_dir)
+            if path:
+                break
+    if not path or not os.path.exists(path):
         return []
     with open(path, "r", encoding="utf-8") as f:
         return [(re.compile(k), _python_replacement(v)) for k, v in json.load(f).items()]
@@ -196,8 +205,8 @@ class CheckpointSource(_PackedW4Mixin, _Fp8Mixin):
     """Tensors of a Hugging Face checkpoint directory (``*.safetensors`` preferred, then ``*.bin`` /
     ``*.pt``), renamed to canonical names through the optional regex weight map."""
 
-    def __init__(self, model_dir: str, model_type: str = "llama"):
-        self.rules = load_weight_map(model_type)
+    def __init__(self, model_dir: str, model_type: str = "llama", hf_model_type: str = ""):
+        self.rules = load_weight_map(model_type, model_dir=model_dir, hf_model_type=hf_model_type)
         self.index: Dict[str, tuple] = {}
         self._bin_cache: Dict[str, dict] = {}
         st = sorted(glob.glob(os.path.join(model_dir, "*.safetensors")))

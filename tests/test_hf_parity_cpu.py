@@ -1,5 +1,8 @@
 """Architecture parity with the Hugging Face implementations: tiny randomly initialised HF models, their state
 dicts loaded through the weight maps, logits compared on CPU in fp32 (prefill of one sequence)."""
+import os
+import re
+
 import pytest
 import torch
 
@@ -367,3 +370,59 @@ def test_checkpoint_directories_on_disk(tmp_path, layout):
         want = hf(torch.tensor([tokens])).logits[0].float()
     got = model.forward(step)
     assert float((got - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_unknown_model_type_with_its_own_weight_map(tmp_path):
+    """A Llama-shaped checkpoint under a model_type nobody knows, with its tensors under other names and a
+    ``<model_type>_weight_map.json`` (``$N`` groups, as written for the reference) next to it: served as Llama with
+    Hugging Face Llama's logits. Without the map the type is refused; a map next to the checkpoint wins over the
+    package's map of the same name."""
+    import json
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from ksanallm_b200.config import find_weight_map, load_model_config, resolve_architecture
+    from ksanallm_b200.models.weights import CheckpointSource, load_weight_map
+    c = LlamaConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=128,
+                    vocab_size=200, max_position_embeddings=128, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    hf = _init(LlamaForCausalLM(c)).eval()
+    d = str(tmp_path)
+    cfg = c.to_dict()
+    cfg["model_type"] = "my_house_model"
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    renamed = {}
+    for k, v in hf.state_dict().items():
+        k = k.replace("model.embed_tokens.", "backbone.tok.").replace("model.norm.", "backbone.final_norm.")
+        k = re.sub(r"^model\.layers\.(\d+)\.", r"backbone.blocks.\1.", k)
+        renamed[k] = v.clone()
+    torch.save(renamed, os.path.join(d, "pytorch_model.bin"))
+    with pytest.raises(ValueError, match="not supported"):
+        load_model_config(d)
+    with open(os.path.join(d, "my_house_model_weight_map.json"), "w") as f:
+        json.dump({r"^backbone\.tok\.(.*)$": "model.embed_tokens.$1", r"^backbone\.final_norm\.(.*)$": "model.norm.$1",
+                   r"^backbone\.blocks\.(\d+)\.(.*)$": "model.layers.$1.$2"}, f)
+    mc = load_model_config(d)
+    assert mc.model_type == "llama" and mc.hf_model_type == "my_house_model"
+    mc.max_token_len = 128
+    model = build_model(mc, CheckpointSource(d, mc.model_type, mc.hf_model_type), device="cpu", dtype=torch.float32)
+    torch.manual_seed(0)
+    tokens = torch.randint(3, 200, (17,)).tolist()
+    T = len(tokens)
+    model.allocate_kv_cache(8, 16)
+    ar = torch.arange(T, dtype=torch.int32)
+    step = StepInput(torch.tensor(tokens, dtype=torch.int32), ar, ar.clone(), torch.tensor([0, T], dtype=torch.int32),
+                     torch.tensor([T], dtype=torch.int32), torch.arange(8, dtype=torch.int32).view(1, 8),
+                     num_multi=1, num_single=0, num_tokens=T, num_multi_tokens=T, max_q_len=T, max_kv_len=T)
+    with torch.no_grad():
+        want = hf(torch.tensor([tokens])).logits[0].float()
+    assert float((model.forward(step) - want).abs().max()) < 2e-4 * max(1.0, float(want.abs().max()))
+    # family by containment, and the search order of the map file
+    assert resolve_architecture("CodeLlama") == "llama" and resolve_architecture("gpt_bigcode") == "gpt"
+    assert find_weight_map("qwen").endswith(os.path.join("weight_map", "qwen_weight_map.json"))
+    with open(os.path.join(d, "qwen_weight_map.json"), "w") as f:
+        json.dump({"^a$": "b"}, f)
+    assert find_weight_map("qwen", d) == os.path.join(d, "qwen_weight_map.json")
+    assert len(load_weight_map("qwen", model_dir=d)) == 1 and len(load_weight_map("qwen")) > 1
+    # config.json's own spelling names the file before the family does
+    with open(os.path.join(d, "gpt2_weight_map.json"), "w") as f:
+        json.dump({"^x$": "y", "^z$": "w"}, f)
+    assert len(load_weight_map("gpt", model_dir=d, hf_model_type="gpt2")) == 2
