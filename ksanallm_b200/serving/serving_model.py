@@ -164,8 +164,15 @@ class ServingModel:
             ne.metrics_set_attributes(dict(prof.attributes))
         # http:// export targets speak OTLP/HTTP with JSON bodies to a collector (/v1/traces, /v1/metrics)
         ne.otlp_configure({str(k): str(v) for k, v in (prof.attributes or {}).items()}, int(prof.export_timeout_millis))
+        stat_file = os.environ.get("KLLM_STAT_FILE", "")
         if prof.metrics_export_url:
             ne.metrics_start_export(prof.metrics_export_url, prof.export_interval_millis)
+        elif stat_file:
+            # no collector configured: one JSON line of all metrics per interval appended to the statistics file
+            # (the variable names it as for the reference's profile writer, src/ksana_llm/profiler/writer.cpp:10-19)
+            if os.path.dirname(stat_file):
+                os.makedirs(os.path.dirname(stat_file), exist_ok=True)
+            ne.metrics_start_export(stat_file, prof.export_interval_millis)
         if prof.trace_export_url:
             ne.span_set_sink(prof.trace_export_url)
         from ..utils import version_reporter

@@ -96,3 +96,30 @@ def test_metrics_endpoint_and_sampling_mapping(client):
     assert c.topk == 1 and c.max_new_tokens == 1024
     c = make_sampling_config({"top_k": 40, "do_sample": True, "top_p": 0.9, "stop_token_ids": [2]})
     assert c.topk == 40 and abs(c.topp - 0.9) < 1e-6 and c.stop_token_ids == [2]
+
+
+def test_statistics_file_receives_metric_lines(tmp_path, monkeypatch):
+    """With KLLM_STAT_FILE set and no collector configured, the metrics go to that file: one JSON line per export
+    interval, naming the request counters."""
+    import time
+    stat = tmp_path / "stats" / "ksana_stat.log"
+    monkeypatch.setenv("KLLM_STAT_FILE", str(stat))
+    tok = ByteTokenizer()
+    ec = EngineConfig()
+    ec.batch_scheduler.max_batch_size = 4
+    ec.batch_scheduler.max_token_len = 64
+    ec.block_manager.device_blocks_num = 32
+    ec.profiler.export_interval_millis = 50
+    llm = LLM(ec, tiny_model_cfg(), weights="random", device="cpu", dtype=torch.float32, tokenizer=tok)
+    model = ServingModel("", llm=llm, tokenizer=tok)
+    model.init_serving()
+    try:
+        req = llm.engine.add_request(tok.encode("hello"), make_sampling_config({"max_new_tokens": 3, "ignore_eos": True}))
+        assert req.done.wait(30)
+        deadline = time.time() + 10
+        while time.time() < deadline and not (stat.exists() and stat.read_text().strip()):
+            time.sleep(0.05)
+    finally:
+        model.shutdown()
+    lines = [json.loads(x) for x in stat.read_text().splitlines() if x.strip()]
+    assert lines and any("forward_req_total_num" in json.dumps(x) for x in lines)
