@@ -22,6 +22,7 @@ import yaml
 from fastapi import FastAPI, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, Response, StreamingResponse
 
+from ..utils import logger
 from ..utils import native_engine as ne
 from .plugin import PluginConfig
 from .serving_model import EndpointConfig, ServingModel
@@ -73,8 +74,33 @@ def prepare_config(args):
 
 
 def load_tokenizer(tokenizer_dir: str):
-    from transformers import AutoTokenizer
-    return AutoTokenizer.from_pretrained(tokenizer_dir, trust_remote_code=True)
+    """Tokenizer of a checkpoint directory, by the reference server's rules (src/ksana_llm/python/serving_server.py:381-390):
+    a directory whose tokenizer_config.json names ``LlamaTokenizer`` gets that class itself (the automatic choice may
+    convert it to a fast tokenizer that splits some inputs differently); a directory with a ``preprocessor_config.json``
+    (multimodal checkpoints) is loaded as a processor, whose text tokenizer serves the server while the processor
+    stays reachable as ``tokenizer.processor`` for plug-ins; everything else through ``AutoTokenizer``."""
+    import transformers
+    cfg = {}
+    cfg_path = os.path.join(tokenizer_dir, "tokenizer_config.json")
+    if os.path.exists(cfg_path):
+        with open(cfg_path, "r", encoding="utf-8") as f:
+            cfg = json.load(f)
+    tok = None
+    if cfg.get("tokenizer_class", "") == "LlamaTokenizer":
+        try:
+            tok = transformers.LlamaTokenizer.from_pretrained(tokenizer_dir)
+        except Exception as e:      # noqa: BLE001 - e.g. no sentencepiece model in the directory: the automatic choice still works
+            logger.warning(f"LlamaTokenizer could not be loaded from {tokenizer_dir} ({e}); using AutoTokenizer")
+    elif os.path.exists(os.path.join(tokenizer_dir, "preprocessor_config.json")):
+        proc = transformers.AutoProcessor.from_pretrained(tokenizer_dir, trust_remote_code=True)
+        tok = getattr(proc, "tokenizer", proc)
+        if tok is not proc:
+            tok.processor = proc
+    if tok is None:
+        tok = transformers.AutoTokenizer.from_pretrained(tokenizer_dir, trust_remote_code=True)
+    if not getattr(tok, "is_fast", True):
+        logger.warning(f"using a slow tokenizer for {tokenizer_dir}: tokenisation may take a noticeable share of the request time")
+    return tok
 
 
 def _sampling_dict(sampling_config: Optional[dict], tokenizer) -> dict:
@@ -199,7 +225,6 @@ def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExec
 
 def main(argv=None):
     args = args_config(argv)
-    from ..utils import logger
     logger.install_logging_handler()          # uvicorn / serving records go to the engine's log sink (KLLM_LOG_FILE)
     logger.info(f"serving_server starting: config {args.config_file}, endpoint {args.endpoint} on {args.host}:{args.port}")
     tokenizer = load_tokenizer(args.tokenizer_dir) if args.tokenizer_dir and os.path.isdir(args.tokenizer_dir) else None

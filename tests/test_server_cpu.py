@@ -123,3 +123,40 @@ def test_statistics_file_receives_metric_lines(tmp_path, monkeypatch):
         model.shutdown()
     lines = [json.loads(x) for x in stat.read_text().splitlines() if x.strip()]
     assert lines and any("forward_req_total_num" in json.dumps(x) for x in lines)
+
+
+def test_tokenizer_loading_rules(tmp_path, monkeypatch):
+    """Which loader a tokenizer directory gets: the class named LlamaTokenizer itself (with the automatic choice as a
+    fallback), a processor for multimodal checkpoints (its text tokenizer serves, the processor stays reachable),
+    AutoTokenizer otherwise."""
+    import transformers
+    from ksanallm_b200.serving.serving_server import load_tokenizer
+    calls = []
+
+    class Tok:
+        is_fast = True
+
+    class Proc:
+        def __init__(self):
+            self.tokenizer = Tok()
+
+    monkeypatch.setattr(transformers.AutoTokenizer, "from_pretrained", classmethod(lambda cls, d, **kw: calls.append(("auto", kw)) or Tok()))
+    monkeypatch.setattr(transformers.AutoProcessor, "from_pretrained", classmethod(lambda cls, d, **kw: calls.append(("processor", kw)) or Proc()))
+    monkeypatch.setattr(transformers.LlamaTokenizer, "from_pretrained", classmethod(lambda cls, d, **kw: calls.append(("llama", kw)) or Tok()))
+    plain = tmp_path / "plain"
+    plain.mkdir()
+    assert isinstance(load_tokenizer(str(plain)), Tok) and calls[-1] == ("auto", {"trust_remote_code": True})
+    llama = tmp_path / "llama"
+    llama.mkdir()
+    (llama / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "LlamaTokenizer"}))
+    assert isinstance(load_tokenizer(str(llama)), Tok) and calls[-1][0] == "llama"
+
+    def broken(cls, d, **kw):
+        raise OSError("no sentencepiece model")
+    monkeypatch.setattr(transformers.LlamaTokenizer, "from_pretrained", classmethod(broken))
+    assert isinstance(load_tokenizer(str(llama)), Tok) and calls[-1][0] == "auto"
+    vl = tmp_path / "vl"
+    vl.mkdir()
+    (vl / "preprocessor_config.json").write_text("{}")
+    tok = load_tokenizer(str(vl))
+    assert isinstance(tok, Tok) and isinstance(tok.processor, Proc) and calls[-1][0] == "processor"
