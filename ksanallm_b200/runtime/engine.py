@@ -42,8 +42,13 @@ class SequenceOutput:
 class Request:
     """Python-side request record: outputs per sibling sequence, completion / streaming signalling."""
 
-    def __init__(self, req_id: int, prompt: List[int], cfg, n_seqs: int, stream: bool = False):
+    def __init__(self, req_id: int, prompt: List[int], cfg, n_seqs: int, stream: bool = False, listener=None):
         self.req_id = req_id
+        # ``listener(item)``: called on the engine's loop thread with every streamed piece (streaming requests) and
+        # with None on completion, in place of a queue that some thread would have to block on (the HTTP front hands
+        # the items to its event loop). It must not block.
+        self.listener = listener
+        self.stream = stream
         self.prompt = list(prompt)
         self.cfg = cfg
         self.outputs = [SequenceOutput() for _ in range(n_seqs)]
@@ -53,7 +58,8 @@ class Request:
         # native waiter / channel (condition variables outside the interpreter; same methods as threading.Event and
         # queue.Queue), the interpreter's own primitives when the runtime library lacks them
         self.done = ne.Waiter() if hasattr(ne, "Waiter") else threading.Event()
-        self.stream_queue = (ne.StreamChannel() if hasattr(ne, "StreamChannel") else queue.Queue()) if stream else None
+        self.stream_queue = ((ne.StreamChannel() if hasattr(ne, "StreamChannel") else queue.Queue())
+                             if (stream and listener is None) else None)
         self.arrive = time.time()
         self.first_token_time: Optional[float] = None
         self.finish_time: Optional[float] = None
@@ -69,6 +75,17 @@ class Request:
 
     def all_finished(self) -> bool:
         return all(o.finished for o in self.outputs)
+
+    def emit(self, item) -> None:
+        """A streamed piece (("step", tokens of every output so far)) or the end marker (None) to whoever follows
+        this request."""
+        if self.stream_queue is not None:
+            self.stream_queue.put(item)
+        if self.listener is not None and (item is None or self.stream):
+            try:
+                self.listener(item)
+            except Exception as e:  # noqa: BLE001 - a follower that went away must not stop the step loop
+                logger.warning(f"listener of request {self.req_id} failed: {e!r}")
 
 
 class ModelRunner:
@@ -423,14 +440,14 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: List[int], sampling=None, stream: bool = False, structured_regex: str = "",
-                    request_target: Optional[dict] = None, refit=None, mrope_positions=None) -> Request:
+                    request_target: Optional[dict] = None, refit=None, mrope_positions=None, listener=None) -> Request:
         cfg = sampling or ne.SamplingConfig()
         cfg.verify_args()          # normalises in place (e.g. beams need as many log-probs as beams); errors resurface below
         with self._lock:
             req_id = self._next_req
             self._next_req += 1
         n = max(cfg.num_beams, cfg.num_return_sequences, 1)
-        req = Request(req_id, prompt, cfg, n, stream)
+        req = Request(req_id, prompt, cfg, n, stream, listener)
         req.request_target, req.refit, req.mrope_positions = request_target, refit, mrope_positions
         # plain = nothing needs the host between a step's sampling and the next forward (see _step_pipelined)
         req.plain = (n == 1 and cfg.num_beams == 1 and not cfg.stop_strings and not structured_regex and
@@ -480,9 +497,8 @@ class LLMEngine:
 
     def _complete(self, req: Request):
         req.finish_time = time.time()
-        if req.stream_queue is not None:
-            req.stream_queue.put(None)
         req.done.set()
+        req.emit(None)
         if req.span_id:
             ne.span_end(req.span_id, {"code": str(req.status_code)})
         with self._lock:
@@ -521,8 +537,8 @@ class LLMEngine:
             req = self.requests.get(rid)
             if req is None:
                 continue
-            if req.stream_queue is not None:
-                req.stream_queue.put(("step", [list(o.tokens) for o in req.outputs]))
+            if req.stream:
+                req.emit(("step", [list(o.tokens) for o in req.outputs]))
             if req.all_finished():
                 n_out = sum(len(o.tokens) for o in req.outputs)
                 ne.report_counter("metric_output_token_num", n_out)

@@ -14,6 +14,7 @@ import asyncio
 import logging
 import os
 import threading
+from functools import partial
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
@@ -127,6 +128,60 @@ class PyAsyncStreamingIterator:
             self.engine.abort(self.req)
 
 
+class AsyncRequestFollower:
+    """Event-loop side of a request: the engine's loop thread calls :meth:`post` with every streamed piece and with
+    None at the end; the items cross to the event loop through ``call_soon_threadsafe`` into an ``asyncio.Queue``.
+    As an async iterator it yields the request's output after every piece (streaming); :meth:`finished` waits for
+    the end (blocking requests). Closing or dropping it before the end (client disconnect) aborts the request."""
+
+    def __init__(self, loop, engine, output_fn):
+        self.loop, self.engine, self.output_fn = loop, engine, output_fn
+        self.queue: asyncio.Queue = asyncio.Queue()
+        self.req = None
+        self._done = False
+        self._end_seen = False
+
+    def post(self, item) -> None:             # engine loop thread
+        try:
+            self.loop.call_soon_threadsafe(self.queue.put_nowait, item)
+        except RuntimeError:                  # the event loop is gone (server shutting down): nobody is listening
+            pass
+
+    async def finished(self) -> None:
+        while not self._done:
+            if await self.queue.get() is None:
+                self._done = True
+
+    def __aiter__(self):
+        return self
+
+    async def __anext__(self):
+        if self._done or self._end_seen:
+            self._done = True
+            raise StopAsyncIteration
+        if await self.queue.get() is None:
+            self._done = True
+            raise StopAsyncIteration
+        # pieces that piled up while the consumer was busy collapse into one output (each stands for "all tokens so
+        # far"); an end marker among them is honoured on the next call, after this last output
+        while not self.queue.empty():
+            if self.queue.get_nowait() is None:
+                self._end_seen = True
+                break
+        return self.output_fn(self.req)
+
+    def close(self) -> None:
+        if not self._done and self.req is not None and not self.req.done.is_set():
+            self.engine.abort(self.req)
+        self._done = True
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
 class ServingModel:
     def __init__(self, config_file: str, llm: Optional[LLM] = None, tokenizer=None):
         self._config_file = config_file
@@ -232,14 +287,13 @@ class ServingModel:
         return KsanaPythonOutput(input_tokens=list(req.prompt), output_tokens=[list(o.tokens) for o in outs],
                                  logprobs=[list(o.logprobs) for o in outs], finished=req.all_finished())
 
-    def generate(self, model_name: str = "", inputs: Optional[List[int]] = None, generation_config: Any = None,
-                 streamer=None, messages=None, req_ctx: Optional[Dict[str, str]] = None, **kwargs):
-        """Returns (Status, KsanaPythonOutput) or, with ``streamer``, (Status, async iterator)."""
+    def _submit(self, inputs, generation_config, streamer, messages, req_ctx, kwargs, listener=None):
+        """Validation, the plug-in's preprocessing and the hand-over to the engine: (Status, request, plug-in input)."""
         gen = generation_config if generation_config is not None else {}
         sampling = make_sampling_config(gen)
         code, msg = sampling.verify_args()
         if code != 0:
-            return Status(code, msg), None
+            return Status(code, msg), None, None
         ksana_input = {"input_tokens": list(inputs or []), "input_refit_embedding": kwargs.get("input_refit_embedding") or {},
                        "additional_params": kwargs.get("additional_params") or {}, "prompt": kwargs.get("prompt")}
         if self.plugin is not None:
@@ -247,7 +301,7 @@ class ServingModel:
                                    additional_params=ksana_input["additional_params"])
         tokens = ksana_input["input_tokens"]
         if not tokens:
-            return Status(1, "empty input tokens"), None
+            return Status(1, "empty input tokens"), None, None
         refit = None
         emb = ksana_input.get("input_refit_embedding") or {}
         if emb.get("pos") and emb.get("embeddings") is not None:
@@ -257,10 +311,19 @@ class ServingModel:
         span = ne.span_start("generate", (req_ctx or {}).get("traceparent", ""))
         req = self.llm.engine.add_request(tokens, sampling, stream=bool(streamer),
                                           structured_regex=kwargs.get("structured_output_regex") or "",
-                                          refit=refit, mrope_positions=mrope)
+                                          refit=refit, mrope_positions=mrope, listener=listener)
         req.span_id = span
         if req.done.is_set() and req.status_code != 0:
-            return Status(req.status_code, req.status_message), None
+            return Status(req.status_code, req.status_message), None, None
+        return Status(), req, ksana_input
+
+    def generate(self, model_name: str = "", inputs: Optional[List[int]] = None, generation_config: Any = None,
+                 streamer=None, messages=None, req_ctx: Optional[Dict[str, str]] = None, **kwargs):
+        """Returns (Status, KsanaPythonOutput) or, with ``streamer``, (Status, async iterator). The calling thread
+        waits for the result; the HTTP front uses :meth:`generate_async`, which holds no thread while a request runs."""
+        status, req, ksana_input = self._submit(inputs, generation_config, streamer, messages, req_ctx, kwargs)
+        if not status.OK():
+            return status, None
         if streamer:
             return Status(), PyAsyncStreamingIterator(self.llm.engine, req, self._output_of)
         req.done.wait()
@@ -269,6 +332,31 @@ class ServingModel:
         out = self._output_of(req)
         if self.plugin is not None:
             self.plugin.postprocess(ksana_python_input=ksana_input, ksana_python_output=out)
+        return Status(), out
+
+    async def generate_async(self, model_name: str = "", inputs: Optional[List[int]] = None, generation_config: Any = None,
+                             streamer=None, messages=None, req_ctx: Optional[Dict[str, str]] = None, executor=None,
+                             **kwargs):
+        """:meth:`generate` for callers on an asyncio event loop. Preparation (validation, plug-in, hand-over to the
+        engine) runs on ``executor``; from then on the engine's loop thread posts every streamed piece and the end of
+        the request to the event loop, so that a request in flight occupies no thread: thousands of open requests
+        cost thousands of small queues, not thousands of blocked threads. Same return values as :meth:`generate`."""
+        loop = asyncio.get_running_loop()
+        follower = AsyncRequestFollower(loop, self.llm.engine, self._output_of)
+        status, req, ksana_input = await loop.run_in_executor(
+            executor, partial(self._submit, inputs, generation_config, streamer, messages, req_ctx, kwargs, follower.post))
+        if not status.OK():
+            return status, None
+        follower.req = req
+        if streamer:
+            return Status(), follower
+        await follower.finished()
+        if req.status_code != 0:
+            return Status(req.status_code, req.status_message), None
+        out = self._output_of(req)
+        if self.plugin is not None:
+            await loop.run_in_executor(executor, partial(self.plugin.postprocess, ksana_python_input=ksana_input,
+                                                         ksana_python_output=out))
         return Status(), out
 
     # ------------------------------------------------------------------ forward

@@ -172,21 +172,24 @@ def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExec
         if regex is not None:
             kwargs["structured_output_regex"] = regex
         gen = _sampling_dict(sampling_config, tokenizer)
-        loop = asyncio.get_event_loop()
-        call = partial(model.generate, model_name=model_name, inputs=input_tokens, generation_config=gen,
-                       messages=messages, streamer=True if enable_streaming else None, req_ctx=req_ctx, **kwargs)
-        status, result = await loop.run_in_executor(executor, call)
+        # no thread waits while the request runs: the engine posts pieces and the end to this event loop
+        status, result = await model.generate_async(model_name=model_name, inputs=input_tokens, generation_config=gen,
+                                                    messages=messages, streamer=True if enable_streaming else None,
+                                                    req_ctx=req_ctx, executor=executor, **kwargs)
         if not status.OK():
             return status, None, enable_streaming
         if enable_streaming:
             async def stream_results():
-                async for out in result:
-                    if out is None:
-                        return
-                    body = {"texts": [_decode(tokenizer, t, True) for t in out.output_tokens],
-                            "output_token_ids": out.output_tokens, "logprobs": out.logprobs,
-                            "input_token_ids": out.input_tokens}
-                    yield json.dumps(body).encode() + b"\0"
+                try:
+                    async for out in result:
+                        if out is None:
+                            return
+                        body = {"texts": [_decode(tokenizer, t, True) for t in out.output_tokens],
+                                "output_token_ids": out.output_tokens, "logprobs": out.logprobs,
+                                "input_token_ids": out.input_tokens}
+                        yield json.dumps(body).encode() + b"\0"
+                finally:
+                    result.close()          # a client that went away mid-stream: the request is aborted
             return status, stream_results(), True
         return status, to_json(result), False
 

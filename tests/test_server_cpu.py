@@ -160,3 +160,78 @@ def test_tokenizer_loading_rules(tmp_path, monkeypatch):
     (vl / "preprocessor_config.json").write_text("{}")
     tok = load_tokenizer(str(vl))
     assert isinstance(tok, Tok) and isinstance(tok.processor, Proc) and calls[-1][0] == "processor"
+
+
+def test_many_open_requests_hold_no_threads():
+    """Forty requests in flight at once (half of them streaming) through a front whose executor has two threads: all
+    of them complete with full-length answers, and the process grows by no thread per open request, because a request
+    that is running waits on the event loop, not on a thread."""
+    import asyncio
+    import threading
+    import httpx
+    tok = ByteTokenizer()
+    ec = EngineConfig()
+    ec.batch_scheduler.max_batch_size = 64
+    ec.batch_scheduler.max_token_len = 128
+    ec.block_manager.device_blocks_num = 512
+    llm = LLM(ec, tiny_model_cfg(), weights="random", device="cpu", dtype=torch.float32, tokenizer=tok)
+    model = ServingModel("", llm=llm, tokenizer=tok)
+    model.init_serving()
+    from concurrent.futures import ThreadPoolExecutor
+    app = create_app(model, tok, executor=ThreadPoolExecutor(max_workers=2))
+    peak = [0]
+
+    async def run():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://test") as c:
+            async def one(i):
+                r = await c.post("/generate", json={"prompt": "request number %d" % i, "stream": i % 2 == 0,
+                                                    "sampling_config": {"max_new_tokens": 24, "ignore_eos": True}}, timeout=120)
+                peak[0] = max(peak[0], threading.active_count())
+                assert r.status_code == 200
+                if i % 2 == 0:
+                    chunks = [json.loads(x) for x in r.content.split(b"\0") if x]
+                    return chunks[-1]["output_token_ids"][0]
+                return r.json()["output_token_ids"][0]
+            return await asyncio.gather(*[one(i) for i in range(40)])
+
+    before = threading.active_count()
+    try:
+        outs = asyncio.run(run())
+    finally:
+        model.shutdown()
+    assert len(outs) == 40 and all(len(o) == 24 for o in outs)
+    assert peak[0] - before <= 6, (before, peak[0])       # executor threads and the loop's helpers, not 40
+
+
+def test_closing_a_stream_follower_aborts_its_request():
+    """A client that leaves mid-stream: closing the follower aborts the request in the engine, which then ends it with
+    the aborted status instead of generating to the end."""
+    import asyncio
+    tok = ByteTokenizer()
+    ec = EngineConfig()
+    ec.batch_scheduler.max_batch_size = 4
+    ec.batch_scheduler.max_token_len = 2048
+    ec.block_manager.device_blocks_num = 256
+    llm = LLM(ec, tiny_model_cfg(), weights="random", device="cpu", dtype=torch.float32, tokenizer=tok)
+    model = ServingModel("", llm=llm, tokenizer=tok)
+    model.init_serving()
+
+    async def run():
+        status, follower = await model.generate_async(inputs=tok.encode("a long story"), streamer=True,
+                                                      generation_config={"max_new_tokens": 1500, "ignore_eos": True})
+        assert status.OK()
+        first = await follower.__anext__()
+        assert 1 <= len(first.output_tokens[0]) < 1500
+        req = follower.req
+        follower.close()
+        for _ in range(600):
+            if req.done.is_set():
+                break
+            await asyncio.sleep(0.01)
+        return req
+
+    try:
+        req = asyncio.run(run())
+    finally:
+        model.shutdown()
+    assert req.done.is_set() and req.aborted and len(req.outputs[0].tokens) < 1500
