@@ -360,8 +360,8 @@ class ServingModel:
         return Status(), out
 
     # ------------------------------------------------------------------ forward
-    def forward(self, request_bytes: bytes, req_ctx: Optional[Dict[str, str]] = None):
-        """msgpack batch of prefill-only requests with request targets -> msgpack responses."""
+    def _forward_submit(self, request_bytes: bytes, listener=None):
+        """Decoding, validation and hand-over of a /forward batch: (Status, requests in flight)."""
         try:
             reqs_in = unpack_requests(request_bytes, self.tokenizer)
         except Exception as e:  # noqa: BLE001
@@ -383,9 +383,41 @@ class ServingModel:
             emb = r.get("input_refit_embedding") or {}
             if emb.get("pos") and emb.get("embeddings") is not None:
                 refit = (list(emb["pos"]), [torch.as_tensor(e, dtype=torch.float32) for e in emb["embeddings"]])
-            pending.append(engine.add_request(r["input_tokens"], s, request_target=r["request_target"], refit=refit))
+            pending.append(engine.add_request(r["input_tokens"], s, request_target=r["request_target"], refit=refit,
+                                              listener=listener))
+        return Status(), pending
+
+    @staticmethod
+    def _forward_pack(pending):
         for req in pending:
-            req.done.wait()
             if req.status_code != 0:
                 return Status(req.status_code, req.status_message), None
         return Status(), pack_responses([(req.prompt, req.response) for req in pending])
+
+    def forward(self, request_bytes: bytes, req_ctx: Optional[Dict[str, str]] = None):
+        """msgpack batch of prefill-only requests with request targets -> msgpack responses."""
+        status, pending = self._forward_submit(request_bytes)
+        if not status.OK():
+            return status, None
+        for req in pending:
+            req.done.wait()
+        return self._forward_pack(pending)
+
+    async def forward_async(self, request_bytes: bytes, req_ctx: Optional[Dict[str, str]] = None, executor=None):
+        """:meth:`forward` for callers on an event loop: decoding and packing run on ``executor``, and no thread waits
+        while the batch is in the engine (every request posts its end to the loop)."""
+        loop = asyncio.get_running_loop()
+        ends: asyncio.Queue = asyncio.Queue()
+
+        def post(item):                       # engine loop thread; only the end of a request matters here
+            if item is None:
+                try:
+                    loop.call_soon_threadsafe(ends.put_nowait, None)
+                except RuntimeError:
+                    pass
+        status, pending = await loop.run_in_executor(executor, partial(self._forward_submit, request_bytes, post))
+        if not status.OK():
+            return status, None
+        for _ in pending:
+            await ends.get()
+        return await loop.run_in_executor(executor, partial(self._forward_pack, pending))

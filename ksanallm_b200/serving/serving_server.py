@@ -10,11 +10,9 @@ engine's broadcast step plans.
 from __future__ import annotations
 
 import argparse
-import asyncio
 import json
 import os
 from concurrent.futures import ThreadPoolExecutor
-from functools import partial
 from typing import Any, Dict, List, Optional
 
 import msgpack
@@ -208,8 +206,7 @@ def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExec
     async def forward(request: Request):
         req_ctx = trace_ctx(request)
         body = await request.body()
-        loop = asyncio.get_event_loop()
-        status, response_bytes = await loop.run_in_executor(executor, partial(model.forward, body, req_ctx))
+        status, response_bytes = await model.forward_async(body, req_ctx, executor=executor)
         if status.OK() and response_bytes is not None:
             return Response(content=response_bytes, media_type="application/x-msgpack")
         err = msgpack.packb({"message": status.GetMessage(), "code": status.GetCode().value})
