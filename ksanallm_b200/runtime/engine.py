@@ -538,7 +538,8 @@ class LLMEngine:
             if req is None:
                 continue
             if req.stream:
-                req.emit(("step", [list(o.tokens) for o in req.outputs]))
+                # queue followers get the tokens so far; a listener reads the request itself on its own thread
+                req.emit(("step", [list(o.tokens) for o in req.outputs] if req.stream_queue is not None else None))
             if req.all_finished():
                 n_out = sum(len(o.tokens) for o in req.outputs)
                 ne.report_counter("metric_output_token_num", n_out)
