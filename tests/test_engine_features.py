@@ -420,3 +420,32 @@ def test_generate_on_a_started_engine_waits_for_the_loop(monkeypatch, native_loo
         eng.stop()
     assert got == want
     assert threading.get_ident() not in stepped_by and len(stepped_by) == 1
+
+
+@pytest.mark.parametrize("quant", ["fp8_block", "nvfp4", "w4a16"])
+def test_quantised_weights_keep_the_perplexity(quant):
+    """Perplexity-style check of the quantised paths (CPU restatements of block FP8, NVFP4 and 4-bit weight-only):
+    the mean next-token loss of a two-layer model over 95 positions stays within 8 % (as a perplexity ratio) of the
+    same model with unquantised weights."""
+    from ksanallm_b200.config import ModelConfig
+    from ksanallm_b200.models.common import StepInput
+    from ksanallm_b200.models.weights import RandomSource, build_model
+    cfg = ModelConfig(model_type="llama", hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                      intermediate_size=512, vocab_size=300, max_position_embeddings=256, max_token_len=256)
+    torch.manual_seed(1)
+    T = 96
+    toks = torch.randint(3, cfg.vocab_size, (T,))
+
+    def loss(q):
+        m = build_model(cfg, RandomSource(seed=3, std=0.05), device="cpu", dtype=torch.float32, quant=q)
+        m.allocate_kv_cache(16, 16)
+        ar = torch.arange(T, dtype=torch.int32)
+        step = StepInput(toks.to(torch.int32), ar, ar.clone(), torch.tensor([0, T], dtype=torch.int32),
+                         torch.tensor([T], dtype=torch.int32), torch.arange(16, dtype=torch.int32).view(1, 16),
+                         num_multi=1, num_single=0, num_tokens=T, num_multi_tokens=T, max_q_len=T, max_kv_len=T)
+        logits = m.forward(step).float()
+        assert logits.shape == (T, cfg.vocab_size)
+        return float(-torch.log_softmax(logits[:-1], -1).gather(1, toks[1:].view(-1, 1)).mean())
+
+    ratio = math.exp(loss(quant) - loss(None))
+    assert 0.92 < ratio < 1.08, ratio
