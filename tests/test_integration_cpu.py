@@ -1,7 +1,8 @@
 """Stand-alone server process end to end (the shape of the reference's tests/integration_test.py): a tiny Hugging
 Face Llama checkpoint and tokenizer are written to disk, ``python serving_server.py --config_file X.yaml --port P`` is
-started as a child process - alone, and as two tensor-parallel ranks under torchrun (rank 0 serves, rank 1 follows the
-broadcast step plans) - and the answers of /generate (blocking and streaming) are compared token by token with Hugging
+started as a child process - alone, as two tensor-parallel ranks under torchrun (rank 0 serves, the others follow the
+broadcast step plans) and as four ranks (more ranks than KV heads: neighbouring ranks hold copies of one KV head, and the
+vocabulary does not divide by four) - and the answers of /generate (blocking and streaming) are compared token by token with Hugging
 Face's own greedy generation from the same files."""
 import json
 import os
@@ -50,7 +51,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.fixture(scope="module", params=[1, 2], ids=["one-process", "two-tensor-parallel-ranks"])
+@pytest.fixture(scope="module", params=[1, 2, 4], ids=["one-process", "two-tensor-parallel-ranks", "four-ranks-sharing-kv-heads"])
 def served(request, tmp_path_factory):
     nproc = request.param
     d = tmp_path_factory.mktemp("served")
