@@ -426,3 +426,35 @@ def test_unknown_model_type_with_its_own_weight_map(tmp_path):
     with open(os.path.join(d, "gpt2_weight_map.json"), "w") as f:
         json.dump({"^x$": "y", "^z$": "w"}, f)
     assert len(load_weight_map("gpt", model_dir=d, hf_model_type="gpt2")) == 2
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_families_under_tensor_parallelism(tmp_path, world):
+    """Every model family as tensor-parallel CPU ranks (gloo, library collectives): each rank loads its shard of the
+    same tiny Hugging Face model - with four ranks there are more ranks than KV heads, and the vocabulary of 203 never
+    divides - and every rank's logits equal Hugging Face's."""
+    import json
+    import socket
+    import subprocess
+    import sys
+    try:
+        from transformers import DeepseekV3Config  # noqa: F401
+        names = "llama,qwen2,gpt2,mixtral,qwen2_moe,glm,deepseek_v3"
+    except ImportError:
+        names = "llama,qwen2,gpt2,mixtral,qwen2_moe,glm"
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = tmp_path / "result.json"
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(here, "tp_families_worker.py"),
+                        str(out), names], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    per_rank = json.loads(out.read_text())
+    assert len(per_rank) == world
+    for rank, res in enumerate(per_rank):
+        assert set(res) == set(names.split(","))
+        for name, v in res.items():
+            assert v["ok"], (rank, name, v)
