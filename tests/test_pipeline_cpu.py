@@ -107,3 +107,31 @@ def test_request_targets_over_pipeline_stages(tmp_path, nproc, pp, mb, port):
         for k in TARGETS:
             assert float((g[k] - w.response[k]).abs().max()) < 1e-3, k
 
+
+
+def test_families_over_pipeline_stages(tmp_path):
+    """Every model family split into two pipeline stages (CPU ranks, gloo) through the public API: the greedy
+    continuations equal Hugging Face's own generation from the same tiny models (embedding kinds, final norms, dense
+    and routed layers, latent attention each land on the stage that needs them)."""
+    import json
+    import socket
+    pytest.importorskip("transformers")
+    try:
+        from transformers import DeepseekV3Config  # noqa: F401
+        names = "llama,qwen2,gpt2,mixtral,qwen2_moe,glm,deepseek_v3"
+    except ImportError:
+        names = "llama,qwen2,gpt2,mixtral,qwen2_moe,glm"
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = tmp_path / "result.json"
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", str(port), os.path.join(here, "pp_families_worker.py"), str(out), "2",
+                        names], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    res = json.loads(out.read_text())
+    assert set(res) == set(names.split(","))
+    for name, v in res.items():
+        assert v["ok"], (name, v)
