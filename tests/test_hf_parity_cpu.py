@@ -458,3 +458,49 @@ def test_families_under_tensor_parallelism(tmp_path, world):
         assert set(res) == set(names.split(","))
         for name, v in res.items():
             assert v["ok"], (rank, name, v)
+
+
+@pytest.mark.parametrize("name", ["llama", "qwen2", "gpt2", "mixtral", "qwen2_moe", "glm", "deepseek_v3"])
+def test_engine_features_across_families(name):
+    """Chunked prefill (16-token pieces), the prefix cache and swap preemption in a small block pool, for every family:
+    five prompts that share a 35-token head, generated in two waves through the engine, continue exactly as Hugging
+    Face's greedy generation does (learned positions, latent-attention caches and routed layers all see prompts in
+    pieces and cached heads)."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from tp_families_worker import family
+    from ksanallm_b200.config import EngineConfig
+    from ksanallm_b200.runtime.engine import LLMEngine
+    from ksanallm_b200.utils import native_engine as ne
+    try:
+        hf, c, _ = family(name)
+    except AttributeError:
+        pytest.skip(f"this transformers build has no {name}")
+    hf = _init(hf, std=0.2).eval()
+    cfg = model_config_from_hf(c.to_dict())
+    cfg.max_token_len = 128
+    cfg.eos_token_ids = []
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    model = build_model(cfg, DictSource(sd, cfg.model_type), device="cpu", dtype=torch.float32)
+    ec = EngineConfig()
+    ec.batch_scheduler.max_batch_size = 8
+    ec.batch_scheduler.max_token_len = 128
+    ec.batch_scheduler.max_step_tokens = 64
+    ec.batch_scheduler.split_fuse_token_num = 16
+    ec.batch_scheduler.enable_auto_prefix_cache = True
+    ec.batch_scheduler.preempt_mode = 0            # swap
+    eng = LLMEngine(model, cfg, ec, num_blocks=9, num_host_blocks=32)      # nine blocks: one sequence gets swapped out
+    g = torch.Generator().manual_seed(2)
+    head = torch.randint(3, 203, (35,), generator=g).tolist()
+    prompts = [head + torch.randint(3, 203, (4 + 3 * i,), generator=g).tolist() for i in range(5)]
+    s = ne.SamplingConfig()
+    s.max_new_tokens, s.ignore_eos, s.topk = 10, True, 1
+    reqs = eng.generate(prompts[:1], s) + eng.generate(prompts[1:], s)
+    for r, p in zip(reqs, prompts):
+        assert r.status_code == 0, r.status_message
+        with torch.no_grad():
+            want = hf.generate(torch.tensor([p]), max_new_tokens=10, do_sample=False, eos_token_id=None, pad_token_id=0)
+        assert list(r.outputs[0].tokens) == want[0, len(p):].tolist()
+    st = eng.scheduler.stats()
+    assert st["prefix_hit_tokens"] >= 4 * 32 and st["preempt_swap"] >= 1 and st["swapped_in_blocks"] >= 1
+    assert eng.scheduler.check_invariants()[0]
