@@ -61,6 +61,9 @@ def main():
     llm.engine.step_hook = hook
     s = ne.SamplingConfig()
     s.max_new_tokens, s.ignore_eos = int(os.environ.get("KSANA_TEST_DP_NEW", "5")), True
+    if os.environ.get("KSANA_TEST_DP_N"):
+        # sampled siblings: every request forks into n sequences that share their prompt blocks (copy-on-write)
+        s.num_return_sequences, s.topk, s.temperature, s.seed = int(os.environ["KSANA_TEST_DP_N"]), 20, 1.0, 1234
     reqs = llm.generate(prompts_for(mc.vocab_size) if llm.rank == 0 else [], s)
     if llm.rank == 0:
         order = sorted(first)
@@ -68,7 +71,7 @@ def main():
         # a request with per-row extras is answered with a status at admission: nothing is scheduled for it
         refused = (llm.engine.add_request([5, 6, 7], s, request_target={"transformer": {"token_reduce_mode": "GATHER_ALL"}})
                    if llm.model.dp is not None else None)
-        torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "first": torch.stack([first[k] for k in order]),
+        torch.save({"tokens": [r.outputs[0].tokens for r in reqs], "all_tokens": [[o.tokens for o in r.outputs] for r in reqs], "first": torch.stack([first[k] for k in order]),
                     "experts": (moe.expert_lo, moe.expert_hi), "gathered_bytes": llm.model.dp.gathered_bytes if llm.model.dp else 0,
                     "dispatched_rows": llm.model.dp.dispatched_rows if llm.model.dp else 0,
                     "peer_memory": bool(llm.model.dp is not None and llm.model.dp.symm is not None),

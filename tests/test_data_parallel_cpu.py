@@ -32,7 +32,7 @@ def test_sub_plan_selects_own_sequences():
     assert sub1.seq_ids.tolist() == [7, 9] and sub1.sample_rows.tolist() == [4, 5] and sub1.num_multi == 1
 
 
-def _single(new_tokens=5):
+def _single(new_tokens=5, n=0):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from dp_worker import engine_cfg, model_cfg, prompts_for
     from ksanallm_b200.models.weights import RandomSource, build_model
@@ -50,7 +50,11 @@ def _single(new_tokens=5):
     eng.step_hook = hook
     s = ne.SamplingConfig()
     s.max_new_tokens, s.ignore_eos = new_tokens, True
+    if n:
+        s.num_return_sequences, s.topk, s.temperature, s.seed = n, 20, 1.0, 1234
     reqs = eng.generate(prompts_for(mc.vocab_size), s)
+    if n:
+        return [[o.tokens for o in r.outputs] for r in reqs], None
     return [r.outputs[0].tokens for r in reqs], torch.stack([first[k] for k in sorted(first)])
 
 
@@ -117,3 +121,19 @@ def test_alltoall_dispatch_moves_fewer_rows_than_allgather(tmp_path):
         res[dispatch] = torch.load(out)
     assert res["alltoall"]["tokens"] == res["allgather"]["tokens"]
     assert 0 < res["alltoall"]["gathered_bytes"] < 0.75 * res["allgather"]["gathered_bytes"]
+
+
+def test_attention_dp_with_sampled_siblings(tmp_path):
+    """Three sampled sequences per request (fixed seed) under attention data parallelism: siblings fork from their
+    request's prompt blocks by copy-on-write inside one rank's pool, every rank runs only its own pool's copies, and
+    all fifteen continuations equal those of the single process."""
+    want, _ = _single(12, n=3)
+    assert all(len(w) == 3 and len(set(map(tuple, w))) > 1 for w in want)          # siblings do differ
+    out = str(tmp_path / "dp.pt")
+    env = dict(os.environ, OMP_NUM_THREADS="1", KSANA_TEST_DP_NEW="12", KSANA_TEST_DP_N="3")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29731", os.path.join(ROOT, "tests", "dp_worker.py"), out, "cpu"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    assert got["all_tokens"] == want
