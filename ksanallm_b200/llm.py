@@ -33,7 +33,9 @@ def init_distributed(device_type: str, pp: int = 1):
     rank, world, local = _dist_env()
     if world == 1:
         return 0, 1, None, None, None
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    # MASTER_HOST is the reference's spelling of the rendezvous address (src/ksana_llm/utils/environment.cpp reads it
+    # with MASTER_PORT / WORLD_SIZE / NODE_RANK): accepted where MASTER_ADDR is not given
+    os.environ.setdefault("MASTER_ADDR", os.environ.get("MASTER_HOST") or "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29511")
     if not dist.is_initialized():
         backend = "nccl" if device_type == "cuda" else "gloo"

@@ -61,7 +61,7 @@ class DistributedCoordinator:
     def from_env(rank: int, world: int) -> Optional["DistributedCoordinator"]:
         if world <= 1 or os.environ.get("KSANA_CONTROL_PLANE", "1") == "0":
             return None
-        host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+        host = os.environ.get("MASTER_ADDR") or os.environ.get("MASTER_HOST") or "127.0.0.1"
         port = int(os.environ.get("KSANA_CONTROL_PORT", int(os.environ.get("MASTER_PORT", "29511")) + 17))
         return DistributedCoordinator(rank, world, host, port,
                                       int(os.environ.get("KSANA_HEARTBEAT_INTERVAL_MS", "5000")),
