@@ -8,6 +8,7 @@
 #include <fcntl.h>
 
 #include <cerrno>
+#include <cmath>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -51,6 +52,9 @@ std::map<std::string, std::string> WithServiceName(std::map<std::string, std::st
   if (!r.count("service.name")) r["service.name"] = "ksana_llm";
   return r;
 }
+
+// JSON has no spelling for infinities and NaN (the minimum of a metric without samples): they go out as 0
+double Num(double v) { return std::isfinite(v) ? v : 0.0; }
 
 int64_t NowNano() {
   return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::system_clock::now().time_since_epoch()).count();
@@ -111,12 +115,12 @@ std::string OtlpMetricsRequestJson(const std::vector<OtlpMetricPoint>& points, c
                               std::to_string(now_unix_nano) + "\"";
     if (p.counter) {
       // cumulative (2) monotonic sum since the profiler started
-      o << "\"sum\":{\"dataPoints\":[{" << times << ",\"asDouble\":" << p.sum
+      o << "\"sum\":{\"dataPoints\":[{" << times << ",\"asDouble\":" << Num(p.sum)
         << "}],\"aggregationTemporality\":2,\"isMonotonic\":true}}";
     } else {
       // a histogram without buckets carries the count, sum, minimum and maximum of the samples
-      o << "\"histogram\":{\"dataPoints\":[{" << times << ",\"count\":\"" << p.count << "\",\"sum\":" << p.sum
-        << ",\"min\":" << p.min << ",\"max\":" << p.max << "}],\"aggregationTemporality\":2}}";
+      o << "\"histogram\":{\"dataPoints\":[{" << times << ",\"count\":\"" << p.count << "\",\"sum\":" << Num(p.sum)
+        << ",\"min\":" << Num(p.min) << ",\"max\":" << Num(p.max) << "}],\"aggregationTemporality\":2}}";
     }
     first = false;
   }
@@ -161,6 +165,7 @@ int HttpPostJson(const OtlpUrl& url, const std::string& body, int timeout_ms) {
     pollfd p{fd, POLLOUT, 0};
     if (poll(&p, 1, left()) != 1) { close(fd); return -3; }
     const ssize_t n = send(fd, data.data() + off, data.size() - off, MSG_NOSIGNAL);
+    if (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) continue;      // poll again, within the deadline
     if (n <= 0) { close(fd); return -2; }
     off += static_cast<size_t>(n);
   }
@@ -170,6 +175,7 @@ int HttpPostJson(const OtlpUrl& url, const std::string& body, int timeout_ms) {
     pollfd p{fd, POLLIN, 0};
     if (poll(&p, 1, left()) != 1) { close(fd); return -3; }
     const ssize_t n = recv(fd, buf, sizeof(buf), 0);
+    if (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) continue;
     if (n <= 0) break;
     answer.append(buf, static_cast<size_t>(n));
   }
