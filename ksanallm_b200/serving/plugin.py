@@ -9,9 +9,12 @@ from __future__ import annotations
 import importlib.util
 import os
 import sys
+import threading
 from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass
 from typing import Optional
+
+from ..utils import logger
 
 
 @dataclass
@@ -20,7 +23,7 @@ class PluginConfig:
     config_file: str = ""
     plugin_name: str = ""
     enable_trt: bool = True
-    thread_num: int = 1
+    thread_pool_size: int = 1          # plug-in calls in flight at once; above 1 the plug-in must be thread-safe
 
 
 def search_plugin_path(model_dir: str, plugin_name: str = "") -> Optional[str]:
@@ -38,32 +41,67 @@ def search_plugin_path(model_dir: str, plugin_name: str = "") -> Optional[str]:
 
 
 class KsanaPlugin:
+    """Loads the plug-in and runs its calls on a small thread pool. On a GPU every pool thread works in a CUDA stream
+    of its own (and waits for it before returning), so that a vision tower neither queues behind the engine's step on
+    the default stream nor holds it up."""
+
     def __init__(self, config: PluginConfig):
         self.config = config
         self._plugin = None
-        self._pool = ThreadPoolExecutor(max_workers=max(1, config.thread_num))
+        workers = max(1, min(int(config.thread_pool_size), 32, (os.cpu_count() or 1) * 5))
+        self._pool = ThreadPoolExecutor(max_workers=workers)
+        self._streams = {}
+        self._streams_lock = threading.Lock()
         path = search_plugin_path(config.model_dir, config.plugin_name)
-        if path is not None:
+        if path is None:
+            return
+        # plug-ins written for the reference import their helpers as top-level modules (``from plugin_utils import
+        # ...``) and their own neighbours by folder name: both folders go on the import path
+        helpers = os.path.abspath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "ksana_plugin"))
+        for folder in (helpers, os.path.dirname(os.path.dirname(path))):
+            if folder not in sys.path:
+                sys.path.append(folder)
+        try:
             spec = importlib.util.spec_from_file_location("ksana_plugin_user", path)
             mod = importlib.util.module_from_spec(spec)
             spec.loader.exec_module(mod)
             cls = getattr(mod, "KsanaPlugin", None)
-            if cls is not None:
-                self._plugin = cls()
-                if hasattr(self._plugin, "init_plugin"):
-                    self._plugin.init_plugin(model_path=config.model_dir, enable_trt=config.enable_trt,
-                                             preprocess=True, postprocess=True)
+            if cls is None:
+                logger.warning(f"plug-in {path} has no KsanaPlugin class; serving without it")
+                return
+            plugin = cls()
+            if hasattr(plugin, "init_plugin"):
+                plugin.init_plugin(model_path=config.model_dir, config_file=config.config_file,
+                                   enable_trt=config.enable_trt, preprocess=True, postprocess=True)
+            self._plugin = plugin
+            logger.info(f"plug-in loaded from {path} ({workers} worker thread(s))")
+        except Exception as e:  # noqa: BLE001 - a broken plug-in must not keep the text model from serving
+            logger.warning(f"plug-in {path} could not be loaded ({e!r}); serving without it")
 
     @property
     def loaded(self) -> bool:
         return self._plugin is not None
 
+    def _call(self, fn, kwargs):
+        import torch
+        if not torch.cuda.is_available():
+            return fn(**kwargs)
+        ident = threading.get_ident()
+        with self._streams_lock:
+            stream = self._streams.get(ident)
+            if stream is None:
+                stream = self._streams[ident] = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            out = fn(**kwargs)
+        stream.synchronize()          # what the plug-in wrote (embeddings) is complete before the engine reads it
+        return out
+
     def preprocess(self, **kwargs):
         if self._plugin is None or not hasattr(self._plugin, "preprocess"):
             return None
-        return self._pool.submit(self._plugin.preprocess, **kwargs).result()
+        return self._pool.submit(self._call, self._plugin.preprocess, kwargs).result()
 
     def postprocess(self, **kwargs):
         if self._plugin is None or not hasattr(self._plugin, "postprocess"):
             return None
-        return self._pool.submit(self._plugin.postprocess, **kwargs).result()
+        return self._pool.submit(self._call, self._plugin.postprocess, kwargs).result()

@@ -230,7 +230,7 @@ def main(argv=None):
     tokenizer = load_tokenizer(args.tokenizer_dir) if args.tokenizer_dir and os.path.isdir(args.tokenizer_dir) else None
     model = ServingModel(args.config_file, tokenizer=tokenizer)
     plugin_config = PluginConfig(model_dir=args.model_dir, config_file=args.config_file, plugin_name=args.model_type,
-                                 enable_trt=args.plugin_enable_trt, thread_num=args.plugin_thread_pool_size)
+                                 enable_trt=args.plugin_enable_trt, thread_pool_size=args.plugin_thread_pool_size)
     endpoint_config = EndpointConfig(args.endpoint, args.host, args.port, args.access_log)
     model.init_serving(plugin_config, endpoint_config, weights="random" if args.random_weights else "checkpoint")
     rank = int(os.environ.get("RANK", "0"))

@@ -151,3 +151,57 @@ def test_qwen_vl_first_generation_tower_and_spans():
     plugin.preprocess(ksana_python_input=inp, additional_params={"images": [img, 1.0 - img]})
     assert inp["input_refit_embedding"]["pos"] == [3, 12]
     assert [tuple(e.shape) for e in inp["input_refit_embedding"]["embeddings"]] == [(4, 128), (4, 128)]
+
+
+def test_plugin_written_for_the_reference_loads_unchanged(tmp_path):
+    """A plug-in in the reference's style: it imports ``plugin_utils`` as a top-level module, a neighbour module by its
+    folder name, expects ``config_file`` among the arguments of ``init_plugin`` and raises the reserved memory share in
+    that YAML. The host loads it, runs pre- and post-processing on its pool, and a broken plug-in only costs a warning."""
+    from ksanallm_b200.serving.plugin import KsanaPlugin as PluginHost, PluginConfig
+    pkg = tmp_path / "plugins" / "my_vl"
+    pkg.mkdir(parents=True)
+    (pkg / "tower_model.py").write_text("SCALE = 3\n")
+    (pkg / "ksana_plugin.py").write_text('''
+import os, sys
+from my_vl.tower_model import SCALE
+from plugin_utils import adjust_device_memory_ratio, check_file_dir, free_cache
+
+
+class KsanaPlugin:
+    def init_plugin(self, **kwargs):
+        self.seen = dict(kwargs)
+        free_cache()
+        adjust_device_memory_ratio(kwargs["config_file"], 0.04)
+
+    def preprocess(self, ksana_python_input, **kwargs):
+        ksana_python_input["input_tokens"] = [t * SCALE for t in ksana_python_input["input_tokens"]]
+
+    def postprocess(self, ksana_python_input, ksana_python_output, **kwargs):
+        ksana_python_output["note"] = "post"
+''')
+    yaml_path = tmp_path / "ksana_llm.yaml"
+    yaml_path.write_text("setting:\n  block_manager:\n    # room for the tower\n    reserved_device_memory_ratio: 0.01   # share\n    block_token_num: 16\n")
+    model_dir = tmp_path / "model"
+    model_dir.mkdir()
+    (model_dir / "ksana_plugin.py").write_text((pkg / "ksana_plugin.py").read_text())
+    import sys
+    sys.path.append(str(tmp_path / "plugins"))            # where "my_vl" lives, as an installed plug-in package would
+    try:
+        host = PluginHost(PluginConfig(model_dir=str(model_dir), config_file=str(yaml_path), plugin_name="my_vl",
+                                       thread_pool_size=2))
+        assert host.loaded and host._plugin.seen["config_file"] == str(yaml_path) and host._plugin.seen["enable_trt"] is True
+        text = yaml_path.read_text()
+        assert "reserved_device_memory_ratio: 0.04   # share" in text and "# room for the tower" in text
+        inp = {"input_tokens": [1, 2, 3]}
+        host.preprocess(ksana_python_input=inp)
+        assert inp["input_tokens"] == [3, 6, 9]
+        out = {}
+        host.postprocess(ksana_python_input=inp, ksana_python_output=out)
+        assert out == {"note": "post"}
+        # a larger value in the file is left alone; a plug-in that fails to import is skipped with a warning
+        from ksanallm_b200.ksana_plugin.plugin_utils import adjust_device_memory_ratio
+        assert adjust_device_memory_ratio(str(yaml_path), 0.02) is False
+        (model_dir / "ksana_plugin.py").write_text("import module_that_does_not_exist\n")
+        assert not PluginHost(PluginConfig(model_dir=str(model_dir), config_file=str(yaml_path))).loaded
+    finally:
+        sys.path.remove(str(tmp_path / "plugins"))
