@@ -37,10 +37,10 @@ def iter_stream(response) -> Iterator[dict]:
                 yield json.loads(chunk.decode("utf-8"))
 
 
-def forward(url: str, requests_list: List[dict]) -> dict:
+def forward(url: str, requests_list: List[dict], api: str = "forward") -> dict:
     """requests_list entries: {"input_tokens"|"prompt", "request_target": [{"target_name", "slice_pos"|"token_id",
     "token_reduce_mode"}]}. Tensors in the reply are decoded to numpy arrays."""
-    r = requests.post(url.rstrip("/") + "/forward", data=msgpack.packb({"requests": requests_list}, use_bin_type=True),
+    r = requests.post(url.rstrip("/") + "/" + api.lstrip("/"), data=msgpack.packb({"requests": requests_list}, use_bin_type=True),
                       headers={"Content-Type": "application/x-msgpack"})
     doc = msgpack.unpackb(r.content, raw=False)
     for resp in doc.get("responses", []) or []:

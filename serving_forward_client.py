@@ -15,6 +15,7 @@ def args_config(argv=None):
     p = argparse.ArgumentParser()
     p.add_argument("--host", type=str, default="localhost")
     p.add_argument("--port", type=int, default=8888)
+    p.add_argument("--api", type=str, default="forward", help="path of the endpoint on the server")
     p.add_argument("--prompt", type=str, default="Hello, my name is")
     p.add_argument("--input_tokens", type=int, nargs="*", default=None)
     p.add_argument("--target", type=str, default="logits", choices=["logits", "layernorm", "transformer"])
@@ -36,7 +37,7 @@ def main(argv=None):
         req["input_tokens"] = list(a.input_tokens)
     else:
         req["prompt"] = a.prompt
-    doc = clients.forward(f"http://{a.host}:{a.port}", [req])
+    doc = clients.forward(f"http://{a.host}:{a.port}", [req], api=a.api)
     out = []
     for resp in doc.get("responses", []) or []:
         for t in resp["response"]:
