@@ -39,7 +39,7 @@ FOLLOW_UPS = [
 SUBJECTS = ["the team", "our supplier", "the committee", "my manager", "the client", "the city council", "the school", "the lab", "the editor", "the landlord"]
 VERBS = ["postponed", "approved", "questioned", "rewrote", "measured", "rejected", "outlined", "shortened", "doubled", "reviewed"]
 OBJECTS = ["the quarterly budget", "the delivery schedule", "the safety report", "the second draft", "the test results", "the floor plan",
-           "the hiring plan", "the survey answers", "the maintenance contract", "the release notes"]
+           "the hiring plan", "the poll results", "the maintenance contract", "the release notes"]
 TAILS = ["after a long discussion", "without telling anyone", "for the third time this year", "because the figures did not add up",
          "and asked for a summary by Friday", "although nobody had objected", "so the deadline moved by two weeks", "which surprised everyone",
          "and nobody knows why", "before the holidays"]
