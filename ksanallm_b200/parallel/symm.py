@@ -128,6 +128,13 @@ class SymmetricComm:
         return os.environ.get("KSANA_PUSH_SIGNAL", "0") == "1"
 
     @property
+    def push_decode(self) -> bool:
+        """Decode-sized batches: whether the row-parallel GEMM's epilogue pushes its rows to every rank (default from
+        ``PUSH_MIN_RANKS`` ranks on) instead of every rank pulling them; ``KSANA_PUSH=0 / 1`` overrides."""
+        want = os.environ.get("KSANA_PUSH")
+        return self.size >= PUSH_MIN_RANKS if want is None else want == "1"
+
+    @property
     def push_prefill(self) -> bool:
         want = os.environ.get("KSANA_PUSH_PREFILL")
         return PUSH_EPILOGUE if want is None else want == "1"
@@ -293,12 +300,8 @@ class SymmetricComm:
             x = quantize(x)
         one_shot = self.one_shot(M)
         gemm_signals = False
-        want_push = os.environ.get("KSANA_PUSH")
         plain_w = writer is None and not W.nvfp4 and not W.w4a16
-        if one_shot:
-            push_mode = plain_w and (want_push == "1" or (want_push is None and self.size >= PUSH_MIN_RANKS))
-        else:
-            push_mode = self.push_prefill and plain_w
+        push_mode = plain_w and (self.push_decode if one_shot else self.push_prefill)
         rows_per = M if one_shot else (M + self.size - 1) // self.size
         bias = W.bias.data_ptr() if (writer is None and W.bias is not None and self.rank == 0) else None
         if writer is not None:

@@ -671,3 +671,30 @@ def test_symmetric_buffer_layout_for_every_group_size(size, max_tokens, hidden):
     assert lay["cand_words"] >= 2 * min(max_tokens, 1024) * CAND_MAX_K
     # a partial product of all rows fits the slot area of one parity (pull mode writes it there in one piece)
     assert size * lay["slot_bytes"] >= max_tokens * row
+
+
+def test_row_parallel_form_by_group_size_and_batch(monkeypatch):
+    """Which form a row-parallel linear takes, decided on the host: every rank reduces all rows itself up to 64 rows
+    while it pulls at most 8 MB; the GEMM pushes its rows from 4 ranks on (2 ranks pull); the switches override."""
+    from ksanallm_b200.parallel.symm import SymmetricComm
+    for var in ("KSANA_PUSH", "KSANA_PUSH_PREFILL", "KSANA_ONE_SHOT_ROWS"):
+        monkeypatch.delenv(var, raising=False)
+
+    def comm(size, hidden=8192):
+        c = SymmetricComm.__new__(SymmetricComm)          # decisions only: no device, no buffer
+        c.size, c.hidden = size, hidden
+        return c
+
+    for size in (2, 4, 8):
+        assert comm(size).one_shot(64) and not comm(size).one_shot(65)
+    assert comm(8).one_shot(64) and not comm(8, hidden=16384).one_shot(64)        # 14.7 MB to pull: split over the ranks
+    assert [comm(n).push_decode for n in (2, 4, 8)] == [False, True, True]
+    assert not comm(8).push_prefill
+    monkeypatch.setenv("KSANA_PUSH", "0")
+    assert not comm(8).push_decode
+    monkeypatch.setenv("KSANA_PUSH", "1")
+    assert comm(2).push_decode
+    monkeypatch.setenv("KSANA_PUSH_PREFILL", "1")
+    assert comm(4).push_prefill
+    monkeypatch.setenv("KSANA_ONE_SHOT_ROWS", "16")
+    assert comm(4).one_shot(16) and not comm(4).one_shot(17)
