@@ -152,3 +152,17 @@ def test_embedding_table_on_the_host_gives_the_same_tokens():
         s.max_new_tokens, s.ignore_eos = 5, True
         outs.append([r.outputs[0].tokens for r in llm.generate([[5, 6, 7, 8], [9, 10]], s)])
     assert outs[0] == outs[1]
+
+
+def test_offline_example_script_runs():
+    """examples/offline_generate.py (random weights, public API) runs on a machine without a GPU and prints two
+    continuations of sixteen tokens."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "offline_generate.py")], capture_output=True, text=True,
+                       timeout=300, env=dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    lines = [l for l in r.stdout.splitlines() if "->" in l]
+    assert len(lines) == 2 and all(len(l.split("->")[1].split(",")) == 16 for l in lines)
