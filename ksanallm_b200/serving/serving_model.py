@@ -78,8 +78,10 @@ def make_sampling_config(gen: Any) -> "ne.SamplingConfig":
     c.topp = float(get("top_p", get("topp", 1.0)) or 1.0)
     c.temperature = float(get("temperature", 1.0) or 1.0)
     do_sample = get("do_sample", None)
-    if do_sample is False or (do_sample is None and c.topk == 1):
-        c.topk = 1
+    if do_sample is False or c.topk == 1:
+        # greedy: the other sampling knobs go back to neutral as well, so that reported log-probabilities are those of
+        # the unscaled distribution
+        c.topk, c.topp, c.temperature = 1, 1.0, 1.0
     mx = get("max_new_tokens", -1)
     c.max_new_tokens = int(mx) if mx is not None and int(mx) > 0 else 1024
     c.logprobs_num = int(get("logprobs_num", get("logprobs", 0)) or 0)
