@@ -33,10 +33,14 @@ logger = logging.getLogger(__name__)
 
 @dataclass
 class EndpointConfig:
-    type: str = "python"
+    endpoint: str = "python"      # "python": the HTTP front of this package; another name: an RPC endpoint plug-in
     host: str = "0.0.0.0"
     port: int = 8080
     access_log: bool = True
+
+    @property
+    def type(self) -> str:
+        return self.endpoint
 
 
 class Status:
@@ -102,8 +106,8 @@ def make_sampling_config(gen: Any) -> "ne.SamplingConfig":
 class PyAsyncStreamingIterator:
     """Async iterator over a streaming request. Dropping it (client disconnect) aborts the request."""
 
-    def __init__(self, engine, req, output_fn):
-        self.engine, self.req, self.output_fn = engine, req, output_fn
+    def __init__(self, engine, req, output_fn, postprocess=None):
+        self.engine, self.req, self.output_fn, self.postprocess = engine, req, output_fn, postprocess
         self._done = False
 
     def __aiter__(self):
@@ -120,10 +124,11 @@ class PyAsyncStreamingIterator:
         item = await loop.run_in_executor(None, self._next_blocking)
         if item is None:
             self._done = True
-            if self.req.status_code != 0:
-                raise StopAsyncIteration
             raise StopAsyncIteration
-        return self.output_fn(self.req)
+        out = self.output_fn(self.req)
+        if self.postprocess is not None:
+            await loop.run_in_executor(None, self.postprocess, out)
+        return out
 
     def __del__(self):
         if not self._done and not self.req.done.is_set():
@@ -136,8 +141,9 @@ class AsyncRequestFollower:
     As an async iterator it yields the request's output after every piece (streaming); :meth:`finished` waits for
     the end (blocking requests). Closing or dropping it before the end (client disconnect) aborts the request."""
 
-    def __init__(self, loop, engine, output_fn):
+    def __init__(self, loop, engine, output_fn, postprocess=None, executor=None):
         self.loop, self.engine, self.output_fn = loop, engine, output_fn
+        self.postprocess, self.executor = postprocess, executor      # the plug-in's hook for every streamed output
         self.queue: asyncio.Queue = asyncio.Queue()
         self.req = None
         self._done = False
@@ -170,7 +176,10 @@ class AsyncRequestFollower:
             if self.queue.get_nowait() is None:
                 self._end_seen = True
                 break
-        return self.output_fn(self.req)
+        out = self.output_fn(self.req)
+        if self.postprocess is not None:
+            await self.loop.run_in_executor(self.executor, self.postprocess, out)
+        return out
 
     def close(self) -> None:
         if not self._done and self.req is not None and not self.req.done.is_set():
@@ -243,7 +252,7 @@ class ServingModel:
         ``Create<Name>Endpoint`` (looked up in the model directory, then on the loader path), which serves requests
         through its own transport and calls back into this model
         (src/ksana_llm/endpoints/endpoint_factory.cpp:19-39, src/ksana_llm/service/inference_server.cpp:96-118)."""
-        kind = (self.endpoint_config.type or "python").lower()
+        kind = (self.endpoint_config.endpoint or "python").lower()
         self.rpc_endpoint = None
         if kind in ("python", "", "none"):
             return
@@ -319,6 +328,13 @@ class ServingModel:
             return Status(req.status_code, req.status_message), None, None
         return Status(), req, ksana_input
 
+    def _stream_postprocess(self, ksana_input):
+        """The plug-in's post-processing as a one-argument call for every streamed output (the reference's streaming
+        iterator runs it on each piece, src/ksana_llm/python/ksana_llm/serving_model.py:45-58); None without a plug-in."""
+        if self.plugin is None or not self.plugin.loaded:
+            return None
+        return lambda out: self.plugin.postprocess(ksana_python_input=ksana_input, ksana_python_output=out)
+
     def generate(self, model_name: str = "", inputs: Optional[List[int]] = None, generation_config: Any = None,
                  streamer=None, messages=None, req_ctx: Optional[Dict[str, str]] = None, **kwargs):
         """Returns (Status, KsanaPythonOutput) or, with ``streamer``, (Status, async iterator). The calling thread
@@ -327,7 +343,8 @@ class ServingModel:
         if not status.OK():
             return status, None
         if streamer:
-            return Status(), PyAsyncStreamingIterator(self.llm.engine, req, self._output_of)
+            return Status(), PyAsyncStreamingIterator(self.llm.engine, req, self._output_of,
+                                                      self._stream_postprocess(ksana_input))
         req.done.wait()
         if req.status_code != 0:
             return Status(req.status_code, req.status_message), None
@@ -351,6 +368,7 @@ class ServingModel:
             return status, None
         follower.req = req
         if streamer:
+            follower.postprocess, follower.executor = self._stream_postprocess(ksana_input), executor
             return Status(), follower
         await follower.finished()
         if req.status_code != 0:

@@ -369,7 +369,8 @@ def test_import_compatibility_package():
     from ksanallm_b200.serving.auto_model import AutoModel
     assert ksana_llm.AutoModel is AutoModel
     assert {"AutoModel", "EndpointConfig", "PluginConfig"} <= set(ksana_llm.__all__)
-    assert ksana_llm.EndpointConfig().type in ("python", "PYTHON", "python ") or hasattr(ksana_llm.EndpointConfig(), "type")
+    assert ksana_llm.EndpointConfig().endpoint == "python" and ksana_llm.EndpointConfig(endpoint="trpc", port=9000).type == "trpc"
+    assert ksana_llm.PluginConfig(thread_pool_size=4).thread_pool_size == 4
 
 
 def test_lost_worker_rank_ends_the_service(tmp_path):

@@ -235,3 +235,49 @@ def test_closing_a_stream_follower_aborts_its_request():
     finally:
         model.shutdown()
     assert req.done.is_set() and req.aborted and len(req.outputs[0].tokens) < 1500
+
+
+def test_streamed_outputs_pass_through_the_plugin():
+    """Every streamed output is handed to the plug-in's post-processing (here it appends a marker token), in the
+    event-loop form and in the blocking iterator."""
+    import asyncio
+
+    class Marker:
+        loaded = True
+        calls = 0
+
+        def preprocess(self, **kw):
+            return None
+
+        def postprocess(self, ksana_python_input, ksana_python_output, **kw):
+            Marker.calls += 1
+            ksana_python_output.output_tokens = [t + [7777] for t in ksana_python_output.output_tokens]
+
+    tok = ByteTokenizer()
+    ec = EngineConfig()
+    ec.batch_scheduler.max_batch_size = 4
+    ec.batch_scheduler.max_token_len = 64
+    ec.block_manager.device_blocks_num = 32
+    llm = LLM(ec, tiny_model_cfg(), weights="random", device="cpu", dtype=torch.float32, tokenizer=tok)
+    model = ServingModel("", llm=llm, tokenizer=tok)
+    model.init_serving()
+    model.plugin = Marker()
+
+    async def run(blocking_iterator):
+        gen = {"max_new_tokens": 6, "ignore_eos": True}
+        if blocking_iterator:
+            status, it = model.generate(inputs=tok.encode("hi"), generation_config=gen, streamer=True)
+        else:
+            status, it = await model.generate_async(inputs=tok.encode("hi"), generation_config=gen, streamer=True)
+        assert status.OK()
+        outs = [o async for o in it]
+        return outs
+
+    try:
+        for blocking_iterator in (False, True):
+            outs = asyncio.run(run(blocking_iterator))
+            assert outs and all(o.output_tokens[0][-1] == 7777 for o in outs)
+            assert len(outs[-1].output_tokens[0]) == 7
+    finally:
+        model.shutdown()
+    assert Marker.calls >= 2
