@@ -64,6 +64,65 @@ class Status:
         return "OK" if self.OK() else f"{self.code}: {self.message}"
 
 
+class _Record:
+    """An attribute record that also answers like a dict: plug-ins written for the reference set attributes
+    (``ksana_python_input.input_tokens = ...``), the plug-ins of this package index (``inp["input_tokens"]``)."""
+
+    def __getitem__(self, key):
+        try:
+            return getattr(self, key)
+        except AttributeError:
+            raise KeyError(key) from None
+
+    def __setitem__(self, key, value):
+        setattr(self, key, value)
+
+    def __contains__(self, key):
+        return hasattr(self, key)
+
+    def get(self, key, default=None):
+        return getattr(self, key, default)
+
+    def setdefault(self, key, default=None):
+        if not hasattr(self, key):
+            setattr(self, key, default)
+        return getattr(self, key)
+
+
+class InputRefitEmbedding(_Record):
+    """Embeddings a plug-in splices over prompt positions: ``pos`` (start position of every piece), the pieces as
+    nested lists (``embeddings``) or tensors (``embedding_tensors``), and ``additional_tensors`` (multimodal rotary
+    positions [3, T] first), as in src/ksana_llm/python/ksana_plugin/qwen2_vl/ksana_plugin.py:128-135."""
+
+    def __init__(self, pos=None, embeddings=None):
+        self.pos = list(pos or [])
+        self.embeddings = embeddings if embeddings is not None else []
+        self.embedding_tensors = ()
+        self.additional_tensors = []
+
+    def pieces(self):
+        return self.embedding_tensors if len(self.embedding_tensors) else self.embeddings
+
+
+class KsanaPythonInput(_Record):
+    """What a plug-in's ``preprocess`` receives and may rewrite."""
+
+    def __init__(self, input_tokens=None, sampling_config=None, model_name: str = "", input_refit_embedding=None,
+                 structured_output_regex: str = "", additional_params=None, prompt=None):
+        self.model_name = model_name
+        self.input_tokens = list(input_tokens or [])
+        self.sampling_config = sampling_config
+        self.input_refit_embedding = input_refit_embedding or {}
+        self.structured_output_regex = structured_output_regex
+        self.additional_params = additional_params or {}
+        self.prompt = prompt
+
+    def __setattr__(self, key, value):
+        if key == "input_refit_embedding" and not isinstance(value, InputRefitEmbedding):
+            value = InputRefitEmbedding((value or {}).get("pos"), (value or {}).get("embeddings"))
+        object.__setattr__(self, key, value)
+
+
 @dataclass
 class KsanaPythonOutput:
     input_tokens: List[int] = field(default_factory=list)
@@ -305,23 +364,27 @@ class ServingModel:
         code, msg = sampling.verify_args()
         if code != 0:
             return Status(code, msg), None, None
-        ksana_input = {"input_tokens": list(inputs or []), "input_refit_embedding": kwargs.get("input_refit_embedding") or {},
-                       "additional_params": kwargs.get("additional_params") or {}, "prompt": kwargs.get("prompt")}
-        if self.plugin is not None:
+        ksana_input = KsanaPythonInput(inputs, sampling, kwargs.get("model_name") or "", kwargs.get("input_refit_embedding"),
+                                       kwargs.get("structured_output_regex") or "", kwargs.get("additional_params"),
+                                       kwargs.get("prompt"))
+        # a request that brings its own spliced embeddings is not pre-processed again (as in the reference)
+        if self.plugin is not None and not ksana_input.input_refit_embedding.pos:
             self.plugin.preprocess(ksana_python_input=ksana_input, messages=messages,
-                                   additional_params=ksana_input["additional_params"])
-        tokens = ksana_input["input_tokens"]
+                                   additional_params=ksana_input.additional_params, prompt=ksana_input.prompt or "")
+        tokens = list(ksana_input.input_tokens)
         if not tokens:
             return Status(1, "empty input tokens"), None, None
         refit = None
-        emb = ksana_input.get("input_refit_embedding") or {}
-        if emb.get("pos") and emb.get("embeddings") is not None:
-            embs = [torch.as_tensor(e, dtype=torch.float32) for e in emb["embeddings"]]
-            refit = (list(emb["pos"]), embs)
-        mrope = ksana_input.get("additional_tensors", {}).get("mrope_positions") if isinstance(ksana_input.get("additional_tensors"), dict) else None
+        emb = ksana_input.input_refit_embedding
+        if emb.pos and emb.pieces() is not None and len(emb.pieces()):
+            refit = (list(emb.pos), [torch.as_tensor(e, dtype=torch.float32) for e in emb.pieces()])
+        extra = ksana_input.get("additional_tensors")
+        mrope = extra.get("mrope_positions") if isinstance(extra, dict) else None
+        if mrope is None and len(emb.additional_tensors):
+            mrope = emb.additional_tensors[0]          # rotary positions [3, T] of a multimodal prompt
         span = ne.span_start("generate", (req_ctx or {}).get("traceparent", ""))
         req = self.llm.engine.add_request(tokens, sampling, stream=bool(streamer),
-                                          structured_regex=kwargs.get("structured_output_regex") or "",
+                                          structured_regex=ksana_input.structured_output_regex or "",
                                           refit=refit, mrope_positions=mrope, listener=listener)
         req.span_id = span
         if req.done.is_set() and req.status_code != 0:

@@ -156,7 +156,8 @@ def test_qwen_vl_first_generation_tower_and_spans():
 def test_plugin_written_for_the_reference_loads_unchanged(tmp_path):
     """A plug-in in the reference's style: it imports ``plugin_utils`` as a top-level module, a neighbour module by its
     folder name, expects ``config_file`` among the arguments of ``init_plugin`` and raises the reserved memory share in
-    that YAML. The host loads it, runs pre- and post-processing on its pool, and a broken plug-in only costs a warning."""
+    that YAML, and rewrites the request through attributes of the input object (tokens, spliced embeddings as
+    tensors). The host loads it, runs pre- and post-processing on its pool, and a broken plug-in only costs a warning."""
     from ksanallm_b200.serving.plugin import KsanaPlugin as PluginHost, PluginConfig
     pkg = tmp_path / "plugins" / "my_vl"
     pkg.mkdir(parents=True)
@@ -173,11 +174,16 @@ class KsanaPlugin:
         free_cache()
         adjust_device_memory_ratio(kwargs["config_file"], 0.04)
 
-    def preprocess(self, ksana_python_input, **kwargs):
-        ksana_python_input["input_tokens"] = [t * SCALE for t in ksana_python_input["input_tokens"]]
+    def preprocess(self, **kwargs):
+        import torch
+        ksana_python_input = kwargs["ksana_python_input"]
+        assert "messages" in kwargs and "additional_params" in kwargs and "prompt" in kwargs
+        ksana_python_input.input_tokens = [t * SCALE for t in ksana_python_input.input_tokens]
+        ksana_python_input.input_refit_embedding.pos = [1]
+        ksana_python_input.input_refit_embedding.embedding_tensors = torch.unbind(torch.full((1, 2, 64), 0.25))
 
-    def postprocess(self, ksana_python_input, ksana_python_output, **kwargs):
-        ksana_python_output["note"] = "post"
+    def postprocess(self, **kwargs):
+        kwargs["ksana_python_output"].output_tokens[0].append(4242)
 ''')
     yaml_path = tmp_path / "ksana_llm.yaml"
     yaml_path.write_text("setting:\n  block_manager:\n    # room for the tower\n    reserved_device_memory_ratio: 0.01   # share\n    block_token_num: 16\n")
@@ -192,12 +198,37 @@ class KsanaPlugin:
         assert host.loaded and host._plugin.seen["config_file"] == str(yaml_path) and host._plugin.seen["enable_trt"] is True
         text = yaml_path.read_text()
         assert "reserved_device_memory_ratio: 0.04   # share" in text and "# room for the tower" in text
-        inp = {"input_tokens": [1, 2, 3]}
-        host.preprocess(ksana_python_input=inp)
-        assert inp["input_tokens"] == [3, 6, 9]
-        out = {}
-        host.postprocess(ksana_python_input=inp, ksana_python_output=out)
-        assert out == {"note": "post"}
+        # through the serving model: the rewritten tokens and the spliced embeddings reach the engine, the answer
+        # passes through the post-processing
+        from ksanallm_b200.config import EngineConfig
+        from ksanallm_b200.llm import LLM
+        from ksanallm_b200.serving.serving_model import KsanaPythonInput, ServingModel
+        from ksanallm_b200.utils import native_engine as ne
+        inp = KsanaPythonInput([1, 2, 3])
+        host.preprocess(ksana_python_input=inp, messages=None, additional_params={}, prompt="")
+        assert inp.input_tokens == [3, 6, 9] and inp["input_tokens"] == [3, 6, 9] and inp.input_refit_embedding.pos == [1]
+        ec = EngineConfig()
+        ec.batch_scheduler.max_token_len = 64
+        ec.block_manager.device_blocks_num = 32
+        llm = LLM(ec, tiny_model_cfg(), weights="random", device="cpu", dtype=torch.float32, tokenizer=ByteTokenizer())
+        model = ServingModel("", llm=llm, tokenizer=ByteTokenizer())
+        model.init_serving()
+        model.plugin = host
+        try:
+            st, out = model.generate(inputs=[1, 2, 3], generation_config={"max_new_tokens": 3, "ignore_eos": True})
+            assert st.OK() and out.input_tokens == [3, 6, 9] and out.output_tokens[0][-1] == 4242
+            s = ne.SamplingConfig()
+            s.max_new_tokens, s.ignore_eos = 3, True
+            want = llm.engine.add_request([3, 6, 9], s, refit=([1], [torch.full((2, 64), 0.25)]))
+            assert want.done.wait(30) and out.output_tokens[0][:-1] == want.outputs[0].tokens
+            plain = llm.engine.add_request([3, 6, 9], s)
+            assert plain.done.wait(30)
+            # a request that brings its own embeddings is not pre-processed again
+            st, own = model.generate(inputs=[3, 6, 9], generation_config={"max_new_tokens": 3, "ignore_eos": True},
+                                     input_refit_embedding={"pos": [1], "embeddings": [torch.full((2, 64), 0.25).tolist()]})
+            assert st.OK() and own.input_tokens == [3, 6, 9] and own.output_tokens[0][:-1] == want.outputs[0].tokens
+        finally:
+            model.shutdown()
         # a larger value in the file is left alone; a plug-in that fails to import is skipped with a warning
         from ksanallm_b200.ksana_plugin.plugin_utils import adjust_device_memory_ratio
         assert adjust_device_memory_ratio(str(yaml_path), 0.02) is False
