@@ -67,6 +67,7 @@ class Request:
         self.aborted = False
         # /forward style extraction
         self.request_target: Optional[dict] = None
+        self.targets_done = False                        # the targets are taken from the prefill step, once
         self.response: Dict[str, torch.Tensor] = {}
         self.refit: Optional[tuple] = None               # (positions, embeddings)
         self.mrope_positions = None
@@ -637,7 +638,7 @@ class LLMEngine:
                         base = int(mp.max()) + 1 - mp.shape[1]
                         s2 = max(start, mp.shape[1])
                         mrope[:, row0 + s2 - start:row0 + ql] = torch.arange(s2, start + ql, dtype=torch.int32) + base
-                if req.request_target:
+                if req.request_target and not req.targets_done:
                     want_hidden = True
                     if "logits" in req.request_target:
                         full_logits.append([row0, ql])

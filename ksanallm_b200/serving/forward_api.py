@@ -66,8 +66,9 @@ def extract_targets(engine, plan, logits) -> None:
     for k, sid in enumerate(plan.seq_ids.tolist()):
         ql = int(plan.q_lens[k])
         ent = engine.seq_to_req.get(sid)
-        if ent is not None and ent[0].request_target:
+        if ent is not None and ent[0].request_target and not ent[0].targets_done:
             req = ent[0]
+            req.targets_done = True          # later (decode) steps of a generating request carry no prompt rows
             hidden_all = getattr(model, "step_hidden", None)
             for name, t in req.request_target.items():
                 pos = target_positions(t, len(req.prompt))

@@ -114,6 +114,7 @@ class KsanaPythonInput(_Record):
         self.sampling_config = sampling_config
         self.input_refit_embedding = input_refit_embedding or {}
         self.structured_output_regex = structured_output_regex
+        self.request_target = {}         # target name -> {"token_id" | "slice_pos", "token_reduce_mode"} (as /forward takes)
         self.additional_params = additional_params or {}
         self.prompt = prompt
 
@@ -129,6 +130,7 @@ class KsanaPythonOutput:
     output_tokens: List[List[int]] = field(default_factory=list)
     logprobs: List[list] = field(default_factory=list)
     response: Dict[str, Any] = field(default_factory=dict)
+    embedding: List[Any] = field(default_factory=list)
     finished: bool = False
 
 
@@ -355,7 +357,8 @@ class ServingModel:
             order = beam_final_order(outs, cfg.length_penalty)
             outs = [outs[i] for i in order][:max(cfg.num_return_sequences, 1)]
         return KsanaPythonOutput(input_tokens=list(req.prompt), output_tokens=[list(o.tokens) for o in outs],
-                                 logprobs=[list(o.logprobs) for o in outs], finished=req.all_finished())
+                                 logprobs=[list(o.logprobs) for o in outs], finished=req.all_finished(),
+                                 response=dict(req.response))
 
     def _submit(self, inputs, generation_config, streamer, messages, req_ctx, kwargs, listener=None):
         """Validation, the plug-in's preprocessing and the hand-over to the engine: (Status, request, plug-in input)."""
@@ -385,6 +388,7 @@ class ServingModel:
         span = ne.span_start("generate", (req_ctx or {}).get("traceparent", ""))
         req = self.llm.engine.add_request(tokens, sampling, stream=bool(streamer),
                                           structured_regex=ksana_input.structured_output_regex or "",
+                                          request_target=dict(ksana_input.request_target) or None,
                                           refit=refit, mrope_positions=mrope, listener=listener)
         req.span_id = span
         if req.done.is_set() and req.status_code != 0:

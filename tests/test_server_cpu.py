@@ -247,7 +247,8 @@ def test_streamed_outputs_pass_through_the_plugin():
         calls = 0
 
         def preprocess(self, **kw):
-            return None
+            # a plug-in may ask for tensors of the prompt as well (same target description as /forward takes)
+            kw["ksana_python_input"].request_target = {"layernorm": {"slice_pos": [[0, 1]], "token_reduce_mode": "GATHER_ALL"}}
 
         def postprocess(self, ksana_python_input, ksana_python_output, **kw):
             Marker.calls += 1
@@ -278,6 +279,7 @@ def test_streamed_outputs_pass_through_the_plugin():
             outs = asyncio.run(run(blocking_iterator))
             assert outs and all(o.output_tokens[0][-1] == 7777 for o in outs)
             assert len(outs[-1].output_tokens[0]) == 7
+            assert tuple(outs[-1].response["layernorm"].shape) == (2, 64)
     finally:
         model.shutdown()
     assert Marker.calls >= 2
