@@ -371,6 +371,9 @@ def test_import_compatibility_package():
     assert {"AutoModel", "EndpointConfig", "PluginConfig"} <= set(ksana_llm.__all__)
     assert ksana_llm.EndpointConfig().endpoint == "python" and ksana_llm.EndpointConfig(endpoint="trpc", port=9000).type == "trpc"
     assert ksana_llm.PluginConfig(thread_pool_size=4).thread_pool_size == 4
+    for bad in ("/no/such/file.yaml", __file__):               # missing, and not a YAML file
+        with pytest.raises(RuntimeError):
+            ksana_llm.AutoModel.from_config(bad)
 
 
 def test_lost_worker_rank_ends_the_service(tmp_path):
