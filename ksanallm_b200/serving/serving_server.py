@@ -26,6 +26,12 @@ from .plugin import PluginConfig
 from .serving_model import EndpointConfig, ServingModel
 
 TRACE_HEADERS = ("x-remote-ip", "traceparent")
+TIMEOUT_KEEP_ALIVE = 5          # seconds an idle client connection is kept open
+
+
+def _flag(text: str) -> bool:
+    """Boolean command-line value: "false", "0", "no" and "off" (any case) are False, everything else True."""
+    return str(text).strip().lower() not in ("false", "0", "no", "off", "")
 
 
 def args_config(argv=None):
@@ -34,8 +40,12 @@ def args_config(argv=None):
     p.add_argument("--tokenizer_dir", type=str, default=None, help="tokenizer dir (default: the model dir)")
     p.add_argument("--host", type=str, default="0.0.0.0")
     p.add_argument("--port", type=int, default=8080)
-    p.add_argument("--endpoint", type=str, default="python", help="server endpoint type")
-    p.add_argument("--access-log", action=argparse.BooleanOptionalAction, default=True)
+    p.add_argument("--endpoint", type=str, default=None,
+                   help="server endpoint type (python, or the name of an RPC endpoint plug-in); default: the YAML's "
+                        "setting.endpoint_type, else python")
+    p.add_argument("--access-log", nargs="?", const=True, default=True, type=_flag,
+                   help="endpoint access log: --access-log, --access-log false, --no-access-log")
+    p.add_argument("--no-access-log", dest="access_log", action="store_false")
     p.add_argument("--ssl-keyfile", type=str, default=None)
     p.add_argument("--ssl-certfile", type=str, default=None)
     p.add_argument("--root-path", type=str, default=None)
@@ -60,7 +70,9 @@ def prepare_config(args):
     plugin = (doc.get("model_spec") or {}).get("plugin_model") or {}
     args.plugin_enable_trt = bool(plugin.get("enable_tensorrt", True))
     args.plugin_thread_pool_size = int(plugin.get("plugin_thread_pool_size", 1))
-    args.endpoint = (doc.get("setting") or {}).get("endpoint_type", args.endpoint)
+    if args.endpoint is None:                  # the command line wins over the YAML
+        args.endpoint = (doc.get("setting") or {}).get("endpoint_type") or "python"
+    args.endpoint = str(args.endpoint).lower()
     args.model_type = ""
     cfg_path = os.path.join(model_dir, "config.json")
     if os.path.exists(cfg_path):
@@ -250,7 +262,8 @@ def main(argv=None):
         log_level = "info"
     try:
         uvicorn.run(app, host=args.host, port=args.port, log_level=log_level, access_log=args.access_log,
-                    ssl_keyfile=args.ssl_keyfile, ssl_certfile=args.ssl_certfile, root_path=args.root_path or "")
+                    timeout_keep_alive=TIMEOUT_KEEP_ALIVE, ssl_keyfile=args.ssl_keyfile, ssl_certfile=args.ssl_certfile,
+                    root_path=args.root_path or "")
     finally:
         model.shutdown()
 

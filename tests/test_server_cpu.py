@@ -283,3 +283,18 @@ def test_streamed_outputs_pass_through_the_plugin():
     finally:
         model.shutdown()
     assert Marker.calls >= 2
+
+
+def test_server_command_line_rules(tmp_path):
+    """--endpoint on the command line wins over the YAML's endpoint_type (which wins over "python"); the access log
+    flag takes the forms launch scripts of the reference use."""
+    from ksanallm_b200.serving.serving_server import args_config
+    y = tmp_path / "c.yaml"
+    y.write_text("setting:\n  endpoint_type: TRPC\nmodel_spec:\n  base_model:\n    model_dir: /tmp/none\n")
+    a = args_config(["--config_file", str(y)])
+    assert a.endpoint == "trpc" and a.access_log is True and a.tokenizer_dir == a.model_dir
+    a = args_config(["--config_file", str(y), "--endpoint", "Python", "--access-log", "False"])
+    assert a.endpoint == "python" and a.access_log is False
+    assert args_config(["--config_file", str(y), "--no-access-log"]).access_log is False
+    y.write_text("model_spec:\n  base_model:\n    model_dir: /tmp/none\n")
+    assert args_config(["--config_file", str(y)]).endpoint == "python"
