@@ -260,6 +260,7 @@ class ServingModel:
         self.llm = llm
         self.tokenizer = tokenizer
         self.plugin: Optional[KsanaPlugin] = None
+        self._stopped = threading.Event()
         self.endpoint_config = EndpointConfig()
         self.model_cfg = llm.model_cfg if llm is not None else None
 
@@ -340,7 +341,12 @@ class ServingModel:
         if rc != 0:
             raise RuntimeError(f"endpoint plug-in {self.rpc_endpoint.path} failed to start (code {rc})")
 
+    def wait_for_shutdown(self, timeout: Optional[float] = None) -> bool:
+        """Blocks until :meth:`shutdown` has run (the process of an RPC endpoint has nothing else to do)."""
+        return self._stopped.wait(timeout)
+
     def shutdown(self):
+        self._stopped.set()
         ep = getattr(self, "rpc_endpoint", None)
         if ep is not None:
             self.rpc_endpoint = None

@@ -248,10 +248,20 @@ def main(argv=None):
     rank = int(os.environ.get("RANK", "0"))
     node_rank = int(os.environ.get("NODE_RANK", "0"))
     if rank != 0 or node_rank != 0:
+        print("Uvicorn running on NONE.", flush=True)      # the line launch scripts wait for, from a rank without a port
         while model.llm.follow():      # worker ranks: execute broadcast step plans until the stop signal
             pass
         if getattr(model.llm, "coordinator", None) is not None:
             model.llm.coordinator.close()
+        return
+    if args.endpoint != "python":
+        # an RPC endpoint plug-in serves on the configured host and port itself: no HTTP front beside it
+        import signal
+        for sig in (signal.SIGTERM, signal.SIGINT):
+            signal.signal(sig, lambda *_: model.shutdown())
+        logger.info(f"endpoint {args.endpoint} serving on {args.host}:{args.port}")
+        while not model.wait_for_shutdown(1.0):
+            pass
         return
     import uvicorn
     app = create_app(model, tokenizer)

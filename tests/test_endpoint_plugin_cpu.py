@@ -77,5 +77,7 @@ def test_serving_model_starts_the_named_endpoint(plugin_dir):
     assert lib.echo_last_status() == 200
     body = json.loads(lib.echo_last_reply().decode())
     assert body["input_token_ids"] == [1, 5, 6, 7] and len(body["output_token_ids"][0]) == 4
+    assert not model.wait_for_shutdown(0)
     lib.echo_request_shutdown()                      # the plug-in lost its peer: it asks the service to stop
     assert lib.echo_stopped() == 1 and model.rpc_endpoint is None
+    assert model.wait_for_shutdown(0)                # what the server process of an RPC endpoint waits for
