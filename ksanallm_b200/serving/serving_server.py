@@ -1,5 +1,6 @@
 """HTTP front: ``POST /generate`` (JSON in; JSON out, or a stream of JSON chunks each terminated by a
-zero byte) and ``POST /forward`` (msgpack in / out), plus ``GET /metrics`` (Prometheus text).
+zero byte) and ``POST /forward`` (msgpack in / out), plus ``GET /metrics`` (Prometheus text) and OpenAI-style
+``/v1/completions``, ``/v1/chat/completions`` and ``/v1/models``.
 
 Request / response fields, the chunk framing and the HTTP 500 ``{"message", "code"}`` error body follow
 src/ksana_llm/python/serving_server.py:41-449. Only node rank 0 serves HTTP; other ranks follow the
@@ -223,6 +224,140 @@ def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExec
             return Response(content=response_bytes, media_type="application/x-msgpack")
         err = msgpack.packb({"message": status.GetMessage(), "code": status.GetCode().value})
         return Response(content=err, status_code=500, media_type="application/x-msgpack")
+
+    # ------------------------------------------------------------------ OpenAI-style routes
+    # /v1/completions, /v1/chat/completions (blocking and server-sent events) and /v1/models over the same engine
+    # path as /generate. The reference's server takes OpenAI-style ``messages`` in /generate only; these routes are
+    # for clients that speak the OpenAI wire format itself.
+    served_name = os.path.basename(os.path.normpath(getattr(model.llm.engine_cfg, "model_dir", "") or "")) or "ksana_llm"
+
+    def openai_error(message: str, status: int = 400, kind: str = "invalid_request_error"):
+        return JSONResponse({"error": {"message": message, "type": kind, "param": None, "code": None}}, status_code=status)
+
+    def openai_sampling(body: dict, default_max: int) -> dict:
+        temperature = body.get("temperature")
+        temperature = 1.0 if temperature is None else float(temperature)
+        greedy = temperature <= 0.0
+        stop = body.get("stop") or []
+        stop = [stop] if isinstance(stop, str) else list(stop)
+        max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or body.get("max_new_tokens") or default_max
+        sc = {"topk": 1 if greedy else int(body.get("top_k") or 50), "temperature": 1.0 if greedy else temperature,
+              "topp": float(body.get("top_p") or 1.0), "max_new_tokens": int(max_tokens),
+              "num_return_sequences": int(body.get("n") or 1), "stop_strings": stop,
+              "repetition_penalty": float(body.get("repetition_penalty") or 1.0), "seed": int(body.get("seed") or 0),
+              "ignore_eos": bool(body.get("ignore_eos", False)), "do_sample": not greedy,
+              "stop_token_ids": [int(t) for t in (body.get("stop_token_ids") or [])]}
+        return _sampling_dict(sc, tokenizer)
+
+    async def openai_generate(kind: str, body: dict, input_tokens: List[int], req_ctx: Dict[str, str]):
+        import time as _time
+        import uuid
+        gen = openai_sampling(body, 16 if kind == "text_completion" else 1024)
+        stream = bool(body.get("stream", False))
+        rid = ("cmpl-" if kind == "text_completion" else "chatcmpl-") + uuid.uuid4().hex[:24]
+        created = int(_time.time())
+        name = body.get("model") or served_name
+        status, result = await model.generate_async(model_name=name, inputs=input_tokens, generation_config=gen,
+                                                    streamer=True if stream else None, req_ctx=req_ctx, executor=executor,
+                                                    prompt=body.get("prompt") if isinstance(body.get("prompt"), str) else None,
+                                                    **({"structured_output_regex": body["structured_output_regex"]}
+                                                       if body.get("structured_output_regex") else {}))
+        if not status.OK():
+            return openai_error(status.GetMessage(), 400 if status.GetCode().value == 1 else 500,
+                                "invalid_request_error" if status.GetCode().value == 1 else "server_error")
+
+        def finish_reason(tokens) -> str:
+            return "length" if len(tokens) >= gen["max_new_tokens"] else "stop"
+
+        def choice(i: int, text: str, reason, delta: bool):
+            if kind == "text_completion":
+                return {"index": i, "text": text, "logprobs": None, "finish_reason": reason}
+            key = "delta" if delta else "message"
+            msg = {"content": text} if delta else {"role": "assistant", "content": text}
+            return {"index": i, key: msg, "logprobs": None, "finish_reason": reason}
+
+        if not stream:
+            texts = [_decode(tokenizer, t) for t in result.output_tokens]
+            n_out = sum(len(t) for t in result.output_tokens)
+            return JSONResponse({
+                "id": rid, "object": kind if kind == "text_completion" else "chat.completion", "created": created, "model": name,
+                "choices": [choice(i, texts[i], finish_reason(result.output_tokens[i]), False) for i in range(len(texts))],
+                "usage": {"prompt_tokens": len(result.input_tokens), "completion_tokens": n_out,
+                          "total_tokens": len(result.input_tokens) + n_out}})
+
+        obj = "text_completion" if kind == "text_completion" else "chat.completion.chunk"
+
+        async def events():
+            sent: Dict[int, str] = {}
+            last = None
+            try:
+                if kind != "text_completion":
+                    first = {"id": rid, "object": obj, "created": created, "model": name,
+                             "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]}
+                    yield b"data: " + json.dumps(first).encode() + b"\n\n"
+                async for out in result:
+                    last = out
+                    choices = []
+                    for i, toks in enumerate(out.output_tokens):
+                        text = _decode(tokenizer, toks, True)
+                        piece = text[len(sent.get(i, "")):]
+                        if piece:
+                            sent[i] = text
+                            choices.append(choice(i, piece, None, True))
+                    if choices:
+                        chunk = {"id": rid, "object": obj, "created": created, "model": name, "choices": choices}
+                        yield b"data: " + json.dumps(chunk).encode() + b"\n\n"
+                if last is not None:
+                    # what the per-step decoding held back (an incomplete character at the tail) goes out with the end
+                    tails = []
+                    for i, t in enumerate(last.output_tokens):
+                        full = _decode(tokenizer, t)
+                        tails.append(full[len(sent.get(i, "")):] if full.startswith(sent.get(i, "")) else "")
+                    n_out = sum(len(t) for t in last.output_tokens)
+                    final = {"id": rid, "object": obj, "created": created, "model": name,
+                             "choices": [choice(i, tails[i], finish_reason(t), True) for i, t in enumerate(last.output_tokens)],
+                             "usage": {"prompt_tokens": len(last.input_tokens), "completion_tokens": n_out,
+                                       "total_tokens": len(last.input_tokens) + n_out}}
+                    yield b"data: " + json.dumps(final).encode() + b"\n\n"
+                yield b"data: [DONE]\n\n"
+            finally:
+                result.close()
+        return StreamingResponse(events(), media_type="text/event-stream")
+
+    @app.get("/v1/models")
+    async def openai_models():
+        return JSONResponse({"object": "list", "data": [{"id": served_name, "object": "model", "owned_by": "ksana_llm"}]})
+
+    @app.post("/v1/completions")
+    async def openai_completions(request: Request):
+        body = await request.json()
+        prompt = body.get("prompt")
+        if isinstance(prompt, list) and prompt and all(isinstance(t, int) for t in prompt):
+            tokens = [int(t) for t in prompt]
+        elif isinstance(prompt, list) and len(prompt) == 1 and isinstance(prompt[0], str):
+            prompt = prompt[0]
+            tokens = None
+        elif isinstance(prompt, str):
+            tokens = None
+        else:
+            return openai_error("prompt must be a string, a list with one string, or a list of token ids")
+        if tokens is None:
+            if tokenizer is None:
+                return openai_error("this server has no tokenizer: send the prompt as a list of token ids")
+            tokens = tokenizer.encode(prompt, add_special_tokens=True)
+        return await openai_generate("text_completion", body, tokens, trace_ctx(request))
+
+    @app.post("/v1/chat")                    # the path the benchmark client's "ksana-server" / "vllm-server" backends use
+    @app.post("/v1/chat/completions")
+    async def openai_chat(request: Request):
+        body = await request.json()
+        messages = body.get("messages")
+        if not isinstance(messages, list) or not messages:
+            return openai_error("messages must be a non-empty list")
+        tokens = render_messages(messages)
+        if tokens is None:
+            return openai_error("this server's tokenizer has no chat template")
+        return await openai_generate("chat.completion", body, tokens, trace_ctx(request))
 
     @app.get("/metrics")
     async def metrics():

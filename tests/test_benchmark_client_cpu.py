@@ -309,3 +309,18 @@ def test_client_speaks_other_backends(foreign_servers, tmp_path, backend, stream
         assert seen["trt-llm"]["text_input"] in ("what is this", "and that") and "tok tok tok" in text
     else:
         assert seen["chat"]["messages"][0]["role"] == "user" and "Hello you" in text
+
+
+@pytest.mark.parametrize("stream", [False, True])
+def test_client_chat_server_backend_against_this_server(server, tmp_path, stream):
+    """The client's chat-server format (``--backend ksana-server``: OpenAI-style body to /v1/chat, usage counts and
+    server-sent events in the answer) against this package's own server."""
+    csv_path = tmp_path / "prompts.csv"
+    csv_path.write_text("prompt\nhello there\nsecond prompt\nthird one\n", encoding="utf-8")
+    args = bt.args_config(["--port", str(server), "--backend", "ksana-server", "--input_csv", str(csv_path), "--max_new_tokens", "5",
+                           "--client_timeout", "60", "--ignore_eos"] +
+                          (["--stream", "--request_rate", "50"] if stream else ["--mode", "sync", "--concurrency", "2"]))
+    s = bt.run_benchmark(args)[0]
+    assert s["finished"] == 3 and s["failed"] == 0 and s["avg_output_tokens"] == 5
+    if stream:
+        assert s["avg_ttft_s"] > 0

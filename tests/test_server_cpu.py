@@ -298,3 +298,42 @@ def test_server_command_line_rules(tmp_path):
     assert args_config(["--config_file", str(y), "--no-access-log"]).access_log is False
     y.write_text("model_spec:\n  base_model:\n    model_dir: /tmp/none\n")
     assert args_config(["--config_file", str(y)]).endpoint == "python"
+
+
+def test_openai_style_routes(client):
+    """/v1/models, /v1/completions and /v1/chat/completions: blocking answers with usage counts, greedy at temperature
+    0 (equal to /generate's greedy tokens), n choices, server-sent events whose deltas add up to the blocking text."""
+    assert client.get("/v1/models").json()["data"][0]["object"] == "model"
+    greedy = client.post("/generate", json={"prompt": "hello", "stream": False,
+                                            "sampling_config": {"max_new_tokens": 6}}).json()
+    r = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 6, "temperature": 0})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    assert body["object"] == "text_completion" and body["id"].startswith("cmpl-") and len(body["choices"]) == 1
+    assert body["choices"][0]["text"] == greedy["texts"][0]
+    assert body["usage"] == {"prompt_tokens": len(greedy["input_token_ids"]), "completion_tokens": len(greedy["output_token_ids"][0]),
+                             "total_tokens": len(greedy["input_token_ids"]) + len(greedy["output_token_ids"][0])}
+    assert body["choices"][0]["finish_reason"] in ("length", "stop")
+    # token ids as the prompt, three sampled choices
+    r = client.post("/v1/completions", json={"prompt": greedy["input_token_ids"], "max_tokens": 4, "n": 3, "seed": 5,
+                                             "ignore_eos": True})
+    assert r.status_code == 200 and [c["index"] for c in r.json()["choices"]] == [0, 1, 2]
+    assert r.json()["usage"]["completion_tokens"] == 12
+    # chat: blocking, then the same request streamed
+    req = {"messages": [{"role": "user", "content": "hi there"}], "max_tokens": 8, "temperature": 0, "ignore_eos": True}
+    chat = client.post("/v1/chat/completions", json=req).json()
+    assert chat["object"] == "chat.completion" and chat["choices"][0]["message"]["role"] == "assistant"
+    assert chat["choices"][0]["finish_reason"] == "length" and chat["usage"]["completion_tokens"] == 8
+    with client.stream("POST", "/v1/chat/completions", json=dict(req, stream=True)) as resp:
+        assert resp.headers["content-type"].startswith("text/event-stream")
+        raw = b"".join(resp.iter_bytes()).decode()
+    events = [e[len("data: "):] for e in raw.split("\n\n") if e.startswith("data: ")]
+    assert events[-1] == "[DONE]"
+    chunks = [json.loads(e) for e in events[:-1]]
+    assert all(c["object"] == "chat.completion.chunk" for c in chunks) and chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"])
+    assert text == chat["choices"][0]["message"]["content"] and chunks[-1]["choices"][0]["finish_reason"] == "length"
+    # errors in the OpenAI shape
+    bad = client.post("/v1/completions", json={"prompt": {"not": "a prompt"}})
+    assert bad.status_code == 400 and bad.json()["error"]["type"] == "invalid_request_error"
+    assert client.post("/v1/chat/completions", json={"messages": []}).status_code == 400
