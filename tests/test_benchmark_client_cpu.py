@@ -152,6 +152,12 @@ def test_command_line_clients_against_live_server(server, capsys):
             assert mod.main(["--host", "127.0.0.1", "--port", str(server), "--prompt", "hello there"] + extra) == 0
         out = capsys.readouterr().out
         assert ("Answer 0" in out) if name == "api_client" else ("[" in out)
+    spec = importlib.util.spec_from_file_location("openai_client", os.path.join(root, "examples", "openai_client.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    for extra in ([], ["--stream"]):
+        assert mod.main(["--host", "127.0.0.1", "--port", str(server), "--max_tokens", "5", "hello there"] + extra) == 0
+    capsys.readouterr()
     # the concurrent example client beside the 7B sample configuration (examples/llama7b/serving_client.py)
     spec = importlib.util.spec_from_file_location("llama7b_client", os.path.join(root, "examples", "llama7b", "serving_client.py"))
     mod = importlib.util.module_from_spec(spec)
