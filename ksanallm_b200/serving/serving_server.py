@@ -263,8 +263,12 @@ def create_app(model: ServingModel, tokenizer, executor: Optional[ThreadPoolExec
                                                     **({"structured_output_regex": body["structured_output_regex"]}
                                                        if body.get("structured_output_regex") else {}))
         if not status.OK():
-            return openai_error(status.GetMessage(), 400 if status.GetCode().value == 1 else 500,
-                                "invalid_request_error" if status.GetCode().value == 1 else "server_error")
+            code = status.GetCode().value
+            if code in (1, 6):            # a bad argument, a prompt beyond the model's length: the client's to fix
+                return openai_error(status.GetMessage(), 400, "invalid_request_error")
+            if code in (5, 7):            # waiting queue full, waited too long: try again later
+                return openai_error(status.GetMessage(), 503, "server_overloaded")
+            return openai_error(status.GetMessage(), 500, "server_error")
 
         def finish_reason(tokens) -> str:
             return "length" if len(tokens) >= gen["max_new_tokens"] else "stop"

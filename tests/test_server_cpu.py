@@ -337,3 +337,5 @@ def test_openai_style_routes(client):
     bad = client.post("/v1/completions", json={"prompt": {"not": "a prompt"}})
     assert bad.status_code == 400 and bad.json()["error"]["type"] == "invalid_request_error"
     assert client.post("/v1/chat/completions", json={"messages": []}).status_code == 400
+    long_prompt = client.post("/v1/completions", json={"prompt": [5] * 500, "max_tokens": 2})        # the model takes 128
+    assert long_prompt.status_code == 400 and long_prompt.json()["error"]["type"] == "invalid_request_error"
